@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("gemv_sweep_llama3_8b", BASELINE.json configs[1]): one step is one pass over the Llama-3-8B
+projection shapes (K->N: 4096->4096, 4096->1024, 4096->14336, 14336->4096, 4096->128256) x {Q4_K, Q6_K,
+Q8_0} x batch {1, 2, 4, 8}: 60 activation-quantize + GEMV pairs.  Weights are seeded synthetic GGUF blocks
+(candle_b200/synth.py), activations N(0, 1).
+
+Metric: achieved HBM bandwidth in GB/s = algorithmic bytes of the step (weights once + f32 activations in +
+f32 outputs, per GEMV) / device time of the step.
+  value     : inputs resident in HBM, the step replayed as one CUDA graph, CUDA-event timed.
+  e2e       : the same step through the public API (QMatMul.forward) with activations starting in pinned host
+              memory and results copied back to pinned host memory inside the timed region.
+  roofline  : the GEMV kernels alone (no quantize launches), CUDA-event timed in this run.
+  cpu_baseline : the reference's CPU algorithm (oracle port, AVX2, all host cores) on a bounded sample.
+
+With N > 1 GPUs (torchrun) every weight matrix is sharded by output rows over the ranks (column-parallel);
+each rank runs its slice and the slices are all-gathered over NCCL.  Total work is fixed: "strong" scaling.
+
+`--impl reference` times the reference's CPU implementation of the path (the oracle port) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096), (4096, 128256)]   # (K, N)
+TYPE_NAMES = ["Q4K", "Q6K", "Q8_0"]
+BATCHES = [1, 2, 4, 8]
+BYTES_PER_ELEM = {"Q4K": 144 / 256, "Q6K": 210 / 256, "Q8_0": 34 / 32, "Q4_0": 18 / 32}
+METRIC = "qmatmul_gemv_hbm_bandwidth"
+UNIT = "GB/s"
+
+
+def gemv_bytes(tname: str, k: int, n: int, b: int) -> float:
+    """Algorithmic bytes of one GEMV: weights once, f32 activations in, f32 outputs out."""
+    return n * k * BYTES_PER_ELEM[tname] + b * k * 4 + b * n * 4
+
+
+def step_bytes(batches=BATCHES) -> float:
+    return sum(gemv_bytes(t, k, n, b) for b in batches for t in TYPE_NAMES for (k, n) in SHAPES)
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()      # the exact process started above
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        hi = [v for v in sm if v >= 0.5 * (mx[0] if mx else 0)] or sm
+        return {"sm_mhz": hi[len(hi) // 2] if hi else None, "sm_max_mhz": mx[0] if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU algorithm (oracle port) on the host cores
+# --------------------------------------------------------------------------------------------------
+def cpu_sample_setup(seed=0):
+    """Bounded sample of the workload for the CPU legs: batch 1 over the fifteen matrices, except that the
+    128256-row head is cut to its first 16032 rows (1/8) so one pass stays within seconds on a few cores."""
+    import numpy as np
+    from oracle import oracle as O
+    rng = np.random.default_rng(seed)
+    items = []
+    for t in TYPE_NAMES:
+        dt = getattr(O, t)
+        for (k, n) in SHAPES:
+            n_s = n // 8 if n > 100000 else n
+            rb = O.row_bytes(dt, k)
+            w = rng.integers(0, 256, size=(n_s, rb), dtype=np.uint8)
+            # plausible f16 scales so the arithmetic stays finite
+            blk = w.reshape(n_s * (k // O.BLOCK_SIZE[dt]), O.TYPE_SIZE[dt])
+            for off in ({O.Q4K: (0, 2), O.Q6K: (208,), O.Q8_0: (0,)}[dt]):
+                blk[:, off:off + 2] = np.full((blk.shape[0],), 1e-3, dtype=np.float16).view(np.uint8).reshape(-1, 2)
+            x = rng.standard_normal((1, k)).astype(np.float32)
+            items.append((t, dt, k, n_s, w, x))
+    nbytes = sum(gemv_bytes(t, k, n_s, 1) for (t, _, k, n_s, _, _) in items)
+    return items, nbytes
+
+
+def cpu_sample_run(items):
+    from oracle import oracle as O
+    for (_, dt, k, n_s, w, x) in items:
+        O.matmul(dt, x, w, n_s, mode=O.SIMD_HW if O.lib().cqo_have_avx2() else O.SIMD_ORDER, nthreads=0)
+
+
+SAMPLE_DESC = ("batch 1 over the 15 (type, shape) matrices of the sweep, head matrix cut to 16032 of 128256 rows; "
+               "k_quants::matmul restated in C with AVX2 dots, all host cores")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    items, nbytes = cpu_sample_setup()
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_sample_run(items)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_sample_run(items)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = nbytes / dt / 1e9
+    cores = O.num_cores()
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 dot products, f32 accumulation", "data": "synthetic",
+        "config": {"workload": "gemv_sweep_llama3_8b", "types": TYPE_NAMES, "shapes_k_n": SHAPES, "batches": BATCHES},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": SAMPLE_DESC},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from candle_b200 import capi
+    from candle_b200.quantized import GgmlDType, QMatMul
+    from candle_b200.synth import random_qtensor
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    L = capi.lib()
+
+    # ---- resident inputs: each rank holds rows [rank*N/g, (rank+1)*N/g) of every matrix
+    mats = {}
+    for ti, t in enumerate(TYPE_NAMES):
+        for si, (k, n) in enumerate(SHAPES):
+            assert n % world == 0
+            qt = random_qtensor(GgmlDType[t], n // world, k, seed=1000 * ti + 10 * si + rank, device=dev)
+            mats[(t, k, n)] = QMatMul.from_qtensor(qt)
+    xs = {(k, b): torch.randn((b, k), device=dev, generator=torch.Generator(device=dev).manual_seed(k + b))
+          for (k, _) in SHAPES for b in BATCHES}
+    outs = {(n, b): torch.empty((b, n // world), device=dev) for (_, n) in SHAPES for b in BATCHES}
+    gathered = {(n, b): torch.empty((world, b, n // world), device=dev) for (_, n) in SHAPES for b in BATCHES} if world > 1 else None
+    order = [(b, t, k, n) for b in BATCHES for t in TYPE_NAMES for (k, n) in SHAPES]
+    total_bytes = step_bytes()
+
+    def step_full():
+        for (b, t, k, n) in order:
+            mats[(t, k, n)].forward(xs[(k, b)], out=outs[(n, b)])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[(n, b)], outs[(n, b)])
+
+    # pre-quantized activations for the GEMV-only (roofline) pass
+    kp = {k: capi.pad(k, 512) for (k, _) in SHAPES}
+    q8 = {}
+    for (k, b), x in xs.items():
+        y = torch.empty((b, kp[k] // 32 * 36), dtype=torch.uint8, device=dev)
+        L.cq_quantize_act(x.data_ptr(), capi.F32, y.data_ptr(), k, kp[k], b, capi.ACT_Q8_1, torch.cuda.current_stream().cuda_stream)
+        q8[(k, b)] = y
+    capi.check("bench setup")
+
+    def step_gemv_only():
+        s = torch.cuda.current_stream().cuda_stream
+        for (b, t, k, n) in order:
+            L.cq_mmvq(int(GgmlDType[t]), capi.ACT_Q8_1, capi.F32, mats[(t, k, n)].qtensor.device_ptr(), q8[(k, b)].data_ptr(),
+                      outs[(n, b)].data_ptr(), k, n // world, kp[k] // 32, n // world, b, s)
+
+    def timed(fn, steps, warmup, use_graph):
+        """CUDA-event time of `steps` calls of fn after `warmup` calls; barrier + synchronize on both sides."""
+        side = torch.cuda.Stream(device=dev)
+        graph = None
+        with torch.cuda.stream(side):
+            for _ in range(max(warmup, 3)):
+                fn()
+            side.synchronize()
+            if use_graph:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    fn()
+                graph.replay()
+                side.synchronize()
+        run = graph.replay if graph is not None else fn
+        with torch.cuda.stream(side):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(steps):
+                run()
+            e1.record(side)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    use_graph = world == 1     # NCCL collectives are launched eagerly
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(step_full, args.steps, args.warmup, use_graph)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_gemv = timed(step_gemv_only, args.steps, args.warmup, use_graph)
+
+    # ---- e2e: host activations -> device, QMatMul.forward, result -> host, all inside the timed region
+    h_x = {key: x.cpu().pin_memory() for key, x in xs.items()}
+    h_y = {key: torch.empty((key[1], key[0]), dtype=torch.float32).pin_memory() for key in
+           {(n, b) for (_, n) in SHAPES for b in BATCHES}}
+    d_x = {key: torch.empty_like(x) for key, x in xs.items()}
+    h2d = sum(b * k * 4 for (b, _, k, _) in order)
+    d2h = sum(b * n * 4 for (b, _, _, n) in order)
+
+    def step_e2e():
+        for (b, t, k, n) in order:
+            d_x[(k, b)].copy_(h_x[(k, b)], non_blocking=True)
+            y = mats[(t, k, n)].forward(d_x[(k, b)], out=outs[(n, b)])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[(n, b)], y)
+                h_y[(n, b)].view(b, world, n // world).copy_(gathered[(n, b)].permute(1, 0, 2), non_blocking=True)
+            else:
+                h_y[(n, b)].copy_(y, non_blocking=True)
+
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, False)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak_gbs()
+    value = total_bytes / ms_step / 1e6
+    gemv_gbs = total_bytes / ms_gemv / 1e6
+    result = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 dot products, f32 accumulation", "data": "synthetic",
+        "config": {"workload": "gemv_sweep_llama3_8b", "types": TYPE_NAMES, "shapes_k_n": SHAPES, "batches": BATCHES,
+                   "gemv_per_step": len(order), "bytes_per_step": total_bytes,
+                   "l2": "1.6 GB of distinct weights are streamed between two uses of the same matrix (L2 is 126 MB)",
+                   "parallelism": f"column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU",
+                   "launch": "CUDA graph replay" if use_graph else "eager launches"},
+        "frac_of_8TBps_nominal_per_gpu": value / world / 8000.0,
+        "gpu_launches": 2 * len(order) * args.steps,
+        "e2e": {"value": total_bytes / ms_e2e / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e},
+        "roofline": {"bound": "hbm", "achieved": gemv_gbs / world, "peak": peak, "unit": "GB/s",
+                     "frac": gemv_gbs / world / peak, "traffic": None, "peak_source": peak_src,
+                     "kernel": "gemv_staged_kernel (all 60 GEMV launches of the step, quantize launches excluded)",
+                     "ms_per_step": ms_gemv, "per_gpu": True},
+        "clocks": clocks,
+    }
+    if world == 1:
+        from oracle import oracle as O
+        items, nbytes = cpu_sample_setup()
+        cpu_sample_run(items)
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 3 or (time.perf_counter() - t0 < 10 and reps < 50):
+            cpu_sample_run(items)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        result["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": O.num_cores(), "kind": "port",
+                                  "sample": SAMPLE_DESC + f"; {reps} passes"}
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,89 @@
+"""ctypes binding of libcandle_q_b200.so (the C ABI declared in include/candle_q_b200.h).
+
+Loading fails loudly when the shared library has not been built: there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libcandle_q_b200.so")
+
+# GGML type ids / element kinds / activation encodings (include/candle_q_b200.h)
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+F32, F16, BF16 = 0, 1, 2
+ACT_Q8_1, ACT_Q8_0, ACT_Q8_K = 0, 1, 2
+
+TYPE_SIZE = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210}
+BLOCK_ELEMS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256}
+TYPE_NAME = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k"}
+ELEM_NAME = {F32: "f32", F16: "f16", BF16: "bf16"}
+
+STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "device-side timeout"}
+
+
+class CandleQError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded shared library.  Raises if it is missing (build it with candle_b200/build.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise CandleQError(
+                f"{LIB_PATH} is missing: build it with `python -m candle_b200.build` "
+                "(nvcc, sm_100a).  There is no CPU or PyTorch fallback for this path.")
+        L = C.CDLL(LIB_PATH)
+        vp, i32 = C.c_void_p, C.c_int
+        L.cq_last_status.restype = i32
+        L.cq_last_cuda_error.restype = i32
+        L.cq_last_message.restype = C.c_char_p
+        L.cq_version.restype = C.c_char_p
+        L.cq_quantize_act.argtypes = [vp, i32, vp, i32, i32, i32, i32, vp]
+        L.cq_mmvq.argtypes = [i32, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.cq_block_dots.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, vp]
+        L.cq_set_tuning.argtypes = [i32, i32]
+        for el in ELEM_NAME.values():
+            getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]
+            for t in TYPE_NAME.values():
+                getattr(L, f"launch_mmvq_gguf_{t}_{el}_plain").argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        i64p, sz = C.POINTER(C.c_int64), C.c_size_t
+        L.cqh_last_error.restype = C.c_char_p
+        L.cqh_qtensor_load.argtypes = [i32, vp, sz, i64p, i32, i32, C.POINTER(vp)]
+        L.cqh_qtensor_wrap.argtypes = [i32, vp, sz, i64p, i32, i32, C.POINTER(vp)]
+        L.cqh_qtensor_free.argtypes = [vp]
+        L.cqh_qtensor_free.restype = None
+        L.cqh_qtensor_data.argtypes = [vp, vp, sz]
+        L.cqh_qtensor_device_ptr.argtypes = [vp]
+        L.cqh_qtensor_device_ptr.restype = vp
+        L.cqh_qmatmul_forward.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
+        L.cqh_set_act_mode.argtypes = [i32]
+        L.cqh_get_act_mode.restype = i32
+        L.cqh_workspace_reserve.argtypes = [i32, sz]
+        _lib = L
+    return _lib
+
+
+def hcheck(rc: int, what: str = "") -> None:
+    """Raise the error text of a failed cqh_* call."""
+    if rc != 0:
+        raise CandleQError(f"{what}: {lib().cqh_last_error().decode()}" if what else lib().cqh_last_error().decode())
+
+
+def check(what: str = "") -> None:
+    """Raise if the library recorded a failure since the last clear."""
+    L = lib()
+    st = L.cq_last_status()
+    if st != 0:
+        msg = L.cq_last_message().decode()
+        L.cq_clear_status()
+        raise CandleQError(f"{what}: {STATUS.get(st, st)}: {msg}")
+
+
+def pad(p: int, q: int) -> int:
+    return (p + q - 1) // q * q

@@ -1,0 +1,129 @@
+// Shared device/host helpers for the B200 (sm_100a) GGUF quantized-matmul library.
+//
+// Block layouts are the GGUF ones candle uses (candle-core/src/quantized/k_quants.rs:77-190,
+// mirrored for CUDA in candle-kernels/src/mmvq_gguf.cu:82-173).  Nothing here depends on torch.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define CQ_WARP 32
+#define CQ_QK 32        // elements per Q4_0 / Q8_0 / Q8_1 block
+#define CQ_QK_K 256     // elements per K-quant super-block
+#define CQ_Q8_BYTES 36  // one activation block: 4 scale bytes + 32 int8
+
+// GGML type ids (candle-core/src/quantized/mod.rs:300-342)
+enum CqType : int { CQ_Q4_0 = 2, CQ_Q8_0 = 8, CQ_Q4_K = 12, CQ_Q6_K = 14 };
+// Output / input element types of the launchers
+enum CqElem : int { CQ_F32 = 0, CQ_F16 = 1, CQ_BF16 = 2 };
+// Activation encodings.  All three use the same 36-byte container per 32 elements
+// (4 scale bytes followed by 32 int8), so one scratch buffer serves every mode.
+//   CQ_ACT_Q8_1 : half d = amax/127, half s = sum(x); q = round(x/d).  What candle's CUDA kernels use
+//                 (candle-kernels/src/mmvq_gguf.cu:811-911).
+//   CQ_ACT_Q8_0 : half d = amax/127, q = round(x * (1/d)); the second half holds nothing.  What candle's
+//                 CPU path uses for Q4_0 / Q8_0 weights (k_quants.rs:658-687).
+//   CQ_ACT_Q8_K : float d (the same for the 8 containers of a 256-element super-block),
+//                 iscale = -127/max, q = round(iscale*x).  What candle's CPU path uses for K-quants
+//                 (k_quants.rs:2320-2358).  bsums are not stored: kernels recompute them exactly.
+enum CqAct : int { CQ_ACT_Q8_1 = 0, CQ_ACT_Q8_0 = 1, CQ_ACT_Q8_K = 2 };
+
+// Status codes kept in a process-wide side channel (the reference launchers return void).
+enum CqStatus : int {
+    CQ_OK = 0,
+    CQ_ERR_BAD_ARG = 1,      // null pointer, non-positive size, K not a multiple of the block size
+    CQ_ERR_UNSUPPORTED = 2,  // shape or type outside what the kernels cover
+    CQ_ERR_CUDA = 3,         // a CUDA runtime call failed (code in cq_last_cuda_error)
+    CQ_ERR_TIMEOUT = 4,      // a bounded device-side wait gave up
+};
+
+struct __align__(2) cq_block_q4_0 { __half d; uint8_t qs[16]; };
+struct __align__(2) cq_block_q8_0 { __half d; int8_t qs[32]; };
+struct __align__(4) cq_block_q8_1 { __half2 ds; int8_t qs[32]; };
+struct __align__(4) cq_block_q4_K { __half2 dm; uint8_t scales[12]; uint8_t qs[128]; };
+struct __align__(2) cq_block_q6_K { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; __half d; };
+static_assert(sizeof(cq_block_q4_0) == 18, "q4_0");
+static_assert(sizeof(cq_block_q8_0) == 34, "q8_0");
+static_assert(sizeof(cq_block_q8_1) == 36, "q8_1");
+static_assert(sizeof(cq_block_q4_K) == 144, "q4_K");
+static_assert(sizeof(cq_block_q6_K) == 210, "q6_K");
+
+__host__ __device__ constexpr int cq_type_size(int t) {
+    return t == CQ_Q4_0 ? 18 : t == CQ_Q8_0 ? 34 : t == CQ_Q4_K ? 144 : t == CQ_Q6_K ? 210 : 0;
+}
+__host__ __device__ constexpr int cq_block_elems(int t) {
+    return (t == CQ_Q4_K || t == CQ_Q6_K) ? CQ_QK_K : CQ_QK;
+}
+
+// ---- status side channel (defined in status.cu) ----
+void cq_set_status(int status, const char *msg);
+bool cq_check_launch(const char *what);
+
+// ---- device helpers ----
+__device__ __forceinline__ int cq_dp4a(int a, int b, int c) { return __dp4a(a, b, c); }
+__device__ __forceinline__ int cq_dp4a_u(unsigned a, int b, int c) {   // unsigned bytes x signed bytes
+    int r;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
+__device__ __forceinline__ float cq_elem_to_float(const float *p, int64_t i) { return p[i]; }
+__device__ __forceinline__ float cq_elem_to_float(const __half *p, int64_t i) { return __half2float(p[i]); }
+__device__ __forceinline__ float cq_elem_to_float(const __nv_bfloat16 *p, int64_t i) { return __bfloat162float(p[i]); }
+
+__device__ __forceinline__ void cq_store_out(void *dst, int kind, int64_t i, float v) {
+    if (kind == CQ_F32) ((float *)dst)[i] = v;
+    else if (kind == CQ_F16) ((__half *)dst)[i] = __float2half(v);
+    else ((__nv_bfloat16 *)dst)[i] = __float2bfloat16(v);
+}
+
+// cp.async: 16 bytes global -> shared, bypassing L1.
+__device__ __forceinline__ void cq_cp_async16(void *smem_dst, const void *gmem_src) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cq_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cq_cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Read NW consecutive 32-bit words that start at a 2-byte-aligned shared-memory address.
+// Reads one aligned word past the last one (callers keep 4 bytes of slack).
+template <int NW> __device__ __forceinline__ void cq_lds_words(const uint8_t *p, uint32_t (&out)[NW]) {
+    const uintptr_t a = (uintptr_t)p;
+    const uint32_t *w = (const uint32_t *)(a & ~(uintptr_t)3);
+    const unsigned sh = (unsigned)(a & 2) * 8;
+    uint32_t t[NW + 1];
+#pragma unroll
+    for (int j = 0; j <= NW; ++j) t[j] = w[j];
+#pragma unroll
+    for (int j = 0; j < NW; ++j) out[j] = __funnelshift_r(t[j], t[j + 1], sh);
+}
+__device__ __forceinline__ uint32_t cq_lds_u16(const uint8_t *p) { return *(const uint16_t *)p; }
+
+// Sum NV per-lane values over the 32 lanes of a warp.  Every value is reduced with the same
+// xor butterfly (16, 8, 4, 2, 1), so the result for one value does not depend on NV.
+// NV must be a power of two <= 32.  On return lane l holds the total of value  l / (32 / NV)  in v[0].
+template <int NV> __device__ __forceinline__ float cq_warp_reduce_many(float (&v)[NV]) {
+    const int lane = threadIdx.x & 31;
+    int n = NV;
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        if (n > 1) {
+            const int half = n >> 1;
+            const bool up = lane & s;
+#pragma unroll
+            for (int i = 0; i < NV / 2; ++i) {
+                if (i < half) {
+                    const float keep = up ? v[i + half] : v[i];
+                    const float send = up ? v[i] : v[i + half];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+                }
+            }
+            n = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], s);
+        }
+    }
+    return v[0];
+}

@@ -1,0 +1,360 @@
+// Decode-path quantized GEMV for B200: dst[j, row] = sum_k W[row, k] * x[j, k], 1 <= j <= 8 batch rows.
+//
+// Replaces candle's `launch_mmvq_gguf_<type>_<dt>_plain` (candle-kernels/src/mmvq_gguf.cu:915-1008; kernel
+// body :644-715), which launches one CTA per weight row, loads weights with 2- and 4-byte accesses and
+// re-reads the Q8_1 activations from L2 in every CTA.
+//
+// Design (HBM-bound, so everything serves coalesced streaming of the weight bytes):
+//   * a CTA owns one "K cover": thread t owns chunk t of every row (see gemv_chunks.cuh) and keeps the int8
+//     activations of that chunk for all batch rows in registers for the life of the kernel;
+//   * weight rows are contiguous in memory, so a batch of RB rows is one flat byte range that all threads
+//     copy into shared memory with 16-byte cp.async (L1 bypass), double buffered: the copy of batch i+1
+//     overlaps the arithmetic of batch i.  GGUF blocks of 18 / 34 / 210 bytes are only 2-byte aligned; the
+//     flat copy does not care, and the 2-byte alignment is resolved when reading shared memory;
+//   * each lane produces RB*B partial sums; a transposing xor-butterfly leaves one finished warp total per
+//     lane (about one shuffle per value), warps are then added in index order through shared memory.
+//     The order of additions for one output does not depend on RB, on the grid or on N, so a row gives the
+//     same bits whether the matrix is whole or sharded by rows across GPUs, and whatever the batch size.
+#include <mutex>
+
+#include "../../include/candle_q_b200.h"
+#include "gemv_chunks.cuh"
+
+namespace {
+
+constexpr int kStages = 2;
+
+__host__ __device__ constexpr int next_pow2(int v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : v <= 8 ? 8 : v <= 16 ? 16 : 32; }
+
+template <int TYPE, int ACT, int B, int RB>
+__global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ y, void *__restrict__ dst,
+                                   int out_kind, int nchunks, int nrows, int stride_col_y, int stride_col_dst,
+                                   int row_bytes, int stage_stride) {
+    constexpr int NV = next_pow2(RB * B);
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    float *red = reinterpret_cast<float *>(smem);                       // [2][nwarps][NV]
+    uint8_t *stages = smem + ((2 * nwarps * NV * 4 + 15) & ~15);
+
+    const bool active = tid < nchunks;
+    ChunkAct<TYPE> act[B];
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < B; ++j) chunk_load_act<TYPE, ACT>(act[j], y + (int64_t)j * stride_col_y * CQ_Q8_BYTES, tid);
+    }
+
+    const int nbatches = (nrows + RB - 1) / RB;
+    auto issue = [&](int batch, int stage) {
+        const int row0 = batch * RB;
+        const int nr = min(RB, nrows - row0);
+        const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
+        const uintptr_t a0 = start & ~(uintptr_t)15;
+        const int total = (int)(start - a0) + nr * row_bytes;
+        uint8_t *sdst = stages + stage * stage_stride;
+        for (int o = tid * 16; o < total; o += blockDim.x * 16) cq_cp_async16(sdst + o, (const void *)(a0 + o));
+    };
+
+    if ((int)blockIdx.x < nbatches) issue(blockIdx.x, 0);
+    cq_cp_async_commit();
+
+    int it = 0;
+    for (int batch = blockIdx.x; batch < nbatches; batch += gridDim.x, ++it) {
+        const int nxt = batch + gridDim.x;
+        if (nxt < nbatches) issue(nxt, (it + 1) % kStages);
+        cq_cp_async_commit();
+        cq_cp_async_wait<kStages - 1>();
+        __syncthreads();
+
+        const int row0 = batch * RB;
+        const int nr = min(RB, nrows - row0);
+        const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
+        const uint8_t *srow = stages + (it % kStages) * stage_stride + (int)(start & 15);
+
+        float v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] = 0.0f;
+        if (active) {
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                if (r < nr) {
+                    ChunkW<TYPE> cw;
+                    cw.load(srow + r * row_bytes, tid);
+#pragma unroll
+                    for (int j = 0; j < B; ++j) v[r * B + j] = cw.template dot<ACT>(act[j]);
+                }
+            }
+        }
+        const float tot = cq_warp_reduce_many<NV>(v);
+        float *rbuf = red + (it & 1) * nwarps * NV;
+        if ((lane & (32 / NV - 1)) == 0) rbuf[warp * NV + lane / (32 / NV)] = tot;
+        __syncthreads();
+        if (tid < RB * B) {
+            float s = rbuf[tid];
+            for (int wv = 1; wv < nwarps; ++wv) s += rbuf[wv * NV + tid];
+            const int r = tid / B, j = tid % B;
+            if (r < nr) cq_store_out(dst, out_kind, (int64_t)j * stride_col_dst + row0 + r, s);
+        }
+    }
+    cq_cp_async_wait<0>();
+}
+
+// ---- host side ----
+
+struct DevInfo { int sms = 0; int smem_optin = 0; };
+DevInfo dev_info() {
+    static std::mutex mu;
+    static DevInfo cache[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cache[dev].sms == 0) {
+        cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&cache[dev].smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (cache[dev].sms <= 0) cache[dev].sms = 148;
+        if (cache[dev].smem_optin <= 0) cache[dev].smem_optin = 227 * 1024;
+    }
+    return cache[dev];
+}
+
+// tuning overrides for experiments (0 = automatic)
+int g_force_rb = 0;
+int g_force_ctas_per_sm = 0;
+
+using GemvKernel = void (*)(const uint8_t *, const uint8_t *, void *, int, int, int, int, int, int, int);
+
+struct KernelEntry { GemvKernel fn = nullptr; int regs = 0; bool attr_set[64] = {}; };
+
+// Table of instantiations for one (weight type, activation encoding): [batch 1..8][RB index: 1,2,4,8].
+template <int TYPE, int ACT> struct KernelTable {
+    KernelEntry e[8][4];
+    template <int B, int RBI> void fill_one() {
+        constexpr int RB = 1 << RBI;
+        if constexpr (RB * B <= 32) e[B - 1][RBI].fn = gemv_staged_kernel<TYPE, ACT, B, RB>;
+    }
+    template <int B> void fill_b() { fill_one<B, 0>(); fill_one<B, 1>(); fill_one<B, 2>(); fill_one<B, 3>(); }
+    KernelTable() { fill_b<1>(); fill_b<2>(); fill_b<3>(); fill_b<4>(); fill_b<5>(); fill_b<6>(); fill_b<7>(); fill_b<8>(); }
+};
+
+struct Plan { KernelEntry *k; int T, RB, grid, smem, stage_stride; };
+
+template <int TYPE, int ACT> bool make_plan(int K, int N, int B, Plan &p) {
+    static KernelTable<TYPE, ACT> table;
+    static std::mutex mu;
+    const int nchunks = K / ChunkGeom<TYPE>::ELEMS;
+    const int T = (nchunks + 31) / 32 * 32;
+    if (T > 1024) return false;
+    const DevInfo di = dev_info();
+    const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
+    const int nwarps = T / 32;
+    bool found = false;
+    for (int rbi = 3; rbi >= 0; --rbi) {
+        const int rb = 1 << rbi;
+        KernelEntry &ke = table.e[B - 1][rbi];
+        if (!ke.fn) continue;
+        if (g_force_rb && rb != g_force_rb) continue;
+        {
+            std::lock_guard<std::mutex> lk(mu);
+            if (ke.regs == 0) {
+                cudaFuncAttributes fa;
+                if (cudaFuncGetAttributes(&fa, (const void *)ke.fn) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+                ke.regs = fa.numRegs;
+            }
+        }
+        const int regs_cta = ((ke.regs + 7) & ~7) * T;     // registers are allocated in units of 8 per thread
+        if (regs_cta > 65536) continue;
+        const int nv = next_pow2(rb * B);
+        const int stage = ((rb * row_bytes + 15 + 15) & ~15) + 16;
+        const int smem = ((2 * nwarps * nv * 4 + 15) & ~15) + kStages * stage;
+        if (smem > di.smem_optin) continue;
+        int cps = 2048 / T;
+        if (cps > 32) cps = 32;
+        if ((228 * 1024) / (smem + 1024) < cps) cps = (228 * 1024) / (smem + 1024);
+        if (65536 / regs_cta < cps) cps = 65536 / regs_cta;
+        if (cps < 1) cps = 1;
+        if (g_force_ctas_per_sm && cps > g_force_ctas_per_sm) cps = g_force_ctas_per_sm;
+        const int nbatches = (N + rb - 1) / rb;
+        const int slots = di.sms * cps;
+        // take the largest row batch that still leaves every CTA slot at least two batches; else the smallest
+        const bool enough = nbatches >= 2 * slots;
+        if (!found || enough || rb == 1 || g_force_rb) {
+            p.k = &ke; p.T = T; p.RB = rb; p.smem = smem; p.stage_stride = stage;
+            p.grid = nbatches < slots ? nbatches : slots;
+            found = true;
+            if (enough || g_force_rb) break;
+        }
+    }
+    return found;
+}
+
+// Returns false when no instantiation fits `B` batch rows in one pass (register file), so the caller splits.
+template <int TYPE, int ACT>
+bool launch_type(const void *w, const void *y, void *dst, int out_kind, int K, int N, int sy, int sd, int B,
+                 cudaStream_t st) {
+    Plan p;
+    if (!make_plan<TYPE, ACT>(K, N, B, p)) return false;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !p.k->attr_set[dev]) {
+        cudaFuncSetAttribute((const void *)p.k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dev_info().smem_optin);
+        p.k->attr_set[dev] = true;
+    }
+    const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
+    p.k->fn<<<p.grid, p.T, p.smem, st>>>((const uint8_t *)w, (const uint8_t *)y, dst, out_kind,
+                                          K / ChunkGeom<TYPE>::ELEMS, N, sy, sd, row_bytes, p.stage_stride);
+    cq_check_launch("gemv");
+    return true;
+}
+
+size_t elem_bytes(int kind) { return kind == CQ_F32 ? 4 : 2; }
+
+}  // namespace
+
+// Generic entry: weights `vx` [nrows_x, ncols_x] in GGUF blocks of `wtype`, activations `vy` as 36-byte
+// containers in encoding `act` ([b_size, stride_col_y] blocks), dst[b_size, stride_col_dst] of `out_kind`.
+extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const void *vy, void *dst, int ncols_x,
+                        int nrows_x, int stride_col_y, int stride_col_dst, int b_size, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!vx || !vy || !dst || ncols_x <= 0 || nrows_x <= 0 || b_size <= 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "mmvq: null pointer or empty shape");
+        return;
+    }
+    if (b_size > 8) {   // the reference silently ignores such calls (`default: break`); we record it
+        cq_set_status(CQ_ERR_UNSUPPORTED, "mmvq: batch size above 8");
+        return;
+    }
+    const int be = cq_block_elems(wtype);
+    if (cq_type_size(wtype) == 0 || ncols_x % be != 0 || stride_col_y * 32 < ncols_x) {
+        cq_set_status(CQ_ERR_BAD_ARG, "mmvq: unsupported weight type, or K not a multiple of the block size");
+        return;
+    }
+    if ((uintptr_t)vx % (wtype == CQ_Q4_K ? 16 : 2) != 0 || (uintptr_t)vy % 4 != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "mmvq: misaligned weight or activation pointer");
+        return;
+    }
+    const bool cpu_act = act != CQ_ACT_Q8_1;
+    if ((act == CQ_ACT_Q8_K) != (cpu_act && be == 256) || (act == CQ_ACT_Q8_0 && be != 32)) {
+        cq_set_status(CQ_ERR_BAD_ARG, "mmvq: activation encoding does not fit the weight type");
+        return;
+    }
+    auto run = [&](int j0, int bb) -> bool {
+        const uint8_t *yy = (const uint8_t *)vy + (size_t)j0 * stride_col_y * CQ_Q8_BYTES;
+        uint8_t *dd = (uint8_t *)dst + (size_t)j0 * stride_col_dst * elem_bytes(out_kind);
+        switch (wtype) {
+        case CQ_Q4_0:
+            return cpu_act ? launch_type<CQ_Q4_0, CQ_ACT_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q4_0, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q8_0:   // same formula for both encodings
+            return launch_type<CQ_Q8_0, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q4_K:
+            return cpu_act ? launch_type<CQ_Q4_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q4_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q6_K:
+            return cpu_act ? launch_type<CQ_Q6_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q6_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        }
+        return false;
+    };
+    // One pass when the activation registers of all batch rows fit; otherwise passes of at most
+    // `per` rows (the per-row result does not depend on how rows are grouped).
+    for (int per = b_size; per >= 1; per = (per + 1) / 2) {
+        if (run(0, per < b_size ? per : b_size)) {
+            for (int j0 = per; j0 < b_size; j0 += per) run(j0, b_size - j0 < per ? b_size - j0 : per);
+            return;
+        }
+        if (per == 1) break;
+    }
+    cq_set_status(CQ_ERR_UNSUPPORTED, "gemv: K too large for one CTA to cover (max 32768 elements; 65536 for Q6_K)");
+}
+
+extern "C" void cq_set_tuning(int rows_per_batch, int ctas_per_sm) {
+    g_force_rb = rows_per_batch;
+    g_force_ctas_per_sm = ctas_per_sm;
+}
+
+// The reference's twelve symbols for the four formats (candle-kernels/src/ffi.rs:61-393).
+#define CQ_MMVQ_PLAIN(name, wtype, kind)                                                                          \
+    extern "C" void name(const void *vx, const void *vy, void *dst, int ncols_x, int nrows_x, int stride_col_y,  \
+                         int stride_col_dst, int b_size, void *stream) {                                         \
+        cq_mmvq(wtype, CQ_ACT_Q8_1, kind, vx, vy, dst, ncols_x, nrows_x, stride_col_y, stride_col_dst, b_size,    \
+                stream);                                                                                          \
+    }
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_0_f32_plain, CQ_Q4_0, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_0_f16_plain, CQ_Q4_0, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_0_bf16_plain, CQ_Q4_0, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q8_0_f32_plain, CQ_Q8_0, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q8_0_f16_plain, CQ_Q8_0, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q8_0_bf16_plain, CQ_Q8_0, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_f32_plain, CQ_Q4_K, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_f16_plain, CQ_Q4_K, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_bf16_plain, CQ_Q4_K, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q6_k_f32_plain, CQ_Q6_K, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q6_k_f16_plain, CQ_Q6_K, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q6_k_bf16_plain, CQ_Q6_K, CQ_BF16)
+
+// ---- diagnostic: exact integer dot products per (row, weight block) ----
+// out[row * nblk + i] (and out_min for the Q4_K "min" term) as defined by the oracle's
+// cqo_cuda_block_dots / cqo_cpu_block_dots.  One thread per (row, block); uses the same chunk code as the GEMV.
+namespace {
+template <int TYPE, int ACT>
+__global__ void block_dots_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ y, int *__restrict__ out,
+                                  int *__restrict__ out_min, int K, int nrows) {
+    constexpr int CPB = cq_block_elems(TYPE) / ChunkGeom<TYPE>::ELEMS;   // chunks per weight block
+    const int nblk = K / cq_block_elems(TYPE);
+    const int row_bytes = nblk * cq_type_size(TYPE);
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)nrows * nblk) return;
+    const int row = (int)(idx / nblk), blk = (int)(idx % nblk);
+    const uint8_t *wrow = w + (int64_t)row * row_bytes;
+    int s = 0, sm = 0;
+    for (int c = 0; c < CPB; ++c) {
+        const int chunk = blk * CPB + c;
+        ChunkAct<TYPE> a;
+        chunk_load_act<TYPE, ACT>(a, y, chunk);
+        ChunkW<TYPE> cw;
+        cw.load(wrow, chunk);
+        if constexpr (TYPE == CQ_Q4_0) {
+            if (ACT == CQ_ACT_Q8_1) s += cw.idot(a); else s += cw.idot(a) - 8 * a.sq[0];
+        } else if constexpr (TYPE == CQ_Q8_0) s += cw.idot(a);
+        else if constexpr (TYPE == CQ_Q4_K) {
+            int d0, d1;
+            cw.idots(a, d0, d1);
+            s += d0 * cw.sc[0] + d1 * cw.sc[1];
+            sm += a.sq[0] * cw.mn[0] + a.sq[1] * cw.mn[1];
+        } else {
+            for (int p = 0; p < 4; ++p) s += cw.idot(a, p) * cw.sc[p];
+        }
+    }
+    out[idx] = s;
+    if (out_min) out_min[idx] = sm;
+}
+}  // namespace
+
+extern "C" void cq_block_dots(int wtype, int act, const void *vx, const void *vy, int *out, int *out_min, int ncols_x,
+                              int nrows_x, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!vx || !vy || !out || cq_type_size(wtype) == 0 || ncols_x % cq_block_elems(wtype) != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "block_dots: bad arguments");
+        return;
+    }
+    const int64_t total = (int64_t)nrows_x * (ncols_x / cq_block_elems(wtype));
+    const int grid = (int)((total + 127) / 128);
+    const uint8_t *w = (const uint8_t *)vx, *y = (const uint8_t *)vy;
+    const bool cpu = act != CQ_ACT_Q8_1;
+    switch (wtype) {
+    case CQ_Q4_0:
+        if (cpu) block_dots_kernel<CQ_Q4_0, CQ_ACT_Q8_0><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q4_0, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q8_0: block_dots_kernel<CQ_Q8_0, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x); break;
+    case CQ_Q4_K:
+        if (cpu) block_dots_kernel<CQ_Q4_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q4_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q6_K:
+        if (cpu) block_dots_kernel<CQ_Q6_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q6_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    }
+    cq_check_launch("block_dots");
+}

@@ -1,0 +1,216 @@
+// Per-format "chunk" arithmetic shared by the decode GEMV, the expert-indexed GEMV and the block-dot
+// diagnostic.  A chunk is the slice of one weight row that one lane owns for the whole kernel:
+//
+//   Q4_0 : one 18-byte block            (32 elements)
+//   Q8_0 : one 34-byte block            (32 elements)
+//   Q4_K : 16 bytes of nibbles          (32 elements: 16 of sub-block 2j and 16 of sub-block 2j+1)
+//   Q6_K : 16+16 bytes ql, 16 bytes qh  (64 elements: 16 at each of the four 32-apart positions)
+//
+// A lane keeps the int8 activations of its chunk (for every batch row) in registers and walks over
+// weight rows, so activations are fetched once per kernel instead of once per row as in the reference
+// kernels (candle-kernels/src/mmvq_gguf.cu:644-715), and weight bytes come from shared memory where
+// they were staged with 16-byte cp.async copies regardless of the 2-byte alignment of the GGUF blocks.
+//
+// Formulas follow the reference per format:
+//   CUDA (Q8_1 activations): candle-kernels/src/mmvq_gguf.cu:192-207 (Q4_0), :280-290 (Q8_0),
+//                            :335-354 (Q4_K), :382-398 (Q6_K)
+//   CPU  (Q8_0 / Q8_K)     : candle-core/src/quantized/k_quants.rs:294-311, :720-738, :1460-1540, :2035-2092
+// The integer parts (dp4a chains) are exact; only the order of the f32 additions differs.
+#pragma once
+#include "common.cuh"
+
+template <int TYPE> struct ChunkGeom;
+template <> struct ChunkGeom<CQ_Q4_0> { static constexpr int ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q8_0> { static constexpr int ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q4_K> { static constexpr int ELEMS = 32, Q8_BLOCKS = 2, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q6_K> { static constexpr int ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
+
+// Activation registers of one chunk for one batch row.
+template <int TYPE> struct ChunkAct {
+    static constexpr int NB = ChunkGeom<TYPE>::Q8_BLOCKS;
+    static constexpr int WPB = ChunkGeom<TYPE>::WORDS / NB;   // int8x4 words per activation block
+    int u[ChunkGeom<TYPE>::WORDS];
+    float d[NB];    // Q8_1 / Q8_0: per-block scale.  Q8_K: d[0] only.
+    float s[NB];    // Q8_1: Q4_0 -> half sum; Q4_K -> d * sum(q).  Q8_0 (Q4_0 only): unused.
+    int sq[NB];     // exact sum of the int8 values held for that block
+};
+
+__device__ __forceinline__ int cq_ld_global_i32(const uint8_t *p) { return *reinterpret_cast<const int *>(p); }
+
+// Which activation block (relative to the first block of the row) and which byte range a chunk needs.
+template <int TYPE> __device__ __forceinline__ void chunk_act_coords(int chunk, int i, int &blk, int &byte0) {
+    if constexpr (TYPE == CQ_Q4_0 || TYPE == CQ_Q8_0) { blk = chunk; byte0 = 0; }
+    else if constexpr (TYPE == CQ_Q4_K) {
+        const int sb = chunk >> 3, c = chunk & 7;
+        blk = sb * 8 + 2 * (c >> 1) + i; byte0 = 16 * (c & 1);
+    } else {
+        const int sb = chunk >> 2, n = (chunk >> 1) & 1, h = chunk & 1;
+        blk = sb * 8 + 4 * n + i; byte0 = 16 * h;
+    }
+}
+
+template <int TYPE, int ACT>
+__device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t *yrow, int chunk) {
+    constexpr int NB = ChunkAct<TYPE>::NB, WPB = ChunkAct<TYPE>::WPB;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        int blk, byte0;
+        chunk_act_coords<TYPE>(chunk, i, blk, byte0);
+        const uint8_t *p = yrow + (int64_t)blk * CQ_Q8_BYTES;
+        int sq = 0;
+#pragma unroll
+        for (int w = 0; w < WPB; ++w) {
+            const int v = cq_ld_global_i32(p + 4 + byte0 + 4 * w);
+            a.u[i * WPB + w] = v;
+            sq = cq_dp4a(0x01010101, v, sq);
+        }
+        a.sq[i] = sq;
+        const int ds = cq_ld_global_i32(p);
+        if constexpr (ACT == CQ_ACT_Q8_K) {
+            a.d[i] = __int_as_float(ds);
+            a.s[i] = 0.0f;
+        } else {
+            const __half2 h2 = *reinterpret_cast<const __half2 *>(&ds);
+            a.d[i] = __low2float(h2);
+            if constexpr (TYPE == CQ_Q4_K) a.s[i] = a.d[i] * (float)sq;
+            else a.s[i] = __high2float(h2);
+        }
+    }
+}
+
+// Raw integer results of one (weight chunk, activation chunk) pair plus the weight-side scales.
+template <int TYPE> struct ChunkW;
+
+template <> struct ChunkW<CQ_Q4_0> {
+    uint32_t lo[4], hi[4];
+    float d;
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const uint8_t *b = row + chunk * 18;
+        d = __half2float(__ushort_as_half((unsigned short)cq_lds_u16(b)));
+        uint32_t q[4];
+        cq_lds_words<4>(b + 2, q);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { lo[w] = q[w] & 0x0F0F0F0Fu; hi[w] = (q[w] >> 4) & 0x0F0F0F0Fu; }
+    }
+    // sum of unsigned nibbles x int8 (the "- 8" offset is applied by the caller)
+    __device__ __forceinline__ int idot(const ChunkAct<CQ_Q4_0> &a) const {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { s = cq_dp4a((int)lo[w], a.u[w], s); s = cq_dp4a((int)hi[w], a.u[4 + w], s); }
+        return s;
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_0> &a) const {
+        const int s = idot(a);
+        if constexpr (ACT == CQ_ACT_Q8_1) return d * ((float)s * a.d[0] - 8.0f * a.s[0]);
+        else return (float)(s - 8 * a.sq[0]) * d * a.d[0];
+    }
+};
+
+template <> struct ChunkW<CQ_Q8_0> {
+    uint32_t q[8];
+    float d;
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const uint8_t *b = row + chunk * 34;
+        d = __half2float(__ushort_as_half((unsigned short)cq_lds_u16(b)));
+        cq_lds_words<8>(b + 2, q);
+    }
+    __device__ __forceinline__ int idot(const ChunkAct<CQ_Q8_0> &a) const {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s = cq_dp4a((int)q[w], a.u[w], s);
+        return s;
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q8_0> &a) const {
+        return (float)idot(a) * d * a.d[0];
+    }
+};
+
+template <> struct ChunkW<CQ_Q4_K> {
+    uint32_t lo[4], hi[4];
+    float d, dmin;
+    int sc[2], mn[2];
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const int sb = chunk >> 3, c = chunk & 7, jp = c >> 1;   // jp: which pair of sub-blocks
+        const uint8_t *b = row + sb * 144;
+        const __half2 dm = *reinterpret_cast<const __half2 *>(b);
+        d = __low2float(dm); dmin = __high2float(dm);
+        // 6-bit scales/mins of sub-blocks 2jp and 2jp+1 (layout: candle-core/src/quantized/utils.rs:50-60)
+        const uint32_t s_hi = cq_lds_u16(b + 4 + 2 * (jp + 2));          // bytes 2jp+4, 2jp+5
+        const uint32_t s_lo = cq_lds_u16(b + 4 + 2 * jp);                // bytes 2jp,   2jp+1
+        const uint32_t s_pp = cq_lds_u16(b + 4 + 2 * (jp & 1));          // bytes 2jp-4, 2jp-3 when jp >= 2
+        uint32_t scp, mnp;
+        if (jp < 2) { scp = s_lo & 0x3f3fu; mnp = s_hi & 0x3f3fu; }
+        else {
+            scp = (s_hi & 0x0f0fu) | ((s_pp & 0xc0c0u) >> 2);
+            mnp = ((s_hi >> 4) & 0x0f0fu) | ((s_lo & 0xc0c0u) >> 2);
+        }
+        sc[0] = scp & 0xFF; sc[1] = scp >> 8; mn[0] = mnp & 0xFF; mn[1] = mnp >> 8;
+        const uint4 q = *reinterpret_cast<const uint4 *>(b + 16 + 16 * c);
+        const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { lo[w] = qq[w] & 0x0F0F0F0Fu; hi[w] = (qq[w] >> 4) & 0x0F0F0F0Fu; }
+    }
+    __device__ __forceinline__ void idots(const ChunkAct<CQ_Q4_K> &a, int &d0, int &d1) const {
+        d0 = 0; d1 = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { d0 = cq_dp4a((int)lo[w], a.u[w], d0); d1 = cq_dp4a((int)hi[w], a.u[4 + w], d1); }
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_K> &a) const {
+        int d0, d1;
+        idots(a, d0, d1);
+        if constexpr (ACT == CQ_ACT_Q8_1) {
+            const float sd = a.d[0] * (float)(d0 * sc[0]) + a.d[1] * (float)(d1 * sc[1]);
+            const float sm = a.s[0] * (float)mn[0] + a.s[1] * (float)mn[1];
+            return d * sd - dmin * sm;
+        } else {
+            const int isd = d0 * sc[0] + d1 * sc[1];
+            const int ism = a.sq[0] * mn[0] + a.sq[1] * mn[1];
+            return a.d[0] * (d * (float)isd - dmin * (float)ism);
+        }
+    }
+};
+
+template <> struct ChunkW<CQ_Q6_K> {
+    uint32_t q[4][4];   // [position][word], unsigned 6-bit values
+    float d;
+    int sc[4];
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const int sb = chunk >> 2, n = (chunk >> 1) & 1, h = chunk & 1;
+        const uint8_t *b = row + sb * 210;
+        uint32_t la[4], lb[4], hh[4];
+        cq_lds_words<4>(b + 64 * n + 16 * h, la);
+        cq_lds_words<4>(b + 64 * n + 32 + 16 * h, lb);
+        cq_lds_words<4>(b + 128 + 32 * n + 16 * h, hh);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            q[0][w] = (la[w] & 0x0F0F0F0Fu) | ((hh[w] << 4) & 0x30303030u);
+            q[1][w] = (lb[w] & 0x0F0F0F0Fu) | ((hh[w] << 2) & 0x30303030u);
+            q[2][w] = ((la[w] >> 4) & 0x0F0F0F0Fu) | (hh[w] & 0x30303030u);
+            q[3][w] = ((lb[w] >> 4) & 0x0F0F0F0Fu) | ((hh[w] >> 2) & 0x30303030u);
+        }
+        const int8_t *s8 = reinterpret_cast<const int8_t *>(b + 192 + 8 * n + h);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) sc[p] = s8[2 * p];
+        d = __half2float(__ushort_as_half((unsigned short)cq_lds_u16(b + 208)));
+    }
+    // exact dot of (q - 32) with the activations of position p
+    __device__ __forceinline__ int idot(const ChunkAct<CQ_Q6_K> &a, int p) const {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) s = cq_dp4a((int)q[p][w], a.u[4 * p + w], s);
+        return s - 32 * a.sq[p];
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q6_K> &a) const {
+        if constexpr (ACT == CQ_ACT_Q8_1) {
+            float sf = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) sf += a.d[p] * (float)(idot(a, p) * sc[p]);
+            return d * sf;
+        } else {
+            int is = 0;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) is += idot(a, p) * sc[p];
+            return a.d[0] * d * (float)is;
+        }
+    }
+};

@@ -1,0 +1,283 @@
+// Host side of the quantized matmul (see qtensor.h) and its flat C interface (cqh_*).
+#include "qtensor.h"
+
+#include <atomic>
+#include <cstring>
+#include <map>
+#include <mutex>
+
+#include "../../../include/candle_q_b200.h"
+
+namespace candle_q {
+
+namespace {
+void cuda_check(cudaError_t e, const char *what) {
+    if (e != cudaSuccess) throw Error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+struct DeviceGuard {
+    int prev = 0;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cuda_check(cudaSetDevice(dev), "cudaSetDevice");
+    }
+    ~DeviceGuard() {
+        int cur = 0;
+        cudaGetDevice(&cur);
+        if (cur != prev) cudaSetDevice(prev);
+    }
+};
+std::atomic<int> g_act_mode{(int)ActMode::Cuda};
+
+void lib_check(const char *what) {
+    const int st = cq_last_status();
+    if (st != 0) {
+        std::string msg = cq_last_message();
+        cq_clear_status();
+        throw Error(std::string(what) + ": " + msg);
+    }
+}
+}  // namespace
+
+GgmlDType ggml_dtype_from_u32(uint32_t u) {
+    switch (u) {
+    case 0: case 1: case 2: case 3: case 6: case 7: case 8: case 9: case 10: case 11: case 12: case 13: case 14:
+    case 15: case 30:
+        return (GgmlDType)u;
+    }
+    throw Error("unknown dtype for tensor " + std::to_string(u));
+}
+
+size_t type_size(GgmlDType t) {
+    switch (t) {
+    case GgmlDType::F32: return 4;
+    case GgmlDType::F16: case GgmlDType::BF16: return 2;
+    case GgmlDType::Q4_0: return 18;
+    case GgmlDType::Q4_1: return 20;
+    case GgmlDType::Q5_0: return 22;
+    case GgmlDType::Q5_1: return 24;
+    case GgmlDType::Q8_0: return 34;
+    case GgmlDType::Q8_1: return 36;
+    case GgmlDType::Q2K: return 84;
+    case GgmlDType::Q3K: return 110;
+    case GgmlDType::Q4K: return 144;
+    case GgmlDType::Q5K: return 176;
+    case GgmlDType::Q6K: return 210;
+    case GgmlDType::Q8K: return 292;
+    }
+    return 0;
+}
+
+size_t block_size(GgmlDType t) {
+    switch (t) {
+    case GgmlDType::F32: case GgmlDType::F16: case GgmlDType::BF16: return 1;
+    case GgmlDType::Q4_0: case GgmlDType::Q4_1: case GgmlDType::Q5_0: case GgmlDType::Q5_1:
+    case GgmlDType::Q8_0: case GgmlDType::Q8_1:
+        return 32;
+    default: return 256;
+    }
+}
+
+const char *dtype_name(GgmlDType t) {
+    switch (t) {
+    case GgmlDType::F32: return "F32"; case GgmlDType::F16: return "F16"; case GgmlDType::BF16: return "BF16";
+    case GgmlDType::Q4_0: return "Q4_0"; case GgmlDType::Q4_1: return "Q4_1"; case GgmlDType::Q5_0: return "Q5_0";
+    case GgmlDType::Q5_1: return "Q5_1"; case GgmlDType::Q8_0: return "Q8_0"; case GgmlDType::Q8_1: return "Q8_1";
+    case GgmlDType::Q2K: return "Q2K"; case GgmlDType::Q3K: return "Q3K"; case GgmlDType::Q4K: return "Q4K";
+    case GgmlDType::Q5K: return "Q5K"; case GgmlDType::Q6K: return "Q6K"; case GgmlDType::Q8K: return "Q8K";
+    }
+    return "?";
+}
+
+bool kernels_support(GgmlDType t) {
+    return t == GgmlDType::Q4_0 || t == GgmlDType::Q8_0 || t == GgmlDType::Q4K || t == GgmlDType::Q6K;
+}
+
+void set_act_mode(ActMode m) { g_act_mode.store((int)m); }
+ActMode act_mode() { return (ActMode)g_act_mode.load(); }
+
+// ---- workspace -------------------------------------------------------------------------------
+namespace {
+struct Slot { void *ptr = nullptr; size_t cap = 0; };
+std::mutex g_ws_mu;
+std::map<int, Slot> g_ws;
+}  // namespace
+
+void *workspace_ensure(int device, size_t bytes) {
+    std::lock_guard<std::mutex> lk(g_ws_mu);
+    Slot &s = g_ws[device];
+    if (s.cap < bytes) {
+        DeviceGuard g(device);
+        const size_t cap = pad(bytes + bytes / 4, 1 << 20);     // grow with head-room, never shrink
+        void *p = nullptr;
+        cuda_check(cudaMalloc(&p, cap), "workspace cudaMalloc");
+        if (s.ptr) cudaFree(s.ptr);     // cudaFree waits for kernels still using the old buffer
+        s.ptr = p;
+        s.cap = cap;
+    }
+    return s.ptr;
+}
+
+// ---- QCudaStorage ----------------------------------------------------------------------------
+QCudaStorage::~QCudaStorage() {
+    if (owned_ && ptr_) {
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(device_);
+        cudaFree(ptr_);
+        cudaSetDevice(prev);
+    }
+}
+
+std::unique_ptr<QCudaStorage> QCudaStorage::load_quantized(int device, GgmlDType dtype, const void *host_data,
+                                                           size_t nbytes) {
+    if (nbytes % type_size(dtype) != 0)
+        throw Error("load_quantized: " + std::to_string(nbytes) + " bytes is not a whole number of " + dtype_name(dtype) + " blocks");
+    DeviceGuard g(device);
+    std::unique_ptr<QCudaStorage> s(new QCudaStorage());
+    const size_t padded = nbytes + MATRIX_ROW_PADDING * type_size(dtype) / block_size(dtype);
+    void *p = nullptr;
+    cuda_check(cudaMalloc(&p, padded), "load_quantized cudaMalloc");
+    s->ptr_ = (uint8_t *)p; s->len_ = nbytes; s->owned_ = true; s->dtype_ = dtype; s->device_ = device;
+    cuda_check(cudaMemset(p, 0, padded), "load_quantized cudaMemset");
+    if (nbytes && host_data) cuda_check(cudaMemcpy(p, host_data, nbytes, cudaMemcpyHostToDevice), "load_quantized cudaMemcpy");
+    return s;
+}
+
+std::unique_ptr<QCudaStorage> QCudaStorage::zeros(int device, size_t elem_count, GgmlDType dtype) {
+    if (elem_count % block_size(dtype) != 0) throw Error("zeros: element count is not a multiple of the block size");
+    return load_quantized(device, dtype, nullptr, elem_count / block_size(dtype) * type_size(dtype));
+}
+
+std::unique_ptr<QCudaStorage> QCudaStorage::wrap_device(int device, GgmlDType dtype, void *device_ptr, size_t nbytes) {
+    if (!device_ptr || nbytes % type_size(dtype) != 0) throw Error("wrap_device: null pointer or partial block");
+    std::unique_ptr<QCudaStorage> s(new QCudaStorage());
+    s->ptr_ = (uint8_t *)device_ptr; s->len_ = nbytes; s->owned_ = false; s->dtype_ = dtype; s->device_ = device;
+    return s;
+}
+
+std::vector<uint8_t> QCudaStorage::data() const {
+    DeviceGuard g(device_);
+    std::vector<uint8_t> out(len_);
+    if (len_) cuda_check(cudaMemcpy(out.data(), ptr_, len_, cudaMemcpyDeviceToHost), "data cudaMemcpy");
+    return out;
+}
+
+void QCudaStorage::fwd(size_t n, size_t k, const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out,
+                       cudaStream_t stream) const {
+    if (ndims < 2) throw Error("input tensor has only one dimension");
+    if ((size_t)dims[ndims - 1] != k) {
+        std::string s = "mismatch on matmul dim [" + std::to_string(n) + ", " + std::to_string(k) + "] [";
+        for (int i = 0; i < ndims; ++i) s += (i ? ", " : "") + std::to_string(dims[i]);
+        throw Error(s + "]");
+    }
+    if (!kernels_support(dtype_)) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(dtype_));
+    if (n * (k / block_size(dtype_)) * type_size(dtype_) != len_ || k % block_size(dtype_) != 0)
+        throw Error("qmatmul: storage size does not match shape");
+    size_t rows = 1;
+    for (int i = 0; i + 1 < ndims; ++i) rows *= (size_t)dims[i];
+    if (rows == 0) return;
+    if (!x || !out) throw Error("qmatmul: null activation or output pointer");
+    DeviceGuard g(device_);
+
+    const bool cpu_exact = act_mode() == ActMode::CpuExact;
+    const int act = !cpu_exact ? CQ_ACT_Q8_1_ENC : (block_size(dtype_) == 256 ? CQ_ACT_Q8_K_ENC : CQ_ACT_Q8_0_ENC);
+    const size_t k_padded = pad(k, MATRIX_ROW_PADDING);
+    const size_t row_q8 = k_padded / 32 * 36;
+    const size_t xs = dtype_size(x_dtype);
+
+    // Decode path: up to 8 rows per launch.  Larger inputs are walked in slices of 8 rows until the
+    // tensor-core prefill kernel takes them over (see cq_mmq below when present).
+    const size_t chunk = MMVQ_MAX_BATCH;
+    uint8_t *scratch = (uint8_t *)workspace_ensure(device_, (rows < chunk ? rows : chunk) * row_q8);
+    for (size_t r0 = 0; r0 < rows; r0 += chunk) {
+        const int b = (int)(rows - r0 < chunk ? rows - r0 : chunk);
+        const uint8_t *xp = (const uint8_t *)x + r0 * k * xs;
+        uint8_t *op = (uint8_t *)out + r0 * n * xs;
+        cq_quantize_act(xp, (int)x_dtype, scratch, (int)k, (int)k_padded, b, act, stream);
+        cq_mmvq((int)dtype_, act, (int)x_dtype, ptr_, scratch, op, (int)k, (int)n, (int)(k_padded / 32), (int)n, b, stream);
+    }
+    lib_check("qmatmul");
+}
+
+// ---- QTensor / QMatMul -----------------------------------------------------------------------
+QTensor::QTensor(std::unique_ptr<QCudaStorage> storage, std::vector<int64_t> dims)
+    : storage_(std::move(storage)), shape_(std::move(dims)) {
+    size_t elems = 1;
+    for (int64_t d : shape_) elems *= (size_t)d;
+    const GgmlDType t = storage_->dtype();
+    // check_shape, mod.rs:518-530: the last dimension must be a whole number of blocks
+    if (shape_.empty() || (size_t)shape_.back() % block_size(t) != 0)
+        throw Error("quantized tensor: the last dim must be divisible by the block size " + std::to_string(block_size(t)));
+    if (elems / block_size(t) * type_size(t) != storage_->storage_size_in_bytes())
+        throw Error("quantized tensor: byte size does not match the shape");
+}
+
+QMatMul::QMatMul(std::shared_ptr<QTensor> t) : t_(std::move(t)) {
+    if (t_->rank() != 2) throw Error("QMatMul expects a rank-2 quantized tensor");
+}
+
+void QMatMul::forward(const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out, cudaStream_t stream) const {
+    const auto &s = t_->shape();
+    t_->storage().fwd((size_t)s[0], (size_t)s[1], x, x_dtype, dims, ndims, out, stream);
+}
+
+}  // namespace candle_q
+
+// ---- flat C interface ------------------------------------------------------------------------
+using namespace candle_q;
+
+namespace {
+thread_local std::string t_err;
+template <typename F> int guarded(F &&f) {
+    try { f(); return 0; }
+    catch (const std::exception &e) { t_err = e.what(); return 1; }
+}
+}  // namespace
+
+extern "C" const char *cqh_last_error(void) { return t_err.c_str(); }
+
+extern "C" int cqh_qtensor_load(int ggml_dtype, const void *host_bytes, size_t nbytes, const int64_t *dims, int ndims,
+                                int device, void **out_handle) {
+    return guarded([&] {
+        auto st = QCudaStorage::load_quantized(device, ggml_dtype_from_u32((uint32_t)ggml_dtype), host_bytes, nbytes);
+        *out_handle = new std::shared_ptr<QTensor>(new QTensor(std::move(st), std::vector<int64_t>(dims, dims + ndims)));
+    });
+}
+
+extern "C" int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int64_t *dims, int ndims,
+                                int device, void **out_handle) {
+    return guarded([&] {
+        auto st = QCudaStorage::wrap_device(device, ggml_dtype_from_u32((uint32_t)ggml_dtype), device_ptr, nbytes);
+        *out_handle = new std::shared_ptr<QTensor>(new QTensor(std::move(st), std::vector<int64_t>(dims, dims + ndims)));
+    });
+}
+
+extern "C" void cqh_qtensor_free(void *handle) { delete (std::shared_ptr<QTensor> *)handle; }
+
+extern "C" int cqh_qtensor_data(void *handle, void *host_out, size_t nbytes) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        auto v = t->data();
+        if (v.size() != nbytes) throw Error("data: size mismatch");
+        std::memcpy(host_out, v.data(), nbytes);
+    });
+}
+
+extern "C" const void *cqh_qtensor_device_ptr(void *handle) {
+    return (*(std::shared_ptr<QTensor> *)handle)->storage().device_ptr();
+}
+
+extern "C" int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
+                                   void *stream) {
+    return guarded([&] {
+        QMatMul mm(*(std::shared_ptr<QTensor> *)handle);
+        mm.forward(x, (DType)x_dtype, dims, ndims, out, (cudaStream_t)stream);
+    });
+}
+
+extern "C" void cqh_set_act_mode(int mode) { set_act_mode(mode ? ActMode::CpuExact : ActMode::Cuda); }
+extern "C" int cqh_get_act_mode(void) { return (int)act_mode(); }
+
+extern "C" int cqh_workspace_reserve(int device, size_t bytes) {
+    return guarded([&] { workspace_ensure(device, bytes); });
+}

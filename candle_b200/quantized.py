@@ -1,0 +1,189 @@
+"""Python face of the host objects: ``GgmlDType``, ``QTensor``, ``QMatMul``.
+
+Mirrors the names and behaviour of candle-core/src/quantized/mod.rs (``GgmlDType`` :281-421, ``QTensor``
+:59-66 and :505-562, ``QMatMul`` :807-852 and ``Module::forward`` :1020-1043) and of candle-pyo3's
+``QTensor.matmul_t`` (candle-pyo3/src/lib.rs:1276-1280).  All arithmetic happens in
+``libcandle_q_b200.so``; torch only supplies device memory and the current stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from . import capi
+from .capi import CandleQError
+
+
+class GgmlDType(enum.IntEnum):
+    """GGML tensor types with their ids in GGUF files (mod.rs:300-342)."""
+    F32 = 0
+    F16 = 1
+    Q4_0 = 2
+    Q4_1 = 3
+    Q5_0 = 6
+    Q5_1 = 7
+    Q8_0 = 8
+    Q8_1 = 9
+    Q2K = 10
+    Q3K = 11
+    Q4K = 12
+    Q5K = 13
+    Q6K = 14
+    Q8K = 15
+    BF16 = 30
+
+    @classmethod
+    def from_u32(cls, u: int) -> "GgmlDType":
+        try:
+            return cls(u)
+        except ValueError:
+            raise CandleQError(f"unknown dtype for tensor {u}") from None
+
+    def type_size(self) -> int:
+        """Bytes per block (mod.rs:387-406)."""
+        return _TYPE_SIZE[self]
+
+    def block_size(self) -> int:
+        """Elements per block (mod.rs:409-421)."""
+        if self in (GgmlDType.F32, GgmlDType.F16, GgmlDType.BF16):
+            return 1
+        if self in (GgmlDType.Q4_0, GgmlDType.Q4_1, GgmlDType.Q5_0, GgmlDType.Q5_1, GgmlDType.Q8_0, GgmlDType.Q8_1):
+            return 32
+        return 256
+
+
+_TYPE_SIZE = {
+    GgmlDType.F32: 4, GgmlDType.F16: 2, GgmlDType.BF16: 2, GgmlDType.Q4_0: 18, GgmlDType.Q4_1: 20,
+    GgmlDType.Q5_0: 22, GgmlDType.Q5_1: 24, GgmlDType.Q8_0: 34, GgmlDType.Q8_1: 36, GgmlDType.Q2K: 84,
+    GgmlDType.Q3K: 110, GgmlDType.Q4K: 144, GgmlDType.Q5K: 176, GgmlDType.Q6K: 210, GgmlDType.Q8K: 292,
+}
+
+_ELEM = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+
+
+def set_activation_mode(cpu_exact: bool) -> None:
+    """False (default): Q8_1 activations, the arithmetic of candle's CUDA kernels.
+    True: activations quantized exactly like candle's CPU path (Q8_0 / Q8_K)."""
+    capi.lib().cqh_set_act_mode(1 if cpu_exact else 0)
+
+
+def _dims(shape: Sequence[int]):
+    arr = (C.c_int64 * len(shape))(*[int(d) for d in shape])
+    return arr, len(shape)
+
+
+class QTensor:
+    """A quantized tensor resident on one CUDA device."""
+
+    def __init__(self, handle: int, dtype: GgmlDType, shape: tuple[int, ...], device: torch.device, keep=None):
+        self._h = C.c_void_p(handle)
+        self._dtype = dtype
+        self._shape = tuple(int(d) for d in shape)
+        self._device = device
+        self._keep = keep   # backing tensor of a non-owning view
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                capi.lib().cqh_qtensor_free(h)
+            except Exception:
+                pass
+
+    @classmethod
+    def from_data(cls, data, dtype: GgmlDType, shape: Sequence[int], device="cuda:0") -> "QTensor":
+        """Upload GGUF blocks held in host memory (``QStorage::from_data`` + ``load_quantized``,
+        mod.rs:94-133, cuda.rs:989-1008)."""
+        dtype = GgmlDType(dtype)
+        device = torch.device(device)
+        if isinstance(data, torch.Tensor):
+            data = data.detach().cpu().contiguous().numpy()
+        buf = np.ascontiguousarray(np.frombuffer(data, dtype=np.uint8) if isinstance(data, (bytes, bytearray, memoryview))
+                                   else np.asarray(data).view(np.uint8).reshape(-1))
+        dims, nd = _dims(shape)
+        h = C.c_void_p()
+        capi.hcheck(capi.lib().cqh_qtensor_load(int(dtype), buf.ctypes.data, buf.size, dims, nd,
+                                                 device.index or 0, C.byref(h)), "QTensor.from_data")
+        return cls(h.value, dtype, tuple(shape), device)
+
+    @classmethod
+    def from_device_blocks(cls, blocks: torch.Tensor, dtype: GgmlDType, shape: Sequence[int]) -> "QTensor":
+        """Non-owning view of GGUF blocks already on the device (``blocks``: contiguous uint8 CUDA tensor)."""
+        dtype = GgmlDType(dtype)
+        if not blocks.is_cuda or blocks.dtype != torch.uint8 or not blocks.is_contiguous():
+            raise CandleQError("from_device_blocks expects a contiguous uint8 CUDA tensor")
+        dims, nd = _dims(shape)
+        h = C.c_void_p()
+        capi.hcheck(capi.lib().cqh_qtensor_wrap(int(dtype), blocks.data_ptr(), blocks.numel(), dims, nd,
+                                                 blocks.device.index or 0, C.byref(h)), "QTensor.from_device_blocks")
+        return cls(h.value, dtype, tuple(shape), blocks.device, keep=blocks)
+
+    @property
+    def shape(self) -> tuple[int, ...]:
+        return self._shape
+
+    @property
+    def dtype(self) -> GgmlDType:
+        return self._dtype
+
+    @property
+    def device(self) -> torch.device:
+        return self._device
+
+    def rank(self) -> int:
+        return len(self._shape)
+
+    def storage_size_in_bytes(self) -> int:
+        n = 1
+        for d in self._shape:
+            n *= d
+        return n // self._dtype.block_size() * self._dtype.type_size()
+
+    def device_ptr(self) -> int:
+        return int(capi.lib().cqh_qtensor_device_ptr(self._h))
+
+    def data(self) -> bytes:
+        """The canonical GGUF bytes (``QTensor::data``, mod.rs:754-756)."""
+        out = np.empty(self.storage_size_in_bytes(), dtype=np.uint8)
+        capi.hcheck(capi.lib().cqh_qtensor_data(self._h, out.ctypes.data, out.size), "QTensor.data")
+        return out.tobytes()
+
+    def matmul_t(self, xs: torch.Tensor) -> torch.Tensor:
+        """xs @ self.T, as candle-pyo3's ``QTensor.matmul_t``."""
+        return QMatMul.from_qtensor(self).forward(xs)
+
+
+class QMatMul:
+    """``QMatMul::QTensor`` variant: y = x . W^T with W quantized."""
+
+    def __init__(self, qtensor: QTensor):
+        if qtensor.rank() != 2:
+            raise CandleQError("QMatMul expects a rank-2 quantized tensor")
+        self.qtensor = qtensor
+
+    @classmethod
+    def from_qtensor(cls, qtensor: QTensor) -> "QMatMul":
+        return cls(qtensor)
+
+    def forward(self, xs: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        if not xs.is_cuda:
+            raise CandleQError("QMatMul.forward needs a CUDA tensor: this build has no CPU path")
+        if xs.dtype not in _ELEM:
+            raise CandleQError(f"Expected f32/f16/bf16, got {xs.dtype}")
+        if not xs.is_contiguous():
+            raise CandleQError("input tensor is not contiguous")
+        n = self.qtensor.shape[0]
+        if out is None:
+            out = torch.empty((*xs.shape[:-1], n), dtype=xs.dtype, device=xs.device)
+        dims, nd = _dims(xs.shape)
+        stream = torch.cuda.current_stream(xs.device).cuda_stream
+        with torch.cuda.device(xs.device):
+            capi.hcheck(capi.lib().cqh_qmatmul_forward(self.qtensor._h, xs.data_ptr(), _ELEM[xs.dtype], dims, nd,
+                                                        out.data_ptr(), stream))
+        return out
+
+    __call__ = forward

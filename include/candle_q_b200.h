@@ -1,0 +1,129 @@
+/*
+ * candle_q_b200.h -- C ABI of libcandle_q_b200: GGUF quantized matmul for NVIDIA B200 (sm_100a).
+ *
+ * The first group of functions has exactly the names and signatures that candle's Rust host binds in
+ * candle-kernels/src/ffi.rs, so this library can stand in for candle's kernel archive for the Q4_0, Q8_0,
+ * Q4_K and Q6_K formats.  All pointers are device pointers unless stated otherwise, `stream` is a
+ * cudaStream_t, nothing synchronises, and the caller owns every buffer.  Like the reference launchers they
+ * return void; the outcome of a failing call is kept in a side channel (cq_last_status).
+ *
+ * The second group (prefix cq_) is this library's own surface: the status channel, the generic entry points
+ * the compatible symbols forward to, activation encodings that reproduce candle's CPU path bit for bit, and
+ * a diagnostic that returns the exact per-block integer dot products.
+ */
+#ifndef CANDLE_Q_B200_H
+#define CANDLE_Q_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------
+ * 1. Symbols of candle-kernels/src/ffi.rs
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Activation rows -> Q8_1 blocks.  Replaces candle-kernels/src/ffi.rs:396-419
+ * (kernels: candle-kernels/src/mmvq_gguf.cu:811-911).  x: [num_rows, kx] contiguous; vy: [num_rows,
+ * kx_padded/32] blocks of 36 bytes; elements in [kx, kx_padded) are written as zeros with d = 0. */
+void launch_mmvq_gguf_quantize_q8_1_f32(const void *x, void *vy, int kx, int kx_padded, int num_rows, void *stream);
+void launch_mmvq_gguf_quantize_q8_1_f16(const void *x, void *vy, int kx, int kx_padded, int num_rows, void *stream);
+void launch_mmvq_gguf_quantize_q8_1_bf16(const void *x, void *vy, int kx, int kx_padded, int num_rows, void *stream);
+
+/* Decode GEMV, batch 1..8.  Replaces candle-kernels/src/ffi.rs:61-393 for four formats
+ * (launchers: candle-kernels/src/mmvq_gguf.cu:915-1008).  vx: weights [nrows_x, ncols_x] as GGUF blocks;
+ * vy: Q8_1 blocks, row j at block j*stride_col_y; dst[j*stride_col_dst + row] in the type of the suffix. */
+#define CQ_DECL_MMVQ(name)                                                                                   \
+    void name(const void *vx, const void *vy, void *dst, int ncols_x, int nrows_x, int stride_col_y,       \
+              int stride_col_dst, int b_size, void *stream)
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_0_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_0_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_0_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q8_0_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q8_0_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q8_0_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_bf16_plain);
+#undef CQ_DECL_MMVQ
+
+/* ------------------------------------------------------------------------------------------------
+ * 2. Library surface
+ * ---------------------------------------------------------------------------------------------- */
+
+/* GGML type ids (candle-core/src/quantized/mod.rs:300-342) accepted as `wtype`. */
+#define CQ_TYPE_Q4_0 2
+#define CQ_TYPE_Q8_0 8
+#define CQ_TYPE_Q4_K 12
+#define CQ_TYPE_Q6_K 14
+/* element types of dense inputs / outputs */
+#define CQ_ELEM_F32 0
+#define CQ_ELEM_F16 1
+#define CQ_ELEM_BF16 2
+/* activation encodings; all use 36 bytes per 32 elements, so candle's Q8_1 scratch sizing fits each one:
+ *   Q8_1: what candle's CUDA kernels use.
+ *   Q8_0: bit-identical values to candle's CPU BlockQ8_0::from_float (k_quants.rs:658-687); Q4_0/Q8_0 weights.
+ *   Q8_K: bit-identical values to candle's CPU BlockQ8K::from_float (k_quants.rs:2320-2358); K-quant weights.
+ * With the last two, GEMV results agree with candle's CPU vec_dot up to f32 summation order. */
+#define CQ_ACT_Q8_1_ENC 0
+#define CQ_ACT_Q8_0_ENC 1
+#define CQ_ACT_Q8_K_ENC 2
+
+/* status side channel: 0 ok, 1 bad argument, 2 unsupported, 3 CUDA error, 4 device-side timeout */
+int cq_last_status(void);
+int cq_last_cuda_error(void);
+const char *cq_last_message(void);
+void cq_clear_status(void);
+const char *cq_version(void);
+
+/* Quantize activation rows of element type `x_elem` into encoding `act`.  No counterpart with this
+ * generality in the reference; launch_mmvq_gguf_quantize_q8_1_* are the act = Q8_1 special cases. */
+void cq_quantize_act(const void *x, int x_elem, void *vy, int kx, int kx_padded, int num_rows, int act, void *stream);
+
+/* GEMV on any supported weight type / activation encoding / output element type; the twelve
+ * launch_mmvq_gguf_*_plain symbols forward here with act = Q8_1. */
+void cq_mmvq(int wtype, int act, int out_elem, const void *vx, const void *vy, void *dst, int ncols_x, int nrows_x,
+             int stride_col_y, int stride_col_dst, int b_size, void *stream);
+
+/* Exact integer dot products per (row, weight block) for ONE activation row: out[row*nblk + i]; for Q4_K
+ * out_min (nullable) receives the integer of the "min" term.  Diagnostic used by the parity tests. */
+void cq_block_dots(int wtype, int act, const void *vx, const void *vy, int *out, int *out_min, int ncols_x,
+                   int nrows_x, void *stream);
+
+/* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
+void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
+
+/* ------------------------------------------------------------------------------------------------
+ * 3. Host objects (C++ classes of candle_b200/csrc/host/qtensor.h behind opaque handles)
+ *    QTensor / QMatMul as in candle-core/src/quantized/mod.rs:59-66, 807-852, 1020-1043 and
+ *    QCudaStorage::{load_quantized, fwd, data} as in candle-core/src/quantized/cuda.rs:846-885, 989-1008.
+ *    Functions returning int give 0 on success, 1 on failure with the text in cqh_last_error().
+ * ---------------------------------------------------------------------------------------------- */
+const char *cqh_last_error(void);
+/* Upload GGUF blocks from host memory; dims = [n, k] for a weight matrix.  */
+int cqh_qtensor_load(int ggml_dtype, const void *host_bytes, size_t nbytes, const int64_t *dims, int ndims, int device,
+                     void **out_handle);
+/* Non-owning view of blocks that already live on the device. */
+int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int64_t *dims, int ndims, int device,
+                     void **out_handle);
+void cqh_qtensor_free(void *handle);
+int cqh_qtensor_data(void *handle, void *host_out, size_t nbytes);
+const void *cqh_qtensor_device_ptr(void *handle);
+/* QMatMul::forward: x [.., k] (device, contiguous, x_dtype = CQ_ELEM_*) -> out [.., n], same element type. */
+int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
+                        void *stream);
+/* 0: Q8_1 activations (candle's CUDA arithmetic, default); 1: activations quantized exactly like candle's CPU path. */
+void cqh_set_act_mode(int mode);
+int cqh_get_act_mode(void);
+/* Grow the per-device scratch ahead of time (it otherwise grows on demand with a synchronising cudaMalloc). */
+int cqh_workspace_reserve(int device, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CANDLE_Q_B200_H */
