@@ -95,6 +95,21 @@ void cq_mmvq(int wtype, int act, int out_elem, const void *vx, const void *vy, v
 void cq_block_dots(int wtype, int act, const void *vx, const void *vy, int *out, int *out_min, int ncols_x,
                    int nrows_x, void *stream);
 
+/* Decode matmul (quantize to Q8_1 + GEMV, the pair of launches candle's host makes for up to 8 rows) for
+ * callers that cannot allocate device memory: a server that has handed all of HBM to weights and KV cache, or a
+ * plugin boundary with nowhere to keep a workspace.  No counterpart in the reference, whose host always brings
+ * its own scratch.  The Q8_1 scratch is a fixed CQ_STATIC_SCRATCH_BYTES array inside the library image, present
+ * on every GPU that loads the library until the process exits.
+ *   vx: weights [nrows_x, ncols_x] GGUF blocks of `wtype`; x: [b_size, ncols_x] of x_elem; dst: [b_size, nrows_x]
+ *   of x_elem.  b_size <= 8 and b_size * pad(ncols_x, 512) / 32 * 36 <= CQ_STATIC_SCRATCH_BYTES, else the call
+ *   records CQ "unsupported" and launches nothing.
+ * Calls no cudaMalloc / cudaFree.  The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress): make that call before any stream capture.  All calls share the array and it keeps
+ * the previous call's contents (none of which is relied on); calls that can overlap on the GPU race on it. */
+#define CQ_STATIC_SCRATCH_BYTES (8 * (32768 / 32) * 36)
+void cq_qmatmul_decode_static(int wtype, const void *vx, const void *x, int x_elem, void *dst, int ncols_x, int nrows_x,
+                              int b_size, void *stream);
+
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
 
