@@ -327,14 +327,52 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """One GEMV case, a few launches, per-launch CUDA-event times: the small command the ncu captures profile.
+    --case TYPE:K:N:B, e.g. Q4K:4096:128256:1."""
+    import torch
+    from candle_b200 import capi
+    from candle_b200.quantized import GgmlDType
+    from candle_b200.synth import random_blocks
+    t, k, n, b = args.case.split(":")
+    k, n, b = int(k), int(n), int(b)
+    dev = torch.device("cuda:0")
+    L = capi.lib()
+    ncopies = max(2, min(16, int(300e6 // (n * k * BYTES_PER_ELEM[t])) + 1))     # rotate through > L2 of weights
+    ws = [random_blocks(GgmlDType[t], n, k, seed=i, device=dev) for i in range(ncopies)]
+    x = torch.randn((b, k), device=dev)
+    kp = capi.pad(k, 512)
+    y = torch.empty((b, kp // 32 * 36), dtype=torch.uint8, device=dev)
+    out = torch.empty((b, n), device=dev)
+    s = torch.cuda.current_stream().cuda_stream
+    L.cq_quantize_act(x.data_ptr(), capi.F32, y.data_ptr(), k, kp, b, capi.ACT_Q8_1, s)
+    times = []
+    for i in range(args.iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        L.cq_mmvq(int(GgmlDType[t]), capi.ACT_Q8_1, capi.F32, ws[i % ncopies].data_ptr(), y.data_ptr(), out.data_ptr(),
+                  k, n, kp // 32, n, b, s)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    capi.check("case")
+    nbytes = gemv_bytes(t, k, n, b)
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(json.dumps({"case": args.case, "us": times, "algorithmic_bytes": nbytes, "best_GBps": nbytes / best / 1e3}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
+    ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

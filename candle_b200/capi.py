@@ -48,6 +48,7 @@ def lib() -> C.CDLL:
         L.cq_mmvq.argtypes = [i32, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_block_dots.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, vp]
         L.cq_set_tuning.argtypes = [i32, i32]
+        L.cq_device_timeout_flag.restype = i32
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]

@@ -87,6 +87,41 @@ template <int N> __device__ __forceinline__ void cq_cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// ---- TMA bulk copy (cp.async.bulk) + mbarrier, with bounded waits ----
+__device__ __forceinline__ unsigned cq_smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cq_mbar_init(uint64_t *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(cq_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void cq_fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void cq_mbar_expect_tx(uint64_t *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cq_smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One thread copies `bytes` (multiple of 16, both addresses 16-byte aligned) from global to shared memory
+// through the TMA unit; completion is signalled on `bar` as transferred bytes.
+__device__ __forceinline__ void cq_bulk_g2s(void *smem_dst, const void *gmem_src, unsigned bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     cq_smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(cq_smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool cq_mbar_try_wait(uint64_t *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(cq_smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Wait for a phase of `bar`, giving up after about a second (2e9 SM cycles).  Returns false on give-up.
+__device__ __forceinline__ bool cq_mbar_wait_bounded(uint64_t *bar, unsigned parity) {
+    if (cq_mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!cq_mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
+    return true;
+}
+
 // Read NW consecutive 32-bit words that start at a 2-byte-aligned shared-memory address.
 // Reads one aligned word past the last one (callers keep 4 bytes of slack).
 template <int NW> __device__ __forceinline__ void cq_lds_words(const uint8_t *p, uint32_t (&out)[NW]) {

@@ -7,9 +7,9 @@
 // Design (HBM-bound, so everything serves coalesced streaming of the weight bytes):
 //   * a CTA owns one "K cover": thread t owns chunk t of every row (see gemv_chunks.cuh) and keeps the int8
 //     activations of that chunk for all batch rows in registers for the life of the kernel;
-//   * weight rows are contiguous in memory, so a batch of RB rows is one flat byte range that all threads
-//     copy into shared memory with 16-byte cp.async (L1 bypass), double buffered: the copy of batch i+1
-//     overlaps the arithmetic of batch i.  GGUF blocks of 18 / 34 / 210 bytes are only 2-byte aligned; the
+//   * weight rows are contiguous in memory, so a batch of RB rows is one flat, 16-byte aligned byte range that
+//     one thread hands to the TMA unit (cp.async.bulk, completion counted on an mbarrier), double buffered:
+//     the copy of batch i+1 overlaps the arithmetic of batch i, and no thread spends issue slots on copying.  GGUF blocks of 18 / 34 / 210 bytes are only 2-byte aligned; the
 //     flat copy does not care, and the 2-byte alignment is resolved when reading shared memory;
 //   * each lane produces RB*B partial sums; a transposing xor-butterfly leaves one finished warp total per
 //     lane (about one shuffle per value), warps are then added in index order through shared memory.
@@ -26,6 +26,9 @@ constexpr int kStages = 2;
 
 __host__ __device__ constexpr int next_pow2(int v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : v <= 8 ? 8 : v <= 16 ? 16 : 32; }
 
+// Set when a bounded wait on a staging barrier gave up (read with cq_device_timeout_flag()).
+__device__ int g_gemv_timeout_flag = 0;
+
 template <int TYPE, int ACT, int B, int RB>
 __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ y, void *__restrict__ dst,
                                    int out_kind, int nchunks, int nrows, int stride_col_y, int stride_col_dst,
@@ -33,8 +36,29 @@ __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t 
     constexpr int NV = next_pow2(RB * B);
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    float *red = reinterpret_cast<float *>(smem);                       // [2][nwarps][NV]
-    uint8_t *stages = smem + ((2 * nwarps * NV * 4 + 15) & ~15);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                 // one mbarrier per stage
+    float *red = reinterpret_cast<float *>(smem + 16);                   // [2][nwarps][NV]
+    uint8_t *stages = smem + 16 + ((2 * nwarps * NV * 4 + 15) & ~15);
+
+    if (tid == 0) {
+        cq_mbar_init(&bars[0], 1);
+        cq_mbar_init(&bars[1], 1);
+        cq_fence_mbar_init();
+    }
+    __syncthreads();
+
+    const int nbatches = (nrows + RB - 1) / RB;
+    // Stage a batch of rows: one flat, 16-byte aligned byte range copied by the TMA unit (one instruction).
+    auto issue = [&](int batch, int stage) {
+        const int row0 = batch * RB;
+        const int nr = min(RB, nrows - row0);
+        const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
+        const uintptr_t a0 = start & ~(uintptr_t)15;
+        const unsigned total = ((unsigned)(start - a0) + (unsigned)(nr * row_bytes) + 15u) & ~15u;
+        cq_mbar_expect_tx(&bars[stage], total);
+        cq_bulk_g2s(stages + stage * stage_stride, (const void *)a0, total, &bars[stage]);
+    };
+    if (tid == 0 && (int)blockIdx.x < nbatches) issue(blockIdx.x, 0);
 
     const bool active = tid < nchunks;
     ChunkAct<TYPE> act[B];
@@ -43,37 +67,27 @@ __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t 
         for (int j = 0; j < B; ++j) chunk_load_act<TYPE, ACT>(act[j], y + (int64_t)j * stride_col_y * CQ_Q8_BYTES, tid);
     }
 
-    const int nbatches = (nrows + RB - 1) / RB;
-    auto issue = [&](int batch, int stage) {
-        const int row0 = batch * RB;
-        const int nr = min(RB, nrows - row0);
-        const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
-        const uintptr_t a0 = start & ~(uintptr_t)15;
-        const int total = (int)(start - a0) + nr * row_bytes;
-        uint8_t *sdst = stages + stage * stage_stride;
-        for (int o = tid * 16; o < total; o += blockDim.x * 16) cq_cp_async16(sdst + o, (const void *)(a0 + o));
-    };
-
-    if ((int)blockIdx.x < nbatches) issue(blockIdx.x, 0);
-    cq_cp_async_commit();
-
     int it = 0;
+    bool pending_next = false;      // thread 0: a copy was issued that no iteration has consumed yet
     for (int batch = blockIdx.x; batch < nbatches; batch += gridDim.x, ++it) {
+        const int stage = it & 1;
         const int nxt = batch + gridDim.x;
-        if (nxt < nbatches) issue(nxt, (it + 1) % kStages);
-        cq_cp_async_commit();
-        cq_cp_async_wait<kStages - 1>();
-        __syncthreads();
+        // the other stage was last read in iteration it-1, which every thread left through a barrier
+        if (tid == 0) {
+            pending_next = nxt < nbatches;
+            if (pending_next) issue(nxt, stage ^ 1);
+        }
+        const bool ok = cq_mbar_wait_bounded(&bars[stage], (it >> 1) & 1);
 
         const int row0 = batch * RB;
         const int nr = min(RB, nrows - row0);
         const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
-        const uint8_t *srow = stages + (it % kStages) * stage_stride + (int)(start & 15);
+        const uint8_t *srow = stages + stage * stage_stride + (int)(start & 15);
 
         float v[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) v[i] = 0.0f;
-        if (active) {
+        if (active && ok) {
 #pragma unroll
             for (int r = 0; r < RB; ++r) {
                 if (r < nr) {
@@ -87,7 +101,14 @@ __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t 
         const float tot = cq_warp_reduce_many<NV>(v);
         float *rbuf = red + (it & 1) * nwarps * NV;
         if ((lane & (32 / NV - 1)) == 0) rbuf[warp * NV + lane / (32 / NV)] = tot;
-        __syncthreads();
+        const int failed = __syncthreads_or(!ok);
+        if (failed) {       // uniform across the CTA: record, drain, leave
+            if (tid == 0) {
+                atomicExch(&g_gemv_timeout_flag, 1);
+                if (pending_next) (void)cq_mbar_wait_bounded(&bars[stage ^ 1], ((it + 1) >> 1) & 1);
+            }
+            return;
+        }
         if (tid < RB * B) {
             float s = rbuf[tid];
             for (int wv = 1; wv < nwarps; ++wv) s += rbuf[wv * NV + tid];
@@ -95,7 +116,6 @@ __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t 
             if (r < nr) cq_store_out(dst, out_kind, (int64_t)j * stride_col_dst + row0 + r, s);
         }
     }
-    cq_cp_async_wait<0>();
 }
 
 // ---- host side ----
@@ -145,7 +165,7 @@ template <int TYPE, int ACT> bool make_plan(int K, int N, int B, Plan &p) {
     const int T = (nchunks + 31) / 32 * 32;
     if (T > 1024) return false;
     const DevInfo di = dev_info();
-    const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
+    const int row_bytes = K / cq_block_elems(ChunkGeom<TYPE>::BASE) * cq_type_size(ChunkGeom<TYPE>::BASE);
     const int nwarps = T / 32;
     bool found = false;
     for (int rbi = 3; rbi >= 0; --rbi) {
@@ -165,7 +185,7 @@ template <int TYPE, int ACT> bool make_plan(int K, int N, int B, Plan &p) {
         if (regs_cta > 65536) continue;
         const int nv = next_pow2(rb * B);
         const int stage = ((rb * row_bytes + 15 + 15) & ~15) + 16;
-        const int smem = ((2 * nwarps * nv * 4 + 15) & ~15) + kStages * stage;
+        const int smem = 16 + ((2 * nwarps * nv * 4 + 15) & ~15) + kStages * stage;
         if (smem > di.smem_optin) continue;
         int cps = 2048 / T;
         if (cps > 32) cps = 32;
@@ -175,8 +195,9 @@ template <int TYPE, int ACT> bool make_plan(int K, int N, int B, Plan &p) {
         if (g_force_ctas_per_sm && cps > g_force_ctas_per_sm) cps = g_force_ctas_per_sm;
         const int nbatches = (N + rb - 1) / rb;
         const int slots = di.sms * cps;
-        // take the largest row batch that still leaves every CTA slot at least two batches; else the smallest
-        const bool enough = nbatches >= 2 * slots;
+        // take the largest row batch that still leaves every CTA slot at least two batches and keeps at least
+        // 512 threads resident per SM; else the smallest
+        const bool enough = nbatches >= 2 * slots && (T * cps >= 512 || rb == 1);
         if (!found || enough || rb == 1 || g_force_rb) {
             p.k = &ke; p.T = T; p.RB = rb; p.smem = smem; p.stage_stride = stage;
             p.grid = nbatches < slots ? nbatches : slots;
@@ -199,7 +220,7 @@ bool launch_type(const void *w, const void *y, void *dst, int out_kind, int K, i
         cudaFuncSetAttribute((const void *)p.k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dev_info().smem_optin);
         p.k->attr_set[dev] = true;
     }
-    const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
+    const int row_bytes = K / cq_block_elems(ChunkGeom<TYPE>::BASE) * cq_type_size(ChunkGeom<TYPE>::BASE);
     p.k->fn<<<p.grid, p.T, p.smem, st>>>((const uint8_t *)w, (const uint8_t *)y, dst, out_kind,
                                           K / ChunkGeom<TYPE>::ELEMS, N, sy, sd, row_bytes, p.stage_stride);
     cq_check_launch("gemv");
@@ -247,8 +268,8 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
         case CQ_Q8_0:   // same formula for both encodings
             return launch_type<CQ_Q8_0, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
         case CQ_Q4_K:
-            return cpu_act ? launch_type<CQ_Q4_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
-                           : launch_type<CQ_Q4_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+            return cpu_act ? launch_type<CQ_Q4_K_WIDE, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q4_K_WIDE, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
         case CQ_Q6_K:
             return cpu_act ? launch_type<CQ_Q6_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
                            : launch_type<CQ_Q6_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
@@ -270,6 +291,14 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
 extern "C" void cq_set_tuning(int rows_per_batch, int ctas_per_sm) {
     g_force_rb = rows_per_batch;
     g_force_ctas_per_sm = ctas_per_sm;
+}
+
+// 1 if any GEMV launch on the current device gave up waiting for a staged copy (synchronises the device).
+extern "C" int cq_device_timeout_flag(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemv_timeout_flag, sizeof v) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+    if (v) cq_set_status(CQ_ERR_TIMEOUT, "gemv: a bounded wait on a staged weight copy gave up");
+    return v;
 }
 
 // The reference's twelve symbols for the four formats (candle-kernels/src/ffi.rs:61-393).

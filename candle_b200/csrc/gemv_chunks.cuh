@@ -19,11 +19,19 @@
 #pragma once
 #include "common.cuh"
 
+// Q4_K has a second, wider chunk geometry: 32 bytes of nibbles = the two whole 32-element sub-blocks of a
+// pair (64 elements).  It halves the per-byte cost of decoding the 6-bit scales; the GEMV uses it for every
+// batch size (so a row gives the same bits in any batch), the block-dot diagnostic uses the 32-element one.
+// Every dot() spells its f32 operations out (__fmul_rn / __fmaf_rn) so that all template instantiations round
+// in the same places.
+constexpr int CQ_Q4_K_WIDE = 1012;
+
 template <int TYPE> struct ChunkGeom;
-template <> struct ChunkGeom<CQ_Q4_0> { static constexpr int ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
-template <> struct ChunkGeom<CQ_Q8_0> { static constexpr int ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
-template <> struct ChunkGeom<CQ_Q4_K> { static constexpr int ELEMS = 32, Q8_BLOCKS = 2, WORDS = 8; };
-template <> struct ChunkGeom<CQ_Q6_K> { static constexpr int ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
+template <> struct ChunkGeom<CQ_Q4_0> { static constexpr int BASE = CQ_Q4_0, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q8_0> { static constexpr int BASE = CQ_Q8_0, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q4_K> { static constexpr int BASE = CQ_Q4_K, ELEMS = 32, Q8_BLOCKS = 2, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q4_K_WIDE> { static constexpr int BASE = CQ_Q4_K, ELEMS = 64, Q8_BLOCKS = 2, WORDS = 16; };
+template <> struct ChunkGeom<CQ_Q6_K> { static constexpr int BASE = CQ_Q6_K, ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
 
 // Activation registers of one chunk for one batch row.
 template <int TYPE> struct ChunkAct {
@@ -43,6 +51,8 @@ template <int TYPE> __device__ __forceinline__ void chunk_act_coords(int chunk, 
     else if constexpr (TYPE == CQ_Q4_K) {
         const int sb = chunk >> 3, c = chunk & 7;
         blk = sb * 8 + 2 * (c >> 1) + i; byte0 = 16 * (c & 1);
+    } else if constexpr (TYPE == CQ_Q4_K_WIDE) {
+        blk = 2 * chunk + i; byte0 = 0;     // chunk = 4 * super-block + pair
     } else {
         const int sb = chunk >> 2, n = (chunk >> 1) & 1, h = chunk & 1;
         blk = sb * 8 + 4 * n + i; byte0 = 16 * h;
@@ -72,7 +82,7 @@ __device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t 
         } else {
             const __half2 h2 = *reinterpret_cast<const __half2 *>(&ds);
             a.d[i] = __low2float(h2);
-            if constexpr (TYPE == CQ_Q4_K) a.s[i] = a.d[i] * (float)sq;
+            if constexpr (TYPE == CQ_Q4_K || TYPE == CQ_Q4_K_WIDE) a.s[i] = a.d[i] * (float)sq;
             else a.s[i] = __high2float(h2);
         }
     }
@@ -101,8 +111,8 @@ template <> struct ChunkW<CQ_Q4_0> {
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_0> &a) const {
         const int s = idot(a);
-        if constexpr (ACT == CQ_ACT_Q8_1) return d * ((float)s * a.d[0] - 8.0f * a.s[0]);
-        else return (float)(s - 8 * a.sq[0]) * d * a.d[0];
+        if constexpr (ACT == CQ_ACT_Q8_1) return __fmul_rn(d, __fmaf_rn((float)s, a.d[0], __fmul_rn(-8.0f, a.s[0])));
+        else return __fmul_rn(__fmul_rn((float)(s - 8 * a.sq[0]), d), a.d[0]);
     }
 };
 
@@ -121,7 +131,7 @@ template <> struct ChunkW<CQ_Q8_0> {
         return s;
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q8_0> &a) const {
-        return (float)idot(a) * d * a.d[0];
+        return __fmul_rn(__fmul_rn((float)idot(a), d), a.d[0]);
     }
 };
 
@@ -159,13 +169,65 @@ template <> struct ChunkW<CQ_Q4_K> {
         int d0, d1;
         idots(a, d0, d1);
         if constexpr (ACT == CQ_ACT_Q8_1) {
-            const float sd = a.d[0] * (float)(d0 * sc[0]) + a.d[1] * (float)(d1 * sc[1]);
-            const float sm = a.s[0] * (float)mn[0] + a.s[1] * (float)mn[1];
-            return d * sd - dmin * sm;
+            const float sd = __fmaf_rn(a.d[1], (float)(d1 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
+            const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
+            return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
         } else {
             const int isd = d0 * sc[0] + d1 * sc[1];
             const int ism = a.sq[0] * mn[0] + a.sq[1] * mn[1];
-            return a.d[0] * (d * (float)isd - dmin * (float)ism);
+            return __fmul_rn(a.d[0], __fmaf_rn(d, (float)isd, -__fmul_rn(dmin, (float)ism)));
+        }
+    }
+};
+
+// 6-bit scales / mins of sub-blocks 2jp and 2jp+1 of a Q4_K super-block at `b`
+// (layout: candle-core/src/quantized/utils.rs:50-60).  Returns them packed as two bytes each.
+__device__ __forceinline__ void q4k_pair_scales(const uint8_t *b, int jp, uint32_t &scp, uint32_t &mnp) {
+    const uint32_t s_hi = cq_lds_u16(b + 4 + 2 * (jp + 2));          // bytes 2jp+4, 2jp+5
+    const uint32_t s_lo = cq_lds_u16(b + 4 + 2 * jp);                // bytes 2jp,   2jp+1
+    const uint32_t s_pp = cq_lds_u16(b + 4 + 2 * (jp & 1));          // bytes 2jp-4, 2jp-3 when jp >= 2
+    if (jp < 2) { scp = s_lo & 0x3f3fu; mnp = s_hi & 0x3f3fu; }
+    else {
+        scp = (s_hi & 0x0f0fu) | ((s_pp & 0xc0c0u) >> 2);
+        mnp = ((s_hi >> 4) & 0x0f0fu) | ((s_lo & 0xc0c0u) >> 2);
+    }
+}
+
+template <> struct ChunkW<CQ_Q4_K_WIDE> {
+    uint32_t lo[8], hi16[8];    // low nibbles; high nibbles left in place (value * 16)
+    float d, dmin;
+    int sc[2], mn[2];
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const int sb = chunk >> 2, jp = chunk & 3;
+        const uint8_t *b = row + sb * 144;
+        const __half2 dm = *reinterpret_cast<const __half2 *>(b);
+        d = __low2float(dm); dmin = __high2float(dm);
+        uint32_t scp, mnp;
+        q4k_pair_scales(b, jp, scp, mnp);
+        sc[0] = scp & 0xFF; sc[1] = scp >> 8; mn[0] = mnp & 0xFF; mn[1] = mnp >> 8;
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(b + 16 + 32 * jp);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(b + 32 + 32 * jp);
+        const uint32_t qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { lo[w] = qq[w] & 0x0F0F0F0Fu; hi16[w] = qq[w] & 0xF0F0F0F0u; }
+    }
+    // d0: dot of sub-block 2jp; d1x16: 16 x dot of sub-block 2jp+1 (unsigned-byte dp4a on the unshifted nibbles)
+    __device__ __forceinline__ void idots(const ChunkAct<CQ_Q4_K_WIDE> &a, int &d0, int &d1x16) const {
+        d0 = 0; d1x16 = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { d0 = cq_dp4a((int)lo[w], a.u[w], d0); d1x16 = cq_dp4a_u(hi16[w], a.u[8 + w], d1x16); }
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_K_WIDE> &a) const {
+        int d0, d1x16;
+        idots(a, d0, d1x16);
+        if constexpr (ACT == CQ_ACT_Q8_1) {
+            const float sd = __fmaf_rn(__fmul_rn(a.d[1], 0.0625f), (float)(d1x16 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
+            const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
+            return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
+        } else {
+            const int isd = d0 * sc[0] + (d1x16 >> 4) * sc[1];
+            const int ism = a.sq[0] * mn[0] + a.sq[1] * mn[1];
+            return __fmul_rn(a.d[0], __fmaf_rn(d, (float)isd, -__fmul_rn(dmin, (float)ism)));
         }
     }
 };
@@ -204,13 +266,13 @@ template <> struct ChunkW<CQ_Q6_K> {
         if constexpr (ACT == CQ_ACT_Q8_1) {
             float sf = 0.0f;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) sf += a.d[p] * (float)(idot(a, p) * sc[p]);
-            return d * sf;
+            for (int p = 0; p < 4; ++p) sf = __fmaf_rn(a.d[p], (float)(idot(a, p) * sc[p]), sf);
+            return __fmul_rn(d, sf);
         } else {
             int is = 0;
 #pragma unroll
             for (int p = 0; p < 4; ++p) is += idot(a, p) * sc[p];
-            return a.d[0] * d * (float)is;
+            return __fmul_rn(__fmul_rn(a.d[0], d), (float)is);
         }
     }
 };

@@ -112,6 +112,9 @@ void cq_qmatmul_decode_static(int wtype, const void *vx, const void *x, int x_el
 
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
+/* 1 if a GEMV on the current device gave up a bounded wait for a staged copy (then also sets status 4).
+ * Synchronises the device. */
+int cq_device_timeout_flag(void);
 
 /* ------------------------------------------------------------------------------------------------
  * 3. Host objects (C++ classes of candle_b200/csrc/host/qtensor.h behind opaque handles)
