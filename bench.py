@@ -361,8 +361,37 @@ def run_case(args):
     print(json.dumps({"case": args.case, "us": times, "algorithmic_bytes": nbytes, "best_GBps": nbytes / best / 1e3}))
 
 
+def run_prefill_case(args):
+    """One prefill GEMM case: --prefill-case M:K:N (Q4_K), a few launches with CUDA-event times (profiling helper)."""
+    import torch
+    from candle_b200 import capi
+    from candle_b200.quantized import GgmlDType
+    from candle_b200.synth import random_blocks
+    m, k, n = (int(v) for v in args.prefill_case.split(":"))
+    dev = torch.device("cuda:0")
+    L = capi.lib()
+    w = random_blocks(GgmlDType.Q4K, n, k, seed=1, device=dev)
+    x = torch.randn((m, k), device=dev)
+    scratch = torch.empty(L.cq_prefill_scratch_bytes(m, k), dtype=torch.uint8, device=dev)
+    out = torch.empty((m, n), device=dev)
+    s = torch.cuda.current_stream().cuda_stream
+    L.cq_prefill_quantize(x.data_ptr(), capi.F32, scratch.data_ptr(), k, m, s)
+    times = []
+    for _ in range(args.iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        L.cq_prefill_gemm(int(GgmlDType.Q4K), w.data_ptr(), scratch.data_ptr(), out.data_ptr(), capi.F32, k, n, m, n, s)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    capi.check("prefill case")
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(json.dumps({"prefill_case": args.prefill_case, "ms": times, "useful_TOPS": 2.0 * m * n * k / best / 1e9}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--gpus", type=int, default=1)
@@ -370,7 +399,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
-    if args.case:
+    if args.prefill_case:
+        run_prefill_case(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -49,6 +49,12 @@ def lib() -> C.CDLL:
         L.cq_block_dots.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, vp]
         L.cq_set_tuning.argtypes = [i32, i32]
         L.cq_device_timeout_flag.restype = i32
+        L.cq_prefill_scratch_bytes.argtypes = [i32, i32]
+        L.cq_prefill_scratch_bytes.restype = C.c_size_t
+        L.cq_prefill_quantize.argtypes = [vp, i32, vp, i32, i32, vp]
+        L.cq_prefill_gemm.argtypes = [i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.cq_prefill_timeout_flag.restype = i32
+        L.cq_prefill_set_debug.argtypes = [i32]
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]

@@ -15,127 +15,36 @@
 //     lane (about one shuffle per value), warps are then added in index order through shared memory.
 //     The order of additions for one output does not depend on RB, on the grid or on N, so a row gives the
 //     same bits whether the matrix is whole or sharded by rows across GPUs, and whatever the batch size.
-#include <mutex>
-
 #include "../../include/candle_q_b200.h"
-#include "gemv_chunks.cuh"
+#include "gemv_body.cuh"
+#include "gemv_plan.cuh"
 
 namespace {
 
-constexpr int kStages = 2;
-
-__host__ __device__ constexpr int next_pow2(int v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : v <= 8 ? 8 : v <= 16 ? 16 : 32; }
-
 // Set when a bounded wait on a staging barrier gave up (read with cq_device_timeout_flag()).
 __device__ int g_gemv_timeout_flag = 0;
+
+struct DenseMap {       // batch column j: activation row j, output row j, no scaling
+    const uint8_t *y;
+    int stride_col_y, stride_col_dst;
+    __device__ __forceinline__ const uint8_t *act_row(int j) const { return y + (int64_t)j * stride_col_y * CQ_Q8_BYTES; }
+    __device__ __forceinline__ int64_t out_offset(int j) const { return (int64_t)j * stride_col_dst; }
+    __device__ __forceinline__ float scale(int) const { return 1.0f; }
+    __device__ __forceinline__ bool valid(int) const { return true; }
+};
 
 template <int TYPE, int ACT, int B, int RB>
 __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ y, void *__restrict__ dst,
                                    int out_kind, int nchunks, int nrows, int stride_col_y, int stride_col_dst,
                                    int row_bytes, int stage_stride) {
-    constexpr int NV = next_pow2(RB * B);
-    extern __shared__ __align__(16) uint8_t smem[];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                 // one mbarrier per stage
-    float *red = reinterpret_cast<float *>(smem + 16);                   // [2][nwarps][NV]
-    uint8_t *stages = smem + 16 + ((2 * nwarps * NV * 4 + 15) & ~15);
-
-    if (tid == 0) {
-        cq_mbar_init(&bars[0], 1);
-        cq_mbar_init(&bars[1], 1);
-        cq_fence_mbar_init();
-    }
-    __syncthreads();
-
-    const int nbatches = (nrows + RB - 1) / RB;
-    // Stage a batch of rows: one flat, 16-byte aligned byte range copied by the TMA unit (one instruction).
-    auto issue = [&](int batch, int stage) {
-        const int row0 = batch * RB;
-        const int nr = min(RB, nrows - row0);
-        const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
-        const uintptr_t a0 = start & ~(uintptr_t)15;
-        const unsigned total = ((unsigned)(start - a0) + (unsigned)(nr * row_bytes) + 15u) & ~15u;
-        cq_mbar_expect_tx(&bars[stage], total);
-        cq_bulk_g2s(stages + stage * stage_stride, (const void *)a0, total, &bars[stage]);
-    };
-    if (tid == 0 && (int)blockIdx.x < nbatches) issue(blockIdx.x, 0);
-
-    const bool active = tid < nchunks;
-    ChunkAct<TYPE> act[B];
-    if (active) {
-#pragma unroll
-        for (int j = 0; j < B; ++j) chunk_load_act<TYPE, ACT>(act[j], y + (int64_t)j * stride_col_y * CQ_Q8_BYTES, tid);
-    }
-
-    int it = 0;
-    bool pending_next = false;      // thread 0: a copy was issued that no iteration has consumed yet
-    for (int batch = blockIdx.x; batch < nbatches; batch += gridDim.x, ++it) {
-        const int stage = it & 1;
-        const int nxt = batch + gridDim.x;
-        // the other stage was last read in iteration it-1, which every thread left through a barrier
-        if (tid == 0) {
-            pending_next = nxt < nbatches;
-            if (pending_next) issue(nxt, stage ^ 1);
-        }
-        const bool ok = cq_mbar_wait_bounded(&bars[stage], (it >> 1) & 1);
-
-        const int row0 = batch * RB;
-        const int nr = min(RB, nrows - row0);
-        const uintptr_t start = (uintptr_t)w + (uintptr_t)row0 * row_bytes;
-        const uint8_t *srow = stages + stage * stage_stride + (int)(start & 15);
-
-        float v[NV];
-#pragma unroll
-        for (int i = 0; i < NV; ++i) v[i] = 0.0f;
-        if (active && ok) {
-#pragma unroll
-            for (int r = 0; r < RB; ++r) {
-                if (r < nr) {
-                    ChunkW<TYPE> cw;
-                    cw.load(srow + r * row_bytes, tid);
-#pragma unroll
-                    for (int j = 0; j < B; ++j) v[r * B + j] = cw.template dot<ACT>(act[j]);
-                }
-            }
-        }
-        const float tot = cq_warp_reduce_many<NV>(v);
-        float *rbuf = red + (it & 1) * nwarps * NV;
-        if ((lane & (32 / NV - 1)) == 0) rbuf[warp * NV + lane / (32 / NV)] = tot;
-        const int failed = __syncthreads_or(!ok);
-        if (failed) {       // uniform across the CTA: record, drain, leave
-            if (tid == 0) {
-                atomicExch(&g_gemv_timeout_flag, 1);
-                if (pending_next) (void)cq_mbar_wait_bounded(&bars[stage ^ 1], ((it + 1) >> 1) & 1);
-            }
-            return;
-        }
-        if (tid < RB * B) {
-            float s = rbuf[tid];
-            for (int wv = 1; wv < nwarps; ++wv) s += rbuf[wv * NV + tid];
-            const int r = tid / B, j = tid % B;
-            if (r < nr) cq_store_out(dst, out_kind, (int64_t)j * stride_col_dst + row0 + r, s);
-        }
-    }
+    const DenseMap map{y, stride_col_y, stride_col_dst};
+    gemv_body<TYPE, ACT, B, RB>(w, map, dst, out_kind, nchunks, nrows, row_bytes, stage_stride, (int)blockIdx.x,
+                                (int)gridDim.x, &g_gemv_timeout_flag);
 }
 
 // ---- host side ----
 
-struct DevInfo { int sms = 0; int smem_optin = 0; };
-DevInfo dev_info() {
-    static std::mutex mu;
-    static DevInfo cache[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    std::lock_guard<std::mutex> lk(mu);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (cache[dev].sms == 0) {
-        cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaDeviceGetAttribute(&cache[dev].smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        if (cache[dev].sms <= 0) cache[dev].sms = 148;
-        if (cache[dev].smem_optin <= 0) cache[dev].smem_optin = 227 * 1024;
-    }
-    return cache[dev];
-}
+using namespace cq_plan;
 
 // tuning overrides for experiments (0 = automatic)
 int g_force_rb = 0;
@@ -143,69 +52,23 @@ int g_force_ctas_per_sm = 0;
 
 using GemvKernel = void (*)(const uint8_t *, const uint8_t *, void *, int, int, int, int, int, int, int);
 
-struct KernelEntry { GemvKernel fn = nullptr; int regs = 0; bool attr_set[64] = {}; };
-
 // Table of instantiations for one (weight type, activation encoding): [batch 1..8][RB index: 1,2,4,8].
 template <int TYPE, int ACT> struct KernelTable {
     KernelEntry e[8][4];
     template <int B, int RBI> void fill_one() {
         constexpr int RB = 1 << RBI;
-        if constexpr (RB * B <= 32) e[B - 1][RBI].fn = gemv_staged_kernel<TYPE, ACT, B, RB>;
+        if constexpr (RB * B <= 32) e[B - 1][RBI].fn = (const void *)gemv_staged_kernel<TYPE, ACT, B, RB>;
     }
     template <int B> void fill_b() { fill_one<B, 0>(); fill_one<B, 1>(); fill_one<B, 2>(); fill_one<B, 3>(); }
     KernelTable() { fill_b<1>(); fill_b<2>(); fill_b<3>(); fill_b<4>(); fill_b<5>(); fill_b<6>(); fill_b<7>(); fill_b<8>(); }
 };
 
-struct Plan { KernelEntry *k; int T, RB, grid, smem, stage_stride; };
-
 template <int TYPE, int ACT> bool make_plan(int K, int N, int B, Plan &p) {
     static KernelTable<TYPE, ACT> table;
-    static std::mutex mu;
     const int nchunks = K / ChunkGeom<TYPE>::ELEMS;
     const int T = (nchunks + 31) / 32 * 32;
-    if (T > 1024) return false;
-    const DevInfo di = dev_info();
     const int row_bytes = K / cq_block_elems(ChunkGeom<TYPE>::BASE) * cq_type_size(ChunkGeom<TYPE>::BASE);
-    const int nwarps = T / 32;
-    bool found = false;
-    for (int rbi = 3; rbi >= 0; --rbi) {
-        const int rb = 1 << rbi;
-        KernelEntry &ke = table.e[B - 1][rbi];
-        if (!ke.fn) continue;
-        if (g_force_rb && rb != g_force_rb) continue;
-        {
-            std::lock_guard<std::mutex> lk(mu);
-            if (ke.regs == 0) {
-                cudaFuncAttributes fa;
-                if (cudaFuncGetAttributes(&fa, (const void *)ke.fn) != cudaSuccess) { (void)cudaGetLastError(); continue; }
-                ke.regs = fa.numRegs;
-            }
-        }
-        const int regs_cta = ((ke.regs + 7) & ~7) * T;     // registers are allocated in units of 8 per thread
-        if (regs_cta > 65536) continue;
-        const int nv = next_pow2(rb * B);
-        const int stage = ((rb * row_bytes + 15 + 15) & ~15) + 16;
-        const int smem = 16 + ((2 * nwarps * nv * 4 + 15) & ~15) + kStages * stage;
-        if (smem > di.smem_optin) continue;
-        int cps = 2048 / T;
-        if (cps > 32) cps = 32;
-        if ((228 * 1024) / (smem + 1024) < cps) cps = (228 * 1024) / (smem + 1024);
-        if (65536 / regs_cta < cps) cps = 65536 / regs_cta;
-        if (cps < 1) cps = 1;
-        if (g_force_ctas_per_sm && cps > g_force_ctas_per_sm) cps = g_force_ctas_per_sm;
-        const int nbatches = (N + rb - 1) / rb;
-        const int slots = di.sms * cps;
-        // take the largest row batch that still leaves every CTA slot at least two batches and keeps at least
-        // 512 threads resident per SM; else the smallest
-        const bool enough = nbatches >= 2 * slots && (T * cps >= 512 || rb == 1);
-        if (!found || enough || rb == 1 || g_force_rb) {
-            p.k = &ke; p.T = T; p.RB = rb; p.smem = smem; p.stage_stride = stage;
-            p.grid = nbatches < slots ? nbatches : slots;
-            found = true;
-            if (enough || g_force_rb) break;
-        }
-    }
-    return found;
+    return choose_plan(table.e[B - 1], T, row_bytes, N, B, 1, g_force_rb, g_force_ctas_per_sm, p);
 }
 
 // Returns false when no instantiation fits `B` batch rows in one pass (register file), so the caller splits.
@@ -214,14 +77,9 @@ bool launch_type(const void *w, const void *y, void *dst, int out_kind, int K, i
                  cudaStream_t st) {
     Plan p;
     if (!make_plan<TYPE, ACT>(K, N, B, p)) return false;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !p.k->attr_set[dev]) {
-        cudaFuncSetAttribute((const void *)p.k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dev_info().smem_optin);
-        p.k->attr_set[dev] = true;
-    }
+    ensure_smem_attr(p.k);
     const int row_bytes = K / cq_block_elems(ChunkGeom<TYPE>::BASE) * cq_type_size(ChunkGeom<TYPE>::BASE);
-    p.k->fn<<<p.grid, p.T, p.smem, st>>>((const uint8_t *)w, (const uint8_t *)y, dst, out_kind,
+    ((GemvKernel)p.k->fn)<<<p.grid, p.T, p.smem, st>>>((const uint8_t *)w, (const uint8_t *)y, dst, out_kind,
                                           K / ChunkGeom<TYPE>::ELEMS, N, sy, sd, row_bytes, p.stage_stride);
     cq_check_launch("gemv");
     return true;

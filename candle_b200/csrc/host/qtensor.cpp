@@ -185,8 +185,17 @@ void QCudaStorage::fwd(size_t n, size_t k, const void *x, DType x_dtype, const i
     const size_t row_q8 = k_padded / 32 * 36;
     const size_t xs = dtype_size(x_dtype);
 
-    // Decode path: up to 8 rows per launch.  Larger inputs are walked in slices of 8 rows until the
-    // tensor-core prefill kernel takes them over (see cq_mmq below when present).
+    // Prefill path: many rows of a Q4_K matrix go to the tensor-core kernel.  It quantizes activations like
+    // candle's CPU path (Q8_K) in every mode: that is the arithmetic the int8 planes are exact for.
+    if (rows > kPrefillMinRows && dtype_ == GgmlDType::Q4K) {
+        const size_t need = cq_prefill_scratch_bytes((int)rows, (int)k);
+        uint8_t *scratch = (uint8_t *)workspace_ensure(device_, need);
+        cq_prefill_quantize(x, (int)x_dtype, scratch, (int)k, (int)rows, stream);
+        cq_prefill_gemm((int)dtype_, ptr_, scratch, out, (int)x_dtype, (int)k, (int)n, (int)rows, (int)n, stream);
+        lib_check("qmatmul prefill");
+        return;
+    }
+    // Decode path: up to 8 rows per launch.  Other formats with more rows are walked in slices of 8 rows.
     const size_t chunk = MMVQ_MAX_BATCH;
     uint8_t *scratch = (uint8_t *)workspace_ensure(device_, (rows < chunk ? rows : chunk) * row_q8);
     for (size_t r0 = 0; r0 < rows; r0 += chunk) {

@@ -1,0 +1,475 @@
+// Prefill-path quantized GEMM for B200: out[t, r] = sum_k x[t, k] * W[r, k] for many tokens, Q4_K weights,
+// on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in TMEM).
+//
+// Replaces candle's MMQ path for this format (host: candle-core/src/quantized/fast_mmq.rs:253-400; kernels:
+// candle-kernels/src/mmq_gguf/mmq_gguf.cuh:3442-3777 with int8 mma.sync, mmq_quantize.cu:11-107).
+//
+// Arithmetic.  Activations are quantized like candle's CPU path: one f32 scale per 256 elements (BlockQ8K,
+// candle-core/src/quantized/k_quants.rs:2320-2358), bit-identical int8 values.  For one super-block the CPU
+// vec_dot (k_quants.rs:1460-1540) computes
+//      d_w * d_a * sum_g sc_g * (q4_g . q8_g)  -  dmin_w * d_a * sum_g m_g * sum(q8_g)
+// with 6-bit sc_g, m_g per 32-element sub-block.  Per-32 scales cannot be applied inside a tensor-core
+// accumulation, so they are folded into the int8 weight operand instead.  With sc = 8*sh + sl (3 bits each)
+// three int8 "planes" are built from every weight row:
+//      P1[k] = sl_g * q4[k]   (<= 105)      P2[k] = sh_g * q4[k]   (<= 105)      Mn[k] = m_g   (<= 63)
+// and  sum_g sc_g (q4_g . q8_g) = 8 * (P2 . q8) + (P1 . q8),   sum_g m_g sum(q8_g) = Mn . q8   exactly, in int32.
+// So a whole super-block (8 K-steps of 32) accumulates in TMEM and is scaled once, in f32, when it is drained.
+//
+// Mapping.  MMA M = 128 tokens (operand A = int8 activations, already laid out for the tensor core by the
+// quantize kernel, fetched with TMA bulk copies), MMA N = 3 planes x 64 weight rows = 192 (operand B, unpacked from
+// the GGUF bytes by four producer warps).  Planes sit side by side in the accumulator columns, so the epilogue
+// thread that owns a token holds all three values of every weight row and combines them locally.  Two TMEM
+// accumulator buffers (2 x 192 columns) and two shared-memory stages let unpacking, MMA and epilogue of
+// consecutive super-blocks overlap.  Warp roles: 0-3 epilogue (TMEM lane quadrant = warp), 4-7 producers, 8 MMA,
+// 9 activation loader (TMA).
+//
+// Every wait is bounded (about a second); a give-up raises a CTA-wide abort flag, all roles leave their loops,
+// TMEM is released and a device flag is set for the host.
+#include "../../include/candle_q_b200.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTokTile = 128;      // MMA M
+constexpr int kRowTile = 64;       // weight rows per CTA
+constexpr int kPlanes = 3;
+constexpr int kN = kPlanes * kRowTile;                 // MMA N = 192
+constexpr int kSlabA = kTokTile * 16;                  // bytes of one 16-byte-wide K slab of A in shared memory
+constexpr int kSlabB = kN * 16;
+constexpr int kStageA = 16 * kSlabA;                   // 32 KiB: 128 tokens x 256 int8
+constexpr int kStageB = 16 * kSlabB;                   // 48 KiB: 192 rows x 256 int8
+constexpr int kStagesA = 3, kStagesB = 2;
+constexpr int kThreads = 10 * 32;
+constexpr int kSmemBytes = 1024 + kStagesA * kStageA + kStagesB * kStageB + 2 * 8 * 512;
+
+__device__ int g_prefill_timeout_flag = 0;
+int g_prefill_dbg = 0;   // experiment switch: bit 0 skips the producers' work, bit 1 the epilogue's (results are then garbage)
+
+// ---- tcgen05 wrappers ----
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, int ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cq_smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, int ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cq_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cq_smem_u32(bar)) : "memory");
+}
+
+// K-major operand without swizzle: 8-row x 16-byte core matrices; LBO = distance between the two 16-byte halves
+// of a 32-byte K step, SBO = distance between 8-row groups (cute::UMMA::SmemDescriptor field layout).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;        // descriptor version of sm_100
+    return d;                      // layout type 0 = no swizzle
+}
+// kind::i8 instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N and M encoded as N>>3, M>>4.
+constexpr uint32_t make_idesc_i8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// int32 -> f32 for |x| < 2^22 without the conversion unit: one integer add and one float add, both exact.
+// (The plane sums are bounded by 7*15*128*256 = 3.44e6 and 63*128*256 = 2.06e6.)  cvt.rn.f32.s32 runs on the
+// quarter-rate XU pipe, which the epilogue would otherwise saturate.
+__device__ __forceinline__ float small_int_to_float(int x) {
+    return __fadd_rn(__int_as_float(x + 0x4B400000), -12582912.0f);
+}
+
+// Wait on `bar` unless the CTA has been aborted; raises the abort flag itself after about a second.
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, unsigned parity, volatile int *abort_flag) {
+    if (cq_mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!cq_mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 2000000000LL) { *abort_flag = 1; return false; }
+    }
+    return true;
+}
+
+struct TileBlob {   // where the activations of (token tile, super-block) live in the scratch
+    __host__ __device__ static size_t tile_rows(int tokens, int tt) {
+        const int left = tokens - tt * kTokTile;
+        const int r = left < kTokTile ? left : kTokTile;
+        return (size_t)((r + 7) / 8 * 8);
+    }
+    __host__ __device__ static size_t offset(int tokens, int nsb, int tt, int sb) {
+        return (size_t)tt * kTokTile * 260 * nsb + (size_t)sb * tile_rows(tokens, tt) * 260;
+    }
+};
+
+// ---- activation quantize into tensor-core tiles ---------------------------------------------------------
+// One warp per (token, super-block): BlockQ8K values (see quantize_act.cu for the rules), written so that the
+// bytes of 8 consecutive tokens x 16 consecutive k form one 128-byte core matrix.
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_q8k_tiles_kernel(const T *__restrict__ x, uint8_t *__restrict__ y, int k,
+                                                                 int tokens) {
+    const int lane = threadIdx.x & 31;
+    const int nsb = k / 256;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (int64_t)tokens * nsb) return;
+    const int tok = (int)(item / nsb), sb = (int)(item % nsb);
+    const T *xr = x + (int64_t)tok * k + sb * 256 + lane * 8;
+    float e[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) e[c] = cq_elem_to_float(xr, c);
+    float amax = 0.0f, vmax = 0.0f;
+    int imax = 0x7fffffff;
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+        if (amax < fabsf(e[c])) { amax = fabsf(e[c]); vmax = e[c]; imax = lane * 8 + c; }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, m);
+        const float ov = __shfl_xor_sync(0xffffffffu, vmax, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, imax, m);
+        if (oa > amax || (oa == amax && oi < imax)) { amax = oa; vmax = ov; imax = oi; }
+    }
+    int q[8];
+    float d = 0.0f;
+    if (amax == 0.0f) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) q[c] = 0;
+    } else {
+        const float iscale = __fdiv_rn(-127.0f, vmax);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float r = roundf(__fmul_rn(iscale, e[c]));
+            r = fminf(fmaxf(r, -128.0f), 127.0f);
+            q[c] = (int)r;
+        }
+        d = __fdiv_rn(1.0f, iscale);
+    }
+    const int tt = tok / kTokTile, tl = tok % kTokTile;
+    const size_t rows = TileBlob::tile_rows(tokens, tt);
+    uint8_t *blob = y + TileBlob::offset(tokens, nsb, tt, sb);
+    // lane holds k bytes [8*lane, 8*lane+8): slab lane/2, byte offset 8*(lane&1) inside the token's 16 bytes
+    int2 packed;
+    packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
+    packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+    *reinterpret_cast<int2 *>(blob + (size_t)(lane >> 1) * rows * 16 + (size_t)tl * 16 + 8 * (lane & 1)) = packed;
+    if (lane == 0) *reinterpret_cast<float *>(blob + rows * 256 + (size_t)tl * 4) = d;
+}
+
+// ---- the GEMM ---------------------------------------------------------------------------------------------
+// Shared memory: [control 1 KiB][A: 3 stages x 32 KiB][B: 2 stages x 48 KiB][d_a ring 8 x 512 B][(d, dmin) ring 8 x 512 B]
+// Dependencies per super-block sb (P_A / P_B producers, M = MMA, E = epilogue):
+//   P_A(sb) after M(sb-3) [bar_doneA]     P_B(sb) after M(sb-2) [bar_acc]      M(sb) after P_A(sb), P_B(sb), E(sb-2)
+//   E(sb) after M(sb) [bar_acc] and after the relay arrive on bar_vis, which carries the visibility of the scale rings.
+// The scale rings are 8 deep: an entry is rewritten for sb+8 only after M(sb+5), which itself waited for E(sb+3).
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_q4k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, void *__restrict__ out_v, int out_kind, int k,
+                   int nrows, int tokens, int stride_out, int dbg) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t *bar_fullA = reinterpret_cast<uint64_t *>(smem);         // [3] activations landed (TMA bytes)
+    uint64_t *bar_fullB = bar_fullA + 3;                               // [2] weight planes written (128 producer threads)
+    uint64_t *bar_acc = bar_fullA + 5;                                 // [2] MMAs of a super-block complete
+    uint64_t *bar_doneA = bar_fullA + 7;                               // [3] same event, tracked per A stage
+    uint64_t *bar_free = bar_fullA + 10;                               // [2] accumulator buffer drained (128 epilogue threads)
+    uint64_t *bar_vis = bar_fullA + 12;                                // [2] relay: scale rings of this super-block are visible
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 128);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 136);
+    uint8_t *stA0 = smem + 1024;
+    uint8_t *stB0 = stA0 + kStagesA * kStageA;
+    uint8_t *ringA = stB0 + kStagesB * kStageB;        // d_a: [8][128] f32
+    uint8_t *ringW = ringA + 8 * 512;                  // (d, dmin): [8][64] float2
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nsb = k / 256;
+    const int row0 = blockIdx.x * kRowTile;
+    const int tt = blockIdx.y;
+    const int tile_rows = (int)TileBlob::tile_rows(tokens, tt);
+    const int row_bytes = nsb * 144;
+
+    if (tid == 0) {
+        for (int i = 0; i < 3; ++i) { cq_mbar_init(&bar_fullA[i], 1); cq_mbar_init(&bar_doneA[i], 1); }
+        for (int i = 0; i < 2; ++i) {
+            cq_mbar_init(&bar_fullB[i], 128);
+            cq_mbar_init(&bar_acc[i], 1);
+            cq_mbar_init(&bar_free[i], 128);
+            cq_mbar_init(&bar_vis[i], 1);
+        }
+        *abort_flag = 0;
+        cq_fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 4 && warp < 8) {
+        // ===== producers =====
+        const int p = tid - 128;
+        const int r = p & 63, h = p >> 6;
+        int grow = row0 + r;
+        if (grow >= nrows) grow = nrows - 1;        // ragged last tile: duplicate a valid row, never stored
+        const uint8_t *wrow = w + (size_t)grow * row_bytes;
+        // the GGUF bytes of the next super-block are fetched one iteration ahead of their use
+        uint4 n_hdr = *reinterpret_cast<const uint4 *>(wrow);
+        uint4 n_q[4];
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) n_q[jp] = *reinterpret_cast<const uint4 *>(wrow + 16 + 32 * jp + 16 * h);
+        for (int sb = 0; sb < nsb; ++sb) {
+            const int s = sb & 1;
+            uint8_t *stB = stB0 + s * kStageB;
+            if (dbg & 1) {
+                if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
+                mbar_arrive(&bar_fullB[s]);
+                continue;
+            }
+            const uint4 hdr = n_hdr;
+            uint4 c_q[4];
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) c_q[jp] = n_q[jp];
+            if (sb + 1 < nsb) {
+                const uint8_t *nblk = wrow + (sb + 1) * 144;
+                n_hdr = *reinterpret_cast<const uint4 *>(nblk);
+#pragma unroll
+                for (int jp = 0; jp < 4; ++jp) n_q[jp] = *reinterpret_cast<const uint4 *>(nblk + 16 + 32 * jp + 16 * h);
+            }
+            if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;   // M(sb-2) has read this stage
+            const uint32_t sw[3] = {hdr.y, hdr.z, hdr.w};         // the 12 scale bytes
+            if (h == 0) {
+                const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
+                *reinterpret_cast<float2 *>(ringW + (sb & 7) * 512 + r * 8) = make_float2(__low2float(dm), __high2float(dm));
+            }
+            auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFF; };
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                uint32_t sc[2], mn[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {       // get_scale_min_k4, candle-core/src/quantized/utils.rs:50-60
+                    const int j = 2 * jp + e;
+                    if (j < 4) { sc[e] = sbyte(j) & 63; mn[e] = sbyte(j + 4) & 63; }
+                    else {
+                        sc[e] = (sbyte(j + 4) & 0xF) | ((sbyte(j - 4) >> 6) << 4);
+                        mn[e] = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
+                    }
+                }
+                const uint4 q = c_q[jp];
+                const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {       // e = 0: low nibbles = sub-block 2jp, e = 1: high nibbles = 2jp+1
+                    const uint32_t sl = sc[e] & 7, sh = sc[e] >> 3, mm = mn[e] * 0x01010101u;
+                    uint32_t p1[4], p2[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t nib = (e ? (qq[i] >> 4) : qq[i]) & 0x0F0F0F0Fu;
+                        p1[i] = nib * sl;           // four byte products, each <= 105: no carries between bytes
+                        p2[i] = nib * sh;
+                    }
+                    const int slab = 2 * (2 * jp + e) + h;
+                    uint8_t *dst = stB + slab * kSlabB + r * 16;
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+                    *reinterpret_cast<uint4 *>(dst + kRowTile * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
+                    *reinterpret_cast<uint4 *>(dst + 2 * kRowTile * 16) = make_uint4(mm, mm, mm, mm);
+                }
+            }
+            fence_proxy_async_smem();       // make these generic-proxy writes visible to the tensor core
+            mbar_arrive(&bar_fullB[s]);
+        }
+    } else if (warp == 9) {
+        // ===== activation loader: one thread keeps up to three super-blocks of int8 activations in flight =====
+        if (lane == 0) {
+            for (int sb = 0; sb < nsb; ++sb) {
+                const int a = sb % kStagesA;
+                if (sb >= kStagesA && !wait_or_abort(&bar_doneA[a], ((sb / kStagesA) - 1) & 1, abort_flag)) break;
+                if (dbg & 1) { mbar_arrive(&bar_fullA[a]); continue; }
+                const uint8_t *blob = act + TileBlob::offset(tokens, nsb, tt, sb);
+                uint8_t *dstA = stA0 + a * kStageA, *dstS = ringA + (sb & 7) * 512;
+                cq_mbar_expect_tx(&bar_fullA[a], (unsigned)(tile_rows * 260));
+                if (tile_rows == kTokTile) cq_bulk_g2s(dstA, blob, kStageA, &bar_fullA[a]);        // scratch layout == smem layout
+                else
+                    for (int sl = 0; sl < 16; ++sl)
+                        cq_bulk_g2s(dstA + sl * kSlabA, blob + (size_t)sl * tile_rows * 16, (unsigned)(tile_rows * 16), &bar_fullA[a]);
+                cq_bulk_g2s(dstS, blob + (size_t)tile_rows * 256, (unsigned)(tile_rows * 4), &bar_fullA[a]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 8) {
+        // ===== MMA issuer =====
+        constexpr uint32_t idesc = make_idesc_i8(kTokTile, kN);
+        for (int sb = 0; sb < nsb; ++sb) {
+            const int s = sb & 1, a = sb % kStagesA;
+            if (!wait_or_abort(&bar_fullA[a], (sb / kStagesA) & 1, abort_flag)) break;
+            if (!wait_or_abort(&bar_fullB[s], (sb >> 1) & 1, abort_flag)) break;
+            if (sb >= 2 && !wait_or_abort(&bar_free[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
+            tc_fence_after();
+            if (lane == 0) {
+                mbar_arrive(&bar_vis[s]);       // relay: everything this thread has acquired is now visible to the epilogue
+                const uint32_t a0 = cq_smem_u32(stA0 + a * kStageA), b0 = cq_smem_u32(stB0 + s * kStageB);
+                const uint32_t tacc = tmem_base + (uint32_t)(s * kN);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint64_t da = make_smem_desc(a0 + ks * 2 * kSlabA, kSlabA, 128);
+                    const uint64_t db = make_smem_desc(b0 + ks * 2 * kSlabB, kSlabB, 128);
+                    tc_mma_i8(tacc, da, db, idesc, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&bar_acc[s]);
+                tc_commit(&bar_doneA[a]);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ===== epilogue: warp q owns TMEM lanes 32q..32q+31 = tokens =====
+        const int tok_local = warp * 32 + lane;
+        const int tok = tt * kTokTile + tok_local;
+        float acc[kRowTile];
+#pragma unroll
+        for (int i = 0; i < kRowTile; ++i) acc[i] = 0.0f;
+        bool alive = true;
+        for (int sb = 0; sb < nsb && alive; ++sb) {
+            const int s = sb & 1;
+            if (!wait_or_abort(&bar_vis[s], (sb >> 1) & 1, abort_flag) ||
+                !wait_or_abort(&bar_acc[s], (sb >> 1) & 1, abort_flag)) { alive = false; break; }
+            tc_fence_after();
+            if (dbg & 2) { tc_fence_before(); mbar_arrive(&bar_free[s]); continue; }
+            const float da = *reinterpret_cast<const float *>(ringA + (sb & 7) * 512 + tok_local * 4);
+            const uint8_t *rw = ringW + (sb & 7) * 512;
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * kN);
+            // 16 weight rows at a time; the TMEM loads of the next chunk are in flight while this one is computed
+            uint32_t v1[2][16], v2[2][16], vm[2][16];
+            tmem_ld16(taddr, v1[0]);
+            tmem_ld16(taddr + kRowTile, v2[0]);
+            tmem_ld16(taddr + 2 * kRowTile, vm[0]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld_wait();
+                if (c < 3) {
+                    tmem_ld16(taddr + (c + 1) * 16, v1[(c + 1) & 1]);
+                    tmem_ld16(taddr + kRowTile + (c + 1) * 16, v2[(c + 1) & 1]);
+                    tmem_ld16(taddr + 2 * kRowTile + (c + 1) * 16, vm[(c + 1) & 1]);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const float4 dw = *reinterpret_cast<const float4 *>(rw + (c * 16 + i) * 8);   // (d, dmin) x 2 rows
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int sdot = 8 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e];     // exact, up to 3.1e7
+                        const float dd = e ? dw.z : dw.x, dmn = e ? dw.w : dw.y;
+                        const float t = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float((int)vm[c & 1][i + e])));
+                        acc[c * 16 + i + e] = __fmaf_rn(da, t, acc[c * 16 + i + e]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bar_free[s]);
+        }
+        if (alive && tok < tokens && out_kind != CQ_F32) {
+#pragma unroll
+            for (int i = 0; i < kRowTile; ++i)
+                if (row0 + i < nrows) cq_store_out(out_v, out_kind, (int64_t)tok * stride_out + row0 + i, acc[i]);
+        } else if (alive && tok < tokens) {
+            float *o = (float *)out_v + (size_t)tok * stride_out + row0;
+            if (row0 + kRowTile <= nrows && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < kRowTile; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < kRowTile; ++i)
+                    if (row0 + i < nrows) o[i] = acc[i];
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicExch(&g_prefill_timeout_flag, 1);
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace
+
+extern "C" size_t cq_prefill_scratch_bytes(int tokens, int k) {
+    if (tokens <= 0 || k <= 0 || k % 256 != 0) return 0;
+    const int nsb = k / 256, ntt = (tokens + kTokTile - 1) / kTokTile;
+    return TileBlob::offset(tokens, nsb, ntt - 1, nsb - 1) + TileBlob::tile_rows(tokens, ntt - 1) * 260 + 256;
+}
+
+extern "C" void cq_prefill_quantize(const void *x, int x_elem, void *scratch, int k, int tokens, void *stream) {
+    if (!x || !scratch || tokens <= 0 || k <= 0 || k % 256 != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "prefill quantize: null pointer, empty shape or K not a multiple of 256");
+        return;
+    }
+    const int64_t items = (int64_t)tokens * (k / 256);
+    const unsigned grid = (unsigned)((items + 7) / 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_elem == CQ_F32) quantize_q8k_tiles_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (uint8_t *)scratch, k, tokens);
+    else if (x_elem == CQ_F16) quantize_q8k_tiles_kernel<__half><<<grid, 256, 0, st>>>((const __half *)x, (uint8_t *)scratch, k, tokens);
+    else if (x_elem == CQ_BF16) quantize_q8k_tiles_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)x, (uint8_t *)scratch, k, tokens);
+    else { cq_set_status(CQ_ERR_BAD_ARG, "prefill quantize: unknown element type"); return; }
+    cq_check_launch("prefill quantize");
+}
+
+extern "C" void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, void *dst, int out_elem, int ncols_x,
+                                int nrows_x, int tokens, int stride_dst, void *stream) {
+    if (!vx || !scratch || !dst || ncols_x <= 0 || nrows_x <= 0 || tokens <= 0 || ncols_x % 256 != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "prefill gemm: null pointer, empty shape or K not a multiple of 256");
+        return;
+    }
+    if (wtype != CQ_Q4_K) {
+        cq_set_status(CQ_ERR_UNSUPPORTED, "prefill gemm: the tensor-core kernel covers Q4_K");
+        return;
+    }
+    if ((uintptr_t)vx % 16 != 0 || (uintptr_t)scratch % 16 != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "prefill gemm: weights and scratch must be 16-byte aligned");
+        return;
+    }
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(prefill_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        attr_done[dev] = true;
+    }
+    const dim3 grid((nrows_x + kRowTile - 1) / kRowTile, (tokens + kTokTile - 1) / kTokTile);
+    prefill_q4k_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>((const uint8_t *)vx, (const uint8_t *)scratch, dst,
+                                                                               out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg);
+    cq_check_launch("prefill gemm");
+}
+
+extern "C" void cq_prefill_set_debug(int flags) { g_prefill_dbg = flags; }
+
+extern "C" int cq_prefill_timeout_flag(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_prefill_timeout_flag, sizeof v) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+    if (v) cq_set_status(CQ_ERR_TIMEOUT, "prefill gemm: a bounded wait gave up");
+    return v;
+}

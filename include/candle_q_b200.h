@@ -110,6 +110,23 @@ void cq_block_dots(int wtype, int act, const void *vx, const void *vy, int *out,
 void cq_qmatmul_decode_static(int wtype, const void *vx, const void *x, int x_elem, void *dst, int ncols_x, int nrows_x,
                               int b_size, void *stream);
 
+/* Prefill path (many tokens) on the int8 tensor cores, Q4_K weights.  Replaces the pair
+ * launch_mmq_quantize_q8_1_* + launch_mmq_gguf_q4_k of candle-kernels/src/ffi.rs:424-630 for callers that go through
+ * this library's host objects; the arithmetic is candle's CPU one (BlockQ8K activations, k_quants.rs:1460-1540,
+ * 2320-2358), so results match the CPU vec_dot up to f32 summation order.
+ *   cq_prefill_scratch_bytes: size of the activation scratch for `tokens` rows of `k` elements (k % 256 == 0).
+ *   cq_prefill_quantize     : x [tokens, k] of x_elem -> scratch (int8 tiles in tensor-core layout + f32 scales).
+ *   cq_prefill_gemm         : dst[t * stride_dst + row] of out_elem, for all tokens and all nrows_x weight rows.
+ *   cq_prefill_timeout_flag : 1 if a launch on the current device gave up a bounded wait (synchronises). */
+size_t cq_prefill_scratch_bytes(int tokens, int k);
+void cq_prefill_quantize(const void *x, int x_elem, void *scratch, int k, int tokens, void *stream);
+void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, void *dst, int out_elem, int ncols_x, int nrows_x,
+                     int tokens, int stride_dst, void *stream);
+int cq_prefill_timeout_flag(void);
+/* Experiment switch for profiling: bit 0 skips the producer warps' work, bit 1 the epilogue's (outputs are then
+ * meaningless); 0 restores normal operation. */
+void cq_prefill_set_debug(int flags);
+
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
 /* 1 if a GEMV on the current device gave up a bounded wait for a staged copy (then also sets status 4).

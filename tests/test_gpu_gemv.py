@@ -220,7 +220,11 @@ def test_qmatmul_forward_api(oracle, cuda_dev):
         mm.forward(torch.zeros(k, 2, device=cuda_dev).t())
     with pytest.raises(capi.CandleQError, match="byte size does not match"):
         QTensor.from_data(wq, GgmlDType.Q4K, (n + 1, k), cuda_dev)
-    # more than 8 rows go down the prefill path and must agree with the decode path row by row
-    xb = torch.from_numpy(np.concatenate([x, x, x])).to(cuda_dev)
+    # 9..16 rows walk the decode kernel in slices and must agree with it row by row
+    xb = torch.from_numpy(np.concatenate([x, x])).to(cuda_dev)
     yb = mm.forward(xb)
-    assert rel_err(yb[:6].cpu().numpy(), ref) <= TOL and rel_err(yb[12:].cpu().numpy(), ref) <= TOL
+    assert rel_err(yb[:6].cpu().numpy(), ref) <= TOL and rel_err(yb[6:].cpu().numpy(), ref) <= TOL
+    # more rows go to the tensor-core prefill kernel, whose arithmetic is the CPU path's (Q8_K activations)
+    xc = np.concatenate([x] * 5)
+    yc = mm.forward(torch.from_numpy(xc).to(cuda_dev))
+    assert rel_err(yc.cpu().numpy(), oracle.matmul(wt, xc, wq, n)) <= TOL

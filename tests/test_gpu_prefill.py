@@ -1,0 +1,113 @@
+"""GPU parity of the prefill path: activation tiles + int8 tcgen05 GEMM for Q4_K, through the C ABI.
+
+The kernel's arithmetic is candle's CPU one (BlockQ8K activations), so the oracle is k_quants::matmul:
+activation int8 values and scales bit-exact, outputs within 1e-3 (max |a - ref| / max |ref|).
+"""
+import numpy as np
+import pytest
+import torch
+
+from candle_b200 import capi
+from candle_b200.quantized import GgmlDType, QMatMul, QTensor
+from candle_b200.synth import random_blocks
+from helpers import make_case, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+Q4K = 12
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _prefill(lib, w_dev, x_dev, k, n, out_dtype=torch.float32):
+    tokens = x_dev.shape[0]
+    elem = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+    scratch = torch.full((lib.cq_prefill_scratch_bytes(tokens, k),), 0x5A, dtype=torch.uint8, device=x_dev.device)
+    out = torch.full((tokens * n + 32,), float("nan"), dtype=out_dtype, device=x_dev.device)
+    lib.cq_prefill_quantize(x_dev.data_ptr(), elem[x_dev.dtype], scratch.data_ptr(), k, tokens, _stream())
+    lib.cq_prefill_gemm(Q4K, w_dev.data_ptr(), scratch.data_ptr(), out.data_ptr(), elem[out_dtype], k, n, tokens, n, _stream())
+    capi.check("prefill")
+    torch.cuda.synchronize()
+    assert lib.cq_prefill_timeout_flag() == 0
+    assert bool(torch.isnan(out[tokens * n:].float()).all()), "output written past its end"
+    assert not bool(torch.isnan(out[:tokens * n].float()).any()), "an output element was left unwritten"
+    return scratch, out[:tokens * n].view(tokens, n)
+
+
+def _tiles_to_q8k(scratch, tokens, k):
+    """Undo the tensor-core tiling of the scratch: returns (int8 [tokens, k], f32 scales [tokens, k/256])."""
+    s = scratch.cpu().numpy()
+    nsb = k // 256
+    q = np.zeros((tokens, k), dtype=np.int8)
+    d = np.zeros((tokens, nsb), dtype=np.float32)
+    for tt in range((tokens + 127) // 128):
+        nt = min(128, tokens - tt * 128)
+        rows = (nt + 7) // 8 * 8
+        for sb in range(nsb):
+            off = tt * 128 * 260 * nsb + sb * rows * 260
+            blob = s[off:off + rows * 260]
+            slabs = blob[:rows * 256].reshape(16, rows, 16)          # [k/16][token][16]
+            q[tt * 128:tt * 128 + nt, sb * 256:(sb + 1) * 256] = slabs.transpose(1, 0, 2).reshape(rows, 256)[:nt].view(np.int8)
+            d[tt * 128:tt * 128 + nt, sb] = blob[rows * 256:rows * 260].view(np.float32)[:nt]
+    return q, d
+
+
+@pytest.mark.parametrize("tokens,k,n", [(128, 256, 64), (17, 512, 64), (100, 1024, 100), (300, 2048, 200),
+                                        (129, 768, 33), (64, 4096, 256), (512, 4096, 384), (1000, 14336, 96)])
+def test_prefill_matches_cpu_vec_dot(lib, oracle, cuda_dev, tokens, k, n):
+    _, x, wq = make_case(oracle, Q4K, k, n, tokens, seed=tokens + k + n)
+    w_dev = torch.from_numpy(wq).to(cuda_dev)
+    x_dev = torch.from_numpy(x).to(cuda_dev)
+    scratch, out = _prefill(lib, w_dev, x_dev, k, n)
+    # activation blocks: identical int8 values and scales to BlockQ8K::from_float
+    q, d = _tiles_to_q8k(scratch, tokens, k)
+    ref_blocks = oracle.quantize(oracle.Q8K, x).reshape(tokens, k // 256, 292)
+    assert np.array_equal(q.reshape(tokens, k // 256, 256), ref_blocks[:, :, 4:260].view(np.int8))
+    assert np.array_equal(d, ref_blocks[:, :, 0:4].copy().view(np.float32).reshape(tokens, k // 256))
+    ref = oracle.matmul(Q4K, x, wq, n)
+    assert rel_err(out.cpu().numpy(), ref) <= TOL
+    assert rel_err(out.cpu().numpy(), ref) <= 1e-5     # only the order of f32 additions differs
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_prefill_half_types(lib, oracle, cuda_dev, dtype):
+    tokens, k, n = 200, 1024, 130
+    _, x, wq = make_case(oracle, Q4K, k, n, tokens, seed=5)
+    xt = torch.from_numpy(x).to(cuda_dev).to(dtype)
+    w_dev = torch.from_numpy(wq).to(cuda_dev)
+    _, out = _prefill(lib, w_dev, xt, k, n, out_dtype=dtype)
+    ref = torch.from_numpy(oracle.matmul(Q4K, xt.float().cpu().numpy(), wq, n)).to(dtype).float().numpy()
+    assert rel_err(out.float().cpu().numpy(), ref) <= (2 ** -8 if dtype == torch.bfloat16 else 2 ** -11) * 1.01
+
+
+def test_prefill_agrees_with_decode_kernel_at_full_size(lib, cuda_dev):
+    """BASELINE configs[2] shape (4096 -> 14336, 2048 tokens), synthetic blocks: every sampled token must give
+    what the decode GEMV gives for it with the same Q8_K activations (two independent kernels, same integers)."""
+    k, n, tokens = 4096, 14336, 2048
+    w = random_blocks(GgmlDType.Q4K, n, k, seed=3, device=cuda_dev)
+    x = torch.randn((tokens, k), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(4))
+    _, out = _prefill(lib, w, x, k, n)
+    rows = torch.tensor([0, 1, 127, 128, 1000, 2047], device=cuda_dev)
+    xs = x[rows].contiguous()
+    kp = capi.pad(k, 512)
+    y = torch.zeros((len(rows), kp // 32 * 36), dtype=torch.uint8, device=cuda_dev)
+    lib.cq_quantize_act(xs.data_ptr(), capi.F32, y.data_ptr(), k, kp, len(rows), capi.ACT_Q8_K, _stream())
+    dec = torch.empty((len(rows), n), device=cuda_dev)
+    lib.cq_mmvq(Q4K, capi.ACT_Q8_K, capi.F32, w.data_ptr(), y.data_ptr(), dec.data_ptr(), k, n, kp // 32, n, len(rows), _stream())
+    capi.check("decode reference")
+    assert rel_err(out[rows].cpu().numpy(), dec.cpu().numpy()) <= 1e-5
+    # duplicated tokens give identical rows (no dependence on the position inside a tile)
+    x2 = torch.cat([x[:300], x[:300]])
+    _, out2 = _prefill(lib, w, x2, k, n)
+    assert torch.equal(out2[:300], out2[300:])
+
+
+def test_qmatmul_routes_many_rows_to_prefill(oracle, cuda_dev):
+    k, n, tokens = 1024, 96, 77
+    _, x, wq = make_case(oracle, Q4K, k, n, tokens, seed=8)
+    mm = QMatMul.from_qtensor(QTensor.from_data(wq, GgmlDType.Q4K, (n, k), cuda_dev))
+    y = mm.forward(torch.from_numpy(x).to(cuda_dev).view(7, 11, k))
+    assert y.shape == (7, 11, n)
+    assert rel_err(y.view(tokens, n).cpu().numpy(), oracle.matmul(Q4K, x, wq, n)) <= TOL
