@@ -55,6 +55,12 @@ def lib() -> C.CDLL:
         L.cq_prefill_gemm.argtypes = [i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_prefill_timeout_flag.restype = i32
         L.cq_prefill_set_debug.argtypes = [i32]
+        i64 = C.c_int64
+        L.moe_gemm_gguf.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64]
+        L.moe_gemm_gguf_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64]
+        L.cq_moe_gemv_sorted.argtypes = [i32, i32, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.cq_indexed_moe_forward.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
+        L.cq_moe_timeout_flag.restype = i32
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]
@@ -71,6 +77,7 @@ def lib() -> C.CDLL:
         L.cqh_qtensor_device_ptr.restype = vp
         L.cqh_qmatmul_forward.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
         L.cqh_set_act_mode.argtypes = [i32]
+        L.cqh_indexed_moe_forward.argtypes = [vp, vp, i32, vp, i32, i32, vp, vp]
         L.cqh_get_act_mode.restype = i32
         L.cqh_workspace_reserve.argtypes = [i32, sz]
         _lib = L

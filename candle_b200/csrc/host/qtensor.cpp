@@ -208,6 +208,26 @@ void QCudaStorage::fwd(size_t n, size_t k, const void *x, DType x_dtype, const i
     lib_check("qmatmul");
 }
 
+void QCudaStorage::indexed_moe_forward(size_t experts, size_t n, size_t k, const float *x, int x_dim1, const uint32_t *ids,
+                                       int batch, int topk, float *out, cudaStream_t stream) const {
+    if (!kernels_support(dtype_)) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(dtype_));
+    if (k % block_size(dtype_) != 0 || experts * n * (k / block_size(dtype_)) * type_size(dtype_) != len_)
+        throw Error("indexed_moe_forward: storage size does not match [experts, n, k]");
+    if (x_dim1 != 1 && x_dim1 != topk) throw Error("indexed_moe_forward: input dim 1 must be 1 or topk");
+    if (batch <= 0 || topk <= 0) return;
+    if (!x || !ids || !out) throw Error("indexed_moe_forward: null pointer");
+    DeviceGuard g(device_);
+    const bool cpu_exact = act_mode() == ActMode::CpuExact;
+    const int act = !cpu_exact ? CQ_ACT_Q8_1_ENC : (block_size(dtype_) == 256 ? CQ_ACT_Q8_K_ENC : CQ_ACT_Q8_0_ENC);
+    const size_t k_padded = pad(k, MATRIX_ROW_PADDING);
+    const size_t rows_in = (size_t)batch * x_dim1;
+    uint8_t *scratch = (uint8_t *)workspace_ensure(device_, rows_in * (k_padded / 32) * 36);
+    cq_quantize_act(x, CQ_ELEM_F32, scratch, (int)k, (int)k_padded, (int)rows_in, act, stream);
+    cq_indexed_moe_forward((int)dtype_, act, ptr_, scratch, ids, out, (int)n, (int)k, batch, topk, (int)k_padded, x_dim1,
+                           (int)experts, stream);
+    lib_check("indexed_moe_forward");
+}
+
 // ---- QTensor / QMatMul -----------------------------------------------------------------------
 QTensor::QTensor(std::unique_ptr<QCudaStorage> storage, std::vector<int64_t> dims)
     : storage_(std::move(storage)), shape_(std::move(dims)) {
@@ -281,6 +301,17 @@ extern "C" int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, con
     return guarded([&] {
         QMatMul mm(*(std::shared_ptr<QTensor> *)handle);
         mm.forward(x, (DType)x_dtype, dims, ndims, out, (cudaStream_t)stream);
+    });
+}
+
+extern "C" int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk,
+                                       float *out, void *stream) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        if (t->rank() != 3) throw Error("indexed_moe_forward expects a rank-3 [experts, n, k] tensor");
+        const auto &sh = t->shape();
+        t->storage().indexed_moe_forward((size_t)sh[0], (size_t)sh[1], (size_t)sh[2], x, x_dim1, ids, batch, topk, out,
+                                         (cudaStream_t)stream);
     });
 }
 

@@ -74,6 +74,11 @@ class QCudaStorage {
     void fwd(size_t n, size_t k, const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out,
              cudaStream_t stream) const;
 
+    // Per (batch entry, slot) GEMV against expert ids[b, slot] of a [experts, n, k] tensor (cuda.rs:587-622).
+    // x: f32 [batch, x_dim1, k] with x_dim1 == topk or 1; ids: u32 [batch, topk]; out: f32 [batch, topk, n].
+    void indexed_moe_forward(size_t experts, size_t n, size_t k, const float *x, int x_dim1, const uint32_t *ids, int batch,
+                             int topk, float *out, cudaStream_t stream) const;
+
   private:
     QCudaStorage() = default;
     uint8_t *ptr_ = nullptr;

@@ -52,6 +52,21 @@ CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_f16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_bf16_plain);
 #undef CQ_DECL_MMVQ
 
+/* Expert-indexed GEMV for quantized MoE layers.  Replaces candle-kernels/src/ffi.rs:25-39 (moe_gemm_gguf) and
+ * :41-56 (moe_gemm_gguf_prefill) for Q8_0 (code 0), Q4K (1) and Q6K (5) experts; other codes record
+ * "unsupported".  weights: [num_experts, size_n, size_k] GGUF blocks; sorted_token_ids / expert_ids: device i32
+ * [size_m]; topk_weights: device f32 or null; output: f32 [rows, size_n]; `stream` is the cudaStream_t as an integer.
+ * Job m: pair = sorted_token_ids[m]; input row = pair (topk_weights given) else pair / topk; output row = pair,
+ * scaled by topk_weights[pair] when given; jobs whose expert id is outside [0, num_experts) write nothing. */
+void moe_gemm_gguf(const float *input, const void *weights, const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                   const float *topk_weights, void *output, int num_experts, int topk, int size_m, int size_n, int size_k,
+                   int gguf_dtype, int64_t stream);
+/* input: f16 (input_dtype 0) or bf16 (1).  Same integer arithmetic as moe_gemm_gguf (the reference switches to a
+ * de-quantize + wmma kernel here). */
+void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int32_t *sorted_token_ids,
+                           const int32_t *expert_ids, const float *topk_weights, void *output, int num_experts, int topk,
+                           int size_m, int size_n, int size_k, int input_dtype, int gguf_dtype, int64_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * 2. Library surface
  * ---------------------------------------------------------------------------------------------- */
@@ -110,6 +125,18 @@ void cq_block_dots(int wtype, int act, const void *vx, const void *vy, int *out,
 void cq_qmatmul_decode_static(int wtype, const void *vx, const void *x, int x_elem, void *dst, int ncols_x, int nrows_x,
                               int b_size, void *stream);
 
+/* MoE GEMV on activations that are already quantized (36-byte containers of encoding `act`, row r at block
+ * r * stride_col_y).  cq_moe_gemv_sorted is what moe_gemm_gguf runs after quantizing; cq_indexed_moe_forward has
+ * the argument list of candle's indexed_moe_forward_<type>_q8_1 kernels (candle-kernels/src/quantized.cu:4669-4680,
+ * launched from candle-core/src/quantized/cuda.rs:505-584): task t = (batch entry, slot), expert = ids[t], input
+ * row = t / topk if input_dim1 == 1 else t, output row = t.  num_experts <= 0 disables the range check on ids. */
+void cq_moe_gemv_sorted(int wtype, int act, const void *weights, const void *y, int stride_col_y,
+                        const int32_t *sorted_token_ids, const int32_t *expert_ids, const float *topk_weights, float *out,
+                        int num_experts, int topk, int size_m, int size_n, int size_k, void *stream);
+void cq_indexed_moe_forward(int wtype, int act, const void *weights, const void *y, const uint32_t *ids, float *out, int n,
+                            int k, int batch, int topk, int k_padded, int input_dim1, int num_experts, void *stream);
+int cq_moe_timeout_flag(void);
+
 /* Prefill path (many tokens) on the int8 tensor cores, Q4_K weights.  Replaces the pair
  * launch_mmq_quantize_q8_1_* + launch_mmq_gguf_q4_k of candle-kernels/src/ffi.rs:424-630 for callers that go through
  * this library's host objects; the arithmetic is candle's CPU one (BlockQ8K activations, k_quants.rs:1460-1540,
@@ -152,6 +179,10 @@ const void *cqh_qtensor_device_ptr(void *handle);
 /* QMatMul::forward: x [.., k] (device, contiguous, x_dtype = CQ_ELEM_*) -> out [.., n], same element type. */
 int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
                         void *stream);
+/* QTensor::indexed_moe_forward (candle-core/src/quantized/mod.rs:758-784, cuda.rs:587-622): handle is a rank-3
+ * tensor [experts, n, k]; x f32 [batch, topk or 1, k]; ids u32 [batch, topk]; out f32 [batch, topk, n]. */
+int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk, float *out,
+                            void *stream);
 /* 0: Q8_1 activations (candle's CUDA arithmetic, default); 1: activations quantized exactly like candle's CPU path. */
 void cqh_set_act_mode(int mode);
 int cqh_get_act_mode(void);

@@ -1,0 +1,113 @@
+"""GPU parity of the expert-indexed paths.  The reference has no test for them ("parity unpinned"): the oracle is
+the per-expert composition of the pinned pieces (Q8_1 quantize + the reference's MMVQ arithmetic per pair)."""
+import numpy as np
+import pytest
+import torch
+
+from candle_b200 import capi
+from candle_b200.moe import moe_gemm_gguf
+from candle_b200.quantized import GgmlDType, QTensor, set_activation_mode
+from helpers import pad, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+TYPES = {"q4_k": 12, "q6_k": 14, "q8_0": 8}
+
+
+def _experts(oracle, wt, e, n, k, seed):
+    rng = np.random.default_rng(seed)
+    wf = (rng.standard_normal((e, n, k)) * 0.02).astype(np.float32)
+    return np.stack([oracle.quantize(wt, wf[i]) for i in range(e)])     # [e, n, row_bytes]
+
+
+def _route(tokens, e, topk, seed):
+    rng = np.random.default_rng(seed)
+    ids = np.stack([rng.choice(e, size=topk, replace=False) for _ in range(tokens)]).astype(np.int32)   # [tokens, topk]
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable").astype(np.int32)     # sorted_token_ids: pair indices by expert
+    return ids, order, flat[order].astype(np.int32)
+
+
+@pytest.mark.parametrize("tname", list(TYPES))
+@pytest.mark.parametrize("tokens,e,topk,n,k", [(1, 16, 4, 96, 512), (5, 32, 8, 768, 2048), (3, 8, 2, 2048, 768)])
+def test_moe_gemm_gguf_sorted(oracle, cuda_dev, tname, tokens, e, topk, n, k):
+    wt = TYPES[tname]
+    if k % capi.BLOCK_ELEMS[wt]:
+        pytest.skip("K not a multiple of the block size")
+    wq = _experts(oracle, wt, e, n, k, seed=tokens + e)
+    ids, sorted_pairs, expert_of = _route(tokens, e, topk, seed=3)
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((tokens, k)).astype(np.float32)
+    tw = rng.random((tokens * topk,), dtype=np.float32)
+    qt = QTensor.from_data(wq.reshape(-1), GgmlDType(wt), (e, n, k), cuda_dev)
+    dev = lambda a: torch.from_numpy(a).to(cuda_dev)
+    # gate/up style: input row = pair / topk, no routing weight
+    out = moe_gemm_gguf(dev(x), qt, None, dev(sorted_pairs), dev(expert_of), topk).cpu().numpy()
+    q8 = oracle.cuda_quantize_q8_1(x, pad(k, 512))
+    ref = np.zeros((tokens * topk, n), dtype=np.float32)
+    for pair in range(tokens * topk):
+        ex = ids.reshape(-1)[pair]
+        ref[pair] = oracle.cuda_mmvq(wt, wq[ex], q8[pair // topk:pair // topk + 1], k, n)[0]
+    assert rel_err(out, ref) <= TOL
+    # down style: one input row per pair, scaled by the routing weight; expert id -1 skips the pair
+    x2 = rng.standard_normal((tokens * topk, k)).astype(np.float32)
+    expert_skip = expert_of.copy()
+    expert_skip[0] = -1
+    out2 = torch.full((tokens * topk, n), 7.0, device=cuda_dev)
+    L = capi.lib()
+    x2d, sp, es, twd = dev(x2), dev(sorted_pairs), dev(expert_skip), dev(tw)
+    L.moe_gemm_gguf(x2d.data_ptr(), qt.device_ptr(), sp.data_ptr(), es.data_ptr(), twd.data_ptr(), out2.data_ptr(), e, topk,
+                    tokens * topk, n, k, {12: 1, 14: 5, 8: 0}[wt], torch.cuda.current_stream().cuda_stream)
+    capi.check("moe down")
+    out2 = out2.cpu().numpy()
+    q8b = oracle.cuda_quantize_q8_1(x2, pad(k, 512))
+    for j, pair in enumerate(sorted_pairs):
+        if j == 0:
+            assert np.all(out2[pair] == 7.0)        # skipped pair: untouched
+            continue
+        ex = expert_of[j]
+        r = oracle.cuda_mmvq(wt, wq[ex], q8b[pair:pair + 1], k, n)[0] * tw[pair]
+        assert rel_err(out2[pair], r) <= TOL
+    assert L.cq_moe_timeout_flag() == 0
+
+
+@pytest.mark.parametrize("tname", list(TYPES))
+@pytest.mark.parametrize("x_dim1_is_one", [True, False])
+def test_indexed_moe_forward(oracle, cuda_dev, tname, x_dim1_is_one):
+    wt = TYPES[tname]
+    e, n, k, batch, topk = 12, 130, 1024, 4, 3
+    wq = _experts(oracle, wt, e, n, k, seed=1)
+    ids, _, _ = _route(batch, e, topk, seed=5)
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((batch, 1 if x_dim1_is_one else topk, k)).astype(np.float32)
+    qt = QTensor.from_data(wq.reshape(-1), GgmlDType(wt), (e, n, k), cuda_dev)
+    out = qt.indexed_moe_forward(torch.from_numpy(x).to(cuda_dev), torch.from_numpy(ids).to(cuda_dev)).cpu().numpy()
+    assert out.shape == (batch, topk, n)
+    for b in range(batch):
+        for s in range(topk):
+            xin = x[b, 0 if x_dim1_is_one else s][None]
+            r = oracle.cuda_mmvq(wt, wq[ids[b, s]], oracle.cuda_quantize_q8_1(xin, pad(k, 512)), k, n)[0]
+            assert rel_err(out[b, s], r) <= TOL
+    # CPU-exact activations: matches the CPU vec_dot per expert
+    set_activation_mode(True)
+    try:
+        out2 = qt.indexed_moe_forward(torch.from_numpy(x).to(cuda_dev), torch.from_numpy(ids).to(cuda_dev)).cpu().numpy()
+    finally:
+        set_activation_mode(False)
+    for b in range(batch):
+        for s in range(topk):
+            xin = x[b, 0 if x_dim1_is_one else s][None]
+            assert rel_err(out2[b, s], oracle.matmul(wt, xin, wq[ids[b, s]], n)[0]) <= TOL
+
+
+def test_moe_prefill_entry_point_matches_decode(oracle, cuda_dev):
+    """f16 activations through moe_gemm_gguf_prefill give what the decode entry point gives for the up-cast values."""
+    wt, e, n, k, tokens, topk = 12, 16, 256, 1024, 40, 4
+    wq = _experts(oracle, wt, e, n, k, seed=4)
+    _, sorted_pairs, expert_of = _route(tokens, e, topk, seed=6)
+    qt = QTensor.from_data(wq.reshape(-1), GgmlDType(wt), (e, n, k), cuda_dev)
+    x = torch.randn((tokens, k), device=cuda_dev).to(torch.float16)
+    sp, eo = torch.from_numpy(sorted_pairs).to(cuda_dev), torch.from_numpy(expert_of).to(cuda_dev)
+    a = moe_gemm_gguf(x, qt, None, sp, eo, topk, is_prefill=True)
+    b = moe_gemm_gguf(x.float(), qt, None, sp, eo, topk, is_prefill=False)
+    assert torch.equal(a, b)
