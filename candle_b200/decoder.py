@@ -1,0 +1,193 @@
+"""Llama-shaped decoder harness: the caller of ``QMatMul::forward`` that BASELINE config 4 describes.
+
+Structure and call order follow candle-transformers/src/models/quantized_llama.rs:178-262, 568-596 (f32 residual
+stream, RMSNorm eps 1e-5, interleaved RoPE, f32 KV cache, GQA attention, SwiGLU, logits for the last position)
+and the greedy loop of candle-examples/examples/quantized/main.rs:616-690.  Weights are random GGUF blocks
+(candle_b200/synth.py) in the Q4_K_M mix: Q6_K for attn_v, ffn_down and the output head, Q4_K elsewhere.
+
+Tensor parallelism: every projection is sharded by output rows (whole heads for q/k/v) and its output slices are
+all-gathered; nothing is ever reduced across ranks, so a token sequence is bit-identical at 1, 2, 4 and 8 GPUs.
+Glue (norms, RoPE, SwiGLU, residuals) is torch elementwise code on replicated tensors; attention is
+``cq_attention_f32``, whose summation order does not depend on how many heads a rank owns.
+Weights are generated in eight row pieces with seeds that do not depend on the world size.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+
+from . import capi
+from .parallel import Gatherer, argmax_sharded
+from .quantized import GgmlDType, QMatMul, QTensor
+from .synth import random_blocks
+
+PIECES = 8   # finest shard granularity; rank r of g holds pieces [r * 8 / g, (r + 1) * 8 / g)
+
+
+@dataclasses.dataclass
+class DecoderConfig:
+    layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+    max_pos: int = 1024
+
+    @staticmethod
+    def llama3_8b() -> "DecoderConfig":
+        return DecoderConfig()
+
+    @staticmethod
+    def tiny() -> "DecoderConfig":
+        return DecoderConfig(layers=2, d_model=1024, n_heads=8, n_kv_heads=8, head_dim=128, ffn=2048, vocab=4096, max_pos=128)
+
+    def weight_bytes_per_token(self) -> int:
+        """Bytes of quantized weights one decoded token streams (whole model, all ranks together)."""
+        q4, q6 = 144 / 256, 210 / 256
+        d, kv = self.d_model, self.n_kv_heads * self.head_dim
+        per_layer = (d * d + kv * d + d * d + 2 * self.ffn * d) * q4 + (kv * d + d * self.ffn) * q6
+        return int(self.layers * per_layer + self.vocab * d * q6)
+
+
+def _sharded_matmul(dtype: GgmlDType, n: int, k: int, seed: int, rank: int, world: int, device) -> QMatMul:
+    per = PIECES // world
+    piece_rows = n // PIECES
+    parts = [random_blocks(dtype, piece_rows, k, seed * 16 + p, device) for p in range(rank * per, (rank + 1) * per)]
+    blocks = torch.cat(parts, dim=0).contiguous()
+    return QMatMul.from_qtensor(QTensor.from_device_blocks(blocks, dtype, (piece_rows * per, k)))
+
+
+class _Layer:
+    pass
+
+
+class LlamaShapedDecoder:
+    def __init__(self, cfg: DecoderConfig, device, rank: int = 0, world: int = 1, batch: int = 1, seed: int = 0, group=None):
+        if PIECES % world or cfg.n_kv_heads % world or cfg.vocab % PIECES or cfg.ffn % PIECES:
+            raise ValueError("world size must divide 8 and the head / vocabulary / ffn sizes")
+        self.cfg, self.device, self.rank, self.world, self.batch = cfg, torch.device(device), rank, world, batch
+        self.gather = Gatherer(group)
+        d, hd = cfg.d_model, cfg.head_dim
+        self.hq_l, self.hkv_l = cfg.n_heads // world, cfg.n_kv_heads // world
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        self.tok_embd = torch.randn((cfg.vocab, d), device=self.device, generator=g) * 0.02      # de-quantized at load in the reference
+        self.layers = []
+        for li in range(cfg.layers):
+            L = _Layer()
+            s = seed * 100003 + li * 16
+            L.attn_norm = 1.0 + 0.1 * torch.randn(d, device=self.device, generator=g)
+            L.ffn_norm = 1.0 + 0.1 * torch.randn(d, device=self.device, generator=g)
+            L.wq = _sharded_matmul(GgmlDType.Q4K, cfg.n_heads * hd, d, s + 1, rank, world, self.device)
+            L.wk = _sharded_matmul(GgmlDType.Q4K, cfg.n_kv_heads * hd, d, s + 2, rank, world, self.device)
+            L.wv = _sharded_matmul(GgmlDType.Q6K, cfg.n_kv_heads * hd, d, s + 3, rank, world, self.device)
+            L.wo = _sharded_matmul(GgmlDType.Q4K, d, cfg.n_heads * hd, s + 4, rank, world, self.device)
+            L.gate = _sharded_matmul(GgmlDType.Q4K, cfg.ffn, d, s + 5, rank, world, self.device)
+            L.up = _sharded_matmul(GgmlDType.Q4K, cfg.ffn, d, s + 6, rank, world, self.device)
+            L.down = _sharded_matmul(GgmlDType.Q6K, d, cfg.ffn, s + 7, rank, world, self.device)
+            L.k_cache = torch.zeros((batch, self.hkv_l, cfg.max_pos, hd), device=self.device)
+            L.v_cache = torch.zeros((batch, self.hkv_l, cfg.max_pos, hd), device=self.device)
+            self.layers.append(L)
+        self.out_norm = 1.0 + 0.1 * torch.randn(d, device=self.device, generator=g)
+        self.output = _sharded_matmul(GgmlDType.Q6K, cfg.vocab, d, seed * 100003 + 999983, rank, world, self.device)
+        self.vocab_start = rank * (cfg.vocab // world)
+        # RoPE tables (quantized_llama.rs:540-556): theta_i = base^(-2i/d), angle = pos * theta_i
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=self.device, dtype=torch.float32) / hd))
+        ang = torch.arange(cfg.max_pos, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+        self.pos = torch.zeros(1, dtype=torch.int32, device=self.device)       # cache position of the next token
+        self._graph = None
+
+    # ---- glue -------------------------------------------------------------------------------------------------
+    def _rms_norm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        return x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + self.cfg.rms_eps) * w
+
+    def _rope(self, x: torch.Tensor, pos_idx: torch.Tensor) -> torch.Tensor:
+        """Interleaved rotary embedding (rope_i): pairs (x[2i], x[2i+1]).  x: [B, T, H, D]."""
+        cos = self.cos.index_select(0, pos_idx)[None, :, None, :]
+        sin = self.sin.index_select(0, pos_idx)[None, :, None, :]
+        xp = x.reshape(*x.shape[:-1], x.shape[-1] // 2, 2)
+        x0, x1 = xp[..., 0], xp[..., 1]
+        return torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1).reshape(x.shape)
+
+    def _attention(self, q, k_cache, v_cache, T):
+        out = torch.empty_like(q)
+        cfg = self.cfg
+        capi.lib().cq_attention_f32(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
+                                    self.batch, T, self.hq_l, self.hkv_l, cfg.head_dim, cfg.max_pos,
+                                    1.0 / math.sqrt(cfg.head_dim), torch.cuda.current_stream(self.device).cuda_stream)
+        return out
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens: int64 [B, T] at cache positions pos .. pos+T-1.  Returns the greedy next token [B] and advances pos."""
+        cfg, B, T = self.cfg, tokens.shape[0], tokens.shape[1]
+        hd = cfg.head_dim
+        pos_idx = self.pos.to(torch.int64) + torch.arange(T, device=self.device)
+        x = self.tok_embd.index_select(0, tokens.reshape(-1))                       # [B*T, d]
+        for L in self.layers:
+            h = self._rms_norm(x, L.attn_norm)
+            q = self._rope(L.wq.forward(h).view(B, T, self.hq_l, hd), pos_idx)
+            k = self._rope(L.wk.forward(h).view(B, T, self.hkv_l, hd), pos_idx)
+            v = L.wv.forward(h).view(B, T, self.hkv_l, hd)
+            L.k_cache.index_copy_(2, pos_idx, k.permute(0, 2, 1, 3))
+            L.v_cache.index_copy_(2, pos_idx, v.permute(0, 2, 1, 3))
+            att = self._attention(q.contiguous(), L.k_cache, L.v_cache, T).view(B * T, self.hq_l * hd)
+            x = x + self.gather(L.wo.forward(self.gather(att)))
+            h = self._rms_norm(x, L.ffn_norm)
+            a = torch.nn.functional.silu(L.gate.forward(h)) * L.up.forward(h)
+            x = x + self.gather(L.down.forward(self.gather(a)))
+        last = x.view(B, T, cfg.d_model)[:, -1, :].contiguous()
+        logits = self.output.forward(self._rms_norm(last, self.out_norm))       # [B, vocab / world]
+        tok = argmax_sharded(logits, self.vocab_start, self.gather)
+        self.pos += T
+        return tok
+
+    # ---- greedy loop ------------------------------------------------------------------------------------------
+    def reset(self):
+        self.pos.zero_()
+
+    def capture_decode_step(self) -> bool:
+        """Record one decode step (T = 1) as a CUDA graph.  Returns False when capture is not possible
+        (then decode_step launches eagerly)."""
+        self._tok_in = torch.zeros((self.batch, 1), dtype=torch.int64, device=self.device)
+        saved = self.pos.clone()
+        try:
+            side = torch.cuda.Stream(device=self.device)
+            with torch.cuda.stream(side):
+                for _ in range(2):                      # warm-up: allocations, attributes, workspace growth
+                    self.forward(self._tok_in)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    self._tok_out = self.forward(self._tok_in)
+            self._graph = graph
+            ok = True
+        except Exception:
+            self._graph = None
+            ok = False
+        torch.cuda.synchronize(self.device)
+        self.pos.copy_(saved)
+        return ok
+
+    def decode_step(self, tok: torch.Tensor) -> torch.Tensor:
+        if self._graph is None:
+            return self.forward(tok.view(self.batch, 1))
+        self._tok_in.copy_(tok.view(self.batch, 1))
+        self._graph.replay()
+        return self._tok_out
+
+    def generate(self, prompt: torch.Tensor, steps: int) -> torch.Tensor:
+        """Greedy decoding: prompt int64 [B, Tp] -> generated tokens [B, steps]."""
+        self.reset()
+        tok = self.forward(prompt)
+        outs = [tok]
+        for _ in range(steps - 1):
+            tok = self.decode_step(tok).clone()
+            outs.append(tok)
+        return torch.stack(outs, dim=1)

@@ -154,6 +154,13 @@ int cq_prefill_timeout_flag(void);
  * meaningless); 0 restores normal operation. */
 void cq_prefill_set_debug(int flags);
 
+/* Causal attention over an f32 KV cache, one CTA per (sequence, head, query), additions in a fixed order so that a
+ * head gives the same bits on any GPU count.  Glue for the decoder harness; stands where candle's quantized models
+ * use dense matmuls and softmax (candle-transformers/src/models/quantized_llama.rs:246-261).
+ * q, out: [batch, tq, hq, 128]; caches: [batch, hkv, tmax, 128]; pos: device int, cache position of query 0. */
+void cq_attention_f32(const float *q, const float *k_cache, const float *v_cache, float *out, const int *pos, int batch,
+                      int tq, int hq, int hkv, int head_dim, int tmax, float scale, void *stream);
+
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
 /* 1 if a GEMV on the current device gave up a bounded wait for a staged copy (then also sets status 4).
