@@ -72,7 +72,7 @@ class LlamaShapedDecoder:
         if PIECES % world or cfg.n_kv_heads % world or cfg.vocab % PIECES or cfg.ffn % PIECES:
             raise ValueError("world size must divide 8 and the head / vocabulary / ffn sizes")
         self.cfg, self.device, self.rank, self.world, self.batch = cfg, torch.device(device), rank, world, batch
-        self.gather = Gatherer(group)
+        self.gather = Gatherer(group, world)
         d, hd = cfg.d_model, cfg.head_dim
         self.hq_l, self.hkv_l = cfg.n_heads // world, cfg.n_kv_heads // world
         g = torch.Generator(device=self.device)

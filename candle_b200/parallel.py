@@ -33,9 +33,9 @@ class Gatherer:
 
     Buffers are allocated once per shape so that the call can sit inside a CUDA graph."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, world: int | None = None):
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self._bufs: dict = {}
 
     def __call__(self, local: torch.Tensor) -> torch.Tensor:
