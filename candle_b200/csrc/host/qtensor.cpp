@@ -185,9 +185,9 @@ void QCudaStorage::fwd(size_t n, size_t k, const void *x, DType x_dtype, const i
     const size_t row_q8 = k_padded / 32 * 36;
     const size_t xs = dtype_size(x_dtype);
 
-    // Prefill path: many rows of a Q4_K matrix go to the tensor-core kernel.  It quantizes activations like
+    // Prefill path: many rows of a Q4_K / Q6_K matrix go to the tensor-core kernel.  It quantizes activations like
     // candle's CPU path (Q8_K) in every mode: that is the arithmetic the int8 planes are exact for.
-    if (rows > kPrefillMinRows && dtype_ == GgmlDType::Q4K) {
+    if (rows > kPrefillMinRows && (dtype_ == GgmlDType::Q4K || dtype_ == GgmlDType::Q6K)) {
         const size_t need = cq_prefill_scratch_bytes((int)rows, (int)k);
         uint8_t *scratch = (uint8_t *)workspace_ensure(device_, need);
         cq_prefill_quantize(x, (int)x_dtype, scratch, (int)k, (int)rows, stream);

@@ -41,7 +41,7 @@ enum class ActMode : int { Cuda = 0, CpuExact = 1 };
 
 constexpr size_t MATRIX_ROW_PADDING = 512;      // cuda.rs:38
 constexpr int MMVQ_MAX_BATCH = 8;               // fast_mmvq.rs:38
-constexpr size_t kPrefillMinRows = 16;          // more rows than this: tensor-core prefill kernel (Q4_K)
+constexpr size_t kPrefillMinRows = 16;          // more rows than this: tensor-core prefill kernel (Q4_K, Q6_K)
 
 struct Error : std::runtime_error { using std::runtime_error::runtime_error; };
 
@@ -69,7 +69,7 @@ class QCudaStorage {
 
     // y = x . W^T.  W is [n, k]; x is contiguous with last dimension k; `out` receives prod(dims[:-1]) * n
     // elements of x's dtype.  Up to 8 rows take the GEMV path (the reference switches to MMQ at the same
-    // point: fast_mmvq.rs:38, cuda.rs:846-861); above 16 rows Q4_K goes to the tcgen05 prefill kernel;
+    // point: fast_mmvq.rs:38, cuda.rs:846-861); above 16 rows Q4_K and Q6_K go to the tcgen05 prefill kernel;
     // everything in between, and the other formats, walk the GEMV in slices of 8 rows.
     void fwd(size_t n, size_t k, const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out,
              cudaStream_t stream) const;

@@ -1,4 +1,4 @@
-// Prefill-path quantized GEMM for B200: out[t, r] = sum_k x[t, k] * W[r, k] for many tokens, Q4_K weights,
+// Prefill-path quantized GEMM for B200: out[t, r] = sum_k x[t, k] * W[r, k] for many tokens, Q4_K and Q6_K weights,
 // on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in TMEM).
 //
 // Replaces candle's MMQ path for this format (host: candle-core/src/quantized/fast_mmq.rs:253-400; kernels:
@@ -184,14 +184,130 @@ __global__ void __launch_bounds__(256) quantize_q8k_tiles_kernel(const T *__rest
     if (lane == 0) *reinterpret_cast<float *>(blob + rows * 256 + (size_t)tl * 4) = d;
 }
 
+// ---- weight planes -----------------------------------------------------------------------------------------
+// RawBlock<T>: the GGUF bytes one producer thread needs for (weight row r, super-block sb, half h) and their
+// expansion into three int8 planes of 16-byte K slabs:  plane j of row r, slab s  ->  stB + s*kSlabB + (64*j + r)*16.
+template <int WTYPE> struct RawBlock;
+
+// Q4_K: thread (r, h) handles bytes [16h, 16h+16) of each of the four 32-byte nibble groups, i.e. elements
+// [16h, 16h+16) of all eight sub-blocks.  Planes: sl*q, sh*q (sc = 8*sh + sl), m replicated.
+template <> struct RawBlock<CQ_Q4_K> {
+    uint4 hdr, q[4];
+    __device__ __forceinline__ void load(const uint8_t *wrow, int sb, int h) {
+        const uint8_t *blk = wrow + sb * 144;
+        hdr = *reinterpret_cast<const uint4 *>(blk);
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) q[jp] = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * jp + 16 * h);
+    }
+    __device__ __forceinline__ void unpack(uint8_t *stB, int r, int h, float2 *wscale) const {
+        const uint32_t sw[3] = {hdr.y, hdr.z, hdr.w};         // the 12 scale bytes
+        if (h == 0) {
+            const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
+            wscale[r] = make_float2(__low2float(dm), __high2float(dm));
+        }
+        auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFF; };
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) {
+            uint32_t sc[2], mn[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {       // get_scale_min_k4, candle-core/src/quantized/utils.rs:50-60
+                const int j = 2 * jp + e;
+                if (j < 4) { sc[e] = sbyte(j) & 63; mn[e] = sbyte(j + 4) & 63; }
+                else {
+                    sc[e] = (sbyte(j + 4) & 0xF) | ((sbyte(j - 4) >> 6) << 4);
+                    mn[e] = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
+                }
+            }
+            const uint32_t qq[4] = {q[jp].x, q[jp].y, q[jp].z, q[jp].w};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {       // e = 0: low nibbles = sub-block 2jp, e = 1: high nibbles = 2jp+1
+                const uint32_t sl = sc[e] & 7, sh = sc[e] >> 3, mm = mn[e] * 0x01010101u;
+                uint32_t p1[4], p2[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t nib = (e ? (qq[i] >> 4) : qq[i]) & 0x0F0F0F0Fu;
+                    p1[i] = nib * sl;           // four byte products, each <= 105: no carries between bytes
+                    p2[i] = nib * sh;
+                }
+                const int slab = 2 * (2 * jp + e) + h;
+                uint8_t *dst = stB + slab * kSlabB + r * 16;
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+                *reinterpret_cast<uint4 *>(dst + kRowTile * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
+                *reinterpret_cast<uint4 *>(dst + 2 * kRowTile * 16) = make_uint4(mm, mm, mm, mm);
+            }
+        }
+    }
+};
+
+// Q6_K (210-byte blocks, 2-byte aligned): thread (r, h) handles the 128 elements of half h: ql[64h, 64h+64),
+// qh[32h, 32h+32), scales[8h, 8h+8).  value = d * sc * (q - 32) with int8 sc per 16 elements and q in 0..63.
+// Planes: with p = |sc| * q (<= 8064):  lo = p & 63, hi = p >> 6 (<= 126), both negated when sc < 0, and sc
+// replicated; then  sum sc (q - 32) q8 = 64 * (hi . q8) + (lo . q8) - 32 * (sc . q8)  exactly.
+// Bytes are fetched as aligned 32-bit words and re-aligned with a funnel shift when the block starts on an odd
+// 16-bit boundary.
+template <> struct RawBlock<CQ_Q6_K> {
+    uint32_t ql[17], qh[9], sc[3];
+    uint32_t d16, sh;
+    __device__ __forceinline__ void load(const uint8_t *wrow, int sb, int h) {
+        const uint8_t *blk = wrow + (size_t)sb * 210;
+        sh = (unsigned)((uintptr_t)blk & 2) * 8;
+        const uint32_t *a = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 64 * h) & ~(uintptr_t)3);
+        const uint32_t *b = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 128 + 32 * h) & ~(uintptr_t)3);
+        const uint32_t *c = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 192 + 8 * h) & ~(uintptr_t)3);
+#pragma unroll
+        for (int i = 0; i < 17; ++i) ql[i] = a[i];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) qh[i] = b[i];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) sc[i] = c[i];
+        d16 = *reinterpret_cast<const uint16_t *>(blk + 208);
+    }
+    __device__ __forceinline__ void unpack(uint8_t *stB, int r, int h, float2 *wscale) const {
+        if (h == 0) wscale[r] = make_float2(__half2float(__ushort_as_half((unsigned short)d16)), 0.0f);
+        const uint32_t s0 = __funnelshift_r(sc[0], sc[1], sh), s1 = __funnelshift_r(sc[1], sc[2], sh);
+#pragma unroll
+        for (int pos = 0; pos < 4; ++pos) {            // elements 128h + 32*pos + [0, 32)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {           // 16 elements sharing one scale: sub-block 8h + 2*pos + hf
+                const int j = 2 * pos + hf;
+                const int scv = (int)(int8_t)(((j < 4 ? s0 : s1) >> (8 * (j & 3))) & 0xFF);
+                const uint32_t mag = (uint32_t)(scv < 0 ? -scv : scv);
+                const bool negate = scv < 0;
+                uint32_t lo[4], hi[4];
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                    const int lw = (pos & 1) * 8 + hf * 4 + wi;        // word of ql: bytes 32*(pos&1) + 16*hf + 4*wi
+                    const int hw = hf * 4 + wi;                        // word of qh: bytes 16*hf + 4*wi
+                    const uint32_t l = __funnelshift_r(ql[lw], ql[lw + 1], sh);
+                    const uint32_t hb = __funnelshift_r(qh[hw], qh[hw + 1], sh);
+                    const uint32_t q6 = ((l >> (4 * (pos >> 1))) & 0x0F0F0F0Fu) | (((hb >> (2 * pos)) & 0x03030303u) << 4);
+                    const uint32_t pe = (q6 & 0x00FF00FFu) * mag, po = ((q6 >> 8) & 0x00FF00FFu) * mag;   // 16-bit lanes, <= 8064
+                    uint32_t lw_ = (pe & 0x003F003Fu) | ((po & 0x003F003Fu) << 8);
+                    uint32_t hw_ = ((pe >> 6) & 0x00FF00FFu) | (((po >> 6) & 0x00FF00FFu) << 8);
+                    // byte-wise negation of bytes in 0..127: (128 - b) ^ 128, no borrow between bytes
+                    lo[wi] = negate ? ((0x80808080u - lw_) ^ 0x80808080u) : lw_;
+                    hi[wi] = negate ? ((0x80808080u - hw_) ^ 0x80808080u) : hw_;
+                }
+                const uint32_t rep = ((uint32_t)scv & 0xFFu) * 0x01010101u;
+                const int slab = 8 * h + j;
+                uint8_t *dst = stB + slab * kSlabB + r * 16;
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(dst + kRowTile * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(dst + 2 * kRowTile * 16) = make_uint4(rep, rep, rep, rep);
+            }
+        }
+    }
+};
+
 // ---- the GEMM ---------------------------------------------------------------------------------------------
 // Shared memory: [control 1 KiB][A: 3 stages x 32 KiB][B: 2 stages x 48 KiB][d_a ring 8 x 512 B][(d, dmin) ring 8 x 512 B]
 // Dependencies per super-block sb (P_A / P_B producers, M = MMA, E = epilogue):
 //   P_A(sb) after M(sb-3) [bar_doneA]     P_B(sb) after M(sb-2) [bar_acc]      M(sb) after P_A(sb), P_B(sb), E(sb-2)
 //   E(sb) after M(sb) [bar_acc] and after the relay arrive on bar_vis, which carries the visibility of the scale rings.
 // The scale rings are 8 deep: an entry is rewritten for sb+8 only after M(sb+5), which itself waited for E(sb+3).
+template <int WTYPE>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_q4k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, void *__restrict__ out_v, int out_kind, int k,
+prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, void *__restrict__ out_v, int out_kind, int k,
                    int nrows, int tokens, int stride_out, int dbg) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t *bar_fullA = reinterpret_cast<uint64_t *>(smem);         // [3] activations landed (TMA bytes)
@@ -212,7 +328,7 @@ prefill_q4k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ ac
     const int row0 = blockIdx.x * kRowTile;
     const int tt = blockIdx.y;
     const int tile_rows = (int)TileBlob::tile_rows(tokens, tt);
-    const int row_bytes = nsb * 144;
+    const int row_bytes = nsb * cq_type_size(WTYPE);
 
     if (tid == 0) {
         for (int i = 0; i < 3; ++i) { cq_mbar_init(&bar_fullA[i], 1); cq_mbar_init(&bar_doneA[i], 1); }
@@ -242,10 +358,8 @@ prefill_q4k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ ac
         if (grow >= nrows) grow = nrows - 1;        // ragged last tile: duplicate a valid row, never stored
         const uint8_t *wrow = w + (size_t)grow * row_bytes;
         // the GGUF bytes of the next super-block are fetched one iteration ahead of their use
-        uint4 n_hdr = *reinterpret_cast<const uint4 *>(wrow);
-        uint4 n_q[4];
-#pragma unroll
-        for (int jp = 0; jp < 4; ++jp) n_q[jp] = *reinterpret_cast<const uint4 *>(wrow + 16 + 32 * jp + 16 * h);
+        RawBlock<WTYPE> nxt_raw;
+        nxt_raw.load(wrow, 0, h);
         for (int sb = 0; sb < nsb; ++sb) {
             const int s = sb & 1;
             uint8_t *stB = stB0 + s * kStageB;
@@ -254,54 +368,10 @@ prefill_q4k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ ac
                 mbar_arrive(&bar_fullB[s]);
                 continue;
             }
-            const uint4 hdr = n_hdr;
-            uint4 c_q[4];
-#pragma unroll
-            for (int jp = 0; jp < 4; ++jp) c_q[jp] = n_q[jp];
-            if (sb + 1 < nsb) {
-                const uint8_t *nblk = wrow + (sb + 1) * 144;
-                n_hdr = *reinterpret_cast<const uint4 *>(nblk);
-#pragma unroll
-                for (int jp = 0; jp < 4; ++jp) n_q[jp] = *reinterpret_cast<const uint4 *>(nblk + 16 + 32 * jp + 16 * h);
-            }
+            const RawBlock<WTYPE> cur = nxt_raw;
+            if (sb + 1 < nsb) nxt_raw.load(wrow, sb + 1, h);
             if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;   // M(sb-2) has read this stage
-            const uint32_t sw[3] = {hdr.y, hdr.z, hdr.w};         // the 12 scale bytes
-            if (h == 0) {
-                const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
-                *reinterpret_cast<float2 *>(ringW + (sb & 7) * 512 + r * 8) = make_float2(__low2float(dm), __high2float(dm));
-            }
-            auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFF; };
-#pragma unroll
-            for (int jp = 0; jp < 4; ++jp) {
-                uint32_t sc[2], mn[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {       // get_scale_min_k4, candle-core/src/quantized/utils.rs:50-60
-                    const int j = 2 * jp + e;
-                    if (j < 4) { sc[e] = sbyte(j) & 63; mn[e] = sbyte(j + 4) & 63; }
-                    else {
-                        sc[e] = (sbyte(j + 4) & 0xF) | ((sbyte(j - 4) >> 6) << 4);
-                        mn[e] = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
-                    }
-                }
-                const uint4 q = c_q[jp];
-                const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {       // e = 0: low nibbles = sub-block 2jp, e = 1: high nibbles = 2jp+1
-                    const uint32_t sl = sc[e] & 7, sh = sc[e] >> 3, mm = mn[e] * 0x01010101u;
-                    uint32_t p1[4], p2[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t nib = (e ? (qq[i] >> 4) : qq[i]) & 0x0F0F0F0Fu;
-                        p1[i] = nib * sl;           // four byte products, each <= 105: no carries between bytes
-                        p2[i] = nib * sh;
-                    }
-                    const int slab = 2 * (2 * jp + e) + h;
-                    uint8_t *dst = stB + slab * kSlabB + r * 16;
-                    *reinterpret_cast<uint4 *>(dst) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
-                    *reinterpret_cast<uint4 *>(dst + kRowTile * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
-                    *reinterpret_cast<uint4 *>(dst + 2 * kRowTile * 16) = make_uint4(mm, mm, mm, mm);
-                }
-            }
+            cur.unpack(stB, r, h, reinterpret_cast<float2 *>(ringW + (sb & 7) * 512));
             fence_proxy_async_smem();       // make these generic-proxy writes visible to the tensor core
             mbar_arrive(&bar_fullB[s]);
         }
@@ -382,9 +452,15 @@ prefill_q4k_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ ac
                     const float4 dw = *reinterpret_cast<const float4 *>(rw + (c * 16 + i) * 8);   // (d, dmin) x 2 rows
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int sdot = 8 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e];     // exact, up to 3.1e7
                         const float dd = e ? dw.z : dw.x, dmn = e ? dw.w : dw.y;
-                        const float t = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float((int)vm[c & 1][i + e])));
+                        float t;
+                        if constexpr (WTYPE == CQ_Q4_K) {
+                            const int sdot = 8 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e];     // exact, up to 3.1e7
+                            t = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float((int)vm[c & 1][i + e])));
+                        } else {        // Q6_K: 64*hi + lo - 32*sum(sc*q8), exact in int32 (< 4.1e8)
+                            const int tot = 64 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e] - 32 * (int)vm[c & 1][i + e];
+                            t = __fmul_rn(dd, (float)tot);
+                        }
                         acc[c * 16 + i + e] = __fmaf_rn(da, t, acc[c * 16 + i + e]);
                     }
                 }
@@ -444,24 +520,30 @@ extern "C" void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, 
         cq_set_status(CQ_ERR_BAD_ARG, "prefill gemm: null pointer, empty shape or K not a multiple of 256");
         return;
     }
-    if (wtype != CQ_Q4_K) {
-        cq_set_status(CQ_ERR_UNSUPPORTED, "prefill gemm: the tensor-core kernel covers Q4_K");
+    if (wtype != CQ_Q4_K && wtype != CQ_Q6_K) {
+        cq_set_status(CQ_ERR_UNSUPPORTED, "prefill gemm: the tensor-core kernel covers Q4_K and Q6_K");
         return;
     }
-    if ((uintptr_t)vx % 16 != 0 || (uintptr_t)scratch % 16 != 0) {
-        cq_set_status(CQ_ERR_BAD_ARG, "prefill gemm: weights and scratch must be 16-byte aligned");
+    if ((uintptr_t)vx % (wtype == CQ_Q4_K ? 16 : 4) != 0 || (uintptr_t)scratch % 16 != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "prefill gemm: misaligned weights (16 bytes for Q4_K, 4 for Q6_K) or scratch (16)");
         return;
     }
-    static bool attr_done[64] = {};
+    static bool attr_done[2][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(prefill_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        attr_done[dev] = true;
+    const int ti = wtype == CQ_Q4_K ? 0 : 1;
+    if (dev >= 0 && dev < 64 && !attr_done[ti][dev]) {
+        if (ti == 0) cudaFuncSetAttribute(prefill_kernel<CQ_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        else cudaFuncSetAttribute(prefill_kernel<CQ_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        attr_done[ti][dev] = true;
     }
     const dim3 grid((nrows_x + kRowTile - 1) / kRowTile, (tokens + kTokTile - 1) / kTokTile);
-    prefill_q4k_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>((const uint8_t *)vx, (const uint8_t *)scratch, dst,
-                                                                               out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg);
+    if (ti == 0)
+        prefill_kernel<CQ_Q4_K><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(
+            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg);
+    else
+        prefill_kernel<CQ_Q6_K><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(
+            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg);
     cq_check_launch("prefill gemm");
 }
 

@@ -21,13 +21,13 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _prefill(lib, w_dev, x_dev, k, n, out_dtype=torch.float32):
+def _prefill(lib, w_dev, x_dev, k, n, out_dtype=torch.float32, wtype=Q4K):
     tokens = x_dev.shape[0]
     elem = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
     scratch = torch.full((lib.cq_prefill_scratch_bytes(tokens, k),), 0x5A, dtype=torch.uint8, device=x_dev.device)
     out = torch.full((tokens * n + 32,), float("nan"), dtype=out_dtype, device=x_dev.device)
     lib.cq_prefill_quantize(x_dev.data_ptr(), elem[x_dev.dtype], scratch.data_ptr(), k, tokens, _stream())
-    lib.cq_prefill_gemm(Q4K, w_dev.data_ptr(), scratch.data_ptr(), out.data_ptr(), elem[out_dtype], k, n, tokens, n, _stream())
+    lib.cq_prefill_gemm(wtype, w_dev.data_ptr(), scratch.data_ptr(), out.data_ptr(), elem[out_dtype], k, n, tokens, n, _stream())
     capi.check("prefill")
     torch.cuda.synchronize()
     assert lib.cq_prefill_timeout_flag() == 0
@@ -69,6 +69,21 @@ def test_prefill_matches_cpu_vec_dot(lib, oracle, cuda_dev, tokens, k, n):
     ref = oracle.matmul(Q4K, x, wq, n)
     assert rel_err(out.cpu().numpy(), ref) <= TOL
     assert rel_err(out.cpu().numpy(), ref) <= 1e-5     # only the order of f32 additions differs
+
+
+@pytest.mark.parametrize("tokens,k,n", [(128, 256, 64), (17, 512, 65), (300, 2048, 200), (130, 4096, 96), (520, 14336, 70)])
+def test_prefill_q6k_matches_cpu_vec_dot(lib, oracle, cuda_dev, tokens, k, n):
+    Q6K = 14
+    _, x, wq = make_case(oracle, Q6K, k, n, tokens, seed=tokens + k + n)
+    # include negative, zero and extreme sub-block scales
+    blk = wq.reshape(-1, 210)
+    blk[0, 192:208] = np.array([-128, 127, 0, -1, 1, -64, 64, 5, -5, 100, -100, 33, -33, 2, -2, 0], dtype=np.int8).view(np.uint8)
+    w_dev = torch.from_numpy(wq).to(cuda_dev)
+    x_dev = torch.from_numpy(x).to(cuda_dev)
+    _, out = _prefill(lib, w_dev, x_dev, k, n, wtype=Q6K)
+    ref = oracle.matmul(Q6K, x, wq, n)
+    assert rel_err(out.cpu().numpy(), ref) <= TOL
+    assert rel_err(out.cpu().numpy(), ref) <= 1e-5
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
