@@ -283,6 +283,14 @@ def run_gpu(args):
 
     ms_e2e = timed(step_e2e, args.steps, args.warmup, False)
 
+    # free the sweep's buffers before building the decoder
+    del mats, xs, outs, q8, h_x, h_y, d_x
+    gathered = None
+    torch.cuda.empty_cache()
+    decode = None
+    if not args.no_decode:
+        decode = [decode_tok_s(dev, rank, world, b) for b in (1, 8)]
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -309,6 +317,8 @@ def run_gpu(args):
                      "kernel": "gemv_staged_kernel (all 60 GEMV launches of the step, quantize launches excluded)",
                      "ms_per_step": ms_gemv, "per_gpu": True},
         "clocks": clocks,
+        "decode": {"model": "Llama-3-8B-shaped, Q4_K_M mix, random weights", "prompt": 512, "steps": 256,
+                   "parallelism": f"row-sharded projections x{world}, all-gather", "runs": decode},
     }
     if world == 1:
         from oracle import oracle as O
@@ -389,8 +399,50 @@ def run_prefill_case(args):
     print(json.dumps({"prefill_case": args.prefill_case, "ms": times, "useful_TOPS": 2.0 * m * n * k / best / 1e9}))
 
 
+def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=True):
+    """BASELINE configs[3]: Llama-3-8B-shaped Q4_K_M decoder, random prompt of `prompt_len` ids (seed 2), `steps` greedy
+    tokens.  Returns (decode tokens/s over all sequences, prompt tokens/s, token checksum)."""
+    import torch
+    import torch.distributed as dist
+    from candle_b200.decoder import DecoderConfig, LlamaShapedDecoder
+    cfg = DecoderConfig.llama3_8b()
+    m = LlamaShapedDecoder(cfg, dev, rank=rank, world=world, batch=batch, seed=1)
+    prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), device=dev, generator=torch.Generator(device=dev).manual_seed(2))
+    m.forward(prompt)          # grows the activation workspace to its final size before anything is recorded
+    graphed = m.capture_decode_step() if use_graph else False
+    m.reset()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    tok = m.forward(prompt)
+    e1.record()
+    toks = [tok]
+    for _ in range(steps - 1):
+        tok = m.decode_step(tok).clone()
+        toks.append(tok)
+    e2.record()
+    torch.cuda.synchronize()
+    t_prompt, t_dec = e0.elapsed_time(e1), e1.elapsed_time(e2)
+    if world > 1:
+        t = torch.tensor([t_prompt, t_dec], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_prompt, t_dec = float(t[0]), float(t[1])
+    checksum = int(torch.stack(toks).sum().item())
+    del m
+    torch.cuda.empty_cache()
+    return {"batch": batch, "decode_tok_s": batch * (steps - 1) / t_dec * 1e3, "ms_per_step": t_dec / (steps - 1),
+            "prompt_tok_s": batch * prompt_len / t_prompt * 1e3, "cuda_graph": bool(graphed), "token_checksum": checksum,
+            "weight_bytes_per_token": cfg.weight_bytes_per_token(),
+            "weight_stream_GBps": cfg.weight_bytes_per_token() / (t_dec / (steps - 1)) / 1e6}
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--decode-case", default=None, help="profile helper: BATCH:PROMPT:STEPS, runs only the decoder measurement")
+    ap.add_argument("--no-graph", action="store_true", help="with --decode-case: launch decode steps eagerly")
+    ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
     ap.add_argument("--iters", type=int, default=4)
@@ -399,7 +451,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
-    if args.prefill_case:
+    if args.decode_case:
+        import torch
+        b_, p_, s_ = (int(v) for v in args.decode_case.split(":"))
+        torch.cuda.set_device(0)
+        print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
+    elif args.prefill_case:
         run_prefill_case(args)
     elif args.case:
         run_case(args)

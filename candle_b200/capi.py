@@ -61,7 +61,11 @@ def lib() -> C.CDLL:
         L.cq_moe_gemv_sorted.argtypes = [i32, i32, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_indexed_moe_forward.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
         L.cq_moe_timeout_flag.restype = i32
-        L.cq_attention_f32.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp]
+        L.cq_attention_f32.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp]
+        L.cq_rms_norm_f32.argtypes = [vp, vp, vp, i32, i32, C.c_float, vp]
+        L.cq_add_rms_norm_f32.argtypes = [vp, vp, vp, vp, i32, i32, C.c_float, vp]
+        L.cq_rope_store_kv_f32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        L.cq_silu_mul_f32.argtypes = [vp, vp, i32, i32, vp]
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]

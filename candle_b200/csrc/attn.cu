@@ -6,7 +6,8 @@
 // eight, which changes f32 rounding and, eventually, greedy tokens.  Here every (sequence, head, query) is one CTA
 // that adds in a fixed order, so a head gives the same bits wherever it runs.
 //
-//   q, out : [B, Tq, Hq, D]      k, v cache : [B, Hkv, Tmax, D]      D = 128, f32, contiguous
+//   q : B*Tq rows of q_stride floats, heads side by side     out : [B, Tq, Hq, D]
+//   k, v cache : [B, Hkv, Tmax, D]      D = 128, f32
 //   pos    : device int, cache position of query 0 (query t attends to keys 0 .. pos + t)
 #include "../../include/candle_q_b200.h"
 #include "common.cuh"
@@ -15,46 +16,73 @@ namespace {
 
 constexpr int kD = 128;
 
-__global__ void __launch_bounds__(128) attention_f32_kernel(const float *__restrict__ q, const float *__restrict__ kc,
-                                                            const float *__restrict__ vc, float *__restrict__ out,
-                                                            const int *__restrict__ pos, int tq, int hq, int hkv, int tmax,
-                                                            float scale) {
+constexpr int kWarps = 32;
+constexpr int kThreads = 32 * kWarps;
+
+// 32 warps; a decode step is latency-bound (one CTA walks the whole context of its head), so the loops keep four
+// independent loads in flight per thread.  The order of additions is a function of the context length only:
+//   scores : key j is reduced by the 8 lanes of one group (lane g of the group owns dims {4(g + 8i) .. +3, i = 0..3},
+//            added in that order, then a 3-step xor butterfly);
+//   output : warp w adds its keys j = w, w + 32, ... in ascending order, lane l owns dims 4l .. 4l+3; the 32 warps'
+//            partial sums are then added in warp order.
+__global__ void __launch_bounds__(kThreads) attention_f32_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+                                                                 const float *__restrict__ vc, float *__restrict__ out,
+                                                                 const int *__restrict__ pos, int tq, int hq, int hkv,
+                                                                 int tmax, float scale, int q_stride) {
     extern __shared__ float scores[];           // [n_ctx]
-    __shared__ float red[4];
+    __shared__ float red[kWarps];
+    __shared__ float4 part[kWarps][32];
     const int h = blockIdx.x, t = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int n_ctx = pos[0] + t + 1;
     if (n_ctx > tmax) n_ctx = tmax;
     const int kvh = h / (hq / hkv);
-    const float *qp = q + (((size_t)b * tq + t) * hq + h) * kD;
+    const float *qp = q + ((size_t)b * tq + t) * q_stride + (size_t)h * kD;
     const float *kp = kc + ((size_t)b * hkv + kvh) * (size_t)tmax * kD;
     const float *vp = vc + ((size_t)b * hkv + kvh) * (size_t)tmax * kD;
 
-    // scores: warp w takes keys w, w+4, ...; each lane 4 dims, fixed in-lane order, xor butterfly across lanes
-    const float4 qv = *reinterpret_cast<const float4 *>(qp + 4 * lane);
-    for (int j = warp; j < n_ctx; j += 4) {
-        const float4 kv = *reinterpret_cast<const float4 *>(kp + (size_t)j * kD + 4 * lane);
-        float s = __fmul_rn(qv.x, kv.x);
-        s = __fmaf_rn(qv.y, kv.y, s);
-        s = __fmaf_rn(qv.z, kv.z, s);
-        s = __fmaf_rn(qv.w, kv.w, s);
+    // scores: 128 keys per pass of the CTA, one key per group of 8 lanes
+    {
+        const int g = tid & 7, grp = tid >> 3;
+        float4 qv[4];
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-        if (lane == 0) scores[j] = __fmul_rn(s, scale);
+        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4 *>(qp + 4 * (g + 8 * i));
+        for (int j0 = 0; j0 < n_ctx; j0 += kThreads / 8) {
+            const int j = j0 + grp;
+            const bool live = j < n_ctx;
+            float4 kv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                kv[i] = live ? *reinterpret_cast<const float4 *>(kp + (size_t)j * kD + 4 * (g + 8 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s = __fmaf_rn(qv[i].x, kv[i].x, s);
+                s = __fmaf_rn(qv[i].y, kv[i].y, s);
+                s = __fmaf_rn(qv[i].z, kv[i].z, s);
+                s = __fmaf_rn(qv[i].w, kv[i].w, s);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            if (live && g == 0) scores[j] = __fmul_rn(s, scale);
+        }
     }
     __syncthreads();
     // max (exact whatever the order)
     float mx = -INFINITY;
-    for (int j = tid; j < n_ctx; j += 128) mx = fmaxf(mx, scores[j]);
+    for (int j = tid; j < n_ctx; j += kThreads) mx = fmaxf(mx, scores[j]);
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
     if (lane == 0) red[warp] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, red[w]);
     __syncthreads();
     // exp and sum: thread-strided partial sums, xor butterfly, warps added in index order
     float sum = 0.0f;
-    for (int j = tid; j < n_ctx; j += 128) {
+    for (int j = tid; j < n_ctx; j += kThreads) {
         const float p = expf(scores[j] - mx);
         scores[j] = p;
         sum += p;
@@ -63,17 +91,50 @@ __global__ void __launch_bounds__(128) attention_f32_kernel(const float *__restr
     for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
     if (lane == 0) red[warp] = sum;
     __syncthreads();
-    sum = ((red[0] + red[1]) + red[2]) + red[3];
-    // weighted values: thread d walks the keys in order
-    float o = 0.0f;
-    for (int j = 0; j < n_ctx; ++j) o = __fmaf_rn(scores[j], vp[(size_t)j * kD + tid], o);
-    out[(((size_t)b * tq + t) * hq + h) * kD + tid] = __fdiv_rn(o, sum);
+    sum = red[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) sum += red[w];
+    // weighted values: four loads in flight, added in ascending key order
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j0 = warp; j0 < n_ctx; j0 += 4 * kWarps) {
+        float4 vv[4];
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = j0 + i * kWarps;
+            const bool live = j < n_ctx;
+            p[i] = live ? scores[j] : 0.0f;
+            vv[i] = live ? *reinterpret_cast<const float4 *>(vp + (size_t)j * kD + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (j0 + i * kWarps < n_ctx) {      // a skipped key must not turn -0 into +0
+                o.x = __fmaf_rn(p[i], vv[i].x, o.x);
+                o.y = __fmaf_rn(p[i], vv[i].y, o.y);
+                o.z = __fmaf_rn(p[i], vv[i].z, o.z);
+                o.w = __fmaf_rn(p[i], vv[i].w, o.w);
+            }
+        }
+    }
+    part[warp][lane] = o;
+    __syncthreads();
+    if (warp == 0) {
+        float4 acc = part[0][lane];
+#pragma unroll 4
+        for (int w = 1; w < kWarps; ++w) {
+            const float4 pw = part[w][lane];
+            acc.x += pw.x; acc.y += pw.y; acc.z += pw.z; acc.w += pw.w;
+        }
+        float4 r;
+        r.x = __fdiv_rn(acc.x, sum); r.y = __fdiv_rn(acc.y, sum); r.z = __fdiv_rn(acc.z, sum); r.w = __fdiv_rn(acc.w, sum);
+        *reinterpret_cast<float4 *>(out + (((size_t)b * tq + t) * hq + h) * kD + 4 * lane) = r;
+    }
 }
 
 }  // namespace
 
 extern "C" void cq_attention_f32(const float *q, const float *k_cache, const float *v_cache, float *out, const int *pos,
-                                 int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale, void *stream) {
+                                 int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, void *stream) {
     if (!q || !k_cache || !v_cache || !out || !pos || batch <= 0 || tq <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0) {
         cq_set_status(CQ_ERR_BAD_ARG, "attention: null pointer or bad head counts");
         return;
@@ -83,7 +144,7 @@ extern "C" void cq_attention_f32(const float *q, const float *k_cache, const flo
         return;
     }
     const dim3 grid(hq, tq, batch);
-    attention_f32_kernel<<<grid, 128, (size_t)tmax * sizeof(float), (cudaStream_t)stream>>>(q, k_cache, v_cache, out, pos, tq,
-                                                                                             hq, hkv, tmax, scale);
+    attention_f32_kernel<<<grid, kThreads, (size_t)tmax * sizeof(float), (cudaStream_t)stream>>>(q, k_cache, v_cache, out, pos, tq,
+                                                                                             hq, hkv, tmax, scale, q_stride);
     cq_check_launch("attention");
 }

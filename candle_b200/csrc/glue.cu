@@ -1,0 +1,129 @@
+// Small f32 glue kernels for the decoder harness: the element-wise steps that sit between the quantized matmuls
+// of a Llama-style block (candle-transformers/src/models/quantized_llama.rs:56-62, 178-262; candle's own kernels for
+// them are candle-kernels/src/reduce.cu:559-681 and unary.cu).  One launch each instead of a chain of tensor ops, so
+// that a decode step is not dominated by launch overhead.  Everything is per row with a fixed order of additions.
+#include "../../include/candle_q_b200.h"
+#include "common.cuh"
+
+namespace {
+
+// out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w      one CTA of 1024 threads per row, d a multiple of 4.
+// With a residual, x[r, :] += residual[r, :] is done (and stored) first.  A thread owns float4 number tid, tid + 1024,
+// ...: the first of them stays in registers, so that a row of up to 4096 floats is read once.  Squares are added
+// element by element per thread, then by an xor butterfly, then over the 32 warps in index order.
+__global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, const float *__restrict__ residual,
+                                                        const float *__restrict__ w, float *__restrict__ out, int d, float eps) {
+    __shared__ float red[32];
+    const int n4 = d >> 2, tid = threadIdx.x;
+    float4 *xr = reinterpret_cast<float4 *>(x + (size_t)blockIdx.x * d);
+    const float4 *rr = residual ? reinterpret_cast<const float4 *>(residual + (size_t)blockIdx.x * d) : nullptr;
+    float4 first = make_float4(0.f, 0.f, 0.f, 0.f);
+    float s = 0.0f;
+    for (int i = tid; i < n4; i += 1024) {
+        float4 v = xr[i];
+        if (rr) {
+            const float4 r = rr[i];
+            v.x = __fadd_rn(v.x, r.x); v.y = __fadd_rn(v.y, r.y); v.z = __fadd_rn(v.z, r.z); v.w = __fadd_rn(v.w, r.w);
+            xr[i] = v;
+        }
+        if (i == tid) first = v;
+        s = __fmaf_rn(v.x, v.x, s); s = __fmaf_rn(v.y, v.y, s); s = __fmaf_rn(v.z, v.z, s); s = __fmaf_rn(v.w, v.w, s);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if ((tid & 31) == 0) red[tid >> 5] = s;
+    __syncthreads();
+    s = red[0];
+#pragma unroll
+    for (int i = 1; i < 32; ++i) s += red[i];
+    const float inv = rsqrtf(__fadd_rn(__fdiv_rn(s, (float)d), eps));
+    float4 *o = reinterpret_cast<float4 *>(out + (size_t)blockIdx.x * d);
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+    for (int i = tid; i < n4; i += 1024) {
+        const float4 v = (i == tid) ? first : xr[i];      // later ones were written by this same thread
+        const float4 g = w4[i];
+        float4 r;
+        r.x = __fmul_rn(__fmul_rn(v.x, inv), g.x); r.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
+        r.z = __fmul_rn(__fmul_rn(v.z, inv), g.z); r.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
+        o[i] = r;
+    }
+}
+
+// Interleaved rotary embedding (pairs (2i, 2i+1), candle's rope_i) applied in place to q and to k, then k and v are
+// written into the caches at position pos + t.  q: [B*T rows of q_stride floats], heads side by side; k, v likewise
+// (so q and k may be column ranges of one projection output); caches [B, Hkv, Tmax, D]; cos / sin: [max_pos, D/2].
+// One thread per pair of elements.
+__global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, float *__restrict__ k, const float *__restrict__ v,
+                                                         const float *__restrict__ cosv, const float *__restrict__ sinv,
+                                                         const int *__restrict__ pos, float *__restrict__ kc,
+                                                         float *__restrict__ vc, int B, int T, int hq, int hkv, int tmax,
+                                                         int half_d, int q_stride, int k_stride, int v_stride) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nq = (int64_t)B * T * hq * half_d, nk = (int64_t)B * T * hkv * half_d;
+    if (idx >= nq + nk) return;
+    const bool is_q = idx < nq;
+    const int64_t e = is_q ? idx : idx - nq;
+    const int heads = is_q ? hq : hkv;
+    const int i = (int)(e % half_d);
+    const int hh = (int)((e / half_d) % heads);
+    const int t = (int)((e / ((int64_t)half_d * heads)) % T);
+    const int b = (int)(e / ((int64_t)half_d * heads * T));
+    const int p = pos[0] + t;
+    const float c = cosv[(size_t)p * half_d + i], s = sinv[(size_t)p * half_d + i];
+    float *src = (is_q ? q : k) + ((size_t)b * T + t) * (is_q ? q_stride : k_stride) + ((size_t)hh * half_d + i) * 2;
+    const float x0 = src[0], x1 = src[1];
+    const float r0 = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+    const float r1 = __fmaf_rn(x0, s, __fmul_rn(x1, c));
+    if (is_q) { src[0] = r0; src[1] = r1; }
+    else if (p < tmax) {
+        const size_t co = ((((size_t)b * hkv + hh) * tmax + p) * half_d + i) * 2;
+        kc[co] = r0; kc[co + 1] = r1;
+        const float *vs = v + ((size_t)b * T + t) * v_stride + ((size_t)hh * half_d + i) * 2;
+        vc[co] = vs[0]; vc[co + 1] = vs[1];
+    }
+}
+
+// out[r, i] = silu(gu[r, i]) * gu[r, f + i]   with gu = [gate | up] rows of width 2f;  silu(x) = x / (1 + exp(-x))
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, float *__restrict__ out, int64_t rows, int f) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * f) return;
+    const int64_t r = idx / f;
+    const int i = (int)(idx % f);
+    const float g = gu[r * 2 * f + i], u = gu[r * 2 * f + f + i];
+    out[idx] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+}
+
+}  // namespace
+
+extern "C" void cq_rms_norm_f32(const float *x, const float *w, float *out, int rows, int d, float eps, void *stream) {
+    if (!x || !w || !out || rows <= 0 || d <= 0 || d % 4) { cq_set_status(CQ_ERR_BAD_ARG, "rms_norm: bad arguments (d must be a multiple of 4)"); return; }
+    rms_norm_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(const_cast<float *>(x), nullptr, w, out, d, eps);
+    cq_check_launch("rms_norm");
+}
+
+extern "C" void cq_add_rms_norm_f32(float *x, const float *residual, const float *w, float *out, int rows, int d, float eps,
+                                    void *stream) {
+    if (!x || !residual || !w || !out || rows <= 0 || d <= 0 || d % 4) { cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm: bad arguments (d must be a multiple of 4)"); return; }
+    rms_norm_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(x, residual, w, out, d, eps);
+    cq_check_launch("add_rms_norm");
+}
+
+extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
+                                     float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
+                                     int q_stride, int k_stride, int v_stride, void *stream) {
+    if (!q || !k || !v || !cosv || !sinv || !pos || !k_cache || !v_cache || batch <= 0 || t <= 0 || head_dim % 2) {
+        cq_set_status(CQ_ERR_BAD_ARG, "rope: bad arguments");
+        return;
+    }
+    const int64_t n = (int64_t)batch * t * (hq + hkv) * (head_dim / 2);
+    rope_store_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(q, k, v, cosv, sinv, pos, k_cache, v_cache, batch,
+                                                                                      t, hq, hkv, tmax, head_dim / 2, q_stride, k_stride, v_stride);
+    cq_check_launch("rope");
+}
+
+extern "C" void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream) {
+    if (!gate_up || !out || rows <= 0 || f <= 0) { cq_set_status(CQ_ERR_BAD_ARG, "silu_mul: bad arguments"); return; }
+    const int64_t n = (int64_t)rows * f;
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate_up, out, rows, f);
+    cq_check_launch("silu_mul");
+}

@@ -97,7 +97,7 @@ ActMode act_mode() { return (ActMode)g_act_mode.load(); }
 
 // ---- workspace -------------------------------------------------------------------------------
 namespace {
-struct Slot { void *ptr = nullptr; size_t cap = 0; };
+struct Slot { void *ptr = nullptr; size_t cap = 0; std::vector<void *> retired; };
 std::mutex g_ws_mu;
 std::map<int, Slot> g_ws;
 }  // namespace
@@ -107,10 +107,12 @@ void *workspace_ensure(int device, size_t bytes) {
     Slot &s = g_ws[device];
     if (s.cap < bytes) {
         DeviceGuard g(device);
-        const size_t cap = pad(bytes + bytes / 4, 1 << 20);     // grow with head-room, never shrink
+        size_t cap = pad(bytes + bytes / 4, 1 << 20);     // grow with head-room, never shrink
+        if (cap < 2 * s.cap) cap = 2 * s.cap;             // geometric growth bounds what the retired buffers hold
         void *p = nullptr;
         cuda_check(cudaMalloc(&p, cap), "workspace cudaMalloc");
-        if (s.ptr) cudaFree(s.ptr);     // cudaFree waits for kernels still using the old buffer
+        // The old buffer is kept until the process ends: launches recorded in a CUDA graph may still point at it.
+        if (s.ptr) s.retired.push_back(s.ptr);
         s.ptr = p;
         s.cap = cap;
     }

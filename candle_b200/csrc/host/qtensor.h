@@ -119,9 +119,9 @@ class QMatMul {
 void set_act_mode(ActMode m);
 ActMode act_mode();
 
-// Per-device grows-only scratch shared by all calls (fast_mmvq.rs:44-81).  Returns a device pointer valid
-// until the next call that needs a larger buffer on the same device.  Growing allocates with cudaMalloc,
-// which synchronises the device: warm the workspace up before capturing a CUDA graph.
+// Per-device grows-only scratch shared by all calls (fast_mmvq.rs:44-81).  Growing allocates a new buffer with
+// cudaMalloc (which synchronises the device, so reserve before capturing a CUDA graph); buffers that were
+// outgrown stay allocated until the process ends, because launches recorded in a graph may still use them.
 void *workspace_ensure(int device, size_t bytes);
 
 }  // namespace candle_q

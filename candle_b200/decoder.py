@@ -7,8 +7,9 @@ and the greedy loop of candle-examples/examples/quantized/main.rs:616-690.  Weig
 
 Tensor parallelism: every projection is sharded by output rows (whole heads for q/k/v) and its output slices are
 all-gathered; nothing is ever reduced across ranks, so a token sequence is bit-identical at 1, 2, 4 and 8 GPUs.
-Glue (norms, RoPE, SwiGLU, residuals) is torch elementwise code on replicated tensors; attention is
-``cq_attention_f32``, whose summation order does not depend on how many heads a rank owns.
+Glue (norm with the pending residual add, RoPE with the KV-cache store, SwiGLU) is one small f32 kernel per step
+(csrc/glue.cu); attention is ``cq_attention_f32``, whose summation order does not depend on how many heads a rank
+owns.  q and k of a layer come from one stacked projection, gate and up from another.
 Weights are generated in eight row pieces with seeds that do not depend on the world size.
 """
 from __future__ import annotations
@@ -55,12 +56,20 @@ class DecoderConfig:
         return int(self.layers * per_layer + self.vocab * d * q6)
 
 
-def _sharded_matmul(dtype: GgmlDType, n: int, k: int, seed: int, rank: int, world: int, device) -> QMatMul:
+def _sharded_blocks(dtype: GgmlDType, n: int, k: int, seed: int, rank: int, world: int, device) -> torch.Tensor:
+    """GGUF blocks of this rank's rows of a [n, k] projection, generated piece by piece."""
     per = PIECES // world
     piece_rows = n // PIECES
-    parts = [random_blocks(dtype, piece_rows, k, seed * 16 + p, device) for p in range(rank * per, (rank + 1) * per)]
-    blocks = torch.cat(parts, dim=0).contiguous()
-    return QMatMul.from_qtensor(QTensor.from_device_blocks(blocks, dtype, (piece_rows * per, k)))
+    return torch.cat([random_blocks(dtype, piece_rows, k, seed * 16 + p, device) for p in range(rank * per, (rank + 1) * per)], dim=0)
+
+
+def _sharded_matmul(dtype: GgmlDType, k: int, parts, rank: int, world: int, device) -> QMatMul:
+    """One QMatMul over the local rows of one or several projections of the same block format that read the same
+    input (`parts`: (rows, seed) pairs).  A GEMV row never depends on its neighbours, so stacking projections does
+    not change any output bit; it only saves launches and activation quantizations."""
+    blocks = torch.cat([_sharded_blocks(dtype, n, k, seed, rank, world, device) for n, seed in parts], dim=0).contiguous()
+    rows = sum(n for n, _ in parts) // world
+    return QMatMul.from_qtensor(QTensor.from_device_blocks(blocks, dtype, (rows, k)))
 
 
 class _Layer:
@@ -84,18 +93,17 @@ class LlamaShapedDecoder:
             s = seed * 100003 + li * 16
             L.attn_norm = 1.0 + 0.1 * torch.randn(d, device=self.device, generator=g)
             L.ffn_norm = 1.0 + 0.1 * torch.randn(d, device=self.device, generator=g)
-            L.wq = _sharded_matmul(GgmlDType.Q4K, cfg.n_heads * hd, d, s + 1, rank, world, self.device)
-            L.wk = _sharded_matmul(GgmlDType.Q4K, cfg.n_kv_heads * hd, d, s + 2, rank, world, self.device)
-            L.wv = _sharded_matmul(GgmlDType.Q6K, cfg.n_kv_heads * hd, d, s + 3, rank, world, self.device)
-            L.wo = _sharded_matmul(GgmlDType.Q4K, d, cfg.n_heads * hd, s + 4, rank, world, self.device)
-            L.gate = _sharded_matmul(GgmlDType.Q4K, cfg.ffn, d, s + 5, rank, world, self.device)
-            L.up = _sharded_matmul(GgmlDType.Q4K, cfg.ffn, d, s + 6, rank, world, self.device)
-            L.down = _sharded_matmul(GgmlDType.Q6K, d, cfg.ffn, s + 7, rank, world, self.device)
+            mm = lambda dtype, k, parts: _sharded_matmul(dtype, k, parts, rank, world, self.device)
+            L.wqk = mm(GgmlDType.Q4K, d, [(cfg.n_heads * hd, s + 1), (cfg.n_kv_heads * hd, s + 2)])    # [q heads | k heads]
+            L.wv = mm(GgmlDType.Q6K, d, [(cfg.n_kv_heads * hd, s + 3)])
+            L.wo = mm(GgmlDType.Q4K, cfg.n_heads * hd, [(d, s + 4)])
+            L.gate_up = mm(GgmlDType.Q4K, d, [(cfg.ffn, s + 5), (cfg.ffn, s + 6)])                     # [gate | up]
+            L.down = mm(GgmlDType.Q6K, cfg.ffn, [(d, s + 7)])
             L.k_cache = torch.zeros((batch, self.hkv_l, cfg.max_pos, hd), device=self.device)
             L.v_cache = torch.zeros((batch, self.hkv_l, cfg.max_pos, hd), device=self.device)
             self.layers.append(L)
         self.out_norm = 1.0 + 0.1 * torch.randn(d, device=self.device, generator=g)
-        self.output = _sharded_matmul(GgmlDType.Q6K, cfg.vocab, d, seed * 100003 + 999983, rank, world, self.device)
+        self.output = _sharded_matmul(GgmlDType.Q6K, d, [(cfg.vocab, seed * 100003 + 999983)], rank, world, self.device)
         self.vocab_start = rank * (cfg.vocab // world)
         # RoPE tables (quantized_llama.rs:540-556): theta_i = base^(-2i/d), angle = pos * theta_i
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=self.device, dtype=torch.float32) / hd))
@@ -105,47 +113,52 @@ class LlamaShapedDecoder:
         self._graph = None
 
     # ---- glue -------------------------------------------------------------------------------------------------
-    def _rms_norm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        return x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + self.cfg.rms_eps) * w
-
-    def _rope(self, x: torch.Tensor, pos_idx: torch.Tensor) -> torch.Tensor:
-        """Interleaved rotary embedding (rope_i): pairs (x[2i], x[2i+1]).  x: [B, T, H, D]."""
-        cos = self.cos.index_select(0, pos_idx)[None, :, None, :]
-        sin = self.sin.index_select(0, pos_idx)[None, :, None, :]
-        xp = x.reshape(*x.shape[:-1], x.shape[-1] // 2, 2)
-        x0, x1 = xp[..., 0], xp[..., 1]
-        return torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1).reshape(x.shape)
-
-    def _attention(self, q, k_cache, v_cache, T):
-        out = torch.empty_like(q)
-        cfg = self.cfg
-        capi.lib().cq_attention_f32(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
-                                    self.batch, T, self.hq_l, self.hkv_l, cfg.head_dim, cfg.max_pos,
-                                    1.0 / math.sqrt(cfg.head_dim), torch.cuda.current_stream(self.device).cuda_stream)
+    def _norm(self, x: torch.Tensor, delta, w: torch.Tensor) -> torch.Tensor:
+        """RMSNorm of x (after x += delta, in place, when a pending residual is given)."""
+        out = torch.empty_like(x)
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        if delta is None:
+            capi.lib().cq_rms_norm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], self.cfg.rms_eps, st)
+        else:
+            capi.lib().cq_add_rms_norm_f32(x.data_ptr(), delta.data_ptr(), w.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1],
+                                           self.cfg.rms_eps, st)
         return out
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens: int64 [B, T] at cache positions pos .. pos+T-1.  Returns the greedy next token [B] and advances pos."""
         cfg, B, T = self.cfg, tokens.shape[0], tokens.shape[1]
-        hd = cfg.head_dim
-        pos_idx = self.pos.to(torch.int64) + torch.arange(T, device=self.device)
-        x = self.tok_embd.index_select(0, tokens.reshape(-1))                       # [B*T, d]
-        for L in self.layers:
-            h = self._rms_norm(x, L.attn_norm)
-            q = self._rope(L.wq.forward(h).view(B, T, self.hq_l, hd), pos_idx)
-            k = self._rope(L.wk.forward(h).view(B, T, self.hkv_l, hd), pos_idx)
-            v = L.wv.forward(h).view(B, T, self.hkv_l, hd)
-            L.k_cache.index_copy_(2, pos_idx, k.permute(0, 2, 1, 3))
-            L.v_cache.index_copy_(2, pos_idx, v.permute(0, 2, 1, 3))
-            att = self._attention(q.contiguous(), L.k_cache, L.v_cache, T).view(B * T, self.hq_l * hd)
-            x = x + self.gather(L.wo.forward(self.gather(att)))
-            h = self._rms_norm(x, L.ffn_norm)
-            a = torch.nn.functional.silu(L.gate.forward(h)) * L.up.forward(h)
-            x = x + self.gather(L.down.forward(self.gather(a)))
-        last = x.view(B, T, cfg.d_model)[:, -1, :].contiguous()
-        logits = self.output.forward(self._rms_norm(last, self.out_norm))       # [B, vocab / world]
-        tok = argmax_sharded(logits, self.vocab_start, self.gather)
-        self.pos += T
+        hd, R, lib = cfg.head_dim, B * T, capi.lib()
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        q_cols, kv_cols = self.hq_l * hd, self.hkv_l * hd
+        f_l = cfg.ffn // self.world
+        scale = 1.0 / math.sqrt(hd)
+        with torch.cuda.device(self.device):
+            x = self.tok_embd.index_select(0, tokens.reshape(-1))                       # [R, d], private to this call
+            delta = None                                                                # residual not yet added to x
+            for L in self.layers:
+                h = self._norm(x, delta, L.attn_norm)
+                qk = L.wqk.forward(h)                                                   # [R, q_cols + kv_cols]
+                v = L.wv.forward(h)                                                     # [R, kv_cols]
+                lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), self.cos.data_ptr(),
+                                         self.sin.data_ptr(), self.pos.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
+                                         B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, q_cols + kv_cols, q_cols + kv_cols,
+                                         kv_cols, st)
+                att = torch.empty((R, q_cols), dtype=torch.float32, device=self.device)
+                lib.cq_attention_f32(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), att.data_ptr(),
+                                     self.pos.data_ptr(), B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale,
+                                     q_cols + kv_cols, st)
+                delta = self.gather(L.wo.forward(self.gather(att)))
+                h = self._norm(x, delta, L.ffn_norm)
+                gu = L.gate_up.forward(h)                                               # [R, 2 * f_l]
+                a = torch.empty((R, f_l), dtype=torch.float32, device=self.device)
+                lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R, f_l, st)
+                delta = self.gather(L.down.forward(self.gather(a)))
+            h = self._norm(x, delta, self.out_norm)
+            capi.check("decoder glue")
+            last = h.view(B, T, cfg.d_model)[:, -1, :].contiguous()
+            logits = self.output.forward(last)                                          # [B, vocab / world]
+            tok = argmax_sharded(logits, self.vocab_start, self.gather)
+            self.pos += T
         return tok
 
     # ---- greedy loop ------------------------------------------------------------------------------------------
@@ -159,6 +172,7 @@ class LlamaShapedDecoder:
         saved = self.pos.clone()
         try:
             side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))     # _tok_in and every earlier write are visible
             with torch.cuda.stream(side):
                 for _ in range(2):                      # warm-up: allocations, attributes, workspace growth
                     self.forward(self._tok_in)

@@ -154,12 +154,26 @@ int cq_prefill_timeout_flag(void);
  * meaningless); 0 restores normal operation. */
 void cq_prefill_set_debug(int flags);
 
-/* Causal attention over an f32 KV cache, one CTA per (sequence, head, query), additions in a fixed order so that a
- * head gives the same bits on any GPU count.  Glue for the decoder harness; stands where candle's quantized models
- * use dense matmuls and softmax (candle-transformers/src/models/quantized_llama.rs:246-261).
- * q, out: [batch, tq, hq, 128]; caches: [batch, hkv, tmax, 128]; pos: device int, cache position of query 0. */
+/* Glue kernels of the decoder harness (f32, fixed order of additions, one launch each).  They stand where candle's
+ * quantized models run chains of tensor ops (candle-transformers/src/models/quantized_llama.rs:56-62, 178-262).
+ *   cq_attention_f32     : causal attention over an f32 KV cache, one CTA per (sequence, head, query), so that a head
+ *                          gives the same bits on any GPU count.  q: batch*tq rows of q_stride floats (heads side by
+ *                          side); out: [batch, tq, hq, 128]; caches: [batch, hkv, tmax, 128]; pos: device int, cache
+ *                          position of query 0.
+ *   cq_rms_norm_f32      : out[r] = x[r] * rsqrt(mean(x[r]^2) + eps) * w.
+ *   cq_add_rms_norm_f32  : x[r] += residual[r] (stored), then the same normalisation of the new x[r].
+ *   cq_rope_store_kv_f32 : interleaved RoPE on q and k in place (rows of q_stride / k_stride floats), then k and v
+ *                          are stored into the caches at position pos + t.  cosv / sinv: [max_pos, head_dim / 2].
+ *   cq_silu_mul_f32      : out[r, i] = silu(gu[r, i]) * gu[r, f + i] for rows gu = [gate | up] of width 2f. */
 void cq_attention_f32(const float *q, const float *k_cache, const float *v_cache, float *out, const int *pos, int batch,
-                      int tq, int hq, int hkv, int head_dim, int tmax, float scale, void *stream);
+                      int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, void *stream);
+void cq_rms_norm_f32(const float *x, const float *w, float *out, int rows, int d, float eps, void *stream);
+void cq_add_rms_norm_f32(float *x, const float *residual, const float *w, float *out, int rows, int d, float eps,
+                         void *stream);
+void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
+                          float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
+                          int q_stride, int k_stride, int v_stride, void *stream);
+void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream);
 
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);

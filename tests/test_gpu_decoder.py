@@ -24,7 +24,7 @@ def test_attention_matches_dense_reference(lib, cuda_dev):
     out = torch.full_like(q, float("nan"))
     pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
     lib.cq_attention_f32(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), pos.data_ptr(), B, Tq, Hq, Hkv, D, Tmax,
-                         1.0 / math.sqrt(D), torch.cuda.current_stream().cuda_stream)
+                         1.0 / math.sqrt(D), Hq * D, torch.cuda.current_stream().cuda_stream)
     capi.check("attention")
     # candle-transformers/src/models/quantized_llama.rs:246-261: repeat_kv, q k^T / sqrt(d), causal mask, softmax, v
     k = kc.repeat_interleave(Hq // Hkv, dim=1)
@@ -35,6 +35,78 @@ def test_attention_matches_dense_reference(lib, cuda_dev):
     s = s.masked_fill(j > pos0 + t, float("-inf"))
     ref = torch.einsum("bhtj,bhjd->bthd", torch.softmax(s, dim=-1), v.double()).float()
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_attention_long_context_and_strided_queries(lib, cuda_dev):
+    """Context longer than one pass of the 8 warps, and q given as a column range of a wider projection output."""
+    torch.manual_seed(1)
+    B, Tq, Hq, Hkv, D, Tmax, pos0 = 1, 1, 4, 2, 128, 700, 612
+    wide = torch.randn(B * Tq, Hq * D + 256, device=cuda_dev)
+    kc = torch.randn(B, Hkv, Tmax, D, device=cuda_dev)
+    vc = torch.randn(B, Hkv, Tmax, D, device=cuda_dev)
+    out = torch.full((B, Tq, Hq, D), float("nan"), device=cuda_dev)
+    pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
+    lib.cq_attention_f32(wide.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), pos.data_ptr(), B, Tq, Hq, Hkv, D, Tmax,
+                         1.0 / math.sqrt(D), Hq * D + 256, torch.cuda.current_stream().cuda_stream)
+    capi.check("attention")
+    q = wide[:, :Hq * D].reshape(B, Tq, Hq, D).double()
+    k = kc.repeat_interleave(Hq // Hkv, dim=1)[:, :, :pos0 + 1].double()
+    v = vc.repeat_interleave(Hq // Hkv, dim=1)[:, :, :pos0 + 1].double()
+    p = torch.softmax(torch.einsum("bthd,bhjd->bhtj", q, k) / math.sqrt(D), dim=-1)
+    ref = torch.einsum("bhtj,bhjd->bthd", p, v).float()
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_glue_kernels_match_torch(lib, cuda_dev):
+    """rms_norm (with and without the pending residual), interleaved RoPE + KV store, SwiGLU - against the tensor
+    formulas of candle-transformers/src/models/quantized_llama.rs:56-62 and 178-262."""
+    torch.manual_seed(3)
+    st = torch.cuda.current_stream().cuda_stream
+    R, d, eps = 5, 1024, 1e-5
+    x, delta, w = torch.randn(R, d, device=cuda_dev), torch.randn(R, d, device=cuda_dev), torch.rand(d, device=cuda_dev) + 0.5
+    out = torch.empty_like(x)
+    lib.cq_rms_norm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), R, d, eps, st)
+    ref = lambda t: (t.double() * torch.rsqrt(t.double().pow(2).mean(-1, keepdim=True) + eps) * w.double()).float()
+    assert torch.allclose(out, ref(x), rtol=1e-5, atol=1e-6)
+    x2 = x.clone()
+    lib.cq_add_rms_norm_f32(x2.data_ptr(), delta.data_ptr(), w.data_ptr(), out.data_ptr(), R, d, eps, st)
+    assert torch.equal(x2, x + delta)
+    assert torch.allclose(out, ref(x + delta), rtol=1e-5, atol=1e-6)
+
+    B, T, Hq, Hkv, D, Tmax, pos0, max_pos = 2, 3, 4, 2, 128, 16, 5, 32
+    qs = (Hq + Hkv) * D
+    qk = torch.randn(B * T, qs, device=cuda_dev)
+    v = torch.randn(B * T, Hkv * D, device=cuda_dev)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=cuda_dev, dtype=torch.float32) / D))
+    ang = torch.arange(max_pos, device=cuda_dev, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc = torch.zeros(B, Hkv, Tmax, D, device=cuda_dev)
+    vc = torch.zeros(B, Hkv, Tmax, D, device=cuda_dev)
+    pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
+    qk0 = qk.clone()
+    lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * Hq * D, v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                             pos.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, T, Hq, Hkv, D, Tmax, qs, qs, Hkv * D, st)
+    capi.check("glue")
+
+    def rope(t):      # [B, T, H, D], pairs (2i, 2i+1)
+        c = cos[pos0:pos0 + T][None, :, None, :].double()
+        s = sin[pos0:pos0 + T][None, :, None, :].double()
+        tp = t.double().reshape(*t.shape[:-1], D // 2, 2)
+        return torch.stack([tp[..., 0] * c - tp[..., 1] * s, tp[..., 0] * s + tp[..., 1] * c], dim=-1).reshape(t.shape).float()
+
+    q_ref = rope(qk0[:, :Hq * D].reshape(B, T, Hq, D))
+    k_ref = rope(qk0[:, Hq * D:].reshape(B, T, Hkv, D))
+    assert torch.allclose(qk[:, :Hq * D].reshape(B, T, Hq, D), q_ref, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(kc[:, :, pos0:pos0 + T], k_ref.permute(0, 2, 1, 3), rtol=1e-5, atol=1e-6)
+    assert torch.equal(vc[:, :, pos0:pos0 + T], v.reshape(B, T, Hkv, D).permute(0, 2, 1, 3))
+    assert float(kc[:, :, :pos0].abs().max()) == 0.0 and float(kc[:, :, pos0 + T:].abs().max()) == 0.0
+
+    f = 384
+    gu = torch.randn(R, 2 * f, device=cuda_dev) * 3
+    a = torch.empty(R, f, device=cuda_dev)
+    lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R, f, st)
+    capi.check("glue")
+    assert torch.allclose(a, (torch.nn.functional.silu(gu[:, :f].double()) * gu[:, f:].double()).float(), rtol=1e-5, atol=1e-6)
 
 
 def test_graph_decode_equals_eager_decode(cuda_dev):
