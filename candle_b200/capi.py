@@ -61,6 +61,11 @@ def lib() -> C.CDLL:
         L.cq_moe_gemv_sorted.argtypes = [i32, i32, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_indexed_moe_forward.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
         L.cq_moe_timeout_flag.restype = i32
+        L.cq_mmq_timeout_flag.restype = i32
+        for lay in ("D4", "DS4", "D2S6"):
+            getattr(L, f"launch_mmq_quantize_q8_1_{lay}").argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, i64, i64, i64, vp]
+        for t in TYPE_NAME.values():
+            getattr(L, f"launch_mmq_gguf_{t}").argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i64, i32, vp]
         L.cq_attention_f32.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp]
         L.cq_rms_norm_f32.argtypes = [vp, vp, vp, i32, i32, C.c_float, vp]
         L.cq_add_rms_norm_f32.argtypes = [vp, vp, vp, vp, i32, i32, C.c_float, vp]

@@ -26,7 +26,12 @@ enum CqElem : int { CQ_F32 = 0, CQ_F16 = 1, CQ_BF16 = 2 };
 //   CQ_ACT_Q8_K : float d (the same for the 8 containers of a 256-element super-block),
 //                 iscale = -127/max, q = round(iscale*x).  What candle's CPU path uses for K-quants
 //                 (k_quants.rs:2320-2358).  bsums are not stored: kernels recompute them exactly.
-enum CqAct : int { CQ_ACT_Q8_1 = 0, CQ_ACT_Q8_0 = 1, CQ_ACT_Q8_K = 2 };
+//   CQ_ACT_MMQ_D4 / CQ_ACT_MMQ_DS4 (internal to the launch_mmq_* entry points): the reference's 144-byte
+//                 block_q8_1_mmq groups of 128 values (four f32 d, or four half2 (d, sum), then 128 int8), stored
+//                 [group][token] (candle-kernels/src/mmq_gguf/mmq_quantize.cu:12-106).  Same arithmetic as Q8_1.
+enum CqAct : int { CQ_ACT_Q8_1 = 0, CQ_ACT_Q8_0 = 1, CQ_ACT_Q8_K = 2, CQ_ACT_MMQ_D4 = 3, CQ_ACT_MMQ_DS4 = 4 };
+#define CQ_MMQ_GROUP_BYTES 144
+__host__ __device__ constexpr bool cq_act_q8_1_like(int act) { return act == CQ_ACT_Q8_1 || act == CQ_ACT_MMQ_D4 || act == CQ_ACT_MMQ_DS4; }
 
 // Status codes kept in a process-wide side channel (the reference launchers return void).
 enum CqStatus : int {

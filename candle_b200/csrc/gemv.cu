@@ -31,6 +31,7 @@ struct DenseMap {       // batch column j: activation row j, output row j, no sc
     __device__ __forceinline__ int64_t out_offset(int j) const { return (int64_t)j * stride_col_dst; }
     __device__ __forceinline__ float scale(int) const { return 1.0f; }
     __device__ __forceinline__ bool valid(int) const { return true; }
+    __device__ __forceinline__ int64_t act_stride() const { return 0; }
 };
 
 template <int TYPE, int ACT, int B, int RB>

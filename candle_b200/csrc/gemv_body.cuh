@@ -1,7 +1,8 @@
 // Body of the staged GEMV, shared by the dense kernel (gemv.cu) and the expert-indexed kernels (moe.cu).
 // See gemv.cu for the design.  `Map` tells the body where batch column j reads its activations and writes its
 // outputs:  act_row(j) -> first 36-byte container of the row,  out_offset(j) -> element offset of output row j,
-// scale(j) -> factor applied to the finished sum (1 for dense),  valid(j) -> whether column j exists.
+// scale(j) -> factor applied to the finished sum (1 for dense),  valid(j) -> whether column j exists,
+// act_stride() -> byte distance between a row's 144-byte groups (MMQ activation encodings only, else 0).
 #pragma once
 #include "gemv_chunks.cuh"
 
@@ -51,8 +52,8 @@ __device__ __forceinline__ void gemv_body(const uint8_t *__restrict__ w, const M
     if (active) {
 #pragma unroll
         for (int j = 0; j < B; ++j)
-            if (map.valid(j)) chunk_load_act<TYPE, ACT>(act[j], map.act_row(j), tid);
-            else chunk_load_act<TYPE, ACT>(act[j], map.act_row(0), tid);      // placeholder, never stored
+            if (map.valid(j)) chunk_load_act<TYPE, ACT>(act[j], map.act_row(j), tid, map.act_stride());
+            else chunk_load_act<TYPE, ACT>(act[j], map.act_row(0), tid, map.act_stride());      // placeholder, never stored
     }
 
     int it = 0;

@@ -59,30 +59,43 @@ template <int TYPE> __device__ __forceinline__ void chunk_act_coords(int chunk, 
     }
 }
 
+// `yrow`: first container of the activation row.  For the MMQ encodings it is the row's first 144-byte group and
+// `group_stride` is the byte distance between consecutive groups of that row (tokens * 144).
 template <int TYPE, int ACT>
-__device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t *yrow, int chunk) {
+__device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t *yrow, int chunk, int64_t group_stride = 0) {
     constexpr int NB = ChunkAct<TYPE>::NB, WPB = ChunkAct<TYPE>::WPB;
+    constexpr bool MMQ = ACT == CQ_ACT_MMQ_D4 || ACT == CQ_ACT_MMQ_DS4;
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
         int blk, byte0;
         chunk_act_coords<TYPE>(chunk, i, blk, byte0);
-        const uint8_t *p = yrow + (int64_t)blk * CQ_Q8_BYTES;
+        const uint8_t *p, *pq;      // scale word, first int8
+        if constexpr (MMQ) {
+            const uint8_t *g = yrow + (int64_t)(blk >> 2) * group_stride;
+            p = g + 4 * (blk & 3);
+            pq = g + 16 + 32 * (blk & 3);
+        } else {
+            p = yrow + (int64_t)blk * CQ_Q8_BYTES;
+            pq = p + 4;
+        }
         int sq = 0;
 #pragma unroll
         for (int w = 0; w < WPB; ++w) {
-            const int v = cq_ld_global_i32(p + 4 + byte0 + 4 * w);
+            const int v = cq_ld_global_i32(pq + byte0 + 4 * w);
             a.u[i * WPB + w] = v;
             sq = cq_dp4a(0x01010101, v, sq);
         }
         a.sq[i] = sq;
         const int ds = cq_ld_global_i32(p);
-        if constexpr (ACT == CQ_ACT_Q8_K) {
+        if constexpr (ACT == CQ_ACT_Q8_K || ACT == CQ_ACT_MMQ_D4) {
             a.d[i] = __int_as_float(ds);
             a.s[i] = 0.0f;
         } else {
             const __half2 h2 = *reinterpret_cast<const __half2 *>(&ds);
             a.d[i] = __low2float(h2);
-            if constexpr (TYPE == CQ_Q4_K || TYPE == CQ_Q4_K_WIDE) a.s[i] = a.d[i] * (float)sq;
+            // Q4_K with Q8_1 containers: d * sum(q) as in the reference's GEMV (mmvq_gguf.cu:335-354); with the MMQ
+            // encoding the stored sum, as in its tiled kernel (mmq_gguf/mmq_vecdotq.cuh:527-551).
+            if constexpr ((TYPE == CQ_Q4_K || TYPE == CQ_Q4_K_WIDE) && !MMQ) a.s[i] = a.d[i] * (float)sq;
             else a.s[i] = __high2float(h2);
         }
     }
@@ -111,7 +124,7 @@ template <> struct ChunkW<CQ_Q4_0> {
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_0> &a) const {
         const int s = idot(a);
-        if constexpr (ACT == CQ_ACT_Q8_1) return __fmul_rn(d, __fmaf_rn((float)s, a.d[0], __fmul_rn(-8.0f, a.s[0])));
+        if constexpr (cq_act_q8_1_like(ACT)) return __fmul_rn(d, __fmaf_rn((float)s, a.d[0], __fmul_rn(-8.0f, a.s[0])));
         else return __fmul_rn(__fmul_rn((float)(s - 8 * a.sq[0]), d), a.d[0]);
     }
 };
@@ -168,7 +181,7 @@ template <> struct ChunkW<CQ_Q4_K> {
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_K> &a) const {
         int d0, d1;
         idots(a, d0, d1);
-        if constexpr (ACT == CQ_ACT_Q8_1) {
+        if constexpr (cq_act_q8_1_like(ACT)) {
             const float sd = __fmaf_rn(a.d[1], (float)(d1 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
             const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
@@ -220,7 +233,7 @@ template <> struct ChunkW<CQ_Q4_K_WIDE> {
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_K_WIDE> &a) const {
         int d0, d1x16;
         idots(a, d0, d1x16);
-        if constexpr (ACT == CQ_ACT_Q8_1) {
+        if constexpr (cq_act_q8_1_like(ACT)) {
             const float sd = __fmaf_rn(__fmul_rn(a.d[1], 0.0625f), (float)(d1x16 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
             const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
@@ -263,7 +276,7 @@ template <> struct ChunkW<CQ_Q6_K> {
         return s - 32 * a.sq[p];
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q6_K> &a) const {
-        if constexpr (ACT == CQ_ACT_Q8_1) {
+        if constexpr (cq_act_q8_1_like(ACT)) {
             float sf = 0.0f;
 #pragma unroll
             for (int p = 0; p < 4; ++p) sf = __fmaf_rn(a.d[p], (float)(idot(a, p) * sc[p]), sf);

@@ -40,6 +40,7 @@ struct MoeMap {     // one activation row, one output row
     __device__ __forceinline__ int64_t out_offset(int) const { return off; }
     __device__ __forceinline__ float scale(int) const { return sc; }
     __device__ __forceinline__ bool valid(int) const { return true; }
+    __device__ __forceinline__ int64_t act_stride() const { return 0; }
 };
 
 // grid (jobs, row blocks).  Index rules: candle-kernels/src/moe/moe_gguf.cu:85-99 (sorted) and

@@ -67,6 +67,33 @@ void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int3
                            const int32_t *expert_ids, const float *topk_weights, void *output, int num_experts, int topk,
                            int size_m, int size_n, int size_k, int input_dtype, int gguf_dtype, int64_t stream);
 
+/* Prompt-phase pair.  Replaces candle-kernels/src/ffi.rs:424-468 (launch_mmq_quantize_q8_1_{D4,DS4,D2S6}) and, for
+ * the four formats, :471-630 (launch_mmq_gguf_<type>); host caller candle-core/src/quantized/fast_mmq.rs:253-400.
+ * Quantize: x f32 (rows of ne00 values, row stride s01, channel strides s02 / s03, optional row gather `ids`) ->
+ * block_q8_1_mmq groups of 144 bytes per 128 values, stored [channel][group][token], ne0 = padded width (a multiple
+ * of 128), ne1 tokens.  The bytes are those of the reference kernel.  DS4 serves Q4_0 / Q4_K, D4 serves Q8_0 / Q6_K.
+ * Matmul: x = weights [nrows_x, ncols_x] (stride_row_x blocks per row), y = that scratch for ncols_y tokens,
+ * dst f32 [ncols_y, stride_col_dst].  tmp_fixup, cc, nsm, smpbo, warp_size are accepted for signature compatibility
+ * and not used.  These entries run GEMV passes of eight tokens; the tensor-core prompt path is cq_prefill_gemm. */
+#define CQ_DECL_MMQ_QUANT(name)                                                                                       \
+    void name(const void *x, const int32_t *ids, void *vy, int type_x, int64_t ne00, int64_t s01, int64_t s02,        \
+              int64_t s03, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3, void *stream)
+CQ_DECL_MMQ_QUANT(launch_mmq_quantize_q8_1_D4);
+CQ_DECL_MMQ_QUANT(launch_mmq_quantize_q8_1_DS4);
+CQ_DECL_MMQ_QUANT(launch_mmq_quantize_q8_1_D2S6);
+#undef CQ_DECL_MMQ_QUANT
+#define CQ_DECL_MMQ(name)                                                                                             \
+    void name(void *tmp_fixup, const void *x, const void *y, void *dst, int64_t ncols_x, int64_t nrows_x,             \
+              int64_t ncols_y, int64_t stride_row_x, int64_t stride_col_dst, int cc, int nsm, int64_t smpbo,           \
+              int warp_size, void *stream)
+CQ_DECL_MMQ(launch_mmq_gguf_q4_0);
+CQ_DECL_MMQ(launch_mmq_gguf_q8_0);
+CQ_DECL_MMQ(launch_mmq_gguf_q4_k);
+CQ_DECL_MMQ(launch_mmq_gguf_q6_k);
+#undef CQ_DECL_MMQ
+/* 1 if a launch_mmq_gguf_* pass gave up a bounded wait on the current device (no reference counterpart). */
+int cq_mmq_timeout_flag(void);
+
 /* ------------------------------------------------------------------------------------------------
  * 2. Library surface
  * ---------------------------------------------------------------------------------------------- */

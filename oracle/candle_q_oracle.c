@@ -1085,34 +1085,102 @@ void cqo_cuda_block_dots(int type, int64_t k, int64_t nrows, const void *w, cons
 
 /* quantize_mmq_q8_1, candle-kernels/src/mmq_gguf/mmq_quantize.cu:11-107, for the call the host
  * makes (fast_mmq.rs:349-366): x f32 [tokens, k] contiguous -> blocks laid out [k_padded/128][tokens].
- * layout 0 = D4 (four f32 d per 128), 1 = DS4 (four half2 (d, sum) per 128).
+ * layout 0 = D4 (four f32 d per 128), 1 = DS4 (four half2 (d, sum) per 128), 2 = D2S6 (two half d per 64 values, six
+ * half sums of the first six 16-value runs; thread sums then butterfly xor 2,1 over 4 threads).
  * d_inv = 127/amax, q = roundf(x*d_inv), d = 1/d_inv; sum = (x0+x1+x2+x3) per thread then
  * butterfly xor 4,2,1 over the 8 threads of a 32-group. */
 void cqo_cuda_quantize_mmq_q8_1(int layout, const float *x, void *vy, int64_t k, int64_t k_padded, int64_t tokens) {
     blk_q8_1_mmq *y = (blk_q8_1_mmq *)vy;
+    const int per_scale = layout == 2 ? 64 : 32, per_sum = layout == 2 ? 16 : 32;
     for (int64_t t = 0; t < tokens; ++t)
         for (int64_t kb = 0; kb < k_padded / 128; ++kb) {
             blk_q8_1_mmq *o = &y[kb * tokens + t];
-            for (int g = 0; g < 4; ++g) {
-                float v[32], amax = 0.f, part[8], nx[8];
-                for (int j = 0; j < 32; ++j) {
-                    const int64_t i0 = kb * 128 + g * 32 + j;
-                    v[j] = i0 < k ? x[t * k + i0] : 0.f;
-                    amax = fmaxf(amax, fabsf(v[j]));
-                }
-                for (int th = 0; th < 8; ++th) part[th] = v[4 * th] + v[4 * th + 1] + v[4 * th + 2] + v[4 * th + 3];
-                for (int mask = 4; mask > 0; mask >>= 1) {
-                    for (int th = 0; th < 8; ++th) nx[th] = part[th] + part[th ^ mask];
-                    memcpy(part, nx, sizeof part);
-                }
+            float v[128];
+            for (int j = 0; j < 128; ++j) {
+                const int64_t i0 = kb * 128 + j;
+                v[j] = i0 < k ? x[t * k + i0] : 0.f;
+            }
+            for (int g = 0; g < 128 / per_scale; ++g) {
+                float amax = 0.f;
+                for (int j = 0; j < per_scale; ++j) amax = fmaxf(amax, fabsf(v[g * per_scale + j]));
                 const float d_inv = 127.0f / amax;
-                for (int j = 0; j < 32; ++j) {
-                    const float r = roundf(v[j] * d_inv);
-                    o->qs[32 * g + j] = (r != r) ? 0 : (int8_t)r;   /* cvt of NaN gives 0 on the GPU */
+                for (int j = 0; j < per_scale; ++j) {
+                    const float r = roundf(v[g * per_scale + j] * d_inv);
+                    o->qs[g * per_scale + j] = (r != r) ? 0 : (int8_t)r;   /* cvt of NaN gives 0 on the GPU */
                 }
                 const float d = 1.0f / d_inv;
-                if (layout == 1) { o->ds4[2 * g] = f32_to_f16(d); o->ds4[2 * g + 1] = f32_to_f16(part[0]); }
-                else o->d4[g] = d;
+                if (layout == 0) o->d4[g] = d;
+                else if (layout == 1) o->ds4[2 * g] = f32_to_f16(d);
+                else o->ds4[g] = f32_to_f16(d);
             }
+            if (layout != 0)
+                for (int g = 0; g < 128 / per_sum; ++g) {
+                    const int nth = per_sum / 4;
+                    float part[8], nx[8];
+                    for (int th = 0; th < nth; ++th) {
+                        const float *q = v + g * per_sum + 4 * th;
+                        part[th] = q[0] + q[1] + q[2] + q[3];
+                    }
+                    for (int mask = nth / 2; mask > 0; mask >>= 1) {
+                        for (int th = 0; th < nth; ++th) nx[th] = part[th] + part[th ^ mask];
+                        memcpy(part, nx, sizeof(float) * nth);
+                    }
+                    if (layout == 1) o->ds4[2 * g + 1] = f32_to_f16(part[0]);
+                    else if (g < 6) o->ds4[2 + g] = f32_to_f16(part[0]);     /* d2s6: two scales, six sums */
+                }
+        }
+}
+
+/* Matmul over the MMQ scratch: dst[t * n + r] = sum over 32-blocks of the reference's per-block terms,
+ * candle-kernels/src/mmq_gguf/mmq_vecdotq.cuh:112-131 (Q4_0: d4 * (sumi * d8 - 8 * s8)), :240-253 (Q8_0: d8_0 * d8_1 *
+ * sumi), :527-551 (Q4_K: dm.x * sum d8 * sc * sumi - dm.y * sum s8 * m), :644-674 (Q6_K: d6 * sum d8 * (sc * sumi)).
+ * The reference adds the per-block f32 terms in the order of its tile loops (or inside mma accumulators), which no
+ * caller can rely on; the integer parts are exact and the block terms are summed in double here. */
+void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k, int64_t n, int64_t tokens) {
+    const blk_q8_1_mmq *y = (const blk_q8_1_mmq *)vy;
+    const int64_t wrb = k / cqo_block_size(type) * cqo_type_size(type);
+    for (int64_t t = 0; t < tokens; ++t)
+        for (int64_t r = 0; r < n; ++r) {
+            const char *row = (const char *)w + r * wrb;
+            double acc = 0.0;
+            for (int64_t b32 = 0; b32 < k / 32; ++b32) {
+                const blk_q8_1_mmq *g = &y[(b32 / 4) * tokens + t];
+                const int j = (int)(b32 % 4);
+                const int8_t *q8 = g->qs + 32 * j;
+                if (type == CQO_Q4_0) {
+                    const blk_q4_0 *b = (const blk_q4_0 *)row + b32;
+                    int sumi = 0;
+                    for (int i = 0; i < 16; ++i) sumi += (b->qs[i] & 0xF) * q8[i] + (b->qs[i] >> 4) * q8[i + 16];
+                    const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
+                    acc += (double)f16_to_f32(b->d) * ((double)sumi * d8 - 8.0 * s8);
+                } else if (type == CQO_Q8_0) {
+                    const blk_q8_0 *b = (const blk_q8_0 *)row + b32;
+                    int sumi = 0;
+                    for (int i = 0; i < 32; ++i) sumi += b->qs[i] * q8[i];
+                    acc += (double)f16_to_f32(b->d) * (double)g->d4[j] * sumi;
+                } else if (type == CQO_Q4K) {
+                    const blk_q4k *b = (const blk_q4k *)row + b32 / 8;
+                    const int sub = (int)(b32 % 8);
+                    uint8_t sc, m;
+                    scale_min_k4(sub, b->scales, &sc, &m);
+                    const uint8_t *q4 = b->qs + 32 * (sub / 2);
+                    int sumi = 0;
+                    for (int i = 0; i < 32; ++i) sumi += ((sub & 1) ? (q4[i] >> 4) : (q4[i] & 0xF)) * q8[i];
+                    const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
+                    acc += (double)f16_to_f32(b->d) * d8 * (double)(sc * sumi) - (double)f16_to_f32(b->dmin) * s8 * m;
+                } else if (type == CQO_Q6K) {
+                    const blk_q6k *b = (const blk_q6k *)row + b32 / 8;
+                    const int sub = (int)(b32 % 8), half = sub / 4, pos = sub % 4;     /* 128-half, 32-apart position */
+                    int tot = 0;
+                    for (int i = 0; i < 32; ++i) {
+                        const uint8_t ql = b->ql[64 * half + 32 * (pos & 1) + i];
+                        const int lo = (pos & 2) ? (ql >> 4) : (ql & 0xF);
+                        const int hi = (b->qh[32 * half + i] >> (2 * pos)) & 3;
+                        tot += b->scales[8 * half + 2 * pos + i / 16] * ((lo | (hi << 4)) - 32) * q8[i];
+                    }
+                    acc += (double)f16_to_f32(b->d) * (double)g->d4[j] * tot;
+                }
+            }
+            dst[t * n + r] = (float)acc;
         }
 }

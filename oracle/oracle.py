@@ -57,6 +57,7 @@ def lib() -> C.CDLL:
         L.cqo_cuda_mmvq.argtypes = [i32, vp, vp, f32p, i32, i32, i32, i32, i32, i32]
         L.cqo_cuda_block_dots.argtypes = [i32, i64, i64, vp, vp, vp, vp]
         L.cqo_cuda_quantize_mmq_q8_1.argtypes = [i32, f32p, vp, i64, i64, i64]
+        L.cqo_cuda_mmq.argtypes = [i32, vp, vp, f32p, i64, i64, i64]
         L.cqo_num_cores.restype = i32
         L.cqo_have_avx2.restype = i32
         _lib = L
@@ -173,13 +174,23 @@ def cuda_block_dots(dtype: int, w_blocks: np.ndarray, q8_1_row: np.ndarray, k: i
 
 
 def cuda_quantize_mmq_q8_1(x, layout: str, k_padded: int | None = None) -> np.ndarray:
-    """``quantize_mmq_q8_1``: x f32 [tokens, k] -> uint8 [k_padded/128, tokens, 144]; layout 'D4' or 'DS4'."""
+    """``quantize_mmq_q8_1``: x f32 [tokens, k] -> uint8 [k_padded/128, tokens, 144]; layout 'D4', 'DS4' or 'D2S6'."""
     x = _f32(x)
     tokens, k = x.shape
     if k_padded is None:
         k_padded = pad(pad(k, 512), 128)
     out = np.zeros((k_padded // 128, tokens, 144), dtype=np.uint8)
-    lib().cqo_cuda_quantize_mmq_q8_1({"D4": 0, "DS4": 1}[layout], _p(x), _p(out), k, k_padded, tokens)
+    lib().cqo_cuda_quantize_mmq_q8_1({"D4": 0, "DS4": 1, "D2S6": 2}[layout], _p(x), _p(out), k, k_padded, tokens)
+    return out
+
+
+def cuda_mmq(dtype: int, w_blocks: np.ndarray, y_mmq: np.ndarray, k: int, n: int) -> np.ndarray:
+    """Matmul over the ``block_q8_1_mmq`` scratch (uint8 [k_padded/128, tokens, 144]) -> f32 [tokens, n]."""
+    w_blocks = np.ascontiguousarray(w_blocks, dtype=np.uint8)
+    y_mmq = np.ascontiguousarray(y_mmq, dtype=np.uint8)
+    tokens = y_mmq.shape[1]
+    out = np.zeros((tokens, n), dtype=np.float32)
+    lib().cqo_cuda_mmq(dtype, _p(w_blocks), _p(y_mmq), _p(out), k, n, tokens)
     return out
 
 
