@@ -71,6 +71,10 @@ def lib() -> C.CDLL:
         L.cq_add_rms_norm_f32.argtypes = [vp, vp, vp, vp, i32, i32, C.c_float, vp]
         L.cq_rope_store_kv_f32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.cq_silu_mul_f32.argtypes = [vp, vp, i32, i32, vp]
+        L.cq_add_rms_norm_q8_1.argtypes = [vp, vp, vp, vp, i32, i32, i32, C.c_float, vp]
+        L.cq_silu_mul_q8_1.argtypes = [vp, vp, i32, i32, i32, vp]
+        L.cq_attention_q8_1.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]
+        L.cq_set_pdl.argtypes = [i32]
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]
@@ -87,6 +91,7 @@ def lib() -> C.CDLL:
         L.cqh_qtensor_device_ptr.restype = vp
         L.cqh_qmatmul_forward.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
         L.cqh_set_act_mode.argtypes = [i32]
+        L.cqh_qmatmul_forward_q8_1.argtypes = [vp, vp, i32, vp, vp]
         L.cqh_indexed_moe_forward.argtypes = [vp, vp, i32, vp, i32, i32, vp, vp]
         L.cqh_get_act_mode.restype = i32
         L.cqh_workspace_reserve.argtypes = [i32, sz]

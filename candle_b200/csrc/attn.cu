@@ -25,15 +25,20 @@ constexpr int kThreads = 32 * kWarps;
 //            added in that order, then a 3-step xor butterfly);
 //   output : warp w adds its keys j = w, w + 32, ... in ascending order, lane l owns dims 4l .. 4l+3; the 32 warps'
 //            partial sums are then added in warp order.
+// Q8: the output row (hq * 128 values) is stored as Q8_1 containers, `out_blocks` containers per row; a head covers
+// four of them.
+template <bool Q8>
 __global__ void __launch_bounds__(kThreads) attention_f32_kernel(const float *__restrict__ q, const float *__restrict__ kc,
-                                                                 const float *__restrict__ vc, float *__restrict__ out,
+                                                                 const float *__restrict__ vc, void *__restrict__ out,
                                                                  const int *__restrict__ pos, int tq, int hq, int hkv,
-                                                                 int tmax, float scale, int q_stride) {
+                                                                 int tmax, float scale, int q_stride, int out_blocks) {
     extern __shared__ float scores[];           // [n_ctx]
     __shared__ float red[kWarps];
     __shared__ float4 part[kWarps][32];
     const int h = blockIdx.x, t = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
     int n_ctx = pos[0] + t + 1;
     if (n_ctx > tmax) n_ctx = tmax;
     const int kvh = h / (hq / hkv);
@@ -125,26 +130,50 @@ __global__ void __launch_bounds__(kThreads) attention_f32_kernel(const float *__
             const float4 pw = part[w][lane];
             acc.x += pw.x; acc.y += pw.y; acc.z += pw.z; acc.w += pw.w;
         }
-        float4 r;
-        r.x = __fdiv_rn(acc.x, sum); r.y = __fdiv_rn(acc.y, sum); r.z = __fdiv_rn(acc.z, sum); r.w = __fdiv_rn(acc.w, sum);
-        *reinterpret_cast<float4 *>(out + (((size_t)b * tq + t) * hq + h) * kD + 4 * lane) = r;
+        const float r[4] = {__fdiv_rn(acc.x, sum), __fdiv_rn(acc.y, sum), __fdiv_rn(acc.z, sum), __fdiv_rn(acc.w, sum)};
+        if constexpr (Q8) {
+            uint8_t *row = reinterpret_cast<uint8_t *>(out) + ((size_t)b * tq + t) * out_blocks * CQ_Q8_BYTES;
+            cq_q8_1_store_block(r, row + (size_t)(4 * h + (lane >> 3)) * CQ_Q8_BYTES, true);
+        } else {
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (((size_t)b * tq + t) * hq + h) * kD + 4 * lane) =
+                make_float4(r[0], r[1], r[2], r[3]);
+        }
     }
 }
 
 }  // namespace
 
-extern "C" void cq_attention_f32(const float *q, const float *k_cache, const float *v_cache, float *out, const int *pos,
-                                 int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, void *stream) {
+namespace {
+bool attention_args_ok(const void *q, const void *k_cache, const void *v_cache, const void *out, const void *pos, int batch, int tq,
+                       int hq, int hkv, int head_dim, int tmax) {
     if (!q || !k_cache || !v_cache || !out || !pos || batch <= 0 || tq <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0) {
         cq_set_status(CQ_ERR_BAD_ARG, "attention: null pointer or bad head counts");
-        return;
+        return false;
     }
-    if (head_dim != kD || tmax <= 0 || tmax > 12000) {
+    if (head_dim != kD || tmax <= 0 || tmax > 12000 || tq > 65535 || batch > 65535) {
         cq_set_status(CQ_ERR_UNSUPPORTED, "attention: head_dim must be 128 and the cache at most 12000 positions");
-        return;
+        return false;
     }
-    const dim3 grid(hq, tq, batch);
-    attention_f32_kernel<<<grid, kThreads, (size_t)tmax * sizeof(float), (cudaStream_t)stream>>>(q, k_cache, v_cache, out, pos, tq,
-                                                                                             hq, hkv, tmax, scale, q_stride);
+    return true;
+}
+}  // namespace
+
+extern "C" void cq_attention_f32(const float *q, const float *k_cache, const float *v_cache, float *out, const int *pos,
+                                 int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, void *stream) {
+    if (!attention_args_ok(q, k_cache, v_cache, out, pos, batch, tq, hq, hkv, head_dim, tmax)) return;
+    cq_launch_k(attention_f32_kernel<false>, dim3(hq, tq, batch), dim3(kThreads), (size_t)tmax * sizeof(float), (cudaStream_t)stream, q,
+                k_cache, v_cache, out, pos, tq, hq, hkv, tmax, scale, q_stride, 0);
     cq_check_launch("attention");
+}
+
+// Same, with the output stored as Q8_1 containers: `out_blocks` containers per (sequence, query) row, of which the first
+// hq * 4 are written (a caller that pads K to 512 zeroes the rest once; they are never touched here).
+extern "C" void cq_attention_q8_1(const float *q, const float *k_cache, const float *v_cache, void *out_q8, const int *pos,
+                                  int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride,
+                                  int out_blocks, void *stream) {
+    if (!attention_args_ok(q, k_cache, v_cache, out_q8, pos, batch, tq, hq, hkv, head_dim, tmax)) return;
+    if (out_blocks < hq * 4) { cq_set_status(CQ_ERR_BAD_ARG, "attention_q8_1: row of containers shorter than hq * 4"); return; }
+    cq_launch_k(attention_f32_kernel<true>, dim3(hq, tq, batch), dim3(kThreads), (size_t)tmax * sizeof(float), (cudaStream_t)stream, q,
+                k_cache, v_cache, out_q8, pos, tq, hq, hkv, tmax, scale, q_stride, out_blocks);
+    cq_check_launch("attention_q8_1");
 }

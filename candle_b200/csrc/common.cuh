@@ -64,6 +64,40 @@ __host__ __device__ constexpr int cq_block_elems(int t) {
 void cq_set_status(int status, const char *msg);
 bool cq_check_launch(const char *what);
 
+// ---- programmatic dependent launch ----
+// Kernels of the decode path are launched with the "programmatic stream serialization" attribute (unless switched off
+// with cq_set_pdl(0)): a kernel may start while its predecessor in the stream is still draining, runs its prologue
+// (barrier set-up, the first weight copies - nothing a predecessor writes) and then waits in cq_pdl_wait() until the
+// predecessor has completed and its writes are visible.  Without the attribute both calls do nothing.
+bool cq_pdl_enabled();
+__device__ __forceinline__ void cq_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void cq_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline void cq_launch_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute &attr, dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = cq_pdl_enabled() ? 1 : 0;
+}
+// Launch `fn` (a __global__ function given as an untyped pointer, arguments as an array of pointers).
+static inline cudaError_t cq_launch(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void **args) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    cq_launch_config(cfg, attr, grid, block, smem, st);
+    return cudaLaunchKernelExC(&cfg, fn, args);
+}
+// Typed front end: cq_launch_k(kernel, grid, block, smem, stream, args...).
+template <typename... P, typename... A>
+static inline cudaError_t cq_launch_k(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... a) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    cq_launch_config(cfg, attr, grid, block, smem, st);
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(a)...);
+}
+
 // ---- device helpers ----
 __device__ __forceinline__ int cq_dp4a(int a, int b, int c) { return __dp4a(a, b, c); }
 __device__ __forceinline__ int cq_dp4a_u(unsigned a, int b, int c) {   // unsigned bytes x signed bytes
@@ -80,6 +114,34 @@ __device__ __forceinline__ void cq_store_out(void *dst, int kind, int64_t i, flo
     if (kind == CQ_F32) ((float *)dst)[i] = v;
     else if (kind == CQ_F16) ((__half *)dst)[i] = __float2half(v);
     else ((__nv_bfloat16 *)dst)[i] = __float2bfloat16(v);
+}
+
+// Q8_1 quantization of one 32-value block held by 8 consecutive lanes, 4 consecutive values each (value index
+// 4 * (lane & 7) + c).  Same arithmetic as the stand-alone quantizer (quantize_act.cu) and so as the reference
+// (candle-kernels/src/mmvq_gguf.cu:811-911): amax / 127, round(x / d), and the sum added in the order of a 32-lane
+// xor butterfly (16, 8, 4 across lanes, 2, 1 inside the lane).  All 32 lanes of the warp must call.
+// `block` is the 36-byte container of this lane's block.
+__device__ __forceinline__ void cq_q8_1_store_block(const float (&e)[4], uint8_t *block, bool write) {
+    const int g = threadIdx.x & 7;
+    float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
+#pragma unroll
+    for (int m = 4; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    float s[4] = {e[0], e[1], e[2], e[3]};
+#pragma unroll
+    for (int m = 4; m > 0; m >>= 1) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[c] += __shfl_xor_sync(0xffffffffu, s[c], m);
+    }
+    const float t0 = s[0] + s[2], t1 = s[1] + s[3];
+    const float sum = t0 + t1;
+    const float d = __fdiv_rn(amax, 127.0f);
+    int q[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) q[c] = (amax == 0.0f) ? 0 : (int)(int8_t)roundf(__fdiv_rn(e[c], d));
+    if (write) {
+        *reinterpret_cast<int *>(block + 4 + 4 * g) = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
+        if (g == 0) *reinterpret_cast<__half2 *>(block) = __halves2half2(__float2half_rn(d), __float2half_rn(sum));
+    }
 }
 
 // cp.async: 16 bytes global -> shared, bypassing L1.

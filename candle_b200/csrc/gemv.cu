@@ -51,8 +51,6 @@ using namespace cq_plan;
 int g_force_rb = 0;
 int g_force_ctas_per_sm = 0;
 
-using GemvKernel = void (*)(const uint8_t *, const uint8_t *, void *, int, int, int, int, int, int, int);
-
 // Table of instantiations for one (weight type, activation encoding): [batch 1..8][RB index: 1,2,4,8].
 template <int TYPE, int ACT> struct KernelTable {
     KernelEntry e[8][4];
@@ -80,8 +78,10 @@ bool launch_type(const void *w, const void *y, void *dst, int out_kind, int K, i
     if (!make_plan<TYPE, ACT>(K, N, B, p)) return false;
     ensure_smem_attr(p.k);
     const int row_bytes = K / cq_block_elems(ChunkGeom<TYPE>::BASE) * cq_type_size(ChunkGeom<TYPE>::BASE);
-    ((GemvKernel)p.k->fn)<<<p.grid, p.T, p.smem, st>>>((const uint8_t *)w, (const uint8_t *)y, dst, out_kind,
-                                          K / ChunkGeom<TYPE>::ELEMS, N, sy, sd, row_bytes, p.stage_stride);
+    const uint8_t *wp = (const uint8_t *)w, *yp = (const uint8_t *)y;
+    int nchunks = K / ChunkGeom<TYPE>::ELEMS, rb = row_bytes, ss = p.stage_stride;
+    void *args[] = {&wp, &yp, &dst, &out_kind, &nchunks, &N, &sy, &sd, &rb, &ss};
+    cq_launch(p.k->fn, dim3(p.grid), dim3(p.T), p.smem, st, args);
     cq_check_launch("gemv");
     return true;
 }

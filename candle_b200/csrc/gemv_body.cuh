@@ -46,6 +46,10 @@ __device__ __forceinline__ void gemv_body(const uint8_t *__restrict__ w, const M
         cq_bulk_g2s(stages + stage * stage_stride, (const void *)a0, total, &bars[stage]);
     };
     if (tid == 0 && bid < nbatches) issue(bid, 0);
+    // Weights are never written by a kernel of the same stream, so the first copy is already in flight while the
+    // predecessor (which produces the activations) drains; everything below reads or writes what it may touch.
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
 
     const bool active = tid < nchunks;
     ChunkAct<TYPE> act[B];

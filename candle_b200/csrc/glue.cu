@@ -2,6 +2,9 @@
 // of a Llama-style block (candle-transformers/src/models/quantized_llama.rs:56-62, 178-262; candle's own kernels for
 // them are candle-kernels/src/reduce.cu:559-681 and unary.cu).  One launch each instead of a chain of tensor ops, so
 // that a decode step is not dominated by launch overhead.  Everything is per row with a fixed order of additions.
+//
+// The steps whose result only feeds a quantized matmul can store it directly as Q8_1 containers (the bytes the
+// stand-alone quantizer would make of the f32 result), which removes one launch and one round trip per matmul.
 #include "../../include/candle_q_b200.h"
 #include "common.cuh"
 
@@ -11,10 +14,15 @@ namespace {
 // With a residual, x[r, :] += residual[r, :] is done (and stored) first.  A thread owns float4 number tid, tid + 1024,
 // ...: the first of them stays in registers, so that a row of up to 4096 floats is read once.  Squares are added
 // element by element per thread, then by an xor butterfly, then over the 32 warps in index order.
+// Q8: the result goes out as Q8_1 containers of a row of k_padded values (zero blocks past d; d a multiple of 32).
+template <bool Q8>
 __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, const float *__restrict__ residual,
-                                                        const float *__restrict__ w, float *__restrict__ out, int d, float eps) {
+                                                        const float *__restrict__ w, void *__restrict__ out, int d, int k_padded,
+                                                        float eps) {
     __shared__ float red[32];
     const int n4 = d >> 2, tid = threadIdx.x;
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
     float4 *xr = reinterpret_cast<float4 *>(x + (size_t)blockIdx.x * d);
     const float4 *rr = residual ? reinterpret_cast<const float4 *>(residual + (size_t)blockIdx.x * d) : nullptr;
     float4 first = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -37,15 +45,23 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, c
 #pragma unroll
     for (int i = 1; i < 32; ++i) s += red[i];
     const float inv = rsqrtf(__fadd_rn(__fdiv_rn(s, (float)d), eps));
-    float4 *o = reinterpret_cast<float4 *>(out + (size_t)blockIdx.x * d);
     const float4 *w4 = reinterpret_cast<const float4 *>(w);
-    for (int i = tid; i < n4; i += 1024) {
-        const float4 v = (i == tid) ? first : xr[i];      // later ones were written by this same thread
-        const float4 g = w4[i];
-        float4 r;
-        r.x = __fmul_rn(__fmul_rn(v.x, inv), g.x); r.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
-        r.z = __fmul_rn(__fmul_rn(v.z, inv), g.z); r.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
-        o[i] = r;
+    const int n4_out = Q8 ? (k_padded >> 2) : n4;
+    for (int i0 = 0; i0 < n4_out; i0 += 1024) {         // whole warps stay together for the block quantizer
+        const int i = i0 + tid;
+        float r[4] = {0.f, 0.f, 0.f, 0.f};
+        if (i < n4) {
+            const float4 v = (i == tid) ? first : xr[i];      // later ones were written by this same thread
+            const float4 g = w4[i];
+            r[0] = __fmul_rn(__fmul_rn(v.x, inv), g.x); r[1] = __fmul_rn(__fmul_rn(v.y, inv), g.y);
+            r[2] = __fmul_rn(__fmul_rn(v.z, inv), g.z); r[3] = __fmul_rn(__fmul_rn(v.w, inv), g.w);
+        }
+        if constexpr (Q8) {
+            uint8_t *row = reinterpret_cast<uint8_t *>(out) + (size_t)blockIdx.x * (k_padded / 32) * CQ_Q8_BYTES;
+            cq_q8_1_store_block(r, row + (size_t)(i >> 3) * CQ_Q8_BYTES, i < n4_out);
+        } else if (i < n4) {
+            reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)blockIdx.x * d)[i] = make_float4(r[0], r[1], r[2], r[3]);
+        }
     }
 }
 
@@ -58,6 +74,8 @@ __global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, 
                                                          const int *__restrict__ pos, float *__restrict__ kc,
                                                          float *__restrict__ vc, int B, int T, int hq, int hkv, int tmax,
                                                          int half_d, int q_stride, int k_stride, int v_stride) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nq = (int64_t)B * T * hq * half_d, nk = (int64_t)B * T * hkv * half_d;
     if (idx >= nq + nk) return;
@@ -83,29 +101,65 @@ __global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, 
     }
 }
 
-// out[r, i] = silu(gu[r, i]) * gu[r, f + i]   with gu = [gate | up] rows of width 2f;  silu(x) = x / (1 + exp(-x))
-__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, float *__restrict__ out, int64_t rows, int f) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= rows * f) return;
-    const int64_t r = idx / f;
-    const int i = (int)(idx % f);
-    const float g = gu[r * 2 * f + i], u = gu[r * 2 * f + f + i];
-    out[idx] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+// out[r, i] = silu(gu[r, i]) * gu[r, f + i]   with gu = [gate | up] rows of width 2f;  silu(x) = x / (1 + exp(-x)).
+// One thread per four consecutive outputs; f a multiple of 4 (of 32 for Q8).  grid (ceil(n4 / 256), rows).
+template <bool Q8>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, void *__restrict__ out, int f, int k_padded) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    const int r = blockIdx.y;
+    const int i = blockIdx.x * 256 + threadIdx.x;       // float4 index inside the row
+    const int n4 = f >> 2, n4_out = Q8 ? (k_padded >> 2) : n4;
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (i < n4) {
+        const float4 g = reinterpret_cast<const float4 *>(gu + (size_t)r * 2 * f)[i];
+        const float4 u = reinterpret_cast<const float4 *>(gu + (size_t)r * 2 * f + f)[i];
+        o[0] = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, expf(-g.x))), u.x);
+        o[1] = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, expf(-g.y))), u.y);
+        o[2] = __fmul_rn(__fdiv_rn(g.z, __fadd_rn(1.0f, expf(-g.z))), u.z);
+        o[3] = __fmul_rn(__fdiv_rn(g.w, __fadd_rn(1.0f, expf(-g.w))), u.w);
+    }
+    if constexpr (Q8) {
+        uint8_t *row = reinterpret_cast<uint8_t *>(out) + (size_t)r * (k_padded / 32) * CQ_Q8_BYTES;
+        cq_q8_1_store_block(o, row + (size_t)(i >> 3) * CQ_Q8_BYTES, i < n4_out);
+    } else if (i < n4) {
+        reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)r * f)[i] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+bool norm_args_ok(const void *x, const void *w, const void *out, int rows, int d, const char *who) {
+    if (!x || !w || !out || rows <= 0 || d <= 0 || d % 4) {
+        cq_set_status(CQ_ERR_BAD_ARG, who);
+        return false;
+    }
+    return true;
 }
 
 }  // namespace
 
 extern "C" void cq_rms_norm_f32(const float *x, const float *w, float *out, int rows, int d, float eps, void *stream) {
-    if (!x || !w || !out || rows <= 0 || d <= 0 || d % 4) { cq_set_status(CQ_ERR_BAD_ARG, "rms_norm: bad arguments (d must be a multiple of 4)"); return; }
-    rms_norm_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(const_cast<float *>(x), nullptr, w, out, d, eps);
+    if (!norm_args_ok(x, w, out, rows, d, "rms_norm: bad arguments (d must be a multiple of 4)")) return;
+    cq_launch_k(rms_norm_kernel<false>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, const_cast<float *>(x), nullptr, w, out, d, d, eps);
     cq_check_launch("rms_norm");
 }
 
 extern "C" void cq_add_rms_norm_f32(float *x, const float *residual, const float *w, float *out, int rows, int d, float eps,
                                     void *stream) {
-    if (!x || !residual || !w || !out || rows <= 0 || d <= 0 || d % 4) { cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm: bad arguments (d must be a multiple of 4)"); return; }
-    rms_norm_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(x, residual, w, out, d, eps);
+    if (!residual) { cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm: null residual"); return; }
+    if (!norm_args_ok(x, w, out, rows, d, "add_rms_norm: bad arguments (d must be a multiple of 4)")) return;
+    cq_launch_k(rms_norm_kernel<false>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out, d, d, eps);
     cq_check_launch("add_rms_norm");
+}
+
+extern "C" void cq_add_rms_norm_q8_1(float *x, const float *residual, const float *w, void *out_q8, int rows, int d, int k_padded,
+                                     float eps, void *stream) {
+    if (!norm_args_ok(x, w, out_q8, rows, d, "add_rms_norm_q8_1: bad arguments")) return;
+    if (d % 32 || k_padded < d || k_padded % 32) {
+        cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm_q8_1: d and k_padded must be multiples of 32, k_padded >= d");
+        return;
+    }
+    cq_launch_k(rms_norm_kernel<true>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out_q8, d, k_padded, eps);
+    cq_check_launch("add_rms_norm_q8_1");
 }
 
 extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
@@ -116,14 +170,26 @@ extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const f
         return;
     }
     const int64_t n = (int64_t)batch * t * (hq + hkv) * (head_dim / 2);
-    rope_store_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(q, k, v, cosv, sinv, pos, k_cache, v_cache, batch,
-                                                                                      t, hq, hkv, tmax, head_dim / 2, q_stride, k_stride, v_stride);
+    cq_launch_k(rope_store_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, q, k, v, cosv, sinv, pos,
+                k_cache, v_cache, batch, t, hq, hkv, tmax, head_dim / 2, q_stride, k_stride, v_stride);
     cq_check_launch("rope");
 }
 
 extern "C" void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream) {
-    if (!gate_up || !out || rows <= 0 || f <= 0) { cq_set_status(CQ_ERR_BAD_ARG, "silu_mul: bad arguments"); return; }
-    const int64_t n = (int64_t)rows * f;
-    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate_up, out, rows, f);
+    if (!gate_up || !out || rows <= 0 || rows > 65535 || f <= 0 || f % 4) {
+        cq_set_status(CQ_ERR_BAD_ARG, "silu_mul: bad arguments (f must be a multiple of 4, at most 65535 rows)");
+        return;
+    }
+    cq_launch_k(silu_mul_kernel<false>, dim3((f / 4 + 255) / 256, rows), dim3(256), 0, (cudaStream_t)stream, gate_up, out, f, f);
     cq_check_launch("silu_mul");
+}
+
+extern "C" void cq_silu_mul_q8_1(const float *gate_up, void *out_q8, int rows, int f, int k_padded, void *stream) {
+    if (!gate_up || !out_q8 || rows <= 0 || rows > 65535 || f <= 0 || f % 32 || k_padded < f || k_padded % 32) {
+        cq_set_status(CQ_ERR_BAD_ARG, "silu_mul_q8_1: bad arguments (f and k_padded multiples of 32, at most 65535 rows)");
+        return;
+    }
+    cq_launch_k(silu_mul_kernel<true>, dim3((k_padded / 4 + 255) / 256, rows), dim3(256), 0, (cudaStream_t)stream, gate_up, out_q8, f,
+                k_padded);
+    cq_check_launch("silu_mul_q8_1");
 }

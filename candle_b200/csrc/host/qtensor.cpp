@@ -210,6 +210,23 @@ void QCudaStorage::fwd(size_t n, size_t k, const void *x, DType x_dtype, const i
     lib_check("qmatmul");
 }
 
+void QCudaStorage::fwd_q8_1(size_t n, size_t k, const void *act_q8_1, size_t rows, float *out, cudaStream_t stream) const {
+    if (!kernels_support(dtype_)) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(dtype_));
+    if (k % block_size(dtype_) != 0 || n * (k / block_size(dtype_)) * type_size(dtype_) != len_)
+        throw Error("qmatmul: storage size does not match shape");
+    if (act_mode() != ActMode::Cuda) throw Error("forward_q8_1: pre-quantized activations need the Q8_1 activation mode");
+    if (rows == 0) return;
+    if (!act_q8_1 || !out) throw Error("qmatmul: null activation or output pointer");
+    DeviceGuard g(device_);
+    const size_t blocks = pad(k, MATRIX_ROW_PADDING) / 32;
+    for (size_t r0 = 0; r0 < rows; r0 += MMVQ_MAX_BATCH) {
+        const int b = (int)(rows - r0 < MMVQ_MAX_BATCH ? rows - r0 : MMVQ_MAX_BATCH);
+        cq_mmvq((int)dtype_, CQ_ACT_Q8_1_ENC, CQ_ELEM_F32, ptr_, (const uint8_t *)act_q8_1 + r0 * blocks * 36, out + r0 * n, (int)k,
+                (int)n, (int)blocks, (int)n, b, stream);
+    }
+    lib_check("qmatmul (pre-quantized)");
+}
+
 void QCudaStorage::indexed_moe_forward(size_t experts, size_t n, size_t k, const float *x, int x_dim1, const uint32_t *ids,
                                        int batch, int topk, float *out, cudaStream_t stream) const {
     if (!kernels_support(dtype_)) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(dtype_));
@@ -250,6 +267,11 @@ QMatMul::QMatMul(std::shared_ptr<QTensor> t) : t_(std::move(t)) {
 void QMatMul::forward(const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out, cudaStream_t stream) const {
     const auto &s = t_->shape();
     t_->storage().fwd((size_t)s[0], (size_t)s[1], x, x_dtype, dims, ndims, out, stream);
+}
+
+void QMatMul::forward_q8_1(const void *act_q8_1, size_t rows, float *out, cudaStream_t stream) const {
+    const auto &s = t_->shape();
+    t_->storage().fwd_q8_1((size_t)s[0], (size_t)s[1], act_q8_1, rows, out, stream);
 }
 
 }  // namespace candle_q
@@ -303,6 +325,14 @@ extern "C" int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, con
     return guarded([&] {
         QMatMul mm(*(std::shared_ptr<QTensor> *)handle);
         mm.forward(x, (DType)x_dtype, dims, ndims, out, (cudaStream_t)stream);
+    });
+}
+
+extern "C" int cqh_qmatmul_forward_q8_1(void *handle, const void *act_q8_1, int rows, float *out, void *stream) {
+    return guarded([&] {
+        QMatMul mm(*(std::shared_ptr<QTensor> *)handle);
+        if (rows < 0) throw Error("forward_q8_1: negative row count");
+        mm.forward_q8_1(act_q8_1, (size_t)rows, out, (cudaStream_t)stream);
     });
 }
 

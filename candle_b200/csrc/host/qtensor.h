@@ -74,6 +74,10 @@ class QCudaStorage {
     void fwd(size_t n, size_t k, const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out,
              cudaStream_t stream) const;
 
+    // The GEMV alone, for a caller whose previous step already produced Q8_1 containers (rows of pad(k, 512) / 32
+    // containers, f32 output [rows, n]): skips the quantize launch.  Only meaningful with Q8_1 activations.
+    void fwd_q8_1(size_t n, size_t k, const void *act_q8_1, size_t rows, float *out, cudaStream_t stream) const;
+
     // Per (batch entry, slot) GEMV against expert ids[b, slot] of a [experts, n, k] tensor (cuda.rs:587-622).
     // x: f32 [batch, x_dim1, k] with x_dim1 == topk or 1; ids: u32 [batch, topk]; out: f32 [batch, topk, n].
     void indexed_moe_forward(size_t experts, size_t n, size_t k, const float *x, int x_dim1, const uint32_t *ids, int batch,
@@ -109,6 +113,8 @@ class QMatMul {
     explicit QMatMul(std::shared_ptr<QTensor> t);     // QMatMul::from_arc for quantized types
     // Module::forward: x [.., k] -> out [.., n] in x's dtype.
     void forward(const void *x, DType x_dtype, const int64_t *dims, int ndims, void *out, cudaStream_t stream) const;
+    // Same product from activations that are already Q8_1 containers ([rows, pad(k, 512) / 32] blocks) -> f32 [rows, n].
+    void forward_q8_1(const void *act_q8_1, size_t rows, float *out, cudaStream_t stream) const;
     const QTensor &qtensor() const { return *t_; }
 
   private:

@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(256) quantize_act32_kernel(const T *__restrict
     constexpr int LPB = 32 / VEC;  // lanes per 32-element block
     const int ix = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     const bool active = ix < k_padded;
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();      // x comes from the predecessor; y may still be read by it
     for (int row = blockIdx.y; row < rows; row += gridDim.y) {
         float e[VEC];
         if (active) load_vec<T, VEC>(x + (int64_t)row * kx, ix, kx, vec_ok, e);
@@ -128,6 +130,8 @@ __global__ void __launch_bounds__(256) quantize_act_q8k_kernel(const T *__restri
                                                                int kx, int k_padded, int rows, bool vec_ok) {
     const int lane = threadIdx.x & 31;
     const int sb = blockIdx.x * 8 + (threadIdx.x >> 5);
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
     if (sb * 256 >= k_padded) return;   // whole warps leave together
     for (int row = blockIdx.y; row < rows; row += gridDim.y) {
         const T *xr = x + (int64_t)row * kx;
@@ -193,13 +197,13 @@ void launch_quantize(const void *x, void *vy, int kx, int kx_padded, int num_row
             return;
         }
         const dim3 grid((kx_padded / 256 + 7) / 8, gy);
-        quantize_act_q8k_kernel<T><<<grid, 256, 0, stream>>>((const T *)x, (uint8_t *)vy, kx, kx_padded, num_rows, vec_ok);
+        cq_launch_k(quantize_act_q8k_kernel<T>, grid, dim3(256), 0, stream, (const T *)x, (uint8_t *)vy, kx, kx_padded, num_rows, vec_ok);
     } else {
         const dim3 grid((kx_padded + 256 * VEC - 1) / (256 * VEC), gy);
         if (act == CQ_ACT_Q8_1)
-            quantize_act32_kernel<T, CQ_ACT_Q8_1><<<grid, 256, 0, stream>>>((const T *)x, (uint8_t *)vy, kx, kx_padded, num_rows, vec_ok);
+            cq_launch_k(quantize_act32_kernel<T, CQ_ACT_Q8_1>, grid, dim3(256), 0, stream, (const T *)x, (uint8_t *)vy, kx, kx_padded, num_rows, vec_ok);
         else if (act == CQ_ACT_Q8_0)
-            quantize_act32_kernel<T, CQ_ACT_Q8_0><<<grid, 256, 0, stream>>>((const T *)x, (uint8_t *)vy, kx, kx_padded, num_rows, vec_ok);
+            cq_launch_k(quantize_act32_kernel<T, CQ_ACT_Q8_0>, grid, dim3(256), 0, stream, (const T *)x, (uint8_t *)vy, kx, kx_padded, num_rows, vec_ok);
         else {
             cq_set_status(CQ_ERR_BAD_ARG, "quantize: unknown activation encoding");
             return;

@@ -33,6 +33,11 @@ bool cq_check_launch(const char *what) {
     return false;
 }
 
+namespace { std::atomic<int> g_pdl{1}; }
+bool cq_pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+// 1 (default): decode-path kernels are launched as programmatic dependents of their predecessor in the stream.
+extern "C" void cq_set_pdl(int on) { g_pdl.store(on ? 1 : 0); }
+
 extern "C" int cq_last_status(void) { return g_status.load(); }
 extern "C" int cq_last_cuda_error(void) { return g_cuda_err.load(); }
 extern "C" const char *cq_last_message(void) {

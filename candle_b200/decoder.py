@@ -111,6 +111,7 @@ class LlamaShapedDecoder:
         self.cos, self.sin = ang.cos(), ang.sin()
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.device)       # cache position of the next token
         self._graph = None
+        self.fuse_quantize = True       # decode steps: producers store Q8_1 containers directly
 
     # ---- glue -------------------------------------------------------------------------------------------------
     def _norm(self, x: torch.Tensor, delta, w: torch.Tensor) -> torch.Tensor:
@@ -124,39 +125,70 @@ class LlamaShapedDecoder:
                                            self.cfg.rms_eps, st)
         return out
 
+    def _norm_q8(self, x: torch.Tensor, delta, w: torch.Tensor) -> torch.Tensor:
+        """The same normalisation, stored as the Q8_1 containers the next matmul reads."""
+        R, d = x.shape
+        out = torch.empty((R, d // 32 * 36), dtype=torch.uint8, device=self.device)
+        capi.lib().cq_add_rms_norm_q8_1(x.data_ptr(), None if delta is None else delta.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                        R, d, d, self.cfg.rms_eps, torch.cuda.current_stream(self.device).cuda_stream)
+        return out
+
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        """tokens: int64 [B, T] at cache positions pos .. pos+T-1.  Returns the greedy next token [B] and advances pos."""
+        """tokens: int64 [B, T] at cache positions pos .. pos+T-1.  Returns the greedy next token [B] and advances pos.
+
+        Up to 8 rows (decode steps) every activation that only feeds a matmul is produced directly as Q8_1 containers
+        and the matmuls skip their quantize launch; the containers are the bytes the stand-alone quantizer would
+        make, so tokens do not depend on which path ran."""
         cfg, B, T = self.cfg, tokens.shape[0], tokens.shape[1]
         hd, R, lib = cfg.head_dim, B * T, capi.lib()
         st = torch.cuda.current_stream(self.device).cuda_stream
         q_cols, kv_cols = self.hq_l * hd, self.hkv_l * hd
         f_l = cfg.ffn // self.world
         scale = 1.0 / math.sqrt(hd)
+        fused = self.fuse_quantize and R <= 8 and lib.cqh_get_act_mode() == 0 and cfg.d_model % 512 == 0 and cfg.ffn % 512 == 0 and \
+            (cfg.n_heads * hd) % 512 == 0
+        u8 = dict(dtype=torch.uint8, device=self.device)
+        f32 = dict(dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
             x = self.tok_embd.index_select(0, tokens.reshape(-1))                       # [R, d], private to this call
             delta = None                                                                # residual not yet added to x
             for L in self.layers:
-                h = self._norm(x, delta, L.attn_norm)
-                qk = L.wqk.forward(h)                                                   # [R, q_cols + kv_cols]
-                v = L.wv.forward(h)                                                     # [R, kv_cols]
+                if fused:
+                    h = self._norm_q8(x, delta, L.attn_norm)
+                    qk, v = L.wqk.forward_q8_1(h), L.wv.forward_q8_1(h)
+                else:
+                    h = self._norm(x, delta, L.attn_norm)
+                    qk, v = L.wqk.forward(h), L.wv.forward(h)                           # [R, q_cols + kv_cols], [R, kv_cols]
                 lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), self.cos.data_ptr(),
                                          self.sin.data_ptr(), self.pos.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
                                          B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, q_cols + kv_cols, q_cols + kv_cols,
                                          kv_cols, st)
-                att = torch.empty((R, q_cols), dtype=torch.float32, device=self.device)
-                lib.cq_attention_f32(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), att.data_ptr(),
-                                     self.pos.data_ptr(), B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale,
-                                     q_cols + kv_cols, st)
-                delta = self.gather(L.wo.forward(self.gather(att)))
-                h = self._norm(x, delta, L.ffn_norm)
-                gu = L.gate_up.forward(h)                                               # [R, 2 * f_l]
-                a = torch.empty((R, f_l), dtype=torch.float32, device=self.device)
-                lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R, f_l, st)
-                delta = self.gather(L.down.forward(self.gather(a)))
-            h = self._norm(x, delta, self.out_norm)
+                if fused:
+                    att = torch.empty((R, q_cols // 32 * 36), **u8)
+                    lib.cq_attention_q8_1(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), att.data_ptr(),
+                                          self.pos.data_ptr(), B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale,
+                                          q_cols + kv_cols, q_cols // 32, st)
+                    delta = self.gather(L.wo.forward_q8_1(self.gather(att)))
+                    h = self._norm_q8(x, delta, L.ffn_norm)
+                    gu = L.gate_up.forward_q8_1(h)                                      # [R, 2 * f_l]
+                    a = torch.empty((R, f_l // 32 * 36), **u8)
+                    lib.cq_silu_mul_q8_1(gu.data_ptr(), a.data_ptr(), R, f_l, f_l, st)
+                    delta = self.gather(L.down.forward_q8_1(self.gather(a)))
+                else:
+                    att = torch.empty((R, q_cols), **f32)
+                    lib.cq_attention_f32(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), att.data_ptr(),
+                                         self.pos.data_ptr(), B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale,
+                                         q_cols + kv_cols, st)
+                    delta = self.gather(L.wo.forward(self.gather(att)))
+                    h = self._norm(x, delta, L.ffn_norm)
+                    gu = L.gate_up.forward(h)
+                    a = torch.empty((R, f_l), **f32)
+                    lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R, f_l, st)
+                    delta = self.gather(L.down.forward(self.gather(a)))
+            h = (self._norm_q8 if fused else self._norm)(x, delta, self.out_norm)
             capi.check("decoder glue")
-            last = h.view(B, T, cfg.d_model)[:, -1, :].contiguous()
-            logits = self.output.forward(last)                                          # [B, vocab / world]
+            last = h.view(B, T, -1)[:, -1, :].contiguous()
+            logits = self.output.forward_q8_1(last) if fused else self.output.forward(last)     # [B, vocab / world]
             tok = argmax_sharded(logits, self.vocab_start, self.gather)
             self.pos += T
         return tok

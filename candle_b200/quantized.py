@@ -205,4 +205,19 @@ class QMatMul:
                                                         out.data_ptr(), stream))
         return out
 
+    def forward_q8_1(self, act: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The GEMV alone: `act` holds Q8_1 containers, uint8 [rows, pad(k, 512) / 32 * 36], made by a fused producer
+        (or the stand-alone quantizer).  Returns f32 [rows, n]."""
+        k = self.qtensor.shape[1]
+        row_bytes = capi.pad(k, 512) // 32 * 36
+        if not act.is_cuda or act.dtype != torch.uint8 or not act.is_contiguous() or act.dim() != 2 or act.shape[1] != row_bytes:
+            raise CandleQError(f"forward_q8_1 expects a contiguous uint8 CUDA tensor [rows, {row_bytes}]")
+        rows, n = act.shape[0], self.qtensor.shape[0]
+        if out is None:
+            out = torch.empty((rows, n), dtype=torch.float32, device=act.device)
+        stream = torch.cuda.current_stream(act.device).cuda_stream
+        with torch.cuda.device(act.device):
+            capi.hcheck(capi.lib().cqh_qmatmul_forward_q8_1(self.qtensor._h, act.data_ptr(), rows, out.data_ptr(), stream))
+        return out
+
     __call__ = forward

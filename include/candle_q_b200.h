@@ -189,6 +189,9 @@ void cq_prefill_set_debug(int flags);
  *                          position of query 0.
  *   cq_rms_norm_f32      : out[r] = x[r] * rsqrt(mean(x[r]^2) + eps) * w.
  *   cq_add_rms_norm_f32  : x[r] += residual[r] (stored), then the same normalisation of the new x[r].
+ *   cq_add_rms_norm_q8_1, cq_silu_mul_q8_1, cq_attention_q8_1 : the same results stored as the Q8_1 containers the
+ *                          stand-alone quantizer would make of them (rows of k_padded / 32, resp. out_blocks,
+ *                          containers), for cqh_qmatmul_forward_q8_1.  residual may be null.
  *   cq_rope_store_kv_f32 : interleaved RoPE on q and k in place (rows of q_stride / k_stride floats), then k and v
  *                          are stored into the caches at position pos + t.  cosv / sinv: [max_pos, head_dim / 2].
  *   cq_silu_mul_f32      : out[r, i] = silu(gu[r, i]) * gu[r, f + i] for rows gu = [gate | up] of width 2f. */
@@ -197,10 +200,20 @@ void cq_attention_f32(const float *q, const float *k_cache, const float *v_cache
 void cq_rms_norm_f32(const float *x, const float *w, float *out, int rows, int d, float eps, void *stream);
 void cq_add_rms_norm_f32(float *x, const float *residual, const float *w, float *out, int rows, int d, float eps,
                          void *stream);
+void cq_add_rms_norm_q8_1(float *x, const float *residual, const float *w, void *out_q8, int rows, int d, int k_padded,
+                          float eps, void *stream);
+void cq_silu_mul_q8_1(const float *gate_up, void *out_q8, int rows, int f, int k_padded, void *stream);
+void cq_attention_q8_1(const float *q, const float *k_cache, const float *v_cache, void *out_q8, const int *pos, int batch,
+                       int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, int out_blocks,
+                       void *stream);
 void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
                           float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
                           int q_stride, int k_stride, int v_stride, void *stream);
 void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream);
+
+/* 1 (default): decode-path kernels (quantize, GEMV, glue, attention) are launched as programmatic dependents of their
+ * predecessor in the stream, so their prologue and first weight copies overlap its tail; 0: plain launches. */
+void cq_set_pdl(int on);
 
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
@@ -227,6 +240,11 @@ const void *cqh_qtensor_device_ptr(void *handle);
 /* QMatMul::forward: x [.., k] (device, contiguous, x_dtype = CQ_ELEM_*) -> out [.., n], same element type. */
 int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
                         void *stream);
+/* The same product from activations that a previous kernel already stored as Q8_1 containers (rows of
+ * pad(k, 512) / 32 containers; cq_add_rms_norm_q8_1, cq_silu_mul_q8_1, cq_attention_q8_1 or the stand-alone quantizer
+ * make them) -> f32 out [rows, n].  No reference counterpart: candle quantizes inside every forward
+ * (candle-core/src/quantized/fast_mmvq.rs:201-235).  Fails in the CPU-exact activation mode. */
+int cqh_qmatmul_forward_q8_1(void *handle, const void *act_q8_1, int rows, float *out, void *stream);
 /* QTensor::indexed_moe_forward (candle-core/src/quantized/mod.rs:758-784, cuda.rs:587-622): handle is a rank-3
  * tensor [experts, n, k]; x f32 [batch, topk or 1, k]; ids u32 [batch, topk]; out f32 [batch, topk, n]. */
 int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk, float *out,

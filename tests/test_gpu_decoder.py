@@ -109,6 +109,78 @@ def test_glue_kernels_match_torch(lib, cuda_dev):
     assert torch.allclose(a, (torch.nn.functional.silu(gu[:, :f].double()) * gu[:, f:].double()).float(), rtol=1e-5, atol=1e-6)
 
 
+def _quantize_rows(lib, x):
+    """Stand-alone Q8_1 quantizer on f32 rows -> uint8 [rows, pad(k, 512) / 32 * 36]."""
+    rows, k = x.shape
+    kp = (k + 511) // 512 * 512
+    out = torch.zeros((rows, kp // 32 * 36), dtype=torch.uint8, device=x.device)
+    lib.launch_mmvq_gguf_quantize_q8_1_f32(x.data_ptr(), out.data_ptr(), k, kp, rows, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+def test_fused_producers_store_the_quantizers_bytes(lib, cuda_dev):
+    """Norm, SwiGLU and attention with Q8_1 output == their f32 result passed through the stand-alone quantizer."""
+    torch.manual_seed(4)
+    st = torch.cuda.current_stream().cuda_stream
+    R, d, eps = 3, 1024, 1e-5
+    x, delta, w = torch.randn(R, d, device=cuda_dev), torch.randn(R, d, device=cuda_dev), torch.rand(d, device=cuda_dev) + 0.5
+    x[1, 64:96] = 0.0
+    delta[1, 64:96] = 0.0                              # an all-zero block: d = 0, q = 0
+    f = torch.empty_like(x)
+    x1, x2 = x.clone(), x.clone()
+    lib.cq_add_rms_norm_f32(x1.data_ptr(), delta.data_ptr(), w.data_ptr(), f.data_ptr(), R, d, eps, st)
+    q8 = torch.full((R, d // 32 * 36), 0xCD, dtype=torch.uint8, device=cuda_dev)
+    lib.cq_add_rms_norm_q8_1(x2.data_ptr(), delta.data_ptr(), w.data_ptr(), q8.data_ptr(), R, d, d, eps, st)
+    assert torch.equal(x1, x2) and torch.equal(q8, _quantize_rows(lib, f))
+    lib.cq_rms_norm_f32(x.data_ptr(), w.data_ptr(), f.data_ptr(), R, d, eps, st)
+    lib.cq_add_rms_norm_q8_1(x.data_ptr(), None, w.data_ptr(), q8.data_ptr(), R, d, d, eps, st)
+    assert torch.equal(q8, _quantize_rows(lib, f))
+    # padded row: 768 values in a row of 1024
+    x3 = torch.randn(R, 768, device=cuda_dev)
+    w3 = torch.rand(768, device=cuda_dev) + 0.5
+    f3 = torch.empty_like(x3)
+    lib.cq_rms_norm_f32(x3.data_ptr(), w3.data_ptr(), f3.data_ptr(), R, 768, eps, st)
+    q3 = torch.full((R, 1024 // 32 * 36), 0xCD, dtype=torch.uint8, device=cuda_dev)
+    lib.cq_add_rms_norm_q8_1(x3.data_ptr(), None, w3.data_ptr(), q3.data_ptr(), R, 768, 1024, eps, st)
+    assert torch.equal(q3, _quantize_rows(lib, f3))
+
+    fdim = 1536
+    gu = torch.randn(R, 2 * fdim, device=cuda_dev) * 3
+    a = torch.empty(R, fdim, device=cuda_dev)
+    lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R, fdim, st)
+    a8 = torch.full((R, fdim // 32 * 36), 0xCD, dtype=torch.uint8, device=cuda_dev)
+    lib.cq_silu_mul_q8_1(gu.data_ptr(), a8.data_ptr(), R, fdim, fdim, st)
+    assert torch.equal(a8, _quantize_rows(lib, a))
+
+    B, Tq, Hq, Hkv, D, Tmax, pos0 = 2, 1, 8, 2, 128, 96, 70
+    q = torch.randn(B * Tq, Hq * D, device=cuda_dev)
+    kc, vc = torch.randn(B, Hkv, Tmax, D, device=cuda_dev), torch.randn(B, Hkv, Tmax, D, device=cuda_dev)
+    pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
+    o = torch.empty(B * Tq, Hq * D, device=cuda_dev)
+    lib.cq_attention_f32(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), pos.data_ptr(), B, Tq, Hq, Hkv, D, Tmax,
+                         0.088, Hq * D, st)
+    o8 = torch.full((B * Tq, Hq * D // 32 * 36), 0xCD, dtype=torch.uint8, device=cuda_dev)
+    lib.cq_attention_q8_1(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o8.data_ptr(), pos.data_ptr(), B, Tq, Hq, Hkv, D, Tmax,
+                          0.088, Hq * D, Hq * D // 32, st)
+    capi.check("fused producers")
+    assert torch.equal(o8, _quantize_rows(lib, o))
+
+
+def test_decode_tokens_do_not_depend_on_fusion_or_dependent_launch(lib, cuda_dev):
+    cfg = DecoderConfig.tiny()
+    prompt = torch.randint(0, cfg.vocab, (2, 20), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(7))
+    m = LlamaShapedDecoder(cfg, cuda_dev, batch=2, seed=3)
+    base = m.generate(prompt, 10)
+    m.fuse_quantize = False
+    assert torch.equal(m.generate(prompt, 10), base)
+    m.fuse_quantize = True
+    lib.cq_set_pdl(0)
+    try:
+        assert torch.equal(m.generate(prompt, 10), base)
+    finally:
+        lib.cq_set_pdl(1)
+
+
 def test_graph_decode_equals_eager_decode(cuda_dev):
     cfg = DecoderConfig.tiny()
     prompt = torch.randint(0, cfg.vocab, (2, 24), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(2))
