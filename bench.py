@@ -348,6 +348,10 @@ def run_case(args):
     k, n, b = int(k), int(n), int(b)
     dev = torch.device("cuda:0")
     L = capi.lib()
+    if args.mma_min_batch is not None:
+        L.cq_set_mma_min_batch(args.mma_min_batch)
+    if args.no_pdl:
+        L.cq_set_pdl(0)
     ncopies = max(2, min(16, int(300e6 // (n * k * BYTES_PER_ELEM[t])) + 1))     # rotate through > L2 of weights
     ws = [random_blocks(GgmlDType[t], n, k, seed=i, device=dev) for i in range(ncopies)]
     x = torch.randn((b, k), device=dev)
@@ -442,6 +446,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--decode-case", default=None, help="profile helper: BATCH:PROMPT:STEPS, runs only the decoder measurement")
     ap.add_argument("--no-graph", action="store_true", help="with --decode-case: launch decode steps eagerly")
+    ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
+    ap.add_argument("--no-pdl", action="store_true", help="with --case: plain launches instead of programmatic dependent launches")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")

@@ -17,6 +17,7 @@
 //     same bits whether the matrix is whole or sharded by rows across GPUs, and whatever the batch size.
 #include "../../include/candle_q_b200.h"
 #include "gemv_body.cuh"
+#include "gemv_mma.cuh"
 #include "gemv_plan.cuh"
 
 namespace {
@@ -86,6 +87,38 @@ bool launch_type(const void *w, const void *y, void *dst, int out_kind, int K, i
     return true;
 }
 
+// ---- tensor-core variant for 2..8 rows (gemv_mma.cuh); same bits as the kernel above ----
+int g_mma_min_batch = 0;        // rows from which the tensor-core kernel is used (0: per-format default, 9: never)
+// Measured on B200 (4096 -> 128256, GB/s of weights): dp4a Q4_K 5286 / 4296 / 3382 / 1659 / 1246 at 1 / 2 / 4 / 6 / 8 rows,
+// tensor-core 2250 at any row count; Q6_K dp4a 3267 at 4 rows, 1820 at 8, tensor-core 2130; Q8_0 dp4a 4140 at 8 rows,
+// tensor-core 2750.
+constexpr int mma_default_min_batch(int wtype) { return wtype == CQ_Q8_0 ? 9 : 5; }
+
+template <int TYPE>
+__global__ void __launch_bounds__(cq_mma::kThreads, 2)
+gemv_mma_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ y, void *__restrict__ dst, int out_kind, int nchunks, int nrows,
+                int stride_col_y, int stride_col_dst, int b, int row_bytes, int tiles_per_cta) {
+    cq_mma::gemv_mma_body<TYPE>(w, y, dst, out_kind, nchunks, nrows, stride_col_y, stride_col_dst, b, row_bytes, tiles_per_cta,
+                                &g_gemv_timeout_flag);
+}
+
+template <int TYPE>
+bool launch_mma(const void *w, const void *y, void *dst, int out_kind, int K, int N, int sy, int sd, int B, cudaStream_t st) {
+    static KernelEntry ke{(const void *)gemv_mma_kernel<TYPE>};
+    const DevInfo di = dev_info();
+    const int ntiles = (N + cq_mma::kTileRows - 1) / cq_mma::kTileRows;
+    int tpc = (ntiles + 2 * di.sms - 1) / (2 * di.sms);
+    if (tpc > cq_mma::kMaxTilesPerCta) tpc = cq_mma::kMaxTilesPerCta;
+    const int grid = (ntiles + tpc - 1) / tpc;
+    const int smem = cq_mma::smem_bytes<TYPE>(tpc) + 16;     // fragment reads may touch a few bytes past the last row
+    if (smem > di.smem_optin) return false;
+    ensure_smem_attr(&ke);
+    const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
+    cq_launch_k(gemv_mma_kernel<TYPE>, dim3(grid), dim3(cq_mma::kThreads), (size_t)smem, st, (const uint8_t *)w, (const uint8_t *)y, dst,
+                out_kind, K / cq_mma::Fmt<TYPE>::CHUNK, N, sy, sd, B, row_bytes, tpc);
+    return cq_check_launch("gemv (tensor core)");
+}
+
 size_t elem_bytes(int kind) { return kind == CQ_F32 ? 4 : 2; }
 
 }  // namespace
@@ -120,6 +153,13 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
     auto run = [&](int j0, int bb) -> bool {
         const uint8_t *yy = (const uint8_t *)vy + (size_t)j0 * stride_col_y * CQ_Q8_BYTES;
         uint8_t *dd = (uint8_t *)dst + (size_t)j0 * stride_col_dst * elem_bytes(out_kind);
+        if (!cpu_act && bb >= (g_mma_min_batch > 0 ? g_mma_min_batch : mma_default_min_batch(wtype))) {
+            switch (wtype) {
+            case CQ_Q8_0: if (launch_mma<CQ_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)) return true; break;
+            case CQ_Q4_K: if (launch_mma<CQ_Q4_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)) return true; break;
+            case CQ_Q6_K: if (launch_mma<CQ_Q6_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)) return true; break;
+            }
+        }
         switch (wtype) {
         case CQ_Q4_0:
             return cpu_act ? launch_type<CQ_Q4_0, CQ_ACT_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
@@ -151,6 +191,9 @@ extern "C" void cq_set_tuning(int rows_per_batch, int ctas_per_sm) {
     g_force_rb = rows_per_batch;
     g_force_ctas_per_sm = ctas_per_sm;
 }
+
+// Rows from which the tensor-core GEMV replaces the dp4a one (0: per-format default; 9 or more: never).  Same bits either way.
+extern "C" void cq_set_mma_min_batch(int rows) { g_mma_min_batch = rows < 0 ? 0 : rows; }
 
 // 1 if any GEMV launch on the current device gave up waiting for a staged copy (synchronises the device).
 extern "C" int cq_device_timeout_flag(void) {

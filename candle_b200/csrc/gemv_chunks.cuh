@@ -234,7 +234,8 @@ template <> struct ChunkW<CQ_Q4_K_WIDE> {
         int d0, d1x16;
         idots(a, d0, d1x16);
         if constexpr (cq_act_q8_1_like(ACT)) {
-            const float sd = __fmaf_rn(__fmul_rn(a.d[1], 0.0625f), (float)(d1x16 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
+            // d1x16 is 16 x an integer, so the shift is exact; both products stay below 2^24 and convert exactly
+            const float sd = __fmaf_rn(a.d[1], (float)((d1x16 >> 4) * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
             const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
         } else {

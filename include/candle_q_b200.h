@@ -215,6 +215,11 @@ void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *st
  * predecessor in the stream, so their prologue and first weight copies overlap its tail; 0: plain launches. */
 void cq_set_pdl(int on);
 
+/* Rows from which the tensor-core GEMV (mma.sync int8) replaces the dp4a one for Q4_K / Q6_K / Q8_0 weights with
+ * Q8_1 activations (0: per-format default, which is 5 for Q4_K / Q6_K and never for Q8_0; 9: never).  Both kernels
+ * produce the same bits, so the choice only affects speed. */
+void cq_set_mma_min_batch(int rows);
+
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
 /* 1 if a GEMV on the current device gave up a bounded wait for a staged copy (then also sets status 4).

@@ -182,6 +182,27 @@ def test_batch_invariance_and_sharding_invariance(lib, oracle, cuda_dev):
             assert torch.equal(torch.cat(parts, dim=1), base)
 
 
+@pytest.mark.parametrize("tname", ["q4_k", "q6_k", "q8_0"])
+@pytest.mark.parametrize("k,n", [(256, 5), (768, 33), (1024, 16), (2048, 100), (4096, 257), (14336, 48), (3072, 40)])
+def test_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle, cuda_dev, tname, k, n):
+    """The mma.sync kernel (2..8 rows) against the dp4a kernel, forced in turn for every batch size: equal bits, with
+    partial groups (K below or not a multiple of 2048 / 1024), ragged last tiles and every column count."""
+    wt = TYPES[tname]
+    _, x, wq = make_case(oracle, wt, k, n, 8, seed=k + n)
+    w_dev = torch.from_numpy(wq).to(cuda_dev)
+    try:
+        for b in range(1, 9):
+            xb = torch.from_numpy(x[:b]).to(cuda_dev)
+            lib.cq_set_mma_min_batch(9)
+            ref = ref_call_sequence(lib, tname, "f32", w_dev, xb, k, n)[1].clone()
+            lib.cq_set_mma_min_batch(1)
+            got = ref_call_sequence(lib, tname, "f32", w_dev, xb, k, n)[1]
+            assert torch.equal(got, ref), f"batch {b}"
+    finally:
+        lib.cq_set_mma_min_batch(0)
+    assert lib.cq_device_timeout_flag() == 0
+
+
 def test_golden_fixtures(lib, cuda_dev):
     """Committed oracle outputs (tests/golden/make_fixtures.py)."""
     g = np.load(GOLD)
