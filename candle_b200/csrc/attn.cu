@@ -144,6 +144,158 @@ __global__ void __launch_bounds__(kThreads) attention_f32_kernel(const float *__
 }  // namespace
 
 namespace {
+
+// ---- decode variant: the context of one (sequence, head, query) is cut into chunks of kChunk keys, one CTA each ----
+// With one query per sequence only `heads` CTAs exist and each walks the whole context alone; here heads x chunks CTAs
+// share the work.  A CTA leaves its chunk's (max, sum, unnormalised output) in `scratch`; the CTA that finishes last
+// (an atomic counter per output row, reset by that CTA) combines the chunks in index order, so the result does not
+// depend on which CTA that was.  Nothing waits for anything.
+constexpr int kChunk = 128, kSplitThreads = 256, kSplitWarps = 8, kPartFloats = 132;
+
+template <bool Q8>
+__global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+                                                                       const float *__restrict__ vc, void *__restrict__ out,
+                                                                       const int *__restrict__ pos, float *__restrict__ scratch,
+                                                                       int *__restrict__ counters, int tq, int hq, int hkv, int tmax,
+                                                                       float scale, int q_stride, int out_blocks) {
+    __shared__ float scores[kChunk];
+    __shared__ float red[kSplitWarps];
+    __shared__ float4 part[kSplitWarps][32];
+    __shared__ int is_last;
+    const int h = blockIdx.x, split = blockIdx.y, bt = blockIdx.z, nsplit = gridDim.y;
+    const int b = bt / tq, t = bt % tq;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    int n_ctx = pos[0] + t + 1;
+    if (n_ctx > tmax) n_ctx = tmax;
+    const int key0 = split * kChunk;
+    if (key0 >= n_ctx) return;                      // the whole CTA: this chunk holds no key of the context
+    const int nk = min(kChunk, n_ctx - key0), nact = (n_ctx + kChunk - 1) / kChunk;
+    const int kvh = h / (hq / hkv);
+    const float *qp = q + (size_t)bt * q_stride + (size_t)h * kD;
+    const float *kp = kc + (((size_t)b * hkv + kvh) * (size_t)tmax + key0) * kD;
+    const float *vp = vc + (((size_t)b * hkv + kvh) * (size_t)tmax + key0) * kD;
+
+    {   // scores: one key per group of 8 lanes, 32 keys per pass
+        const int g = tid & 7, grp = tid >> 3;
+        float4 qv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4 *>(qp + 4 * (g + 8 * i));
+#pragma unroll
+        for (int j0 = 0; j0 < kChunk; j0 += kSplitThreads / 8) {
+            const int j = j0 + grp;
+            const bool live = j < nk;
+            float4 kv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                kv[i] = live ? *reinterpret_cast<const float4 *>(kp + (size_t)j * kD + 4 * (g + 8 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s = __fmaf_rn(qv[i].x, kv[i].x, s);
+                s = __fmaf_rn(qv[i].y, kv[i].y, s);
+                s = __fmaf_rn(qv[i].z, kv[i].z, s);
+                s = __fmaf_rn(qv[i].w, kv[i].w, s);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            if (live && g == 0) scores[j] = __fmul_rn(s, scale);
+        }
+    }
+    __syncthreads();
+    float mx = tid < nk ? scores[tid] : -INFINITY;           // kChunk <= kSplitThreads
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < kSplitWarps; ++w) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    float sum = 0.0f;
+    if (tid < nk) {
+        sum = expf(scores[tid] - mx);
+        scores[tid] = sum;
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = red[0];
+#pragma unroll
+    for (int w = 1; w < kSplitWarps; ++w) sum += red[w];
+    // weighted values: warp w takes keys w, w + 8, ... in ascending order, four loads in flight
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j0 = 0; j0 < kChunk; j0 += 4 * kSplitWarps) {
+        float4 vv[4];
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = j0 + warp + i * kSplitWarps;
+            const bool live = j < nk;
+            p[i] = live ? scores[j] : 0.0f;
+            vv[i] = live ? *reinterpret_cast<const float4 *>(vp + (size_t)j * kD + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (j0 + warp + i * kSplitWarps < nk) {
+                o.x = __fmaf_rn(p[i], vv[i].x, o.x);
+                o.y = __fmaf_rn(p[i], vv[i].y, o.y);
+                o.z = __fmaf_rn(p[i], vv[i].z, o.z);
+                o.w = __fmaf_rn(p[i], vv[i].w, o.w);
+            }
+        }
+    }
+    part[warp][lane] = o;
+    __syncthreads();
+    float *mine = scratch + ((size_t)(bt * hq + h) * nsplit + split) * kPartFloats;
+    if (warp == 0) {
+        float4 acc = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < kSplitWarps; ++w) {
+            const float4 pw = part[w][lane];
+            acc.x += pw.x; acc.y += pw.y; acc.z += pw.z; acc.w += pw.w;
+        }
+        *reinterpret_cast<float4 *>(mine + 4 * lane) = acc;
+        if (lane == 0) { mine[128] = mx; mine[129] = sum; }
+        __threadfence();
+    }
+    __syncthreads();
+    if (tid == 0) is_last = atomicAdd(&counters[bt * hq + h], 1) == nact - 1;
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    // combine the chunks in index order (read around L1: other SMs wrote them)
+    const float *base = scratch + (size_t)(bt * hq + h) * nsplit * kPartFloats;
+    float big = -INFINITY;
+    for (int s = 0; s < nact; ++s) big = fmaxf(big, __ldcg(base + (size_t)s * kPartFloats + 128));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.0f;
+    for (int s = 0; s < nact; ++s) {
+        const float *ps = base + (size_t)s * kPartFloats;
+        const float wgt = expf(__ldcg(ps + 128) - big);
+        const float4 po = __ldcg(reinterpret_cast<const float4 *>(ps + 4 * lane));
+        den = __fmaf_rn(wgt, __ldcg(ps + 129), den);
+        acc.x = __fmaf_rn(wgt, po.x, acc.x); acc.y = __fmaf_rn(wgt, po.y, acc.y);
+        acc.z = __fmaf_rn(wgt, po.z, acc.z); acc.w = __fmaf_rn(wgt, po.w, acc.w);
+    }
+    const float r[4] = {__fdiv_rn(acc.x, den), __fdiv_rn(acc.y, den), __fdiv_rn(acc.z, den), __fdiv_rn(acc.w, den)};
+    if constexpr (Q8) {
+        uint8_t *row = reinterpret_cast<uint8_t *>(out) + (size_t)bt * out_blocks * CQ_Q8_BYTES;
+        cq_q8_1_store_block(r, row + (size_t)(4 * h + (lane >> 3)) * CQ_Q8_BYTES, true);
+    } else {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + ((size_t)bt * hq + h) * kD + 4 * lane) =
+            make_float4(r[0], r[1], r[2], r[3]);
+    }
+    if (lane == 0) counters[bt * hq + h] = 0;        // ready for the next launch
+}
+
+}  // namespace
+
+namespace {
 bool attention_args_ok(const void *q, const void *k_cache, const void *v_cache, const void *out, const void *pos, int batch, int tq,
                        int hq, int hkv, int head_dim, int tmax) {
     if (!q || !k_cache || !v_cache || !out || !pos || batch <= 0 || tq <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0) {
@@ -176,4 +328,31 @@ extern "C" void cq_attention_q8_1(const float *q, const float *k_cache, const fl
     cq_launch_k(attention_f32_kernel<true>, dim3(hq, tq, batch), dim3(kThreads), (size_t)tmax * sizeof(float), (cudaStream_t)stream, q,
                 k_cache, v_cache, out_q8, pos, tq, hq, hkv, tmax, scale, q_stride, out_blocks);
     cq_check_launch("attention_q8_1");
+}
+
+// Decode variant (few queries): the context is cut into chunks of 128 keys, one CTA per (head, chunk, query); see
+// attention_split_kernel.  scratch: cq_attention_split_scratch_floats(...) floats; counters: batch * tq * hq ints that are
+// zero before the first call (every call leaves them zero).  out_q8 != 0: `out` receives Q8_1 containers, out_blocks per row.
+// The additions follow the chunking, so results differ in the last bits from cq_attention_f32: a caller picks one of the
+// two by (batch, tq) only.
+extern "C" size_t cq_attention_split_scratch_floats(int batch, int tq, int hq, int tmax) {
+    return (size_t)batch * tq * hq * ((tmax + kChunk - 1) / kChunk) * kPartFloats;
+}
+
+extern "C" void cq_attention_split(const float *q, const float *k_cache, const float *v_cache, void *out, int out_q8, const int *pos,
+                                   float *scratch, int *counters, int batch, int tq, int hq, int hkv, int head_dim, int tmax,
+                                   float scale, int q_stride, int out_blocks, void *stream) {
+    if (!attention_args_ok(q, k_cache, v_cache, out, pos, batch, tq, hq, hkv, head_dim, tmax)) return;
+    if (!scratch || !counters || (out_q8 && out_blocks < hq * 4) || (int64_t)batch * tq > 65535) {
+        cq_set_status(CQ_ERR_BAD_ARG, "attention_split: null scratch, short container row, or more than 65535 queries");
+        return;
+    }
+    const dim3 grid(hq, (tmax + kChunk - 1) / kChunk, batch * tq);
+    if (out_q8)
+        cq_launch_k(attention_split_kernel<true>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos, scratch,
+                    counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks);
+    else
+        cq_launch_k(attention_split_kernel<false>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos,
+                    scratch, counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks);
+    cq_check_launch("attention_split");
 }

@@ -26,6 +26,10 @@
 // in the same places.
 constexpr int CQ_Q4_K_WIDE = 1012;
 
+// int -> float without the conversion pipe, which dp4a already keeps busy on this GPU: exact for |i| < 2^22, so the
+// result is the one a conversion instruction gives.
+__device__ __forceinline__ float cq_small_int_to_float(int i) { return __int_as_float(i + 0x4B400000) - 12582912.0f; }
+
 template <int TYPE> struct ChunkGeom;
 template <> struct ChunkGeom<CQ_Q4_0> { static constexpr int BASE = CQ_Q4_0, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
 template <> struct ChunkGeom<CQ_Q8_0> { static constexpr int BASE = CQ_Q8_0, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
@@ -124,7 +128,7 @@ template <> struct ChunkW<CQ_Q4_0> {
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_0> &a) const {
         const int s = idot(a);
-        if constexpr (cq_act_q8_1_like(ACT)) return __fmul_rn(d, __fmaf_rn((float)s, a.d[0], __fmul_rn(-8.0f, a.s[0])));
+        if constexpr (cq_act_q8_1_like(ACT)) return __fmul_rn(d, __fmaf_rn(cq_small_int_to_float(s), a.d[0], __fmul_rn(-8.0f, a.s[0])));
         else return __fmul_rn(__fmul_rn((float)(s - 8 * a.sq[0]), d), a.d[0]);
     }
 };
@@ -144,7 +148,7 @@ template <> struct ChunkW<CQ_Q8_0> {
         return s;
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q8_0> &a) const {
-        return __fmul_rn(__fmul_rn((float)idot(a), d), a.d[0]);
+        return __fmul_rn(__fmul_rn(cq_small_int_to_float(idot(a)), d), a.d[0]);
     }
 };
 
@@ -182,8 +186,8 @@ template <> struct ChunkW<CQ_Q4_K> {
         int d0, d1;
         idots(a, d0, d1);
         if constexpr (cq_act_q8_1_like(ACT)) {
-            const float sd = __fmaf_rn(a.d[1], (float)(d1 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
-            const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
+            const float sd = __fmaf_rn(a.d[1], cq_small_int_to_float(d1 * sc[1]), __fmul_rn(a.d[0], cq_small_int_to_float(d0 * sc[0])));
+            const float sm = __fmaf_rn(a.s[1], cq_small_int_to_float(mn[1]), __fmul_rn(a.s[0], cq_small_int_to_float(mn[0])));
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
         } else {
             const int isd = d0 * sc[0] + d1 * sc[1];
@@ -235,8 +239,8 @@ template <> struct ChunkW<CQ_Q4_K_WIDE> {
         idots(a, d0, d1x16);
         if constexpr (cq_act_q8_1_like(ACT)) {
             // d1x16 is 16 x an integer, so the shift is exact; both products stay below 2^24 and convert exactly
-            const float sd = __fmaf_rn(a.d[1], (float)((d1x16 >> 4) * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
-            const float sm = __fmaf_rn(a.s[1], (float)mn[1], __fmul_rn(a.s[0], (float)mn[0]));
+            const float sd = __fmaf_rn(a.d[1], cq_small_int_to_float((d1x16 >> 4) * sc[1]), __fmul_rn(a.d[0], cq_small_int_to_float(d0 * sc[0])));
+            const float sm = __fmaf_rn(a.s[1], cq_small_int_to_float(mn[1]), __fmul_rn(a.s[0], cq_small_int_to_float(mn[0])));
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
         } else {
             const int isd = d0 * sc[0] + (d1x16 >> 4) * sc[1];
@@ -280,7 +284,8 @@ template <> struct ChunkW<CQ_Q6_K> {
         if constexpr (cq_act_q8_1_like(ACT)) {
             float sf = 0.0f;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) sf = __fmaf_rn(a.d[p], (float)(idot(a, p) * sc[p]), sf);
+            for (int p = 0; p < 4; ++p)      // |idot * sc| < 2^24: the f32 product of the two exact factors is that integer
+                sf = __fmaf_rn(a.d[p], __fmul_rn(cq_small_int_to_float(idot(a, p)), cq_small_int_to_float(sc[p])), sf);
             return __fmul_rn(d, sf);
         } else {
             int is = 0;

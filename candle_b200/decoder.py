@@ -112,6 +112,7 @@ class LlamaShapedDecoder:
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.device)       # cache position of the next token
         self._graph = None
         self.fuse_quantize = True       # decode steps: producers store Q8_1 containers directly
+        self._att_scratch = None        # split-context attention: partial results and arrival counters
 
     # ---- glue -------------------------------------------------------------------------------------------------
     def _norm(self, x: torch.Tensor, delta, w: torch.Tensor) -> torch.Tensor:
@@ -133,6 +134,31 @@ class LlamaShapedDecoder:
                                         R, d, d, self.cfg.rms_eps, torch.cuda.current_stream(self.device).cuda_stream)
         return out
 
+    def _attention(self, qk: torch.Tensor, L, B: int, T: int, out: torch.Tensor, q8: bool) -> None:
+        """Causal attention of the rotated queries in `qk` over the layer's cache.  Up to 64 queries the context is
+        split over several CTAs per head (a different, equally fixed order of additions), else one CTA per head;
+        the choice depends on (B, T) only, so it is the same at every tensor-parallel width."""
+        cfg, lib, hd = self.cfg, capi.lib(), self.cfg.head_dim
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        q_stride = (self.hq_l + self.hkv_l) * hd
+        scale = 1.0 / math.sqrt(hd)
+        blocks = self.hq_l * hd // 32
+        if B * T <= 64:
+            if self._att_scratch is None:
+                n = lib.cq_attention_split_scratch_floats(64, 1, self.hq_l, cfg.max_pos)
+                self._att_scratch = (torch.empty(n, dtype=torch.float32, device=self.device),
+                                     torch.zeros(64 * self.hq_l, dtype=torch.int32, device=self.device))
+            scratch, counters = self._att_scratch
+            lib.cq_attention_split(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), 1 if q8 else 0,
+                                   self.pos.data_ptr(), scratch.data_ptr(), counters.data_ptr(), B, T, self.hq_l, self.hkv_l, hd,
+                                   cfg.max_pos, scale, q_stride, blocks, st)
+        elif q8:
+            lib.cq_attention_q8_1(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
+                                  B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale, q_stride, blocks, st)
+        else:
+            lib.cq_attention_f32(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
+                                 B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale, q_stride, st)
+
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens: int64 [B, T] at cache positions pos .. pos+T-1.  Returns the greedy next token [B] and advances pos.
 
@@ -144,7 +170,6 @@ class LlamaShapedDecoder:
         st = torch.cuda.current_stream(self.device).cuda_stream
         q_cols, kv_cols = self.hq_l * hd, self.hkv_l * hd
         f_l = cfg.ffn // self.world
-        scale = 1.0 / math.sqrt(hd)
         fused = self.fuse_quantize and R <= 8 and lib.cqh_get_act_mode() == 0 and cfg.d_model % 512 == 0 and cfg.ffn % 512 == 0 and \
             (cfg.n_heads * hd) % 512 == 0
         u8 = dict(dtype=torch.uint8, device=self.device)
@@ -165,9 +190,7 @@ class LlamaShapedDecoder:
                                          kv_cols, st)
                 if fused:
                     att = torch.empty((R, q_cols // 32 * 36), **u8)
-                    lib.cq_attention_q8_1(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), att.data_ptr(),
-                                          self.pos.data_ptr(), B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale,
-                                          q_cols + kv_cols, q_cols // 32, st)
+                    self._attention(qk, L, B, T, att, True)
                     delta = self.gather(L.wo.forward_q8_1(self.gather(att)))
                     h = self._norm_q8(x, delta, L.ffn_norm)
                     gu = L.gate_up.forward_q8_1(h)                                      # [R, 2 * f_l]
@@ -176,9 +199,7 @@ class LlamaShapedDecoder:
                     delta = self.gather(L.down.forward_q8_1(self.gather(a)))
                 else:
                     att = torch.empty((R, q_cols), **f32)
-                    lib.cq_attention_f32(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), att.data_ptr(),
-                                         self.pos.data_ptr(), B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale,
-                                         q_cols + kv_cols, st)
+                    self._attention(qk, L, B, T, att, False)
                     delta = self.gather(L.wo.forward(self.gather(att)))
                     h = self._norm(x, delta, L.ffn_norm)
                     gu = L.gate_up.forward(h)

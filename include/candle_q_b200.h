@@ -206,6 +206,13 @@ void cq_silu_mul_q8_1(const float *gate_up, void *out_q8, int rows, int f, int k
 void cq_attention_q8_1(const float *q, const float *k_cache, const float *v_cache, void *out_q8, const int *pos, int batch,
                        int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, int out_blocks,
                        void *stream);
+/* Decode variant of the attention (few queries): heads x chunks-of-128-keys CTAs; the last CTA of an output row combines
+ * the chunks in index order.  scratch: cq_attention_split_scratch_floats() floats; counters: batch * tq * hq ints, zero
+ * before the first call and after every call.  out_q8 != 0: Q8_1 containers as cq_attention_q8_1. */
+size_t cq_attention_split_scratch_floats(int batch, int tq, int hq, int tmax);
+void cq_attention_split(const float *q, const float *k_cache, const float *v_cache, void *out, int out_q8, const int *pos,
+                        float *scratch, int *counters, int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale,
+                        int q_stride, int out_blocks, void *stream);
 void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
                           float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
                           int q_stride, int k_stride, int v_stride, void *stream);

@@ -57,6 +57,38 @@ def test_attention_long_context_and_strided_queries(lib, cuda_dev):
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("pos0", [0, 5, 127, 128, 300, 699])
+def test_split_attention_matches_dense_reference(lib, cuda_dev, pos0):
+    """Decode variant (chunks of 128 keys, last CTA combines): f32 output against the dense formula, Q8_1 output against
+    the stand-alone quantizer applied to the f32 output, and the arrival counters back at zero."""
+    torch.manual_seed(pos0)
+    st = torch.cuda.current_stream().cuda_stream
+    B, Tq, Hq, Hkv, D, Tmax = 3, 1, 8, 2, 128, 700
+    wide = torch.randn(B * Tq, Hq * D + 128, device=cuda_dev)
+    kc, vc = torch.randn(B, Hkv, Tmax, D, device=cuda_dev), torch.randn(B, Hkv, Tmax, D, device=cuda_dev)
+    pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
+    scratch = torch.full((lib.cq_attention_split_scratch_floats(B, Tq, Hq, Tmax),), float("nan"), device=cuda_dev)
+    counters = torch.zeros(B * Tq * Hq, dtype=torch.int32, device=cuda_dev)
+    out = torch.full((B * Tq, Hq * D), float("nan"), device=cuda_dev)
+    args = (pos.data_ptr(), scratch.data_ptr(), counters.data_ptr(), B, Tq, Hq, Hkv, D, Tmax, 1.0 / math.sqrt(D), Hq * D + 128)
+    lib.cq_attention_split(wide.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), 0, *args, Hq * D // 32, st)
+    capi.check("split attention")
+    assert int(counters.abs().sum()) == 0
+    q = wide[:, :Hq * D].reshape(B, Tq, Hq, D).double()
+    k = kc.repeat_interleave(Hq // Hkv, dim=1)[:, :, :pos0 + 1].double()
+    v = vc.repeat_interleave(Hq // Hkv, dim=1)[:, :, :pos0 + 1].double()
+    p = torch.softmax(torch.einsum("bthd,bhjd->bhtj", q, k) / math.sqrt(D), dim=-1)
+    ref = torch.einsum("bhtj,bhjd->bthd", p, v).float().reshape(B * Tq, Hq * D)
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+    o8 = torch.full((B * Tq, Hq * D // 32 * 36), 0xCD, dtype=torch.uint8, device=cuda_dev)
+    lib.cq_attention_split(wide.data_ptr(), kc.data_ptr(), vc.data_ptr(), o8.data_ptr(), 1, *args, Hq * D // 32, st)
+    again = torch.empty_like(out)
+    lib.cq_attention_split(wide.data_ptr(), kc.data_ptr(), vc.data_ptr(), again.data_ptr(), 0, *args, Hq * D // 32, st)
+    capi.check("split attention")
+    assert torch.equal(again, out) and int(counters.abs().sum()) == 0
+    assert torch.equal(o8, _quantize_rows(lib, out))
+
+
 def test_glue_kernels_match_torch(lib, cuda_dev):
     """rms_norm (with and without the pending residual), interleaved RoPE + KV store, SwiGLU - against the tensor
     formulas of candle-transformers/src/models/quantized_llama.rs:56-62 and 178-262."""
