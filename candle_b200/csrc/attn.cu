@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const fl
                                                                        const float *__restrict__ vc, void *__restrict__ out,
                                                                        const int *__restrict__ pos, float *__restrict__ scratch,
                                                                        int *__restrict__ counters, int tq, int hq, int hkv, int tmax,
-                                                                       float scale, int q_stride, int out_blocks) {
+                                                                       float scale, int q_stride, int out_blocks, int eager_keys) {
     __shared__ float scores[kChunk];
     __shared__ float red[kSplitWarps];
     __shared__ float4 part[kSplitWarps][32];
@@ -167,42 +167,60 @@ __global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const fl
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     cq_pdl_launch_dependents();
     cq_pdl_wait();
-    int n_ctx = pos[0] + t + 1;
-    if (n_ctx > tmax) n_ctx = tmax;
+    // A decode step is a chain of memory round trips, so loads are issued as early as their addresses are known: with
+    // `eager_keys` (one or two sequences) the keys of the chunk do not wait for the context length - rows up to tmax
+    // exist and surplus ones are masked later, at the price of reading chunks past the context; the values are
+    // requested before the softmax reductions start.
     const int key0 = split * kChunk;
-    if (key0 >= n_ctx) return;                      // the whole CTA: this chunk holds no key of the context
-    const int nk = min(kChunk, n_ctx - key0), nact = (n_ctx + kChunk - 1) / kChunk;
     const int kvh = h / (hq / hkv);
     const float *qp = q + (size_t)bt * q_stride + (size_t)h * kD;
     const float *kp = kc + (((size_t)b * hkv + kvh) * (size_t)tmax + key0) * kD;
     const float *vp = vc + (((size_t)b * hkv + kvh) * (size_t)tmax + key0) * kD;
-
-    {   // scores: one key per group of 8 lanes, 32 keys per pass
-        const int g = tid & 7, grp = tid >> 3;
-        float4 qv[4];
+    int n_ctx = tmax;
+    if (!eager_keys) {
+        n_ctx = min(pos[0] + t + 1, tmax);
+        if (key0 >= n_ctx) return;                  // the whole CTA: this chunk holds no key of the context
+    }
+    const int in_cache = min(kChunk, n_ctx - key0);     // rows of this chunk to fetch (eager: all that exist)
+    const int g = tid & 7, grp = tid >> 3;
+    float4 qv[4], kv[kChunk / 32][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4 *>(qp + 4 * (g + 8 * i));
+    for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4 *>(qp + 4 * (g + 8 * i));
 #pragma unroll
-        for (int j0 = 0; j0 < kChunk; j0 += kSplitThreads / 8) {
-            const int j = j0 + grp;
-            const bool live = j < nk;
-            float4 kv[4];
+    for (int r = 0; r < kChunk / 32; ++r) {
+        const int j = 32 * r + grp;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                kv[i] = live ? *reinterpret_cast<const float4 *>(kp + (size_t)j * kD + 4 * (g + 8 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            float s = 0.0f;
+        for (int i = 0; i < 4; ++i)
+            kv[r][i] = j < in_cache ? *reinterpret_cast<const float4 *>(kp + (size_t)j * kD + 4 * (g + 8 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (eager_keys) {
+        n_ctx = min(pos[0] + t + 1, tmax);
+        if (key0 >= n_ctx) return;
+    }
+    const int nk = min(kChunk, n_ctx - key0), nact = (n_ctx + kChunk - 1) / kChunk;
+    // values: warp w takes keys w, w + 8, ... of the chunk
+    float4 vv[kChunk / kSplitWarps];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                s = __fmaf_rn(qv[i].x, kv[i].x, s);
-                s = __fmaf_rn(qv[i].y, kv[i].y, s);
-                s = __fmaf_rn(qv[i].z, kv[i].z, s);
-                s = __fmaf_rn(qv[i].w, kv[i].w, s);
-            }
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            if (live && g == 0) scores[j] = __fmul_rn(s, scale);
+    for (int i = 0; i < kChunk / kSplitWarps; ++i) {
+        const int j = warp + i * kSplitWarps;
+        vv[i] = j < nk ? *reinterpret_cast<const float4 *>(vp + (size_t)j * kD + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // scores: one key per group of 8 lanes, 32 keys per pass
+#pragma unroll
+    for (int r = 0; r < kChunk / 32; ++r) {
+        const int j = 32 * r + grp;
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s = __fmaf_rn(qv[i].x, kv[r][i].x, s);
+            s = __fmaf_rn(qv[i].y, kv[r][i].y, s);
+            s = __fmaf_rn(qv[i].z, kv[r][i].z, s);
+            s = __fmaf_rn(qv[i].w, kv[r][i].w, s);
         }
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if (j < nk && g == 0) scores[j] = __fmul_rn(s, scale);
     }
     __syncthreads();
     float mx = tid < nk ? scores[tid] : -INFINITY;           // kChunk <= kSplitThreads
@@ -226,27 +244,17 @@ __global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const fl
     sum = red[0];
 #pragma unroll
     for (int w = 1; w < kSplitWarps; ++w) sum += red[w];
-    // weighted values: warp w takes keys w, w + 8, ... in ascending order, four loads in flight
+    // weighted values, keys in ascending order per warp
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int j0 = 0; j0 < kChunk; j0 += 4 * kSplitWarps) {
-        float4 vv[4];
-        float p[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int j = j0 + warp + i * kSplitWarps;
-            const bool live = j < nk;
-            p[i] = live ? scores[j] : 0.0f;
-            vv[i] = live ? *reinterpret_cast<const float4 *>(vp + (size_t)j * kD + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (j0 + warp + i * kSplitWarps < nk) {
-                o.x = __fmaf_rn(p[i], vv[i].x, o.x);
-                o.y = __fmaf_rn(p[i], vv[i].y, o.y);
-                o.z = __fmaf_rn(p[i], vv[i].z, o.z);
-                o.w = __fmaf_rn(p[i], vv[i].w, o.w);
-            }
+    for (int i = 0; i < kChunk / kSplitWarps; ++i) {
+        const int j = warp + i * kSplitWarps;
+        if (j < nk) {           // a skipped key must not turn -0 into +0
+            const float p = scores[j];
+            o.x = __fmaf_rn(p, vv[i].x, o.x);
+            o.y = __fmaf_rn(p, vv[i].y, o.y);
+            o.z = __fmaf_rn(p, vv[i].z, o.z);
+            o.w = __fmaf_rn(p, vv[i].w, o.w);
         }
     }
     part[warp][lane] = o;
@@ -270,17 +278,40 @@ __global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const fl
     __threadfence();
     // combine the chunks in index order (read around L1: other SMs wrote them)
     const float *base = scratch + (size_t)(bt * hq + h) * nsplit * kPartFloats;
-    float big = -INFINITY;
-    for (int s = 0; s < nact; ++s) big = fmaxf(big, __ldcg(base + (size_t)s * kPartFloats + 128));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float den = 0.0f;
-    for (int s = 0; s < nact; ++s) {
-        const float *ps = base + (size_t)s * kPartFloats;
-        const float wgt = expf(__ldcg(ps + 128) - big);
-        const float4 po = __ldcg(reinterpret_cast<const float4 *>(ps + 4 * lane));
-        den = __fmaf_rn(wgt, __ldcg(ps + 129), den);
-        acc.x = __fmaf_rn(wgt, po.x, acc.x); acc.y = __fmaf_rn(wgt, po.y, acc.y);
-        acc.z = __fmaf_rn(wgt, po.z, acc.z); acc.w = __fmaf_rn(wgt, po.w, acc.w);
+    float den = 0.0f, big = -INFINITY;
+    if (nact <= 8) {        // all chunks requested at once
+        float ms[8], ls[8];
+        float4 po[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const float *ps = base + (size_t)s * kPartFloats;
+            const bool liv = s < nact;
+            ms[s] = liv ? __ldcg(ps + 128) : -INFINITY;
+            ls[s] = liv ? __ldcg(ps + 129) : 0.0f;
+            po[s] = liv ? __ldcg(reinterpret_cast<const float4 *>(ps + 4 * lane)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) big = fmaxf(big, ms[s]);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s < nact) {
+                const float wgt = expf(ms[s] - big);
+                den = __fmaf_rn(wgt, ls[s], den);
+                acc.x = __fmaf_rn(wgt, po[s].x, acc.x); acc.y = __fmaf_rn(wgt, po[s].y, acc.y);
+                acc.z = __fmaf_rn(wgt, po[s].z, acc.z); acc.w = __fmaf_rn(wgt, po[s].w, acc.w);
+            }
+        }
+    } else {
+        for (int s = 0; s < nact; ++s) big = fmaxf(big, __ldcg(base + (size_t)s * kPartFloats + 128));
+        for (int s = 0; s < nact; ++s) {
+            const float *ps = base + (size_t)s * kPartFloats;
+            const float wgt = expf(__ldcg(ps + 128) - big);
+            const float4 po = __ldcg(reinterpret_cast<const float4 *>(ps + 4 * lane));
+            den = __fmaf_rn(wgt, __ldcg(ps + 129), den);
+            acc.x = __fmaf_rn(wgt, po.x, acc.x); acc.y = __fmaf_rn(wgt, po.y, acc.y);
+            acc.z = __fmaf_rn(wgt, po.z, acc.z); acc.w = __fmaf_rn(wgt, po.w, acc.w);
+        }
     }
     const float r[4] = {__fdiv_rn(acc.x, den), __fdiv_rn(acc.y, den), __fdiv_rn(acc.z, den), __fdiv_rn(acc.w, den)};
     if constexpr (Q8) {
@@ -348,11 +379,12 @@ extern "C" void cq_attention_split(const float *q, const float *k_cache, const f
         return;
     }
     const dim3 grid(hq, (tmax + kChunk - 1) / kChunk, batch * tq);
+    const int eager = batch * tq <= 2 ? 1 : 0;
     if (out_q8)
         cq_launch_k(attention_split_kernel<true>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos, scratch,
-                    counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks);
+                    counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks, eager);
     else
         cq_launch_k(attention_split_kernel<false>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos,
-                    scratch, counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks);
+                    scratch, counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks, eager);
     cq_check_launch("attention_split");
 }
