@@ -47,6 +47,9 @@ def gemv_bytes(tname: str, k: int, n: int, b: int) -> float:
     return n * k * BYTES_PER_ELEM[tname] + b * k * 4 + b * n * 4
 
 
+DRAM_TRAFFIC_RATIO = 1.014      # measured: (295.52 + 4.57) MB of DRAM traffic for 296.03 MB algorithmic
+
+
 def step_bytes(batches=BATCHES) -> float:
     return sum(gemv_bytes(t, k, n, b) for b in batches for t in TYPE_NAMES for (k, n) in SHAPES)
 
@@ -319,8 +322,12 @@ def run_gpu(args):
         "e2e": {"value": total_bytes / ms_e2e / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
         "roofline": {"bound": "hbm", "achieved": gemv_gbs / world, "peak": peak, "unit": "GB/s",
-                     "frac": gemv_gbs / world / peak, "traffic": None, "peak_source": peak_src,
-                     "kernel": "gemv_staged_kernel (all 60 GEMV launches of the step, quantize launches excluded)",
+                     "frac": gemv_gbs / world / peak, "traffic": DRAM_TRAFFIC_RATIO * total_bytes / world,
+                     "traffic_source": "bytes per step and GPU: algorithmic bytes x 1.014, the ratio of dram__bytes_read+write to "
+                                       "algorithmic bytes in the ncu capture of the Q4_K 4096->128256 launch "
+                                       "(profiles/gemv_staged_q4k_4096x128256_b1.md); the 60 launches of a step are too many to capture",
+                     "peak_source": peak_src,
+                     "kernel": "gemv_staged_kernel / gemv_mma_kernel (all 60 GEMV launches of the step, quantize launches excluded)",
                      "ms_per_step": ms_gemv, "per_gpu": True},
         "clocks": clocks,
         "decode": {"model": "Llama-3-8B-shaped, Q4_K_M mix, random weights", "prompt": 512, "steps": 256,
@@ -454,6 +461,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="with --decode-case: launch decode steps eagerly")
     ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
     ap.add_argument("--no-pdl", action="store_true", help="with --case: plain launches instead of programmatic dependent launches")
+    ap.add_argument("--tune", default=None, help="with --decode-case: RB:CTAS_PER_SM forced for every GEMV (experiment hook)")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
@@ -466,6 +474,10 @@ def main():
     if args.decode_case:
         import torch
         b_, p_, s_ = (int(v) for v in args.decode_case.split(":"))
+        if args.tune:
+            from candle_b200 import capi
+            rb_, cps_ = (int(v) for v in args.tune.split(":"))
+            capi.lib().cq_set_tuning(rb_, cps_)
         torch.cuda.set_device(0)
         print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
     elif args.prefill_case:

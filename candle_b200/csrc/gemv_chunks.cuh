@@ -26,8 +26,8 @@
 // in the same places.
 constexpr int CQ_Q4_K_WIDE = 1012;
 
-// int -> float without the conversion pipe, which dp4a already keeps busy on this GPU: exact for |i| < 2^22, so the
-// result is the one a conversion instruction gives.
+// int -> float with an integer add and a float subtract instead of a conversion instruction: exact for |i| < 2^22,
+// so the result is the one the conversion gives.
 __device__ __forceinline__ float cq_small_int_to_float(int i) { return __int_as_float(i + 0x4B400000) - 12582912.0f; }
 
 template <int TYPE> struct ChunkGeom;

@@ -1,9 +1,9 @@
 // Tensor-core GEMV for up to 8 activation rows (Q4_K, Q6_K, Q8_0 weights, Q8_1 activations).
 //
-// Why: on this GPU `dp4a` issues on the quarter-rate conversion pipe; the dp4a GEMV (gemv_body.cuh) already keeps that
-// pipe 74 % busy with one activation row, so every further row costs time although HBM has room.  Here the integer dot
-// products of 16 weight rows x 8 activation rows x 32 (or 16) elements are one `mma.sync` (s8 x s8 -> s32), whose cost
-// does not depend on how many of the 8 columns are in use.
+// Why: the dp4a GEMV (gemv_body.cuh) spends instructions per (weight byte, activation row): with one row it streams
+// weights at 88 % of the copy bandwidth, with 8 rows it is bound by instruction issue at a fifth of that.  Here the
+// integer dot products of 16 weight rows x 8 activation rows x 32 (or 16) elements are one `mma.sync` (s8 x s8 -> s32),
+// so the cost does not depend on how many of the 8 columns are in use.
 //
 // Results are bit-identical to the dp4a GEMV: the f32 value of every (row, column, chunk) is computed with the same
 // operations as ChunkW<TYPE>::dot (integer parts are exact either way; int -> float conversions are exact in both), and
