@@ -96,6 +96,9 @@ def lib() -> C.CDLL:
         L.cqh_qmatmul_forward.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
         L.cqh_set_act_mode.argtypes = [i32]
         L.cqh_qmatmul_forward_q8_1.argtypes = [vp, vp, i32, vp, vp]
+        L.cqh_qmatmul_forward_q8_1_pair.argtypes = [vp, vp, vp, i32, vp, vp, vp]
+        L.cq_mmvq_pair_q4k_q6k.argtypes = [vp, i32, vp, vp, i32, vp, vp, i32, i32, vp]
+        L.cq_mmvq_pair_q4k_q6k.restype = i32
         L.cqh_indexed_moe_forward.argtypes = [vp, vp, i32, vp, i32, i32, vp, vp]
         L.cqh_get_act_mode.restype = i32
         L.cqh_workspace_reserve.argtypes = [i32, sz]

@@ -119,6 +119,62 @@ bool launch_mma(const void *w, const void *y, void *dst, int out_kind, int K, in
     return cq_check_launch("gemv (tensor core)");
 }
 
+// ---- two matrices that read the same single activation row, one launch (decode: [wq|wk] in Q4_K and wv in Q6_K) ----
+// CTAs [0, grid_a) run the GEMV of matrix A, the rest that of matrix B; each output is computed by the same body as in
+// a launch of its own, so no bit changes.  K is common, so both parts want the same number of threads.
+template <int TA, int TB, int RB>
+__global__ void gemv_pair_kernel(const uint8_t *__restrict__ wa, const uint8_t *__restrict__ wb, const uint8_t *__restrict__ y,
+                                 float *__restrict__ dst_a, float *__restrict__ dst_b, int nchunks, int nrows_a, int nrows_b,
+                                 int stride_col_y, int row_bytes_a, int row_bytes_b, int stage_a, int stage_b, int grid_a) {
+    if ((int)blockIdx.x < grid_a) {
+        const DenseMap map{y, stride_col_y, nrows_a};
+        gemv_body<TA, CQ_ACT_Q8_1, 1, RB>(wa, map, dst_a, CQ_F32, nchunks, nrows_a, row_bytes_a, stage_a, (int)blockIdx.x, grid_a,
+                                          &g_gemv_timeout_flag);
+    } else {
+        const DenseMap map{y, stride_col_y, nrows_b};
+        gemv_body<TB, CQ_ACT_Q8_1, 1, RB>(wb, map, dst_b, CQ_F32, nchunks, nrows_b, row_bytes_b, stage_b, (int)blockIdx.x - grid_a,
+                                          (int)gridDim.x - grid_a, &g_gemv_timeout_flag);
+    }
+}
+
+template <int TA, int TB, int RB>
+bool launch_pair_rb(const void *wa, const void *wb, const void *y, float *da, float *db, int K, int na, int nb, int sy, cudaStream_t st) {
+    static KernelEntry ke{(const void *)gemv_pair_kernel<TA, TB, RB>};
+    const DevInfo di = dev_info();
+    const int nchunks = K / ChunkGeom<TA>::ELEMS, T = (nchunks + 31) / 32 * 32;
+    const int rba = K / cq_block_elems(ChunkGeom<TA>::BASE) * cq_type_size(ChunkGeom<TA>::BASE);
+    const int rbb = K / cq_block_elems(ChunkGeom<TB>::BASE) * cq_type_size(ChunkGeom<TB>::BASE);
+    const int stage_a = cq_gemv_stage_bytes(RB, rba), stage_b = cq_gemv_stage_bytes(RB, rbb);
+    const int smem_a = cq_gemv_smem_bytes(T / 32, cq_next_pow2(RB), stage_a), smem_b = cq_gemv_smem_bytes(T / 32, cq_next_pow2(RB), stage_b);
+    const int smem = smem_a > smem_b ? smem_a : smem_b;
+    if (T > 1024 || smem > di.smem_optin) return false;
+    if (ke.regs == 0) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, ke.fn) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+        ke.regs = fa.numRegs;
+    }
+    int cps = 2048 / T;
+    if (cps > 32) cps = 32;
+    if ((228 * 1024) / (smem + 1024) < cps) cps = (228 * 1024) / (smem + 1024);
+    const int regs_cta = ((ke.regs + 7) & ~7) * T;
+    if (regs_cta > 65536) return false;
+    if (65536 / regs_cta < cps) cps = 65536 / regs_cta;
+    if (cps < 1) cps = 1;
+    const int slots = di.sms * cps;
+    const int batches_a = (na + RB - 1) / RB, batches_b = (nb + RB - 1) / RB;
+    // CTA slots in proportion to the bytes of the two matrices
+    const double share = (double)na * rba / ((double)na * rba + (double)nb * rbb);
+    int grid_a = (int)(slots * share), grid_b = slots - grid_a;
+    if (grid_a < 1) grid_a = 1;
+    if (grid_b < 1) grid_b = 1;
+    if (grid_a > batches_a) grid_a = batches_a;
+    if (grid_b > batches_b) grid_b = batches_b;
+    ensure_smem_attr(&ke);
+    cq_launch_k(gemv_pair_kernel<TA, TB, RB>, dim3(grid_a + grid_b), dim3(T), (size_t)smem, st, (const uint8_t *)wa, (const uint8_t *)wb,
+                (const uint8_t *)y, da, db, nchunks, na, nb, sy, rba, rbb, stage_a, stage_b, grid_a);
+    return cq_check_launch("gemv pair");
+}
+
 size_t elem_bytes(int kind) { return kind == CQ_F32 ? 4 : 2; }
 
 }  // namespace
@@ -185,6 +241,27 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
         if (per == 1) break;
     }
     cq_set_status(CQ_ERR_UNSUPPORTED, "gemv: K too large for one CTA to cover (max 32768 elements; 65536 for Q6_K)");
+}
+
+// One activation row (Q8_1 containers) against a Q4_K matrix A and a Q6_K matrix B of the same K in one launch; f32
+// outputs.  Returns 1 when launched, 0 when the shapes are not covered (the caller then makes two cq_mmvq calls); each
+// output has the bits of a cq_mmvq call of its own.
+extern "C" int cq_mmvq_pair_q4k_q6k(const void *wa, int nrows_a, float *dst_a, const void *wb, int nrows_b, float *dst_b,
+                                    const void *vy, int ncols_x, int stride_col_y, void *stream) {
+    if (!wa || !wb || !dst_a || !dst_b || !vy || nrows_a <= 0 || nrows_b <= 0 || ncols_x <= 0 || ncols_x % 256 != 0 ||
+        stride_col_y * 32 < ncols_x || (uintptr_t)wa % 16 != 0 || (uintptr_t)wb % 2 != 0 || (uintptr_t)vy % 4 != 0)
+        return 0;
+    // rows per batch: the largest of 4, 2, 1 that still gives every CTA slot two batches (as the single-matrix plan does)
+    const DevInfo di = dev_info();
+    const int T = (ncols_x / 64 + 31) / 32 * 32;
+    const long long slots = (long long)di.sms * (2048 / T > 32 ? 32 : 2048 / T);
+    const long long rows = (long long)nrows_a + nrows_b;
+    cudaStream_t st = (cudaStream_t)stream;
+    bool ok;
+    if (rows >= 8 * slots) ok = launch_pair_rb<CQ_Q4_K_WIDE, CQ_Q6_K, 4>(wa, wb, vy, dst_a, dst_b, ncols_x, nrows_a, nrows_b, stride_col_y, st);
+    else if (rows >= 4 * slots) ok = launch_pair_rb<CQ_Q4_K_WIDE, CQ_Q6_K, 2>(wa, wb, vy, dst_a, dst_b, ncols_x, nrows_a, nrows_b, stride_col_y, st);
+    else ok = launch_pair_rb<CQ_Q4_K_WIDE, CQ_Q6_K, 1>(wa, wb, vy, dst_a, dst_b, ncols_x, nrows_a, nrows_b, stride_col_y, st);
+    return ok ? 1 : 0;
 }
 
 extern "C" void cq_set_tuning(int rows_per_batch, int ctas_per_sm) {

@@ -336,6 +336,30 @@ extern "C" int cqh_qmatmul_forward_q8_1(void *handle, const void *act_q8_1, int 
     });
 }
 
+extern "C" int cqh_qmatmul_forward_q8_1_pair(void *handle_a, void *handle_b, const void *act_q8_1, int rows, float *out_a,
+                                             float *out_b, void *stream) {
+    return guarded([&] {
+        auto &ta = *(std::shared_ptr<QTensor> *)handle_a;
+        auto &tb = *(std::shared_ptr<QTensor> *)handle_b;
+        if (ta->rank() != 2 || tb->rank() != 2) throw Error("forward_q8_1_pair expects rank-2 quantized tensors");
+        const auto &sa = ta->shape();
+        const auto &sb = tb->shape();
+        if (sa[1] != sb[1]) throw Error("forward_q8_1_pair: the two matrices must share K");
+        if (rows == 1 && ta->dtype() == GgmlDType::Q4K && tb->dtype() == GgmlDType::Q6K && act_mode() == ActMode::Cuda &&
+            ta->storage().device() == tb->storage().device() && act_q8_1 && out_a && out_b) {
+            DeviceGuard g(ta->storage().device());
+            const int blocks = (int)(pad((size_t)sa[1], MATRIX_ROW_PADDING) / 32);
+            if (cq_mmvq_pair_q4k_q6k(ta->storage().device_ptr(), (int)sa[0], out_a, tb->storage().device_ptr(), (int)sb[0], out_b,
+                                     act_q8_1, (int)sa[1], blocks, stream)) {
+                lib_check("qmatmul pair");
+                return;
+            }
+        }
+        QMatMul(ta).forward_q8_1(act_q8_1, (size_t)rows, out_a, (cudaStream_t)stream);
+        QMatMul(tb).forward_q8_1(act_q8_1, (size_t)rows, out_b, (cudaStream_t)stream);
+    });
+}
+
 extern "C" int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk,
                                        float *out, void *stream) {
     return guarded([&] {

@@ -180,7 +180,7 @@ class LlamaShapedDecoder:
             for L in self.layers:
                 if fused:
                     h = self._norm_q8(x, delta, L.attn_norm)
-                    qk, v = L.wqk.forward_q8_1(h), L.wv.forward_q8_1(h)
+                    qk, v = L.wqk.forward_q8_1_pair(L.wv, h)
                 else:
                     h = self._norm(x, delta, L.attn_norm)
                     qk, v = L.wqk.forward(h), L.wv.forward(h)                           # [R, q_cols + kv_cols], [R, kv_cols]

@@ -19,7 +19,9 @@ _CODE = {GgmlDType.Q8_0: 0, GgmlDType.Q4K: 1, GgmlDType.Q2K: 2, GgmlDType.Q3K: 3
 
 
 def moe_gemm_gguf(xs: torch.Tensor, weights: QTensor, topk_weights: torch.Tensor | None, sorted_token_ids: torch.Tensor,
-                  expert_ids: torch.Tensor, topk: int, is_prefill: bool = False) -> torch.Tensor:
+                  expert_ids: torch.Tensor, topk: int, is_prefill: bool = False, zero_init: bool = False) -> torch.Tensor:
+    """zero_init: start from a zeroed output (pairs whose expert id is out of range are skipped and would otherwise
+    be left uninitialised) - what an expert-parallel rank needs before the pair outputs are summed across ranks."""
     if weights.rank() != 3:
         raise CandleQError("moe_gemm_gguf expects expert weights of rank 3 [experts, n, k]")
     if weights.dtype not in _CODE:
@@ -34,7 +36,7 @@ def moe_gemm_gguf(xs: torch.Tensor, weights: QTensor, topk_weights: torch.Tensor
     sti = sorted_token_ids.to(torch.int32).contiguous()
     eid = expert_ids.to(torch.int32).contiguous()
     tw = None if topk_weights is None else topk_weights.to(torch.float32).contiguous().view(-1)
-    out = torch.empty((size_m, n), dtype=torch.float32, device=xs.device)
+    out = (torch.zeros if zero_init else torch.empty)((size_m, n), dtype=torch.float32, device=xs.device)
     L = capi.lib()
     stream = torch.cuda.current_stream(xs.device).cuda_stream
     with torch.cuda.device(xs.device):

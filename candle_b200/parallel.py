@@ -48,6 +48,8 @@ class Gatherer:
                                torch.empty((rows, self.world * n_local), dtype=local.dtype, device=local.device))
         stacked, full = self._bufs[key]
         dist.all_gather_into_tensor(stacked, local.contiguous(), group=self.group)
+        if rows == 1:       # rank-major slices of a single row are already the gathered row
+            return stacked.view(1, self.world * n_local)
         full.view(rows, self.world, n_local).copy_(stacked.view(self.world, rows, n_local).permute(1, 0, 2))
         return full
 

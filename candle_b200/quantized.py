@@ -220,4 +220,18 @@ class QMatMul:
             capi.hcheck(capi.lib().cqh_qmatmul_forward_q8_1(self.qtensor._h, act.data_ptr(), rows, out.data_ptr(), stream))
         return out
 
+    def forward_q8_1_pair(self, other: "QMatMul", act: torch.Tensor):
+        """`self` and `other` applied to the same Q8_1 containers; one launch when a single row meets a (Q4_K, Q6_K)
+        pair of equal K, two otherwise.  Returns (f32 [rows, n_self], f32 [rows, n_other])."""
+        rows = act.shape[0]
+        if not act.is_cuda or act.dtype != torch.uint8 or not act.is_contiguous() or act.dim() != 2:
+            raise CandleQError("forward_q8_1_pair expects a contiguous uint8 CUDA tensor of Q8_1 containers")
+        out_a = torch.empty((rows, self.qtensor.shape[0]), dtype=torch.float32, device=act.device)
+        out_b = torch.empty((rows, other.qtensor.shape[0]), dtype=torch.float32, device=act.device)
+        stream = torch.cuda.current_stream(act.device).cuda_stream
+        with torch.cuda.device(act.device):
+            capi.hcheck(capi.lib().cqh_qmatmul_forward_q8_1_pair(self.qtensor._h, other.qtensor._h, act.data_ptr(), rows,
+                                                                 out_a.data_ptr(), out_b.data_ptr(), stream))
+        return out_a, out_b
+
     __call__ = forward

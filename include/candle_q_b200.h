@@ -222,6 +222,13 @@ void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *st
  * predecessor in the stream, so their prologue and first weight copies overlap its tail; 0: plain launches. */
 void cq_set_pdl(int on);
 
+/* One activation row (Q8_1 containers, stride_col_y of them) against a Q4_K matrix A [nrows_a, ncols_x] and a Q6_K
+ * matrix B [nrows_b, ncols_x] in a single launch (a decoder's [wq|wk] and wv read the same normalised row); f32
+ * outputs, each with the bits of its own cq_mmvq call.  Returns 1 when launched, 0 when the shapes are not covered
+ * (nothing was launched: call cq_mmvq twice).  No reference counterpart. */
+int cq_mmvq_pair_q4k_q6k(const void *wa, int nrows_a, float *dst_a, const void *wb, int nrows_b, float *dst_b, const void *vy,
+                         int ncols_x, int stride_col_y, void *stream);
+
 /* Rows from which the tensor-core GEMV (mma.sync int8) replaces the dp4a one for Q4_K / Q6_K / Q8_0 weights with
  * Q8_1 activations (0: per-format default, which is 5 for Q4_K / Q6_K and never for Q8_0; 9: never).  Both kernels
  * produce the same bits, so the choice only affects speed. */
@@ -257,6 +264,10 @@ int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t 
  * make them) -> f32 out [rows, n].  No reference counterpart: candle quantizes inside every forward
  * (candle-core/src/quantized/fast_mmvq.rs:201-235).  Fails in the CPU-exact activation mode. */
 int cqh_qmatmul_forward_q8_1(void *handle, const void *act_q8_1, int rows, float *out, void *stream);
+/* Two matmuls over the same pre-quantized activations; a single row against a (Q4_K, Q6_K) pair of equal K goes out as
+ * one launch (cq_mmvq_pair_q4k_q6k), everything else as two cqh_qmatmul_forward_q8_1 calls.  Same bits either way. */
+int cqh_qmatmul_forward_q8_1_pair(void *handle_a, void *handle_b, const void *act_q8_1, int rows, float *out_a, float *out_b,
+                                  void *stream);
 /* QTensor::indexed_moe_forward (candle-core/src/quantized/mod.rs:758-784, cuda.rs:587-622): handle is a rank-3
  * tensor [experts, n, k]; x f32 [batch, topk or 1, k]; ids u32 [batch, topk]; out f32 [batch, topk, n]. */
 int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk, float *out,

@@ -203,6 +203,21 @@ def test_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle, cuda_dev,
     assert lib.cq_device_timeout_flag() == 0
 
 
+@pytest.mark.parametrize("k,na,nb", [(256, 3, 2), (4096, 5120, 1024), (1024, 70, 33), (14336, 40, 24)])
+def test_paired_launch_gives_the_bits_of_two_launches(oracle, cuda_dev, k, na, nb):
+    """QMatMul.forward_q8_1_pair: a Q4_K and a Q6_K matrix over the same Q8_1 row in one launch, and the fall-back to two
+    launches for more rows."""
+    _, x, wa = make_case(oracle, TYPES["q4_k"], k, na, 3, seed=k)
+    _, _, wb = make_case(oracle, TYPES["q6_k"], k, nb, 3, seed=k + 1)
+    ma = QMatMul.from_qtensor(QTensor.from_data(wa.reshape(-1), GgmlDType.Q4K, (na, k), cuda_dev))
+    mb = QMatMul.from_qtensor(QTensor.from_data(wb.reshape(-1), GgmlDType.Q6K, (nb, k), cuda_dev))
+    for rows in (1, 3):
+        q8 = torch.from_numpy(oracle.cuda_quantize_q8_1(x[:rows], pad(k, 512))).to(cuda_dev)
+        ya, yb = ma.forward_q8_1_pair(mb, q8)
+        assert torch.equal(ya, ma.forward_q8_1(q8)) and torch.equal(yb, mb.forward_q8_1(q8))
+        assert torch.equal(ya, ma.forward(torch.from_numpy(x[:rows]).to(cuda_dev)))
+
+
 def test_golden_fixtures(lib, cuda_dev):
     """Committed oracle outputs (tests/golden/make_fixtures.py)."""
     g = np.load(GOLD)

@@ -111,3 +111,62 @@ def test_moe_prefill_entry_point_matches_decode(oracle, cuda_dev):
     a = moe_gemm_gguf(x, qt, None, sp, eo, topk, is_prefill=True)
     b = moe_gemm_gguf(x.float(), qt, None, sp, eo, topk, is_prefill=False)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("is_prefill", [False, True])
+def test_fused_moe_block_matches_per_expert_matmuls(oracle, cuda_dev, is_prefill):
+    """FusedMoeGGUF::forward (candle-transformers/src/fused_moe.rs:222-301) against the same block written with one
+    dense QMatMul per (token, expert): routing, SwiGLU, routing weights, sum over the token's experts.  Then the
+    experts are split over two emulated ranks: pair outputs add up to the same bits."""
+    from candle_b200.fused_moe import FusedMoeGGUF, route
+    from candle_b200.quantized import QMatMul
+    e, topk, hidden, inter, tokens = 8, 2, 512, 256, 6
+    wt = 12
+    g_w = _experts(oracle, wt, e, inter, hidden, seed=1)
+    u_w = _experts(oracle, wt, e, inter, hidden, seed=2)
+    d_w = _experts(oracle, wt, e, hidden, inter, seed=3)
+    mk = lambda w, n, k, lo=0, hi=e: QTensor.from_data(w[lo:hi].reshape(-1), GgmlDType(wt), (hi - lo, n, k), cuda_dev)
+    torch.manual_seed(0)
+    router = torch.randn(e, hidden, device=cuda_dev) * 0.1
+    xs = torch.randn(2, tokens // 2, hidden, device=cuda_dev)
+    moe = FusedMoeGGUF(router, mk(g_w, inter, hidden), mk(u_w, inter, hidden), mk(d_w, hidden, inter), topk, True)
+    ys = moe.forward(xs, is_prefill)
+    assert ys.shape == xs.shape and ys.dtype == xs.dtype
+    # the same block, one dense matmul per pair
+    x = xs.reshape(-1, hidden)
+    tw, ids = route(torch.nn.functional.linear(x, router), topk, True)
+    dense = lambda w, n, k, ex: QMatMul.from_qtensor(QTensor.from_data(w[ex].reshape(-1), GgmlDType(wt), (n, k), cuda_dev))
+    cast = (lambda t: t.to(torch.bfloat16).to(torch.float32)) if is_prefill else (lambda t: t)
+    ref = torch.zeros_like(x)
+    for t in range(tokens):
+        acc = []
+        for s in range(topk):
+            ex = int(ids[t, s])
+            xin = cast(x[t:t + 1])
+            h = dense(u_w, inter, hidden, ex).forward(xin) * torch.nn.functional.silu(dense(g_w, inter, hidden, ex).forward(xin))
+            acc.append(dense(d_w, hidden, inter, ex).forward(cast(h)) * tw[t, s])
+        ref[t] = torch.stack(acc).sum(dim=0)[0]
+    assert rel_err(ys.reshape(-1, hidden).cpu().numpy(), ref.cpu().numpy()) <= 1e-5
+    # two emulated expert-parallel ranks: each owns four experts, pair outputs are added
+    parts = []
+    for r in range(2):
+        m = FusedMoeGGUF(router, mk(g_w, inter, hidden, 4 * r, 4 * r + 4), mk(u_w, inter, hidden, 4 * r, 4 * r + 4),
+                         mk(d_w, hidden, inter, 4 * r, 4 * r + 4), topk, True, expert_offset=4 * r)
+        m.world = 1                      # no process group here: collect the per-rank pair sums by hand
+        parts.append(m)
+    # run each rank's pairs with zero-initialised outputs and add them, as the all-reduce would
+    from candle_b200.fused_moe import sort_pairs
+    from candle_b200.moe import moe_gemm_gguf
+    experts, pairs = sort_pairs(ids)
+    total = None
+    for r, m in enumerate(parts):
+        loc = experts - 4 * r
+        xin = x.to(torch.bfloat16) if is_prefill else x
+        g = moe_gemm_gguf(xin, m.gate_experts, None, pairs, loc, topk, is_prefill, zero_init=True)
+        u = moe_gemm_gguf(xin, m.up_experts, None, pairs, loc, topk, is_prefill, zero_init=True)
+        h = u * torch.nn.functional.silu(g)
+        h = h.to(torch.bfloat16) if is_prefill else h
+        y = moe_gemm_gguf(h, m.down_experts, tw, pairs, loc, topk, is_prefill, zero_init=True)
+        total = y if total is None else total + y
+    ep = total.reshape(tokens, topk, hidden).sum(dim=1)
+    assert torch.equal(ep, ys.reshape(-1, hidden))

@@ -44,3 +44,27 @@ def test_missing_library_is_an_error(monkeypatch, tmp_path):
     monkeypatch.setattr(capi, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(capi.CandleQError, match="no CPU or PyTorch fallback"):
         capi.lib()
+
+
+def test_moe_routing_matches_numpy_restatement():
+    """fused_moe.rs:233-260: softmax, top-k (descending), renormalisation, pairs sorted by expert."""
+    import numpy as np
+    import torch
+    from candle_b200.fused_moe import route, sort_pairs
+    rng = np.random.default_rng(0)
+    logits = rng.standard_normal((7, 16)).astype(np.float32)
+    w, ids = route(torch.from_numpy(logits), 4, True)
+    e = np.exp(logits - logits.max(-1, keepdims=True))
+    p = e / e.sum(-1, keepdims=True)
+    ref_ids = np.argsort(-p, axis=-1, kind="stable")[:, :4]
+    ref_w = np.take_along_axis(p, ref_ids, -1)
+    ref_w = ref_w / ref_w.sum(-1, keepdims=True)
+    assert np.array_equal(ids.numpy(), ref_ids)
+    assert np.allclose(w.numpy(), ref_w, rtol=1e-6, atol=1e-7)
+    w2, _ = route(torch.from_numpy(logits), 4, False)
+    assert np.allclose(w2.numpy(), np.take_along_axis(p, ref_ids, -1), rtol=1e-6, atol=1e-7)
+    experts, pairs = sort_pairs(ids)
+    flat = ref_ids.reshape(-1)
+    assert np.array_equal(experts.numpy(), np.sort(flat, kind="stable"))
+    assert np.array_equal(flat[pairs.numpy()], experts.numpy())          # pair indices in expert order
+    assert sorted(pairs.tolist()) == list(range(flat.size))
