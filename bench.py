@@ -416,6 +416,31 @@ def run_prefill_case(args):
     print(json.dumps({"prefill_case": args.prefill_case, "ms": times, "useful_TOPS": 2.0 * m * n * k / best / 1e9}))
 
 
+def run_dequant_case(args):
+    """De-quantize one tensor: --dequant-case TYPE:N:K, a few launches with CUDA-event times (profiling helper).
+    Bytes = GGUF blocks read + f32 written."""
+    import torch
+    from candle_b200.quantized import GgmlDType, QTensor
+    from candle_b200.synth import random_blocks
+    t, n, k = args.dequant_case.split(":")
+    n, k = int(n), int(k)
+    dev = torch.device("cuda:0")
+    blocks = random_blocks(GgmlDType[t], n, k, seed=1, device=dev)
+    qt = QTensor.from_device_blocks(blocks, GgmlDType[t], (n, k))
+    times = []
+    for _ in range(args.iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = qt.dequantize()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+        del out
+    nbytes = blocks.numel() + 4.0 * n * k
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(json.dumps({"dequant_case": args.dequant_case, "us": times, "bytes": nbytes, "best_GBps": nbytes / best / 1e3}))
+
+
 def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=True):
     """BASELINE configs[3]: Llama-3-8B-shaped Q4_K_M decoder, random prompt of `prompt_len` ids (seed 2), `steps` greedy
     tokens.  Returns (decode tokens/s over all sequences, prompt tokens/s, token checksum)."""
@@ -462,6 +487,7 @@ def main():
     ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
     ap.add_argument("--no-pdl", action="store_true", help="with --case: plain launches instead of programmatic dependent launches")
     ap.add_argument("--tune", default=None, help="with --decode-case: RB:CTAS_PER_SM forced for every GEMV (experiment hook)")
+    ap.add_argument("--dequant-case", default=None, help="profile helper: TYPE:N:K, de-quantizes one tensor to f32")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
@@ -482,6 +508,8 @@ def main():
         print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
     elif args.prefill_case:
         run_prefill_case(args)
+    elif args.dequant_case:
+        run_dequant_case(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

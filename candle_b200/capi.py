@@ -95,6 +95,11 @@ def lib() -> C.CDLL:
         L.cqh_qtensor_device_ptr.restype = vp
         L.cqh_qmatmul_forward.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
         L.cqh_set_act_mode.argtypes = [i32]
+        L.cqh_qtensor_dequantize.argtypes = [vp, vp, i32, vp]
+        L.cqh_qtensor_embedding.argtypes = [vp, vp, i64, vp, i32, vp]
+        L.cq_dequantize.argtypes = [i32, vp, vp, i32, i64, i64, vp]
+        L.cq_get_rows.argtypes = [i32, vp, vp, vp, i32, i64, i64, i64, vp]
+        L.cq_get_rows_bad_id.restype = i32
         L.cqh_qmatmul_forward_q8_1.argtypes = [vp, vp, i32, vp, vp]
         L.cqh_qmatmul_forward_q8_1_pair.argtypes = [vp, vp, vp, i32, vp, vp, vp]
         L.cq_mmvq_pair_q4k_q6k.argtypes = [vp, i32, vp, vp, i32, vp, vp, i32, i32, vp]
@@ -102,6 +107,24 @@ def lib() -> C.CDLL:
         L.cqh_indexed_moe_forward.argtypes = [vp, vp, i32, vp, i32, i32, vp, vp]
         L.cqh_get_act_mode.restype = i32
         L.cqh_workspace_reserve.argtypes = [i32, sz]
+        u64 = C.c_uint64
+        L.cqh_gguf_last_error.restype = C.c_char_p
+        L.cqh_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+        L.cqh_gguf_close.argtypes = [vp]
+        L.cqh_gguf_close.restype = None
+        L.cqh_gguf_version.argtypes = [vp]
+        L.cqh_gguf_tensor_data_offset.argtypes = [vp]
+        L.cqh_gguf_tensor_data_offset.restype = u64
+        L.cqh_gguf_tensor_count.argtypes = [vp]
+        L.cqh_gguf_tensor_count.restype = i64
+        L.cqh_gguf_metadata_json.argtypes = [vp]
+        L.cqh_gguf_metadata_json.restype = C.c_char_p
+        L.cqh_gguf_find_tensor.argtypes = [vp, C.c_char_p]
+        L.cqh_gguf_find_tensor.restype = i64
+        L.cqh_gguf_tensor_info.argtypes = [vp, i64, C.POINTER(C.c_char_p), C.POINTER(i32), i64p, C.POINTER(i32), C.POINTER(u64),
+                                           C.POINTER(u64)]
+        L.cqh_gguf_read_tensor.argtypes = [vp, i64, vp, u64]
+        L.cqh_gguf_load_tensor.argtypes = [vp, i64, i32, i64, i64, C.POINTER(vp)]
         _lib = L
     return _lib
 

@@ -371,6 +371,41 @@ extern "C" int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1,
     });
 }
 
+// QTensor::dequantize / dequantize_f16 (mod.rs:689-710): the whole tensor as f32 / f16 / bf16 on its device.
+extern "C" int cqh_qtensor_dequantize(void *handle, void *out, int out_dtype, void *stream) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        if (!kernels_support(t->dtype())) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(t->dtype()));
+        const auto &sh = t->shape();
+        size_t elems = 1;
+        for (int64_t d : sh) elems *= (size_t)d;
+        if (elems == 0) return;
+        if (!out) throw Error("dequantize: null output pointer");
+        const size_t k = (size_t)sh.back();
+        DeviceGuard g(t->storage().device());
+        cq_dequantize((int)t->dtype(), t->storage().device_ptr(), out, out_dtype, (int64_t)(elems / k), (int64_t)k, stream);
+        lib_check("dequantize");
+    });
+}
+
+// QTensor::embedding (mod.rs:712-748): rows ids[i] of a [rows, hidden] tensor, de-quantized.
+extern "C" int cqh_qtensor_embedding(void *handle, const uint32_t *ids, int64_t n_ids, void *out, int out_dtype, void *stream) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        if (t->rank() != 2) throw Error("embedding expects a rank-2 [rows, hidden] quantized tensor");
+        if (!kernels_support(t->dtype())) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(t->dtype()));
+        const auto &sh = t->shape();
+        if ((size_t)sh[1] % block_size(t->dtype()) != 0)
+            throw Error("quantized embedding hidden size " + std::to_string(sh[1]) + " is not divisible by block size " +
+                        std::to_string(block_size(t->dtype())));
+        if (n_ids <= 0) return;
+        if (!ids || !out) throw Error("embedding: null pointer");
+        DeviceGuard g(t->storage().device());
+        cq_get_rows((int)t->dtype(), t->storage().device_ptr(), (const int32_t *)ids, out, out_dtype, n_ids, sh[0], sh[1], stream);
+        lib_check("embedding");
+    });
+}
+
 extern "C" void cqh_set_act_mode(int mode) { set_act_mode(mode ? ActMode::CpuExact : ActMode::Cuda); }
 extern "C" int cqh_get_act_mode(void) { return (int)act_mode(); }
 

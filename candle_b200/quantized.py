@@ -171,6 +171,32 @@ class QTensor:
                                                             out.data_ptr(), stream))
         return out
 
+    def dequantize(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """``QTensor::dequantize`` / ``dequantize_f16`` (mod.rs:689-710): the tensor as f32 (f16, bf16) on its device."""
+        if dtype not in _ELEM:
+            raise CandleQError(f"Expected f32/f16/bf16, got {dtype}")
+        out = torch.empty(self._shape, dtype=dtype, device=self._device)
+        stream = torch.cuda.current_stream(self._device).cuda_stream
+        with torch.cuda.device(self._device):
+            capi.hcheck(capi.lib().cqh_qtensor_dequantize(self._h, out.data_ptr(), _ELEM[dtype], stream), "QTensor.dequantize")
+        return out
+
+    def embedding(self, ids: torch.Tensor, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """``QTensor::embedding`` (mod.rs:712-748): rows `ids` of a [rows, hidden] tensor -> [*ids.shape, hidden]."""
+        if self.rank() != 2:
+            raise CandleQError("embedding expects a rank-2 [rows, hidden] quantized tensor")
+        flat = ids.to(device=self._device, dtype=torch.int64).reshape(-1)
+        if flat.numel() and (int(flat.min()) < 0 or int(flat.max()) >= self._shape[0]):
+            bad = int(flat[(flat < 0) | (flat >= self._shape[0])][0])
+            raise CandleQError(f"embedding id {bad} is out of range for {self._shape[0]} rows")
+        ids32 = flat.to(torch.int32).contiguous()
+        out = torch.empty((*ids.shape, self._shape[1]), dtype=dtype, device=self._device)
+        stream = torch.cuda.current_stream(self._device).cuda_stream
+        with torch.cuda.device(self._device):
+            capi.hcheck(capi.lib().cqh_qtensor_embedding(self._h, ids32.data_ptr(), ids32.numel(), out.data_ptr(), _ELEM[dtype], stream),
+                        "QTensor.embedding")
+        return out
+
     def matmul_t(self, xs: torch.Tensor) -> torch.Tensor:
         """xs @ self.T, as candle-pyo3's ``QTensor.matmul_t``."""
         return QMatMul.from_qtensor(self).forward(xs)

@@ -234,6 +234,14 @@ int cq_mmvq_pair_q4k_q6k(const void *wa, int nrows_a, float *dst_a, const void *
  * produce the same bits, so the choice only affects speed. */
 void cq_set_mma_min_batch(int rows);
 
+/* De-quantize n_rows rows of k elements (replaces candle-kernels/src/quantized.cu:759-1460 `dequantize_block_*`), and
+ * the gathered-row form behind QTensor::embedding.  cq_get_rows_bad_id: 1 if an id was out of range since the last query
+ * (synchronises the device and clears the flag). */
+void cq_dequantize(int wtype, const void *w, void *out, int out_kind, int64_t n_rows, int64_t k, void *stream);
+void cq_get_rows(int wtype, const void *w, const int32_t *ids, void *out, int out_kind, int64_t n_ids, int64_t n_rows, int64_t k,
+                 void *stream);
+int cq_get_rows_bad_id(void);
+
 /* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
 void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
 /* 1 if a GEMV on the current device gave up a bounded wait for a staged copy (then also sets status 4).
@@ -272,11 +280,37 @@ int cqh_qmatmul_forward_q8_1_pair(void *handle_a, void *handle_b, const void *ac
  * tensor [experts, n, k]; x f32 [batch, topk or 1, k]; ids u32 [batch, topk]; out f32 [batch, topk, n]. */
 int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk, float *out,
                             void *stream);
+/* QTensor::dequantize / dequantize_f16 (candle-core/src/quantized/mod.rs:689-710) and QTensor::embedding (:712-748) for
+ * the four formats: values of the CPU `to_float` bit for bit, as out_dtype (CQ_ELEM_*).  ids: device u32 [n_ids]; an id
+ * outside the tensor gives a row of zeros and is reported by cq_get_rows_bad_id(). */
+int cqh_qtensor_dequantize(void *handle, void *out, int out_dtype, void *stream);
+int cqh_qtensor_embedding(void *handle, const uint32_t *ids, int64_t n_ids, void *out, int out_dtype, void *stream);
 /* 0: Q8_1 activations (candle's CUDA arithmetic, default); 1: activations quantized exactly like candle's CPU path. */
 void cqh_set_act_mode(int mode);
 int cqh_get_act_mode(void);
 /* Grow the per-device scratch ahead of time (it otherwise grows on demand with a synchronising cudaMalloc). */
 int cqh_workspace_reserve(int device, size_t bytes);
+
+/* ------------------------------------------------------------------------------------------------
+ * GGUF container (candle-core/src/quantized/gguf_file.rs:470-581 `Content::read`, :88-119 `TensorInfo::read`).
+ * The file stays memory-mapped while the handle lives; a tensor - or rows [row_start, row_start + row_count) of its
+ * outermost dimension, row_count < 0 meaning all - is copied from the mapping to the device without a host copy and
+ * comes back as a QTensor handle (free it with cqh_qtensor_free).  Dimensions are reported outermost first, as candle
+ * does.  cqh_gguf_metadata_json: all metadata as one JSON object (arrays nested, non-finite floats as null).
+ * Functions returning int give 0 on success, else cqh_gguf_last_error() holds the message (the reference's wording).
+ * ---------------------------------------------------------------------------------------------- */
+const char *cqh_gguf_last_error(void);
+int cqh_gguf_open(const char *path, void **out_handle);
+void cqh_gguf_close(void *handle);
+int cqh_gguf_version(void *handle);
+uint64_t cqh_gguf_tensor_data_offset(void *handle);
+int64_t cqh_gguf_tensor_count(void *handle);
+const char *cqh_gguf_metadata_json(void *handle);
+int64_t cqh_gguf_find_tensor(void *handle, const char *name);
+int cqh_gguf_tensor_info(void *handle, int64_t index, const char **name, int *ggml_dtype, int64_t *dims, int *ndims,
+                         uint64_t *offset, uint64_t *nbytes);
+int cqh_gguf_read_tensor(void *handle, int64_t index, void *host_out, uint64_t nbytes);
+int cqh_gguf_load_tensor(void *handle, int64_t index, int device, int64_t row_start, int64_t row_count, void **out_qtensor);
 
 #ifdef __cplusplus
 }

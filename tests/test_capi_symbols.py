@@ -15,7 +15,7 @@ def declared_functions():
         src = re.sub(r"#define CQ_DECL_\w+\(name\).*?\n(?:.*\\\n)*.*\n", "", src)
         for m in re.finditer(r"CQ_DECL_\w+\((\w+)\);", src):
             names.add(m.group(1))
-        for m in re.finditer(r"^\s*(?:const\s+)?(?:void|int|char|size_t)\s*\*?\s*(\w+)\s*\(", src, flags=re.M):
+        for m in re.finditer(r"^\s*(?:const\s+)?(?:void|int|char|size_t|int64_t|uint64_t)\s*\*?\s*(\w+)\s*\(", src, flags=re.M):
             names.add(m.group(1))
     return sorted(names)
 
