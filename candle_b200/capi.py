@@ -75,6 +75,9 @@ def lib() -> C.CDLL:
         L.cq_silu_mul_q8_1.argtypes = [vp, vp, i32, i32, i32, vp]
         L.cq_attention_q8_1.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]
         L.cq_set_pdl.argtypes = [i32]
+        L.cq_moe_route_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        L.cq_qknorm_rope_store_kv_f32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32,
+                                                  C.c_float, i32, vp]
         L.cq_attention_split_scratch_floats.argtypes = [i32, i32, i32, i32]
         L.cq_attention_split_scratch_floats.restype = C.c_size_t
         L.cq_attention_split.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]

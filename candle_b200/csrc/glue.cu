@@ -127,6 +127,128 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__
     }
 }
 
+// Router of a mixture-of-experts block (candle-transformers/src/fused_moe.rs:233-247): softmax over the experts, the k
+// largest probabilities in descending order (lowest index first among equals), optionally divided by their sum.
+// One warp per token; experts <= 1024.  The softmax sum is added lane-strided, then by an xor butterfly.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int32_t *__restrict__ ids,
+                                                        float *__restrict__ weights, int tokens, int experts, int k, int norm) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= tokens) return;
+    constexpr int PER = 32;                    // experts per lane at most (1024 / 32)
+    float p[PER];
+    const float *row = logits + (size_t)tok * experts;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = lane + 32 * i;
+        p[i] = e < experts ? row[e] : -INFINITY;
+        mx = fmaxf(mx, p[i]);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        p[i] = lane + 32 * i < experts ? expf(p[i] - mx) : 0.0f;
+        sum += p[i];
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) p[i] = lane + 32 * i < experts ? __fdiv_rn(p[i], sum) : -1.0f;      // taken ones become -1 too
+    float chosen = 0.0f, total = 0.0f;         // lane s keeps the probability of slot s (k <= 32)
+    int chosen_id = 0;
+    for (int s = 0; s < k; ++s) {
+        float best = -1.0f;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (p[i] > best) { best = p[i]; best_e = lane + 32 * i; }       // ascending e inside a lane: first maximum wins
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, m);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, m);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if ((best_e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i)
+                if (i == (best_e >> 5)) p[i] = -1.0f;
+        }
+        if (lane == s) { chosen = best; chosen_id = best_e; }
+        total += best;                          // slot order, the same in every lane
+    }
+    if (lane < k) {
+        ids[(size_t)tok * k + lane] = chosen_id;
+        weights[(size_t)tok * k + lane] = norm ? __fdiv_rn(chosen, total) : chosen;
+    }
+}
+
+// Per-head RMSNorm of q and k (weights qw / kw of head_dim values, either may be null), rotary embedding in the
+// non-interleaved form (pairs (i, i + head_dim / 2)) or the interleaved one, then k and v stored into the caches: the
+// attention preamble of candle-transformers/src/models/quantized_qwen3.rs:136-183 in one launch.  head_dim = 128: one warp
+// per (row, head), lane l holds dims 4l..4l+3; the norm's sum of squares is added per lane, then by an xor butterfly.
+__global__ void __launch_bounds__(128) qknorm_rope_store_kernel(float *__restrict__ q, float *__restrict__ k, const float *__restrict__ v,
+                                                                const float *__restrict__ qw, const float *__restrict__ kw,
+                                                                const float *__restrict__ cosv, const float *__restrict__ sinv,
+                                                                const int *__restrict__ pos, float *__restrict__ kc,
+                                                                float *__restrict__ vc, int B, int T, int hq, int hkv, int tmax,
+                                                                int q_stride, int k_stride, int v_stride, float eps, int neox) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    const int64_t unit = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int64_t nq = (int64_t)B * T * hq, nk = (int64_t)B * T * hkv;
+    if (unit >= nq + nk) return;
+    const bool is_q = unit < nq;
+    const int64_t u = is_q ? unit : unit - nq;
+    const int heads = is_q ? hq : hkv;
+    const int hh = (int)(u % heads);
+    const int64_t bt = u / heads;
+    const int t = (int)(bt % T), b = (int)(bt / T);
+    const int p = pos[0] + t;
+    float *src = (is_q ? q : k) + bt * (is_q ? q_stride : k_stride) + (size_t)hh * 128 + 4 * lane;
+    float4 x = *reinterpret_cast<const float4 *>(src);
+    const float *nw = is_q ? qw : kw;
+    if (nw) {
+        float ss = __fmul_rn(x.x, x.x);
+        ss = __fmaf_rn(x.y, x.y, ss); ss = __fmaf_rn(x.z, x.z, ss); ss = __fmaf_rn(x.w, x.w, ss);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, 128.0f), eps));
+        const float4 g = *reinterpret_cast<const float4 *>(nw + 4 * lane);
+        x.x = __fmul_rn(__fmul_rn(x.x, inv), g.x); x.y = __fmul_rn(__fmul_rn(x.y, inv), g.y);
+        x.z = __fmul_rn(__fmul_rn(x.z, inv), g.z); x.w = __fmul_rn(__fmul_rn(x.w, inv), g.w);
+    }
+    float4 r;
+    if (neox) {     // dims i < 64 pair with i + 64, which lane l ^ 16 holds; cos / sin index = i mod 64
+        const float4 o = make_float4(__shfl_xor_sync(0xffffffffu, x.x, 16), __shfl_xor_sync(0xffffffffu, x.y, 16),
+                                     __shfl_xor_sync(0xffffffffu, x.z, 16), __shfl_xor_sync(0xffffffffu, x.w, 16));
+        const float4 c = *reinterpret_cast<const float4 *>(cosv + (size_t)p * 64 + 4 * (lane & 15));
+        const float4 s = *reinterpret_cast<const float4 *>(sinv + (size_t)p * 64 + 4 * (lane & 15));
+        if (lane < 16) {        // x1 * cos - x2 * sin
+            r.x = __fmaf_rn(x.x, c.x, -__fmul_rn(o.x, s.x)); r.y = __fmaf_rn(x.y, c.y, -__fmul_rn(o.y, s.y));
+            r.z = __fmaf_rn(x.z, c.z, -__fmul_rn(o.z, s.z)); r.w = __fmaf_rn(x.w, c.w, -__fmul_rn(o.w, s.w));
+        } else {                // x1 * sin + x2 * cos, with x2 = own value
+            r.x = __fmaf_rn(o.x, s.x, __fmul_rn(x.x, c.x)); r.y = __fmaf_rn(o.y, s.y, __fmul_rn(x.y, c.y));
+            r.z = __fmaf_rn(o.z, s.z, __fmul_rn(x.z, c.z)); r.w = __fmaf_rn(o.w, s.w, __fmul_rn(x.w, c.w));
+        }
+    } else {        // pairs (2i, 2i+1): both inside this lane
+        const float2 c = *reinterpret_cast<const float2 *>(cosv + (size_t)p * 64 + 2 * lane);
+        const float2 s = *reinterpret_cast<const float2 *>(sinv + (size_t)p * 64 + 2 * lane);
+        r.x = __fmaf_rn(x.x, c.x, -__fmul_rn(x.y, s.x)); r.y = __fmaf_rn(x.x, s.x, __fmul_rn(x.y, c.x));
+        r.z = __fmaf_rn(x.z, c.y, -__fmul_rn(x.w, s.y)); r.w = __fmaf_rn(x.z, s.y, __fmul_rn(x.w, c.y));
+    }
+    if (is_q) *reinterpret_cast<float4 *>(src) = r;
+    else if (p < tmax) {
+        const size_t co = (((size_t)b * hkv + hh) * tmax + p) * 128 + 4 * lane;
+        *reinterpret_cast<float4 *>(kc + co) = r;
+        *reinterpret_cast<float4 *>(vc + co) = *reinterpret_cast<const float4 *>(v + bt * v_stride + (size_t)hh * 128 + 4 * lane);
+    }
+}
+
 bool norm_args_ok(const void *x, const void *w, const void *out, int rows, int d, const char *who) {
     if (!x || !w || !out || rows <= 0 || d <= 0 || d % 4) {
         cq_set_status(CQ_ERR_BAD_ARG, who);
@@ -192,4 +314,33 @@ extern "C" void cq_silu_mul_q8_1(const float *gate_up, void *out_q8, int rows, i
     cq_launch_k(silu_mul_kernel<true>, dim3((k_padded / 4 + 255) / 256, rows), dim3(256), 0, (cudaStream_t)stream, gate_up, out_q8, f,
                 k_padded);
     cq_check_launch("silu_mul_q8_1");
+}
+
+extern "C" void cq_moe_route_f32(const float *logits, int32_t *ids, float *weights, int tokens, int experts, int k, int norm_topk_prob,
+                                 void *stream) {
+    if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || experts > 1024 || k <= 0 || k > 32 || k > experts) {
+        cq_set_status(CQ_ERR_BAD_ARG, "moe_route: bad arguments (experts <= 1024, k <= 32)");
+        return;
+    }
+    cq_launch_k(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, ids, weights, tokens, experts, k,
+                norm_topk_prob);
+    cq_check_launch("moe_route");
+}
+
+extern "C" void cq_qknorm_rope_store_kv_f32(float *q, float *k, const float *v, const float *q_norm_w, const float *k_norm_w,
+                                            const float *cosv, const float *sinv, const int *pos, float *k_cache, float *v_cache,
+                                            int batch, int t, int hq, int hkv, int head_dim, int tmax, int q_stride, int k_stride,
+                                            int v_stride, float eps, int neox, void *stream) {
+    if (!q || !k || !v || !cosv || !sinv || !pos || !k_cache || !v_cache || batch <= 0 || t <= 0 || hq <= 0 || hkv <= 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "qknorm_rope: bad arguments");
+        return;
+    }
+    if (head_dim != 128 || q_stride % 4 || k_stride % 4 || v_stride % 4) {
+        cq_set_status(CQ_ERR_UNSUPPORTED, "qknorm_rope: head_dim must be 128 and row strides multiples of 4");
+        return;
+    }
+    const int64_t units = (int64_t)batch * t * (hq + hkv);
+    cq_launch_k(qknorm_rope_store_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, q, k, v, q_norm_w,
+                k_norm_w, cosv, sinv, pos, k_cache, v_cache, batch, t, hq, hkv, tmax, q_stride, k_stride, v_stride, eps, neox);
+    cq_check_launch("qknorm_rope");
 }

@@ -152,9 +152,10 @@ class QTensor:
         capi.hcheck(capi.lib().cqh_qtensor_data(self._h, out.ctypes.data, out.size), "QTensor.data")
         return out.tobytes()
 
-    def indexed_moe_forward(self, x: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    def indexed_moe_forward(self, x: torch.Tensor, ids: torch.Tensor, zero_init: bool = False) -> torch.Tensor:
         """``QTensor::indexed_moe_forward`` (mod.rs:758-784): self is [experts, n, k]; x f32 [batch, topk or 1, k];
-        ids u32/i32 [batch, topk] -> f32 [batch, topk, n]."""
+        ids u32/i32 [batch, topk] -> f32 [batch, topk, n].  Ids outside [0, experts) are skipped; with `zero_init` their
+        output rows read as zero (an expert-parallel rank passes ids shifted by its first expert)."""
         if self.rank() != 3:
             raise CandleQError("indexed_moe_forward expects a rank-3 [experts, n, k] tensor")
         if not x.is_cuda or x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 3:
@@ -164,7 +165,7 @@ class QTensor:
             raise CandleQError(f"mismatch on matmul dim {list(self._shape)} {list(x.shape)}")
         ids32 = ids.to(torch.int32).contiguous()
         topk = ids32.shape[1]
-        out = torch.empty((batch, topk, self._shape[1]), dtype=torch.float32, device=x.device)
+        out = (torch.zeros if zero_init else torch.empty)((batch, topk, self._shape[1]), dtype=torch.float32, device=x.device)
         stream = torch.cuda.current_stream(x.device).cuda_stream
         with torch.cuda.device(x.device):
             capi.hcheck(capi.lib().cqh_indexed_moe_forward(self._h, x.data_ptr(), x_dim1, ids32.data_ptr(), batch, topk,

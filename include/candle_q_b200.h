@@ -217,6 +217,19 @@ void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv,
                           float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
                           int q_stride, int k_stride, int v_stride, void *stream);
 void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream);
+/* Glue of the mixture-of-experts harness.
+ *   cq_moe_route_f32           : softmax over `experts` (<= 1024) logits per token, the k (<= 32) largest probabilities in
+ *                                descending order (lowest expert index among equals) as ids / weights [tokens, k]; with
+ *                                norm_topk_prob the weights are divided by their sum
+ *                                (candle-transformers/src/fused_moe.rs:233-247).
+ *   cq_qknorm_rope_store_kv_f32: optional per-head RMSNorm of q and k (weights of 128 values, null to skip), rotary
+ *                                embedding (neox != 0: pairs (i, i + 64); else (2i, 2i + 1)), k and v stored into the
+ *                                caches - candle-transformers/src/models/quantized_qwen3.rs:136-183.  head_dim 128. */
+void cq_moe_route_f32(const float *logits, int32_t *ids, float *weights, int tokens, int experts, int k, int norm_topk_prob,
+                      void *stream);
+void cq_qknorm_rope_store_kv_f32(float *q, float *k, const float *v, const float *q_norm_w, const float *k_norm_w, const float *cosv,
+                                 const float *sinv, const int *pos, float *k_cache, float *v_cache, int batch, int t, int hq, int hkv,
+                                 int head_dim, int tmax, int q_stride, int k_stride, int v_stride, float eps, int neox, void *stream);
 
 /* 1 (default): decode-path kernels (quantize, GEMV, glue, attention) are launched as programmatic dependents of their
  * predecessor in the stream, so their prologue and first weight copies overlap its tail; 0: plain launches. */

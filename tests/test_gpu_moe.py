@@ -170,3 +170,84 @@ def test_fused_moe_block_matches_per_expert_matmuls(oracle, cuda_dev, is_prefill
         total = y if total is None else total + y
     ep = total.reshape(tokens, topk, hidden).sum(dim=1)
     assert torch.equal(ep, ys.reshape(-1, hidden))
+
+
+def test_route_kernel_matches_the_tensor_formula(cuda_dev):
+    """cq_moe_route_f32 against softmax -> top-k -> renormalise written with tensor ops (fused_moe.rs:233-247)."""
+    from candle_b200.fused_moe import route
+    L = capi.lib()
+    torch.manual_seed(5)
+    for tokens, experts, k, norm in ((1, 128, 8, True), (7, 16, 4, False), (33, 60, 6, True), (2, 1024, 32, True)):
+        logits = torch.randn(tokens, experts, device=cuda_dev) * 2
+        logits[0, 3] = logits[0, 1]                       # a tie: the lower index must come first
+        ids = torch.empty((tokens, k), dtype=torch.int32, device=cuda_dev)
+        w = torch.empty((tokens, k), dtype=torch.float32, device=cuda_dev)
+        L.cq_moe_route_f32(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), tokens, experts, k, 1 if norm else 0,
+                           torch.cuda.current_stream().cuda_stream)
+        capi.check("route")
+        ref_w, ref_ids = route(logits, k, norm)
+        assert torch.equal(ids.long(), ref_ids)
+        assert torch.allclose(w, ref_w, rtol=1e-5, atol=1e-7)
+
+
+def test_qknorm_neox_rope_kernel(cuda_dev):
+    """Per-head RMSNorm + non-interleaved RoPE + KV store against the tensor formulas
+    (candle-transformers/src/models/quantized_qwen3.rs:136-183)."""
+    L = capi.lib()
+    torch.manual_seed(6)
+    B, T, Hq, Hkv, D, Tmax, pos0, eps = 2, 3, 4, 2, 128, 16, 4, 1e-6
+    stride = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(B * T, stride, device=cuda_dev)
+    qkv0 = qkv.clone()
+    qw, kw = torch.rand(D, device=cuda_dev) + 0.5, torch.rand(D, device=cuda_dev) + 0.5
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device=cuda_dev, dtype=torch.float32) / D))
+    ang = torch.arange(32, device=cuda_dev, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc, vc = torch.zeros(B, Hkv, Tmax, D, device=cuda_dev), torch.zeros(B, Hkv, Tmax, D, device=cuda_dev)
+    pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
+    base = qkv.data_ptr()
+    L.cq_qknorm_rope_store_kv_f32(base, base + 4 * Hq * D, base + 4 * (Hq + Hkv) * D, qw.data_ptr(), kw.data_ptr(), cos.data_ptr(),
+                                  sin.data_ptr(), pos.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, T, Hq, Hkv, D, Tmax, stride, stride,
+                                  stride, eps, 1, torch.cuda.current_stream().cuda_stream)
+    capi.check("qknorm rope")
+
+    def ref(x, w):          # x [B, T, H, D] double
+        x = x.double()
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.double()
+        c = cos[pos0:pos0 + T][None, :, None, :].double()
+        s = sin[pos0:pos0 + T][None, :, None, :].double()
+        x1, x2 = x[..., :D // 2], x[..., D // 2:]
+        return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1).float()
+
+    q_ref = ref(qkv0[:, :Hq * D].reshape(B, T, Hq, D), qw)
+    k_ref = ref(qkv0[:, Hq * D:(Hq + Hkv) * D].reshape(B, T, Hkv, D), kw)
+    assert torch.allclose(qkv[:, :Hq * D].reshape(B, T, Hq, D), q_ref, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(kc[:, :, pos0:pos0 + T], k_ref.permute(0, 2, 1, 3), rtol=1e-5, atol=1e-5)
+    assert torch.equal(vc[:, :, pos0:pos0 + T], qkv0[:, (Hq + Hkv) * D:].reshape(B, T, Hkv, D).permute(0, 2, 1, 3))
+    assert torch.equal(qkv[:, Hq * D:], qkv0[:, Hq * D:])            # k and v in the projection output stay as they were
+
+
+def test_moe_decoder_graph_equals_eager(cuda_dev):
+    from candle_b200.moe_decoder import MoeDecoderConfig, MoeShapedDecoder
+    cfg = MoeDecoderConfig.tiny()
+    prompt = torch.randint(0, cfg.vocab, (2, 20), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(2))
+    m = MoeShapedDecoder(cfg, cuda_dev, batch=2, seed=1)
+    eager = m.generate(prompt, 10)
+    assert m.capture_decode_step()
+    assert torch.equal(m.generate(prompt, 10), eager)
+    assert eager.shape == (2, 10) and int(eager.min()) >= 0 and int(eager.max()) < cfg.vocab
+    assert not torch.equal(m.generate((prompt + 1) % cfg.vocab, 10), eager)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_tokens_match_single_gpu(tmp_path):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "ep.txt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(root, "candle_b200", "tp_check.py"), "--moe", "--out", str(out)]
+    r = subprocess.run(cmd, cwd=root, env=dict(os.environ, NCCL_NVLS_ENABLE="0"), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert out.read_text().strip() == "identical"
