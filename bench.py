@@ -416,6 +416,44 @@ def run_prefill_case(args):
     print(json.dumps({"prefill_case": args.prefill_case, "ms": times, "useful_TOPS": 2.0 * m * n * k / best / 1e9}))
 
 
+def moe_decode_tok_s(dev, rank, world, batch, prompt_len=1024, steps=256, use_graph=True):
+    """BASELINE configs[4]: Qwen3-30B-A3B-shaped mixture-of-experts decoder (experts Q4_K, attention and head Q6_K, random
+    weights), expert parallel over `world` ranks: random prompt, then greedy decoding."""
+    import torch
+    import torch.distributed as dist
+    from candle_b200.moe_decoder import MoeDecoderConfig, MoeShapedDecoder
+    cfg = MoeDecoderConfig.qwen3_30b_a3b()
+    m = MoeShapedDecoder(cfg, dev, rank=rank, world=world, batch=batch, seed=1)
+    prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+    m.forward(prompt[:, :min(prompt_len, 64)])      # grows the activation workspace before anything is recorded
+    graphed = m.capture_decode_step() if use_graph else False
+    m.reset()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    tok = m.forward(prompt)
+    e1.record()
+    toks = [tok]
+    for _ in range(steps - 1):
+        tok = m.decode_step(tok).clone()
+        toks.append(tok)
+    e2.record()
+    torch.cuda.synchronize()
+    t_prompt, t_dec = e0.elapsed_time(e1), e1.elapsed_time(e2)
+    if world > 1:
+        t = torch.tensor([t_prompt, t_dec], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_prompt, t_dec = float(t[0]), float(t[1])
+    checksum = int(torch.stack(toks).sum().item())
+    del m
+    torch.cuda.empty_cache()
+    return {"batch": batch, "decode_tok_s": batch * (steps - 1) / t_dec * 1e3, "ms_per_step": t_dec / (steps - 1),
+            "prompt_tok_s": batch * prompt_len / t_prompt * 1e3, "cuda_graph": bool(graphed), "token_checksum": checksum,
+            "active_weight_bytes_per_token": cfg.active_weight_bytes_per_token(), "experts_per_rank": cfg.experts // world}
+
+
 def run_dequant_case(args):
     """De-quantize one tensor: --dequant-case TYPE:N:K, a few launches with CUDA-event times (profiling helper).
     Bytes = GGUF blocks read + f32 written."""
@@ -487,6 +525,8 @@ def main():
     ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
     ap.add_argument("--no-pdl", action="store_true", help="with --case: plain launches instead of programmatic dependent launches")
     ap.add_argument("--tune", default=None, help="with --decode-case: RB:CTAS_PER_SM forced for every GEMV (experiment hook)")
+    ap.add_argument("--moe-decode-case", default=None, help="BATCH:PROMPT:STEPS, runs the mixture-of-experts decoder measurement "
+                    "(under torchrun: expert parallel)")
     ap.add_argument("--dequant-case", default=None, help="profile helper: TYPE:N:K, de-quantizes one tensor to f32")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
@@ -508,6 +548,20 @@ def main():
         print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
     elif args.prefill_case:
         run_prefill_case(args)
+    elif args.moe_decode_case:
+        import torch
+        import torch.distributed as dist
+        b_, p_, s_ = (int(v) for v in args.moe_decode_case.split(":"))
+        world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        res = moe_decode_tok_s(torch.device(f"cuda:{local}"), rank, world, b_, p_, s_, use_graph=not args.no_graph)
+        if rank == 0:
+            print(json.dumps(dict(res, n_gpus=world)))
+        if world > 1:
+            dist.destroy_process_group()
     elif args.dequant_case:
         run_dequant_case(args)
     elif args.case:
