@@ -61,6 +61,9 @@ def lib() -> C.CDLL:
         L.cq_moe_gemv_sorted.argtypes = [i32, i32, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_indexed_moe_forward.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
         L.cq_moe_timeout_flag.restype = i32
+        L.cq_moe_prefill_scratch_bytes.argtypes = [i32, i32, i32]
+        L.cq_moe_prefill_scratch_bytes.restype = C.c_size_t
+        L.cq_moe_prefill_gemm.argtypes = [i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_mmq_timeout_flag.restype = i32
         for lay in ("D4", "DS4", "D2S6"):
             getattr(L, f"launch_mmq_quantize_q8_1_{lay}").argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, i64, i64, i64, vp]

@@ -104,12 +104,13 @@ __global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, 
 // out[r, i] = silu(gu[r, i]) * gu[r, f + i]   with gu = [gate | up] rows of width 2f;  silu(x) = x / (1 + exp(-x)).
 // One thread per four consecutive outputs; f a multiple of 4 (of 32 for Q8).  grid (ceil(n4 / 256), rows).
 template <bool Q8>
-__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, void *__restrict__ out, int f, int k_padded) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__ gu, void *__restrict__ out, int f, int k_padded,
+                                                       int rows) {
     cq_pdl_launch_dependents();
     cq_pdl_wait();
-    const int r = blockIdx.y;
     const int i = blockIdx.x * 256 + threadIdx.x;       // float4 index inside the row
     const int n4 = f >> 2, n4_out = Q8 ? (k_padded >> 2) : n4;
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {  // rows beyond the grid limit are walked by the same CTAs
     float o[4] = {0.f, 0.f, 0.f, 0.f};
     if (i < n4) {
         const float4 g = reinterpret_cast<const float4 *>(gu + (size_t)r * 2 * f)[i];
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__
     } else if (i < n4) {
         reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)r * f)[i] = make_float4(o[0], o[1], o[2], o[3]);
     }
+  }
 }
 
 // Router of a mixture-of-experts block (candle-transformers/src/fused_moe.rs:233-247): softmax over the experts, the k
@@ -298,21 +300,22 @@ extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const f
 }
 
 extern "C" void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream) {
-    if (!gate_up || !out || rows <= 0 || rows > 65535 || f <= 0 || f % 4) {
-        cq_set_status(CQ_ERR_BAD_ARG, "silu_mul: bad arguments (f must be a multiple of 4, at most 65535 rows)");
+    if (!gate_up || !out || rows <= 0 || f <= 0 || f % 4) {
+        cq_set_status(CQ_ERR_BAD_ARG, "silu_mul: bad arguments (f must be a multiple of 4)");
         return;
     }
-    cq_launch_k(silu_mul_kernel<false>, dim3((f / 4 + 255) / 256, rows), dim3(256), 0, (cudaStream_t)stream, gate_up, out, f, f);
+    cq_launch_k(silu_mul_kernel<false>, dim3((f / 4 + 255) / 256, rows < 65535 ? rows : 65535), dim3(256), 0, (cudaStream_t)stream, gate_up,
+                out, f, f, rows);
     cq_check_launch("silu_mul");
 }
 
 extern "C" void cq_silu_mul_q8_1(const float *gate_up, void *out_q8, int rows, int f, int k_padded, void *stream) {
-    if (!gate_up || !out_q8 || rows <= 0 || rows > 65535 || f <= 0 || f % 32 || k_padded < f || k_padded % 32) {
-        cq_set_status(CQ_ERR_BAD_ARG, "silu_mul_q8_1: bad arguments (f and k_padded multiples of 32, at most 65535 rows)");
+    if (!gate_up || !out_q8 || rows <= 0 || f <= 0 || f % 32 || k_padded < f || k_padded % 32) {
+        cq_set_status(CQ_ERR_BAD_ARG, "silu_mul_q8_1: bad arguments (f and k_padded multiples of 32)");
         return;
     }
-    cq_launch_k(silu_mul_kernel<true>, dim3((k_padded / 4 + 255) / 256, rows), dim3(256), 0, (cudaStream_t)stream, gate_up, out_q8, f,
-                k_padded);
+    cq_launch_k(silu_mul_kernel<true>, dim3((k_padded / 4 + 255) / 256, rows < 65535 ? rows : 65535), dim3(256), 0, (cudaStream_t)stream,
+                gate_up, out_q8, f, k_padded, rows);
     cq_check_launch("silu_mul_q8_1");
 }
 

@@ -194,12 +194,30 @@ extern "C" void moe_gemm_gguf(const float *input, const void *weights, const int
 
 // candle-kernels/src/ffi.rs:41-56: f16 (input_dtype 0) or bf16 (1) activations, f32 output.  The reference
 // de-quantizes the expert weights to half precision and multiplies with wmma (candle-kernels/src/moe/
-// moe_wmma_gguf.cu:124-300); this entry point instead uses the same integer arithmetic as the decode entry point
-// (activations to Q8_1), so a token gives the same result whether it arrives in a prompt or in a decode step.
+// moe_wmma_gguf.cu:124-300).  Here Q4_K / Q6_K experts with at least kMoePrefillMinPairs pairs go to the grouped
+// tensor-core kernel (cq_moe_prefill_gemm: int8 tcgen05 MMAs over Q8_K activations, the CPU path's arithmetic); fewer
+// pairs, and Q8_0 experts, take the integer GEMV of the decode entry point.
+constexpr int kMoePrefillMinPairs = 64;
 extern "C" void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int32_t *sorted_token_ids,
                                       const int32_t *expert_ids, const float *topk_weights, void *output, int num_experts,
                                       int topk, int size_m, int size_n, int size_k, int input_dtype, int gguf_dtype,
                                       int64_t stream) {
+    const int wtype = wtype_of_moe_code(gguf_dtype);
+    cudaStream_t st = (cudaStream_t)(uintptr_t)stream;
+    if ((wtype == CQ_Q4_K || wtype == CQ_Q6_K) && size_m >= kMoePrefillMinPairs && size_k % 256 == 0 && num_experts <= 1024 && input &&
+        output) {
+        const size_t need = cq_moe_prefill_scratch_bytes(size_m, num_experts, size_k);
+        void *scratch = nullptr;
+        if (need == 0 || cudaMallocAsync(&scratch, need, st) != cudaSuccess) {
+            (void)cudaGetLastError();
+            cq_set_status(CQ_ERR_CUDA, "moe_gemm_gguf_prefill: cudaMallocAsync failed");
+            return;
+        }
+        cq_moe_prefill_gemm(wtype, input, input_dtype == 0 ? CQ_F16 : CQ_BF16, weights, sorted_token_ids, expert_ids, topk_weights,
+                            (float *)output, scratch, num_experts, topk, size_m, size_n, size_k, st);
+        cudaFreeAsync(scratch, st);
+        return;
+    }
     moe_ffi(input, input_dtype == 0 ? CQ_F16 : CQ_BF16, weights, sorted_token_ids, expert_ids, topk_weights, output, num_experts,
             topk, size_m, size_n, size_k, gguf_dtype, (cudaStream_t)(uintptr_t)stream);
 }

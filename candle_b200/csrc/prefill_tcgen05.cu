@@ -134,18 +134,12 @@ struct TileBlob {   // where the activations of (token tile, super-block) live i
 // ---- activation quantize into tensor-core tiles ---------------------------------------------------------
 // One warp per (token, super-block): BlockQ8K values (see quantize_act.cu for the rules), written so that the
 // bytes of 8 consecutive tokens x 16 consecutive k form one 128-byte core matrix.
+// `xr`: the 8 values of this lane (null: a padding row of zeros); the result goes to token slot `tl` of the tile blob.
 template <typename T>
-__global__ void __launch_bounds__(256) quantize_q8k_tiles_kernel(const T *__restrict__ x, uint8_t *__restrict__ y, int k,
-                                                                 int tokens) {
-    const int lane = threadIdx.x & 31;
-    const int nsb = k / 256;
-    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (item >= (int64_t)tokens * nsb) return;
-    const int tok = (int)(item / nsb), sb = (int)(item % nsb);
-    const T *xr = x + (int64_t)tok * k + sb * 256 + lane * 8;
+__device__ __forceinline__ void quantize_q8k_row_part(const T *xr, uint8_t *blob, size_t rows, int tl, int lane) {
     float e[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) e[c] = cq_elem_to_float(xr, c);
+    for (int c = 0; c < 8; ++c) e[c] = xr ? cq_elem_to_float(xr, c) : 0.0f;
     float amax = 0.0f, vmax = 0.0f;
     int imax = 0x7fffffff;
 #pragma unroll
@@ -173,15 +167,91 @@ __global__ void __launch_bounds__(256) quantize_q8k_tiles_kernel(const T *__rest
         }
         d = __fdiv_rn(1.0f, iscale);
     }
-    const int tt = tok / kTokTile, tl = tok % kTokTile;
-    const size_t rows = TileBlob::tile_rows(tokens, tt);
-    uint8_t *blob = y + TileBlob::offset(tokens, nsb, tt, sb);
     // lane holds k bytes [8*lane, 8*lane+8): slab lane/2, byte offset 8*(lane&1) inside the token's 16 bytes
     int2 packed;
     packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
     packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
     *reinterpret_cast<int2 *>(blob + (size_t)(lane >> 1) * rows * 16 + (size_t)tl * 16 + 8 * (lane & 1)) = packed;
     if (lane == 0) *reinterpret_cast<float *>(blob + rows * 256 + (size_t)tl * 4) = d;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_q8k_tiles_kernel(const T *__restrict__ x, uint8_t *__restrict__ y, int k,
+                                                                 int tokens) {
+    const int lane = threadIdx.x & 31;
+    const int nsb = k / 256;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (int64_t)tokens * nsb) return;
+    const int tok = (int)(item / nsb), sb = (int)(item % nsb);
+    const int tt = tok / kTokTile, tl = tok % kTokTile;
+    quantize_q8k_row_part<T>(x + (int64_t)tok * k + sb * 256 + lane * 8, y + TileBlob::offset(tokens, nsb, tt, sb),
+                             TileBlob::tile_rows(tokens, tt), tl, lane);
+}
+
+// ---- grouped (expert-indexed) mode ------------------------------------------------------------------------
+// Jobs m = 0..M-1 are (token, expert) pairs sorted by expert (candle-nn/src/moe.rs:286-337): pair = sorted_token_ids[m],
+// expert = expert_ids[m]; input row = pair when routing weights are given, else pair / topk; output row = pair, scaled
+// by topk_weights[pair] when given.  The jobs of one expert are cut into tiles of 128; a table of (expert, first job,
+// valid rows) per tile is built on the device (the host never sees the routing), over-sized to ceil(M / 128) + experts
+// tiles; tiles past the last one have zero valid rows and their CTAs leave at once.
+struct GroupInfo {
+    const int *tiles;                  // [max_tiles][4]: expert, first job, valid rows, 0; null: dense mode
+    const int32_t *sorted_token_ids;
+    const float *topk_weights;
+    long long expert_stride;           // bytes between experts
+    int topk;
+};
+
+// One CTA.  expert_ids ascending (ids outside [0, num_experts) - another rank's experts - may sit at either end).
+__global__ void __launch_bounds__(1024) moe_tiles_kernel(const int32_t *__restrict__ expert_ids, int m, int num_experts,
+                                                         int max_tiles, int *__restrict__ tiles) {
+    __shared__ int start[1025], first_tile[1025];
+    const int tid = threadIdx.x;
+    for (int e = tid; e <= num_experts; e += 1024) {       // start[e] = first job whose expert is >= e
+        int lo = 0, hi = m;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (expert_ids[mid] < e) lo = mid + 1; else hi = mid;
+        }
+        start[e] = lo;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int t = 0;
+        for (int e = 0; e < num_experts; ++e) { first_tile[e] = t; t += (start[e + 1] - start[e] + kTokTile - 1) / kTokTile; }
+        first_tile[num_experts] = t;
+    }
+    __syncthreads();
+    for (int e = tid; e < num_experts; e += 1024) {
+        const int cnt = start[e + 1] - start[e];
+        for (int j = 0; j * kTokTile < cnt; ++j) {
+            int *t = tiles + 4 * (first_tile[e] + j);
+            t[0] = e; t[1] = start[e] + j * kTokTile; t[2] = min(kTokTile, cnt - j * kTokTile); t[3] = 0;
+        }
+    }
+    for (int t = first_tile[num_experts] + tid; t < max_tiles; t += 1024) { tiles[4 * t] = 0; tiles[4 * t + 1] = 0; tiles[4 * t + 2] = 0; tiles[4 * t + 3] = 0; }
+}
+
+// One warp per (tile row, super-block): the input row of that job, or zeros for the padding rows of a tile.
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_q8k_tiles_grouped_kernel(const T *__restrict__ x, uint8_t *__restrict__ y, int k,
+                                                                         int max_tiles, GroupInfo gi) {
+    const int lane = threadIdx.x & 31;
+    const int nsb = k / 256;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (int64_t)max_tiles * kTokTile * nsb) return;
+    const int sb = (int)(item % nsb);
+    const int64_t slot = item / nsb;
+    const int tt = (int)(slot / kTokTile), tl = (int)(slot % kTokTile);
+    const int *ti = gi.tiles + 4 * tt;
+    if (ti[2] == 0) return;                                 // unused tile: nobody reads its blob
+    const T *xr = nullptr;
+    if (tl < ti[2]) {
+        const int pair = gi.sorted_token_ids[ti[1] + tl];
+        const int64_t in_row = gi.topk_weights ? pair : pair / gi.topk;
+        xr = x + in_row * k + sb * 256 + lane * 8;
+    }
+    quantize_q8k_row_part<T>(xr, y + TileBlob::offset(max_tiles * kTokTile, nsb, tt, sb), kTokTile, tl, lane);
 }
 
 // ---- weight planes -----------------------------------------------------------------------------------------
@@ -308,8 +378,18 @@ template <> struct RawBlock<CQ_Q6_K> {
 template <int WTYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, void *__restrict__ out_v, int out_kind, int k,
-                   int nrows, int tokens, int stride_out, int dbg) {
+                   int nrows, int tokens, int stride_out, int dbg, const GroupInfo gi) {
     extern __shared__ __align__(1024) uint8_t smem[];
+    // grouped mode: this CTA's token tile belongs to one expert; `tokens` is then max_tiles * 128 (every tile is stored
+    // full-size) and rows past `valid` are padding
+    int valid = kTokTile, job0 = 0;
+    if (gi.tiles) {
+        const int *ti = gi.tiles + 4 * blockIdx.y;
+        valid = ti[2];
+        if (valid == 0) return;                             // the whole CTA, before any barrier or TMEM allocation
+        w += (long long)ti[0] * gi.expert_stride;
+        job0 = ti[1];
+    }
     uint64_t *bar_fullA = reinterpret_cast<uint64_t *>(smem);         // [3] activations landed (TMA bytes)
     uint64_t *bar_fullB = bar_fullA + 3;                               // [2] weight planes written (128 producer threads)
     uint64_t *bar_acc = bar_fullA + 5;                                 // [2] MMAs of a super-block complete
@@ -468,12 +548,26 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
             tc_fence_before();
             mbar_arrive(&bar_free[s]);
         }
-        if (alive && tok < tokens && out_kind != CQ_F32) {
+        bool store = alive && tok < tokens;
+        int64_t orow = tok;
+        if (gi.tiles) {         // output row = the pair of this job, scaled by its routing weight
+            store = alive && tok_local < valid;
+            if (store) {
+                const int pair = gi.sorted_token_ids[job0 + tok_local];
+                orow = pair;
+                if (gi.topk_weights) {
+                    const float sc = gi.topk_weights[pair];
+#pragma unroll
+                    for (int i = 0; i < kRowTile; ++i) acc[i] = __fmul_rn(acc[i], sc);
+                }
+            }
+        }
+        if (store && out_kind != CQ_F32) {
 #pragma unroll
             for (int i = 0; i < kRowTile; ++i)
-                if (row0 + i < nrows) cq_store_out(out_v, out_kind, (int64_t)tok * stride_out + row0 + i, acc[i]);
-        } else if (alive && tok < tokens) {
-            float *o = (float *)out_v + (size_t)tok * stride_out + row0;
+                if (row0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + row0 + i, acc[i]);
+        } else if (store) {
+            float *o = (float *)out_v + (size_t)orow * stride_out + row0;
             if (row0 + kRowTile <= nrows && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
                 for (int i = 0; i < kRowTile; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
@@ -540,11 +634,76 @@ extern "C" void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, 
     const dim3 grid((nrows_x + kRowTile - 1) / kRowTile, (tokens + kTokTile - 1) / kTokTile);
     if (ti == 0)
         prefill_kernel<CQ_Q4_K><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(
-            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg);
+            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg, GroupInfo{});
     else
         prefill_kernel<CQ_Q6_K><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(
-            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg);
+            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg, GroupInfo{});
     cq_check_launch("prefill gemm");
+}
+
+// ---- grouped entry points (quantized mixture-of-experts, many tokens) ----
+namespace {
+int moe_max_tiles(int size_m, int num_experts) { return (size_m + kTokTile - 1) / kTokTile + num_experts; }
+size_t moe_table_bytes(int max_tiles) { return ((size_t)max_tiles * 16 + 255) / 256 * 256; }
+}  // namespace
+
+extern "C" size_t cq_moe_prefill_scratch_bytes(int size_m, int num_experts, int k) {
+    if (size_m <= 0 || num_experts <= 0 || num_experts > 1024 || k <= 0 || k % 256 != 0) return 0;
+    const int mt = moe_max_tiles(size_m, num_experts);
+    return moe_table_bytes(mt) + (size_t)mt * kTokTile * 260 * (k / 256) + 256;
+}
+
+// out[pair, :] = W[expert of the pair] . x[input row of the pair] (times topk_weights[pair]) for all size_m sorted pairs, on
+// the tensor cores.  Same job rules as moe_gemm_gguf; arithmetic of the dense prefill kernel (Q8_K activations).
+// `scratch`: cq_moe_prefill_scratch_bytes(size_m, num_experts, size_k) bytes.  Rows of pairs whose expert id is outside
+// [0, num_experts) are not written.
+extern "C" void cq_moe_prefill_gemm(int wtype, const void *input, int in_elem, const void *weights, const int32_t *sorted_token_ids,
+                                    const int32_t *expert_ids, const float *topk_weights, float *out, void *scratch, int num_experts,
+                                    int topk, int size_m, int size_n, int size_k, void *stream) {
+    if (!input || !weights || !sorted_token_ids || !expert_ids || !out || !scratch || num_experts <= 0 || num_experts > 1024 ||
+        topk <= 0 || size_m <= 0 || size_n <= 0 || size_k <= 0 || size_k % 256 != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "moe prefill: null pointer, empty shape, more than 1024 experts or K not a multiple of 256");
+        return;
+    }
+    if (wtype != CQ_Q4_K && wtype != CQ_Q6_K) {
+        cq_set_status(CQ_ERR_UNSUPPORTED, "moe prefill: the tensor-core kernel covers Q4_K and Q6_K");
+        return;
+    }
+    const long long expert_stride = (long long)size_n * (size_k / 256) * cq_type_size(wtype);
+    if ((uintptr_t)weights % 16 != 0 || (uintptr_t)scratch % 256 != 0 || (wtype == CQ_Q4_K ? expert_stride % 16 : expert_stride % 4) != 0) {
+        cq_set_status(CQ_ERR_BAD_ARG, "moe prefill: misaligned weights or scratch");
+        return;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const int mt = moe_max_tiles(size_m, num_experts);
+    int *tiles = (int *)scratch;
+    uint8_t *blobs = (uint8_t *)scratch + moe_table_bytes(mt);
+    moe_tiles_kernel<<<1, 1024, 0, st>>>(expert_ids, size_m, num_experts, mt, tiles);
+    const GroupInfo gi{tiles, sorted_token_ids, topk_weights, expert_stride, topk};
+    const int64_t items = (int64_t)mt * kTokTile * (size_k / 256);
+    const unsigned qgrid = (unsigned)((items + 7) / 8);
+    if (in_elem == CQ_F32) quantize_q8k_tiles_grouped_kernel<float><<<qgrid, 256, 0, st>>>((const float *)input, blobs, size_k, mt, gi);
+    else if (in_elem == CQ_F16) quantize_q8k_tiles_grouped_kernel<__half><<<qgrid, 256, 0, st>>>((const __half *)input, blobs, size_k, mt, gi);
+    else if (in_elem == CQ_BF16)
+        quantize_q8k_tiles_grouped_kernel<__nv_bfloat16><<<qgrid, 256, 0, st>>>((const __nv_bfloat16 *)input, blobs, size_k, mt, gi);
+    else { cq_set_status(CQ_ERR_BAD_ARG, "moe prefill: unknown input element type"); return; }
+    static bool attr_done[2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int ti = wtype == CQ_Q4_K ? 0 : 1;
+    if (dev >= 0 && dev < 64 && !attr_done[ti][dev]) {
+        if (ti == 0) cudaFuncSetAttribute(prefill_kernel<CQ_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        else cudaFuncSetAttribute(prefill_kernel<CQ_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        attr_done[ti][dev] = true;
+    }
+    const dim3 grid((size_n + kRowTile - 1) / kRowTile, mt);
+    if (ti == 0)
+        prefill_kernel<CQ_Q4_K><<<grid, kThreads, kSmemBytes, st>>>((const uint8_t *)weights, blobs, out, CQ_F32, size_k, size_n,
+                                                                     mt * kTokTile, size_n, g_prefill_dbg, gi);
+    else
+        prefill_kernel<CQ_Q6_K><<<grid, kThreads, kSmemBytes, st>>>((const uint8_t *)weights, blobs, out, CQ_F32, size_k, size_n,
+                                                                     mt * kTokTile, size_n, g_prefill_dbg, gi);
+    cq_check_launch("moe prefill gemm");
 }
 
 extern "C" void cq_prefill_set_debug(int flags) { g_prefill_dbg = flags; }

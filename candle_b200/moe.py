@@ -54,3 +54,31 @@ def moe_gemm_gguf(xs: torch.Tensor, weights: QTensor, topk_weights: torch.Tensor
                             _CODE[weights.dtype], stream)
     capi.check("moe_gemm_gguf")
     return out
+
+
+def moe_prefill_gemm(xs: torch.Tensor, weights: QTensor, topk_weights: torch.Tensor | None, sorted_token_ids: torch.Tensor,
+                     expert_ids: torch.Tensor, topk: int, zero_init: bool = False) -> torch.Tensor:
+    """The grouped tensor-core GEMM (``cq_moe_prefill_gemm``) with the argument meaning of ``moe_gemm_gguf``; xs may be f32,
+    f16 or bf16.  Q4_K / Q6_K experts only."""
+    if weights.rank() != 3 or weights.dtype not in (GgmlDType.Q4K, GgmlDType.Q6K):
+        raise CandleQError("moe_prefill_gemm expects Q4K or Q6K expert weights of rank 3 [experts, n, k]")
+    num_experts, n, k = weights.shape
+    if xs.dim() != 2 or xs.shape[1] != k or not xs.is_cuda or not xs.is_contiguous():
+        raise CandleQError(f"moe_prefill_gemm: input must be a contiguous CUDA matrix [rows, {k}]")
+    elem = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}.get(xs.dtype)
+    if elem is None:
+        raise CandleQError(f"Expected f32/f16/bf16, got {xs.dtype}")
+    size_m = sorted_token_ids.numel()
+    if topk_weights is None and xs.shape[0] * topk != size_m or topk_weights is not None and xs.shape[0] != size_m:
+        raise CandleQError("moe_prefill_gemm: input rows do not match the number of (token, expert) pairs")
+    sti, eid = sorted_token_ids.to(torch.int32).contiguous(), expert_ids.to(torch.int32).contiguous()
+    tw = None if topk_weights is None else topk_weights.to(torch.float32).contiguous().view(-1)
+    out = (torch.zeros if zero_init else torch.empty)((size_m, n), dtype=torch.float32, device=xs.device)
+    L = capi.lib()
+    scratch = torch.empty(L.cq_moe_prefill_scratch_bytes(size_m, num_experts, k), dtype=torch.uint8, device=xs.device)
+    with torch.cuda.device(xs.device):
+        L.cq_moe_prefill_gemm(int(weights.dtype), xs.data_ptr(), elem, weights.device_ptr(), sti.data_ptr(), eid.data_ptr(),
+                              tw.data_ptr() if tw is not None else None, out.data_ptr(), scratch.data_ptr(), num_experts, topk, size_m,
+                              n, k, torch.cuda.current_stream(xs.device).cuda_stream)
+    capi.check("moe_prefill_gemm")
+    return out

@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from . import capi
 from .decoder import LlamaShapedDecoder
+from .moe import moe_prefill_gemm
 from .quantized import GgmlDType, QMatMul, QTensor
 from .synth import random_blocks
 
@@ -146,10 +147,17 @@ class MoeShapedDecoder:
         lib.cq_moe_route_f32(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), R, cfg.experts, k, 1 if cfg.norm_topk_prob else 0, st)
         local = ids - self.e0 if self.world > 1 else ids           # other ranks' experts fall outside [0, e_local): skipped
         zero = self.world > 1
-        gu = L.gate_up.indexed_moe_forward(h.view(R, 1, -1), local, zero_init=zero)               # [R, k, 2f]
         a = torch.empty((R, k, f), dtype=torch.float32, device=self.device)
-        lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
-        y = L.down.indexed_moe_forward(a, local, zero_init=zero)                                  # [R, k, d]
+        if R * k >= 64:         # prompt: pairs sorted by expert, grouped GEMM on the tensor cores
+            experts, pairs = torch.sort(local.reshape(-1), stable=True)
+            gu = moe_prefill_gemm(h, L.gate_up, None, pairs, experts, k, zero_init=zero)          # [R * k, 2f]
+            lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
+            y = moe_prefill_gemm(a.view(R * k, f), L.down, torch.ones(R * k, device=self.device), pairs, experts, k,
+                                 zero_init=zero).view(R, k, -1)
+        else:
+            gu = L.gate_up.indexed_moe_forward(h.view(R, 1, -1), local, zero_init=zero)           # [R, k, 2f]
+            lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
+            y = L.down.indexed_moe_forward(a, local, zero_init=zero)                              # [R, k, d]
         if self.world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)                            # one value plus zeros: exact
         return (y * w.unsqueeze(-1)).sum(dim=1)

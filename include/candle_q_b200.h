@@ -61,8 +61,9 @@ CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_bf16_plain);
 void moe_gemm_gguf(const float *input, const void *weights, const int32_t *sorted_token_ids, const int32_t *expert_ids,
                    const float *topk_weights, void *output, int num_experts, int topk, int size_m, int size_n, int size_k,
                    int gguf_dtype, int64_t stream);
-/* input: f16 (input_dtype 0) or bf16 (1).  Same integer arithmetic as moe_gemm_gguf (the reference switches to a
- * de-quantize + wmma kernel here). */
+/* input: f16 (input_dtype 0) or bf16 (1).  Q4K / Q6K experts with 64 or more pairs run on the grouped tensor-core
+ * kernel (cq_moe_prefill_gemm, Q8_K activation arithmetic); otherwise the integer GEMV of moe_gemm_gguf.  (The
+ * reference de-quantizes the experts to half precision and multiplies with wmma here.) */
 void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int32_t *sorted_token_ids,
                            const int32_t *expert_ids, const float *topk_weights, void *output, int num_experts, int topk,
                            int size_m, int size_n, int size_k, int input_dtype, int gguf_dtype, int64_t stream);
@@ -163,6 +164,15 @@ void cq_moe_gemv_sorted(int wtype, int act, const void *weights, const void *y, 
 void cq_indexed_moe_forward(int wtype, int act, const void *weights, const void *y, const uint32_t *ids, float *out, int n,
                             int k, int batch, int topk, int k_padded, int input_dim1, int num_experts, void *stream);
 int cq_moe_timeout_flag(void);
+/* Grouped prompt-phase GEMM of a quantized MoE layer on the int8 tensor cores (Q4_K / Q6_K experts, num_experts <= 1024,
+ * size_k % 256 == 0): same job rules as moe_gemm_gguf (pairs sorted by expert), input of in_elem (CQ_ELEM_*), f32 output
+ * rows indexed by pair.  The pairs of an expert are cut into tiles of 128 on the device; `scratch` holds the tile table
+ * and the int8 activation tiles (cq_moe_prefill_scratch_bytes, 256-byte aligned).  Arithmetic: Q8_K activations as the
+ * dense prefill kernel.  Pairs whose expert id is outside [0, num_experts) are not written. */
+size_t cq_moe_prefill_scratch_bytes(int size_m, int num_experts, int k);
+void cq_moe_prefill_gemm(int wtype, const void *input, int in_elem, const void *weights, const int32_t *sorted_token_ids,
+                         const int32_t *expert_ids, const float *topk_weights, float *out, void *scratch, int num_experts,
+                         int topk, int size_m, int size_n, int size_k, void *stream);
 
 /* Prefill path (many tokens) on the int8 tensor cores, Q4_K weights.  Replaces the pair
  * launch_mmq_quantize_q8_1_* + launch_mmq_gguf_q4_k of candle-kernels/src/ffi.rs:424-630 for callers that go through

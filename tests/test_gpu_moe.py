@@ -100,17 +100,23 @@ def test_indexed_moe_forward(oracle, cuda_dev, tname, x_dim1_is_one):
             assert rel_err(out2[b, s], oracle.matmul(wt, xin, wq[ids[b, s]], n)[0]) <= TOL
 
 
-def test_moe_prefill_entry_point_matches_decode(oracle, cuda_dev):
-    """f16 activations through moe_gemm_gguf_prefill give what the decode entry point gives for the up-cast values."""
-    wt, e, n, k, tokens, topk = 12, 16, 256, 1024, 40, 4
+def test_moe_prefill_entry_point_small_and_large(oracle, cuda_dev):
+    """moe_gemm_gguf_prefill: under 64 pairs it is the decode entry point on the up-cast values (same bits); from 64 pairs on
+    the grouped tensor-core kernel, whose arithmetic is the CPU path's (Q8_K activations)."""
+    wt, e, n, k, topk = 12, 16, 256, 1024, 4
     wq = _experts(oracle, wt, e, n, k, seed=4)
-    _, sorted_pairs, expert_of = _route(tokens, e, topk, seed=6)
     qt = QTensor.from_data(wq.reshape(-1), GgmlDType(wt), (e, n, k), cuda_dev)
-    x = torch.randn((tokens, k), device=cuda_dev).to(torch.float16)
-    sp, eo = torch.from_numpy(sorted_pairs).to(cuda_dev), torch.from_numpy(expert_of).to(cuda_dev)
-    a = moe_gemm_gguf(x, qt, None, sp, eo, topk, is_prefill=True)
-    b = moe_gemm_gguf(x.float(), qt, None, sp, eo, topk, is_prefill=False)
-    assert torch.equal(a, b)
+    for tokens in (10, 40):
+        ids, sorted_pairs, expert_of = _route(tokens, e, topk, seed=6)
+        x = torch.randn((tokens, k), device=cuda_dev).to(torch.float16)
+        sp, eo = torch.from_numpy(sorted_pairs).to(cuda_dev), torch.from_numpy(expert_of).to(cuda_dev)
+        a = moe_gemm_gguf(x, qt, None, sp, eo, topk, is_prefill=True)
+        if tokens * topk < 64:
+            assert torch.equal(a, moe_gemm_gguf(x.float(), qt, None, sp, eo, topk, is_prefill=False))
+        else:
+            xf = x.float().cpu().numpy()
+            ref = np.stack([oracle.matmul(wt, xf[p // topk][None, :], wq[ids.reshape(-1)[p]], n)[0] for p in range(tokens * topk)])
+            assert rel_err(a.cpu().numpy(), ref) <= 1e-5
 
 
 @pytest.mark.parametrize("is_prefill", [False, True])
@@ -251,3 +257,55 @@ def test_expert_parallel_tokens_match_single_gpu(tmp_path):
     r = subprocess.run(cmd, cwd=root, env=dict(os.environ, NCCL_NVLS_ENABLE="0"), capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert out.read_text().strip() == "identical"
+
+
+@pytest.mark.parametrize("tname", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("with_weights", [False, True])
+def test_grouped_tensor_core_gemm_matches_cpu_arithmetic(oracle, cuda_dev, tname, with_weights):
+    """cq_moe_prefill_gemm: pairs sorted by expert, experts with more than one tile, with an empty expert, and with ids of
+    another rank's experts (skipped).  Oracle: the reference CPU matmul (Q8_K activations) of each pair's expert."""
+    from candle_b200.moe import moe_prefill_gemm
+    wt = TYPES[tname]
+    e, n, k, topk = 5, 192, 512, 2
+    wq = _experts(oracle, wt, e, n, k, seed=11)
+    rng = np.random.default_rng(12)
+    tokens = 170
+    # expert 0 gets 300 pairs (three tiles), expert 2 none, the others a few; two pairs belong to "another rank" (-1, 7)
+    flat = np.concatenate([np.zeros(300, np.int32), np.full(17, 1, np.int32), np.full(20, 3, np.int32), np.full(1, 4, np.int32),
+                           np.array([-1, 7], np.int32)])
+    assert flat.size == tokens * topk
+    rng.shuffle(flat)
+    order = np.argsort(flat, kind="stable").astype(np.int32)        # sorted_token_ids
+    experts_sorted = flat[order]
+    dev = lambda a: torch.from_numpy(a).to(cuda_dev)
+    qt = QTensor.from_data(wq.reshape(-1), GgmlDType(wt), (e, n, k), cuda_dev)
+    if with_weights:            # down-projection style: one input row per pair, scaled
+        x = rng.standard_normal((tokens * topk, k)).astype(np.float32)
+        tw = rng.random(tokens * topk, dtype=np.float32)
+        out = moe_prefill_gemm(dev(x), qt, dev(tw), dev(order), dev(experts_sorted), topk, zero_init=True).cpu().numpy()
+    else:                       # gate / up style: input row = pair // topk
+        x = rng.standard_normal((tokens, k)).astype(np.float32)
+        tw = None
+        out = moe_prefill_gemm(dev(x), qt, None, dev(order), dev(experts_sorted), topk, zero_init=True).cpu().numpy()
+    assert capi.lib().cq_prefill_timeout_flag() == 0
+    ref = np.zeros_like(out)
+    for pair in range(tokens * topk):
+        ex = flat[pair]
+        if ex < 0 or ex >= e:
+            continue
+        row = x[pair] if with_weights else x[pair // topk]
+        ref[pair] = oracle.matmul(wt, row[None, :], wq[ex], n)[0] * (tw[pair] if with_weights else 1.0)
+    assert rel_err(out, ref) <= 1e-5
+    skipped = np.where((flat < 0) | (flat >= e))[0]
+    assert np.all(out[skipped] == 0.0)
+    # bf16 input through the reference's FFI name takes the same kernel
+    if not with_weights:
+        xb = dev(x).to(torch.bfloat16)
+        out_b = moe_gemm_gguf(xb, qt, None, dev(order), dev(experts_sorted), topk, is_prefill=True, zero_init=True).cpu().numpy()
+        ref_b = np.zeros_like(out_b)
+        xr = xb.to(torch.float32).cpu().numpy()
+        for pair in range(tokens * topk):
+            ex = flat[pair]
+            if 0 <= ex < e:
+                ref_b[pair] = oracle.matmul(wt, xr[pair // topk][None, :], wq[ex], n)[0]
+        assert rel_err(out_b, ref_b) <= 1e-5
