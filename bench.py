@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload ("gemv_sweep_llama3_8b", BASELINE.json configs[1]): one step is one pass over the Llama-3-8B
+Workload ("gemv_sweep_llama3_8b"): one step is one pass over the Llama-3-8B
 projection shapes (K->N: 4096->4096, 4096->1024, 4096->14336, 14336->4096, 4096->128256) x {Q4_K, Q6_K,
 Q8_0} x batch {1, 2, 4, 8}: 60 activation-quantize + GEMV pairs.  Weights are seeded synthetic GGUF blocks
 (candle_b200/synth.py), activations N(0, 1).
@@ -417,7 +417,7 @@ def run_prefill_case(args):
 
 
 def moe_decode_tok_s(dev, rank, world, batch, prompt_len=1024, steps=256, use_graph=True):
-    """BASELINE configs[4]: Qwen3-30B-A3B-shaped mixture-of-experts decoder (experts Q4_K, attention and head Q6_K, random
+    """Qwen3-30B-A3B-shaped mixture-of-experts decoder (experts Q4_K, attention and head Q6_K, random
     weights), expert parallel over `world` ranks: random prompt, then greedy decoding."""
     import torch
     import torch.distributed as dist
@@ -480,7 +480,7 @@ def run_dequant_case(args):
 
 
 def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=True):
-    """BASELINE configs[3]: Llama-3-8B-shaped Q4_K_M decoder, random prompt of `prompt_len` ids (seed 2), `steps` greedy
+    """Llama-3-8B-shaped Q4_K_M decoder, random prompt of `prompt_len` ids (seed 2), `steps` greedy
     tokens.  Returns (decode tokens/s over all sequences, prompt tokens/s, token checksum)."""
     import torch
     import torch.distributed as dist

@@ -194,17 +194,19 @@ extern "C" void moe_gemm_gguf(const float *input, const void *weights, const int
 
 // candle-kernels/src/ffi.rs:41-56: f16 (input_dtype 0) or bf16 (1) activations, f32 output.  The reference
 // de-quantizes the expert weights to half precision and multiplies with wmma (candle-kernels/src/moe/
-// moe_wmma_gguf.cu:124-300).  Here Q4_K / Q6_K experts with at least kMoePrefillMinPairs pairs go to the grouped
-// tensor-core kernel (cq_moe_prefill_gemm: int8 tcgen05 MMAs over Q8_K activations, the CPU path's arithmetic); fewer
+// moe_wmma_gguf.cu:124-300).  Here Q4_K / Q6_K experts go to the grouped tensor-core kernel (cq_moe_prefill_gemm: int8
+// tcgen05 MMAs over Q8_K activations, the CPU path's arithmetic) when there are at least 64 pairs and at least four per
+// expert on average - a tile unpacks its expert's weights once, which costs about as much as five GEMV jobs; fewer
 // pairs, and Q8_0 experts, take the integer GEMV of the decode entry point.
-constexpr int kMoePrefillMinPairs = 64;
+constexpr int kMoePrefillMinPairs = 64, kMoePrefillPairsPerExpert = 4;
 extern "C" void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int32_t *sorted_token_ids,
                                       const int32_t *expert_ids, const float *topk_weights, void *output, int num_experts,
                                       int topk, int size_m, int size_n, int size_k, int input_dtype, int gguf_dtype,
                                       int64_t stream) {
     const int wtype = wtype_of_moe_code(gguf_dtype);
     cudaStream_t st = (cudaStream_t)(uintptr_t)stream;
-    if ((wtype == CQ_Q4_K || wtype == CQ_Q6_K) && size_m >= kMoePrefillMinPairs && size_k % 256 == 0 && num_experts <= 1024 && input &&
+    if ((wtype == CQ_Q4_K || wtype == CQ_Q6_K) && size_m >= kMoePrefillMinPairs && size_m >= kMoePrefillPairsPerExpert * num_experts &&
+        size_k % 256 == 0 && num_experts <= 1024 && input &&
         output) {
         const size_t need = cq_moe_prefill_scratch_bytes(size_m, num_experts, size_k);
         void *scratch = nullptr;

@@ -1,4 +1,5 @@
-"""Llama-shaped decoder harness: the caller of ``QMatMul::forward`` that BASELINE config 4 describes.
+"""Llama-shaped decoder harness: a caller of ``QMatMul::forward`` with the shape of Llama-3-8B (32 layers, d = 4096, 32 query / 8 KV heads of 128,
+FFN 14336, vocabulary 128256).
 
 Structure and call order follow candle-transformers/src/models/quantized_llama.rs:178-262, 568-596 (f32 residual
 stream, RMSNorm eps 1e-5, interleaved RoPE, f32 KV cache, GQA attention, SwiGLU, logits for the last position)

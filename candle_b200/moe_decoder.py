@@ -1,5 +1,5 @@
-"""Mixture-of-experts decoder harness: the caller of the expert-indexed matmuls that BASELINE config 5 describes
-(Qwen3-30B-A3B shape: 48 layers, d = 2048, 32 query / 4 KV heads of 128, 128 experts of width 768, 8 per token).
+"""Mixture-of-experts decoder harness: a caller of the expert-indexed matmuls with the shape of Qwen3-30B-A3B
+(48 layers, d = 2048, 32 query / 4 KV heads of 128, 128 experts of width 768, 8 per token).
 
 Structure follows candle-transformers/src/models/quantized_qwen3_moe.rs:168-218, 295-304, 398-421 and
 candle-transformers/src/fused_moe.rs:222-301: f32 residual stream, RMSNorm, q/k/v projections, per-head RMSNorm of q
@@ -148,7 +148,7 @@ class MoeShapedDecoder:
         local = ids - self.e0 if self.world > 1 else ids           # other ranks' experts fall outside [0, e_local): skipped
         zero = self.world > 1
         a = torch.empty((R, k, f), dtype=torch.float32, device=self.device)
-        if R * k >= 64:         # prompt: pairs sorted by expert, grouped GEMM on the tensor cores
+        if R * k >= max(64, 4 * self.e_local):     # prompt: pairs sorted by expert, grouped GEMM on the tensor cores
             experts, pairs = torch.sort(local.reshape(-1), stable=True)
             gu = moe_prefill_gemm(h, L.gate_up, None, pairs, experts, k, zero_init=zero)          # [R * k, 2f]
             lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)

@@ -61,8 +61,8 @@ CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_bf16_plain);
 void moe_gemm_gguf(const float *input, const void *weights, const int32_t *sorted_token_ids, const int32_t *expert_ids,
                    const float *topk_weights, void *output, int num_experts, int topk, int size_m, int size_n, int size_k,
                    int gguf_dtype, int64_t stream);
-/* input: f16 (input_dtype 0) or bf16 (1).  Q4K / Q6K experts with 64 or more pairs run on the grouped tensor-core
- * kernel (cq_moe_prefill_gemm, Q8_K activation arithmetic); otherwise the integer GEMV of moe_gemm_gguf.  (The
+/* input: f16 (input_dtype 0) or bf16 (1).  Q4K / Q6K experts with 64 or more pairs and at least four pairs per expert
+ * on average run on the grouped tensor-core kernel (cq_moe_prefill_gemm, Q8_K activation arithmetic); otherwise the integer GEMV of moe_gemm_gguf.  (The
  * reference de-quantizes the experts to half precision and multiplies with wmma here.) */
 void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int32_t *sorted_token_ids,
                            const int32_t *expert_ids, const float *topk_weights, void *output, int num_experts, int topk,

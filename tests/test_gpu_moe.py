@@ -111,7 +111,7 @@ def test_moe_prefill_entry_point_small_and_large(oracle, cuda_dev):
         x = torch.randn((tokens, k), device=cuda_dev).to(torch.float16)
         sp, eo = torch.from_numpy(sorted_pairs).to(cuda_dev), torch.from_numpy(expert_of).to(cuda_dev)
         a = moe_gemm_gguf(x, qt, None, sp, eo, topk, is_prefill=True)
-        if tokens * topk < 64:
+        if tokens * topk < 64:          # (and at least four pairs per expert: 160 >= 4 * 16 in the larger case)
             assert torch.equal(a, moe_gemm_gguf(x.float(), qt, None, sp, eo, topk, is_prefill=False))
         else:
             xf = x.float().cpu().numpy()

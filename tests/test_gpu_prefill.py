@@ -98,7 +98,7 @@ def test_prefill_half_types(lib, oracle, cuda_dev, dtype):
 
 
 def test_prefill_agrees_with_decode_kernel_at_full_size(lib, cuda_dev):
-    """BASELINE configs[2] shape (4096 -> 14336, 2048 tokens), synthetic blocks: every sampled token must give
+    """The benchmark's prefill shape (4096 -> 14336, 2048 tokens), synthetic blocks: every sampled token must give
     what the decode GEMV gives for it with the same Q8_K activations (two independent kernels, same integers)."""
     k, n, tokens = 4096, 14336, 2048
     w = random_blocks(GgmlDType.Q4K, n, k, seed=3, device=cuda_dev)
