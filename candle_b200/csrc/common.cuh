@@ -14,7 +14,7 @@
 #define CQ_Q8_BYTES 36  // one activation block: 4 scale bytes + 32 int8
 
 // GGML type ids (candle-core/src/quantized/mod.rs:300-342)
-enum CqType : int { CQ_Q4_0 = 2, CQ_Q8_0 = 8, CQ_Q4_K = 12, CQ_Q6_K = 14 };
+enum CqType : int { CQ_Q4_0 = 2, CQ_Q8_0 = 8, CQ_Q4_K = 12, CQ_Q5_K = 13, CQ_Q6_K = 14 };
 // Output / input element types of the launchers
 enum CqElem : int { CQ_F32 = 0, CQ_F16 = 1, CQ_BF16 = 2 };
 // Activation encodings.  All three use the same 36-byte container per 32 elements
@@ -54,10 +54,10 @@ static_assert(sizeof(cq_block_q4_K) == 144, "q4_K");
 static_assert(sizeof(cq_block_q6_K) == 210, "q6_K");
 
 __host__ __device__ constexpr int cq_type_size(int t) {
-    return t == CQ_Q4_0 ? 18 : t == CQ_Q8_0 ? 34 : t == CQ_Q4_K ? 144 : t == CQ_Q6_K ? 210 : 0;
+    return t == CQ_Q4_0 ? 18 : t == CQ_Q8_0 ? 34 : t == CQ_Q4_K ? 144 : t == CQ_Q5_K ? 176 : t == CQ_Q6_K ? 210 : 0;
 }
 __host__ __device__ constexpr int cq_block_elems(int t) {
-    return (t == CQ_Q4_K || t == CQ_Q6_K) ? CQ_QK_K : CQ_QK;
+    return (t == CQ_Q4_K || t == CQ_Q5_K || t == CQ_Q6_K) ? CQ_QK_K : CQ_QK;
 }
 
 // ---- status side channel (defined in status.cu) ----

@@ -46,6 +46,22 @@ template <int TYPE> __device__ __forceinline__ void unit_values(const uint8_t *r
             const int nib = l0 >= 32 ? (q[i] >> 4) : (q[i] & 0xF);
             v[i] = __fsub_rn(__fmul_rn(d1, (float)nib), m1);
         }
+    } else if constexpr (TYPE == CQ_Q5_K) {
+        const uint8_t *b = row + u * 176;
+        const float d = ldh(b), dmin = ldh(b + 2);
+        const int sub = e0 / 32, l0 = e0 % 32;
+        const uint8_t *s = b + 4;
+        int sc, mn;
+        if (sub < 4) { sc = s[sub] & 63; mn = s[sub + 4] & 63; }
+        else { sc = (s[sub + 4] & 0xF) | ((s[sub - 4] >> 6) << 4); mn = (s[sub + 4] >> 4) | ((s[sub] >> 6) << 4); }
+        const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
+        const uint8_t *q = b + 48 + 32 * (sub / 2) + l0, *qh = b + 16 + l0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int nib = (sub & 1) ? (q[i] >> 4) : (q[i] & 0xF);
+            const float to_add = ((qh[i] >> sub) & 1) ? 16.0f : 0.0f;
+            v[i] = __fsub_rn(__fmul_rn(d1, __fadd_rn((float)nib, to_add)), m1);
+        }
     } else {        // Q6_K
         const uint8_t *b = row + u * 210;
         const float d = ldh(b + 208);
@@ -116,6 +132,7 @@ bool dispatch(int wtype, const void *w, const int32_t *ids, void *out, int out_k
     case CQ_Q4_0: launch_rows<CQ_Q4_0>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q8_0: launch_rows<CQ_Q8_0>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q4_K: launch_rows<CQ_Q4_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
+    case CQ_Q5_K: launch_rows<CQ_Q5_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q6_K: launch_rows<CQ_Q6_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     }
     return false;

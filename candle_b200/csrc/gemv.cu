@@ -197,7 +197,7 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
         cq_set_status(CQ_ERR_BAD_ARG, "mmvq: unsupported weight type, or K not a multiple of the block size");
         return;
     }
-    if ((uintptr_t)vx % (wtype == CQ_Q4_K ? 16 : 2) != 0 || (uintptr_t)vy % 4 != 0) {
+    if ((uintptr_t)vx % ((wtype == CQ_Q4_K || wtype == CQ_Q5_K) ? 16 : 2) != 0 || (uintptr_t)vy % 4 != 0) {
         cq_set_status(CQ_ERR_BAD_ARG, "mmvq: misaligned weight or activation pointer");
         return;
     }
@@ -225,6 +225,9 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
         case CQ_Q4_K:
             return cpu_act ? launch_type<CQ_Q4_K_WIDE, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
                            : launch_type<CQ_Q4_K_WIDE, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q5_K:
+            return cpu_act ? launch_type<CQ_Q5_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q5_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
         case CQ_Q6_K:
             return cpu_act ? launch_type<CQ_Q6_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
                            : launch_type<CQ_Q6_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
@@ -280,7 +283,7 @@ extern "C" int cq_device_timeout_flag(void) {
     return v;
 }
 
-// The reference's twelve symbols for the four formats (candle-kernels/src/ffi.rs:61-393).
+// The reference's fifteen symbols for the five formats (candle-kernels/src/ffi.rs:61-393).
 #define CQ_MMVQ_PLAIN(name, wtype, kind)                                                                          \
     extern "C" void name(const void *vx, const void *vy, void *dst, int ncols_x, int nrows_x, int stride_col_y,  \
                          int stride_col_dst, int b_size, void *stream) {                                         \
@@ -296,6 +299,9 @@ CQ_MMVQ_PLAIN(launch_mmvq_gguf_q8_0_bf16_plain, CQ_Q8_0, CQ_BF16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_f32_plain, CQ_Q4_K, CQ_F32)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_f16_plain, CQ_Q4_K, CQ_F16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_bf16_plain, CQ_Q4_K, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_k_f32_plain, CQ_Q5_K, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_k_f16_plain, CQ_Q5_K, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_k_bf16_plain, CQ_Q5_K, CQ_BF16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q6_k_f32_plain, CQ_Q6_K, CQ_F32)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q6_k_f16_plain, CQ_Q6_K, CQ_F16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q6_k_bf16_plain, CQ_Q6_K, CQ_BF16)
@@ -324,7 +330,7 @@ __global__ void block_dots_kernel(const uint8_t *__restrict__ w, const uint8_t *
         if constexpr (TYPE == CQ_Q4_0) {
             if (ACT == CQ_ACT_Q8_1) s += cw.idot(a); else s += cw.idot(a) - 8 * a.sq[0];
         } else if constexpr (TYPE == CQ_Q8_0) s += cw.idot(a);
-        else if constexpr (TYPE == CQ_Q4_K) {
+        else if constexpr (TYPE == CQ_Q4_K || TYPE == CQ_Q5_K) {
             int d0, d1;
             cw.idots(a, d0, d1);
             s += d0 * cw.sc[0] + d1 * cw.sc[1];
@@ -358,6 +364,10 @@ extern "C" void cq_block_dots(int wtype, int act, const void *vx, const void *vy
     case CQ_Q4_K:
         if (cpu) block_dots_kernel<CQ_Q4_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
         else block_dots_kernel<CQ_Q4_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q5_K:
+        if (cpu) block_dots_kernel<CQ_Q5_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q5_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
         break;
     case CQ_Q6_K:
         if (cpu) block_dots_kernel<CQ_Q6_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);

@@ -4,6 +4,7 @@
 //   Q4_0 : one 18-byte block            (32 elements)
 //   Q8_0 : one 34-byte block            (32 elements)
 //   Q4_K : 16 bytes of nibbles          (32 elements: 16 of sub-block 2j and 16 of sub-block 2j+1)
+//   Q5_K : 32 bytes of nibbles + the 32 bytes of fifth bits  (64 elements: the two sub-blocks of a pair)
 //   Q6_K : 16+16 bytes ql, 16 bytes qh  (64 elements: 16 at each of the four 32-apart positions)
 //
 // A lane keeps the int8 activations of its chunk (for every batch row) in registers and walks over
@@ -35,6 +36,7 @@ template <> struct ChunkGeom<CQ_Q4_0> { static constexpr int BASE = CQ_Q4_0, ELE
 template <> struct ChunkGeom<CQ_Q8_0> { static constexpr int BASE = CQ_Q8_0, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
 template <> struct ChunkGeom<CQ_Q4_K> { static constexpr int BASE = CQ_Q4_K, ELEMS = 32, Q8_BLOCKS = 2, WORDS = 8; };
 template <> struct ChunkGeom<CQ_Q4_K_WIDE> { static constexpr int BASE = CQ_Q4_K, ELEMS = 64, Q8_BLOCKS = 2, WORDS = 16; };
+template <> struct ChunkGeom<CQ_Q5_K> { static constexpr int BASE = CQ_Q5_K, ELEMS = 64, Q8_BLOCKS = 2, WORDS = 16; };
 template <> struct ChunkGeom<CQ_Q6_K> { static constexpr int BASE = CQ_Q6_K, ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
 
 // Activation registers of one chunk for one batch row.
@@ -55,7 +57,7 @@ template <int TYPE> __device__ __forceinline__ void chunk_act_coords(int chunk, 
     else if constexpr (TYPE == CQ_Q4_K) {
         const int sb = chunk >> 3, c = chunk & 7;
         blk = sb * 8 + 2 * (c >> 1) + i; byte0 = 16 * (c & 1);
-    } else if constexpr (TYPE == CQ_Q4_K_WIDE) {
+    } else if constexpr (TYPE == CQ_Q4_K_WIDE || TYPE == CQ_Q5_K) {
         blk = 2 * chunk + i; byte0 = 0;     // chunk = 4 * super-block + pair
     } else {
         const int sb = chunk >> 2, n = (chunk >> 1) & 1, h = chunk & 1;
@@ -99,7 +101,7 @@ __device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t 
             a.d[i] = __low2float(h2);
             // Q4_K with Q8_1 containers: d * sum(q) as in the reference's GEMV (mmvq_gguf.cu:335-354); with the MMQ
             // encoding the stored sum, as in its tiled kernel (mmq_gguf/mmq_vecdotq.cuh:527-551).
-            if constexpr ((TYPE == CQ_Q4_K || TYPE == CQ_Q4_K_WIDE) && !MMQ) a.s[i] = a.d[i] * (float)sq;
+            if constexpr ((TYPE == CQ_Q4_K || TYPE == CQ_Q4_K_WIDE || TYPE == CQ_Q5_K) && !MMQ) a.s[i] = a.d[i] * (float)sq;
             else a.s[i] = __high2float(h2);
         }
     }
@@ -244,6 +246,52 @@ template <> struct ChunkW<CQ_Q4_K_WIDE> {
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
         } else {
             const int isd = d0 * sc[0] + (d1x16 >> 4) * sc[1];
+            const int ism = a.sq[0] * mn[0] + a.sq[1] * mn[1];
+            return __fmul_rn(a.d[0], __fmaf_rn(d, (float)isd, -__fmul_rn(dmin, (float)ism)));
+        }
+    }
+};
+
+// Q5_K: the layout of Q4_K with 32 bytes `qh` between the scales and the nibbles; bit g of qh[l] is the fifth bit of
+// element l of sub-block g (candle-core/src/quantized/k_quants.rs:1962-1995).  Same formulas as Q4_K
+// (candle-kernels/src/mmvq_gguf.cu:357-381), values 0..31.
+template <> struct ChunkW<CQ_Q5_K> {
+    uint32_t lo[8], hi[8];
+    float d, dmin;
+    int sc[2], mn[2];
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const int sb = chunk >> 2, jp = chunk & 3;
+        const uint8_t *b = row + sb * 176;
+        const __half2 dm = *reinterpret_cast<const __half2 *>(b);
+        d = __low2float(dm); dmin = __high2float(dm);
+        uint32_t scp, mnp;
+        q4k_pair_scales(b, jp, scp, mnp);
+        sc[0] = scp & 0xFF; sc[1] = scp >> 8; mn[0] = mnp & 0xFF; mn[1] = mnp >> 8;
+        const uint4 h0 = *reinterpret_cast<const uint4 *>(b + 16), h1 = *reinterpret_cast<const uint4 *>(b + 32);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(b + 48 + 32 * jp), q1 = *reinterpret_cast<const uint4 *>(b + 64 + 32 * jp);
+        const uint32_t qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const uint32_t hb = hh[w] >> (2 * jp);
+            lo[w] = (qq[w] & 0x0F0F0F0Fu) | ((hb << 4) & 0x10101010u);
+            hi[w] = ((qq[w] >> 4) & 0x0F0F0F0Fu) | ((hb << 3) & 0x10101010u);
+        }
+    }
+    __device__ __forceinline__ void idots(const ChunkAct<CQ_Q5_K> &a, int &d0, int &d1) const {
+        d0 = 0; d1 = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { d0 = cq_dp4a((int)lo[w], a.u[w], d0); d1 = cq_dp4a((int)hi[w], a.u[8 + w], d1); }
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q5_K> &a) const {
+        int d0, d1;
+        idots(a, d0, d1);
+        if constexpr (cq_act_q8_1_like(ACT)) {      // products below 32 * 31 * 127 * 63 = 7.9e6 < 2^24: the conversion is exact
+            const float sd = __fmaf_rn(a.d[1], (float)(d1 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
+            const float sm = __fmaf_rn(a.s[1], cq_small_int_to_float(mn[1]), __fmul_rn(a.s[0], cq_small_int_to_float(mn[0])));
+            return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
+        } else {
+            const int isd = d0 * sc[0] + d1 * sc[1];
             const int ism = a.sq[0] * mn[0] + a.sq[1] * mn[1];
             return __fmul_rn(a.d[0], __fmaf_rn(d, (float)isd, -__fmul_rn(dmin, (float)ism)));
         }

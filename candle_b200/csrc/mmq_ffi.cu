@@ -161,7 +161,7 @@ void launch_mmq(const void *x, const void *y, void *dst, int64_t ncols_x, int64_
         cq_set_status(CQ_ERR_UNSUPPORTED, "mmq: weight rows must be contiguous and the output row stride at least N");
         return;
     }
-    if ((uintptr_t)x % (BASE == CQ_Q4_K ? 16 : 2) != 0 || (uintptr_t)y % 16 != 0) {
+    if ((uintptr_t)x % ((BASE == CQ_Q4_K || BASE == CQ_Q5_K) ? 16 : 2) != 0 || (uintptr_t)y % 16 != 0) {
         cq_set_status(CQ_ERR_BAD_ARG, "mmq: misaligned weight or activation pointer");
         return;
     }
@@ -191,6 +191,7 @@ CQ_MMQ_QUANTIZE(launch_mmq_quantize_q8_1_D2S6, 2)
 CQ_MMQ_GEMM(launch_mmq_gguf_q4_0, CQ_Q4_0, CQ_ACT_MMQ_DS4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q8_0, CQ_Q8_0, CQ_ACT_MMQ_D4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q4_k, CQ_Q4_K_WIDE, CQ_ACT_MMQ_DS4)
+CQ_MMQ_GEMM(launch_mmq_gguf_q5_k, CQ_Q5_K, CQ_ACT_MMQ_DS4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q6_k, CQ_Q6_K, CQ_ACT_MMQ_D4)
 
 // 1 if any launch_mmq_gguf_* pass on the current device gave up waiting for a staged copy (synchronises the device).

@@ -47,6 +47,9 @@ CQ_DECL_MMVQ(launch_mmvq_gguf_q8_0_bf16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_f32_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_f16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_k_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_k_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_k_bf16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_f32_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_f16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_bf16_plain);
@@ -90,6 +93,7 @@ CQ_DECL_MMQ_QUANT(launch_mmq_quantize_q8_1_D2S6);
 CQ_DECL_MMQ(launch_mmq_gguf_q4_0);
 CQ_DECL_MMQ(launch_mmq_gguf_q8_0);
 CQ_DECL_MMQ(launch_mmq_gguf_q4_k);
+CQ_DECL_MMQ(launch_mmq_gguf_q5_k);
 CQ_DECL_MMQ(launch_mmq_gguf_q6_k);
 #undef CQ_DECL_MMQ
 /* 1 if a launch_mmq_gguf_* pass gave up a bounded wait on the current device (no reference counterpart). */
@@ -103,6 +107,7 @@ int cq_mmq_timeout_flag(void);
 #define CQ_TYPE_Q4_0 2
 #define CQ_TYPE_Q8_0 8
 #define CQ_TYPE_Q4_K 12
+#define CQ_TYPE_Q5_K 13
 #define CQ_TYPE_Q6_K 14
 /* element types of dense inputs / outputs */
 #define CQ_ELEM_F32 0

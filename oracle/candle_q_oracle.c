@@ -42,7 +42,7 @@
 typedef _Float16 f16_t; /* IEEE binary16, conversions round to nearest even like half::f16 */
 
 /* GGML type ids, candle-core/src/quantized/mod.rs:300-342 */
-enum { CQO_Q4_0 = 2, CQO_Q8_0 = 8, CQO_Q8_1 = 9, CQO_Q4K = 12, CQO_Q6K = 14, CQO_Q8K = 15 };
+enum { CQO_Q4_0 = 2, CQO_Q8_0 = 8, CQO_Q8_1 = 9, CQO_Q4K = 12, CQO_Q5K = 13, CQO_Q6K = 14, CQO_Q8K = 15 };
 
 /* Block layouts, candle-core/src/quantized/k_quants.rs:77-190 (all packed, little endian). */
 #pragma pack(push, 1)
@@ -50,6 +50,7 @@ typedef struct { f16_t d; uint8_t qs[16]; } blk_q4_0;                           
 typedef struct { f16_t d; int8_t qs[32]; } blk_q8_0;                                /* 34 B  */
 typedef struct { f16_t d; f16_t s; int8_t qs[32]; } blk_q8_1;                       /* 36 B  */
 typedef struct { f16_t d; f16_t dmin; uint8_t scales[12]; uint8_t qs[128]; } blk_q4k; /* 144 B */
+typedef struct { f16_t d; f16_t dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; } blk_q5k; /* 176 B */
 typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; f16_t d; } blk_q6k; /* 210 B */
 typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8k;             /* 292 B */
 /* candle-kernels/src/mmq_gguf/mmq_common.cuh block_q8_1_mmq: 4 scale words + 128 int8 */
@@ -60,6 +61,7 @@ _Static_assert(sizeof(blk_q4_0) == 18, "q4_0");
 _Static_assert(sizeof(blk_q8_0) == 34, "q8_0");
 _Static_assert(sizeof(blk_q8_1) == 36, "q8_1");
 _Static_assert(sizeof(blk_q4k) == 144, "q4k");
+_Static_assert(sizeof(blk_q5k) == 176, "q5k");
 _Static_assert(sizeof(blk_q6k) == 210, "q6k");
 _Static_assert(sizeof(blk_q8k) == 292, "q8k");
 _Static_assert(sizeof(blk_q8_1_mmq) == 144, "q8_1_mmq");
@@ -67,11 +69,11 @@ _Static_assert(sizeof(blk_q8_1_mmq) == 144, "q8_1_mmq");
 int cqo_type_size(int t) {
     switch (t) {
     case CQO_Q4_0: return 18; case CQO_Q8_0: return 34; case CQO_Q8_1: return 36;
-    case CQO_Q4K: return 144; case CQO_Q6K: return 210; case CQO_Q8K: return 292;
+    case CQO_Q4K: return 144; case CQO_Q5K: return 176; case CQO_Q6K: return 210; case CQO_Q8K: return 292;
     }
     return 0;
 }
-int cqo_block_size(int t) { return (t == CQO_Q4K || t == CQO_Q6K || t == CQO_Q8K) ? QK_K : QK; }
+int cqo_block_size(int t) { return (t == CQO_Q4K || t == CQO_Q5K || t == CQO_Q6K || t == CQO_Q8K) ? QK_K : QK; }
 int cqo_have_avx2(void) { return CQO_HAVE_AVX2; }
 
 /* Minimal parallel-for over [0, n): contiguous static chunks on `nthreads` pthreads (<= 0: all
@@ -307,6 +309,65 @@ void cqo_quantize_q4k(const float *x, void *vy, int64_t k) {
     }
 }
 
+/* BlockQ5K::from_float, k_quants.rs:1804-1877: as Q4K with 31 levels; the fifth bit of element l of sub-block g goes to
+ * bit g of qh[l]. */
+void cqo_quantize_q5k(const float *x, void *vy, int64_t k) {
+    blk_q5k *y = (blk_q5k *)vy;
+    for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+        const float *xb = x + ib * QK_K;
+        blk_q5k *b = &y[ib];
+        float mins[8], scales[8];
+        for (int j = 0; j < 8; ++j) make_qkx1(31, 5, xb + 32 * j, 32, &scales[j], &mins[j]);
+        float max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 8; ++j) { max_scale = fmaxf(scales[j], max_scale); max_min = fmaxf(mins[j], max_min); }
+        const float inv_scale = max_scale > 0.f ? 63.0f / max_scale : 0.f;
+        const float inv_min = max_min > 0.f ? 63.0f / max_min : 0.f;
+        memset(b->scales, 0, 12);
+        for (int j = 0; j < 8; ++j) {
+            int32_t a = nearest_int(inv_scale * scales[j]); if (a > 63) a = 63;
+            int32_t c = nearest_int(inv_min * mins[j]);     if (c > 63) c = 63;
+            const uint8_t ls = (uint8_t)clampi(a, 0, 255), lm = (uint8_t)clampi(c, 0, 255);
+            if (j < 4) { b->scales[j] = ls; b->scales[j + 4] = lm; }
+            else {
+                b->scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                b->scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                b->scales[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        b->d = f32_to_f16(max_scale / 63.0f);
+        b->dmin = f32_to_f16(max_min / 63.0f);
+        uint8_t l[QK_K];
+        memset(l, 0, sizeof l);
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, m;
+            scale_min_k4(j, b->scales, &sc, &m);
+            const float d = f16_to_f32(b->d) * (float)sc;
+            if (d == 0.f) continue;
+            const float dm = f16_to_f32(b->dmin) * (float)m;
+            for (int ii = 0; ii < 32; ++ii)
+                l[32 * j + ii] = (uint8_t)clampi(nearest_int((xb[32 * j + ii] + dm) / d), 0, 31);
+        }
+        memset(b->qh, 0, 32);
+        uint8_t m1 = 1, m2 = 2;
+        for (int n = 0; n < QK_K; n += 64) {
+            for (int j = 0; j < 32; ++j) {
+                uint8_t l1 = l[n + j], l2 = l[n + j + 32];
+                if (l1 > 15) { l1 -= 16; b->qh[j] |= m1; }
+                if (l2 > 15) { l2 -= 16; b->qh[j] |= m2; }
+                b->qs[(n / 64) * 32 + j] = (uint8_t)(l1 | (l2 << 4));
+            }
+            m1 <<= 2; m2 <<= 2;
+        }
+    }
+}
+
+/* element e (0..255) of a Q5K block as its 5-bit value */
+static inline int q5k_value(const blk_q5k *b, int e) {
+    const int g = e / 32, l = e % 32;                 /* sub-block, element */
+    const uint8_t q = b->qs[32 * (g / 2) + l];
+    return ((g & 1) ? (q >> 4) : (q & 0xF)) + (((b->qh[l] >> g) & 1) << 4);
+}
+
 /* make_qx_quants(n, nmax, x, ls, rmse_type=1, qw=null), utils.rs:62-224 (rmse_type < 3 branch) */
 static float make_qx(int n, int nmax, const float *x, int8_t *ls) {
     float max = 0.f, amax = 0.f;
@@ -441,6 +502,23 @@ void cqo_dequantize(int type, const void *vx, float *y, int64_t k) {
                 for (int t = 0; t < 32; ++t) *o++ = d2 * (float)(q[t] >> 4) - m2;
             }
         }
+    } else if (type == CQO_Q5K) {      /* k_quants.rs:1962-1995: d1 * (q + 16 * bit) - m1 */
+        const blk_q5k *x = (const blk_q5k *)vx;
+        for (int64_t i = 0; i < k / QK_K; ++i) {
+            const float d = f16_to_f32(x[i].d), mn = f16_to_f32(x[i].dmin);
+            float *o = y + i * QK_K;
+            for (int g = 0; g < 8; ++g) {
+                uint8_t sc, m;
+                scale_min_k4(g, x[i].scales, &sc, &m);
+                const float d1 = d * (float)sc, m1 = mn * (float)m;
+                for (int l = 0; l < 32; ++l) {
+                    const uint8_t q = x[i].qs[32 * (g / 2) + l];
+                    const float base = (float)((g & 1) ? (q >> 4) : (q & 0xF));
+                    const float to_add = ((x[i].qh[l] >> g) & 1) ? 16.0f : 0.0f;
+                    *o++ = d1 * (base + to_add) - m1;
+                }
+            }
+        }
     } else if (type == CQO_Q6K) {
         const blk_q6k *x = (const blk_q6k *)vx;
         for (int64_t i = 0; i < k / QK_K; ++i) {
@@ -476,6 +554,7 @@ void cqo_quantize(int type, const float *x, void *y, int64_t k) {
     case CQO_Q8_0: cqo_quantize_q8_0(x, y, k); break;
     case CQO_Q8_1: cqo_quantize_q8_1_cpu(x, y, k); break;
     case CQO_Q4K: cqo_quantize_q4k(x, y, k); break;
+    case CQO_Q5K: cqo_quantize_q5k(x, y, k); break;
     case CQO_Q6K: cqo_quantize_q6k(x, y, k); break;
     case CQO_Q8K: cqo_quantize_q8k(x, y, k); break;
     }
@@ -534,6 +613,31 @@ static float dot_q4k_q8k_scalar(int64_t n, const blk_q4k *x, const blk_q8k *y) {
             }
         uint8_t sc[8], mn[8];
         q4k_scales(&x[i], sc, mn);
+        int32_t sumi = 0;
+        for (int j = 0; j < 16; ++j) sumi += (int32_t)y[i].bsums[j] * mn[j / 2];
+        const int8_t *a = a8, *q8 = y[i].qs;
+        for (int g = 0; g < 8; ++g)
+            for (int r = 0; r < 4; ++r, a += 8, q8 += 8)
+                for (int l = 0; l < 8; ++l) aux32[l] += (int32_t)sc[g] * (int16_t)(q8[l] * a[l]);
+        const float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; ++l) sums[l] += d * (float)aux32[l];
+        const float dmin = f16_to_f32(x[i].dmin) * y[i].d;
+        sumf -= dmin * (float)sumi;
+    }
+    float t = -0.0f;
+    for (int l = 0; l < 8; ++l) t += sums[l];
+    return sumf + t;
+}
+/* Q5K x Q8K, k_quants.rs:1714-1801.  The AVX2 variant (avx.rs) differs only in the order of the f32 additions; it is not
+ * restated, every mode of cqo_vec_dot uses this one for Q5K. */
+static float dot_q5k_q8k_scalar(int64_t n, const blk_q5k *x, const blk_q8k *y) {
+    float sums[8] = {0}, sumf = 0.f;
+    for (int64_t i = 0; i < n / QK_K; ++i) {
+        int8_t a8[QK_K];
+        int32_t aux32[8] = {0};
+        for (int e = 0; e < QK_K; ++e) a8[e] = (int8_t)q5k_value(&x[i], e);
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; ++j) scale_min_k4(j, x[i].scales, &sc[j], &mn[j]);
         int32_t sumi = 0;
         for (int j = 0; j < 16; ++j) sumi += (int32_t)y[i].bsums[j] * mn[j / 2];
         const int8_t *a = a8, *q8 = y[i].qs;
@@ -770,6 +874,7 @@ static float dot_q6k_q8k_hw(int64_t n, const blk_q6k *x, const blk_q8k *y) {
 
 /* mode: 0 scalar (vec_dot_unopt), 1 AVX2 order in portable code, 2 AVX2 hardware */
 float cqo_vec_dot(int type, int mode, int64_t n, const void *x, const void *y) {
+    if (type == CQO_Q5K) return dot_q5k_q8k_scalar(n, (const blk_q5k *)x, (const blk_q8k *)y);
 #if CQO_HAVE_AVX2
     if (mode == 2) {
         switch (type) {
@@ -829,6 +934,17 @@ void cqo_cpu_block_dots(int type, int64_t k, int64_t nrows, const void *w, const
                     s += sc[g] * t;
                 }
                 for (int j = 0; j < 16; ++j) sm += (int32_t)y->bsums[j] * mn[j / 2];
+            } else if (type == CQO_Q5K) {
+                const blk_q5k *x = (const blk_q5k *)w + r * nb + i;
+                const blk_q8k *y = (const blk_q8k *)act + i;
+                for (int g = 0; g < 8; ++g) {
+                    uint8_t sc, m;
+                    scale_min_k4(g, x->scales, &sc, &m);
+                    int32_t t = 0;
+                    for (int e = 0; e < 32; ++e) t += q5k_value(x, 32 * g + e) * y->qs[32 * g + e];
+                    s += sc * t;
+                    sm += ((int32_t)y->bsums[2 * g] + y->bsums[2 * g + 1]) * m;
+                }
             } else if (type == CQO_Q6K) {
                 const blk_q6k *x = (const blk_q6k *)w + r * nb + i;
                 const blk_q8k *y = (const blk_q8k *)act + i;
@@ -956,6 +1072,35 @@ static float cuda_thread_dot(int type, const void *wrow, const blk_q8_1 *y, int 
         const float d = f16_to_f32(b->d), dmin = f16_to_f32(b->dmin);
         return acc + (fma ? fmaf(d, sumf_d, -(dmin * sumf_m)) : d * sumf_d - dmin * sumf_m);
     }
+    if (type == CQO_Q5K) {             /* vdr 2, qi 32, mmvq_gguf.cu:357-381, 568-606 */
+        const blk_q5k *b = (const blk_q5k *)wrow + kbx;
+        const int off = 2 * ((iqs / 2) / 4);
+        const uint8_t *ql = b->qs + 16 * off + 4 * ((iqs / 2) % 4), *qh = b->qh + 4 * ((iqs / 2) % 4);
+        const int32_t vl0 = ld_i32(ql), vl1 = ld_i32(ql + 16);
+        const int32_t vh0 = (int32_t)((uint32_t)ld_i32(qh) >> off), vh1 = (int32_t)((uint32_t)ld_i32(qh + 16) >> off);
+        uint8_t sc[2], mn[2];
+        scale_min_k4(off, b->scales, &sc[0], &mn[0]);
+        scale_min_k4(off + 1, b->scales, &sc[1], &mn[1]);
+        float sumf_d = 0.f, sumf_m = 0.f;
+        for (int i = 0; i < 2; ++i) {
+            const blk_q8_1 *yi = y + off + i;
+            const int32_t u0 = ld_i32(yi->qs + 4 * ((iqs / 2) % 4)), u1 = ld_i32(yi->qs + 4 * ((iqs / 2) % 4) + 16);
+            const int32_t v0 = ((vl0 >> (4 * i)) & 0x0F0F0F0F) | (((vh0 >> i) << 4) & 0x10101010);
+            const int32_t v1 = ((vl1 >> (4 * i)) & 0x0F0F0F0F) | (((vh1 >> i) << 4) & 0x10101010);
+            const int32_t dot1 = dp4a(v0, u0, dp4a(v1, u1, 0));
+            const int32_t dot2 = dp4a(0x01010101, u0, dp4a(0x01010101, u1, 0));
+            const float d8 = f16_to_f32(yi->d);
+            if (fma) {
+                sumf_d = fmaf(d8, (float)(dot1 * sc[i]), sumf_d);
+                sumf_m = fmaf(d8, (float)(dot2 * mn[i]), sumf_m);
+            } else {
+                sumf_d += d8 * (float)(dot1 * sc[i]);
+                sumf_m += d8 * (float)(dot2 * mn[i]);
+            }
+        }
+        const float d = f16_to_f32(b->d), dmin = f16_to_f32(b->dmin);
+        return acc + (fma ? fmaf(d, sumf_d, -(dmin * sumf_m)) : d * sumf_d - dmin * sumf_m);
+    }
     if (type == CQO_Q6K) {             /* vdr 1, qi 32 */
         const blk_q6k *b = (const blk_q6k *)wrow + kbx;
         const int off = 4 * (iqs / 16) + (iqs % 16) / 8;
@@ -984,7 +1129,7 @@ static void cuda_lane_map(int type, int *qk, int *qi, int *vdr) {
     switch (type) {
     case CQO_Q4_0: *qk = 32; *qi = 4; *vdr = 2; break;
     case CQO_Q8_0: *qk = 32; *qi = 8; *vdr = 2; break;
-    case CQO_Q4K: *qk = 256; *qi = 32; *vdr = 2; break;
+    case CQO_Q4K: case CQO_Q5K: *qk = 256; *qi = 32; *vdr = 2; break;
     default: *qk = 256; *qi = 32; *vdr = 1; break;
     }
 }
@@ -1067,6 +1212,20 @@ void cqo_cuda_block_dots(int type, int64_t k, int64_t nrows, const void *w, cons
                     }
                     s += sc[g] * t;
                     sm += mn[g] * q;
+                }
+            } else if (type == CQO_Q5K) {
+                const blk_q5k *x = (const blk_q5k *)w + r * nb + i;
+                for (int g = 0; g < 8; ++g) {
+                    uint8_t sc, m;
+                    scale_min_k4(g, x->scales, &sc, &m);
+                    int32_t t = 0, q = 0;
+                    for (int e = 0; e < 32; ++e) {
+                        const int8_t a = y[8 * i + g].qs[e];
+                        t += q5k_value(x, 32 * g + e) * a;
+                        q += a;
+                    }
+                    s += sc * t;
+                    sm += m * q;
                 }
             } else if (type == CQO_Q6K) {
                 const blk_q6k *x = (const blk_q6k *)w + r * nb + i;
@@ -1166,6 +1325,15 @@ void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k
                     const uint8_t *q4 = b->qs + 32 * (sub / 2);
                     int sumi = 0;
                     for (int i = 0; i < 32; ++i) sumi += ((sub & 1) ? (q4[i] >> 4) : (q4[i] & 0xF)) * q8[i];
+                    const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
+                    acc += (double)f16_to_f32(b->d) * d8 * (double)(sc * sumi) - (double)f16_to_f32(b->dmin) * s8 * m;
+                } else if (type == CQO_Q5K) {
+                    const blk_q5k *b = (const blk_q5k *)row + b32 / 8;
+                    const int sub = (int)(b32 % 8);
+                    uint8_t sc, m;
+                    scale_min_k4(sub, b->scales, &sc, &m);
+                    int sumi = 0;
+                    for (int i = 0; i < 32; ++i) sumi += q5k_value(b, 32 * sub + i) * q8[i];
                     const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
                     acc += (double)f16_to_f32(b->d) * d8 * (double)(sc * sumi) - (double)f16_to_f32(b->dmin) * s8 * m;
                 } else if (type == CQO_Q6K) {

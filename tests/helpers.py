@@ -2,9 +2,9 @@
 import numpy as np
 
 # reference GGML ids <-> names used in symbol names
-TYPES = {"q4_0": 2, "q8_0": 8, "q4_k": 12, "q6_k": 14}
-BLOCK = {2: 32, 8: 32, 12: 256, 14: 256}
-TSIZE = {2: 18, 8: 34, 12: 144, 14: 210}
+TYPES = {"q4_0": 2, "q8_0": 8, "q4_k": 12, "q5_k": 13, "q6_k": 14}
+BLOCK = {2: 32, 8: 32, 12: 256, 13: 256, 14: 256}
+TSIZE = {2: 18, 8: 34, 12: 144, 13: 176, 14: 210}
 
 
 def pad(p, q):

@@ -70,7 +70,7 @@ def test_block_integer_dots_exact(lib, oracle, cuda_dev, tname, k, n):
     nblk = k // capi.BLOCK_ELEMS[wt]
     for act, oracle_dots, act_blocks in (
         (capi.ACT_Q8_1, oracle.cuda_block_dots, None),
-        (capi.ACT_Q8_K if nblk * 256 == k and wt in (12, 14) else capi.ACT_Q8_0, oracle.cpu_block_dots, "cpu"),
+        (capi.ACT_Q8_K if nblk * 256 == k and wt in (12, 13, 14) else capi.ACT_Q8_0, oracle.cpu_block_dots, "cpu"),
     ):
         y = torch.zeros((pad(k, 512) // 32 * 36,), dtype=torch.uint8, device=cuda_dev)
         lib.cq_quantize_act(x_dev.data_ptr(), capi.F32, y.data_ptr(), k, pad(k, 512), 1, act, _stream())
@@ -108,7 +108,7 @@ def test_cpu_exact_mode_matches_cpu_vec_dot(lib, oracle, cuda_dev, tname, k, n, 
     if k % capi.BLOCK_ELEMS[wt]:
         pytest.skip("K not a multiple of the block size")
     _, x, wq = make_case(oracle, wt, k, n, b, seed=3 * k + n)
-    act = capi.ACT_Q8_K if wt in (12, 14) else capi.ACT_Q8_0
+    act = capi.ACT_Q8_K if wt in (12, 13, 14) else capi.ACT_Q8_0
     w_dev = torch.from_numpy(wq).to(cuda_dev)
     x_dev = torch.from_numpy(x).to(cuda_dev)
     kp = pad(k, 512)

@@ -13,7 +13,7 @@ from candle_b200 import capi
 from helpers import TYPES, make_case, pad, rel_err
 
 pytestmark = pytest.mark.gpu
-LAYOUT = {"q4_0": "DS4", "q8_0": "D4", "q4_k": "DS4", "q6_k": "D4"}     # fast_mmq.rs:58-72
+LAYOUT = {"q4_0": "DS4", "q8_0": "D4", "q4_k": "DS4", "q5_k": "DS4", "q6_k": "D4"}     # fast_mmq.rs:58-72
 GROUP = 144
 
 

@@ -81,6 +81,7 @@ def _test_vector2(bound, size):
 
 @pytest.mark.parametrize("name,probe,tol,tol_big", [
     ("Q4K", [-0.5, -0.373, -0.25, 0.0, 0.288, 0.498], 0.017, 4.5),     # quantized_tests.rs:846-891
+    ("Q5K", [-0.5, -0.373, -0.25, 0.0, 0.279, 0.499], 0.009, 2.5),     # quantized_tests.rs:893-938
     ("Q6K", [-0.497, -0.372, -0.25, -0.0, 0.284, 0.5], 0.008, 2.0),    # quantized_tests.rs:940-985
     ("Q8K", [-0.5, -0.374, -0.25, -0.0, 0.283, 0.499], 0.008, 0.6),    # quantized_tests.rs:987-1032
 ])
@@ -97,10 +98,10 @@ def test_k_quant_roundtrip_probes(oracle, name, probe, tol, tol_big):
     assert np.abs(dbig - big).max() < tol_big
 
 
-GGML_ERR = {"Q4_0": 0.001143, "Q8_0": 0.000092, "Q4K": 0.002425, "Q6K": 0.000952}   # quantized_tests.rs:1101-1122
+GGML_ERR = {"Q4_0": 0.001143, "Q8_0": 0.000092, "Q4K": 0.002425, "Q5K": 0.000740, "Q6K": 0.000952}   # quantized_tests.rs:1101-1122
 
 
-@pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "Q4K", "Q6K"])
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "Q4K", "Q5K", "Q6K"])
 @pytest.mark.parametrize("variant", [0, 1])
 def test_ggml_matmul_error(oracle, name, variant):
     """candle-core/tests/quantized_tests.rs:1126-1191: opt == unopt within 1e-6 * len, matmul == vec_dot,
@@ -131,7 +132,7 @@ def test_ggml_matmul_error(oracle, name, variant):
         assert err <= 0.02 and err - 1e-5 <= GGML_ERR[name] * err_m
 
 
-@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q8_0", 0.002), ("Q4K", 0.002), ("Q6K", 0.002)])
+@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q8_0", 0.002), ("Q4K", 0.002), ("Q5K", 0.002), ("Q6K", 0.002)])
 def test_quantization_rmse(oracle, name, limit):
     """ggml_quantization_error_test, candle-core/tests/quantized_tests.rs:531-552 (limits :14-17)."""
     dt = getattr(oracle, name)
@@ -154,6 +155,6 @@ def test_batch_invariance(oracle):
 def test_degenerate_blocks_do_not_trap(oracle):
     """All-zero super-blocks: Q6K makes iscale = -128/0 (k_quants.rs:2122-2127); casts saturate, nothing traps."""
     z = np.zeros(512, dtype=np.float32)
-    for dt in (oracle.Q4_0, oracle.Q8_0, oracle.Q4K, oracle.Q6K, oracle.Q8K):
+    for dt in (oracle.Q4_0, oracle.Q8_0, oracle.Q4K, oracle.Q5K, oracle.Q6K, oracle.Q8K):
         d = oracle.dequantize(dt, oracle.quantize(dt, z), 512)[0]
         assert np.all(d == 0)
