@@ -11,13 +11,13 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "lib", "libcandle_q_b200.so")
 
 # GGML type ids / element kinds / activation encodings (include/candle_q_b200.h)
-Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 2, 3, 6, 7, 8, 10, 11, 12, 13, 14
 F32, F16, BF16 = 0, 1, 2
 ACT_Q8_1, ACT_Q8_0, ACT_Q8_K = 0, 1, 2
 
-TYPE_SIZE = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210}
-BLOCK_ELEMS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256}
-TYPE_NAME = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k"}
+TYPE_SIZE = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34, Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210}
+BLOCK_ELEMS = {Q4_0: 32, Q4_1: 32, Q5_0: 32, Q5_1: 32, Q8_0: 32, Q2_K: 256, Q3_K: 256, Q4_K: 256, Q5_K: 256, Q6_K: 256}
+TYPE_NAME = {Q4_0: "q4_0", Q4_1: "q4_1", Q5_0: "q5_0", Q5_1: "q5_1", Q8_0: "q8_0", Q2_K: "q2_k", Q3_K: "q3_k", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k"}
 ELEM_NAME = {F32: "f32", F16: "f16", BF16: "bf16"}
 
 STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "device-side timeout"}

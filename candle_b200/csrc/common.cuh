@@ -14,7 +14,7 @@
 #define CQ_Q8_BYTES 36  // one activation block: 4 scale bytes + 32 int8
 
 // GGML type ids (candle-core/src/quantized/mod.rs:300-342)
-enum CqType : int { CQ_Q4_0 = 2, CQ_Q8_0 = 8, CQ_Q4_K = 12, CQ_Q5_K = 13, CQ_Q6_K = 14 };
+enum CqType : int { CQ_Q4_0 = 2, CQ_Q4_1 = 3, CQ_Q5_0 = 6, CQ_Q5_1 = 7, CQ_Q8_0 = 8, CQ_Q2_K = 10, CQ_Q3_K = 11, CQ_Q4_K = 12, CQ_Q5_K = 13, CQ_Q6_K = 14 };
 // Output / input element types of the launchers
 enum CqElem : int { CQ_F32 = 0, CQ_F16 = 1, CQ_BF16 = 2 };
 // Activation encodings.  All three use the same 36-byte container per 32 elements
@@ -26,12 +26,12 @@ enum CqElem : int { CQ_F32 = 0, CQ_F16 = 1, CQ_BF16 = 2 };
 //   CQ_ACT_Q8_K : float d (the same for the 8 containers of a 256-element super-block),
 //                 iscale = -127/max, q = round(iscale*x).  What candle's CPU path uses for K-quants
 //                 (k_quants.rs:2320-2358).  bsums are not stored: kernels recompute them exactly.
-//   CQ_ACT_MMQ_D4 / CQ_ACT_MMQ_DS4 (internal to the launch_mmq_* entry points): the reference's 144-byte
+//   CQ_ACT_MMQ_D4 / CQ_ACT_MMQ_DS4 / CQ_ACT_MMQ_D2S6 (internal to the launch_mmq_* entry points): the reference's 144-byte
 //                 block_q8_1_mmq groups of 128 values (four f32 d, or four half2 (d, sum), then 128 int8), stored
 //                 [group][token] (candle-kernels/src/mmq_gguf/mmq_quantize.cu:12-106).  Same arithmetic as Q8_1.
-enum CqAct : int { CQ_ACT_Q8_1 = 0, CQ_ACT_Q8_0 = 1, CQ_ACT_Q8_K = 2, CQ_ACT_MMQ_D4 = 3, CQ_ACT_MMQ_DS4 = 4 };
+enum CqAct : int { CQ_ACT_Q8_1 = 0, CQ_ACT_Q8_0 = 1, CQ_ACT_Q8_K = 2, CQ_ACT_MMQ_D4 = 3, CQ_ACT_MMQ_DS4 = 4, CQ_ACT_MMQ_D2S6 = 5 };
 #define CQ_MMQ_GROUP_BYTES 144
-__host__ __device__ constexpr bool cq_act_q8_1_like(int act) { return act == CQ_ACT_Q8_1 || act == CQ_ACT_MMQ_D4 || act == CQ_ACT_MMQ_DS4; }
+__host__ __device__ constexpr bool cq_act_q8_1_like(int act) { return act == CQ_ACT_Q8_1 || act == CQ_ACT_MMQ_D4 || act == CQ_ACT_MMQ_DS4 || act == CQ_ACT_MMQ_D2S6; }
 
 // Status codes kept in a process-wide side channel (the reference launchers return void).
 enum CqStatus : int {
@@ -54,10 +54,10 @@ static_assert(sizeof(cq_block_q4_K) == 144, "q4_K");
 static_assert(sizeof(cq_block_q6_K) == 210, "q6_K");
 
 __host__ __device__ constexpr int cq_type_size(int t) {
-    return t == CQ_Q4_0 ? 18 : t == CQ_Q8_0 ? 34 : t == CQ_Q4_K ? 144 : t == CQ_Q5_K ? 176 : t == CQ_Q6_K ? 210 : 0;
+    return t == CQ_Q4_0 ? 18 : t == CQ_Q4_1 ? 20 : t == CQ_Q5_0 ? 22 : t == CQ_Q5_1 ? 24 : t == CQ_Q8_0 ? 34 : t == CQ_Q2_K ? 84 : t == CQ_Q3_K ? 110 : t == CQ_Q4_K ? 144 : t == CQ_Q5_K ? 176 : t == CQ_Q6_K ? 210 : 0;
 }
 __host__ __device__ constexpr int cq_block_elems(int t) {
-    return (t == CQ_Q4_K || t == CQ_Q5_K || t == CQ_Q6_K) ? CQ_QK_K : CQ_QK;
+    return (t == CQ_Q2_K || t == CQ_Q3_K || t == CQ_Q4_K || t == CQ_Q5_K || t == CQ_Q6_K) ? CQ_QK_K : CQ_QK;
 }
 
 // ---- status side channel (defined in status.cu) ----

@@ -31,6 +31,23 @@ template <int TYPE> __device__ __forceinline__ void unit_values(const uint8_t *r
             const int q = j < 16 ? (ldb(b + 2 + j) & 0xF) : (ldb(b + 2 + j - 16) >> 4);
             v[i] = __fmul_rn((float)(q - 8), d);
         }
+    } else if constexpr (TYPE == CQ_Q4_1 || TYPE == CQ_Q5_0 || TYPE == CQ_Q5_1) {
+        // k_quants.rs:392-412 (q * d + m), :496-518 ((q - 16) * d), :604-629 (q * d + m); bit e of qh belongs to element e
+        constexpr bool FIVE = TYPE != CQ_Q4_1, HAS_M = TYPE != CQ_Q5_0;
+        const uint8_t *b = row + (u * 8 + e0 / 32) * cq_type_size(TYPE);
+        const float d = ldh(b), m = HAS_M ? ldh(b + 2) : 0.0f;
+        const uint8_t *ph = b + (HAS_M ? 4 : 2), *pq = ph + (FIVE ? 4 : 0);
+        uint32_t qh = 0;
+        if constexpr (FIVE) qh = (uint32_t)ph[0] | ((uint32_t)ph[1] << 8) | ((uint32_t)ph[2] << 16) | ((uint32_t)ph[3] << 24);
+        const int j0 = e0 % 32;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int j = j0 + i;
+            int q = j < 16 ? (ldb(pq + j) & 0xF) : (ldb(pq + j - 16) >> 4);
+            if constexpr (FIVE) q |= (int)((qh >> j) & 1u) << 4;
+            if constexpr (TYPE == CQ_Q5_0) v[i] = __fmul_rn((float)(q - 16), d);
+            else v[i] = __fadd_rn(__fmul_rn((float)q, d), m);
+        }
     } else if constexpr (TYPE == CQ_Q4_K) {
         const uint8_t *b = row + u * 144;
         const float d = ldh(b), dmin = ldh(b + 2);
@@ -61,6 +78,29 @@ template <int TYPE> __device__ __forceinline__ void unit_values(const uint8_t *r
             const int nib = (sub & 1) ? (q[i] >> 4) : (q[i] & 0xF);
             const float to_add = ((qh[i] >> sub) & 1) ? 16.0f : 0.0f;
             v[i] = __fsub_rn(__fmul_rn(d1, __fadd_rn((float)nib, to_add)), m1);
+        }
+    } else if constexpr (TYPE == CQ_Q2_K) {         // k_quants.rs:1013-1049: d * (sc & 0xF) * q - dmin * (sc >> 4)
+        const uint8_t *b = row + u * 84;
+        const float d = ldh(b + 80), dmin = ldh(b + 82);
+        const int n = e0 / 128, pos = (e0 % 128) / 32, l0 = e0 % 32;
+        const int sc = ldb(b + 8 * n + 2 * pos + l0 / 16);
+        const float dl = __fmul_rn(d, (float)(sc & 0xF)), ml = __fmul_rn(dmin, (float)(sc >> 4));
+        const uint8_t *q = b + 16 + 32 * n + l0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fsub_rn(__fmul_rn(dl, (float)((q[i] >> (2 * pos)) & 3)), ml);
+    } else if constexpr (TYPE == CQ_Q3_K) {         // k_quants.rs:1372-1421: d * (scale - 32) * (q - (mask bit ? 0 : 4))
+        const uint8_t *b = row + u * 110;
+        const float d = ldh(b + 108);
+        const int n = e0 / 128, pos = (e0 % 128) / 32, l0 = e0 % 32;
+        const int j = 8 * n + 2 * pos + l0 / 16;
+        const int lo = j < 8 ? (ldb(b + 96 + j) & 0xF) : (ldb(b + 96 + j - 8) >> 4);
+        const int sc = (lo | (((ldb(b + 104 + (j & 3)) >> (2 * (j >> 2))) & 3) << 4)) - 32;
+        const float dl = __fmul_rn(d, (float)sc);
+        const uint8_t *q = b + 32 + 32 * n + l0, *hm = b + l0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int val = ((q[i] >> (2 * pos)) & 3) - (((hm[i] >> (4 * n + pos)) & 1) ? 0 : 4);
+            v[i] = __fmul_rn(dl, (float)val);
         }
     } else {        // Q6_K
         const uint8_t *b = row + u * 210;
@@ -130,7 +170,12 @@ bool dispatch(int wtype, const void *w, const int32_t *ids, void *out, int out_k
               cudaStream_t st) {
     switch (wtype) {
     case CQ_Q4_0: launch_rows<CQ_Q4_0>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
+    case CQ_Q4_1: launch_rows<CQ_Q4_1>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
+    case CQ_Q5_0: launch_rows<CQ_Q5_0>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
+    case CQ_Q5_1: launch_rows<CQ_Q5_1>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q8_0: launch_rows<CQ_Q8_0>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
+    case CQ_Q2_K: launch_rows<CQ_Q2_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
+    case CQ_Q3_K: launch_rows<CQ_Q3_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q4_K: launch_rows<CQ_Q4_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q5_K: launch_rows<CQ_Q5_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;
     case CQ_Q6_K: launch_rows<CQ_Q6_K>(w, ids, out, out_kind, k, out_rows, n_rows, st); return true;

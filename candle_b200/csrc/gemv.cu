@@ -220,11 +220,26 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
         case CQ_Q4_0:
             return cpu_act ? launch_type<CQ_Q4_0, CQ_ACT_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
                            : launch_type<CQ_Q4_0, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q4_1:
+            return cpu_act ? launch_type<CQ_Q4_1, CQ_ACT_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q4_1, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q5_0:
+            return cpu_act ? launch_type<CQ_Q5_0, CQ_ACT_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q5_0, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q5_1:
+            return cpu_act ? launch_type<CQ_Q5_1, CQ_ACT_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q5_1, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
         case CQ_Q8_0:   // same formula for both encodings
             return launch_type<CQ_Q8_0, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
         case CQ_Q4_K:
             return cpu_act ? launch_type<CQ_Q4_K_WIDE, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
                            : launch_type<CQ_Q4_K_WIDE, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q2_K:
+            return cpu_act ? launch_type<CQ_Q2_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q2_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
+        case CQ_Q3_K:
+            return cpu_act ? launch_type<CQ_Q3_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
+                           : launch_type<CQ_Q3_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
         case CQ_Q5_K:
             return cpu_act ? launch_type<CQ_Q5_K, CQ_ACT_Q8_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)
                            : launch_type<CQ_Q5_K, CQ_ACT_Q8_1>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st);
@@ -283,7 +298,7 @@ extern "C" int cq_device_timeout_flag(void) {
     return v;
 }
 
-// The reference's fifteen symbols for the five formats (candle-kernels/src/ffi.rs:61-393).
+// The reference's thirty symbols for its ten formats (candle-kernels/src/ffi.rs:61-393).
 #define CQ_MMVQ_PLAIN(name, wtype, kind)                                                                          \
     extern "C" void name(const void *vx, const void *vy, void *dst, int ncols_x, int nrows_x, int stride_col_y,  \
                          int stride_col_dst, int b_size, void *stream) {                                         \
@@ -299,6 +314,21 @@ CQ_MMVQ_PLAIN(launch_mmvq_gguf_q8_0_bf16_plain, CQ_Q8_0, CQ_BF16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_f32_plain, CQ_Q4_K, CQ_F32)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_f16_plain, CQ_Q4_K, CQ_F16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_k_bf16_plain, CQ_Q4_K, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_1_f32_plain, CQ_Q4_1, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_1_f16_plain, CQ_Q4_1, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q4_1_bf16_plain, CQ_Q4_1, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_0_f32_plain, CQ_Q5_0, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_0_f16_plain, CQ_Q5_0, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_0_bf16_plain, CQ_Q5_0, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_1_f32_plain, CQ_Q5_1, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_1_f16_plain, CQ_Q5_1, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_1_bf16_plain, CQ_Q5_1, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q2_k_f32_plain, CQ_Q2_K, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q2_k_f16_plain, CQ_Q2_K, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q2_k_bf16_plain, CQ_Q2_K, CQ_BF16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q3_k_f32_plain, CQ_Q3_K, CQ_F32)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q3_k_f16_plain, CQ_Q3_K, CQ_F16)
+CQ_MMVQ_PLAIN(launch_mmvq_gguf_q3_k_bf16_plain, CQ_Q3_K, CQ_BF16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_k_f32_plain, CQ_Q5_K, CQ_F32)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_k_f16_plain, CQ_Q5_K, CQ_F16)
 CQ_MMVQ_PLAIN(launch_mmvq_gguf_q5_k_bf16_plain, CQ_Q5_K, CQ_BF16)
@@ -329,14 +359,19 @@ __global__ void block_dots_kernel(const uint8_t *__restrict__ w, const uint8_t *
         cw.load(wrow, chunk);
         if constexpr (TYPE == CQ_Q4_0) {
             if (ACT == CQ_ACT_Q8_1) s += cw.idot(a); else s += cw.idot(a) - 8 * a.sq[0];
-        } else if constexpr (TYPE == CQ_Q8_0) s += cw.idot(a);
+        } else if constexpr (TYPE == CQ_Q5_0) {
+            if (ACT == CQ_ACT_Q8_1) s += cw.idot(a); else s += cw.idot(a) - 16 * a.sq[0];
+        } else if constexpr (TYPE == CQ_Q8_0 || TYPE == CQ_Q4_1 || TYPE == CQ_Q5_1) s += cw.idot(a);
         else if constexpr (TYPE == CQ_Q4_K || TYPE == CQ_Q5_K) {
             int d0, d1;
             cw.idots(a, d0, d1);
             s += d0 * cw.sc[0] + d1 * cw.sc[1];
             sm += a.sq[0] * cw.mn[0] + a.sq[1] * cw.mn[1];
         } else {
-            for (int p = 0; p < 4; ++p) s += cw.idot(a, p) * cw.sc[p];
+            for (int p = 0; p < 4; ++p) {
+                s += cw.idot(a, p) * cw.sc[p];
+                if constexpr (TYPE == CQ_Q2_K) sm += cw.mn[p] * a.sq[p];
+            }
         }
     }
     out[idx] = s;
@@ -360,10 +395,30 @@ extern "C" void cq_block_dots(int wtype, int act, const void *vx, const void *vy
         if (cpu) block_dots_kernel<CQ_Q4_0, CQ_ACT_Q8_0><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
         else block_dots_kernel<CQ_Q4_0, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
         break;
+    case CQ_Q4_1:
+        if (cpu) block_dots_kernel<CQ_Q4_1, CQ_ACT_Q8_0><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q4_1, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q5_0:
+        if (cpu) block_dots_kernel<CQ_Q5_0, CQ_ACT_Q8_0><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q5_0, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q5_1:
+        if (cpu) block_dots_kernel<CQ_Q5_1, CQ_ACT_Q8_0><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q5_1, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
     case CQ_Q8_0: block_dots_kernel<CQ_Q8_0, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x); break;
     case CQ_Q4_K:
         if (cpu) block_dots_kernel<CQ_Q4_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
         else block_dots_kernel<CQ_Q4_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q2_K:
+        if (cpu) block_dots_kernel<CQ_Q2_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q2_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        break;
+    case CQ_Q3_K:
+        if (cpu) block_dots_kernel<CQ_Q3_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
+        else block_dots_kernel<CQ_Q3_K, CQ_ACT_Q8_1><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);
         break;
     case CQ_Q5_K:
         if (cpu) block_dots_kernel<CQ_Q5_K, CQ_ACT_Q8_K><<<grid, 128, 0, st>>>(w, y, out, out_min, ncols_x, nrows_x);

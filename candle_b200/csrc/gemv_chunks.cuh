@@ -6,6 +6,7 @@
 //   Q4_K : 16 bytes of nibbles          (32 elements: 16 of sub-block 2j and 16 of sub-block 2j+1)
 //   Q5_K : 32 bytes of nibbles + the 32 bytes of fifth bits  (64 elements: the two sub-blocks of a pair)
 //   Q6_K : 16+16 bytes ql, 16 bytes qh  (64 elements: 16 at each of the four 32-apart positions)
+//   Q2_K : 16 bytes of 2-bit values; Q3_K : the same plus 16 bytes of the high-bit mask  (64 elements, as Q6_K)
 //
 // A lane keeps the int8 activations of its chunk (for every batch row) in registers and walks over
 // weight rows, so activations are fetched once per kernel instead of once per row as in the reference
@@ -37,6 +38,11 @@ template <> struct ChunkGeom<CQ_Q8_0> { static constexpr int BASE = CQ_Q8_0, ELE
 template <> struct ChunkGeom<CQ_Q4_K> { static constexpr int BASE = CQ_Q4_K, ELEMS = 32, Q8_BLOCKS = 2, WORDS = 8; };
 template <> struct ChunkGeom<CQ_Q4_K_WIDE> { static constexpr int BASE = CQ_Q4_K, ELEMS = 64, Q8_BLOCKS = 2, WORDS = 16; };
 template <> struct ChunkGeom<CQ_Q5_K> { static constexpr int BASE = CQ_Q5_K, ELEMS = 64, Q8_BLOCKS = 2, WORDS = 16; };
+template <> struct ChunkGeom<CQ_Q4_1> { static constexpr int BASE = CQ_Q4_1, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q5_0> { static constexpr int BASE = CQ_Q5_0, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q5_1> { static constexpr int BASE = CQ_Q5_1, ELEMS = 32, Q8_BLOCKS = 1, WORDS = 8; };
+template <> struct ChunkGeom<CQ_Q2_K> { static constexpr int BASE = CQ_Q2_K, ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
+template <> struct ChunkGeom<CQ_Q3_K> { static constexpr int BASE = CQ_Q3_K, ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
 template <> struct ChunkGeom<CQ_Q6_K> { static constexpr int BASE = CQ_Q6_K, ELEMS = 64, Q8_BLOCKS = 4, WORDS = 16; };
 
 // Activation registers of one chunk for one batch row.
@@ -53,7 +59,7 @@ __device__ __forceinline__ int cq_ld_global_i32(const uint8_t *p) { return *rein
 
 // Which activation block (relative to the first block of the row) and which byte range a chunk needs.
 template <int TYPE> __device__ __forceinline__ void chunk_act_coords(int chunk, int i, int &blk, int &byte0) {
-    if constexpr (TYPE == CQ_Q4_0 || TYPE == CQ_Q8_0) { blk = chunk; byte0 = 0; }
+    if constexpr (TYPE == CQ_Q4_0 || TYPE == CQ_Q4_1 || TYPE == CQ_Q5_0 || TYPE == CQ_Q5_1 || TYPE == CQ_Q8_0) { blk = chunk; byte0 = 0; }
     else if constexpr (TYPE == CQ_Q4_K) {
         const int sb = chunk >> 3, c = chunk & 7;
         blk = sb * 8 + 2 * (c >> 1) + i; byte0 = 16 * (c & 1);
@@ -70,7 +76,7 @@ template <int TYPE> __device__ __forceinline__ void chunk_act_coords(int chunk, 
 template <int TYPE, int ACT>
 __device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t *yrow, int chunk, int64_t group_stride = 0) {
     constexpr int NB = ChunkAct<TYPE>::NB, WPB = ChunkAct<TYPE>::WPB;
-    constexpr bool MMQ = ACT == CQ_ACT_MMQ_D4 || ACT == CQ_ACT_MMQ_DS4;
+    constexpr bool MMQ = ACT == CQ_ACT_MMQ_D4 || ACT == CQ_ACT_MMQ_DS4 || ACT == CQ_ACT_MMQ_D2S6;
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
         int blk, byte0;
@@ -92,6 +98,15 @@ __device__ __forceinline__ void chunk_load_act(ChunkAct<TYPE> &a, const uint8_t 
             sq = cq_dp4a(0x01010101, v, sq);
         }
         a.sq[i] = sq;
+        if constexpr (ACT == CQ_ACT_MMQ_D2S6) {
+            // Group header: two f16 scales (one per 64 values), then the f16 sums of the first six 16-value runs
+            // (candle-kernels/src/mmq_gguf/mmq_gguf.cuh:60-78, layout D2S6).  A chunk holds run 2 * (blk & 3) + h of its group.
+            const uint8_t *g = yrow + (int64_t)(blk >> 2) * group_stride;
+            const int run = 2 * (blk & 3) + (byte0 >> 4);
+            a.d[i] = __half2float(*reinterpret_cast<const __half *>(g + 2 * ((blk & 3) >> 1)));
+            a.s[i] = run < 6 ? __half2float(*reinterpret_cast<const __half *>(g + 4 + 2 * run)) : 0.0f;
+            continue;
+        }
         const int ds = cq_ld_global_i32(p);
         if constexpr (ACT == CQ_ACT_Q8_K || ACT == CQ_ACT_MMQ_D4) {
             a.d[i] = __int_as_float(ds);
@@ -134,6 +149,58 @@ template <> struct ChunkW<CQ_Q4_0> {
         else return __fmul_rn(__fmul_rn((float)(s - 8 * a.sq[0]), d), a.d[0]);
     }
 };
+
+// Q4_1, Q5_0, Q5_1: one 32-element block per chunk.  Elements 0..15 are the low nibbles, 16..31 the high nibbles; the
+// 5-bit formats add bit e of the little-endian word qh to element e (candle-core/src/quantized/k_quants.rs:323-351,
+// 434-455, 529-559; candle-kernels/src/mmvq_gguf.cu:208-274).  Codes stay unsigned here; Q5_0's "- 16" is applied
+// by the formula, like Q4_0's "- 8".
+__device__ __forceinline__ uint32_t cq_spread4(uint32_t n) { return ((n & 0xFu) * 0x00204081u) & 0x01010101u; }   // bit i -> bit 8 i
+
+template <int TYPE> struct ChunkW32 {
+    static constexpr bool FIVE = TYPE != CQ_Q4_1, HAS_M = TYPE != CQ_Q5_0;
+    uint32_t lo[4], hi[4];
+    float d, m;
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const uint8_t *b = row + chunk * cq_type_size(TYPE);
+        d = __half2float(__ushort_as_half((unsigned short)cq_lds_u16(b)));
+        m = HAS_M ? __half2float(__ushort_as_half((unsigned short)cq_lds_u16(b + 2))) : 0.0f;
+        const uint8_t *pq = b + (HAS_M ? 4 : 2);
+        if constexpr (FIVE) {
+            uint32_t t[5];
+            cq_lds_words<5>(pq, t);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                lo[w] = (t[1 + w] & 0x0F0F0F0Fu) | (cq_spread4(t[0] >> (4 * w)) << 4);
+                hi[w] = ((t[1 + w] >> 4) & 0x0F0F0F0Fu) | (cq_spread4(t[0] >> (16 + 4 * w)) << 4);
+            }
+        } else {
+            uint32_t q[4];
+            cq_lds_words<4>(pq, q);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) { lo[w] = q[w] & 0x0F0F0F0Fu; hi[w] = (q[w] >> 4) & 0x0F0F0F0Fu; }
+        }
+    }
+    __device__ __forceinline__ int idot(const ChunkAct<TYPE> &a) const {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { s = cq_dp4a((int)lo[w], a.u[w], s); s = cq_dp4a((int)hi[w], a.u[4 + w], s); }
+        return s;
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<TYPE> &a) const {
+        const int s = idot(a);
+        if constexpr (TYPE == CQ_Q5_0) {
+            if constexpr (ACT == CQ_ACT_Q8_1) return __fmul_rn(d, __fmaf_rn(cq_small_int_to_float(s), a.d[0], __fmul_rn(-16.0f, a.s[0])));
+            else if constexpr (ACT == CQ_ACT_MMQ_D4) return __fmul_rn(__fmul_rn(d, a.d[0]), (float)(s - 16 * a.sq[0]));   // signed tiles, D4
+            else return __fmul_rn(__fmul_rn((float)(s - 16 * a.sq[0]), d), a.d[0]);
+        } else {
+            if constexpr (cq_act_q8_1_like(ACT)) return __fmaf_rn(cq_small_int_to_float(s), __fmul_rn(d, a.d[0]), __fmul_rn(m, a.s[0]));
+            else return __fadd_rn(__fmul_rn(__fmul_rn((float)s, d), a.d[0]), __fmul_rn(m, a.s[0]));      // CPU: BlockQ8_1 with its own s
+        }
+    }
+};
+template <> struct ChunkW<CQ_Q4_1> : ChunkW32<CQ_Q4_1> {};
+template <> struct ChunkW<CQ_Q5_0> : ChunkW32<CQ_Q5_0> {};
+template <> struct ChunkW<CQ_Q5_1> : ChunkW32<CQ_Q5_1> {};
 
 template <> struct ChunkW<CQ_Q8_0> {
     uint32_t q[8];
@@ -294,6 +361,107 @@ template <> struct ChunkW<CQ_Q5_K> {
             const int isd = d0 * sc[0] + d1 * sc[1];
             const int ism = a.sq[0] * mn[0] + a.sq[1] * mn[1];
             return __fmul_rn(a.d[0], __fmaf_rn(d, (float)isd, -__fmul_rn(dmin, (float)ism)));
+        }
+    }
+};
+
+// Q2_K and Q3_K share Q6_K's geometry: chunk (super-block, 128-half n, 16-element half h) holds 16 elements at each of
+// the four 32-apart positions p, and position p has scale number 8n + 2p + h
+// (candle-core/src/quantized/k_quants.rs:1013-1049, 1372-1421; candle-kernels/src/mmvq_gguf.cu:293-334, 492-531).
+template <> struct ChunkW<CQ_Q2_K> {
+    uint32_t q[4];      // 16 bytes: four 2-bit values each
+    float d, dmin;
+    __half dh, dminh;
+    int sc[4], mn[4];
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const int sb = chunk >> 2, n = (chunk >> 1) & 1, h = chunk & 1;
+        const uint8_t *b = row + sb * 84;
+        cq_lds_words<4>(b + 16 + 32 * n + 16 * h, q);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) { const int s = b[8 * n + h + 2 * p]; sc[p] = s & 0xF; mn[p] = s >> 4; }
+        dh = __ushort_as_half((unsigned short)cq_lds_u16(b + 80));
+        dminh = __ushort_as_half((unsigned short)cq_lds_u16(b + 82));
+        d = __half2float(dh);
+        dmin = __half2float(dminh);
+    }
+    __device__ __forceinline__ int idot(const ChunkAct<CQ_Q2_K> &a, int p) const {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) s = cq_dp4a((int)((q[w] >> (2 * p)) & 0x03030303u), a.u[4 * p + w], s);
+        return s;
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q2_K> &a) const {
+        if constexpr (ACT == CQ_ACT_MMQ_D2S6) {
+            // The reference's tile kernel (mmq_gguf.cuh:1518-1575, mmq_vecdotq.cuh:388-437): scale and minimum are
+            // multiplied into f16 first; the first 96 values of a 128-group take the stored sums of the floats, the
+            // last 32 (position 3 of a chunk) the int8 sums times the group's scale.
+            float acc = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float dx = __half2float(__hmul(dh, __int2half_rn(sc[p]))), dm = __half2float(__hmul(dminh, __int2half_rn(mn[p])));
+                acc = __fmaf_rn(a.d[p], __fmul_rn(dx, cq_small_int_to_float(idot(a, p))), acc);
+                if (p < 3) acc = __fmaf_rn(-dm, a.s[p], acc);
+                else acc = __fmaf_rn(-a.d[p], __fmul_rn(dm, cq_small_int_to_float(a.sq[p])), acc);
+            }
+            return acc;
+        } else if constexpr (cq_act_q8_1_like(ACT)) {
+            float sd = 0.0f, sm = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                sd = __fmaf_rn(a.d[p], cq_small_int_to_float(idot(a, p) * sc[p]), sd);
+                sm = __fmaf_rn(a.d[p], cq_small_int_to_float(mn[p] * a.sq[p]), sm);
+            }
+            return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));
+        } else {
+            int is = 0, im = 0;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) { is += idot(a, p) * sc[p]; im += mn[p] * a.sq[p]; }
+            return __fmul_rn(a.d[0], __fmaf_rn(d, (float)is, -__fmul_rn(dmin, (float)im)));
+        }
+    }
+};
+
+template <> struct ChunkW<CQ_Q3_K> {
+    uint32_t q[4][4];   // [position][word], signed bytes -4..3
+    float d;
+    int sc[4];
+    __device__ __forceinline__ void load(const uint8_t *row, int chunk) {
+        const int sb = chunk >> 2, n = (chunk >> 1) & 1, h = chunk & 1;
+        const uint8_t *b = row + sb * 110;
+        uint32_t ql[4], hm[4];
+        cq_lds_words<4>(b + 32 + 32 * n + 16 * h, ql);
+        cq_lds_words<4>(b + 16 * h, hm);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                // value = two bits, plus 4 when the mask bit is set, minus 4: bytes 0..7 minus 4 without borrows
+                const uint32_t u = ((ql[w] >> (2 * p)) & 0x03030303u) | (((hm[w] >> (4 * n + p)) & 0x01010101u) << 2);
+                q[p][w] = ((u | 0x80808080u) - 0x04040404u) ^ 0x80808080u;
+            }
+            const int j = 8 * n + h + 2 * p;
+            const int lo = j < 8 ? (b[96 + j] & 0xF) : (b[96 + j - 8] >> 4);
+            sc[p] = (lo | (((b[104 + (j & 3)] >> (2 * (j >> 2))) & 3) << 4)) - 32;
+        }
+        d = __half2float(__ushort_as_half((unsigned short)cq_lds_u16(b + 108)));
+    }
+    __device__ __forceinline__ int idot(const ChunkAct<CQ_Q3_K> &a, int p) const {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) s = cq_dp4a((int)q[p][w], a.u[4 * p + w], s);
+        return s;
+    }
+    template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q3_K> &a) const {
+        if constexpr (cq_act_q8_1_like(ACT)) {
+            float sf = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) sf = __fmaf_rn(a.d[p], cq_small_int_to_float(idot(a, p) * sc[p]), sf);
+            return __fmul_rn(d, sf);
+        } else {
+            int is = 0;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) is += idot(a, p) * sc[p];
+            return __fmul_rn(__fmul_rn(a.d[0], d), (float)is);
         }
     }
 };

@@ -89,7 +89,7 @@ const char *dtype_name(GgmlDType t) {
 }
 
 bool kernels_support(GgmlDType t) {
-    return t == GgmlDType::Q4_0 || t == GgmlDType::Q8_0 || t == GgmlDType::Q4K || t == GgmlDType::Q5K || t == GgmlDType::Q6K;
+    return t == GgmlDType::Q4_0 || t == GgmlDType::Q4_1 || t == GgmlDType::Q5_0 || t == GgmlDType::Q5_1 || t == GgmlDType::Q8_0 || t == GgmlDType::Q2K || t == GgmlDType::Q3K || t == GgmlDType::Q4K || t == GgmlDType::Q5K || t == GgmlDType::Q6K;
 }
 
 void set_act_mode(ActMode m) { g_act_mode.store((int)m); }

@@ -189,7 +189,12 @@ CQ_MMQ_QUANTIZE(launch_mmq_quantize_q8_1_D2S6, 2)
         launch_mmq<TYPE, ACT>(x, y, dst, ncols_x, nrows_x, ncols_y, stride_row_x, stride_col_dst, stream);                  \
     }
 CQ_MMQ_GEMM(launch_mmq_gguf_q4_0, CQ_Q4_0, CQ_ACT_MMQ_DS4)
+CQ_MMQ_GEMM(launch_mmq_gguf_q4_1, CQ_Q4_1, CQ_ACT_MMQ_DS4)
+CQ_MMQ_GEMM(launch_mmq_gguf_q5_0, CQ_Q5_0, CQ_ACT_MMQ_D4)
+CQ_MMQ_GEMM(launch_mmq_gguf_q5_1, CQ_Q5_1, CQ_ACT_MMQ_DS4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q8_0, CQ_Q8_0, CQ_ACT_MMQ_D4)
+CQ_MMQ_GEMM(launch_mmq_gguf_q2_k, CQ_Q2_K, CQ_ACT_MMQ_D2S6)
+CQ_MMQ_GEMM(launch_mmq_gguf_q3_k, CQ_Q3_K, CQ_ACT_MMQ_D4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q4_k, CQ_Q4_K_WIDE, CQ_ACT_MMQ_DS4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q5_k, CQ_Q5_K, CQ_ACT_MMQ_DS4)
 CQ_MMQ_GEMM(launch_mmq_gguf_q6_k, CQ_Q6_K, CQ_ACT_MMQ_D4)

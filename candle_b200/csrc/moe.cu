@@ -102,6 +102,8 @@ bool dispatch(int wtype, int act, const MoeArgs &a, int K, int N, int jobs, cuda
     case CQ_Q8_0: return launch_moe<CQ_Q8_0, CQ_ACT_Q8_1>(a, K, N, jobs, st);
     case CQ_Q4_0: return cpu ? launch_moe<CQ_Q4_0, CQ_ACT_Q8_0>(a, K, N, jobs, st) : launch_moe<CQ_Q4_0, CQ_ACT_Q8_1>(a, K, N, jobs, st);
     case CQ_Q4_K: return cpu ? launch_moe<CQ_Q4_K_WIDE, CQ_ACT_Q8_K>(a, K, N, jobs, st) : launch_moe<CQ_Q4_K_WIDE, CQ_ACT_Q8_1>(a, K, N, jobs, st);
+    case CQ_Q2_K: return cpu ? launch_moe<CQ_Q2_K, CQ_ACT_Q8_K>(a, K, N, jobs, st) : launch_moe<CQ_Q2_K, CQ_ACT_Q8_1>(a, K, N, jobs, st);
+    case CQ_Q3_K: return cpu ? launch_moe<CQ_Q3_K, CQ_ACT_Q8_K>(a, K, N, jobs, st) : launch_moe<CQ_Q3_K, CQ_ACT_Q8_1>(a, K, N, jobs, st);
     case CQ_Q5_K: return cpu ? launch_moe<CQ_Q5_K, CQ_ACT_Q8_K>(a, K, N, jobs, st) : launch_moe<CQ_Q5_K, CQ_ACT_Q8_1>(a, K, N, jobs, st);
     case CQ_Q6_K: return cpu ? launch_moe<CQ_Q6_K, CQ_ACT_Q8_K>(a, K, N, jobs, st) : launch_moe<CQ_Q6_K, CQ_ACT_Q8_1>(a, K, N, jobs, st);
     }
@@ -126,7 +128,7 @@ bool check_common(const void *w, const void *y, const void *out, int wtype, int 
 }
 
 int wtype_of_moe_code(int code) {      // candle-kernels/src/ffi.rs:36: Q8_0: 0, Q4K: 1, Q2K: 2, Q3K: 3, Q5K: 4, Q6K: 5
-    return code == 0 ? CQ_Q8_0 : code == 1 ? CQ_Q4_K : code == 4 ? CQ_Q5_K : code == 5 ? CQ_Q6_K : -1;
+    return code == 0 ? CQ_Q8_0 : code == 1 ? CQ_Q4_K : code == 2 ? CQ_Q2_K : code == 3 ? CQ_Q3_K : code == 4 ? CQ_Q5_K : code == 5 ? CQ_Q6_K : -1;
 }
 
 }  // namespace

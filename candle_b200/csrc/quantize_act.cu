@@ -108,6 +108,13 @@ __global__ void __launch_bounds__(256) quantize_act32_kernel(const T *__restrict
                 q[c] = (int)r;
             }
         }
+        int isum = 0;
+        if (ACT != CQ_ACT_Q8_1) {
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) isum += q[c];
+#pragma unroll
+            for (int m = LPB / 2; m > 0; m >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, m);
+        }
         if (active) {
             const int blk = ix / 32, in_blk = ix % 32;
             uint8_t *out = y + ((int64_t)row * (k_padded / 32) + blk) * CQ_Q8_BYTES;
@@ -116,7 +123,10 @@ __global__ void __launch_bounds__(256) quantize_act32_kernel(const T *__restrict
             for (int c = 0; c < VEC; c += 4) qs[c / 4] = pack4(q[c], q[c + 1], q[c + 2], q[c + 3]);
             if (in_blk == 0) {
                 const __half hd = __float2half_rn(d);
-                const __half hs = (ACT == CQ_ACT_Q8_1) ? __float2half_rn(sum) : __ushort_as_half(0);
+                // CPU encoding: the `s` of the CPU's BlockQ8_1, f16(sum of q) * d rounded to f16 (k_quants.rs:789-797),
+                // so that the container serves both BlockQ8_0 (s ignored) and BlockQ8_1 readers.
+                const __half hs = (ACT == CQ_ACT_Q8_1) ? __float2half_rn(sum)
+                                                       : __float2half_rn(__fmul_rn(__half2float(__float2half_rn((float)isum)), __half2float(hd)));
                 *reinterpret_cast<__half2 *>(out) = __halves2half2(hd, hs);
             }
         }

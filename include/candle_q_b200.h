@@ -47,6 +47,21 @@ CQ_DECL_MMVQ(launch_mmvq_gguf_q8_0_bf16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_f32_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_f16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q4_k_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_1_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_1_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q4_1_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_0_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_0_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_0_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_1_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_1_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q5_1_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q2_k_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q2_k_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q2_k_bf16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q3_k_f32_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q3_k_f16_plain);
+CQ_DECL_MMVQ(launch_mmvq_gguf_q3_k_bf16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q5_k_f32_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q5_k_f16_plain);
 CQ_DECL_MMVQ(launch_mmvq_gguf_q5_k_bf16_plain);
@@ -93,6 +108,11 @@ CQ_DECL_MMQ_QUANT(launch_mmq_quantize_q8_1_D2S6);
 CQ_DECL_MMQ(launch_mmq_gguf_q4_0);
 CQ_DECL_MMQ(launch_mmq_gguf_q8_0);
 CQ_DECL_MMQ(launch_mmq_gguf_q4_k);
+CQ_DECL_MMQ(launch_mmq_gguf_q4_1);
+CQ_DECL_MMQ(launch_mmq_gguf_q5_0);
+CQ_DECL_MMQ(launch_mmq_gguf_q5_1);
+CQ_DECL_MMQ(launch_mmq_gguf_q2_k);
+CQ_DECL_MMQ(launch_mmq_gguf_q3_k);
 CQ_DECL_MMQ(launch_mmq_gguf_q5_k);
 CQ_DECL_MMQ(launch_mmq_gguf_q6_k);
 #undef CQ_DECL_MMQ
@@ -107,6 +127,11 @@ int cq_mmq_timeout_flag(void);
 #define CQ_TYPE_Q4_0 2
 #define CQ_TYPE_Q8_0 8
 #define CQ_TYPE_Q4_K 12
+#define CQ_TYPE_Q4_1 3
+#define CQ_TYPE_Q5_0 6
+#define CQ_TYPE_Q5_1 7
+#define CQ_TYPE_Q2_K 10
+#define CQ_TYPE_Q3_K 11
 #define CQ_TYPE_Q5_K 13
 #define CQ_TYPE_Q6_K 14
 /* element types of dense inputs / outputs */

@@ -42,14 +42,19 @@
 typedef _Float16 f16_t; /* IEEE binary16, conversions round to nearest even like half::f16 */
 
 /* GGML type ids, candle-core/src/quantized/mod.rs:300-342 */
-enum { CQO_Q4_0 = 2, CQO_Q8_0 = 8, CQO_Q8_1 = 9, CQO_Q4K = 12, CQO_Q5K = 13, CQO_Q6K = 14, CQO_Q8K = 15 };
+enum { CQO_Q4_0 = 2, CQO_Q4_1 = 3, CQO_Q5_0 = 6, CQO_Q5_1 = 7, CQO_Q8_0 = 8, CQO_Q8_1 = 9, CQO_Q2K = 10, CQO_Q3K = 11, CQO_Q4K = 12, CQO_Q5K = 13, CQO_Q6K = 14, CQO_Q8K = 15 };
 
 /* Block layouts, candle-core/src/quantized/k_quants.rs:77-190 (all packed, little endian). */
 #pragma pack(push, 1)
 typedef struct { f16_t d; uint8_t qs[16]; } blk_q4_0;                               /* 18 B  */
+typedef struct { f16_t d; f16_t m; uint8_t qs[16]; } blk_q4_1;                      /* 20 B  */
+typedef struct { f16_t d; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_0;                /* 22 B  */
+typedef struct { f16_t d; f16_t m; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_1;       /* 24 B  */
 typedef struct { f16_t d; int8_t qs[32]; } blk_q8_0;                                /* 34 B  */
 typedef struct { f16_t d; f16_t s; int8_t qs[32]; } blk_q8_1;                       /* 36 B  */
 typedef struct { f16_t d; f16_t dmin; uint8_t scales[12]; uint8_t qs[128]; } blk_q4k; /* 144 B */
+typedef struct { uint8_t scales[16]; uint8_t qs[64]; f16_t d; f16_t dmin; } blk_q2k;                 /* 84 B  */
+typedef struct { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; f16_t d; } blk_q3k;           /* 110 B */
 typedef struct { f16_t d; f16_t dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; } blk_q5k; /* 176 B */
 typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; f16_t d; } blk_q6k; /* 210 B */
 typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } blk_q8k;             /* 292 B */
@@ -58,9 +63,14 @@ typedef struct { union { float d4[4]; f16_t ds4[8]; }; int8_t qs[128]; } blk_q8_
 #pragma pack(pop)
 
 _Static_assert(sizeof(blk_q4_0) == 18, "q4_0");
+_Static_assert(sizeof(blk_q4_1) == 20, "q4_1");
+_Static_assert(sizeof(blk_q5_0) == 22, "q5_0");
+_Static_assert(sizeof(blk_q5_1) == 24, "q5_1");
 _Static_assert(sizeof(blk_q8_0) == 34, "q8_0");
 _Static_assert(sizeof(blk_q8_1) == 36, "q8_1");
 _Static_assert(sizeof(blk_q4k) == 144, "q4k");
+_Static_assert(sizeof(blk_q2k) == 84, "q2k");
+_Static_assert(sizeof(blk_q3k) == 110, "q3k");
 _Static_assert(sizeof(blk_q5k) == 176, "q5k");
 _Static_assert(sizeof(blk_q6k) == 210, "q6k");
 _Static_assert(sizeof(blk_q8k) == 292, "q8k");
@@ -68,12 +78,13 @@ _Static_assert(sizeof(blk_q8_1_mmq) == 144, "q8_1_mmq");
 
 int cqo_type_size(int t) {
     switch (t) {
-    case CQO_Q4_0: return 18; case CQO_Q8_0: return 34; case CQO_Q8_1: return 36;
-    case CQO_Q4K: return 144; case CQO_Q5K: return 176; case CQO_Q6K: return 210; case CQO_Q8K: return 292;
+    case CQO_Q4_0: return 18; case CQO_Q4_1: return 20; case CQO_Q5_0: return 22; case CQO_Q5_1: return 24;
+    case CQO_Q8_0: return 34; case CQO_Q8_1: return 36;
+    case CQO_Q2K: return 84; case CQO_Q3K: return 110; case CQO_Q4K: return 144; case CQO_Q5K: return 176; case CQO_Q6K: return 210; case CQO_Q8K: return 292;
     }
     return 0;
 }
-int cqo_block_size(int t) { return (t == CQO_Q4K || t == CQO_Q5K || t == CQO_Q6K || t == CQO_Q8K) ? QK_K : QK; }
+int cqo_block_size(int t) { return (t == CQO_Q2K || t == CQO_Q3K || t == CQO_Q4K || t == CQO_Q5K || t == CQO_Q6K || t == CQO_Q8K) ? QK_K : QK; }
 int cqo_have_avx2(void) { return CQO_HAVE_AVX2; }
 
 /* Minimal parallel-for over [0, n): contiguous static chunks on `nthreads` pthreads (<= 0: all
@@ -156,6 +167,80 @@ void cqo_quantize_q4_0(const float *x, void *vy, int64_t k) {
             y[i].qs[j] = (uint8_t)(a | (b << 4));
         }
     }
+}
+
+/* BlockQ4_1::from_float, k_quants.rs:353-389 */
+void cqo_quantize_q4_1(const float *x, void *vy, int64_t k) {
+    blk_q4_1 *y = (blk_q4_1 *)vy;
+    for (int64_t i = 0; i < k / QK; ++i) {
+        const float *xs = x + i * QK;
+        float mn = INFINITY, mx = -INFINITY;
+        for (int j = 0; j < QK; ++j) { mn = fminf(xs[j], mn); mx = fmaxf(xs[j], mx); }
+        const float d = (mx - mn) / 15.0f;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        y[i].d = f32_to_f16(d);
+        y[i].m = f32_to_f16(mn);
+        for (int j = 0; j < QK / 2; ++j) {
+            uint8_t a = sat_u8((xs[j] - mn) * id + 0.5f), b = sat_u8((xs[QK / 2 + j] - mn) * id + 0.5f);
+            if (a > 15) a = 15;
+            if (b > 15) b = 15;
+            y[i].qs[j] = (uint8_t)(a | (b << 4));
+        }
+    }
+}
+
+/* BlockQ5_0::from_float, k_quants.rs:457-493 */
+void cqo_quantize_q5_0(const float *x, void *vy, int64_t k) {
+    blk_q5_0 *y = (blk_q5_0 *)vy;
+    for (int64_t i = 0; i < k / QK; ++i) {
+        const float *xs = x + i * QK;
+        float amax = 0.f, max = 0.f;
+        for (int j = 0; j < QK; ++j)
+            if (amax < fabsf(xs[j])) { amax = fabsf(xs[j]); max = xs[j]; }
+        const float d = max / -16.0f;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        y[i].d = f32_to_f16(d);
+        uint32_t qh = 0;
+        for (int j = 0; j < QK / 2; ++j) {
+            int8_t a = sat_i8(xs[j] * id + 16.5f), b = sat_i8(xs[j + QK / 2] * id + 16.5f);
+            if (a > 31) a = 31;
+            if (b > 31) b = 31;
+            const uint8_t xi0 = (uint8_t)a, xi1 = (uint8_t)b;
+            y[i].qs[j] = (uint8_t)((xi0 & 0x0F) | ((xi1 & 0x0F) << 4));
+            qh |= (uint32_t)((xi0 & 0x10) >> 4) << j;
+            qh |= (uint32_t)((xi1 & 0x10) >> 4) << (j + QK / 2);
+        }
+        memcpy(y[i].qh, &qh, 4);
+    }
+}
+
+/* BlockQ5_1::from_float, k_quants.rs:562-601 */
+void cqo_quantize_q5_1(const float *x, void *vy, int64_t k) {
+    blk_q5_1 *y = (blk_q5_1 *)vy;
+    for (int64_t i = 0; i < k / QK; ++i) {
+        const float *xs = x + i * QK;
+        float mn = INFINITY, mx = -INFINITY;
+        for (int j = 0; j < QK; ++j) { mn = fminf(xs[j], mn); mx = fmaxf(xs[j], mx); }
+        const float d = (mx - mn) / 31.0f;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        y[i].d = f32_to_f16(d);
+        y[i].m = f32_to_f16(mn);
+        uint32_t qh = 0;
+        for (int j = 0; j < QK / 2; ++j) {
+            const uint8_t xi0 = sat_u8((xs[j] - mn) * id + 0.5f), xi1 = sat_u8((xs[QK / 2 + j] - mn) * id + 0.5f);
+            y[i].qs[j] = (uint8_t)((xi0 & 0x0F) | ((xi1 & 0x0F) << 4));
+            qh |= (uint32_t)((xi0 & 0x10) >> 4) << j;
+            qh |= (uint32_t)((xi1 & 0x10) >> 4) << (j + QK / 2);
+        }
+        memcpy(y[i].qh, &qh, 4);
+    }
+}
+
+/* Element e (0..31) of a 32-element block as the unsigned code the formats store: 4 bits, or 4 bits plus the qh bit. */
+static inline int q4_code(const uint8_t *qs, int e) { return e < 16 ? (qs[e] & 0xF) : (qs[e - 16] >> 4); }
+static inline int q5_code(const uint8_t *qs, const uint8_t *qh, int e) {
+    uint32_t h; memcpy(&h, qh, 4);
+    return q4_code(qs, e) | (int)(((h >> e) & 1u) << 4);
 }
 
 /* BlockQ8_0::from_float, k_quants.rs:658-687 */
@@ -306,6 +391,144 @@ void cqo_quantize_q4k(const float *x, void *vy, int64_t k) {
         }
         for (int j = 0; j < QK_K; j += 64)
             for (int t = 0; t < 32; ++t) b->qs[(j / 64) * 32 + t] = (uint8_t)(l[j + t] | (l[j + t + 32] << 4));
+    }
+}
+
+/* element e (0..255) of a Q2K / Q3K block: both pack four 32-apart positions of a 128-half into one byte, and give every
+ * run of 16 elements its own scale; index of that scale: 8 * half + 2 * position + (l / 16). */
+static inline int q2k_value(const blk_q2k *b, int e) {
+    const int n = e / 128, p = (e % 128) / 32, l = e % 32;
+    return (b->qs[32 * n + l] >> (2 * p)) & 3;
+}
+static inline int q3k_value(const blk_q3k *b, int e) {     /* -4 .. 3 */
+    const int n = e / 128, p = (e % 128) / 32, l = e % 32;
+    return (int)((b->qs[32 * n + l] >> (2 * p)) & 3) - (((b->hmask[l] >> (4 * n + p)) & 1) ? 0 : 4);
+}
+static inline int q23k_scale_index(int e) { return 8 * (e / 128) + 2 * ((e % 128) / 32) + (e % 32) / 16; }
+static inline int q3k_scale(const blk_q3k *b, int j) {      /* 6-bit scale j minus 32, k_quants.rs:1227-1233 */
+    const int lo = j < 8 ? (b->scales[j] & 0xF) : (b->scales[j - 8] >> 4);
+    return (lo | (((b->scales[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32;
+}
+
+/* BlockQ2K::from_float, k_quants.rs:891-953 */
+void cqo_quantize_q2k(const float *x, void *vy, int64_t k) {
+    blk_q2k *y = (blk_q2k *)vy;
+    for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+        const float *xb = x + ib * QK_K;
+        blk_q2k *b = &y[ib];
+        float mins[16], scales[16];
+        for (int j = 0; j < 16; ++j) make_qkx1(3, 5, xb + 16 * j, 16, &scales[j], &mins[j]);
+        float max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 16; ++j) { max_scale = fmaxf(scales[j], max_scale); max_min = fmaxf(mins[j], max_min); }
+        if (max_scale > 0.f) {
+            const float iscale = 15.0f / max_scale;
+            for (int j = 0; j < 16; ++j) b->scales[j] = (uint8_t)clampi(nearest_int(iscale * scales[j]), 0, 255);
+            b->d = f32_to_f16(max_scale / 15.0f);
+        } else {
+            memset(b->scales, 0, 16);
+            b->d = f32_to_f16(0.f);
+        }
+        if (max_min > 0.f) {
+            const float iscale = 15.0f / max_min;
+            for (int j = 0; j < 16; ++j) b->scales[j] |= (uint8_t)((uint8_t)clampi(nearest_int(iscale * mins[j]), 0, 255) << 4);
+            b->dmin = f32_to_f16(max_min / 15.0f);
+        } else {
+            b->dmin = f32_to_f16(0.f);
+        }
+        uint8_t L[QK_K];
+        memset(L, 0, sizeof L);
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_to_f32(b->d) * (float)(b->scales[j] & 0xF);
+            if (d == 0.f) continue;
+            const float dm = f16_to_f32(b->dmin) * (float)(b->scales[j] >> 4);
+            for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (uint8_t)clampi(nearest_int((xb[16 * j + ii] + dm) / d), 0, 3);
+        }
+        for (int j = 0; j < QK_K; j += 128)
+            for (int l = 0; l < 32; ++l)
+                b->qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+/* make_q3_quants(x, nmax, do_rmse = true), utils.rs:287-352: returns the scale */
+static float make_q3(const float *x, int n, int nmax) {
+    int8_t l[32];
+    float max = 0.f, amax = 0.f;
+    for (int i = 0; i < n; ++i) { const float ax = fabsf(x[i]); if (ax > amax) { amax = ax; max = x[i]; } }
+    if (amax == 0.f) return 0.f;
+    const float iscale = -(float)nmax / max;
+    float sumlx = 0.f, suml2 = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const int32_t li = clampi(nearest_int(iscale * x[i]), -nmax, nmax - 1);
+        l[i] = (int8_t)li;
+        const float w = x[i] * x[i];
+        sumlx += w * x[i] * (float)li;
+        suml2 += w * (float)(li * li);
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int n_changed = 0;
+        for (int i = 0; i < n; ++i) {
+            const float w = x[i] * x[i];
+            float slx = sumlx - w * x[i] * (float)l[i];
+            if (slx > 0.f) {
+                float sl2 = suml2 - w * (float)((int32_t)l[i] * (int32_t)l[i]);
+                const int32_t new_l = clampi(nearest_int(x[i] * sl2 / slx), -nmax, nmax - 1);
+                if (new_l != (int32_t)l[i]) {
+                    slx += w * x[i] * (float)new_l;
+                    sl2 += w * (float)(new_l * new_l);
+                    if (sl2 > 0.f && slx * slx * suml2 > sumlx * sumlx * sl2) {
+                        l[i] = (int8_t)new_l;
+                        sumlx = slx; suml2 = sl2;
+                        ++n_changed;
+                    }
+                }
+            }
+        }
+        if (!n_changed) break;
+    }
+    return sumlx / suml2;
+}
+
+/* BlockQ3K::from_float, k_quants.rs:1190-1268 */
+void cqo_quantize_q3k(const float *x, void *vy, int64_t k) {
+    blk_q3k *y = (blk_q3k *)vy;
+    for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+        const float *xb = x + ib * QK_K;
+        blk_q3k *b = &y[ib];
+        float scales[16];
+        for (int j = 0; j < 16; ++j) scales[j] = make_q3(xb + 16 * j, 16, 4);
+        float max_scale = 0.f;
+        for (int j = 0; j < 16; ++j) if (fabsf(scales[j]) > fabsf(max_scale)) max_scale = scales[j];
+        memset(b->scales, 0, 12);
+        if (max_scale != 0.f) {
+            const float iscale = -32.0f / max_scale;
+            for (int j = 0; j < 16; ++j) {
+                int32_t lv = clampi(nearest_int(iscale * scales[j]), -32, 31) + 32;
+                if (j < 8) b->scales[j] = (uint8_t)(lv & 0xF);
+                else b->scales[j - 8] |= (uint8_t)((lv & 0xF) << 4);
+                lv >>= 4;
+                b->scales[j % 4 + 8] |= (uint8_t)(lv << (2 * (j / 4)));
+            }
+            b->d = f32_to_f16(1.0f / iscale);
+        } else {
+            b->d = f32_to_f16(0.f);
+        }
+        int8_t L[QK_K];
+        memset(L, 0, sizeof L);
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_to_f32(b->d) * (float)q3k_scale(b, j);
+            if (d != 0.f)
+                for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (int8_t)(clampi(nearest_int(xb[16 * j + ii] / d), -4, 3) + 4);
+        }
+        memset(b->hmask, 0, 32);
+        int m = 0;
+        uint8_t hm = 1;
+        for (int e = 0; e < QK_K; ++e) {
+            if (L[e] > 3) { b->hmask[m] |= hm; L[e] -= 4; }
+            if (++m == QK_K / 8) { m = 0; hm <<= 1; }
+        }
+        for (int j = 0; j < QK_K; j += 128)
+            for (int l = 0; l < 32; ++l)
+                b->qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
     }
 }
 
@@ -480,6 +703,24 @@ void cqo_dequantize(int type, const void *vx, float *y, int64_t k) {
                 y[i * QK + j + 16] = (float)((int)(x[i].qs[j] >> 4) - 8) * d;
             }
         }
+    } else if (type == CQO_Q4_1) {         /* k_quants.rs:392-412: q * d + m */
+        const blk_q4_1 *x = (const blk_q4_1 *)vx;
+        for (int64_t i = 0; i < k / QK; ++i) {
+            const float d = f16_to_f32(x[i].d), m = f16_to_f32(x[i].m);
+            for (int j = 0; j < QK; ++j) y[i * QK + j] = (float)q4_code(x[i].qs, j) * d + m;
+        }
+    } else if (type == CQO_Q5_0) {         /* k_quants.rs:496-518: (q - 16) * d */
+        const blk_q5_0 *x = (const blk_q5_0 *)vx;
+        for (int64_t i = 0; i < k / QK; ++i) {
+            const float d = f16_to_f32(x[i].d);
+            for (int j = 0; j < QK; ++j) y[i * QK + j] = (float)(q5_code(x[i].qs, x[i].qh, j) - 16) * d;
+        }
+    } else if (type == CQO_Q5_1) {         /* k_quants.rs:604-629: q * d + m */
+        const blk_q5_1 *x = (const blk_q5_1 *)vx;
+        for (int64_t i = 0; i < k / QK; ++i) {
+            const float d = f16_to_f32(x[i].d), m = f16_to_f32(x[i].m);
+            for (int j = 0; j < QK; ++j) y[i * QK + j] = (float)q5_code(x[i].qs, x[i].qh, j) * d + m;
+        }
     } else if (type == CQO_Q8_0) {
         const blk_q8_0 *x = (const blk_q8_0 *)vx;
         for (int64_t i = 0; i < k / QK; ++i) {
@@ -500,6 +741,25 @@ void cqo_dequantize(int type, const void *vx, float *y, int64_t k) {
                 const float d2 = d * (float)sc, m2 = mn * (float)m;
                 for (int t = 0; t < 32; ++t) *o++ = d1 * (float)(q[t] & 0xF) - m1;
                 for (int t = 0; t < 32; ++t) *o++ = d2 * (float)(q[t] >> 4) - m2;
+            }
+        }
+    } else if (type == CQO_Q2K) {      /* k_quants.rs:1013-1049: dl * q - ml */
+        const blk_q2k *x = (const blk_q2k *)vx;
+        for (int64_t i = 0; i < k / QK_K; ++i) {
+            const float d = f16_to_f32(x[i].d), mn = f16_to_f32(x[i].dmin);
+            for (int e = 0; e < QK_K; ++e) {
+                const uint8_t sc = x[i].scales[q23k_scale_index(e)];
+                const float dl = d * (float)(sc & 0xF), ml = mn * (float)(sc >> 4);
+                y[i * QK_K + e] = dl * (float)q2k_value(&x[i], e) - ml;
+            }
+        }
+    } else if (type == CQO_Q3K) {      /* k_quants.rs:1372-1421: d * (scale - 32) * (q - 4 or q) */
+        const blk_q3k *x = (const blk_q3k *)vx;
+        for (int64_t i = 0; i < k / QK_K; ++i) {
+            const float d = f16_to_f32(x[i].d);
+            for (int e = 0; e < QK_K; ++e) {
+                const float dl = d * ((float)(int8_t)(q3k_scale(&x[i], q23k_scale_index(e)) + 32) - 32.0f);
+                y[i * QK_K + e] = dl * (float)q3k_value(&x[i], e);
             }
         }
     } else if (type == CQO_Q5K) {      /* k_quants.rs:1962-1995: d1 * (q + 16 * bit) - m1 */
@@ -551,8 +811,13 @@ void cqo_dequantize(int type, const void *vx, float *y, int64_t k) {
 void cqo_quantize(int type, const float *x, void *y, int64_t k) {
     switch (type) {
     case CQO_Q4_0: cqo_quantize_q4_0(x, y, k); break;
+    case CQO_Q4_1: cqo_quantize_q4_1(x, y, k); break;
+    case CQO_Q5_0: cqo_quantize_q5_0(x, y, k); break;
+    case CQO_Q5_1: cqo_quantize_q5_1(x, y, k); break;
     case CQO_Q8_0: cqo_quantize_q8_0(x, y, k); break;
     case CQO_Q8_1: cqo_quantize_q8_1_cpu(x, y, k); break;
+    case CQO_Q2K: cqo_quantize_q2k(x, y, k); break;
+    case CQO_Q3K: cqo_quantize_q3k(x, y, k); break;
     case CQO_Q4K: cqo_quantize_q4k(x, y, k); break;
     case CQO_Q5K: cqo_quantize_q5k(x, y, k); break;
     case CQO_Q6K: cqo_quantize_q6k(x, y, k); break;
@@ -627,6 +892,41 @@ static float dot_q4k_q8k_scalar(int64_t n, const blk_q4k *x, const blk_q8k *y) {
     float t = -0.0f;
     for (int l = 0; l < 8; ++l) t += sums[l];
     return sumf + t;
+}
+/* Q2K x Q8K, k_quants.rs:838-888; Q3K x Q8K, k_quants.rs:1068-1188.  As for Q5K, only the scalar order is restated. */
+static float dot_q2k_q8k_scalar(int64_t n, const blk_q2k *x, const blk_q8k *y) {
+    float sumf = 0.f;
+    for (int64_t i = 0; i < n / QK_K; ++i) {
+        int32_t summs = 0, isum = 0;
+        for (int j = 0; j < 16; ++j) summs += (int32_t)y[i].bsums[j] * (x[i].scales[j] >> 4);
+        const float dall = y[i].d * f16_to_f32(x[i].d), dmin = y[i].d * f16_to_f32(x[i].dmin);
+        for (int g = 0; g < 16; ++g) {          /* run of 16 elements in memory order of q8: e = 16 g .. */
+            int32_t isuml = 0;
+            for (int l = 0; l < 16; ++l) isuml += (int32_t)y[i].qs[16 * g + l] * q2k_value(&x[i], 16 * g + l);
+            isum += (int32_t)(x[i].scales[q23k_scale_index(16 * g)] & 0xF) * isuml;
+        }
+        sumf += dall * (float)isum - dmin * (float)summs;
+    }
+    return sumf;
+}
+static float dot_q3k_q8k_scalar(int64_t n, const blk_q3k *x, const blk_q8k *y) {
+    float sums[8] = {0};
+    for (int64_t i = 0; i < n / QK_K; ++i) {
+        int32_t aux32[8] = {0};
+        for (int g = 0; g < 16; ++g) {
+            const int32_t scale = q3k_scale(&x[i], q23k_scale_index(16 * g));
+            for (int r = 0; r < 2; ++r)
+                for (int l = 0; l < 8; ++l) {
+                    const int e = 16 * g + 8 * r + l;
+                    aux32[l] += scale * (int16_t)(y[i].qs[e] * (int8_t)q3k_value(&x[i], e));
+                }
+        }
+        const float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; ++l) sums[l] += d * (float)aux32[l];
+    }
+    float t = -0.0f;
+    for (int l = 0; l < 8; ++l) t += sums[l];
+    return t;
 }
 /* Q5K x Q8K, k_quants.rs:1714-1801.  The AVX2 variant (avx.rs) differs only in the order of the f32 additions; it is not
  * restated, every mode of cqo_vec_dot uses this one for Q5K. */
@@ -874,7 +1174,35 @@ static float dot_q6k_q8k_hw(int64_t n, const blk_q6k *x, const blk_q8k *y) {
 
 /* mode: 0 scalar (vec_dot_unopt), 1 AVX2 order in portable code, 2 AVX2 hardware */
 float cqo_vec_dot(int type, int mode, int64_t n, const void *x, const void *y) {
+    if (type == CQO_Q4_1 || type == CQO_Q5_0 || type == CQO_Q5_1) {
+        /* vec_dot_unopt, k_quants.rs:323-351 (Q4_1 x Q8_1), :434-455 (Q5_0 x Q8_0), :529-559 (Q5_1 x Q8_1); no SIMD variant */
+        float sumf = 0.f;
+        for (int64_t i = 0; i < n / QK; ++i) {
+            int32_t sumi = 0;
+            if (type == CQO_Q4_1) {
+                const blk_q4_1 *b = (const blk_q4_1 *)x + i;
+                const blk_q8_1 *a = (const blk_q8_1 *)y + i;
+                for (int j = 0; j < 16; ++j) sumi += q4_code(b->qs, j) * a->qs[j] + q4_code(b->qs, j + 16) * a->qs[j + 16];
+                sumf += (float)sumi * f16_to_f32(b->d) * f16_to_f32(a->d) + f16_to_f32(b->m) * f16_to_f32(a->s);
+            } else if (type == CQO_Q5_0) {
+                const blk_q5_0 *b = (const blk_q5_0 *)x + i;
+                const blk_q8_0 *a = (const blk_q8_0 *)y + i;
+                for (int j = 0; j < 16; ++j)
+                    sumi += (q5_code(b->qs, b->qh, j) - 16) * a->qs[j] + (q5_code(b->qs, b->qh, j + 16) - 16) * a->qs[j + 16];
+                sumf += (float)sumi * f16_to_f32(b->d) * f16_to_f32(a->d);
+            } else {
+                const blk_q5_1 *b = (const blk_q5_1 *)x + i;
+                const blk_q8_1 *a = (const blk_q8_1 *)y + i;
+                for (int j = 0; j < 16; ++j)
+                    sumi += q5_code(b->qs, b->qh, j) * a->qs[j] + q5_code(b->qs, b->qh, j + 16) * a->qs[j + 16];
+                sumf += (float)sumi * f16_to_f32(b->d) * f16_to_f32(a->d) + f16_to_f32(b->m) * f16_to_f32(a->s);
+            }
+        }
+        return sumf;
+    }
     if (type == CQO_Q5K) return dot_q5k_q8k_scalar(n, (const blk_q5k *)x, (const blk_q8k *)y);
+    if (type == CQO_Q2K) return dot_q2k_q8k_scalar(n, (const blk_q2k *)x, (const blk_q8k *)y);
+    if (type == CQO_Q3K) return dot_q3k_q8k_scalar(n, (const blk_q3k *)x, (const blk_q8k *)y);
 #if CQO_HAVE_AVX2
     if (mode == 2) {
         switch (type) {
@@ -903,7 +1231,10 @@ float cqo_vec_dot(int type, int mode, int64_t n, const void *x, const void *y) {
 }
 
 /* VecDotType of each weight type: Q4_0, Q8_0 -> Q8_0; K-quants -> Q8K (k_quants.rs:216,637,1426,2002) */
-int cqo_vec_dot_type(int type) { return (type == CQO_Q4_0 || type == CQO_Q8_0) ? CQO_Q8_0 : CQO_Q8K; }
+int cqo_vec_dot_type(int type) {
+    if (type == CQO_Q4_1 || type == CQO_Q5_1) return CQO_Q8_1;      /* k_quants.rs:317, 524 */
+    return (type == CQO_Q4_0 || type == CQO_Q5_0 || type == CQO_Q8_0) ? CQO_Q8_0 : CQO_Q8K;
+}
 
 /* Per-block integer dot products of the CPU path: out[r * nblk + i] = the int32 the block
  * contributes before any float scale.  Q4K reports sum_g sc_g * dot_g and, in out_min, sum bsums*m. */
@@ -918,6 +1249,18 @@ void cqo_cpu_block_dots(int type, int64_t k, int64_t nrows, const void *w, const
                 const blk_q8_0 *y = (const blk_q8_0 *)act + i;
                 for (int j = 0; j < 16; ++j)
                     s += ((x->qs[j] & 0xF) - 8) * y->qs[j] + ((x->qs[j] >> 4) - 8) * y->qs[j + 16];
+            } else if (type == CQO_Q4_1) {
+                const blk_q4_1 *x = (const blk_q4_1 *)w + r * nb + i;
+                const blk_q8_1 *y = (const blk_q8_1 *)act + i;
+                for (int j = 0; j < 32; ++j) s += q4_code(x->qs, j) * y->qs[j];
+            } else if (type == CQO_Q5_0) {
+                const blk_q5_0 *x = (const blk_q5_0 *)w + r * nb + i;
+                const blk_q8_0 *y = (const blk_q8_0 *)act + i;
+                for (int j = 0; j < 32; ++j) s += (q5_code(x->qs, x->qh, j) - 16) * y->qs[j];
+            } else if (type == CQO_Q5_1) {
+                const blk_q5_1 *x = (const blk_q5_1 *)w + r * nb + i;
+                const blk_q8_1 *y = (const blk_q8_1 *)act + i;
+                for (int j = 0; j < 32; ++j) s += q5_code(x->qs, x->qh, j) * y->qs[j];
             } else if (type == CQO_Q8_0) {
                 const blk_q8_0 *x = (const blk_q8_0 *)w + r * nb + i;
                 const blk_q8_0 *y = (const blk_q8_0 *)act + i;
@@ -934,6 +1277,15 @@ void cqo_cpu_block_dots(int type, int64_t k, int64_t nrows, const void *w, const
                     s += sc[g] * t;
                 }
                 for (int j = 0; j < 16; ++j) sm += (int32_t)y->bsums[j] * mn[j / 2];
+            } else if (type == CQO_Q2K) {
+                const blk_q2k *x = (const blk_q2k *)w + r * nb + i;
+                const blk_q8k *y = (const blk_q8k *)act + i;
+                for (int e = 0; e < QK_K; ++e) s += (int32_t)(x->scales[q23k_scale_index(e)] & 0xF) * q2k_value(x, e) * y->qs[e];
+                for (int j = 0; j < 16; ++j) sm += (int32_t)y->bsums[j] * (x->scales[j] >> 4);
+            } else if (type == CQO_Q3K) {
+                const blk_q3k *x = (const blk_q3k *)w + r * nb + i;
+                const blk_q8k *y = (const blk_q8k *)act + i;
+                for (int e = 0; e < QK_K; ++e) s += q3k_scale(x, q23k_scale_index(e)) * q3k_value(x, e) * y->qs[e];
             } else if (type == CQO_Q5K) {
                 const blk_q5k *x = (const blk_q5k *)w + r * nb + i;
                 const blk_q8k *y = (const blk_q8k *)act + i;
@@ -1039,6 +1391,28 @@ static float cuda_thread_dot(int type, const void *wrow, const blk_q8_1 *y, int 
         const float inner = fma ? fmaf((float)sumi, d8, -(4.0f * s8)) : (float)sumi * d8 - 4.0f * s8;
         return fma ? fmaf(d4, inner, acc) : acc + d4 * inner;
     }
+    if (type == CQO_Q4_1 || type == CQO_Q5_0 || type == CQO_Q5_1) {    /* vdr 2, qi 4; mmvq_gguf.cu:208-274, 422-474 */
+        const uint8_t *qs, *qh = NULL;
+        float d, m = 0.f;
+        if (type == CQO_Q4_1) { const blk_q4_1 *b = (const blk_q4_1 *)wrow + kbx; qs = b->qs; d = f16_to_f32(b->d); m = f16_to_f32(b->m); }
+        else if (type == CQO_Q5_0) { const blk_q5_0 *b = (const blk_q5_0 *)wrow + kbx; qs = b->qs; qh = b->qh; d = f16_to_f32(b->d); }
+        else { const blk_q5_1 *b = (const blk_q5_1 *)wrow + kbx; qs = b->qs; qh = b->qh; d = f16_to_f32(b->d); m = f16_to_f32(b->m); }
+        int32_t sumi = 0;
+        for (int i = 0; i < 2; ++i)
+            for (int e = 0; e < 4; ++e) {
+                const int j = 4 * (iqs + i) + e;
+                const int lo = qh ? q5_code(qs, qh, j) : q4_code(qs, j), hi = qh ? q5_code(qs, qh, j + 16) : q4_code(qs, j + 16);
+                sumi += lo * y->qs[j] + hi * y->qs[j + 16];
+            }
+        const float d8 = f16_to_f32(y->d), s8 = f16_to_f32(y->s);
+        if (type == CQO_Q5_0) {        /* d5 * (sumi * d8 - 8 * s8): (16 * vdr / QI5_0) = 8 */
+            const float inner = fma ? fmaf((float)sumi, d8, -(8.0f * s8)) : (float)sumi * d8 - 8.0f * s8;
+            return fma ? fmaf(d, inner, acc) : acc + d * inner;
+        }
+        /* sumi * (d * d8) + (m * s8) / 2: each of the block's two threads adds half of the m * s8 term */
+        const float dd = d * d8, ms = m * s8 * 0.5f;
+        return acc + (fma ? fmaf((float)sumi, dd, ms) : (float)sumi * dd + ms);
+    }
     if (type == CQO_Q8_0) {            /* vdr 2, qi 8 */
         const blk_q8_0 *b = (const blk_q8_0 *)wrow + kbx;
         int32_t sumi = 0;
@@ -1071,6 +1445,47 @@ static float cuda_thread_dot(int type, const void *wrow, const blk_q8_1 *y, int 
         }
         const float d = f16_to_f32(b->d), dmin = f16_to_f32(b->dmin);
         return acc + (fma ? fmaf(d, sumf_d, -(dmin * sumf_m)) : d * sumf_d - dmin * sumf_m);
+    }
+    if (type == CQO_Q2K || type == CQO_Q3K) {      /* vdr 1, qi 16, mmvq_gguf.cu:293-334, 492-531 */
+        const int off = 4 * (iqs / 8), sco = iqs - iqs % 8 + (iqs % 8) / 4;
+        float sumf_d = 0.f, sumf_m = 0.f;
+        if (type == CQO_Q2K) {
+            const blk_q2k *b = (const blk_q2k *)wrow + kbx;
+            const int32_t v = ld_i32(b->qs + 4 * iqs);
+            for (int i = 0; i < 4; ++i) {
+                const blk_q8_1 *yi = y + off + i;
+                const int32_t u = ld_i32(yi->qs + 4 * (iqs % 8));
+                const int32_t sc = b->scales[sco + 2 * i];
+                const int32_t vi = (v >> (2 * i)) & 0x03030303;
+                int32_t m = sc >> 4;
+                m |= m << 8; m |= m << 16;
+                const float d8 = f16_to_f32(yi->d);
+                if (fma) {
+                    sumf_d = fmaf(d8, (float)(dp4a(vi, u, 0) * (sc & 0xF)), sumf_d);
+                    sumf_m = fmaf(d8, (float)dp4a(m, u, 0), sumf_m);
+                } else {
+                    sumf_d += d8 * (float)(dp4a(vi, u, 0) * (sc & 0xF));
+                    sumf_m += d8 * (float)dp4a(m, u, 0);
+                }
+            }
+            const float d = f16_to_f32(b->d), dmin = f16_to_f32(b->dmin);
+            return acc + (fma ? fmaf(d, sumf_d, -(dmin * sumf_m)) : d * sumf_d - dmin * sumf_m);
+        }
+        const blk_q3k *b = (const blk_q3k *)wrow + kbx;
+        const int32_t vl = ld_i32(b->qs + 4 * iqs);
+        const int32_t vh = (int32_t)(~(uint32_t)ld_i32(b->hmask + 4 * (iqs % 8)) >> off);
+        for (int i = 0; i < 4; ++i) {
+            const blk_q8_1 *yi = y + off + i;
+            const int32_t u = ld_i32(yi->qs + 4 * (iqs % 8));
+            const int32_t sc = q3k_scale(b, sco + 2 * i);
+            const int32_t vil = (vl >> (2 * i)) & 0x03030303, vih = ((vh >> i) << 2) & 0x04040404;
+            int32_t vi = 0;
+            for (int q = 0; q < 4; ++q)
+                vi |= (int32_t)(uint8_t)(int8_t)(((vil >> (8 * q)) & 0xFF) - ((vih >> (8 * q)) & 0xFF)) << (8 * q);
+            const float d8 = f16_to_f32(yi->d);
+            sumf_d = fma ? fmaf(d8, (float)(dp4a(vi, u, 0) * sc), sumf_d) : sumf_d + d8 * (float)(dp4a(vi, u, 0) * sc);
+        }
+        return fma ? fmaf(f16_to_f32(b->d), sumf_d, acc) : acc + f16_to_f32(b->d) * sumf_d;
     }
     if (type == CQO_Q5K) {             /* vdr 2, qi 32, mmvq_gguf.cu:357-381, 568-606 */
         const blk_q5k *b = (const blk_q5k *)wrow + kbx;
@@ -1127,9 +1542,10 @@ static float cuda_thread_dot(int type, const void *wrow, const blk_q8_1 *y, int 
 
 static void cuda_lane_map(int type, int *qk, int *qi, int *vdr) {
     switch (type) {
-    case CQO_Q4_0: *qk = 32; *qi = 4; *vdr = 2; break;
+    case CQO_Q4_0: case CQO_Q4_1: case CQO_Q5_0: case CQO_Q5_1: *qk = 32; *qi = 4; *vdr = 2; break;
     case CQO_Q8_0: *qk = 32; *qi = 8; *vdr = 2; break;
     case CQO_Q4K: case CQO_Q5K: *qk = 256; *qi = 32; *vdr = 2; break;
+    case CQO_Q2K: case CQO_Q3K: *qk = 256; *qi = 16; *vdr = 1; break;
     default: *qk = 256; *qi = 32; *vdr = 1; break;
     }
 }
@@ -1196,6 +1612,15 @@ void cqo_cuda_block_dots(int type, int64_t k, int64_t nrows, const void *w, cons
             if (type == CQO_Q4_0) {
                 const blk_q4_0 *x = (const blk_q4_0 *)w + r * nb + i;
                 for (int j = 0; j < 16; ++j) s += (x->qs[j] & 0xF) * y[i].qs[j] + (x->qs[j] >> 4) * y[i].qs[j + 16];
+            } else if (type == CQO_Q4_1) {
+                const blk_q4_1 *x = (const blk_q4_1 *)w + r * nb + i;
+                for (int j = 0; j < 32; ++j) s += q4_code(x->qs, j) * y[i].qs[j];
+            } else if (type == CQO_Q5_0) {
+                const blk_q5_0 *x = (const blk_q5_0 *)w + r * nb + i;
+                for (int j = 0; j < 32; ++j) s += q5_code(x->qs, x->qh, j) * y[i].qs[j];
+            } else if (type == CQO_Q5_1) {
+                const blk_q5_1 *x = (const blk_q5_1 *)w + r * nb + i;
+                for (int j = 0; j < 32; ++j) s += q5_code(x->qs, x->qh, j) * y[i].qs[j];
             } else if (type == CQO_Q8_0) {
                 const blk_q8_0 *x = (const blk_q8_0 *)w + r * nb + i;
                 for (int j = 0; j < 32; ++j) s += (int32_t)x->qs[j] * y[i].qs[j];
@@ -1213,6 +1638,17 @@ void cqo_cuda_block_dots(int type, int64_t k, int64_t nrows, const void *w, cons
                     s += sc[g] * t;
                     sm += mn[g] * q;
                 }
+            } else if (type == CQO_Q2K) {
+                const blk_q2k *x = (const blk_q2k *)w + r * nb + i;
+                for (int e = 0; e < QK_K; ++e) {
+                    const uint8_t sc = x->scales[q23k_scale_index(e)];
+                    const int8_t a = y[8 * i + e / 32].qs[e % 32];
+                    s += (int32_t)(sc & 0xF) * q2k_value(x, e) * a;
+                    sm += (int32_t)(sc >> 4) * a;
+                }
+            } else if (type == CQO_Q3K) {
+                const blk_q3k *x = (const blk_q3k *)w + r * nb + i;
+                for (int e = 0; e < QK_K; ++e) s += q3k_scale(x, q23k_scale_index(e)) * q3k_value(x, e) * y[8 * i + e / 32].qs[e % 32];
             } else if (type == CQO_Q5K) {
                 const blk_q5k *x = (const blk_q5k *)w + r * nb + i;
                 for (int g = 0; g < 8; ++g) {
@@ -1312,6 +1748,27 @@ void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k
                     for (int i = 0; i < 16; ++i) sumi += (b->qs[i] & 0xF) * q8[i] + (b->qs[i] >> 4) * q8[i + 16];
                     const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
                     acc += (double)f16_to_f32(b->d) * ((double)sumi * d8 - 8.0 * s8);
+                } else if (type == CQO_Q4_1 || type == CQO_Q5_1) {
+                    /* DS4, tiles of unsigned codes with (d, m): d * d8 * sumi + m * s8 per 32-block
+                     * (mmq_gguf.cuh vec_dot_q8_1_q8_1_mma, f32 products) */
+                    int sumi = 0;
+                    float d, m;
+                    if (type == CQO_Q4_1) {
+                        const blk_q4_1 *b = (const blk_q4_1 *)row + b32;
+                        for (int i = 0; i < 32; ++i) sumi += q4_code(b->qs, i) * q8[i];
+                        d = f16_to_f32(b->d); m = f16_to_f32(b->m);
+                    } else {
+                        const blk_q5_1 *b = (const blk_q5_1 *)row + b32;
+                        for (int i = 0; i < 32; ++i) sumi += q5_code(b->qs, b->qh, i) * q8[i];
+                        d = f16_to_f32(b->d); m = f16_to_f32(b->m);
+                    }
+                    const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
+                    acc += (double)d * d8 * sumi + (double)m * s8;
+                } else if (type == CQO_Q5_0) {       /* D4, tiles of signed codes - 16: d * d8 * sumi */
+                    const blk_q5_0 *b = (const blk_q5_0 *)row + b32;
+                    int sumi = 0;
+                    for (int i = 0; i < 32; ++i) sumi += (q5_code(b->qs, b->qh, i) - 16) * q8[i];
+                    acc += (double)f16_to_f32(b->d) * (double)g->d4[j] * sumi;
                 } else if (type == CQO_Q8_0) {
                     const blk_q8_0 *b = (const blk_q8_0 *)row + b32;
                     int sumi = 0;
@@ -1327,6 +1784,30 @@ void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k
                     for (int i = 0; i < 32; ++i) sumi += ((sub & 1) ? (q4[i] >> 4) : (q4[i] & 0xF)) * q8[i];
                     const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
                     acc += (double)f16_to_f32(b->d) * d8 * (double)(sc * sumi) - (double)f16_to_f32(b->dmin) * s8 * m;
+                } else if (type == CQO_Q2K) {
+                    /* D2S6, mmq_gguf.cuh:1518-1575 + mmq_vecdotq.cuh:388-437: per 16-run the f16 products
+                     * d * (sc & 15) and dmin * (sc >> 4); the first six runs of a 128-group subtract the stored f16 sum
+                     * of the floats, the last two the int8 sum times the scale of their 64 values. */
+                    const blk_q2k *b = (const blk_q2k *)row + b32 / 8;
+                    const int e0 = 32 * (int)(b32 % 8);
+                    for (int hrun = 0; hrun < 2; ++hrun) {
+                        const int run = 2 * j + hrun;
+                        const uint8_t sc = b->scales[q23k_scale_index(e0 + 16 * hrun)];
+                        const float dx = f16_to_f32(f32_to_f16(f16_to_f32(b->d) * (float)(sc & 0xF)));
+                        const float dm = f16_to_f32(f32_to_f16(f16_to_f32(b->dmin) * (float)(sc >> 4)));
+                        const float d8 = f16_to_f32(g->ds4[j / 2]);
+                        int sumi = 0, sumq = 0;
+                        for (int i = 16 * hrun; i < 16 * hrun + 16; ++i) { sumi += q2k_value(b, e0 + i) * q8[i]; sumq += q8[i]; }
+                        acc += (double)d8 * dx * sumi;
+                        if (run < 6) acc -= (double)dm * f16_to_f32(g->ds4[2 + run]);
+                        else acc -= (double)d8 * dm * sumq;
+                    }
+                } else if (type == CQO_Q3K) {        /* D4: d * sum over the two 16-runs of sc * dot, times d8 */
+                    const blk_q3k *b = (const blk_q3k *)row + b32 / 8;
+                    const int e0 = 32 * (int)(b32 % 8);
+                    int tot = 0;
+                    for (int i = 0; i < 32; ++i) tot += q3k_scale(b, q23k_scale_index(e0 + i)) * q3k_value(b, e0 + i) * q8[i];
+                    acc += (double)f16_to_f32(b->d) * (double)g->d4[j] * tot;
                 } else if (type == CQO_Q5K) {
                     const blk_q5k *b = (const blk_q5k *)row + b32 / 8;
                     const int sub = (int)(b32 % 8);

@@ -19,11 +19,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libcandle_q_oracle.so")
 
 # GGML type ids (candle-core/src/quantized/mod.rs:300-342)
-Q4_0, Q8_0, Q8_1, Q4K, Q5K, Q6K, Q8K = 2, 8, 9, 12, 13, 14, 15
-TYPE_SIZE = {Q4_0: 18, Q8_0: 34, Q8_1: 36, Q4K: 144, Q5K: 176, Q6K: 210, Q8K: 292}
-BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q8_1: 32, Q4K: 256, Q5K: 256, Q6K: 256, Q8K: 256}
-NAMES = {"q4_0": Q4_0, "q8_0": Q8_0, "q8_1": Q8_1, "q4k": Q4K, "q5k": Q5K, "q6k": Q6K, "q8k": Q8K,
-         "q4_k": Q4K, "q5_k": Q5K, "q6_k": Q6K, "q8_k": Q8K}
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q2K, Q3K, Q4K, Q5K, Q6K, Q8K = 2, 3, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15
+TYPE_SIZE = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34, Q8_1: 36, Q2K: 84, Q3K: 110, Q4K: 144, Q5K: 176, Q6K: 210, Q8K: 292}
+BLOCK_SIZE = {Q4_0: 32, Q4_1: 32, Q5_0: 32, Q5_1: 32, Q8_0: 32, Q8_1: 32, Q2K: 256, Q3K: 256, Q4K: 256, Q5K: 256, Q6K: 256, Q8K: 256}
+NAMES = {"q4_0": Q4_0, "q4_1": Q4_1, "q5_0": Q5_0, "q5_1": Q5_1, "q8_0": Q8_0, "q8_1": Q8_1, "q2k": Q2K, "q3k": Q3K, "q4k": Q4K, "q5k": Q5K, "q6k": Q6K, "q8k": Q8K,
+         "q2_k": Q2K, "q3_k": Q3K, "q4_k": Q4K, "q5_k": Q5K, "q6_k": Q6K, "q8_k": Q8K}
 # dot-product accumulation orders of cqo_vec_dot
 SCALAR, SIMD_ORDER, SIMD_HW = 0, 1, 2
 
@@ -110,7 +110,7 @@ def vec_dot(dtype: int, w_row: np.ndarray, act_row: np.ndarray, k: int, mode: in
 
 
 def vec_dot_type(dtype: int) -> int:
-    return Q8_0 if dtype in (Q4_0, Q8_0) else Q8K
+    return int(lib().cqo_vec_dot_type(dtype))
 
 
 def matmul(dtype: int, lhs, w_blocks: np.ndarray, n: int, mode: int = SIMD_ORDER, nthreads: int = 0) -> np.ndarray:

@@ -2,9 +2,9 @@
 import numpy as np
 
 # reference GGML ids <-> names used in symbol names
-TYPES = {"q4_0": 2, "q8_0": 8, "q4_k": 12, "q5_k": 13, "q6_k": 14}
-BLOCK = {2: 32, 8: 32, 12: 256, 13: 256, 14: 256}
-TSIZE = {2: 18, 8: 34, 12: 144, 13: 176, 14: 210}
+TYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q2_k": 10, "q3_k": 11, "q4_k": 12, "q5_k": 13, "q6_k": 14}
+BLOCK = {2: 32, 3: 32, 6: 32, 7: 32, 8: 32, 10: 256, 11: 256, 12: 256, 13: 256, 14: 256}
+TSIZE = {2: 18, 3: 20, 6: 22, 7: 24, 8: 34, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210}
 
 
 def pad(p, q):

@@ -22,14 +22,14 @@ def declared_functions():
 
 def test_header_declares_the_reference_symbols():
     names = declared_functions()
-    for t in ("q4_0", "q8_0", "q4_k", "q5_k", "q6_k"):
+    for t in ("q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k"):
         for e in ("f32", "f16", "bf16"):
             assert f"launch_mmvq_gguf_{t}_{e}_plain" in names     # candle-kernels/src/ffi.rs:61-393
     for e in ("f32", "f16", "bf16"):
         assert f"launch_mmvq_gguf_quantize_q8_1_{e}" in names     # candle-kernels/src/ffi.rs:396-419
     for lay in ("D4", "DS4", "D2S6"):
         assert f"launch_mmq_quantize_q8_1_{lay}" in names         # candle-kernels/src/ffi.rs:424-468
-    for t in ("q4_0", "q8_0", "q4_k", "q5_k", "q6_k"):
+    for t in ("q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k"):
         assert f"launch_mmq_gguf_{t}" in names                    # candle-kernels/src/ffi.rs:471-630
     assert "moe_gemm_gguf" in names and "moe_gemm_gguf_prefill" in names      # candle-kernels/src/ffi.rs:25-56
 

@@ -70,7 +70,7 @@ def test_block_integer_dots_exact(lib, oracle, cuda_dev, tname, k, n):
     nblk = k // capi.BLOCK_ELEMS[wt]
     for act, oracle_dots, act_blocks in (
         (capi.ACT_Q8_1, oracle.cuda_block_dots, None),
-        (capi.ACT_Q8_K if nblk * 256 == k and wt in (12, 13, 14) else capi.ACT_Q8_0, oracle.cpu_block_dots, "cpu"),
+        (capi.ACT_Q8_K if nblk * 256 == k and wt in (10, 11, 12, 13, 14) else capi.ACT_Q8_0, oracle.cpu_block_dots, "cpu"),
     ):
         y = torch.zeros((pad(k, 512) // 32 * 36,), dtype=torch.uint8, device=cuda_dev)
         lib.cq_quantize_act(x_dev.data_ptr(), capi.F32, y.data_ptr(), k, pad(k, 512), 1, act, _stream())
@@ -83,14 +83,16 @@ def test_block_integer_dots_exact(lib, oracle, cuda_dev, tname, k, n):
         else:
             rd, rm = oracle_dots(wt, wq, oracle.quantize(oracle.vec_dot_type(wt), x), k, n)
         assert np.array_equal(dots.cpu().numpy(), rd)
-        if wt == 12:
+        if wt in (10, 12, 13):
             assert np.array_equal(dmin.cpu().numpy(), rm)
 
 
 def _unpack_cpu_exact(containers, wt, k):
     """Repack the library's 36-byte containers into the reference's CPU block layout for a byte compare."""
     c = containers.reshape(-1, 36)
-    if wt in (2, 8):        # BlockQ8_0: f16 d + 32 int8 (34 bytes)
+    if wt in (3, 7):        # BlockQ8_1 of the CPU path: f16 d, f16 s, 32 int8 -- the container itself
+        return c.reshape(-1)
+    if wt in (2, 6, 8):     # BlockQ8_0: f16 d + 32 int8 (34 bytes)
         return np.concatenate([c[:, 0:2], c[:, 4:36]], axis=1).reshape(-1)
     nsb = k // 256          # BlockQ8K: f32 d + 256 int8 + 16 int16 bsums (292 bytes)
     c = c[:nsb * 8].reshape(nsb, 8, 36)
@@ -108,7 +110,7 @@ def test_cpu_exact_mode_matches_cpu_vec_dot(lib, oracle, cuda_dev, tname, k, n, 
     if k % capi.BLOCK_ELEMS[wt]:
         pytest.skip("K not a multiple of the block size")
     _, x, wq = make_case(oracle, wt, k, n, b, seed=3 * k + n)
-    act = capi.ACT_Q8_K if wt in (12, 13, 14) else capi.ACT_Q8_0
+    act = capi.ACT_Q8_K if wt in (10, 11, 12, 13, 14) else capi.ACT_Q8_0
     w_dev = torch.from_numpy(wq).to(cuda_dev)
     x_dev = torch.from_numpy(x).to(cuda_dev)
     kp = pad(k, 512)

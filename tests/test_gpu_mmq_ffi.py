@@ -13,7 +13,7 @@ from candle_b200 import capi
 from helpers import TYPES, make_case, pad, rel_err
 
 pytestmark = pytest.mark.gpu
-LAYOUT = {"q4_0": "DS4", "q8_0": "D4", "q4_k": "DS4", "q5_k": "DS4", "q6_k": "D4"}     # fast_mmq.rs:58-72
+LAYOUT = {"q4_0": "DS4", "q4_1": "DS4", "q5_0": "D4", "q5_1": "DS4", "q8_0": "D4", "q2_k": "D2S6", "q3_k": "D4", "q4_k": "DS4", "q5_k": "DS4", "q6_k": "D4"}     # fast_mmq.rs:58-72
 GROUP = 144
 
 
@@ -62,7 +62,7 @@ def test_mmq_quantizer_row_gather(lib, oracle, cuda_dev):
     assert np.array_equal(got, oracle.cuda_quantize_mmq_q8_1(x[ids], "DS4", 512))
 
 
-@pytest.mark.parametrize("tname", list(TYPES))
+@pytest.mark.parametrize("tname", list(LAYOUT))
 @pytest.mark.parametrize("k,n,tokens", [(256, 3, 1), (512, 70, 9), (4096, 130, 16), (1024, 48, 37), (14336, 24, 11)])
 def test_mmq_matmul_matches_oracle(lib, oracle, cuda_dev, tname, k, n, tokens):
     wt = TYPES[tname]
@@ -72,7 +72,7 @@ def test_mmq_matmul_matches_oracle(lib, oracle, cuda_dev, tname, k, n, tokens):
     scratch = quantize_call(lib, LAYOUT[tname], x_dev, k, k_padded)
     out = torch.full((tokens * n + 16,), float("nan"), dtype=torch.float32, device=cuda_dev)
     fixup = torch.empty(1024, dtype=torch.float32, device=cuda_dev)
-    blk = 32 if tname in ("q4_0", "q8_0") else 256
+    blk = 256 if tname.endswith("_k") else 32
     getattr(lib, f"launch_mmq_gguf_{tname}")(fixup.data_ptr(), w_dev.data_ptr(), scratch.data_ptr(), out.data_ptr(), k, n, tokens,
                                             k // blk, n, 1000, 148, 232448, 32, _stream())
     capi.check("mmq matmul")

@@ -11,7 +11,7 @@ from helpers import pad, rel_err
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3
-TYPES = {"q4_k": 12, "q5_k": 13, "q6_k": 14, "q8_0": 8}
+TYPES = {"q2_k": 10, "q3_k": 11, "q4_k": 12, "q5_k": 13, "q6_k": 14, "q8_0": 8}
 
 
 def _experts(oracle, wt, e, n, k, seed):
@@ -57,7 +57,7 @@ def test_moe_gemm_gguf_sorted(oracle, cuda_dev, tname, tokens, e, topk, n, k):
     L = capi.lib()
     x2d, sp, es, twd = dev(x2), dev(sorted_pairs), dev(expert_skip), dev(tw)
     L.moe_gemm_gguf(x2d.data_ptr(), qt.device_ptr(), sp.data_ptr(), es.data_ptr(), twd.data_ptr(), out2.data_ptr(), e, topk,
-                    tokens * topk, n, k, {12: 1, 13: 4, 14: 5, 8: 0}[wt], torch.cuda.current_stream().cuda_stream)
+                    tokens * topk, n, k, {10: 2, 11: 3, 12: 1, 13: 4, 14: 5, 8: 0}[wt], torch.cuda.current_stream().cuda_stream)
     capi.check("moe down")
     out2 = out2.cpu().numpy()
     q8b = oracle.cuda_quantize_q8_1(x2, pad(k, 512))

@@ -74,12 +74,58 @@ def test_q4_0_roundtrip_vector(oracle):
     assert d.tolist() == expect
 
 
+def _round3(v):
+    """round_vector of the reference's tests: three decimals (candle-core/tests/quantized_tests.rs:1034-1040)."""
+    t = np.asarray(v, dtype=np.float32) * np.float32(1000.0)
+    r = np.copysign(np.floor(np.abs(t) + np.float32(0.5)), t).astype(np.float32)      # f32::round: halves away from zero
+    return [float(x) for x in r / np.float32(1000.0)]
+
+
+Q4_1_EXPECT = [
+    0.0, 0.0, 2.066, 2.066, 4.133, 4.133, 6.199, 6.199, 8.266, 8.266, 10.332, 10.332,
+    12.398, 12.398, 14.465, 14.465, 16.531, 16.531, 18.598, 18.598, 20.664, 20.664, 22.73,
+    22.73, 24.797, 24.797, 26.863, 26.863, 28.93, 28.93, 30.996, 30.996, 32.0, 32.0,
+    34.066, 34.066, 36.133, 36.133, 38.199, 38.199, 40.266, 40.266, 42.332, 42.332, 44.398,
+    44.398, 46.465, 46.465, 48.531, 48.531, 50.598, 50.598, 52.664, 52.664, 54.73, 54.73,
+    56.797, 56.797, 58.863, 58.863, 60.93, 60.93, 62.996, 62.996, 64.0, 64.0, 66.066,
+    66.066, 68.133, 68.133, 70.199, 70.199, 72.266, 72.266, 74.332, 74.332, 76.398, 76.398,
+    78.465, 78.465, 80.531, 80.531, 82.598, 82.598, 84.664, 84.664, 86.73, 86.73, 88.797,
+    88.797, 90.863, 90.863, 92.93, 92.93, 94.996, 94.996, 96.0, 96.0, 98.066, 98.066,
+    100.133, 100.133, 102.199, 102.199, 104.266, 104.266, 106.332, 106.332, 108.398,
+    108.398, 110.465, 110.465, 112.531, 112.531, 114.598, 114.598, 116.664, 116.664,
+    118.73, 118.73, 120.797, 120.797, 122.863, 122.863, 124.93, 124.93, 126.996, 126.996]
+Q5_0_EXPECT = [
+    -0.0, 1.938, 1.938, 3.875, 3.875, 5.813, 5.813, 7.75, 7.75, 9.688, 9.688, 11.625,
+    11.625, 13.563, 13.563, 15.5, 15.5, 17.438, 17.438, 19.375, 19.375, 21.313, 21.313,
+    23.25, 23.25, 25.188, 25.188, 27.125, 27.125, 29.063, 29.063, 31.0, 31.5, 31.5, 35.438,
+    35.438, 35.438, 35.438, 39.375, 39.375, 39.375, 39.375, 43.313, 43.313, 43.313, 43.313,
+    47.25, 47.25, 47.25, 47.25, 51.188, 51.188, 51.188, 51.188, 55.125, 55.125, 55.125,
+    55.125, 59.063, 59.063, 59.063, 59.063, 63.0, 63.0, 65.313, 65.313, 65.313, 65.313,
+    65.313, 71.25, 71.25, 71.25, 71.25, 71.25, 71.25, 77.188, 77.188, 77.188, 77.188,
+    77.188, 77.188, 83.125, 83.125, 83.125, 83.125, 83.125, 83.125, 89.063, 89.063, 89.063,
+    89.063, 89.063, 89.063, 95.0, 95.0, 95.0, 95.25, 95.25, 95.25, 95.25, 103.188, 103.188,
+    103.188, 103.188, 103.188, 103.188, 103.188, 103.188, 111.125, 111.125, 111.125,
+    111.125, 111.125, 111.125, 111.125, 111.125, 119.063, 119.063, 119.063, 119.063,
+    119.063, 119.063, 119.063, 119.063, 127.0, 127.0, 127.0, 127.0]
+
+
+@pytest.mark.parametrize("name,expect", [("Q4_1", Q4_1_EXPECT), ("Q5_0", Q5_0_EXPECT), ("Q5_1", [float(v) for v in range(128)])])
+def test_q4_1_q5_0_q5_1_roundtrip_vectors(oracle, name, expect):
+    """candle-core/tests/quantized_tests.rs:379-411 (Q4_1), :412-444 (Q5_0), :446-474 (Q5_1): 0..127 quantized and back."""
+    dt = getattr(oracle, name)
+    src = np.arange(128, dtype=np.float32)
+    d = oracle.dequantize(dt, oracle.quantize(dt, src), 128)[0]
+    assert _round3(d) == [float(np.float32(e)) for e in expect]
+
+
 def _test_vector2(bound, size):
     v = np.arange(size, dtype=np.float32)
     return ((v - np.float32(size) / np.float32(2.0)) * np.float32(bound) / (np.float32(size) / np.float32(2.0))).astype(np.float32)
 
 
 @pytest.mark.parametrize("name,probe,tol,tol_big", [
+    ("Q2K", [-0.499, -0.366, -0.249, 0.0, 0.295, 0.492], 0.1, 6.0),    # quantized_tests.rs:752-797
+    ("Q3K", [-0.493, -0.37, -0.243, -0.0, 0.292, 0.492], 0.03, 3.5),   # quantized_tests.rs:799-844
     ("Q4K", [-0.5, -0.373, -0.25, 0.0, 0.288, 0.498], 0.017, 4.5),     # quantized_tests.rs:846-891
     ("Q5K", [-0.5, -0.373, -0.25, 0.0, 0.279, 0.499], 0.009, 2.5),     # quantized_tests.rs:893-938
     ("Q6K", [-0.497, -0.372, -0.25, -0.0, 0.284, 0.5], 0.008, 2.0),    # quantized_tests.rs:940-985
@@ -98,10 +144,10 @@ def test_k_quant_roundtrip_probes(oracle, name, probe, tol, tol_big):
     assert np.abs(dbig - big).max() < tol_big
 
 
-GGML_ERR = {"Q4_0": 0.001143, "Q8_0": 0.000092, "Q4K": 0.002425, "Q5K": 0.000740, "Q6K": 0.000952}   # quantized_tests.rs:1101-1122
+GGML_ERR = {"Q4_0": 0.001143, "Q4_1": 0.008, "Q5_0": 0.001353, "Q5_1": 0.00149, "Q8_0": 0.000092, "Q2K": 0.004086, "Q3K": 0.017, "Q4K": 0.002425, "Q5K": 0.000740, "Q6K": 0.000952}   # quantized_tests.rs:1101-1122
 
 
-@pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "Q4K", "Q5K", "Q6K"])
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2K", "Q3K", "Q4K", "Q5K", "Q6K"])
 @pytest.mark.parametrize("variant", [0, 1])
 def test_ggml_matmul_error(oracle, name, variant):
     """candle-core/tests/quantized_tests.rs:1126-1191: opt == unopt within 1e-6 * len, matmul == vec_dot,
@@ -132,7 +178,7 @@ def test_ggml_matmul_error(oracle, name, variant):
         assert err <= 0.02 and err - 1e-5 <= GGML_ERR[name] * err_m
 
 
-@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q8_0", 0.002), ("Q4K", 0.002), ("Q5K", 0.002), ("Q6K", 0.002)])
+@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q4_1", 0.002), ("Q5_0", 0.002), ("Q5_1", 0.002), ("Q8_0", 0.002), ("Q2K", 0.0075), ("Q3K", 0.0040), ("Q4K", 0.002), ("Q5K", 0.002), ("Q6K", 0.002)])
 def test_quantization_rmse(oracle, name, limit):
     """ggml_quantization_error_test, candle-core/tests/quantized_tests.rs:531-552 (limits :14-17)."""
     dt = getattr(oracle, name)
@@ -155,6 +201,6 @@ def test_batch_invariance(oracle):
 def test_degenerate_blocks_do_not_trap(oracle):
     """All-zero super-blocks: Q6K makes iscale = -128/0 (k_quants.rs:2122-2127); casts saturate, nothing traps."""
     z = np.zeros(512, dtype=np.float32)
-    for dt in (oracle.Q4_0, oracle.Q8_0, oracle.Q4K, oracle.Q5K, oracle.Q6K, oracle.Q8K):
+    for dt in (oracle.Q4_0, oracle.Q4_1, oracle.Q5_0, oracle.Q5_1, oracle.Q8_0, oracle.Q2K, oracle.Q3K, oracle.Q4K, oracle.Q5K, oracle.Q6K, oracle.Q8K):
         d = oracle.dequantize(dt, oracle.quantize(dt, z), 512)[0]
         assert np.all(d == 0)
