@@ -10,18 +10,23 @@
 //      d_w * d_a * sum_g sc_g * (q4_g . q8_g)  -  dmin_w * d_a * sum_g m_g * sum(q8_g)
 // with 6-bit sc_g, m_g per 32-element sub-block.  Per-32 scales cannot be applied inside a tensor-core
 // accumulation, so they are folded into the int8 weight operand instead.  With sc = 8*sh + sl (3 bits each)
-// three int8 "planes" are built from every weight row:
-//      P1[k] = sl_g * q4[k]   (<= 105)      P2[k] = sh_g * q4[k]   (<= 105)      Mn[k] = m_g   (<= 63)
-// and  sum_g sc_g (q4_g . q8_g) = 8 * (P2 . q8) + (P1 . q8),   sum_g m_g sum(q8_g) = Mn . q8   exactly, in int32.
-// So a whole super-block (8 K-steps of 32) accumulates in TMEM and is scaled once, in f32, when it is drained.
+// two int8 "planes" are built from every weight row:
+//      P1[k] = sl_g * q4[k]   (<= 105)      P2[k] = sh_g * q4[k]   (<= 105)
+// and  sum_g sc_g (q4_g . q8_g) = 8 * (P2 . q8) + (P1 . q8)  exactly, in int32.  The second term needs only the sums
+// of the activations over 16-element runs (the bsums of BlockQ8K): the quantize kernel stores them split as
+// 64 * hi + lo (two int8 each), and ONE more K = 32 step multiplies the 16 lo and 16 hi bytes with the per-run
+// minimum, giving  sum_g m_g sum(q8_g) = L + 64 * H  in two further accumulator columns per weight row.
+// So a whole super-block (8 + 1 K-steps of 32) accumulates in TMEM and is scaled once, in f32, when it is drained.
+// (An earlier layout carried the minimum as a third replicated plane: 12 instead of 9 units of tensor time and a third
+// more shared-memory stores per super-block.)
 //
 // Mapping.  MMA M = 128 tokens (operand A = int8 activations, already laid out for the tensor core by the
-// quantize kernel, fetched with TMA bulk copies), MMA N = 3 planes x 64 weight rows = 192 (operand B, unpacked from
-// the GGUF bytes by four producer warps).  Planes sit side by side in the accumulator columns, so the epilogue
-// thread that owns a token holds all three values of every weight row and combines them locally.  Two TMEM
-// accumulator buffers (2 x 192 columns) and two shared-memory stages let unpacking, MMA and epilogue of
-// consecutive super-blocks overlap.  Warp roles: 0-3 epilogue (TMEM lane quadrant = warp), 4-7 producers, 8 MMA,
-// 9 activation loader (TMA).
+// quantize kernel, fetched with TMA bulk copies), MMA N = 2 planes x 64 weight rows = 128 (operand B, unpacked from
+// the GGUF bytes by eight producer warps).  Planes sit side by side in the accumulator columns, so the epilogue
+// thread that owns a token holds all four values of a weight row and combines them locally.  Two TMEM
+// accumulator buffers (2 x 256 columns) and two shared-memory stages let unpacking, MMA and epilogue of
+// consecutive super-blocks overlap.  Warp roles: 0-7 epilogue (TMEM lane quadrant = warp % 4, half of the weight rows
+// each), 8-15 producers, 16 MMA, 17 activation loader (TMA).
 //
 // Every wait is bounded (about a second); a give-up raises a CTA-wide abort flag, all roles leave their loops,
 // TMEM is released and a device flag is set for the host.
@@ -32,18 +37,22 @@ namespace {
 
 constexpr int kTokTile = 128;      // MMA M
 constexpr int kRowTile = 64;       // weight rows per CTA
-constexpr int kPlanes = 3;
-constexpr int kN = kPlanes * kRowTile;                 // MMA N = 192
+constexpr int kPlanes = 2;
+constexpr int kN = kPlanes * kRowTile;                 // MMA N = 128: [plane 0 of 64 rows | plane 1 of 64 rows]
 constexpr int kSlabA = kTokTile * 16;                  // bytes of one 16-byte-wide K slab of A in shared memory
 constexpr int kSlabB = kN * 16;
-constexpr int kStageA = 16 * kSlabA;                   // 32 KiB: 128 tokens x 256 int8
-constexpr int kStageB = 16 * kSlabB;                   // 48 KiB: 192 rows x 256 int8
+constexpr int kSlabsA = 18;                            // 16 slabs of int8 activations + 2 of split block sums
+constexpr int kStageA = kSlabsA * kSlabA;              // 36 KiB
+constexpr int kStageB = 18 * kSlabB;                   // 36 KiB: 128 rows x 256 int8, then the 128 x 32 operand of the sums MMA
+constexpr int kTokBytes = 16 * kSlabsA + 4;            // scratch bytes per (token, super-block): 288 operand bytes + f32 d
+constexpr int kAccCols = 2 * kN;                       // accumulator columns per buffer: products, then sums
 constexpr int kStagesA = 3, kStagesB = 2;
-constexpr int kThreads = 10 * 32;
+constexpr int kEpiWarps = 8, kProdWarps = 8;
+constexpr int kThreads = (kEpiWarps + kProdWarps + 2) * 32;
 constexpr int kSmemBytes = 1024 + kStagesA * kStageA + kStagesB * kStageB + 2 * 8 * 512;
 
 __device__ int g_prefill_timeout_flag = 0;
-int g_prefill_dbg = 0;   // experiment switch: bit 0 skips the producers' work, bit 1 the epilogue's (results are then garbage)
+int g_prefill_dbg = 0;   // experiment switch: bit 0 skips the producers' work, bit 1 the epilogue's, bit 2 the MMA warp's waits for both (results are then garbage)
 
 // ---- tcgen05 wrappers ----
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, int ncols) {
@@ -80,6 +89,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -127,7 +141,7 @@ struct TileBlob {   // where the activations of (token tile, super-block) live i
         return (size_t)((r + 7) / 8 * 8);
     }
     __host__ __device__ static size_t offset(int tokens, int nsb, int tt, int sb) {
-        return (size_t)tt * kTokTile * 260 * nsb + (size_t)sb * tile_rows(tokens, tt) * 260;
+        return (size_t)tt * kTokTile * kTokBytes * nsb + (size_t)sb * tile_rows(tokens, tt) * kTokBytes;
     }
 };
 
@@ -172,7 +186,15 @@ __device__ __forceinline__ void quantize_q8k_row_part(const T *xr, uint8_t *blob
     packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
     packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
     *reinterpret_cast<int2 *>(blob + (size_t)(lane >> 1) * rows * 16 + (size_t)tl * 16 + 8 * (lane & 1)) = packed;
-    if (lane == 0) *reinterpret_cast<float *>(blob + rows * 256 + (size_t)tl * 4) = d;
+    // Sums of the sixteen 16-element runs (the bsums of BlockQ8K), split as 64 * hi + lo with lo in 0..63 and hi in
+    // -32..31 so that both parts are int8 operands: slab 16 holds the sixteen lo bytes, slab 17 the sixteen hi bytes.
+    int bs = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
+    bs += __shfl_xor_sync(0xffffffffu, bs, 1);
+    if ((lane & 1) == 0) {
+        blob[(size_t)16 * rows * 16 + (size_t)tl * 16 + (lane >> 1)] = (uint8_t)(bs & 63);
+        blob[(size_t)17 * rows * 16 + (size_t)tl * 16 + (lane >> 1)] = (uint8_t)(bs >> 6);
+    }
+    if (lane == 0) *reinterpret_cast<float *>(blob + rows * (16 * kSlabsA) + (size_t)tl * 4) = d;
 }
 
 template <typename T>
@@ -255,102 +277,111 @@ __global__ void __launch_bounds__(256) quantize_q8k_tiles_grouped_kernel(const T
 }
 
 // ---- weight planes -----------------------------------------------------------------------------------------
-// RawBlock<T>: the GGUF bytes one producer thread needs for (weight row r, super-block sb, half h) and their
-// expansion into three int8 planes of 16-byte K slabs:  plane j of row r, slab s  ->  stB + s*kSlabB + (64*j + r)*16.
+// RawBlock<T>: the GGUF bytes one producer thread needs for (weight row r, super-block sb, half h, part jh) and their
+// expansion into two int8 planes of 16-byte K slabs:  plane j of row r, slab s  ->  stB + s*kSlabB + (64*j + r)*16,
+// plus this thread's bytes of the operand of the sums MMA (slabs 16 and 17 of the stage): row r of slab 16 and row
+// 64 + r of slab 17 hold one int8 per 16-element run (the other halves of those slabs stay zero), so that with the split
+// block sums  bsum = 64 * hi + lo  of the activations one K = 32 step yields  sum_j v_j lo_j  in accumulator column r and
+// sum_j v_j hi_j  in column 64 + r.
 template <int WTYPE> struct RawBlock;
 
-// Q4_K: thread (r, h) handles bytes [16h, 16h+16) of each of the four 32-byte nibble groups, i.e. elements
-// [16h, 16h+16) of all eight sub-blocks.  Planes: sl*q, sh*q (sc = 8*sh + sl), m replicated.
+// Q4_K: thread (r, h, jh) handles bytes [16h, 16h+16) of the nibble groups 2jh and 2jh+1, i.e. elements [16h, 16h+16) of
+// sub-blocks 4jh .. 4jh+3.  Planes: sl*q, sh*q (sc = 8*sh + sl); sums operand: the 6-bit mins, each for its two runs.
 template <> struct RawBlock<CQ_Q4_K> {
-    uint4 hdr, q[4];
-    __device__ __forceinline__ void load(const uint8_t *wrow, int sb, int h) {
+    uint4 hdr, q[2];
+    __device__ __forceinline__ void load(const uint8_t *wrow, int sb, int h, int jh) {
         const uint8_t *blk = wrow + sb * 144;
         hdr = *reinterpret_cast<const uint4 *>(blk);
 #pragma unroll
-        for (int jp = 0; jp < 4; ++jp) q[jp] = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * jp + 16 * h);
+        for (int i = 0; i < 2; ++i) q[i] = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * (2 * jh + i) + 16 * h);
     }
-    __device__ __forceinline__ void unpack(uint8_t *stB, int r, int h, float2 *wscale) const {
+    __device__ __forceinline__ void unpack(uint8_t *stB, int r, int h, int jh, float2 *wscale) const {
         const uint32_t sw[3] = {hdr.y, hdr.z, hdr.w};         // the 12 scale bytes
-        if (h == 0) {
+        if (h == 0 && jh == 0) {
             const __half2 dm = *reinterpret_cast<const __half2 *>(&hdr.x);
             wscale[r] = make_float2(__low2float(dm), __high2float(dm));
         }
         auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFF; };
+        uint32_t mins[2];
 #pragma unroll
-        for (int jp = 0; jp < 4; ++jp) {
+        for (int i = 0; i < 2; ++i) {
+            const int jp = 2 * jh + i;
             uint32_t sc[2], mn[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {       // get_scale_min_k4, candle-core/src/quantized/utils.rs:50-60
                 const int j = 2 * jp + e;
-                if (j < 4) { sc[e] = sbyte(j) & 63; mn[e] = sbyte(j + 4) & 63; }
+                if (jh == 0) { sc[e] = sbyte(j) & 63; mn[e] = sbyte(j + 4) & 63; }
                 else {
                     sc[e] = (sbyte(j + 4) & 0xF) | ((sbyte(j - 4) >> 6) << 4);
                     mn[e] = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
                 }
             }
-            const uint32_t qq[4] = {q[jp].x, q[jp].y, q[jp].z, q[jp].w};
+            mins[i] = mn[0] * 0x00000101u + mn[1] * 0x01010000u;    // runs 4jp, 4jp+1 | 4jp+2, 4jp+3
+            const uint32_t qq[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
 #pragma unroll
             for (int e = 0; e < 2; ++e) {       // e = 0: low nibbles = sub-block 2jp, e = 1: high nibbles = 2jp+1
-                const uint32_t sl = sc[e] & 7, sh = sc[e] >> 3, mm = mn[e] * 0x01010101u;
+                const uint32_t sl = sc[e] & 7, sh = sc[e] >> 3;
                 uint32_t p1[4], p2[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t nib = (e ? (qq[i] >> 4) : qq[i]) & 0x0F0F0F0Fu;
-                    p1[i] = nib * sl;           // four byte products, each <= 105: no carries between bytes
-                    p2[i] = nib * sh;
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t nib = (e ? (qq[w] >> 4) : qq[w]) & 0x0F0F0F0Fu;
+                    p1[w] = nib * sl;           // four byte products, each <= 105: no carries between bytes
+                    p2[w] = nib * sh;
                 }
                 const int slab = 2 * (2 * jp + e) + h;
                 uint8_t *dst = stB + slab * kSlabB + r * 16;
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
                 *reinterpret_cast<uint4 *>(dst + kRowTile * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
-                *reinterpret_cast<uint4 *>(dst + 2 * kRowTile * 16) = make_uint4(mm, mm, mm, mm);
             }
+        }
+        if (h == 0) {       // runs 8jh .. 8jh+7
+            *reinterpret_cast<uint2 *>(stB + 16 * kSlabB + r * 16 + 8 * jh) = make_uint2(mins[0], mins[1]);
+            *reinterpret_cast<uint2 *>(stB + 17 * kSlabB + (kRowTile + r) * 16 + 8 * jh) = make_uint2(mins[0], mins[1]);
         }
     }
 };
 
-// Q6_K (210-byte blocks, 2-byte aligned): thread (r, h) handles the 128 elements of half h: ql[64h, 64h+64),
-// qh[32h, 32h+32), scales[8h, 8h+8).  value = d * sc * (q - 32) with int8 sc per 16 elements and q in 0..63.
-// Planes: with p = |sc| * q (<= 8064):  lo = p & 63, hi = p >> 6 (<= 126), both negated when sc < 0, and sc
-// replicated; then  sum sc (q - 32) q8 = 64 * (hi . q8) + (lo . q8) - 32 * (sc . q8)  exactly.
-// Bytes are fetched as aligned 32-bit words and re-aligned with a funnel shift when the block starts on an odd
-// 16-bit boundary.
+// Q6_K (210-byte blocks, 2-byte aligned): thread (r, h, jh) handles the 64 elements 128h + 32*pos + [0, 32) for pos = 2jh,
+// 2jh+1: nibble jh of ql[64h, 64h+64), bit pairs 2*pos of qh[32h, 32h+32), scales[8h + 4jh, +4).  value = d * sc * (q - 32)
+// with int8 sc per 16 elements and q in 0..63.  Planes: with p = |sc| * q (<= 8064):  lo = p & 63, hi = p >> 6 (<= 126), both
+// negated when sc < 0; sums operand: sc per run; then  sum sc (q - 32) q8 = 64 * (hi . q8) + (lo . q8) - 32 * sum_j sc_j bsum_j
+// exactly.  Bytes are fetched as aligned 32-bit words and re-aligned with a funnel shift when the block starts on an
+// odd 16-bit boundary.
 template <> struct RawBlock<CQ_Q6_K> {
-    uint32_t ql[17], qh[9], sc[3];
+    uint32_t ql[17], qh[9], sc[2];
     uint32_t d16, sh;
-    __device__ __forceinline__ void load(const uint8_t *wrow, int sb, int h) {
+    __device__ __forceinline__ void load(const uint8_t *wrow, int sb, int h, int jh) {
         const uint8_t *blk = wrow + (size_t)sb * 210;
         sh = (unsigned)((uintptr_t)blk & 2) * 8;
         const uint32_t *a = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 64 * h) & ~(uintptr_t)3);
         const uint32_t *b = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 128 + 32 * h) & ~(uintptr_t)3);
-        const uint32_t *c = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 192 + 8 * h) & ~(uintptr_t)3);
+        const uint32_t *c = reinterpret_cast<const uint32_t *>((uintptr_t)(blk + 192 + 8 * h + 4 * jh) & ~(uintptr_t)3);
 #pragma unroll
         for (int i = 0; i < 17; ++i) ql[i] = a[i];
 #pragma unroll
         for (int i = 0; i < 9; ++i) qh[i] = b[i];
-#pragma unroll
-        for (int i = 0; i < 3; ++i) sc[i] = c[i];
+        sc[0] = c[0]; sc[1] = c[1];
         d16 = *reinterpret_cast<const uint16_t *>(blk + 208);
     }
-    __device__ __forceinline__ void unpack(uint8_t *stB, int r, int h, float2 *wscale) const {
-        if (h == 0) wscale[r] = make_float2(__half2float(__ushort_as_half((unsigned short)d16)), 0.0f);
-        const uint32_t s0 = __funnelshift_r(sc[0], sc[1], sh), s1 = __funnelshift_r(sc[1], sc[2], sh);
+    __device__ __forceinline__ void unpack(uint8_t *stB, int r, int h, int jh, float2 *wscale) const {
+        if (h == 0 && jh == 0) wscale[r] = make_float2(__half2float(__ushort_as_half((unsigned short)d16)), 0.0f);
+        const uint32_t s4 = __funnelshift_r(sc[0], sc[1], sh);      // the scales of runs 8h + 4jh .. +3
 #pragma unroll
-        for (int pos = 0; pos < 4; ++pos) {            // elements 128h + 32*pos + [0, 32)
+        for (int pp = 0; pp < 2; ++pp) {               // pos = 2jh + pp: elements 128h + 32*pos + [0, 32)
+            const int pos = 2 * jh + pp;
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {           // 16 elements sharing one scale: sub-block 8h + 2*pos + hf
-                const int j = 2 * pos + hf;
-                const int scv = (int)(int8_t)(((j < 4 ? s0 : s1) >> (8 * (j & 3))) & 0xFF);
+            for (int hf = 0; hf < 2; ++hf) {           // 16 elements sharing one scale: run 8h + 2*pos + hf
+                const int scv = (int)(int8_t)((s4 >> (8 * (2 * pp + hf))) & 0xFF);
                 const uint32_t mag = (uint32_t)(scv < 0 ? -scv : scv);
                 const bool negate = scv < 0;
                 uint32_t lo[4], hi[4];
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi) {
-                    const int lw = (pos & 1) * 8 + hf * 4 + wi;        // word of ql: bytes 32*(pos&1) + 16*hf + 4*wi
+                    const int lw = pp * 8 + hf * 4 + wi;               // word of ql: bytes 32*(pos&1) + 16*hf + 4*wi
                     const int hw = hf * 4 + wi;                        // word of qh: bytes 16*hf + 4*wi
                     const uint32_t l = __funnelshift_r(ql[lw], ql[lw + 1], sh);
                     const uint32_t hb = __funnelshift_r(qh[hw], qh[hw + 1], sh);
-                    const uint32_t q6 = ((l >> (4 * (pos >> 1))) & 0x0F0F0F0Fu) | (((hb >> (2 * pos)) & 0x03030303u) << 4);
+                    const uint32_t q6 = ((l >> (4 * jh)) & 0x0F0F0F0Fu) | (((hb >> (2 * pos)) & 0x03030303u) << 4);
                     const uint32_t pe = (q6 & 0x00FF00FFu) * mag, po = ((q6 >> 8) & 0x00FF00FFu) * mag;   // 16-bit lanes, <= 8064
                     uint32_t lw_ = (pe & 0x003F003Fu) | ((po & 0x003F003Fu) << 8);
                     uint32_t hw_ = ((pe >> 6) & 0x00FF00FFu) | (((po >> 6) & 0x00FF00FFu) << 8);
@@ -358,23 +389,26 @@ template <> struct RawBlock<CQ_Q6_K> {
                     lo[wi] = negate ? ((0x80808080u - lw_) ^ 0x80808080u) : lw_;
                     hi[wi] = negate ? ((0x80808080u - hw_) ^ 0x80808080u) : hw_;
                 }
-                const uint32_t rep = ((uint32_t)scv & 0xFFu) * 0x01010101u;
-                const int slab = 8 * h + j;
+                const int slab = 8 * h + 2 * pos + hf;
                 uint8_t *dst = stB + slab * kSlabB + r * 16;
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 *reinterpret_cast<uint4 *>(dst + kRowTile * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4 *>(dst + 2 * kRowTile * 16) = make_uint4(rep, rep, rep, rep);
             }
         }
+        *reinterpret_cast<uint32_t *>(stB + 16 * kSlabB + r * 16 + 8 * h + 4 * jh) = s4;
+        *reinterpret_cast<uint32_t *>(stB + 17 * kSlabB + (kRowTile + r) * 16 + 8 * h + 4 * jh) = s4;
     }
 };
 
 // ---- the GEMM ---------------------------------------------------------------------------------------------
-// Shared memory: [control 1 KiB][A: 3 stages x 32 KiB][B: 2 stages x 48 KiB][d_a ring 8 x 512 B][(d, dmin) ring 8 x 512 B]
+// Shared memory: [control 1 KiB][A: 3 stages x 36 KiB][B: 2 stages x 36 KiB][d_a ring 8 x 512 B][(d, dmin) ring 8 x 512 B]
+// Tensor memory: two accumulator buffers of 256 columns: [plane 0 | plane 1 | sums lo | sums hi], 64 weight rows each.
+// Per super-block the MMA warp issues eight K = 32 steps into the product columns and one into the sums columns.
 // Dependencies per super-block sb (P_A / P_B producers, M = MMA, E = epilogue):
 //   P_A(sb) after M(sb-3) [bar_doneA]     P_B(sb) after M(sb-2) [bar_acc]      M(sb) after P_A(sb), P_B(sb), E(sb-2)
 //   E(sb) after M(sb) [bar_acc] and after the relay arrive on bar_vis, which carries the visibility of the scale rings.
 // The scale rings are 8 deep: an entry is rewritten for sb+8 only after M(sb+5), which itself waited for E(sb+3).
+// Warps: 0-7 epilogue (TMEM lane quadrant = warp % 4, weight rows 32 * (warp / 4) ..), 8-15 producers, 16 MMA, 17 loader.
 template <int WTYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, void *__restrict__ out_v, int out_kind, int k,
@@ -391,10 +425,10 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
         job0 = ti[1];
     }
     uint64_t *bar_fullA = reinterpret_cast<uint64_t *>(smem);         // [3] activations landed (TMA bytes)
-    uint64_t *bar_fullB = bar_fullA + 3;                               // [2] weight planes written (128 producer threads)
+    uint64_t *bar_fullB = bar_fullA + 3;                               // [2] weight planes written (all producer threads)
     uint64_t *bar_acc = bar_fullA + 5;                                 // [2] MMAs of a super-block complete
     uint64_t *bar_doneA = bar_fullA + 7;                               // [3] same event, tracked per A stage
-    uint64_t *bar_free = bar_fullA + 10;                               // [2] accumulator buffer drained (128 epilogue threads)
+    uint64_t *bar_free = bar_fullA + 10;                               // [2] accumulator buffer drained (all epilogue threads)
     uint64_t *bar_vis = bar_fullA + 12;                                // [2] relay: scale rings of this super-block are visible
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 128);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 136);
@@ -413,9 +447,9 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
     if (tid == 0) {
         for (int i = 0; i < 3; ++i) { cq_mbar_init(&bar_fullA[i], 1); cq_mbar_init(&bar_doneA[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            cq_mbar_init(&bar_fullB[i], 128);
+            cq_mbar_init(&bar_fullB[i], kProdWarps * 32);
             cq_mbar_init(&bar_acc[i], 1);
-            cq_mbar_init(&bar_free[i], 128);
+            cq_mbar_init(&bar_free[i], kEpiWarps * 32);
             cq_mbar_init(&bar_vis[i], 1);
         }
         *abort_flag = 0;
@@ -430,32 +464,39 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp >= 4 && warp < 8) {
+    if (warp >= kEpiWarps && warp < kEpiWarps + kProdWarps) {
         // ===== producers =====
-        const int p = tid - 128;
-        const int r = p & 63, h = p >> 6;
+        const int p = tid - kEpiWarps * 32;
+        const int r = p & 63, h = (p >> 6) & 1, jh = p >> 7;
         int grow = row0 + r;
         if (grow >= nrows) grow = nrows - 1;        // ragged last tile: duplicate a valid row, never stored
         const uint8_t *wrow = w + (size_t)grow * row_bytes;
+        // the halves of the sums operand that stay zero: rows 64.. of slab 16 and rows ..63 of slab 17, both stages
+        for (int i = p; i < kStagesB * 2 * 64; i += kProdWarps * 32) {
+            const int st = i >> 7, which = (i >> 6) & 1, row = i & 63;
+            uint8_t *z = stB0 + st * kStageB + (16 + which) * kSlabB + ((which ? 0 : kRowTile) + row) * 16;
+            *reinterpret_cast<uint4 *>(z) = make_uint4(0u, 0u, 0u, 0u);
+        }
         // the GGUF bytes of the next super-block are fetched one iteration ahead of their use
         RawBlock<WTYPE> nxt_raw;
-        nxt_raw.load(wrow, 0, h);
+        nxt_raw.load(wrow, 0, h, jh);
         for (int sb = 0; sb < nsb; ++sb) {
             const int s = sb & 1;
             uint8_t *stB = stB0 + s * kStageB;
             if (dbg & 1) {
                 if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
+                fence_proxy_async_smem();
                 mbar_arrive(&bar_fullB[s]);
                 continue;
             }
             const RawBlock<WTYPE> cur = nxt_raw;
-            if (sb + 1 < nsb) nxt_raw.load(wrow, sb + 1, h);
+            if (sb + 1 < nsb) nxt_raw.load(wrow, sb + 1, h, jh);
             if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;   // M(sb-2) has read this stage
-            cur.unpack(stB, r, h, reinterpret_cast<float2 *>(ringW + (sb & 7) * 512));
+            cur.unpack(stB, r, h, jh, reinterpret_cast<float2 *>(ringW + (sb & 7) * 512));
             fence_proxy_async_smem();       // make these generic-proxy writes visible to the tensor core
             mbar_arrive(&bar_fullB[s]);
         }
-    } else if (warp == 9) {
+    } else if (warp == kEpiWarps + kProdWarps + 1) {
         // ===== activation loader: one thread keeps up to three super-blocks of int8 activations in flight =====
         if (lane == 0) {
             for (int sb = 0; sb < nsb; ++sb) {
@@ -464,46 +505,52 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
                 if (dbg & 1) { mbar_arrive(&bar_fullA[a]); continue; }
                 const uint8_t *blob = act + TileBlob::offset(tokens, nsb, tt, sb);
                 uint8_t *dstA = stA0 + a * kStageA, *dstS = ringA + (sb & 7) * 512;
-                cq_mbar_expect_tx(&bar_fullA[a], (unsigned)(tile_rows * 260));
+                cq_mbar_expect_tx(&bar_fullA[a], (unsigned)(tile_rows * kTokBytes));
                 if (tile_rows == kTokTile) cq_bulk_g2s(dstA, blob, kStageA, &bar_fullA[a]);        // scratch layout == smem layout
                 else
-                    for (int sl = 0; sl < 16; ++sl)
+                    for (int sl = 0; sl < kSlabsA; ++sl)
                         cq_bulk_g2s(dstA + sl * kSlabA, blob + (size_t)sl * tile_rows * 16, (unsigned)(tile_rows * 16), &bar_fullA[a]);
-                cq_bulk_g2s(dstS, blob + (size_t)tile_rows * 256, (unsigned)(tile_rows * 4), &bar_fullA[a]);
+                cq_bulk_g2s(dstS, blob + (size_t)tile_rows * (16 * kSlabsA), (unsigned)(tile_rows * 4), &bar_fullA[a]);
             }
         }
         __syncwarp();
-    } else if (warp == 8) {
+    } else if (warp == kEpiWarps + kProdWarps) {
         // ===== MMA issuer =====
         constexpr uint32_t idesc = make_idesc_i8(kTokTile, kN);
         for (int sb = 0; sb < nsb; ++sb) {
             const int s = sb & 1, a = sb % kStagesA;
             if (!wait_or_abort(&bar_fullA[a], (sb / kStagesA) & 1, abort_flag)) break;
-            if (!wait_or_abort(&bar_fullB[s], (sb >> 1) & 1, abort_flag)) break;
-            if (sb >= 2 && !wait_or_abort(&bar_free[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
+            if (!(dbg & 4)) {
+                if (!wait_or_abort(&bar_fullB[s], (sb >> 1) & 1, abort_flag)) break;
+                if (sb >= 2 && !wait_or_abort(&bar_free[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
+            }
             tc_fence_after();
             if (lane == 0) {
                 mbar_arrive(&bar_vis[s]);       // relay: everything this thread has acquired is now visible to the epilogue
                 const uint32_t a0 = cq_smem_u32(stA0 + a * kStageA), b0 = cq_smem_u32(stB0 + s * kStageB);
-                const uint32_t tacc = tmem_base + (uint32_t)(s * kN);
+                const uint32_t tacc = tmem_base + (uint32_t)(s * kAccCols);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint64_t da = make_smem_desc(a0 + ks * 2 * kSlabA, kSlabA, 128);
                     const uint64_t db = make_smem_desc(b0 + ks * 2 * kSlabB, kSlabB, 128);
                     tc_mma_i8(tacc, da, db, idesc, ks > 0 ? 1u : 0u);
                 }
+                // split block sums x per-run minimum / scale -> columns kN ..
+                tc_mma_i8(tacc + kN, make_smem_desc(a0 + 16 * kSlabA, kSlabA, 128), make_smem_desc(b0 + 16 * kSlabB, kSlabB, 128), idesc, 0u);
                 tc_commit(&bar_acc[s]);
                 tc_commit(&bar_doneA[a]);
             }
             __syncwarp();
         }
     } else {
-        // ===== epilogue: warp q owns TMEM lanes 32q..32q+31 = tokens =====
-        const int tok_local = warp * 32 + lane;
+        // ===== epilogue: warp q owns TMEM lanes 32 (q % 4) .. +31 = tokens, weight rows 32 (q / 4) .. +31 =====
+        constexpr int kMyRows = kRowTile * 4 / kEpiWarps;      // 32
+        const int quad = warp & 3, rh = warp >> 2;
+        const int tok_local = quad * 32 + lane;
         const int tok = tt * kTokTile + tok_local;
-        float acc[kRowTile];
+        float acc[kMyRows];
 #pragma unroll
-        for (int i = 0; i < kRowTile; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < kMyRows; ++i) acc[i] = 0.0f;
         bool alive = true;
         for (int sb = 0; sb < nsb && alive; ++sb) {
             const int s = sb & 1;
@@ -512,36 +559,39 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
             tc_fence_after();
             if (dbg & 2) { tc_fence_before(); mbar_arrive(&bar_free[s]); continue; }
             const float da = *reinterpret_cast<const float *>(ringA + (sb & 7) * 512 + tok_local * 4);
-            const uint8_t *rw = ringW + (sb & 7) * 512;
-            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * kN);
-            // 16 weight rows at a time; the TMEM loads of the next chunk are in flight while this one is computed
-            uint32_t v1[2][16], v2[2][16], vm[2][16];
-            tmem_ld16(taddr, v1[0]);
-            tmem_ld16(taddr + kRowTile, v2[0]);
-            tmem_ld16(taddr + 2 * kRowTile, vm[0]);
+            const uint8_t *rw = ringW + (sb & 7) * 512 + rh * kMyRows * 8;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(s * kAccCols + rh * kMyRows);
+            // 8 weight rows at a time; the TMEM loads of the next chunk are in flight while this one is computed
+            uint32_t v1[2][8], v2[2][8], vl[2][8], vh[2][8];
+            tmem_ld8(taddr, v1[0]);
+            tmem_ld8(taddr + kRowTile, v2[0]);
+            tmem_ld8(taddr + 2 * kRowTile, vl[0]);
+            tmem_ld8(taddr + 3 * kRowTile, vh[0]);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kMyRows / 8; ++c) {
                 tmem_ld_wait();
-                if (c < 3) {
-                    tmem_ld16(taddr + (c + 1) * 16, v1[(c + 1) & 1]);
-                    tmem_ld16(taddr + kRowTile + (c + 1) * 16, v2[(c + 1) & 1]);
-                    tmem_ld16(taddr + 2 * kRowTile + (c + 1) * 16, vm[(c + 1) & 1]);
+                if (c + 1 < kMyRows / 8) {
+                    tmem_ld8(taddr + (c + 1) * 8, v1[(c + 1) & 1]);
+                    tmem_ld8(taddr + kRowTile + (c + 1) * 8, v2[(c + 1) & 1]);
+                    tmem_ld8(taddr + 2 * kRowTile + (c + 1) * 8, vl[(c + 1) & 1]);
+                    tmem_ld8(taddr + 3 * kRowTile + (c + 1) * 8, vh[(c + 1) & 1]);
                 }
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    const float4 dw = *reinterpret_cast<const float4 *>(rw + (c * 16 + i) * 8);   // (d, dmin) x 2 rows
+                for (int i = 0; i < 8; i += 2) {
+                    const float4 dw = *reinterpret_cast<const float4 *>(rw + (c * 8 + i) * 8);   // (d, dmin) x 2 rows
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float dd = e ? dw.z : dw.x, dmn = e ? dw.w : dw.y;
+                        const int sums = 64 * (int)vh[c & 1][i + e] + (int)vl[c & 1][i + e];        // sum_j v_j bsum_j, exact
                         float t;
                         if constexpr (WTYPE == CQ_Q4_K) {
                             const int sdot = 8 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e];     // exact, up to 3.1e7
-                            t = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float((int)vm[c & 1][i + e])));
-                        } else {        // Q6_K: 64*hi + lo - 32*sum(sc*q8), exact in int32 (< 4.1e8)
-                            const int tot = 64 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e] - 32 * (int)vm[c & 1][i + e];
+                            t = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float(sums)));
+                        } else {        // Q6_K: 64*hi + lo - 32*sum(sc*bsum), exact in int32 (< 4.1e8)
+                            const int tot = 64 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e] - 32 * sums;
                             t = __fmul_rn(dd, (float)tot);
                         }
-                        acc[c * 16 + i + e] = __fmaf_rn(da, t, acc[c * 16 + i + e]);
+                        acc[c * 8 + i + e] = __fmaf_rn(da, t, acc[c * 8 + i + e]);
                     }
                 }
             }
@@ -558,23 +608,24 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
                 if (gi.topk_weights) {
                     const float sc = gi.topk_weights[pair];
 #pragma unroll
-                    for (int i = 0; i < kRowTile; ++i) acc[i] = __fmul_rn(acc[i], sc);
+                    for (int i = 0; i < kMyRows; ++i) acc[i] = __fmul_rn(acc[i], sc);
                 }
             }
         }
+        const int c0 = row0 + rh * kMyRows;
         if (store && out_kind != CQ_F32) {
 #pragma unroll
-            for (int i = 0; i < kRowTile; ++i)
-                if (row0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + row0 + i, acc[i]);
+            for (int i = 0; i < kMyRows; ++i)
+                if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
         } else if (store) {
-            float *o = (float *)out_v + (size_t)orow * stride_out + row0;
-            if (row0 + kRowTile <= nrows && (((uintptr_t)o) & 15) == 0) {
+            float *o = (float *)out_v + (size_t)orow * stride_out + c0;
+            if (c0 + kMyRows <= nrows && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
-                for (int i = 0; i < kRowTile; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                for (int i = 0; i < kMyRows; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
             } else {
 #pragma unroll
-                for (int i = 0; i < kRowTile; ++i)
-                    if (row0 + i < nrows) o[i] = acc[i];
+                for (int i = 0; i < kMyRows; ++i)
+                    if (c0 + i < nrows) o[i] = acc[i];
             }
         }
     }
@@ -590,7 +641,7 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
 extern "C" size_t cq_prefill_scratch_bytes(int tokens, int k) {
     if (tokens <= 0 || k <= 0 || k % 256 != 0) return 0;
     const int nsb = k / 256, ntt = (tokens + kTokTile - 1) / kTokTile;
-    return TileBlob::offset(tokens, nsb, ntt - 1, nsb - 1) + TileBlob::tile_rows(tokens, ntt - 1) * 260 + 256;
+    return TileBlob::offset(tokens, nsb, ntt - 1, nsb - 1) + TileBlob::tile_rows(tokens, ntt - 1) * kTokBytes + 256;
 }
 
 extern "C" void cq_prefill_quantize(const void *x, int x_elem, void *scratch, int k, int tokens, void *stream) {
@@ -650,7 +701,7 @@ size_t moe_table_bytes(int max_tiles) { return ((size_t)max_tiles * 16 + 255) / 
 extern "C" size_t cq_moe_prefill_scratch_bytes(int size_m, int num_experts, int k) {
     if (size_m <= 0 || num_experts <= 0 || num_experts > 1024 || k <= 0 || k % 256 != 0) return 0;
     const int mt = moe_max_tiles(size_m, num_experts);
-    return moe_table_bytes(mt) + (size_t)mt * kTokTile * 260 * (k / 256) + 256;
+    return moe_table_bytes(mt) + (size_t)mt * kTokTile * kTokBytes * (k / 256) + 256;
 }
 
 // out[pair, :] = W[expert of the pair] . x[input row of the pair] (times topk_weights[pair]) for all size_m sorted pairs, on

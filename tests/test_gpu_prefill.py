@@ -37,21 +37,26 @@ def _prefill(lib, w_dev, x_dev, k, n, out_dtype=torch.float32, wtype=Q4K):
 
 
 def _tiles_to_q8k(scratch, tokens, k):
-    """Undo the tensor-core tiling of the scratch: returns (int8 [tokens, k], f32 scales [tokens, k/256])."""
+    """Undo the tensor-core tiling of the scratch: returns (int8 [tokens, k], f32 scales [tokens, k/256],
+    int32 sums of the sixteen 16-element runs [tokens, k/16] rebuilt from their 64 * hi + lo split)."""
     s = scratch.cpu().numpy()
     nsb = k // 256
     q = np.zeros((tokens, k), dtype=np.int8)
     d = np.zeros((tokens, nsb), dtype=np.float32)
+    bs = np.zeros((tokens, nsb, 16), dtype=np.int32)
     for tt in range((tokens + 127) // 128):
         nt = min(128, tokens - tt * 128)
         rows = (nt + 7) // 8 * 8
         for sb in range(nsb):
-            off = tt * 128 * 260 * nsb + sb * rows * 260
-            blob = s[off:off + rows * 260]
-            slabs = blob[:rows * 256].reshape(16, rows, 16)          # [k/16][token][16]
-            q[tt * 128:tt * 128 + nt, sb * 256:(sb + 1) * 256] = slabs.transpose(1, 0, 2).reshape(rows, 256)[:nt].view(np.int8)
-            d[tt * 128:tt * 128 + nt, sb] = blob[rows * 256:rows * 260].view(np.float32)[:nt]
-    return q, d
+            off = tt * 128 * 292 * nsb + sb * rows * 292
+            blob = s[off:off + rows * 292]
+            slabs = blob[:rows * 288].reshape(18, rows, 16)          # [k/16 | lo | hi][token][16]
+            q[tt * 128:tt * 128 + nt, sb * 256:(sb + 1) * 256] = slabs[:16].transpose(1, 0, 2).reshape(rows, 256)[:nt].view(np.int8)
+            lo, hi = slabs[16][:nt].astype(np.int32), slabs[17][:nt].view(np.int8).astype(np.int32)
+            assert lo.max(initial=0) <= 63
+            bs[tt * 128:tt * 128 + nt, sb] = 64 * hi + lo
+            d[tt * 128:tt * 128 + nt, sb] = blob[rows * 288:rows * 292].view(np.float32)[:nt]
+    return q, d, bs
 
 
 @pytest.mark.parametrize("tokens,k,n", [(128, 256, 64), (17, 512, 64), (100, 1024, 100), (300, 2048, 200),
@@ -62,10 +67,11 @@ def test_prefill_matches_cpu_vec_dot(lib, oracle, cuda_dev, tokens, k, n):
     x_dev = torch.from_numpy(x).to(cuda_dev)
     scratch, out = _prefill(lib, w_dev, x_dev, k, n)
     # activation blocks: identical int8 values and scales to BlockQ8K::from_float
-    q, d = _tiles_to_q8k(scratch, tokens, k)
+    q, d, bs = _tiles_to_q8k(scratch, tokens, k)
     ref_blocks = oracle.quantize(oracle.Q8K, x).reshape(tokens, k // 256, 292)
     assert np.array_equal(q.reshape(tokens, k // 256, 256), ref_blocks[:, :, 4:260].view(np.int8))
     assert np.array_equal(d, ref_blocks[:, :, 0:4].copy().view(np.float32).reshape(tokens, k // 256))
+    assert np.array_equal(bs, ref_blocks[:, :, 260:292].copy().view(np.int16).astype(np.int32).reshape(tokens, k // 256, 16))
     ref = oracle.matmul(Q4K, x, wq, n)
     assert rel_err(out.cpu().numpy(), ref) <= TOL
     assert rel_err(out.cpu().numpy(), ref) <= 1e-5     # only the order of f32 additions differs
