@@ -46,13 +46,13 @@ constexpr int kStageA = kSlabsA * kSlabA;              // 36 KiB
 constexpr int kStageB = 18 * kSlabB;                   // 36 KiB: 128 rows x 256 int8, then the 128 x 32 operand of the sums MMA
 constexpr int kTokBytes = 16 * kSlabsA + 4;            // scratch bytes per (token, super-block): 288 operand bytes + f32 d
 constexpr int kAccCols = 2 * kN;                       // accumulator columns per buffer: products, then sums
-constexpr int kStagesA = 3, kStagesB = 2;
+constexpr int kStagesA = 3, kStagesB = 3;
 constexpr int kEpiWarps = 8, kProdWarps = 8;
 constexpr int kThreads = (kEpiWarps + kProdWarps + 2) * 32;
 constexpr int kSmemBytes = 1024 + kStagesA * kStageA + kStagesB * kStageB + 2 * 8 * 512;
 
 __device__ int g_prefill_timeout_flag = 0;
-int g_prefill_dbg = 0;   // experiment switch: bit 0 skips the producers' work, bit 1 the epilogue's, bit 2 the MMA warp's waits for both (results are then garbage)
+int g_prefill_dbg = 0;   // experiment switch: bit 0 skips the producers' work and the activation copies, bit 1 the epilogue's arithmetic (results are then garbage)
 
 // ---- tcgen05 wrappers ----
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, int ncols) {
@@ -401,37 +401,53 @@ template <> struct RawBlock<CQ_Q6_K> {
 };
 
 // ---- the GEMM ---------------------------------------------------------------------------------------------
-// Shared memory: [control 1 KiB][A: 3 stages x 36 KiB][B: 2 stages x 36 KiB][d_a ring 8 x 512 B][(d, dmin) ring 8 x 512 B]
+// Persistent: one CTA per SM walks tiles (64 weight rows x 128 tokens) t = blockIdx.x, + gridDim.x, ...; consecutive tile
+// numbers share the weight rows, so the CTAs running at one time re-read the same weights and activations from L2.
+// All rings and barrier phases run on a counter `it` of super-blocks that continues across tiles, so the producers,
+// the loader and the MMA warp start the next tile while the epilogue still stores the previous one.
+// Shared memory: [control 1 KiB][A: 3 stages x 36 KiB][B: 3 stages x 36 KiB][d_a ring 8 x 512 B][(d, dmin) ring 8 x 512 B]
 // Tensor memory: two accumulator buffers of 256 columns: [plane 0 | plane 1 | sums lo | sums hi], 64 weight rows each.
 // Per super-block the MMA warp issues eight K = 32 steps into the product columns and one into the sums columns.
-// Dependencies per super-block sb (P_A / P_B producers, M = MMA, E = epilogue):
-//   P_A(sb) after M(sb-3) [bar_doneA]     P_B(sb) after M(sb-2) [bar_acc]      M(sb) after P_A(sb), P_B(sb), E(sb-2)
-//   E(sb) after M(sb) [bar_acc] and after the relay arrive on bar_vis, which carries the visibility of the scale rings.
-// The scale rings are 8 deep: an entry is rewritten for sb+8 only after M(sb+5), which itself waited for E(sb+3).
+// Dependencies per super-block i (P_A / P_B producers, M = MMA, E = epilogue):
+//   P_A(i) after M(i-3) [bar_doneA]     P_B(i) after M(i-3) [bar_doneB]     M(i) after P_A(i), P_B(i), E(i-2) [bar_free]
+//   E(i) after M(i) [bar_acc] and after the relay arrive on bar_vis, which carries the visibility of the scale rings.
+// The scale rings are 8 deep: an entry is rewritten for i+8 only after M(i+5), which itself waited for E(i+3).
 // Warps: 0-7 epilogue (TMEM lane quadrant = warp % 4, weight rows 32 * (warp / 4) ..), 8-15 producers, 16 MMA, 17 loader.
+struct TileCtx {
+    const uint8_t *w;       // weight matrix of this tile (grouped mode: of its expert)
+    int row0, tt, valid, job0;
+};
+// false: nothing to do for tile t (grouped mode, unused tile).  Every role evaluates this for the same t, so all skip alike.
+__device__ __forceinline__ bool tile_ctx(int t, int ntt, const uint8_t *w, const GroupInfo &gi, TileCtx &c) {
+    c.row0 = (t / ntt) * kRowTile;
+    c.tt = t % ntt;
+    c.valid = kTokTile;
+    c.job0 = 0;
+    c.w = w;
+    if (gi.tiles) {
+        const int *ti = gi.tiles + 4 * c.tt;
+        c.valid = ti[2];
+        if (c.valid == 0) return false;
+        c.w = w + (long long)ti[0] * gi.expert_stride;
+        c.job0 = ti[1];
+    }
+    return true;
+}
+
 template <int WTYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, void *__restrict__ out_v, int out_kind, int k,
-                   int nrows, int tokens, int stride_out, int dbg, const GroupInfo gi) {
+                   int nrows, int tokens, int stride_out, int dbg, int ntt, int ntiles, const GroupInfo gi) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    // grouped mode: this CTA's token tile belongs to one expert; `tokens` is then max_tiles * 128 (every tile is stored
-    // full-size) and rows past `valid` are padding
-    int valid = kTokTile, job0 = 0;
-    if (gi.tiles) {
-        const int *ti = gi.tiles + 4 * blockIdx.y;
-        valid = ti[2];
-        if (valid == 0) return;                             // the whole CTA, before any barrier or TMEM allocation
-        w += (long long)ti[0] * gi.expert_stride;
-        job0 = ti[1];
-    }
     uint64_t *bar_fullA = reinterpret_cast<uint64_t *>(smem);         // [3] activations landed (TMA bytes)
-    uint64_t *bar_fullB = bar_fullA + 3;                               // [2] weight planes written (all producer threads)
-    uint64_t *bar_acc = bar_fullA + 5;                                 // [2] MMAs of a super-block complete
-    uint64_t *bar_doneA = bar_fullA + 7;                               // [3] same event, tracked per A stage
-    uint64_t *bar_free = bar_fullA + 10;                               // [2] accumulator buffer drained (all epilogue threads)
-    uint64_t *bar_vis = bar_fullA + 12;                                // [2] relay: scale rings of this super-block are visible
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 128);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 136);
+    uint64_t *bar_fullB = bar_fullA + 3;                               // [3] weight planes written (all producer threads)
+    uint64_t *bar_doneA = bar_fullA + 6;                               // [3] MMAs that read this A stage are complete
+    uint64_t *bar_doneB = bar_fullA + 9;                               // [3] same for the B stage
+    uint64_t *bar_acc = bar_fullA + 12;                                // [2] MMAs of a super-block complete
+    uint64_t *bar_free = bar_fullA + 14;                               // [2] accumulator buffer drained (all epilogue threads)
+    uint64_t *bar_vis = bar_fullA + 16;                                // [2] relay: scale rings of this super-block are visible
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 256);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 264);
     uint8_t *stA0 = smem + 1024;
     uint8_t *stB0 = stA0 + kStagesA * kStageA;
     uint8_t *ringA = stB0 + kStagesB * kStageB;        // d_a: [8][128] f32
@@ -439,15 +455,16 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nsb = k / 256;
-    const int row0 = blockIdx.x * kRowTile;
-    const int tt = blockIdx.y;
-    const int tile_rows = (int)TileBlob::tile_rows(tokens, tt);
     const int row_bytes = nsb * cq_type_size(WTYPE);
 
     if (tid == 0) {
-        for (int i = 0; i < 3; ++i) { cq_mbar_init(&bar_fullA[i], 1); cq_mbar_init(&bar_doneA[i], 1); }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 3; ++i) {
+            cq_mbar_init(&bar_fullA[i], 1);
+            cq_mbar_init(&bar_doneA[i], 1);
             cq_mbar_init(&bar_fullB[i], kProdWarps * 32);
+            cq_mbar_init(&bar_doneB[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             cq_mbar_init(&bar_acc[i], 1);
             cq_mbar_init(&bar_free[i], kEpiWarps * 32);
             cq_mbar_init(&bar_vis[i], 1);
@@ -468,164 +485,196 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
         // ===== producers =====
         const int p = tid - kEpiWarps * 32;
         const int r = p & 63, h = (p >> 6) & 1, jh = p >> 7;
-        int grow = row0 + r;
-        if (grow >= nrows) grow = nrows - 1;        // ragged last tile: duplicate a valid row, never stored
-        const uint8_t *wrow = w + (size_t)grow * row_bytes;
-        // the halves of the sums operand that stay zero: rows 64.. of slab 16 and rows ..63 of slab 17, both stages
+        // the halves of the sums operand that stay zero: rows 64.. of slab 16 and rows ..63 of slab 17, every stage
         for (int i = p; i < kStagesB * 2 * 64; i += kProdWarps * 32) {
             const int st = i >> 7, which = (i >> 6) & 1, row = i & 63;
             uint8_t *z = stB0 + st * kStageB + (16 + which) * kSlabB + ((which ? 0 : kRowTile) + row) * 16;
             *reinterpret_cast<uint4 *>(z) = make_uint4(0u, 0u, 0u, 0u);
         }
-        // the GGUF bytes of the next super-block are fetched one iteration ahead of their use
+        auto row_of = [&](const TileCtx &c) -> const uint8_t * {
+            int grow = c.row0 + r;
+            if (grow >= nrows) grow = nrows - 1;        // ragged last tile: duplicate a valid row, never stored
+            return c.w + (size_t)grow * row_bytes;
+        };
+        auto next_tile = [&](int t, TileCtx &c) -> int {      // first tile >= t of this CTA that has work, or ntiles
+            while (t < ntiles && !tile_ctx(t, ntt, w, gi, c)) t += gridDim.x;
+            return t;
+        };
+        // the GGUF bytes of the next super-block (of this or of the next tile) are fetched one iteration ahead of their use
+        TileCtx cx;
+        int t = next_tile(blockIdx.x, cx);
+        const uint8_t *wrow = t < ntiles ? row_of(cx) : nullptr;
         RawBlock<WTYPE> nxt_raw;
-        nxt_raw.load(wrow, 0, h, jh);
-        for (int sb = 0; sb < nsb; ++sb) {
-            const int s = sb & 1;
-            uint8_t *stB = stB0 + s * kStageB;
-            if (dbg & 1) {
-                if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
-                fence_proxy_async_smem();
+        if (t < ntiles) nxt_raw.load(wrow, 0, h, jh);
+        int it = 0;
+        bool alive = true;
+        while (t < ntiles && alive) {
+            TileCtx nx;
+            const int tn = next_tile(t + gridDim.x, nx);
+            const uint8_t *wnext = tn < ntiles ? row_of(nx) : nullptr;
+            for (int sb = 0; sb < nsb; ++sb, ++it) {
+                const int s = it % kStagesB;
+                uint8_t *stB = stB0 + s * kStageB;
+                const RawBlock<WTYPE> cur = nxt_raw;
+                if (!(dbg & 1)) {
+                    if (sb + 1 < nsb) nxt_raw.load(wrow, sb + 1, h, jh);
+                    else if (wnext) nxt_raw.load(wnext, 0, h, jh);
+                }
+                if (it >= kStagesB && !wait_or_abort(&bar_doneB[s], ((it / kStagesB) - 1) & 1, abort_flag)) { alive = false; break; }
+                if (!(dbg & 1)) cur.unpack(stB, r, h, jh, reinterpret_cast<float2 *>(ringW + (it & 7) * 512));
+                fence_proxy_async_smem();       // make these generic-proxy writes visible to the tensor core
                 mbar_arrive(&bar_fullB[s]);
-                continue;
             }
-            const RawBlock<WTYPE> cur = nxt_raw;
-            if (sb + 1 < nsb) nxt_raw.load(wrow, sb + 1, h, jh);
-            if (sb >= 2 && !wait_or_abort(&bar_acc[s], ((sb >> 1) - 1) & 1, abort_flag)) break;   // M(sb-2) has read this stage
-            cur.unpack(stB, r, h, jh, reinterpret_cast<float2 *>(ringW + (sb & 7) * 512));
-            fence_proxy_async_smem();       // make these generic-proxy writes visible to the tensor core
-            mbar_arrive(&bar_fullB[s]);
+            t = tn; wrow = wnext;
         }
     } else if (warp == kEpiWarps + kProdWarps + 1) {
         // ===== activation loader: one thread keeps up to three super-blocks of int8 activations in flight =====
         if (lane == 0) {
-            for (int sb = 0; sb < nsb; ++sb) {
-                const int a = sb % kStagesA;
-                if (sb >= kStagesA && !wait_or_abort(&bar_doneA[a], ((sb / kStagesA) - 1) & 1, abort_flag)) break;
-                if (dbg & 1) { mbar_arrive(&bar_fullA[a]); continue; }
-                const uint8_t *blob = act + TileBlob::offset(tokens, nsb, tt, sb);
-                uint8_t *dstA = stA0 + a * kStageA, *dstS = ringA + (sb & 7) * 512;
-                cq_mbar_expect_tx(&bar_fullA[a], (unsigned)(tile_rows * kTokBytes));
-                if (tile_rows == kTokTile) cq_bulk_g2s(dstA, blob, kStageA, &bar_fullA[a]);        // scratch layout == smem layout
-                else
-                    for (int sl = 0; sl < kSlabsA; ++sl)
-                        cq_bulk_g2s(dstA + sl * kSlabA, blob + (size_t)sl * tile_rows * 16, (unsigned)(tile_rows * 16), &bar_fullA[a]);
-                cq_bulk_g2s(dstS, blob + (size_t)tile_rows * (16 * kSlabsA), (unsigned)(tile_rows * 4), &bar_fullA[a]);
+            int it = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+                TileCtx cx;
+                if (!tile_ctx(t, ntt, w, gi, cx)) continue;
+                const int tile_rows = (int)TileBlob::tile_rows(tokens, cx.tt);
+                for (int sb = 0; sb < nsb; ++sb, ++it) {
+                    const int a = it % kStagesA;
+                    if (it >= kStagesA && !wait_or_abort(&bar_doneA[a], ((it / kStagesA) - 1) & 1, abort_flag)) { alive = false; break; }
+                    if (dbg & 1) { mbar_arrive(&bar_fullA[a]); continue; }
+                    const uint8_t *blob = act + TileBlob::offset(tokens, nsb, cx.tt, sb);
+                    uint8_t *dstA = stA0 + a * kStageA, *dstS = ringA + (it & 7) * 512;
+                    cq_mbar_expect_tx(&bar_fullA[a], (unsigned)(tile_rows * kTokBytes));
+                    if (tile_rows == kTokTile) cq_bulk_g2s(dstA, blob, kStageA, &bar_fullA[a]);        // scratch layout == smem layout
+                    else
+                        for (int sl = 0; sl < kSlabsA; ++sl)
+                            cq_bulk_g2s(dstA + sl * kSlabA, blob + (size_t)sl * tile_rows * 16, (unsigned)(tile_rows * 16), &bar_fullA[a]);
+                    cq_bulk_g2s(dstS, blob + (size_t)tile_rows * (16 * kSlabsA), (unsigned)(tile_rows * 4), &bar_fullA[a]);
+                }
             }
         }
         __syncwarp();
     } else if (warp == kEpiWarps + kProdWarps) {
         // ===== MMA issuer =====
         constexpr uint32_t idesc = make_idesc_i8(kTokTile, kN);
-        for (int sb = 0; sb < nsb; ++sb) {
-            const int s = sb & 1, a = sb % kStagesA;
-            if (!wait_or_abort(&bar_fullA[a], (sb / kStagesA) & 1, abort_flag)) break;
-            if (!(dbg & 4)) {
-                if (!wait_or_abort(&bar_fullB[s], (sb >> 1) & 1, abort_flag)) break;
-                if (sb >= 2 && !wait_or_abort(&bar_free[s], ((sb >> 1) - 1) & 1, abort_flag)) break;
-            }
-            tc_fence_after();
-            if (lane == 0) {
-                mbar_arrive(&bar_vis[s]);       // relay: everything this thread has acquired is now visible to the epilogue
-                const uint32_t a0 = cq_smem_u32(stA0 + a * kStageA), b0 = cq_smem_u32(stB0 + s * kStageB);
-                const uint32_t tacc = tmem_base + (uint32_t)(s * kAccCols);
+        int it = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+            TileCtx cx;
+            if (!tile_ctx(t, ntt, w, gi, cx)) continue;
+            for (int sb = 0; sb < nsb; ++sb, ++it) {
+                const int a = it % kStagesA, s = it % kStagesB, c = it & 1;
+                if (!wait_or_abort(&bar_fullA[a], (it / kStagesA) & 1, abort_flag) ||
+                    !wait_or_abort(&bar_fullB[s], (it / kStagesB) & 1, abort_flag) ||
+                    (it >= 2 && !wait_or_abort(&bar_free[c], ((it >> 1) - 1) & 1, abort_flag))) { alive = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    mbar_arrive(&bar_vis[c]);       // relay: everything this thread has acquired is now visible to the epilogue
+                    const uint32_t a0 = cq_smem_u32(stA0 + a * kStageA), b0 = cq_smem_u32(stB0 + s * kStageB);
+                    const uint32_t tacc = tmem_base + (uint32_t)(c * kAccCols);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint64_t da = make_smem_desc(a0 + ks * 2 * kSlabA, kSlabA, 128);
-                    const uint64_t db = make_smem_desc(b0 + ks * 2 * kSlabB, kSlabB, 128);
-                    tc_mma_i8(tacc, da, db, idesc, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint64_t da = make_smem_desc(a0 + ks * 2 * kSlabA, kSlabA, 128);
+                        const uint64_t db = make_smem_desc(b0 + ks * 2 * kSlabB, kSlabB, 128);
+                        tc_mma_i8(tacc, da, db, idesc, ks > 0 ? 1u : 0u);
+                    }
+                    // split block sums x per-run minimum / scale -> columns kN ..
+                    tc_mma_i8(tacc + kN, make_smem_desc(a0 + 16 * kSlabA, kSlabA, 128), make_smem_desc(b0 + 16 * kSlabB, kSlabB, 128), idesc, 0u);
+                    tc_commit(&bar_acc[c]);
+                    tc_commit(&bar_doneA[a]);
+                    tc_commit(&bar_doneB[s]);
                 }
-                // split block sums x per-run minimum / scale -> columns kN ..
-                tc_mma_i8(tacc + kN, make_smem_desc(a0 + 16 * kSlabA, kSlabA, 128), make_smem_desc(b0 + 16 * kSlabB, kSlabB, 128), idesc, 0u);
-                tc_commit(&bar_acc[s]);
-                tc_commit(&bar_doneA[a]);
+                __syncwarp();
             }
-            __syncwarp();
         }
     } else {
         // ===== epilogue: warp q owns TMEM lanes 32 (q % 4) .. +31 = tokens, weight rows 32 (q / 4) .. +31 =====
         constexpr int kMyRows = kRowTile * 4 / kEpiWarps;      // 32
         const int quad = warp & 3, rh = warp >> 2;
         const int tok_local = quad * 32 + lane;
-        const int tok = tt * kTokTile + tok_local;
-        float acc[kMyRows];
-#pragma unroll
-        for (int i = 0; i < kMyRows; ++i) acc[i] = 0.0f;
+        int it = 0;
         bool alive = true;
-        for (int sb = 0; sb < nsb && alive; ++sb) {
-            const int s = sb & 1;
-            if (!wait_or_abort(&bar_vis[s], (sb >> 1) & 1, abort_flag) ||
-                !wait_or_abort(&bar_acc[s], (sb >> 1) & 1, abort_flag)) { alive = false; break; }
-            tc_fence_after();
-            if (dbg & 2) { tc_fence_before(); mbar_arrive(&bar_free[s]); continue; }
-            const float da = *reinterpret_cast<const float *>(ringA + (sb & 7) * 512 + tok_local * 4);
-            const uint8_t *rw = ringW + (sb & 7) * 512 + rh * kMyRows * 8;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(s * kAccCols + rh * kMyRows);
-            // 8 weight rows at a time; the TMEM loads of the next chunk are in flight while this one is computed
-            uint32_t v1[2][8], v2[2][8], vl[2][8], vh[2][8];
-            tmem_ld8(taddr, v1[0]);
-            tmem_ld8(taddr + kRowTile, v2[0]);
-            tmem_ld8(taddr + 2 * kRowTile, vl[0]);
-            tmem_ld8(taddr + 3 * kRowTile, vh[0]);
+        for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+            TileCtx cx;
+            if (!tile_ctx(t, ntt, w, gi, cx)) continue;
+            const int tok = cx.tt * kTokTile + tok_local;
+            float acc[kMyRows];
 #pragma unroll
-            for (int c = 0; c < kMyRows / 8; ++c) {
-                tmem_ld_wait();
-                if (c + 1 < kMyRows / 8) {
-                    tmem_ld8(taddr + (c + 1) * 8, v1[(c + 1) & 1]);
-                    tmem_ld8(taddr + kRowTile + (c + 1) * 8, v2[(c + 1) & 1]);
-                    tmem_ld8(taddr + 2 * kRowTile + (c + 1) * 8, vl[(c + 1) & 1]);
-                    tmem_ld8(taddr + 3 * kRowTile + (c + 1) * 8, vh[(c + 1) & 1]);
-                }
+            for (int i = 0; i < kMyRows; ++i) acc[i] = 0.0f;
+            for (int sb = 0; sb < nsb; ++sb, ++it) {
+                const int c = it & 1;
+                if (!wait_or_abort(&bar_vis[c], (it >> 1) & 1, abort_flag) ||
+                    !wait_or_abort(&bar_acc[c], (it >> 1) & 1, abort_flag)) { alive = false; break; }
+                tc_fence_after();
+                if (dbg & 2) { tc_fence_before(); mbar_arrive(&bar_free[c]); continue; }
+                const float da = *reinterpret_cast<const float *>(ringA + (it & 7) * 512 + tok_local * 4);
+                const uint8_t *rw = ringW + (it & 7) * 512 + rh * kMyRows * 8;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * kAccCols + rh * kMyRows);
+                // 8 weight rows at a time; the TMEM loads of the next chunk are in flight while this one is computed
+                uint32_t v1[2][8], v2[2][8], vl[2][8], vh[2][8];
+                tmem_ld8(taddr, v1[0]);
+                tmem_ld8(taddr + kRowTile, v2[0]);
+                tmem_ld8(taddr + 2 * kRowTile, vl[0]);
+                tmem_ld8(taddr + 3 * kRowTile, vh[0]);
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    const float4 dw = *reinterpret_cast<const float4 *>(rw + (c * 8 + i) * 8);   // (d, dmin) x 2 rows
+                for (int ch = 0; ch < kMyRows / 8; ++ch) {
+                    tmem_ld_wait();
+                    if (ch + 1 < kMyRows / 8) {
+                        tmem_ld8(taddr + (ch + 1) * 8, v1[(ch + 1) & 1]);
+                        tmem_ld8(taddr + kRowTile + (ch + 1) * 8, v2[(ch + 1) & 1]);
+                        tmem_ld8(taddr + 2 * kRowTile + (ch + 1) * 8, vl[(ch + 1) & 1]);
+                        tmem_ld8(taddr + 3 * kRowTile + (ch + 1) * 8, vh[(ch + 1) & 1]);
+                    }
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const float dd = e ? dw.z : dw.x, dmn = e ? dw.w : dw.y;
-                        const int sums = 64 * (int)vh[c & 1][i + e] + (int)vl[c & 1][i + e];        // sum_j v_j bsum_j, exact
-                        float t;
-                        if constexpr (WTYPE == CQ_Q4_K) {
-                            const int sdot = 8 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e];     // exact, up to 3.1e7
-                            t = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float(sums)));
-                        } else {        // Q6_K: 64*hi + lo - 32*sum(sc*bsum), exact in int32 (< 4.1e8)
-                            const int tot = 64 * (int)v2[c & 1][i + e] + (int)v1[c & 1][i + e] - 32 * sums;
-                            t = __fmul_rn(dd, (float)tot);
+                    for (int i = 0; i < 8; i += 2) {
+                        const float4 dw = *reinterpret_cast<const float4 *>(rw + (ch * 8 + i) * 8);   // (d, dmin) x 2 rows
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float dd = e ? dw.z : dw.x, dmn = e ? dw.w : dw.y;
+                            const int sums = 64 * (int)vh[ch & 1][i + e] + (int)vl[ch & 1][i + e];        // sum_j v_j bsum_j, exact
+                            float tv;
+                            if constexpr (WTYPE == CQ_Q4_K) {
+                                const int sdot = 8 * (int)v2[ch & 1][i + e] + (int)v1[ch & 1][i + e];     // exact, up to 3.1e7
+                                tv = __fmaf_rn(dd, (float)sdot, -__fmul_rn(dmn, small_int_to_float(sums)));
+                            } else {        // Q6_K: 64*hi + lo - 32*sum(sc*bsum), exact in int32 (< 4.1e8)
+                                const int tot = 64 * (int)v2[ch & 1][i + e] + (int)v1[ch & 1][i + e] - 32 * sums;
+                                tv = __fmul_rn(dd, (float)tot);
+                            }
+                            acc[ch * 8 + i + e] = __fmaf_rn(da, tv, acc[ch * 8 + i + e]);
                         }
-                        acc[c * 8 + i + e] = __fmaf_rn(da, t, acc[c * 8 + i + e]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&bar_free[c]);
+            }
+            if (!alive) break;
+            bool store = tok < tokens;
+            int64_t orow = tok;
+            if (gi.tiles) {         // output row = the pair of this job, scaled by its routing weight
+                store = tok_local < cx.valid;
+                if (store) {
+                    const int pair = gi.sorted_token_ids[cx.job0 + tok_local];
+                    orow = pair;
+                    if (gi.topk_weights) {
+                        const float sc = gi.topk_weights[pair];
+#pragma unroll
+                        for (int i = 0; i < kMyRows; ++i) acc[i] = __fmul_rn(acc[i], sc);
                     }
                 }
             }
-            tc_fence_before();
-            mbar_arrive(&bar_free[s]);
-        }
-        bool store = alive && tok < tokens;
-        int64_t orow = tok;
-        if (gi.tiles) {         // output row = the pair of this job, scaled by its routing weight
-            store = alive && tok_local < valid;
-            if (store) {
-                const int pair = gi.sorted_token_ids[job0 + tok_local];
-                orow = pair;
-                if (gi.topk_weights) {
-                    const float sc = gi.topk_weights[pair];
-#pragma unroll
-                    for (int i = 0; i < kMyRows; ++i) acc[i] = __fmul_rn(acc[i], sc);
-                }
-            }
-        }
-        const int c0 = row0 + rh * kMyRows;
-        if (store && out_kind != CQ_F32) {
-#pragma unroll
-            for (int i = 0; i < kMyRows; ++i)
-                if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
-        } else if (store) {
-            float *o = (float *)out_v + (size_t)orow * stride_out + c0;
-            if (c0 + kMyRows <= nrows && (((uintptr_t)o) & 15) == 0) {
-#pragma unroll
-                for (int i = 0; i < kMyRows; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-            } else {
+            const int c0 = cx.row0 + rh * kMyRows;
+            if (store && out_kind != CQ_F32) {
 #pragma unroll
                 for (int i = 0; i < kMyRows; ++i)
-                    if (c0 + i < nrows) o[i] = acc[i];
+                    if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
+            } else if (store) {
+                float *o = (float *)out_v + (size_t)orow * stride_out + c0;
+                if (c0 + kMyRows <= nrows && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+                    for (int i = 0; i < kMyRows; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kMyRows; ++i)
+                        if (c0 + i < nrows) o[i] = acc[i];
+                }
             }
         }
     }
@@ -634,6 +683,19 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
     __syncthreads();
     if (tid == 0 && *abort_flag) atomicExch(&g_prefill_timeout_flag, 1);
     if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+// One CTA per SM, or one per tile when there are fewer tiles.
+static unsigned prefill_grid(int ntiles) {
+    static int sms[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int n = 148;
+    if (dev >= 0 && dev < 64) {
+        if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (sms[dev] > 0) n = sms[dev];
+    }
+    return (unsigned)(ntiles < n ? ntiles : n);
 }
 
 }  // namespace
@@ -682,13 +744,14 @@ extern "C" void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, 
         else cudaFuncSetAttribute(prefill_kernel<CQ_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         attr_done[ti][dev] = true;
     }
-    const dim3 grid((nrows_x + kRowTile - 1) / kRowTile, (tokens + kTokTile - 1) / kTokTile);
+    const int ntt = (tokens + kTokTile - 1) / kTokTile, ntiles = ((nrows_x + kRowTile - 1) / kRowTile) * ntt;
+    const unsigned grid = prefill_grid(ntiles);
     if (ti == 0)
         prefill_kernel<CQ_Q4_K><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(
-            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg, GroupInfo{});
+            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg, ntt, ntiles, GroupInfo{});
     else
         prefill_kernel<CQ_Q6_K><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(
-            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg, GroupInfo{});
+            (const uint8_t *)vx, (const uint8_t *)scratch, dst, out_elem, ncols_x, nrows_x, tokens, stride_dst, g_prefill_dbg, ntt, ntiles, GroupInfo{});
     cq_check_launch("prefill gemm");
 }
 
@@ -747,13 +810,14 @@ extern "C" void cq_moe_prefill_gemm(int wtype, const void *input, int in_elem, c
         else cudaFuncSetAttribute(prefill_kernel<CQ_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         attr_done[ti][dev] = true;
     }
-    const dim3 grid((size_n + kRowTile - 1) / kRowTile, mt);
+    const int ntiles = ((size_n + kRowTile - 1) / kRowTile) * mt;
+    const unsigned grid = prefill_grid(ntiles);
     if (ti == 0)
         prefill_kernel<CQ_Q4_K><<<grid, kThreads, kSmemBytes, st>>>((const uint8_t *)weights, blobs, out, CQ_F32, size_k, size_n,
-                                                                     mt * kTokTile, size_n, g_prefill_dbg, gi);
+                                                                     mt * kTokTile, size_n, g_prefill_dbg, mt, ntiles, gi);
     else
         prefill_kernel<CQ_Q6_K><<<grid, kThreads, kSmemBytes, st>>>((const uint8_t *)weights, blobs, out, CQ_F32, size_k, size_n,
-                                                                     mt * kTokTile, size_n, g_prefill_dbg, gi);
+                                                                     mt * kTokTile, size_n, g_prefill_dbg, mt, ntiles, gi);
     cq_check_launch("moe prefill gemm");
 }
 
