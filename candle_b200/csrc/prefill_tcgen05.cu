@@ -123,11 +123,15 @@ __device__ __forceinline__ float small_int_to_float(int x) {
     return __fadd_rn(__int_as_float(x + 0x4B400000), -12582912.0f);
 }
 
-// Wait on `bar` unless the CTA has been aborted; raises the abort flag itself after about a second.
+// Wait on `bar` unless the CTA has been aborted; raises the abort flag itself after about a second.  The abort flag
+// and the clock are looked at once in 32 polls only: each poll already sleeps inside mbarrier.try_wait, and the
+// waiting warps must not take issue slots and shared-memory bandwidth from the working ones.
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, unsigned parity, volatile int *abort_flag) {
     if (cq_mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    unsigned polls = 0;
     while (!cq_mbar_try_wait(bar, parity)) {
+        if ((++polls & 31u) != 0) continue;
         if (*abort_flag) return false;
         if (clock64() - t0 > 2000000000LL) { *abort_flag = 1; return false; }
     }
