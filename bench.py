@@ -17,7 +17,8 @@ f32 outputs, per GEMV) / device time of the step.
   cpu_baseline : the reference's CPU algorithm (oracle port, AVX2, all host cores) on a bounded sample.
 
 With N > 1 GPUs (torchrun) every weight matrix is sharded by output rows over the ranks (column-parallel);
-each rank runs its slice and the slices are all-gathered over NCCL.  Total work is fixed: "strong" scaling.
+each rank runs its slice and the slices are all-gathered by one kernel over NVLink peer memory (csrc/peer_gather.cu).
+Total work is fixed: "strong" scaling.
 
 `--impl reference` times the reference's CPU implementation of the path (the oracle port) on the host cores.
 """
@@ -199,7 +200,11 @@ def run_gpu(args):
     xs = {(k, b): torch.randn((b, k), device=dev, generator=torch.Generator(device=dev).manual_seed(k + b))
           for (k, _) in SHAPES for b in BATCHES}
     outs = {(n, b): torch.empty((b, n // world), device=dev) for (_, n) in SHAPES for b in BATCHES}
-    gathered = {(n, b): torch.empty((world, b, n // world), device=dev) for (_, n) in SHAPES for b in BATCHES} if world > 1 else None
+    gather = None
+    if world > 1:       # one kernel over NVLink peer memory per gather (falls back to the NCCL collective with CQ_PEER_GATHER=0)
+        from candle_b200.parallel import make_gatherer
+        gather = make_gatherer(None, world, dev)
+    gather_kind = "peer-memory gather kernel" if type(gather).__name__ == "PeerGatherer" else "NCCL all-gather"
     order = [(b, t, k, n) for b in BATCHES for t in TYPE_NAMES for (k, n) in SHAPES]
     total_bytes = step_bytes()
 
@@ -207,7 +212,7 @@ def run_gpu(args):
         for (b, t, k, n) in order:
             mats[(t, k, n)].forward(xs[(k, b)], out=outs[(n, b)])
             if world > 1:
-                dist.all_gather_into_tensor(gathered[(n, b)], outs[(n, b)])
+                gather(outs[(n, b)])
 
     # pre-quantized activations for the GEMV-only (roofline) pass
     kp = {k: capi.pad(k, 512) for (k, _) in SHAPES}
@@ -263,7 +268,7 @@ def run_gpu(args):
             ms = float(t.item())
         return ms / steps
 
-    use_graph = True           # the NCCL all-gathers of the sharded run are recorded into the graph as well
+    use_graph = True           # the gathers of the sharded run are kernels of this library (or NCCL calls) and are recorded as well
     graphed = []
     sampler = ClockSampler(local)
     if rank == 0:
@@ -285,8 +290,7 @@ def run_gpu(args):
             d_x[(k, b)].copy_(h_x[(k, b)], non_blocking=True)
             y = mats[(t, k, n)].forward(d_x[(k, b)], out=outs[(n, b)])
             if world > 1:
-                dist.all_gather_into_tensor(gathered[(n, b)], y)
-                h_y[(n, b)].view(b, world, n // world).copy_(gathered[(n, b)].permute(1, 0, 2), non_blocking=True)
+                h_y[(n, b)].copy_(gather(y), non_blocking=True)
             else:
                 h_y[(n, b)].copy_(y, non_blocking=True)
 
@@ -294,7 +298,7 @@ def run_gpu(args):
 
     # free the sweep's buffers before building the decoder
     del mats, xs, outs, q8, h_x, h_y, d_x
-    gathered = None
+    gather = None
     torch.cuda.empty_cache()
     decode = None
     if not args.no_decode:
@@ -315,7 +319,7 @@ def run_gpu(args):
         "config": {"workload": "gemv_sweep_llama3_8b", "types": TYPE_NAMES, "shapes_k_n": SHAPES, "batches": BATCHES,
                    "gemv_per_step": len(order), "bytes_per_step": total_bytes,
                    "l2": "1.6 GB of distinct weights are streamed between two uses of the same matrix (L2 is 126 MB)",
-                   "parallelism": f"column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU",
+                   "parallelism": f"column-parallel x{world} + {gather_kind}" if world > 1 else "single GPU",
                    "launch": "CUDA graph replay" if graphed and graphed[0] else "eager launches"},
         "frac_of_8TBps_nominal_per_gpu": value / world / 8000.0,
         "gpu_launches": 2 * len(order) * args.steps,

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libcandle_q_b200.so")
 Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 2, 3, 6, 7, 8, 10, 11, 12, 13, 14
 F32, F16, BF16 = 0, 1, 2
 ACT_Q8_1, ACT_Q8_0, ACT_Q8_K = 0, 1, 2
+MAX_PEERS = 8      # CQ_MAX_PEERS
 
 TYPE_SIZE = {Q4_0: 18, Q4_1: 20, Q5_0: 22, Q5_1: 24, Q8_0: 34, Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210}
 BLOCK_ELEMS = {Q4_0: 32, Q4_1: 32, Q5_0: 32, Q5_1: 32, Q8_0: 32, Q2_K: 256, Q3_K: 256, Q4_K: 256, Q5_K: 256, Q6_K: 256}
@@ -74,6 +75,10 @@ def lib() -> C.CDLL:
         L.cq_add_rms_norm_f32.argtypes = [vp, vp, vp, vp, i32, i32, C.c_float, vp]
         L.cq_rope_store_kv_f32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
         L.cq_silu_mul_f32.argtypes = [vp, vp, i32, i32, vp]
+        L.cq_peer_gather_words.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.cq_peer_gather_stage_bytes.argtypes = [i32, i32, i32]
+        L.cq_peer_gather_stage_bytes.restype = C.c_size_t
+        L.cq_peer_gather_timeout_flag.restype = i32
         L.cq_add_rms_norm_q8_1.argtypes = [vp, vp, vp, vp, i32, i32, i32, C.c_float, vp]
         L.cq_silu_mul_q8_1.argtypes = [vp, vp, i32, i32, i32, vp]
         L.cq_attention_q8_1.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]

@@ -1,0 +1,117 @@
+// All-gather of row-sharded GEMV outputs over NVLink peer memory, one kernel per gather, no library collective.
+//
+// Where candle's multi-GPU example reduces the partial sums of K-sharded projections with NCCL
+// (candle-examples/examples/llama_multiprocess/model.rs:28-66, `AllReduce` custom op over cudarc's nccl bindings), this
+// library shards weight ROWS, so a rank owns whole output columns and the exchange is an all-gather of a few kilobytes:
+// latency, not bandwidth.  The kernel therefore sends data and arrival signal in one store: every rank holds, for each
+// gather site, a staging area of 8-byte slots {word, epoch} that all ranks have mapped (CUDA virtual-memory handles
+// exchanged once at set-up by the host); 8-byte stores arrive whole.  A thread
+//   1. stores its words of this rank's slice, tagged with the current epoch, into the staging areas of all other ranks
+//      (plain peer stores) and into the local result,
+//   2. then polls the slots the other ranks fill here until each carries the epoch, and moves the word into the result
+//      [rows, n_total] (columns [p * n_local, +n_local) for rank p).
+// No fence, flag or atomic crosses the link: a gather costs one NVLink hop plus the polling.  `epoch` counts the gathers
+// of this rank in device memory (all ranks issue the same sequence), so the kernel can be replayed from a CUDA graph and
+// stale slots never match.  Every poll is bounded (about a second); after a give-up a device flag is raised and the
+// kernel returns.  A staging area must not be the target of two consecutive gathers (a fast rank would overwrite slots
+// a slow one has not read yet); with one other gather in between, that gather orders the accesses.  The host side
+// alternates two areas per shape for that.
+#include "../../include/candle_q_b200.h"
+#include "common.cuh"
+
+namespace {
+
+struct PeerPtrs { void *p[CQ_MAX_PEERS]; };
+
+__device__ int g_peer_gather_timeout = 0;
+
+__device__ __forceinline__ void st_slot(uint2 *p, uint32_t word, uint32_t epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+// stage.p[q]: staging area of rank q, [world][rows * n_local] slots, as mapped here.
+// state[0]: gathers completed by this rank, state[1]: CTAs of the running launch that are done.
+__global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__restrict__ src, int src_stride, PeerPtrs stage,
+                                                          uint32_t *__restrict__ dst, unsigned *state, int rows, int n_local,
+                                                          int n_total, int rank, int world) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();      // the slice is the preceding kernel's output
+    const unsigned epoch = *(volatile unsigned *)state + 1u;      // only the CTA that finishes last advances it
+    const int64_t total = (int64_t)rows * n_local;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < total; i += nthr) {
+        const int j = (int)(i / n_local), c = (int)(i % n_local);
+        const uint32_t v = src[(int64_t)j * src_stride + c];
+        for (int q = 1; q < world; ++q) {
+            const int p = (rank + q) % world;
+            st_slot((uint2 *)stage.p[p] + (int64_t)rank * total + i, v, epoch);
+        }
+        dst[(int64_t)j * n_total + (int64_t)rank * n_local + c] = v;
+    }
+    const uint2 *mine = (const uint2 *)stage.p[rank];
+    bool gave_up = false;
+    for (int q = 1; q < world && !gave_up; ++q) {
+        const int p = (rank + world - q) % world;      // the rank whose first store went to this one comes first
+        for (int64_t i = tid; i < total; i += nthr) {
+            const uint2 *slot = mine + (int64_t)p * total + i;
+            uint2 v = ld_slot(slot);
+            if (v.y != epoch) {
+                const long long t0 = clock64();
+                while ((v = ld_slot(slot)).y != epoch) {
+                    if (clock64() - t0 > 2000000000LL) { gave_up = true; break; }
+                }
+                if (gave_up) break;
+            }
+            const int j = (int)(i / n_local), c = (int)(i % n_local);
+            dst[(int64_t)j * n_total + (int64_t)p * n_local + c] = v.x;
+        }
+    }
+    if (gave_up) atomicExch(&g_peer_gather_timeout, 1);
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(&state[1], 1u) == gridDim.x - 1) {
+        state[1] = 0u;
+        __threadfence();
+        *(volatile unsigned *)state = epoch;
+    }
+}
+
+}  // namespace
+
+extern "C" size_t cq_peer_gather_stage_bytes(int rows, int n_local, int world) {
+    if (rows <= 0 || n_local <= 0 || world < 1) return 0;
+    return (size_t)world * rows * n_local * 8;
+}
+
+extern "C" void cq_peer_gather_words(const void *src, int src_stride, void *const *peer_stage, void *dst, void *state, int rows,
+                                     int n_local, int n_total, int rank, int world, void *stream) {
+    if (!src || !peer_stage || !dst || !state || rows <= 0 || n_local <= 0 || world < 1 || world > CQ_MAX_PEERS || rank < 0 ||
+        rank >= world || n_total < world * n_local || src_stride < n_local) {
+        cq_set_status(CQ_ERR_BAD_ARG, "peer gather: null pointer or inconsistent shape");
+        return;
+    }
+    PeerPtrs s{};
+    for (int p = 0; p < world; ++p) {
+        if (!peer_stage[p] || (uintptr_t)peer_stage[p] % 8 != 0) { cq_set_status(CQ_ERR_BAD_ARG, "peer gather: missing or misaligned staging pointer"); return; }
+        s.p[p] = peer_stage[p];
+    }
+    const int64_t total = (int64_t)rows * n_local;
+    int grid = (int)((total + 1023) / 1024);       // four words per thread, at most 32 CTAs
+    if (grid > 32) grid = 32;
+    if (grid < 1) grid = 1;
+    cq_launch_k(peer_gather_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const uint32_t *)src, src_stride, s,
+                (uint32_t *)dst, (unsigned *)state, rows, n_local, n_total, rank, world);
+    cq_check_launch("peer gather");
+}
+
+// 1 if a peer gather on the current device gave up waiting for another rank's data (synchronises the device).
+extern "C" int cq_peer_gather_timeout_flag(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_peer_gather_timeout, sizeof v) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+    if (v) cq_set_status(CQ_ERR_TIMEOUT, "peer gather: a bounded wait for another rank gave up");
+    return v;
+}

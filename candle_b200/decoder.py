@@ -21,7 +21,7 @@ import math
 import torch
 
 from . import capi
-from .parallel import Gatherer, argmax_sharded
+from .parallel import Gatherer, argmax_sharded, make_gatherer
 from .quantized import GgmlDType, QMatMul, QTensor
 from .synth import random_blocks
 
@@ -82,7 +82,7 @@ class LlamaShapedDecoder:
         if PIECES % world or cfg.n_kv_heads % world or cfg.vocab % PIECES or cfg.ffn % PIECES:
             raise ValueError("world size must divide 8 and the head / vocabulary / ffn sizes")
         self.cfg, self.device, self.rank, self.world, self.batch = cfg, torch.device(device), rank, world, batch
-        self.gather = Gatherer(group, world)
+        self.gather = make_gatherer(group, world, self.device)
         d, hd = cfg.d_model, cfg.head_dim
         self.hq_l, self.hkv_l = cfg.n_heads // world, cfg.n_kv_heads // world
         g = torch.Generator(device=self.device)

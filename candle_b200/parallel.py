@@ -6,9 +6,13 @@ The per-element summation order does not depend on the shard count, so results a
 world size - which K-sharding followed by an all-reduce (the scheme of candle's only multi-GPU example,
 candle-examples/examples/llama_multiprocess/model.rs:13-137) cannot give.
 
-Host logic here is device-free and is exercised on CPU with the gloo backend.
+On CUDA the exchange runs as one kernel of this library over NVLink peer memory (`PeerGatherer`, csrc/peer_gather.cu);
+`Gatherer` (a library all-gather) is the portable form and what the CPU tests with the gloo backend exercise.
 """
 from __future__ import annotations
+
+import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -52,6 +56,90 @@ class Gatherer:
             return stacked.view(1, self.world * n_local)
         full.view(rows, self.world, n_local).copy_(stacked.view(self.world, rows, n_local).permute(1, 0, 2))
         return full
+
+
+class PeerGatherer(Gatherer):
+    """The same gather as one kernel over peer memory: every rank stores its slice, word by word together with an epoch
+    tag, into staging areas of all other ranks and picks up what they stored here (`cq_peer_gather_words`).  The staging
+    areas live in symmetric memory (`torch.distributed._symmetric_memory`: one CUDA virtual-memory allocation per rank,
+    mapped by all); they are made on first use of a shape, which is a collective step, so shapes must first occur
+    outside CUDA-graph capture and in the same order on all ranks.  Two areas per shape alternate when one shape is
+    gathered twice in a row.  Slices above `MAX_WORDS` 32-bit words (prompts) go through the library all-gather: the
+    slot protocol doubles the bytes on the link and is built for latency, not bandwidth."""
+
+    MAX_WORDS = 1 << 17     # 512 KiB per rank
+
+    def __init__(self, group=None, world: int | None = None):
+        super().__init__(group, world)
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import capi
+        self._symm, self._capi = symm_mem, capi
+        g = group if group is not None else dist.group.WORLD
+        self._group_name = g.group_name
+        self.rank = dist.get_rank(g)
+        if self.world > capi.MAX_PEERS:
+            raise ValueError(f"at most {capi.MAX_PEERS} ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._keep = []
+        self._state = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._slots: dict = {}
+        self._last = None
+
+    def _new_slot(self, rows: int, n_local: int, dtype):
+        nbytes = self._capi.lib().cq_peer_gather_stage_bytes(rows, n_local, self.world)
+        stage = self._symm.empty((nbytes,), dtype=torch.uint8, device=self.device)
+        hdl = self._symm.rendezvous(stage, group=self._group_name)
+        stage.zero_()
+        self._keep.append((stage, hdl))
+        ptrs = (ctypes.c_void_p * self._capi.MAX_PEERS)(*[int(p) for p in hdl.buffer_ptrs])
+        return torch.empty((rows, self.world * n_local), dtype=dtype, device=self.device), ptrs
+
+    def __call__(self, local: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return local
+        if local.dim() != 2:
+            raise ValueError("peer gather takes a 2-d tensor")
+        if local.numel() * local.element_size() > 4 * self.MAX_WORDS:
+            self._last = None       # a library collective in between orders the accesses like any other gather
+            return super().__call__(local)
+        dtype = local.dtype
+        if local.element_size() != 4:       # e.g. rows of Q8_1 containers (uint8, 36 bytes each): move them as 32-bit words
+            if (local.shape[1] * local.element_size()) % 4 != 0:
+                raise ValueError("peer gather: rows must be whole 32-bit words")
+            local = local.contiguous().view(torch.int32)
+        elif local.stride(1) != 1:
+            local = local.contiguous()
+        rows, n_local = local.shape
+        key = (rows, n_local, local.dtype)
+        if key not in self._slots:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("a new gather shape inside CUDA-graph capture: run the step once before capturing")
+            self._slots[key] = [[self._new_slot(rows, n_local, local.dtype) for _ in range(2)], 0]
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)      # nobody stores into a staging area before its owner has zeroed it
+        entry = self._slots[key]
+        if self._last == key:
+            entry[1] ^= 1       # never the same staging area twice in a row
+        self._last = key
+        full, ptrs = entry[0][entry[1]]
+        self._capi.lib().cq_peer_gather_words(local.data_ptr(), local.stride(0), ptrs, full.data_ptr(), self._state.data_ptr(),
+                                               rows, n_local, self.world * n_local, self.rank, self.world,
+                                               torch.cuda.current_stream().cuda_stream)
+        return full if full.dtype == dtype else full.view(dtype)
+
+    def check(self) -> None:
+        """Raises if any gather so far gave up waiting for another rank (synchronises the device)."""
+        if self._capi.lib().cq_peer_gather_timeout_flag() != 0:
+            raise RuntimeError("peer gather: a bounded wait for another rank gave up")
+
+
+def make_gatherer(group=None, world: int | None = None, device=None) -> Gatherer:
+    """`PeerGatherer` on CUDA with more than one rank (unless CQ_PEER_GATHER=0), else the library all-gather."""
+    w = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+    on_cuda = device is not None and torch.device(device).type == "cuda"
+    if w > 1 and on_cuda and os.environ.get("CQ_PEER_GATHER", "1") != "0":
+        return PeerGatherer(group, w)
+    return Gatherer(group, w)
 
 
 def argmax_sharded(local_logits: torch.Tensor, vocab_start: int, gather: Gatherer) -> torch.Tensor:

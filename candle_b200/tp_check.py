@@ -17,6 +17,71 @@ from candle_b200.decoder import DecoderConfig, LlamaShapedDecoder  # noqa: E402
 from candle_b200.moe_decoder import MoeDecoderConfig, MoeShapedDecoder  # noqa: E402
 
 
+def check_gather(dev, rank, world) -> str:
+    """Peer-memory gather against the library all-gather: ragged and aligned widths, 1-8 rows, strided slices, one shape
+    twice in a row, eager and replayed from a CUDA graph.  All ranks return the same verdict."""
+    from candle_b200.parallel import Gatherer, PeerGatherer
+    ref, peer = Gatherer(None, world), PeerGatherer(None, world)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    bad = []
+    shapes = [(1, 4096), (2, 1024), (8, 16032), (3, 7), (5, 130), (1, 2), (4, 512), (4, 512), (4, 512), (8, 3584)]
+    for it, (rows, n_local) in enumerate(shapes * 3):
+        wide = torch.randn((rows, n_local + 12), device=dev, generator=gen)
+        local = wide[:, 4:4 + n_local] if it % 2 else wide[:, :n_local].contiguous()
+        want = ref(local).clone()
+        got = peer(local)
+        if not torch.equal(got, want):
+            bad.append((it, rows, n_local))
+    for rows, blocks in ((1, 16), (8, 112), (3, 5)):       # rows of 36-byte containers travel as 32-bit words
+        u = torch.randint(0, 256, (rows, 36 * blocks), device=dev, dtype=torch.uint8, generator=gen)
+        if not torch.equal(peer(u), ref(u)):
+            bad.append(("u8", rows, blocks))
+    # replayed from a graph: three gathers of different shapes, new data before every replay
+    xs = [torch.zeros((r, n), device=dev) for (r, n) in ((2, 1024), (1, 4096), (8, 16032))]
+    for x in xs:
+        peer(x)
+    side = torch.cuda.Stream(device=dev)
+    outs = []
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            outs = [peer(x) for x in xs]
+    for rep in range(4):
+        for x in xs:
+            x.copy_(torch.randn(x.shape, device=dev, generator=gen))
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        for x, o in zip(xs, outs):
+            if not torch.equal(o, ref(x)):
+                bad.append(("graph", rep, tuple(x.shape)))
+    peer.check()
+    # cost of one gather: 100 alternating gathers of a decode-sized and a head-sized slice, replayed from a graph
+    for name, g_ in (("peer", peer), ("nccl", ref)):
+        a, b = torch.randn((1, 4096 // world), device=dev), torch.randn((1, 128256 // world), device=dev)
+        g_(a); g_(b)
+        with torch.cuda.stream(side):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                for _ in range(50):
+                    g_(a); g_(b)
+            gr.replay()
+            side.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(5):
+                gr.replay()
+            e1.record(side)
+            side.synchronize()
+        if rank == 0:
+            print(f"{name} gather: {e0.elapsed_time(e1) * 1000.0 / 500:.2f} us per gather (world {world})", flush=True)
+    peer.check()
+    flag = torch.tensor([len(bad)], device=dev)
+    dist.all_reduce(flag)
+    return "identical" if int(flag.item()) == 0 else f"peer gather differs: {bad[:4]} (rank {rank})"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--full", action="store_true", help="Llama-3-8B shape instead of the tiny test shape")
@@ -25,11 +90,21 @@ def main():
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--moe", action="store_true", help="the mixture-of-experts harness (expert parallel) instead of the dense one")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--gather", action="store_true", help="check the peer-memory gather kernel against the NCCL all-gather")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
     dist.init_process_group("nccl", device_id=dev)
+    if args.gather:
+        verdict = check_gather(dev, rank, world)
+        if rank == 0:
+            print(verdict)
+            if args.out:
+                open(args.out, "w").write(verdict + "\n")
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if verdict == "identical" else 1)
     if args.moe:
         cfg = MoeDecoderConfig.qwen3_30b_a3b() if args.full else MoeDecoderConfig.tiny()
         Model = MoeShapedDecoder

@@ -257,6 +257,20 @@ void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv,
                           float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
                           int q_stride, int k_stride, int v_stride, void *stream);
 void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream);
+
+/* All-gather of row-sharded outputs over NVLink peer memory in one kernel (replaces the NCCL collective that
+ * candle-examples/examples/llama_multiprocess/model.rs:28-66 issues per projection).  `src`: this rank's slice, `rows`
+ * rows of `n_local` 32-bit words, row stride `src_stride` words.  `peer_stage[p]`: rank p's staging area of
+ * cq_peer_gather_stage_bytes() bytes (zero at set-up, 8-byte aligned) as mapped into THIS process (host array of `world`
+ * device pointers).  `dst`: this rank's result [rows, n_total]; rank p's slice lands in columns [p * n_local, +n_local).
+ * `state`: two 32-bit words of this rank's device memory, zero at set-up, shared by all gathers of the rank.  The kernel
+ * returns when all ranks' slices are in `dst`, or after about a second (then cq_peer_gather_timeout_flag() reports 1).
+ * All ranks must issue the same sequence of gathers, and one staging area must not serve two consecutive gathers. */
+#define CQ_MAX_PEERS 8
+size_t cq_peer_gather_stage_bytes(int rows, int n_local, int world);
+void cq_peer_gather_words(const void *src, int src_stride, void *const *peer_stage, void *dst, void *state, int rows,
+                          int n_local, int n_total, int rank, int world, void *stream);
+int cq_peer_gather_timeout_flag(void);
 /* Glue of the mixture-of-experts harness.
  *   cq_moe_route_f32           : softmax over `experts` (<= 1024) logits per token, the k (<= 32) largest probabilities in
  *                                descending order (lowest expert index among equals) as ids / weights [tokens, k]; with

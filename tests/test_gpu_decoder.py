@@ -228,6 +228,19 @@ def test_graph_decode_equals_eager_decode(cuda_dev):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_peer_gather_matches_library_all_gather(tmp_path):
+    """The one-kernel gather over NVLink peer memory against the NCCL all-gather, under torchrun with 2 ranks."""
+    out = tmp_path / "verdict.txt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(ROOT, "candle_b200", "tp_check.py"),
+           "--gather", "--out", str(out)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert out.read_text().strip() == "identical"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tensor_parallel_tokens_match_single_gpu(tmp_path):
     """Launches the consistency script under torchrun with 2 ranks; rank 0 compares with its own 1-GPU run."""
     out = tmp_path / "tp.txt"
