@@ -44,31 +44,46 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
     const unsigned epoch = *(volatile unsigned *)state + 1u;      // only the CTA that finishes last advances it
     const int64_t total = (int64_t)rows * n_local;
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = tid; i < total; i += nthr) {
+    // Work items are (peer offset q, word i), word fastest: consecutive threads touch consecutive slots, and the items of
+    // one thread belong to different peers or distant words, so that its loads are independent.
+    const int64_t items = total * world;
+    for (int64_t it = tid; it < items; it += nthr) {
+        const int q = (int)(it / total);
+        const int64_t i = it % total;
         const int j = (int)(i / n_local), c = (int)(i % n_local);
         const uint32_t v = src[(int64_t)j * src_stride + c];
-        for (int q = 1; q < world; ++q) {
-            const int p = (rank + q) % world;
-            st_slot((uint2 *)stage.p[p] + (int64_t)rank * total + i, v, epoch);
-        }
-        dst[(int64_t)j * n_total + (int64_t)rank * n_local + c] = v;
+        if (q == 0) dst[(int64_t)j * n_total + (int64_t)rank * n_local + c] = v;
+        else st_slot((uint2 *)stage.p[(rank + q) % world] + (int64_t)rank * total + i, v, epoch);
     }
     const uint2 *mine = (const uint2 *)stage.p[rank];
     bool gave_up = false;
-    for (int q = 1; q < world && !gave_up; ++q) {
-        const int p = (rank + world - q) % world;      // the rank whose first store went to this one comes first
-        for (int64_t i = tid; i < total; i += nthr) {
-            const uint2 *slot = mine + (int64_t)p * total + i;
-            uint2 v = ld_slot(slot);
-            if (v.y != epoch) {
+    constexpr int U = 4;        // slots in flight per thread
+    for (int64_t it0 = total + tid; it0 < items && !gave_up; it0 += U * nthr) {
+        uint2 v[U];
+        const uint2 *slot[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t it = it0 + u * nthr;
+            slot[u] = nullptr;
+            if (it < items) {
+                const int p = (rank + world - (int)(it / total)) % world;
+                slot[u] = mine + (int64_t)p * total + it % total;
+                v[u] = ld_slot(slot[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!slot[u] || gave_up) continue;
+            if (v[u].y != epoch) {
                 const long long t0 = clock64();
-                while ((v = ld_slot(slot)).y != epoch) {
+                while ((v[u] = ld_slot(slot[u])).y != epoch) {
                     if (clock64() - t0 > 2000000000LL) { gave_up = true; break; }
                 }
-                if (gave_up) break;
+                if (gave_up) continue;
             }
-            const int j = (int)(i / n_local), c = (int)(i % n_local);
-            dst[(int64_t)j * n_total + (int64_t)p * n_local + c] = v.x;
+            const int64_t it = it0 + u * nthr, i = it % total;
+            const int p = (rank + world - (int)(it / total)) % world;
+            dst[(i / n_local) * n_total + (int64_t)p * n_local + i % n_local] = v[u].x;
         }
     }
     if (gave_up) atomicExch(&g_peer_gather_timeout, 1);
@@ -100,8 +115,8 @@ extern "C" void cq_peer_gather_words(const void *src, int src_stride, void *cons
         s.p[p] = peer_stage[p];
     }
     const int64_t total = (int64_t)rows * n_local;
-    int grid = (int)((total + 1023) / 1024);       // four words per thread, at most 32 CTAs
-    if (grid > 32) grid = 32;
+    int grid = (int)((total * world + 255) / 256);  // one (peer, word) item per thread while that fits in 64 CTAs
+    if (grid > 64) grid = 64;
     if (grid < 1) grid = 1;
     cq_launch_k(peer_gather_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const uint32_t *)src, src_stride, s,
                 (uint32_t *)dst, (unsigned *)state, rows, n_local, n_total, rank, world);

@@ -64,10 +64,11 @@ class PeerGatherer(Gatherer):
     areas live in symmetric memory (`torch.distributed._symmetric_memory`: one CUDA virtual-memory allocation per rank,
     mapped by all); they are made on first use of a shape, which is a collective step, so shapes must first occur
     outside CUDA-graph capture and in the same order on all ranks.  Two areas per shape alternate when one shape is
-    gathered twice in a row.  Slices above `MAX_WORDS` 32-bit words (prompts) go through the library all-gather: the
-    slot protocol doubles the bytes on the link and is built for latency, not bandwidth."""
+    gathered twice in a row.  When a rank would send more than `MAX_SENT_WORDS` 32-bit words in total (prompts, the
+    vocabulary slice of a large batch on many ranks) the library all-gather is used: the slot protocol doubles the bytes
+    on the link and is built for latency, not bandwidth."""
 
-    MAX_WORDS = 1 << 17     # 512 KiB per rank
+    MAX_SENT_WORDS = 1 << 18     # slice words x (world - 1)
 
     def __init__(self, group=None, world: int | None = None):
         super().__init__(group, world)
@@ -99,7 +100,7 @@ class PeerGatherer(Gatherer):
             return local
         if local.dim() != 2:
             raise ValueError("peer gather takes a 2-d tensor")
-        if local.numel() * local.element_size() > 4 * self.MAX_WORDS:
+        if local.numel() * local.element_size() * (self.world - 1) > 4 * self.MAX_SENT_WORDS:
             self._last = None       # a library collective in between orders the accesses like any other gather
             return super().__call__(local)
         dtype = local.dtype
