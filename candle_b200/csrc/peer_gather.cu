@@ -24,6 +24,7 @@ namespace {
 struct PeerPtrs { void *p[CQ_MAX_PEERS]; };
 
 __device__ int g_peer_gather_timeout = 0;
+__device__ long long g_peer_gather_limit = 2000000000LL;     // SM clocks a poll may last: about a second
 
 __device__ __forceinline__ void st_slot(uint2 *p, uint32_t word, uint32_t epoch) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(epoch) : "memory");
@@ -57,6 +58,7 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
     }
     const uint2 *mine = (const uint2 *)stage.p[rank];
     bool gave_up = false;
+    const long long limit = g_peer_gather_limit;
     constexpr int U = 4;        // slots in flight per thread
     for (int64_t it0 = total + tid; it0 < items && !gave_up; it0 += U * nthr) {
         uint2 v[U];
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
             if (v[u].y != epoch) {
                 const long long t0 = clock64();
                 while ((v[u] = ld_slot(slot[u])).y != epoch) {
-                    if (clock64() - t0 > 2000000000LL) { gave_up = true; break; }
+                    if (clock64() - t0 > limit) { gave_up = true; break; }
                 }
                 if (gave_up) continue;
             }
@@ -121,6 +123,15 @@ extern "C" void cq_peer_gather_words(const void *src, int src_stride, void *cons
     cq_launch_k(peer_gather_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const uint32_t *)src, src_stride, s,
                 (uint32_t *)dst, (unsigned *)state, rows, n_local, n_total, rank, world);
     cq_check_launch("peer gather");
+}
+
+// How long a poll may last, in SM clocks (default 2e9, about a second); tests shorten it.
+extern "C" void cq_peer_gather_set_limit_clocks(long long clocks) {
+    if (clocks > 0) cudaMemcpyToSymbol(g_peer_gather_limit, &clocks, sizeof clocks);
+}
+extern "C" void cq_peer_gather_clear_timeout(void) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_peer_gather_timeout, &z, sizeof z);
 }
 
 // 1 if a peer gather on the current device gave up waiting for another rank's data (synchronises the device).

@@ -271,6 +271,8 @@ size_t cq_peer_gather_stage_bytes(int rows, int n_local, int world);
 void cq_peer_gather_words(const void *src, int src_stride, void *const *peer_stage, void *dst, void *state, int rows,
                           int n_local, int n_total, int rank, int world, void *stream);
 int cq_peer_gather_timeout_flag(void);
+void cq_peer_gather_clear_timeout(void);                /* after a reported give-up */
+void cq_peer_gather_set_limit_clocks(long long clocks); /* how long a poll may last (default 2e9 SM clocks) */
 /* Glue of the mixture-of-experts harness.
  *   cq_moe_route_f32           : softmax over `experts` (<= 1024) logits per token, the k (<= 32) largest probabilities in
  *                                descending order (lowest expert index among equals) as ids / weights [tokens, k]; with

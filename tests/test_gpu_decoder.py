@@ -250,3 +250,46 @@ def test_tensor_parallel_tokens_match_single_gpu(tmp_path):
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert out.read_text().strip() == "identical"
+
+
+@pytest.mark.gpu
+def test_peer_gather_gives_up_when_a_rank_never_arrives(lib, cuda_dev):
+    """Failure detection without a fault: a second "rank" whose staging area nobody fills.  The kernel's bounded poll
+    runs out (limit shortened to about 10 ms), the device flag is raised, the kernel returns and the context stays
+    usable; with the slots filled by hand the same call completes and delivers both slices."""
+    import ctypes
+    rows, n_local, world = 2, 64, 2
+    nbytes = lib.cq_peer_gather_stage_bytes(rows, n_local, world)
+    mine = torch.zeros(nbytes, dtype=torch.uint8, device=cuda_dev)          # rank 0's staging area
+    other = torch.zeros(nbytes, dtype=torch.uint8, device=cuda_dev)         # stands for rank 1's, on the same GPU
+    ptrs = (ctypes.c_void_p * capi.MAX_PEERS)(mine.data_ptr(), other.data_ptr())
+    state = torch.zeros(4, dtype=torch.int32, device=cuda_dev)
+    src = torch.arange(rows * n_local, dtype=torch.float32, device=cuda_dev).view(rows, n_local)
+    dst = torch.full((rows, world * n_local), -1.0, device=cuda_dev)
+    st = torch.cuda.current_stream().cuda_stream
+    lib.cq_peer_gather_clear_timeout()
+    lib.cq_peer_gather_set_limit_clocks(20_000_000)
+    try:
+        lib.cq_peer_gather_words(src.data_ptr(), n_local, ptrs, dst.data_ptr(), state.data_ptr(), rows, n_local, world * n_local, 0, world, st)
+        torch.cuda.synchronize()
+        assert lib.cq_peer_gather_timeout_flag() == 1
+        lib.cq_clear_status()
+        lib.cq_peer_gather_clear_timeout()
+        assert torch.equal(dst[:, :n_local], src)                           # the local slice was delivered
+        assert int(state[0].item()) == 1                                    # the gather still counts: epochs stay aligned
+        # what rank 0 sent sits in the other area, tagged with epoch 1
+        sent = other.view(torch.int32).view(world, rows * n_local, 2)[0]
+        assert torch.equal(sent[:, 0].view(torch.float32).view(rows, n_local), src) and bool((sent[:, 1] == 1).all())
+        # now play rank 1 by hand for epoch 2: fill rank 0's slots, then the same call completes
+        theirs = src + 1000.0
+        slots = mine.view(torch.int32).view(world, rows * n_local, 2)
+        slots[1, :, 0] = theirs.view(torch.int32).view(-1)
+        slots[1, :, 1] = 2
+        lib.cq_peer_gather_words(src.data_ptr(), n_local, ptrs, dst.data_ptr(), state.data_ptr(), rows, n_local, world * n_local, 0, world, st)
+        torch.cuda.synchronize()
+        assert lib.cq_peer_gather_timeout_flag() == 0
+        assert torch.equal(dst[:, n_local:], theirs) and torch.equal(dst[:, :n_local], src)
+    finally:
+        lib.cq_peer_gather_set_limit_clocks(2_000_000_000)
+        lib.cq_peer_gather_clear_timeout()
+        lib.cq_clear_status()
