@@ -32,7 +32,7 @@ void launch_mmvq_gguf_quantize_q8_1_f32(const void *x, void *vy, int kx, int kx_
 void launch_mmvq_gguf_quantize_q8_1_f16(const void *x, void *vy, int kx, int kx_padded, int num_rows, void *stream);
 void launch_mmvq_gguf_quantize_q8_1_bf16(const void *x, void *vy, int kx, int kx_padded, int num_rows, void *stream);
 
-/* Decode GEMV, batch 1..8.  Replaces candle-kernels/src/ffi.rs:61-393 for four formats
+/* Decode GEMV, batch 1..8.  Replaces candle-kernels/src/ffi.rs:61-393 for all ten formats
  * (launchers: candle-kernels/src/mmvq_gguf.cu:915-1008).  vx: weights [nrows_x, ncols_x] as GGUF blocks;
  * vy: Q8_1 blocks, row j at block j*stride_col_y; dst[j*stride_col_dst + row] in the type of the suffix. */
 #define CQ_DECL_MMVQ(name)                                                                                   \
@@ -87,7 +87,7 @@ void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int3
                            int size_m, int size_n, int size_k, int input_dtype, int gguf_dtype, int64_t stream);
 
 /* Prompt-phase pair.  Replaces candle-kernels/src/ffi.rs:424-468 (launch_mmq_quantize_q8_1_{D4,DS4,D2S6}) and, for
- * the four formats, :471-630 (launch_mmq_gguf_<type>); host caller candle-core/src/quantized/fast_mmq.rs:253-400.
+ * the ten formats, :471-630 (launch_mmq_gguf_<type>); host caller candle-core/src/quantized/fast_mmq.rs:253-400.
  * Quantize: x f32 (rows of ne00 values, row stride s01, channel strides s02 / s03, optional row gather `ids`) ->
  * block_q8_1_mmq groups of 144 bytes per 128 values, stored [channel][group][token], ne0 = padded width (a multiple
  * of 128), ne1 tokens.  The bytes are those of the reference kernel.  DS4 serves Q4_0 / Q4_K, D4 serves Q8_0 / Q6_K.
@@ -158,7 +158,7 @@ const char *cq_version(void);
  * generality in the reference; launch_mmvq_gguf_quantize_q8_1_* are the act = Q8_1 special cases. */
 void cq_quantize_act(const void *x, int x_elem, void *vy, int kx, int kx_padded, int num_rows, int act, void *stream);
 
-/* GEMV on any supported weight type / activation encoding / output element type; the twelve
+/* GEMV on any supported weight type / activation encoding / output element type; the thirty
  * launch_mmvq_gguf_*_plain symbols forward here with act = Q8_1. */
 void cq_mmvq(int wtype, int act, int out_elem, const void *vx, const void *vy, void *dst, int ncols_x, int nrows_x,
              int stride_col_y, int stride_col_dst, int b_size, void *stream);
@@ -350,7 +350,7 @@ int cqh_qmatmul_forward_q8_1_pair(void *handle_a, void *handle_b, const void *ac
 int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1, const uint32_t *ids, int batch, int topk, float *out,
                             void *stream);
 /* QTensor::dequantize / dequantize_f16 (candle-core/src/quantized/mod.rs:689-710) and QTensor::embedding (:712-748) for
- * the four formats: values of the CPU `to_float` bit for bit, as out_dtype (CQ_ELEM_*).  ids: device u32 [n_ids]; an id
+ * the ten formats: values of the CPU `to_float` bit for bit, as out_dtype (CQ_ELEM_*).  ids: device u32 [n_ids]; an id
  * outside the tensor gives a row of zeros and is reported by cq_get_rows_bad_id(). */
 int cqh_qtensor_dequantize(void *handle, void *out, int out_dtype, void *stream);
 int cqh_qtensor_embedding(void *handle, const uint32_t *ids, int64_t n_ids, void *out, int out_dtype, void *stream);
