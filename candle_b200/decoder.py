@@ -97,7 +97,9 @@ class LlamaShapedDecoder:
             mm = lambda dtype, k, parts: _sharded_matmul(dtype, k, parts, rank, world, self.device)
             L.wqk = mm(GgmlDType.Q4K, d, [(cfg.n_heads * hd, s + 1), (cfg.n_kv_heads * hd, s + 2)])    # [q heads | k heads]
             L.wv = mm(GgmlDType.Q6K, d, [(cfg.n_kv_heads * hd, s + 3)])
-            L.wo = mm(GgmlDType.Q4K, cfg.n_heads * hd, [(d, s + 4)])
+            # wo is small (9 MB at the Llama-3-8B shape): every rank keeps all of it and computes the whole projection
+            # from the gathered attention output - cheaper than a slice plus a second exchange, and the same bits
+            L.wo = _sharded_matmul(GgmlDType.Q4K, cfg.n_heads * hd, [(d, s + 4)], 0, 1, self.device)
             L.gate_up = mm(GgmlDType.Q4K, d, [(cfg.ffn, s + 5), (cfg.ffn, s + 6)])                     # [gate | up]
             L.down = mm(GgmlDType.Q6K, cfg.ffn, [(d, s + 7)])
             L.k_cache = torch.zeros((batch, self.hkv_l, cfg.max_pos, hd), device=self.device)
@@ -192,7 +194,7 @@ class LlamaShapedDecoder:
                 if fused:
                     att = torch.empty((R, q_cols // 32 * 36), **u8)
                     self._attention(qk, L, B, T, att, True)
-                    delta = self.gather(L.wo.forward_q8_1(self.gather(att)))
+                    delta = L.wo.forward_q8_1(self.gather(att))
                     h = self._norm_q8(x, delta, L.ffn_norm)
                     gu = L.gate_up.forward_q8_1(h)                                      # [R, 2 * f_l]
                     a = torch.empty((R, f_l // 32 * 36), **u8)
@@ -201,7 +203,7 @@ class LlamaShapedDecoder:
                 else:
                     att = torch.empty((R, q_cols), **f32)
                     self._attention(qk, L, B, T, att, False)
-                    delta = self.gather(L.wo.forward(self.gather(att)))
+                    delta = L.wo.forward(self.gather(att))
                     h = self._norm(x, delta, L.ffn_norm)
                     gu = L.gate_up.forward(h)
                     a = torch.empty((R, f_l), **f32)
