@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import sys
 
 import torch
 import torch.distributed as dist
@@ -139,7 +140,19 @@ def make_gatherer(group=None, world: int | None = None, device=None) -> Gatherer
     w = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
     on_cuda = device is not None and torch.device(device).type == "cuda"
     if w > 1 and on_cuda and os.environ.get("CQ_PEER_GATHER", "1") != "0":
-        return PeerGatherer(group, w)
+        ok = 1
+        try:
+            pg = PeerGatherer(group, w)
+            pg(torch.zeros((1, 8), device=device))      # first staging area: the step that needs peer mappings to work
+            pg.check()
+        except Exception as e:      # no peer access between these GPUs, or an older torch: every rank must learn of it
+            ok = 0
+            print(f"candle_b200: peer-memory gather unavailable ({type(e).__name__}: {e}); using the library all-gather",
+                  file=sys.stderr)
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 1:
+            return pg
     return Gatherer(group, w)
 
 
