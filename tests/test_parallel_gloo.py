@@ -39,6 +39,8 @@ def _worker(rank, world, port, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         g = Gatherer()
+        from candle_b200.parallel import make_gatherer
+        assert type(make_gatherer(None, world, torch.device("cpu"))) is Gatherer      # the peer-memory kernel is for CUDA only
         full = torch.arange(3 * 8, dtype=torch.float32).view(3, 8) * 1.5
         s, c = shard_rows(8, world, rank)
         out = g(full[:, s:s + c].contiguous())
