@@ -488,7 +488,10 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
     if (warp >= kEpiWarps && warp < kEpiWarps + kProdWarps) {
         // ===== producers =====
         const int p = tid - kEpiWarps * 32;
-        const int r = p & 63, h = (p >> 6) & 1, jh = p >> 7;
+        // lane = (row % 8) + 8 h + 16 jh: the four threads of a row sit in one warp, so a warp's loads cover 8 rows x 64
+        // contiguous bytes (and 8 headers) instead of 32 rows x 16 bytes; eight consecutive lanes still store eight
+        // consecutive 16-byte rows of one slab (no bank conflicts)
+        const int r = ((p >> 5) << 3) | (p & 7), h = (p >> 3) & 1, jh = (p >> 4) & 1;
         // the halves of the sums operand that stay zero: rows 64.. of slab 16 and rows ..63 of slab 17, every stage
         for (int i = p; i < kStagesB * 2 * 64; i += kProdWarps * 32) {
             const int st = i >> 7, which = (i >> 6) & 1, row = i & 63;
