@@ -393,7 +393,8 @@ def run_case(args):
 
 
 def run_prefill_case(args):
-    """One prefill GEMM case: --prefill-case M:K:N (Q4_K), a few launches with CUDA-event times (profiling helper)."""
+    """One prefill GEMM case: --prefill-case M:K:N (--prefill-type Q4K | Q6K), a few launches with CUDA-event times
+    (profiling helper)."""
     import torch
     from candle_b200 import capi
     from candle_b200.quantized import GgmlDType
@@ -401,7 +402,8 @@ def run_prefill_case(args):
     m, k, n = (int(v) for v in args.prefill_case.split(":"))
     dev = torch.device("cuda:0")
     L = capi.lib()
-    w = random_blocks(GgmlDType.Q4K, n, k, seed=1, device=dev)
+    wt = GgmlDType[args.prefill_type]
+    w = random_blocks(wt, n, k, seed=1, device=dev)
     x = torch.randn((m, k), device=dev)
     scratch = torch.empty(L.cq_prefill_scratch_bytes(m, k), dtype=torch.uint8, device=dev)
     out = torch.empty((m, n), device=dev)
@@ -411,13 +413,13 @@ def run_prefill_case(args):
     for _ in range(args.iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        L.cq_prefill_gemm(int(GgmlDType.Q4K), w.data_ptr(), scratch.data_ptr(), out.data_ptr(), capi.F32, k, n, m, n, s)
+        L.cq_prefill_gemm(int(wt), w.data_ptr(), scratch.data_ptr(), out.data_ptr(), capi.F32, k, n, m, n, s)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
     capi.check("prefill case")
     best = min(times[1:]) if len(times) > 1 else times[0]
-    print(json.dumps({"prefill_case": args.prefill_case, "ms": times, "useful_TOPS": 2.0 * m * n * k / best / 1e9}))
+    print(json.dumps({"prefill_case": args.prefill_case, "type": args.prefill_type, "ms": times, "useful_TOPS": 2.0 * m * n * k / best / 1e9}))
 
 
 def moe_decode_tok_s(dev, rank, world, batch, prompt_len=1024, steps=256, use_graph=True):
@@ -534,6 +536,7 @@ def main():
     ap.add_argument("--dequant-case", default=None, help="profile helper: TYPE:N:K, de-quantizes one tensor to f32")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
+    ap.add_argument("--prefill-type", default="Q4K", choices=["Q4K", "Q6K"], help="weight format of --prefill-case")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--gpus", type=int, default=1)
