@@ -48,6 +48,7 @@ constexpr int kTokBytes = 16 * kSlabsA + 4;            // scratch bytes per (tok
 constexpr int kAccCols = 2 * kN;                       // accumulator columns per buffer: products, then sums
 constexpr int kStagesA = 3, kStagesB = 3;
 constexpr int kEpiWarps = 8, kProdWarps = 8;
+constexpr bool kEpiPrefetch = false;    // epilogue: fetch the next accumulator chunk while this one is computed
 constexpr int kThreads = (kEpiWarps + kProdWarps + 2) * 32;
 constexpr int kSmemBytes = 1024 + kStagesA * kStageA + kStagesB * kStageB + 2 * 8 * 512;
 
@@ -624,7 +625,7 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
 #pragma unroll
                 for (int ch = 0; ch < kMyRows / 8; ++ch) {
                     tmem_ld_wait();
-                    if (ch + 1 < kMyRows / 8) {
+                    if (kEpiPrefetch && ch + 1 < kMyRows / 8) {
                         tmem_ld8(taddr + (ch + 1) * 8, v1[(ch + 1) & 1]);
                         tmem_ld8(taddr + kRowTile + (ch + 1) * 8, v2[(ch + 1) & 1]);
                         tmem_ld8(taddr + 2 * kRowTile + (ch + 1) * 8, vl[(ch + 1) & 1]);
@@ -647,6 +648,12 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
                             }
                             acc[ch * 8 + i + e] = __fmaf_rn(da, tv, acc[ch * 8 + i + e]);
                         }
+                    }
+                    if (!kEpiPrefetch && ch + 1 < kMyRows / 8) {
+                        tmem_ld8(taddr + (ch + 1) * 8, v1[(ch + 1) & 1]);
+                        tmem_ld8(taddr + kRowTile + (ch + 1) * 8, v2[(ch + 1) & 1]);
+                        tmem_ld8(taddr + 2 * kRowTile + (ch + 1) * 8, vl[(ch + 1) & 1]);
+                        tmem_ld8(taddr + 3 * kRowTile + (ch + 1) * 8, vh[(ch + 1) & 1]);
                     }
                 }
                 tc_fence_before();
