@@ -14,7 +14,16 @@ f32 outputs, per GEMV) / device time of the step.
   e2e       : the same step through the public API (QMatMul.forward) with activations starting in pinned host
               memory and results copied back to pinned host memory inside the timed region.
   roofline  : the GEMV kernels alone (no quantize launches), CUDA-event timed in this run.
-  cpu_baseline : the reference's CPU algorithm (oracle port, AVX2, all host cores) on a bounded sample.
+  cpu_baseline : the reference's CPU algorithm (oracle port, AVX2, host threads = physical cores) on the same sweep.
+Further objects of the same JSON line (reported beside the headline, not part of `value`):
+  sustained   : the same graph replayed for at least a second.
+  gemv_cases  : GB/s of every (format, shape, batch) GEMV launch on its own (L2 flushed before each launch).
+  int8_peak   : an int8 library GEMM 8192^3 measured in this process: the denominator of the prompt kernel's fraction.
+  prefill     : prompt-phase GEMM, Q4_K 4096->14336 and 14336->4096, M = 128 .. 8192 tokens, f32 and bf16 inputs: useful
+                TOP/s of the tcgen05 kernel, of the whole forward (quantize + GEMM), and of the reference's own two-call
+                protocol (launch_mmq_quantize_q8_1_DS4 + launch_mmq_gguf_q4_k) served by this library.
+  moe         : Qwen3-30B-A3B-shaped mixture-of-experts decoder (tokens/s) and the grouped expert GEMM (TOP/s).
+  decode      : Llama-3-8B-shaped Q4_K_M decoder, tokens/s at batch 1 and 8.
 
 With N > 1 GPUs (torchrun) every weight matrix is sharded by output rows over the ranks (column-parallel);
 each rank runs its slice and the slices are all-gathered by one kernel over NVLink peer memory (csrc/peer_gather.cu).
@@ -113,9 +122,36 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------
 # reference arm: the reference's CPU algorithm (oracle port) on the host cores
 # --------------------------------------------------------------------------------------------------
+def host_cpu_info():
+    """(model name, physical cores, logical cores) of the host, from /proc/cpuinfo."""
+    model, phys, logical = "unknown", set(), 0
+    try:
+        pid = cid = None
+        for ln in open("/proc/cpuinfo"):
+            if ln.startswith("model name") and model == "unknown":
+                model = ln.split(":", 1)[1].strip()
+            elif ln.startswith("processor"):
+                logical += 1
+            elif ln.startswith("physical id"):
+                pid = ln.split(":", 1)[1].strip()
+            elif ln.startswith("core id"):
+                cid = ln.split(":", 1)[1].strip()
+                phys.add((pid, cid))
+    except OSError:
+        pass
+    logical = logical or (os.cpu_count() or 1)
+    return model, (len(phys) or logical), logical
+
+
+def cpu_threads():
+    """Threads of the CPU legs: the physical cores, the reference's default (candle-core/src/utils.rs:312-325)."""
+    return max(1, host_cpu_info()[1])
+
+
 def cpu_sample_setup(seed=0):
-    """Bounded sample of the workload for the CPU legs: batch 1 over the fifteen matrices, except that the
-    128256-row head is cut to its first 16032 rows (1/8) so one pass stays within seconds on a few cores."""
+    """The CPU legs run the benchmark's own sweep: the fifteen full matrices (the 128256-row head included) at batch
+    1, 2, 4 and 8 - the same config as the GPU arm.  Block bytes are random with plausible f16 scales (throughput does
+    not depend on the values)."""
     import numpy as np
     from oracle import oracle as O
     rng = np.random.default_rng(seed)
@@ -123,51 +159,193 @@ def cpu_sample_setup(seed=0):
     for t in TYPE_NAMES:
         dt = getattr(O, t)
         for (k, n) in SHAPES:
-            n_s = n // 8 if n > 100000 else n
             rb = O.row_bytes(dt, k)
-            w = rng.integers(0, 256, size=(n_s, rb), dtype=np.uint8)
-            # plausible f16 scales so the arithmetic stays finite
-            blk = w.reshape(n_s * (k // O.BLOCK_SIZE[dt]), O.TYPE_SIZE[dt])
+            w = rng.integers(0, 256, size=(n, rb), dtype=np.uint8)
+            blk = w.reshape(n * (k // O.BLOCK_SIZE[dt]), O.TYPE_SIZE[dt])
             for off in ({O.Q4K: (0, 2), O.Q6K: (208,), O.Q8_0: (0,)}[dt]):
                 blk[:, off:off + 2] = np.full((blk.shape[0],), 1e-3, dtype=np.float16).view(np.uint8).reshape(-1, 2)
-            x = rng.standard_normal((1, k)).astype(np.float32)
-            items.append((t, dt, k, n_s, w, x))
-    nbytes = sum(gemv_bytes(t, k, n_s, 1) for (t, _, k, n_s, _, _) in items)
+            xs = {b: rng.standard_normal((b, k)).astype(np.float32) for b in BATCHES}
+            items.append((t, dt, k, n, w, xs))
+    nbytes = sum(gemv_bytes(t, k, n, b) for (t, _, k, n, _, _) in items for b in BATCHES)
     return items, nbytes
 
 
-def cpu_sample_run(items):
+def cpu_sample_run(items, nthreads):
     from oracle import oracle as O
-    for (_, dt, k, n_s, w, x) in items:
-        O.matmul(dt, x, w, n_s, mode=O.SIMD_HW if O.lib().cqo_have_avx2() else O.SIMD_ORDER, nthreads=0)
+    mode = O.SIMD_HW if O.lib().cqo_have_avx2() else O.SIMD_ORDER
+    for b in BATCHES:
+        for (_, dt, k, n, w, xs) in items:
+            O.matmul(dt, xs[b], w, n, mode=mode, nthreads=nthreads)
 
 
-SAMPLE_DESC = ("batch 1 over the 15 (type, shape) matrices of the sweep, head matrix cut to 16032 of 128256 rows; "
-               "k_quants::matmul restated in C with AVX2 dots, all host cores")
+SAMPLE_DESC = ("one full pass of the sweep: the 15 (type, shape) matrices at batch 1, 2, 4 and 8, full sizes; "
+               "k_quants::matmul restated in C with AVX2 dots, one thread per physical core")
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle as O
     items, nbytes = cpu_sample_setup()
-    for _ in range(max(1, min(args.warmup, 2))):
-        cpu_sample_run(items)
+    nthreads = cpu_threads()
+    model, phys, logical = host_cpu_info()
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_sample_run(items, nthreads)
+    steps = max(1, min(args.steps, 8))      # a pass takes about a second of CPU time: bound the run to a few minutes
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_sample_run(items)
-    dt = (time.perf_counter() - t0) / args.steps
+    for _ in range(steps):
+        cpu_sample_run(items, nthreads)
+    dt = (time.perf_counter() - t0) / steps
     val = nbytes / dt / 1e9
-    cores = O.num_cores()
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 dot products, f32 accumulation", "data": "synthetic",
         "config": {"workload": "gemv_sweep_llama3_8b", "types": TYPE_NAMES, "shapes_k_n": SHAPES, "batches": BATCHES},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": SAMPLE_DESC},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": nthreads, "kind": "port", "sample": SAMPLE_DESC,
+                         "cpu_model": model, "physical_cores": phys, "logical_cores": logical},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def token_hash(toks) -> str:
+    """SHA-256 of the generated token ids (order-sensitive, unlike a sum)."""
+    import hashlib
+    import torch
+    return hashlib.sha256(torch.stack(toks).to(torch.int64).cpu().numpy().tobytes()).hexdigest()[:16]
+
+
+def measure_int8_peak(dev):
+    """int8 x int8 -> int32 library GEMM 8192^3 (torch._int_mm, cuBLASLt) in this process: best of 10 launches and the
+    mean of a 2 s back-to-back loop.  It is the denominator of the prompt kernel's fraction; 4500 TOP/s is the nominal
+    dense int8 figure of the part."""
+    import torch
+    n = 8192
+    try:
+        a = torch.randint(-127, 127, (n, n), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 127, (n, n), dtype=torch.int8, device=dev).t()      # column-major right operand
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch._int_mm(a, b); e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(2000.0 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        sus = e0.elapsed_time(e1) / reps
+        ops = 2.0 * n * n * n
+        return {"burst_tops": ops / best / 1e9, "sustained_tops": ops / sus / 1e9, "nominal_tops": 4500.0,
+                "how": "torch._int_mm int8 8192^3 (library GEMM): best of 10 launches; mean of a 2 s back-to-back loop"}
+    except Exception as e:      # no int8 library GEMM in this build
+        return {"burst_tops": None, "sustained_tops": None, "nominal_tops": 4500.0, "how": f"torch._int_mm unavailable: {e}"}
+
+
+def _time_launches(fn, iters):
+    """Mean CUDA-event time in ms of `iters` back-to-back calls of fn(i) after two warm-up calls."""
+    import torch
+    fn(0); fn(1)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def measure_prefill(dev, rank, world, peak_tops):
+    """BASELINE config 3: Q4_K 4096->14336 and 14336->4096, M = 128, 512, 2048, 8192 tokens, f32 and bf16 activations;
+    the output dimension is sharded over `world` ranks.  Per case the useful rate 2*M*N*K / t of (a) the tcgen05 GEMM
+    alone, (b) QMatMul.forward (activation tiles + GEMM), (c) for f32: the reference's two-call protocol served by this
+    library (launch_mmq_quantize_q8_1_DS4 + launch_mmq_gguf_q4_k).  Weights rotate through four copies so that
+    consecutive launches do not find them in L2."""
+    import torch
+    import torch.distributed as dist
+    from candle_b200 import capi
+    from candle_b200.quantized import GgmlDType, QMatMul, QTensor
+    from candle_b200.synth import random_blocks
+    L = capi.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    out = []
+    for (k, n) in ((4096, 14336), (14336, 4096)):
+        n_l = n // world
+        ws = [random_blocks(GgmlDType.Q4K, n_l, k, seed=7 + 10 * i + rank, device=dev) for i in range(4)]
+        mms = [QMatMul.from_qtensor(QTensor.from_device_blocks(w, GgmlDType.Q4K, (n_l, k))) for w in ws]
+        for m in (128, 512, 2048, 8192):
+            ops = 2.0 * m * n * k          # whole job, all ranks
+            iters = 20 if m <= 2048 else 8
+            for tdt, ename, ecode in ((torch.float32, "f32", capi.F32), (torch.bfloat16, "bf16", capi.BF16)):
+                x = torch.randn((m, k), device=dev, generator=torch.Generator(device=dev).manual_seed(m + k)).to(tdt)
+                y = torch.empty((m, n_l), dtype=tdt, device=dev)
+                scratch = torch.empty(L.cq_prefill_scratch_bytes(m, k), dtype=torch.uint8, device=dev)
+                L.cq_prefill_quantize(x.data_ptr(), ecode, scratch.data_ptr(), k, m, st)
+                t_gemm = _time_launches(lambda i: L.cq_prefill_gemm(12, ws[i % 4].data_ptr(), scratch.data_ptr(), y.data_ptr(), ecode,
+                                                                     k, n_l, m, n_l, st), iters)
+                t_fwd = _time_launches(lambda i: mms[i % 4].forward(x, out=y), iters)
+                row = {"k": k, "n": n, "m": m, "in": ename, "gemm_ms": t_gemm, "forward_ms": t_fwd}
+                if ename == "f32":      # the drop-in route: the reference's own scratch and entry points
+                    kp = capi.pad(k, 512)
+                    mmq_scratch = torch.empty(((kp // 128) * m + 128) * 144, dtype=torch.uint8, device=dev)
+                    fixup = torch.empty(4 << 20, dtype=torch.float32, device=dev)
+                    y32 = torch.empty((m, n_l), dtype=torch.float32, device=dev)
+
+                    def dropin(i):
+                        L.launch_mmq_quantize_q8_1_DS4(x.data_ptr(), None, mmq_scratch.data_ptr(), 0, k, k, 0, 0, kp, m, 1, 1, st)
+                        L.launch_mmq_gguf_q4_k(fixup.data_ptr(), ws[i % 4].data_ptr(), mmq_scratch.data_ptr(), y32.data_ptr(), k, n_l, m,
+                                               k // 256, n_l, 1000, 148, 232448, 32, st)
+                    row["dropin_mmq_ms"] = _time_launches(dropin, 3 if m >= 2048 else 6)
+                    del mmq_scratch, fixup, y32
+                capi.check("prefill bench")
+                t = torch.tensor([row["gemm_ms"], row["forward_ms"], row.get("dropin_mmq_ms", 0.0)], device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                row["gemm_ms"], row["forward_ms"] = float(t[0]), float(t[1])
+                row["gemm_tops"] = ops / row["gemm_ms"] / 1e9
+                row["forward_tops"] = ops / row["forward_ms"] / 1e9
+                if "dropin_mmq_ms" in row:
+                    row["dropin_mmq_ms"] = float(t[2])
+                    row["dropin_mmq_tops"] = ops / row["dropin_mmq_ms"] / 1e9
+                if peak_tops:
+                    row["gemm_frac_of_int8_peak"] = row["gemm_tops"] / (peak_tops * world)
+                out.append(row)
+                del x, y, scratch
+        del ws, mms
+        torch.cuda.empty_cache()
+    assert L.cq_prefill_timeout_flag() == 0, "a prefill launch gave up a bounded wait"
+    return out
+
+
+def measure_moe_gemm(dev):
+    """The grouped expert GEMM at the Qwen3-30B-A3B shape: 1024 tokens x top-8 = 8192 (token, expert) pairs over 128
+    Q4_K experts, gate|up (2048 -> 1536) and down (768 -> 2048); useful TOP/s = 2 * pairs * n * k / t."""
+    import torch
+    from candle_b200.moe import moe_prefill_gemm
+    from candle_b200.quantized import GgmlDType, QTensor
+    from candle_b200.synth import random_blocks
+    tokens, topk, experts = 1024, 8, 128
+    g = torch.Generator(device=dev).manual_seed(11)
+    ids = torch.stack([torch.randperm(experts, device=dev, generator=g)[:topk] for _ in range(tokens)]).to(torch.int32)
+    expert_ids, pairs = torch.sort(ids.reshape(-1), stable=True)
+    res = []
+    for name, n, k, per_pair in (("gate_up", 1536, 2048, False), ("down", 2048, 768, True)):
+        w = QTensor.from_device_blocks(random_blocks(GgmlDType.Q4K, experts * n, k, seed=5, device=dev).reshape(-1), GgmlDType.Q4K,
+                                       (experts, n, k))
+        x = torch.randn((tokens * topk if per_pair else tokens, k), device=dev, generator=g)
+        tw = torch.ones(tokens * topk, device=dev) if per_pair else None
+        ms = _time_launches(lambda i: moe_prefill_gemm(x, w, tw, pairs, expert_ids, topk), 10)
+        res.append({"matmul": name, "pairs": tokens * topk, "n": n, "k": k, "ms": ms, "useful_tops": 2.0 * tokens * topk * n * k / ms / 1e9})
+        del w, x
+    torch.cuda.empty_cache()
+    return res
 
 
 # --------------------------------------------------------------------------------------------------
@@ -274,8 +452,33 @@ def run_gpu(args):
     if rank == 0:
         sampler.start()
     ms_step = timed(step_full, args.steps, args.warmup, use_graph)
+    # the same step for at least a second (the K-step region above lasts tens of milliseconds): clocks are sampled here too
+    sus_steps = max(args.steps, int(1100.0 / max(ms_step, 1e-3)) + 1)
+    ms_sustained = timed(step_full, sus_steps, 1, use_graph)
     clocks = sampler.stop() if rank == 0 else None
     ms_gemv = timed(step_gemv_only, args.steps, args.warmup, use_graph)
+    ms_gemv_sustained = timed(step_gemv_only, sus_steps, 1, use_graph)
+    if gather is not None and hasattr(gather, "check"):
+        gather.check()          # a gather that gave up its bounded wait would have timed garbage
+
+    # ---- every GEMV launch on its own: L2 flushed (a 256 MB write) before each launch, events around the launch
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    per_case = {}
+    s_ = torch.cuda.current_stream().cuda_stream
+    for (b, t, k, n) in order:
+        best = float("inf")
+        for _ in range(5):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            L.cq_mmvq(int(GgmlDType[t]), capi.ACT_Q8_1, capi.F32, mats[(t, k, n)].qtensor.device_ptr(), q8[(k, b)].data_ptr(),
+                      outs[(n, b)].data_ptr(), k, n // world, kp[k] // 32, n // world, b, s_)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        per_case.setdefault(t, {}).setdefault(f"{k}x{n}", {})[str(b)] = round(gemv_bytes(t, k, n // world, b) / best / 1e6, 1)
+    del flush
+    capi.check("per-case sweep")
 
     # ---- e2e: host activations -> device, QMatMul.forward, result -> host, all inside the timed region
     h_x = {key: x.cpu().pin_memory() for key, x in xs.items()}
@@ -295,14 +498,27 @@ def run_gpu(args):
                 h_y[(n, b)].copy_(y, non_blocking=True)
 
     ms_e2e = timed(step_e2e, args.steps, args.warmup, False)
+    if gather is not None and hasattr(gather, "check"):
+        gather.check()
 
-    # free the sweep's buffers before building the decoder
+    # free the sweep's buffers before the other measurements
     del mats, xs, outs, q8, h_x, h_y, d_x
     gather = None
     torch.cuda.empty_cache()
+    int8_peak = measure_int8_peak(dev) if not args.no_prefill else None
+    prefill = None
+    if not args.no_prefill:
+        prefill = measure_prefill(dev, rank, world, int8_peak["burst_tops"] if int8_peak else None)
     decode = None
     if not args.no_decode:
         decode = [decode_tok_s(dev, rank, world, b) for b in (1, 8)]
+    moe = None
+    if not args.no_moe:
+        moe = {"model": "Qwen3-30B-A3B-shaped, experts Q4_K, attention and head Q6_K, random weights", "prompt": 1024, "steps": 128,
+               "parallelism": f"expert parallel x{world}" if world > 1 else "single GPU",
+               "runs": [moe_decode_tok_s(dev, rank, world, b, 1024, 128) for b in (1, 8)]}
+        if world == 1:
+            moe["grouped_gemm"] = measure_moe_gemm(dev)
 
     if rank != 0:
         if world > 1:
@@ -323,6 +539,13 @@ def run_gpu(args):
                    "launch": "CUDA graph replay" if graphed and graphed[0] else "eager launches"},
         "frac_of_8TBps_nominal_per_gpu": value / world / 8000.0,
         "gpu_launches": 2 * len(order) * args.steps,
+        "sustained": {"value": total_bytes / ms_sustained / 1e6, "unit": UNIT, "steps": sus_steps, "ms_per_step": ms_sustained,
+                      "gemv_only_GBps": total_bytes / ms_gemv_sustained / 1e6},
+        "gemv_cases": {"unit": "GB/s per launch (algorithmic bytes, this rank's shard), L2 flushed before each launch, best of 5",
+                       "by_type_shape_batch": per_case},
+        "int8_peak": int8_peak,
+        "prefill": prefill,
+        "moe": moe,
         "e2e": {"value": total_bytes / ms_e2e / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
         "roofline": {"bound": "hbm", "achieved": gemv_gbs / world, "peak": peak, "unit": "GB/s",
@@ -338,17 +561,19 @@ def run_gpu(args):
                    "parallelism": f"row-sharded projections x{world}, all-gather", "runs": decode},
     }
     if world == 1:
-        from oracle import oracle as O
         items, nbytes = cpu_sample_setup()
-        cpu_sample_run(items)
+        nthreads = cpu_threads()
+        model, phys, logical = host_cpu_info()
+        cpu_sample_run(items, nthreads)
         t0 = time.perf_counter()
         reps = 0
-        while reps < 3 or (time.perf_counter() - t0 < 10 and reps < 50):
-            cpu_sample_run(items)
+        while reps < 2 or (time.perf_counter() - t0 < 10 and reps < 20):
+            cpu_sample_run(items, nthreads)
             reps += 1
         dt = (time.perf_counter() - t0) / reps
-        result["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": O.num_cores(), "kind": "port",
-                                  "sample": SAMPLE_DESC + f"; {reps} passes"}
+        result["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": nthreads, "kind": "port",
+                                  "sample": SAMPLE_DESC + f"; {reps} passes", "cpu_model": model, "physical_cores": phys,
+                                  "logical_cores": logical}
     print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
@@ -452,11 +677,12 @@ def moe_decode_tok_s(dev, rank, world, batch, prompt_len=1024, steps=256, use_gr
         t = torch.tensor([t_prompt, t_dec], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_prompt, t_dec = float(t[0]), float(t[1])
-    checksum = int(torch.stack(toks).sum().item())
+    m.check()
+    checksum = token_hash(toks)
     del m
     torch.cuda.empty_cache()
     return {"batch": batch, "decode_tok_s": batch * (steps - 1) / t_dec * 1e3, "ms_per_step": t_dec / (steps - 1),
-            "prompt_tok_s": batch * prompt_len / t_prompt * 1e3, "cuda_graph": bool(graphed), "token_checksum": checksum,
+            "prompt_tok_s": batch * prompt_len / t_prompt * 1e3, "cuda_graph": bool(graphed), "token_hash": checksum,
             "active_weight_bytes_per_token": cfg.active_weight_bytes_per_token(), "experts_per_rank": cfg.experts // world}
 
 
@@ -515,11 +741,12 @@ def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=T
         t = torch.tensor([t_prompt, t_dec], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_prompt, t_dec = float(t[0]), float(t[1])
-    checksum = int(torch.stack(toks).sum().item())
+    m.check()
+    checksum = token_hash(toks)
     del m
     torch.cuda.empty_cache()
     return {"batch": batch, "decode_tok_s": batch * (steps - 1) / t_dec * 1e3, "ms_per_step": t_dec / (steps - 1),
-            "prompt_tok_s": batch * prompt_len / t_prompt * 1e3, "cuda_graph": bool(graphed), "token_checksum": checksum,
+            "prompt_tok_s": batch * prompt_len / t_prompt * 1e3, "cuda_graph": bool(graphed), "token_hash": checksum,
             "weight_bytes_per_token": cfg.weight_bytes_per_token(),
             "weight_stream_GBps": cfg.weight_bytes_per_token() / (t_dec / (steps - 1)) / 1e6}
 
@@ -535,6 +762,8 @@ def main():
                     "(under torchrun: expert parallel)")
     ap.add_argument("--dequant-case", default=None, help="profile helper: TYPE:N:K, de-quantizes one tensor to f32")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode measurement")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the int8 peak and prompt-phase GEMM measurements")
+    ap.add_argument("--no-moe", action="store_true", help="skip the mixture-of-experts measurements")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--prefill-type", default="Q4K", choices=["Q4K", "Q6K"], help="weight format of --prefill-case")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
@@ -547,10 +776,14 @@ def main():
     if args.decode_case:
         import torch
         b_, p_, s_ = (int(v) for v in args.decode_case.split(":"))
-        if args.tune:
+        if args.tune:       # needs a library built with -DCQ_EXPERIMENT
+            import ctypes
             from candle_b200 import capi
             rb_, cps_ = (int(v) for v in args.tune.split(":"))
-            capi.lib().cq_set_tuning(rb_, cps_)
+            fn = getattr(capi.lib(), "cq_set_tuning", None)
+            if fn is None:
+                raise SystemExit("--tune needs an experiment build of the library (nvcc -DCQ_EXPERIMENT)")
+            fn(ctypes.c_int(rb_), ctypes.c_int(cps_))
         torch.cuda.set_device(0)
         print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
     elif args.prefill_case:

@@ -48,14 +48,14 @@ def lib() -> C.CDLL:
         L.cq_quantize_act.argtypes = [vp, i32, vp, i32, i32, i32, i32, vp]
         L.cq_mmvq.argtypes = [i32, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_block_dots.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32, vp]
-        L.cq_set_tuning.argtypes = [i32, i32]
+        L.cq_mmvq_plan.argtypes = [i32, i32, i32, i32, i32, C.POINTER(i32)]
+        L.cq_mmvq_plan.restype = i32
         L.cq_device_timeout_flag.restype = i32
         L.cq_prefill_scratch_bytes.argtypes = [i32, i32]
         L.cq_prefill_scratch_bytes.restype = C.c_size_t
         L.cq_prefill_quantize.argtypes = [vp, i32, vp, i32, i32, vp]
         L.cq_prefill_gemm.argtypes = [i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_prefill_timeout_flag.restype = i32
-        L.cq_prefill_set_debug.argtypes = [i32]
         i64 = C.c_int64
         L.moe_gemm_gguf.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64]
         L.moe_gemm_gguf_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64]
@@ -84,6 +84,7 @@ def lib() -> C.CDLL:
         L.cq_silu_mul_q8_1.argtypes = [vp, vp, i32, i32, i32, vp]
         L.cq_attention_q8_1.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]
         L.cq_set_pdl.argtypes = [i32]
+        L.cq_glue_position_overflow_flag.restype = i32
         L.cq_moe_route_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
         L.cq_qknorm_rope_store_kv_f32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32,
                                                   C.c_float, i32, vp]
@@ -112,6 +113,7 @@ def lib() -> C.CDLL:
         L.cq_dequantize.argtypes = [i32, vp, vp, i32, i64, i64, vp]
         L.cq_get_rows.argtypes = [i32, vp, vp, vp, i32, i64, i64, i64, vp]
         L.cq_get_rows_bad_id.restype = i32
+        L.cq_convert_plain.argtypes = [i32, vp, vp, i32, i64, vp]
         L.cqh_qmatmul_forward_q8_1.argtypes = [vp, vp, i32, vp, vp]
         L.cqh_qmatmul_forward_q8_1_pair.argtypes = [vp, vp, vp, i32, vp, vp, vp]
         L.cq_mmvq_pair_q4k_q6k.argtypes = [vp, i32, vp, vp, i32, vp, vp, i32, i32, vp]

@@ -63,6 +63,8 @@ __host__ __device__ constexpr int cq_block_elems(int t) {
 // ---- status side channel (defined in status.cu) ----
 void cq_set_status(int status, const char *msg);
 bool cq_check_launch(const char *what);
+// Failures recorded so far by any thread (monotonic): lets a two-launch entry point see that its first step failed.
+unsigned cq_failure_count();
 
 // ---- programmatic dependent launch ----
 // Kernels of the decode path are launched with the "programmatic stream serialization" attribute (unless switched off

@@ -59,6 +59,10 @@ extern "C" void cq_qmatmul_decode_static(int wtype, const void *vx, const void *
         cq_set_status(CQ_ERR_BAD_ARG, "decode_static: null pointer or empty shape");
         return;
     }
+    if (x_elem != CQ_F32 && x_elem != CQ_F16 && x_elem != CQ_BF16) {      // also the type of dst: reject before any launch
+        cq_set_status(CQ_ERR_BAD_ARG, "decode_static: x_elem must be CQ_F32, CQ_F16 or CQ_BF16");
+        return;
+    }
     if (b_size > 8) {
         cq_set_status(CQ_ERR_UNSUPPORTED, "decode_static: at most 8 activation rows per call");
         return;
@@ -72,7 +76,11 @@ extern "C" void cq_qmatmul_decode_static(int wtype, const void *vx, const void *
     }
     void *scratch = scratch_on_current_device();
     if (!scratch) return;
+    // The GEMV must never run over what an earlier call left in the shared array: stop when the quantize step was
+    // rejected or failed to launch (any failure recorded meanwhile, by any thread, counts).
+    const unsigned failures_before = cq_failure_count();
     cq_quantize_act(x, x_elem, scratch, ncols_x, (int)k_padded, b_size, CQ_ACT_Q8_1_ENC, stream);
+    if (cq_failure_count() != failures_before) return;
     cq_mmvq(wtype, CQ_ACT_Q8_1_ENC, x_elem, vx, scratch, dst, ncols_x, nrows_x, (int)(k_padded / 32), nrows_x, b_size,
             stream);
 }

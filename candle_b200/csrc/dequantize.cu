@@ -185,6 +185,43 @@ bool dispatch(int wtype, const void *w, const int32_t *ids, void *out, int out_k
 
 }  // namespace
 
+// ---- unquantized GGUF tensors (F32, F16, BF16): `QTensor::dequantize` is a plain element conversion for them ----
+namespace {
+template <class In> __device__ __forceinline__ float plain_to_float(In v);
+template <> __device__ __forceinline__ float plain_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float plain_to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float plain_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <class In>
+__global__ void __launch_bounds__(256) convert_plain_kernel(const In *__restrict__ src, void *__restrict__ out, int out_kind, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = plain_to_float<In>(src[i]);
+        if (out_kind == CQ_F32) reinterpret_cast<float *>(out)[i] = v;
+        else if (out_kind == CQ_F16) reinterpret_cast<__half *>(out)[i] = __float2half_rn(v);
+        else reinterpret_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(v);
+    }
+}
+}  // namespace
+
+// out[i] = float(src[i]) rounded once to out_kind, for GGUF tensors stored as F32 (ggml id 0), F16 (1) or BF16 (30):
+// what `QTensor::dequantize` / `dequantize_f16` give for them (candle-core/src/quantized/mod.rs:689-710; the reference
+// converts on the CPU, k_quants.rs `GgmlType for f32 / f16 / bf16`).
+extern "C" void cq_convert_plain(int ggml_dtype, const void *src, void *out, int out_kind, int64_t n, void *stream) {
+    if (!src || !out || n <= 0 || (out_kind != CQ_F32 && out_kind != CQ_F16 && out_kind != CQ_BF16)) {
+        cq_set_status(CQ_ERR_BAD_ARG, "convert_plain: null pointer, empty tensor or unknown output type");
+        return;
+    }
+    int64_t blocks = (n + 255) / 256;
+    const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (ggml_dtype == 0) convert_plain_kernel<float><<<grid, 256, 0, st>>>((const float *)src, out, out_kind, n);
+    else if (ggml_dtype == 1) convert_plain_kernel<__half><<<grid, 256, 0, st>>>((const __half *)src, out, out_kind, n);
+    else if (ggml_dtype == 30) convert_plain_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)src, out, out_kind, n);
+    else { cq_set_status(CQ_ERR_BAD_ARG, "convert_plain: source type must be F32 (0), F16 (1) or BF16 (30)"); return; }
+    cq_check_launch("convert_plain");
+}
+
 // out[r, :] = to_float(W[r, :]) for a tensor of n_rows rows of k elements (k a multiple of the block size).
 extern "C" void cq_dequantize(int wtype, const void *w, void *out, int out_kind, int64_t n_rows, int64_t k, void *stream) {
     if (!w || !out || n_rows <= 0 || k <= 0 || cq_type_size(wtype) == 0 || k % cq_block_elems(wtype) != 0 || n_rows > 65535 * 64LL) {

@@ -48,9 +48,23 @@ __global__ void gemv_staged_kernel(const uint8_t *__restrict__ w, const uint8_t 
 
 using namespace cq_plan;
 
-// tuning overrides for experiments (0 = automatic)
+// tuning overrides: variables only in experiment builds (-DCQ_EXPERIMENT); the default library plans by itself
+#ifdef CQ_EXPERIMENT
 int g_force_rb = 0;
 int g_force_ctas_per_sm = 0;
+#else
+constexpr int g_force_rb = 0;
+constexpr int g_force_ctas_per_sm = 0;
+#endif
+
+// Read-only plan query (cq_mmvq_plan): when set, the launch helpers below record what they would launch and return.
+thread_local int *g_plan_out = nullptr;
+enum { kPlanStaged = 0, kPlanMma = 1 };
+inline bool record_plan(int kind, int rows_per_batch, int grid, int threads) {
+    if (!g_plan_out) return false;
+    g_plan_out[0] = kind; g_plan_out[1] = rows_per_batch; g_plan_out[2] = grid; g_plan_out[3] = threads;
+    return true;
+}
 
 // Table of instantiations for one (weight type, activation encoding): [batch 1..8][RB index: 1,2,4,8].
 template <int TYPE, int ACT> struct KernelTable {
@@ -77,6 +91,7 @@ bool launch_type(const void *w, const void *y, void *dst, int out_kind, int K, i
                  cudaStream_t st) {
     Plan p;
     if (!make_plan<TYPE, ACT>(K, N, B, p)) return false;
+    if (record_plan(kPlanStaged, p.RB, p.grid, p.T)) return true;
     ensure_smem_attr(p.k);
     const int row_bytes = K / cq_block_elems(ChunkGeom<TYPE>::BASE) * cq_type_size(ChunkGeom<TYPE>::BASE);
     const uint8_t *wp = (const uint8_t *)w, *yp = (const uint8_t *)y;
@@ -112,6 +127,7 @@ bool launch_mma(const void *w, const void *y, void *dst, int out_kind, int K, in
     const int grid = (ntiles + tpc - 1) / tpc;
     const int smem = cq_mma::smem_bytes<TYPE>(tpc) + 16;     // fragment reads may touch a few bytes past the last row
     if (smem > di.smem_optin) return false;
+    if (record_plan(kPlanMma, cq_mma::kTileRows * tpc, grid, cq_mma::kThreads)) return true;
     ensure_smem_attr(&ke);
     const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
     cq_launch_k(gemv_mma_kernel<TYPE>, dim3(grid), dim3(cq_mma::kThreads), (size_t)smem, st, (const uint8_t *)w, (const uint8_t *)y, dst,
@@ -282,9 +298,24 @@ extern "C" int cq_mmvq_pair_q4k_q6k(const void *wa, int nrows_a, float *dst_a, c
     return ok ? 1 : 0;
 }
 
+#ifdef CQ_EXPERIMENT
 extern "C" void cq_set_tuning(int rows_per_batch, int ctas_per_sm) {
     g_force_rb = rows_per_batch;
     g_force_ctas_per_sm = ctas_per_sm;
+}
+#endif
+
+// What cq_mmvq would launch for these arguments, without launching: out[0] kernel (0 staged dp4a, 1 tensor core),
+// out[1] weight rows per staged batch (rows per CTA for the tensor-core kernel), out[2] grid, out[3] threads per CTA,
+// all for the first pass when the batch is split.  Returns 0, or -1 when the arguments are rejected.
+extern "C" int cq_mmvq_plan(int wtype, int act, int ncols_x, int nrows_x, int b_size, int *out) {
+    if (!out) return -1;
+    alignas(16) static const uint8_t dummy[16] = {};
+    out[0] = out[1] = out[2] = out[3] = -1;
+    g_plan_out = out;
+    cq_mmvq(wtype, act, CQ_F32, dummy, dummy, (void *)dummy, ncols_x, nrows_x, (ncols_x + 511) / 512 * 16, nrows_x, b_size, nullptr);
+    g_plan_out = nullptr;
+    return out[0] < 0 ? -1 : 0;
 }
 
 // Rows from which the tensor-core GEMV replaces the dp4a one (0: per-format default; 9 or more: never).  Same bits either way.

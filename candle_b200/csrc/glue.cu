@@ -65,6 +65,10 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, c
     }
 }
 
+// Set when a rope / KV-store kernel met a position at or beyond the cache length `tmax` (the cos / sin tables must hold
+// at least tmax rows): the element is skipped, nothing is read or written out of range.
+__device__ int g_glue_pos_overflow = 0;
+
 // Interleaved rotary embedding (pairs (2i, 2i+1), candle's rope_i) applied in place to q and to k, then k and v are
 // written into the caches at position pos + t.  q: [B*T rows of q_stride floats], heads side by side; k, v likewise
 // (so q and k may be column ranges of one projection output); caches [B, Hkv, Tmax, D]; cos / sin: [max_pos, D/2].
@@ -87,13 +91,14 @@ __global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, 
     const int t = (int)((e / ((int64_t)half_d * heads)) % T);
     const int b = (int)(e / ((int64_t)half_d * heads * T));
     const int p = pos[0] + t;
+    if (p < 0 || p >= tmax) { g_glue_pos_overflow = 1; return; }       // past the tables and the cache: skip, report
     const float c = cosv[(size_t)p * half_d + i], s = sinv[(size_t)p * half_d + i];
     float *src = (is_q ? q : k) + ((size_t)b * T + t) * (is_q ? q_stride : k_stride) + ((size_t)hh * half_d + i) * 2;
     const float x0 = src[0], x1 = src[1];
     const float r0 = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
     const float r1 = __fmaf_rn(x0, s, __fmul_rn(x1, c));
     if (is_q) { src[0] = r0; src[1] = r1; }
-    else if (p < tmax) {
+    else {
         const size_t co = ((((size_t)b * hkv + hh) * tmax + p) * half_d + i) * 2;
         kc[co] = r0; kc[co + 1] = r1;
         const float *vs = v + ((size_t)b * T + t) * v_stride + ((size_t)hh * half_d + i) * 2;
@@ -211,6 +216,7 @@ __global__ void __launch_bounds__(128) qknorm_rope_store_kernel(float *__restric
     const int64_t bt = u / heads;
     const int t = (int)(bt % T), b = (int)(bt / T);
     const int p = pos[0] + t;
+    if (p < 0 || p >= tmax) { g_glue_pos_overflow = 1; return; }       // whole warp: p is the same in every lane
     float *src = (is_q ? q : k) + bt * (is_q ? q_stride : k_stride) + (size_t)hh * 128 + 4 * lane;
     float4 x = *reinterpret_cast<const float4 *>(src);
     const float *nw = is_q ? qw : kw;
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(128) qknorm_rope_store_kernel(float *__restric
         r.z = __fmaf_rn(x.z, c.y, -__fmul_rn(x.w, s.y)); r.w = __fmaf_rn(x.z, s.y, __fmul_rn(x.w, c.y));
     }
     if (is_q) *reinterpret_cast<float4 *>(src) = r;
-    else if (p < tmax) {
+    else {
         const size_t co = (((size_t)b * hkv + hh) * tmax + p) * 128 + 4 * lane;
         *reinterpret_cast<float4 *>(kc + co) = r;
         *reinterpret_cast<float4 *>(vc + co) = *reinterpret_cast<const float4 *>(v + bt * v_stride + (size_t)hh * 128 + 4 * lane);
@@ -297,6 +303,19 @@ extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const f
     cq_launch_k(rope_store_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, q, k, v, cosv, sinv, pos,
                 k_cache, v_cache, batch, t, hq, hkv, tmax, head_dim / 2, q_stride, k_stride, v_stride);
     cq_check_launch("rope");
+}
+
+// 1 if a rope / KV-store launch on the current device met a position at or beyond tmax since the last query
+// (synchronises the device and clears the flag).
+extern "C" int cq_glue_position_overflow_flag(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_glue_pos_overflow, sizeof v) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+    if (v) {
+        const int z = 0;
+        cudaMemcpyToSymbol(g_glue_pos_overflow, &z, sizeof z);
+        cq_set_status(CQ_ERR_BAD_ARG, "rope: a position reached the end of the KV cache / rotary tables");
+    }
+    return v;
 }
 
 extern "C" void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *stream) {

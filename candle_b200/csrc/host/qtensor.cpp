@@ -375,12 +375,19 @@ extern "C" int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1,
 extern "C" int cqh_qtensor_dequantize(void *handle, void *out, int out_dtype, void *stream) {
     return guarded([&] {
         auto &t = *(std::shared_ptr<QTensor> *)handle;
-        if (!kernels_support(t->dtype())) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(t->dtype()));
+        const bool plain = t->dtype() == GgmlDType::F32 || t->dtype() == GgmlDType::F16 || t->dtype() == GgmlDType::BF16;
+        if (!plain && !kernels_support(t->dtype())) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(t->dtype()));
         const auto &sh = t->shape();
         size_t elems = 1;
         for (int64_t d : sh) elems *= (size_t)d;
         if (elems == 0) return;
         if (!out) throw Error("dequantize: null output pointer");
+        if (plain) {        // unquantized GGUF tensors: an element conversion
+            DeviceGuard g(t->storage().device());
+            cq_convert_plain((int)t->dtype(), t->storage().device_ptr(), out, out_dtype, (int64_t)elems, stream);
+            lib_check("dequantize");
+            return;
+        }
         const size_t k = (size_t)sh.back();
         DeviceGuard g(t->storage().device());
         cq_dequantize((int)t->dtype(), t->storage().device_ptr(), out, out_dtype, (int64_t)(elems / k), (int64_t)k, stream);

@@ -14,14 +14,16 @@
 // of this rank in device memory (all ranks issue the same sequence), so the kernel can be replayed from a CUDA graph and
 // stale slots never match.  Every poll is bounded (about a second); after a give-up a device flag is raised and the
 // kernel returns.  A staging area must not be the target of two consecutive gathers (a fast rank would overwrite slots
-// a slow one has not read yet); with one other gather in between, that gather orders the accesses.  The host side
-// alternates two areas per shape for that.
+// a slow one has not read yet); with one other gather in between, that gather orders the accesses.  Every gather site
+// therefore has two areas and the KERNEL picks one by the parity of the epoch: consecutive gathers of a rank always
+// differ in parity, whatever their shapes, in eager runs and in replays of a CUDA graph alike (a choice made on the
+// host would be frozen into the graph and could repeat across the replay boundary).
 #include "../../include/candle_q_b200.h"
 #include "common.cuh"
 
 namespace {
 
-struct PeerPtrs { void *p[CQ_MAX_PEERS]; };
+struct PeerPtrs { void *p[2][CQ_MAX_PEERS]; };     // [epoch parity][rank]
 
 __device__ int g_peer_gather_timeout = 0;
 __device__ long long g_peer_gather_limit = 2000000000LL;     // SM clocks a poll may last: about a second
@@ -35,7 +37,7 @@ __device__ __forceinline__ uint2 ld_slot(const uint2 *p) {
     return v;
 }
 
-// stage.p[q]: staging area of rank q, [world][rows * n_local] slots, as mapped here.
+// stage.p[e][q]: staging area of rank q for epochs of parity e, [world][rows * n_local] slots, as mapped here.
 // state[0]: gathers completed by this rank, state[1]: CTAs of the running launch that are done.
 __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__restrict__ src, int src_stride, PeerPtrs stage,
                                                           uint32_t *__restrict__ dst, unsigned *state, int rows, int n_local,
@@ -43,6 +45,7 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
     cq_pdl_launch_dependents();
     cq_pdl_wait();      // the slice is the preceding kernel's output
     const unsigned epoch = *(volatile unsigned *)state + 1u;      // only the CTA that finishes last advances it
+    void *const *area = stage.p[epoch & 1u];
     const int64_t total = (int64_t)rows * n_local;
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
     // Work items are (peer offset q, word i), word fastest: consecutive threads touch consecutive slots, and the items of
@@ -54,9 +57,9 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
         const int j = (int)(i / n_local), c = (int)(i % n_local);
         const uint32_t v = src[(int64_t)j * src_stride + c];
         if (q == 0) dst[(int64_t)j * n_total + (int64_t)rank * n_local + c] = v;
-        else st_slot((uint2 *)stage.p[(rank + q) % world] + (int64_t)rank * total + i, v, epoch);
+        else st_slot((uint2 *)area[(rank + q) % world] + (int64_t)rank * total + i, v, epoch);
     }
-    const uint2 *mine = (const uint2 *)stage.p[rank];
+    const uint2 *mine = (const uint2 *)area[rank];
     bool gave_up = false;
     const long long limit = g_peer_gather_limit;
     constexpr int U = 4;        // slots in flight per thread
@@ -112,10 +115,12 @@ extern "C" void cq_peer_gather_words(const void *src, int src_stride, void *cons
         return;
     }
     PeerPtrs s{};
-    for (int p = 0; p < world; ++p) {
-        if (!peer_stage[p] || (uintptr_t)peer_stage[p] % 8 != 0) { cq_set_status(CQ_ERR_BAD_ARG, "peer gather: missing or misaligned staging pointer"); return; }
-        s.p[p] = peer_stage[p];
-    }
+    for (int e = 0; e < 2; ++e)
+        for (int p = 0; p < world; ++p) {
+            void *a = peer_stage[e * CQ_MAX_PEERS + p];
+            if (!a || (uintptr_t)a % 8 != 0) { cq_set_status(CQ_ERR_BAD_ARG, "peer gather: missing or misaligned staging pointer"); return; }
+            s.p[e][p] = a;
+        }
     const int64_t total = (int64_t)rows * n_local;
     int grid = (int)((total * world + 255) / 256);  // one (peer, word) item per thread while that fits in 64 CTAs
     if (grid > 64) grid = 64;

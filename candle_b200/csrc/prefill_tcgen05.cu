@@ -53,7 +53,13 @@ constexpr int kThreads = (kEpiWarps + kProdWarps + 2) * 32;
 constexpr int kSmemBytes = 1024 + kStagesA * kStageA + kStagesB * kStageB + 2 * 8 * 512;
 
 __device__ int g_prefill_timeout_flag = 0;
-int g_prefill_dbg = 0;   // experiment switch: bit 0 skips the producers' work and the activation copies, bit 1 the epilogue's arithmetic (results are then garbage)
+// Role switches for profiling exist only in experiment builds (-DCQ_EXPERIMENT): bit 0 skips the producers' work and the
+// activation copies, bit 1 the epilogue's arithmetic (results are then garbage).  The default library always passes 0.
+#ifdef CQ_EXPERIMENT
+int g_prefill_dbg = 0;
+#else
+constexpr int g_prefill_dbg = 0;
+#endif
 
 // ---- tcgen05 wrappers ----
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, int ncols) {
@@ -835,7 +841,9 @@ extern "C" void cq_moe_prefill_gemm(int wtype, const void *input, int in_elem, c
     cq_check_launch("moe prefill gemm");
 }
 
+#ifdef CQ_EXPERIMENT
 extern "C" void cq_prefill_set_debug(int flags) { g_prefill_dbg = flags; }
+#endif
 
 extern "C" int cq_prefill_timeout_flag(void) {
     int v = 0;

@@ -12,11 +12,15 @@
 namespace {
 std::atomic<int> g_status{CQ_OK};
 std::atomic<int> g_cuda_err{0};
+std::atomic<unsigned> g_failures{0};     // how many failures were ever recorded (never cleared)
 std::mutex g_msg_mu;
 char g_msg[256] = "";
 }  // namespace
 
+unsigned cq_failure_count() { return g_failures.load(); }
+
 void cq_set_status(int status, const char *msg) {
+    if (status != CQ_OK) g_failures.fetch_add(1);
     g_status.store(status);
     std::lock_guard<std::mutex> lk(g_msg_mu);
     std::snprintf(g_msg, sizeof g_msg, "%s", msg ? msg : "");

@@ -113,9 +113,14 @@ class LlamaShapedDecoder:
         ang = torch.arange(cfg.max_pos, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos(), ang.sin()
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.device)       # cache position of the next token
+        self._pos_host = 0      # host copy of pos: positions are checked against max_pos before anything is launched
         self._graph = None
         self.fuse_quantize = True       # decode steps: producers store Q8_1 containers directly
         self._att_scratch = None        # split-context attention: partial results and arrival counters
+        if world > 1:       # ranks build their shards at different speeds: line up before the first gather, whose polls are bounded
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=group)
 
     # ---- glue -------------------------------------------------------------------------------------------------
     def _norm(self, x: torch.Tensor, delta, w: torch.Tensor) -> torch.Tensor:
@@ -169,6 +174,7 @@ class LlamaShapedDecoder:
         and the matmuls skip their quantize launch; the containers are the bytes the stand-alone quantizer would
         make, so tokens do not depend on which path ran."""
         cfg, B, T = self.cfg, tokens.shape[0], tokens.shape[1]
+        self._claim_positions(T)
         hd, R, lib = cfg.head_dim, B * T, capi.lib()
         st = torch.cuda.current_stream(self.device).cuda_stream
         q_cols, kv_cols = self.hq_l * hd, self.hkv_l * hd
@@ -213,19 +219,38 @@ class LlamaShapedDecoder:
             capi.check("decoder glue")
             last = h.view(B, T, -1)[:, -1, :].contiguous()
             logits = self.output.forward_q8_1(last) if fused else self.output.forward(last)     # [B, vocab / world]
+            self.last_logits = logits       # this rank's vocabulary slice, last position (read by tests)
             tok = argmax_sharded(logits, self.vocab_start, self.gather)
             self.pos += T
         return tok
 
     # ---- greedy loop ------------------------------------------------------------------------------------------
+    def _claim_positions(self, t: int) -> None:
+        """Host-side bound on cache positions: raises before anything is launched when `t` more tokens would run past
+        the KV cache and the rotary tables (both hold cfg.max_pos positions)."""
+        if self._pos_host + t > self.cfg.max_pos:
+            raise ValueError(f"position {self._pos_host} + {t} tokens exceeds max_pos = {self.cfg.max_pos}")
+        self._pos_host += t
+
+    def check(self) -> None:
+        """Raises if a device-side check tripped since the last call: a peer gather that gave up waiting for another
+        rank, or a rope / KV-store launch that met a position beyond the cache (synchronises the device)."""
+        chk = getattr(getattr(self, "gather", None), "check", None)
+        if chk is not None:
+            chk()
+        if capi.lib().cq_glue_position_overflow_flag() != 0:
+            capi.lib().cq_clear_status()
+            raise RuntimeError("a decode step ran past max_pos: tokens after that point are invalid")
+
     def reset(self):
         self.pos.zero_()
+        self._pos_host = 0
 
     def capture_decode_step(self) -> bool:
         """Record one decode step (T = 1) as a CUDA graph.  Returns False when capture is not possible
         (then decode_step launches eagerly)."""
         self._tok_in = torch.zeros((self.batch, 1), dtype=torch.int64, device=self.device)
-        saved = self.pos.clone()
+        saved, saved_host = self.pos.clone(), self._pos_host
         try:
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))     # _tok_in and every earlier write are visible
@@ -243,21 +268,26 @@ class LlamaShapedDecoder:
             ok = False
         torch.cuda.synchronize(self.device)
         self.pos.copy_(saved)
+        self._pos_host = saved_host
         return ok
 
     def decode_step(self, tok: torch.Tensor) -> torch.Tensor:
         if self._graph is None:
             return self.forward(tok.view(self.batch, 1))
+        self._claim_positions(1)        # the replayed step advances the device-side position
         self._tok_in.copy_(tok.view(self.batch, 1))
         self._graph.replay()
         return self._tok_out
 
     def generate(self, prompt: torch.Tensor, steps: int) -> torch.Tensor:
         """Greedy decoding: prompt int64 [B, Tp] -> generated tokens [B, steps]."""
+        if prompt.shape[1] + max(steps - 1, 0) > self.cfg.max_pos:
+            raise ValueError(f"prompt of {prompt.shape[1]} tokens plus {steps} steps exceeds max_pos = {self.cfg.max_pos}")
         self.reset()
         tok = self.forward(prompt)
         outs = [tok]
         for _ in range(steps - 1):
             tok = self.decode_step(tok).clone()
             outs.append(tok)
+        self.check()
         return torch.stack(outs, dim=1)

@@ -107,6 +107,7 @@ class MoeShapedDecoder:
         ang = torch.arange(cfg.max_pos, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos().contiguous(), ang.sin().contiguous()
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._pos_host = 0      # host copy of pos: positions are checked against max_pos before anything is launched
         self._graph = None
         self._att_scratch = None
         self.hq_l, self.hkv_l = cfg.n_heads, cfg.n_kv_heads      # attention is replicated: every rank owns all heads
@@ -114,6 +115,8 @@ class MoeShapedDecoder:
     # the norm and attention helpers are those of the dense harness
     _norm = LlamaShapedDecoder._norm
     reset = LlamaShapedDecoder.reset
+    check = LlamaShapedDecoder.check
+    _claim_positions = LlamaShapedDecoder._claim_positions
     capture_decode_step = LlamaShapedDecoder.capture_decode_step
     decode_step = LlamaShapedDecoder.decode_step
     generate = LlamaShapedDecoder.generate
@@ -165,6 +168,7 @@ class MoeShapedDecoder:
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens int64 [B, T] at cache positions pos .. pos+T-1 -> greedy next token [B]; advances pos."""
         cfg, B, T = self.cfg, tokens.shape[0], tokens.shape[1]
+        self._claim_positions(T)
         hd, R, lib = cfg.head_dim, B * T, capi.lib()
         st = torch.cuda.current_stream(self.device).cuda_stream
         q_cols, kv_cols = cfg.n_heads * hd, cfg.n_kv_heads * hd
@@ -189,6 +193,7 @@ class MoeShapedDecoder:
             capi.check("moe decoder glue")
             last = h.view(B, T, cfg.d_model)[:, -1, :].contiguous()
             logits = self.output.forward(last)
+            self.last_logits = logits       # last position (read by tests)
             # first maximum, as argmax over the row
             mx = logits.max(dim=-1, keepdim=True).values
             ar = torch.arange(logits.shape[-1], device=self.device)

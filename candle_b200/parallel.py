@@ -64,8 +64,10 @@ class PeerGatherer(Gatherer):
     tag, into staging areas of all other ranks and picks up what they stored here (`cq_peer_gather_words`).  The staging
     areas live in symmetric memory (`torch.distributed._symmetric_memory`: one CUDA virtual-memory allocation per rank,
     mapped by all); they are made on first use of a shape, which is a collective step, so shapes must first occur
-    outside CUDA-graph capture and in the same order on all ranks.  Two areas per shape alternate when one shape is
-    gathered twice in a row.  When a rank would send more than `MAX_SENT_WORDS` 32-bit words in total (prompts, the
+    outside CUDA-graph capture and in the same order on all ranks.  Every shape has two areas and the kernel picks one by
+    the parity of its device-side epoch counter, so two consecutive gathers never store into the same area - in eager
+    runs and across the replays of a CUDA graph (two result buffers alternate on the host so that back-to-back gathers
+    of one shape return different tensors).  When a rank would send more than `MAX_SENT_WORDS` 32-bit words in total (prompts, the
     vocabulary slice of a large batch on many ranks) the library all-gather is used: the slot protocol doubles the bytes
     on the link and is built for latency, not bandwidth."""
 
@@ -93,8 +95,7 @@ class PeerGatherer(Gatherer):
         hdl = self._symm.rendezvous(stage, group=self._group_name)
         stage.zero_()
         self._keep.append((stage, hdl))
-        ptrs = (ctypes.c_void_p * self._capi.MAX_PEERS)(*[int(p) for p in hdl.buffer_ptrs])
-        return torch.empty((rows, self.world * n_local), dtype=dtype, device=self.device), ptrs
+        return [int(p) for p in hdl.buffer_ptrs]
 
     def __call__(self, local: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
@@ -116,14 +117,20 @@ class PeerGatherer(Gatherer):
         if key not in self._slots:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("a new gather shape inside CUDA-graph capture: run the step once before capturing")
-            self._slots[key] = [[self._new_slot(rows, n_local, local.dtype) for _ in range(2)], 0]
+            areas = [self._new_slot(rows, n_local, local.dtype) for _ in range(2)]      # even / odd epochs
+            ptrs = (ctypes.c_void_p * (2 * self._capi.MAX_PEERS))()
+            for e in range(2):
+                for p, a in enumerate(areas[e]):
+                    ptrs[e * self._capi.MAX_PEERS + p] = a
+            outs = [torch.empty((rows, self.world * n_local), dtype=local.dtype, device=self.device) for _ in range(2)]
+            self._slots[key] = [outs, 0, ptrs]
             torch.cuda.synchronize()
             dist.barrier(group=self.group)      # nobody stores into a staging area before its owner has zeroed it
         entry = self._slots[key]
         if self._last == key:
-            entry[1] ^= 1       # never the same staging area twice in a row
+            entry[1] ^= 1       # back-to-back gathers of one shape return different result tensors
         self._last = key
-        full, ptrs = entry[0][entry[1]]
+        full, ptrs = entry[0][entry[1]], entry[2]
         self._capi.lib().cq_peer_gather_words(local.data_ptr(), local.stride(0), ptrs, full.data_ptr(), self._state.data_ptr(),
                                                rows, n_local, self.world * n_local, self.rank, self.world,
                                                torch.cuda.current_stream().cuda_stream)
@@ -147,6 +154,12 @@ def make_gatherer(group=None, world: int | None = None, device=None) -> Gatherer
             pg.check()
         except Exception as e:      # no peer access between these GPUs, or an older torch: every rank must learn of it
             ok = 0
+            try:        # a probe that gave up leaves the device flag set: clear it so later checks see only their own gathers
+                from . import capi
+                capi.lib().cq_peer_gather_clear_timeout()
+                capi.lib().cq_clear_status()
+            except Exception:
+                pass
             print(f"candle_b200: peer-memory gather unavailable ({type(e).__name__}: {e}); using the library all-gather",
                   file=sys.stderr)
         flag = torch.tensor([ok], device=device)

@@ -203,23 +203,65 @@ class QTensor:
         return QMatMul.from_qtensor(self).forward(xs)
 
 
-class QMatMul:
-    """``QMatMul::QTensor`` variant: y = x . W^T with W quantized."""
+def _env_switch(name: str) -> bool:
+    """The reference's reading of its switches (mod.rs:814-834): set, not empty and not "0"."""
+    import os
+    v = os.environ.get(name)
+    return v is not None and v != "" and v != "0"
 
-    def __init__(self, qtensor: QTensor):
-        if qtensor.rank() != 2:
+
+class QMatMul:
+    """y = x . W^T.  The three variants of the reference's ``QMatMul`` enum (mod.rs:807-852, 1020-1043):
+
+    * ``kind == "QTensor"``   - W stays quantized and the product runs in this library's kernels;
+    * ``kind == "Tensor"``    - W de-quantized to a dense f32 tensor: always for GGUF tensors stored as F32 / F16 / BF16
+      (norm vectors, sometimes whole matrices), and for every tensor when ``CANDLE_DEQUANTIZE_ALL`` is set;
+    * ``kind == "TensorF16"`` - W de-quantized to f16 when ``CANDLE_DEQUANTIZE_ALL_F16`` is set; inputs are cast to f16
+      for the product and the result back to the input type.
+
+    The two dense variants multiply with the tensor library's GEMM, as the reference does with its own."""
+
+    def __init__(self, qtensor: QTensor, _dense: torch.Tensor | None = None, _kind: str = "QTensor"):
+        if qtensor.rank() != 2 and _dense is None:
             raise CandleQError("QMatMul expects a rank-2 quantized tensor")
         self.qtensor = qtensor
+        self.dense = _dense
+        self.kind = _kind
 
     @classmethod
     def from_qtensor(cls, qtensor: QTensor) -> "QMatMul":
+        """``QMatMul::from_arc`` (mod.rs:837-852); the switches are read at every call, not cached per thread."""
+        plain = qtensor.dtype in (GgmlDType.F32, GgmlDType.F16, GgmlDType.BF16)
+        if plain or _env_switch("CANDLE_DEQUANTIZE_ALL"):
+            return cls(qtensor, qtensor.dequantize(torch.float32), "Tensor")
+        if _env_switch("CANDLE_DEQUANTIZE_ALL_F16"):
+            return cls(qtensor, qtensor.dequantize(torch.float16), "TensorF16")
         return cls(qtensor)
+
+    def dequantize_f16(self) -> torch.Tensor:
+        """``QMatMul::dequantize_f16`` (mod.rs:858-864)."""
+        if self.kind == "QTensor":
+            return self.qtensor.dequantize(torch.float16)
+        return self.dense.to(torch.float16)
+
+    def _forward_dense(self, xs: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
+        w = self.dense
+        if self.kind == "TensorF16":
+            y = torch.matmul(xs.to(torch.float16), w.t()).to(xs.dtype)
+        else:
+            y = torch.matmul(xs, w.t().to(xs.dtype) if w.dtype != xs.dtype else w.t())
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
 
     def forward(self, xs: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         if not xs.is_cuda:
             raise CandleQError("QMatMul.forward needs a CUDA tensor: this build has no CPU path")
         if xs.dtype not in _ELEM:
             raise CandleQError(f"Expected f32/f16/bf16, got {xs.dtype}")
+        if self.kind != "QTensor":
+            return self._forward_dense(xs, out)
         if not xs.is_contiguous():
             raise CandleQError("input tensor is not contiguous")
         n = self.qtensor.shape[0]

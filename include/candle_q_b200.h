@@ -217,9 +217,6 @@ void cq_prefill_quantize(const void *x, int x_elem, void *scratch, int k, int to
 void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, void *dst, int out_elem, int ncols_x, int nrows_x,
                      int tokens, int stride_dst, void *stream);
 int cq_prefill_timeout_flag(void);
-/* Experiment switch for profiling: bit 0 skips the producer warps' work, bit 1 the epilogue's (outputs are then
- * meaningless); 0 restores normal operation. */
-void cq_prefill_set_debug(int flags);
 
 /* Glue kernels of the decoder harness (f32, fixed order of additions, one launch each).  They stand where candle's
  * quantized models run chains of tensor ops (candle-transformers/src/models/quantized_llama.rs:56-62, 178-262).
@@ -260,12 +257,14 @@ void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *st
 
 /* All-gather of row-sharded outputs over NVLink peer memory in one kernel (replaces the NCCL collective that
  * candle-examples/examples/llama_multiprocess/model.rs:28-66 issues per projection).  `src`: this rank's slice, `rows`
- * rows of `n_local` 32-bit words, row stride `src_stride` words.  `peer_stage[p]`: rank p's staging area of
- * cq_peer_gather_stage_bytes() bytes (zero at set-up, 8-byte aligned) as mapped into THIS process (host array of `world`
- * device pointers).  `dst`: this rank's result [rows, n_total]; rank p's slice lands in columns [p * n_local, +n_local).
+ * rows of `n_local` 32-bit words, row stride `src_stride` words.  `peer_stage[e * CQ_MAX_PEERS + p]`: rank p's staging
+ * area for gathers whose epoch has parity e (two areas per gather site, each cq_peer_gather_stage_bytes() bytes, zero at
+ * set-up, 8-byte aligned) as mapped into THIS process (host array of 2 * CQ_MAX_PEERS device pointers).  The kernel
+ * picks the area from the device-side epoch counter, so consecutive gathers never share one, also across the replays
+ * of a CUDA graph.  `dst`: this rank's result [rows, n_total]; rank p's slice lands in columns [p * n_local, +n_local).
  * `state`: two 32-bit words of this rank's device memory, zero at set-up, shared by all gathers of the rank.  The kernel
  * returns when all ranks' slices are in `dst`, or after about a second (then cq_peer_gather_timeout_flag() reports 1).
- * All ranks must issue the same sequence of gathers, and one staging area must not serve two consecutive gathers. */
+ * All ranks must issue the same sequence of gathers. */
 #define CQ_MAX_PEERS 8
 size_t cq_peer_gather_stage_bytes(int rows, int n_local, int world);
 void cq_peer_gather_words(const void *src, int src_stride, void *const *peer_stage, void *dst, void *state, int rows,
@@ -286,6 +285,10 @@ void cq_moe_route_f32(const float *logits, int32_t *ids, float *weights, int tok
 void cq_qknorm_rope_store_kv_f32(float *q, float *k, const float *v, const float *q_norm_w, const float *k_norm_w, const float *cosv,
                                  const float *sinv, const int *pos, float *k_cache, float *v_cache, int batch, int t, int hq, int hkv,
                                  int head_dim, int tmax, int q_stride, int k_stride, int v_stride, float eps, int neox, void *stream);
+/* Both rope / KV-store kernels need cos / sin tables of at least `tmax` rows.  A position pos[0] + t at or beyond tmax
+ * is skipped (nothing out of range is read or written) and reported here: 1 if that happened on the current device
+ * since the last query (synchronises the device, clears the flag, sets status 1). */
+int cq_glue_position_overflow_flag(void);
 
 /* 1 (default): decode-path kernels (quantize, GEMV, glue, attention) are launched as programmatic dependents of their
  * predecessor in the stream, so their prologue and first weight copies overlap its tail; 0: plain launches. */
@@ -310,9 +313,16 @@ void cq_dequantize(int wtype, const void *w, void *out, int out_kind, int64_t n_
 void cq_get_rows(int wtype, const void *w, const int32_t *ids, void *out, int out_kind, int64_t n_ids, int64_t n_rows, int64_t k,
                  void *stream);
 int cq_get_rows_bad_id(void);
+/* Element conversion for GGUF tensors stored unquantized - F32 (ggml id 0), F16 (1), BF16 (30): what QTensor::dequantize
+ * and dequantize_f16 give for them (candle-core/src/quantized/mod.rs:689-710).  out[i] = src[i] rounded once to out_kind. */
+void cq_convert_plain(int ggml_dtype, const void *src, void *out, int out_kind, int64_t n, void *stream);
 
-/* Experiment hook: force rows-per-batch and the CTA-per-SM cap of the GEMV (0, 0 restores automatic). */
-void cq_set_tuning(int rows_per_batch, int ctas_per_sm);
+/* Read-only: what cq_mmvq would launch for these arguments, nothing is launched.  out[0] kernel (0 staged dp4a GEMV,
+ * 1 tensor-core GEMV), out[1] weight rows per staged batch (rows per CTA for the tensor-core kernel), out[2] grid,
+ * out[3] threads per CTA.  Returns 0, or -1 when cq_mmvq would reject the arguments.  No counterpart in the reference
+ * (its launch shape is fixed: one CTA per weight row, candle-kernels/src/mmvq_gguf.cu:915-1008); tests use it to show
+ * which kernel instantiations a parity case exercised. */
+int cq_mmvq_plan(int wtype, int act, int ncols_x, int nrows_x, int b_size, int *out);
 /* 1 if a GEMV on the current device gave up a bounded wait for a staged copy (then also sets status 4).
  * Synchronises the device. */
 int cq_device_timeout_flag(void);

@@ -26,3 +26,29 @@ def rel_err(a, ref):
     a = np.asarray(a, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     return float(np.abs(a - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+# ---- the benchmark's own inputs (BASELINE configs), regenerated from seeds ------------------------------------------------
+# Weights: f32 N(0, 0.02) from seed 0, quantized by the reference's quantizer (restated in the oracle); activations: f32
+# N(0, 1) from seed 1.  numpy's PCG64 + ziggurat float32 stream; rows are drawn in order, so generating in row chunks
+# gives the same values as one call.  tests/golden/baseline_sha256.json pins the resulting bytes.
+def baseline_weights(oracle, wtype, k, n, chunk_rows=8192):
+    rng = np.random.Generator(np.random.PCG64(0))
+    parts = []
+    for r0 in range(0, n, chunk_rows):
+        rows = min(chunk_rows, n - r0)
+        wf = rng.standard_normal((rows, k), dtype=np.float32)
+        wf *= np.float32(0.02)
+        parts.append(oracle.quantize(wtype, wf))
+    return np.concatenate(parts, axis=0) if len(parts) > 1 else parts[0]
+
+
+def baseline_acts(k, rows):
+    """The first `rows` rows of the seed-1 activation stream of width k (so batch 2 is the first two rows of batch 8)."""
+    rng = np.random.Generator(np.random.PCG64(1))
+    return rng.standard_normal((rows, k), dtype=np.float32)
+
+
+def sha256_hex(a) -> str:
+    import hashlib
+    return hashlib.sha256(np.ascontiguousarray(a).view(np.uint8).tobytes()).hexdigest()

@@ -232,7 +232,7 @@ def test_peer_gather_matches_library_all_gather(tmp_path):
     """The one-kernel gather over NVLink peer memory against the NCCL all-gather, under torchrun with 2 ranks."""
     out = tmp_path / "verdict.txt"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29533", os.path.join(ROOT, "candle_b200", "tp_check.py"),
+           "--master-port", "29533", os.path.join(ROOT, "tests", "tp_check.py"),
            "--gather", "--out", str(out)]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
@@ -245,7 +245,7 @@ def test_tensor_parallel_tokens_match_single_gpu(tmp_path):
     """Launches the consistency script under torchrun with 2 ranks; rank 0 compares with its own 1-GPU run."""
     out = tmp_path / "tp.txt"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29611", os.path.join(ROOT, "candle_b200", "tp_check.py"), "--out", str(out)]
+           "--master-port", "29611", os.path.join(ROOT, "tests", "tp_check.py"), "--out", str(out)]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
@@ -260,9 +260,13 @@ def test_peer_gather_gives_up_when_a_rank_never_arrives(lib, cuda_dev):
     import ctypes
     rows, n_local, world = 2, 64, 2
     nbytes = lib.cq_peer_gather_stage_bytes(rows, n_local, world)
-    mine = torch.zeros(nbytes, dtype=torch.uint8, device=cuda_dev)          # rank 0's staging area
-    other = torch.zeros(nbytes, dtype=torch.uint8, device=cuda_dev)         # stands for rank 1's, on the same GPU
-    ptrs = (ctypes.c_void_p * capi.MAX_PEERS)(mine.data_ptr(), other.data_ptr())
+    # two staging areas per rank: the kernel takes the one of its epoch's parity (epoch 1 -> odd, epoch 2 -> even)
+    mine = [torch.zeros(nbytes, dtype=torch.uint8, device=cuda_dev) for _ in range(2)]      # rank 0's areas
+    other = [torch.zeros(nbytes, dtype=torch.uint8, device=cuda_dev) for _ in range(2)]     # stand for rank 1's, on the same GPU
+    ptrs = (ctypes.c_void_p * (2 * capi.MAX_PEERS))()
+    for e in range(2):
+        ptrs[e * capi.MAX_PEERS + 0] = mine[e].data_ptr()
+        ptrs[e * capi.MAX_PEERS + 1] = other[e].data_ptr()
     state = torch.zeros(4, dtype=torch.int32, device=cuda_dev)
     src = torch.arange(rows * n_local, dtype=torch.float32, device=cuda_dev).view(rows, n_local)
     dst = torch.full((rows, world * n_local), -1.0, device=cuda_dev)
@@ -277,18 +281,21 @@ def test_peer_gather_gives_up_when_a_rank_never_arrives(lib, cuda_dev):
         lib.cq_peer_gather_clear_timeout()
         assert torch.equal(dst[:, :n_local], src)                           # the local slice was delivered
         assert int(state[0].item()) == 1                                    # the gather still counts: epochs stay aligned
-        # what rank 0 sent sits in the other area, tagged with epoch 1
-        sent = other.view(torch.int32).view(world, rows * n_local, 2)[0]
+        # what rank 0 sent sits in the other rank's odd-epoch area, tagged with epoch 1; the even-epoch area is untouched
+        sent = other[1].view(torch.int32).view(world, rows * n_local, 2)[0]
         assert torch.equal(sent[:, 0].view(torch.float32).view(rows, n_local), src) and bool((sent[:, 1] == 1).all())
-        # now play rank 1 by hand for epoch 2: fill rank 0's slots, then the same call completes
+        assert not bool(other[0].any())
+        # now play rank 1 by hand for epoch 2: fill rank 0's even-epoch slots, then the same call completes
         theirs = src + 1000.0
-        slots = mine.view(torch.int32).view(world, rows * n_local, 2)
+        slots = mine[0].view(torch.int32).view(world, rows * n_local, 2)
         slots[1, :, 0] = theirs.view(torch.int32).view(-1)
         slots[1, :, 1] = 2
         lib.cq_peer_gather_words(src.data_ptr(), n_local, ptrs, dst.data_ptr(), state.data_ptr(), rows, n_local, world * n_local, 0, world, st)
         torch.cuda.synchronize()
         assert lib.cq_peer_gather_timeout_flag() == 0
         assert torch.equal(dst[:, n_local:], theirs) and torch.equal(dst[:, :n_local], src)
+        sent2 = other[0].view(torch.int32).view(world, rows * n_local, 2)[0]
+        assert bool((sent2[:, 1] == 2).all())                               # the second gather went to the other area
     finally:
         lib.cq_peer_gather_set_limit_clocks(2_000_000_000)
         lib.cq_peer_gather_clear_timeout()

@@ -6,7 +6,7 @@ import torch
 
 from candle_b200 import capi
 from candle_b200.capi import CandleQError
-from candle_b200.quantized import GgmlDType, QTensor
+from candle_b200.quantized import GgmlDType, QMatMul, QTensor
 from helpers import TYPES
 
 pytestmark = pytest.mark.gpu
@@ -63,3 +63,48 @@ def test_embedding_gathers_dequantized_rows(oracle, cuda_dev, tname):
     assert np.array_equal(o[0].cpu().numpy(), ref[2]) and float(o[1].abs().max()) == 0.0
     assert L.cq_get_rows_bad_id() == 1 and L.cq_get_rows_bad_id() == 0
     L.cq_clear_status()
+
+
+def test_qmatmul_variants_for_unquantized_tensors_and_dequantize_switches(oracle, cuda_dev, monkeypatch):
+    """``QMatMul::from_arc`` (candle-core/src/quantized/mod.rs:837-852): GGUF tensors stored as F32 / F16 / BF16 become the
+    dense `Tensor` variant; CANDLE_DEQUANTIZE_ALL turns every tensor into it, CANDLE_DEQUANTIZE_ALL_F16 into `TensorF16`;
+    forward of the dense variants is x . W^T over the de-quantized values (:1020-1043)."""
+    rng = np.random.default_rng(5)
+    n, k = 48, 256
+    wf = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((3, 5, k)).astype(np.float32)
+    xd = torch.from_numpy(x).to(cuda_dev)
+    monkeypatch.delenv("CANDLE_DEQUANTIZE_ALL", raising=False)
+    monkeypatch.delenv("CANDLE_DEQUANTIZE_ALL_F16", raising=False)
+    for dt, host in ((GgmlDType.F32, wf), (GgmlDType.F16, wf.astype(np.float16)),
+                     (GgmlDType.BF16, oracle.f32_to_bf16_bits(wf))):
+        qt = QTensor.from_data(host, dt, (n, k), cuda_dev)
+        vals = wf if dt == GgmlDType.F32 else host.astype(np.float32) if dt == GgmlDType.F16 else oracle.bf16_bits_to_f32(host)
+        assert np.array_equal(qt.dequantize().cpu().numpy(), vals.reshape(n, k))
+        mm = QMatMul.from_qtensor(qt)
+        assert mm.kind == "Tensor" and mm.dense.dtype == torch.float32
+        y = mm.forward(xd).cpu().numpy()
+        assert y.shape == (3, 5, n)
+        ref = x.reshape(-1, k).astype(np.float64) @ vals.reshape(n, k).astype(np.float64).T
+        assert np.abs(y.reshape(-1, n) - ref).max() / np.abs(ref).max() <= 1e-3      # tf32 may be in use for dense f32 products
+    # a quantized tensor under the two switches
+    wq = oracle.quantize(oracle.Q4K, wf)
+    deq = oracle.dequantize(oracle.Q4K, wq, k)
+    qt = QTensor.from_data(wq, GgmlDType.Q4K, (n, k), cuda_dev)
+    assert QMatMul.from_qtensor(qt).kind == "QTensor"
+    for zero_like in ("", "0"):
+        monkeypatch.setenv("CANDLE_DEQUANTIZE_ALL", zero_like)
+        assert QMatMul.from_qtensor(qt).kind == "QTensor"
+    monkeypatch.setenv("CANDLE_DEQUANTIZE_ALL", "1")
+    mm = QMatMul.from_qtensor(qt)
+    assert mm.kind == "Tensor" and np.array_equal(mm.dense.cpu().numpy(), deq)
+    ref = x.reshape(-1, k).astype(np.float64) @ deq.astype(np.float64).T
+    assert np.abs(mm.forward(xd).cpu().numpy().reshape(-1, n) - ref).max() / np.abs(ref).max() <= 1e-3
+    monkeypatch.delenv("CANDLE_DEQUANTIZE_ALL")
+    monkeypatch.setenv("CANDLE_DEQUANTIZE_ALL_F16", "yes")
+    mm = QMatMul.from_qtensor(qt)
+    assert mm.kind == "TensorF16" and mm.dense.dtype == torch.float16
+    y16 = mm.forward(xd)
+    assert y16.dtype == torch.float32
+    assert np.abs(y16.cpu().numpy().reshape(-1, n) - ref).max() / np.abs(ref).max() <= 2e-2     # f16 weights, inputs and product
+    assert torch.equal(mm.dequantize_f16(), mm.dense)

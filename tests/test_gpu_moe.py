@@ -253,7 +253,7 @@ def test_expert_parallel_tokens_match_single_gpu(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     out = tmp_path / "ep.txt"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29631", os.path.join(root, "candle_b200", "tp_check.py"), "--moe", "--out", str(out)]
+           "--master-port", "29631", os.path.join(root, "tests", "tp_check.py"), "--moe", "--out", str(out)]
     r = subprocess.run(cmd, cwd=root, env=dict(os.environ, NCCL_NVLS_ENABLE="0"), capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert out.read_text().strip() == "identical"

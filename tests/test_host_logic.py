@@ -68,3 +68,23 @@ def test_moe_routing_matches_numpy_restatement():
     assert np.array_equal(experts.numpy(), np.sort(flat, kind="stable"))
     assert np.array_equal(flat[pairs.numpy()], experts.numpy())          # pair indices in expert order
     assert sorted(pairs.tolist()) == list(range(flat.size))
+
+
+def test_decoder_refuses_positions_beyond_max_pos():
+    """The host-side bound of the decoder harness: claiming positions past max_pos raises before anything is launched
+    (the KV cache and the rotary tables hold max_pos positions)."""
+    import types
+
+    import pytest
+
+    from candle_b200.decoder import DecoderConfig, LlamaShapedDecoder
+    stub = types.SimpleNamespace(cfg=DecoderConfig.tiny(), _pos_host=0)
+    LlamaShapedDecoder._claim_positions(stub, 100)
+    LlamaShapedDecoder._claim_positions(stub, 28)
+    assert stub._pos_host == 128 == stub.cfg.max_pos
+    with pytest.raises(ValueError, match="max_pos"):
+        LlamaShapedDecoder._claim_positions(stub, 1)
+    assert stub._pos_host == 128
+    stub2 = types.SimpleNamespace(cfg=DecoderConfig.tiny(), _pos_host=0)
+    with pytest.raises(ValueError, match="max_pos"):
+        LlamaShapedDecoder.generate(stub2, __import__("torch").zeros((1, 120), dtype=__import__("torch").int64), 10)

@@ -1,6 +1,6 @@
 """Token bit-consistency check: greedy tokens of a tensor-parallel run against a single-GPU run of the same model.
 
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node=N --master-addr 127.0.0.1 candle_b200/tp_check.py [--full]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node=N --master-addr 127.0.0.1 tests/tp_check.py [--full]
 
 Every rank builds its shard; rank 0 also builds the whole model on its own GPU and compares the token sequences.
 Prints / writes "identical" or the first difference.
@@ -55,6 +55,24 @@ def check_gather(dev, rank, world) -> str:
         for x, o in zip(xs, outs):
             if not torch.equal(o, ref(x)):
                 bad.append(("graph", rep, tuple(x.shape)))
+    peer.check()
+    # a graph that holds ONE gather, replayed many times: consecutive replays must not share a staging area (the kernel
+    # alternates by its device-side epoch; a host-side choice would be frozen into the graph)
+    x1 = torch.zeros((4, 512), device=dev)
+    peer(x1)
+    with torch.cuda.stream(side):
+        g1 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g1, stream=side):
+            o1 = peer(x1)
+    for rep in range(40):
+        x1.copy_(torch.randn(x1.shape, device=dev, generator=gen))
+        torch.cuda.synchronize()
+        if rep % 2 == rank % 2:        # ranks take turns being late
+            torch.cuda._sleep(2_000_000)
+        g1.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(o1, ref(x1)):
+            bad.append(("one-gather graph", rep))
     peer.check()
     # cost of one gather: 100 alternating gathers of a decode-sized and a head-sized slice, replayed from a graph
     for name, g_ in (("peer", peer), ("nccl", ref)):
