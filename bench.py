@@ -208,6 +208,44 @@ def run_reference(args):
     }))
 
 
+class IsolatedTimer:
+    """Time of one launch on its own: a CUDA graph of five {L2 flush (a 256 MB fill), launch} pairs minus a graph of the
+    five flushes alone, best of three replays each.  Launch latency that a neighbour would hide in a stream is included."""
+
+    def __init__(self, dev):
+        import torch
+        self.torch, self.dev = torch, dev
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        self.side = torch.cuda.Stream(device=dev)
+        self.t_flush = self._graph_ms(lambda: None)
+
+    def _graph_ms(self, launch):
+        torch = self.torch
+
+        def body():
+            for i in range(5):
+                self.flush.fill_(i)
+                launch()
+        with torch.cuda.stream(self.side):
+            body()
+            self.side.synchronize()
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph, stream=self.side):
+                body()
+            best = float("inf")
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.side)
+                gph.replay()
+                e1.record(self.side)
+                self.side.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+        return best
+
+    def ms(self, launch) -> float:
+        return max((self._graph_ms(launch) - self.t_flush) / 5.0, 1e-4)
+
+
 def token_hash(toks) -> str:
     """SHA-256 of the generated token ids (order-sensitive, unlike a sum)."""
     import hashlib
@@ -461,23 +499,15 @@ def run_gpu(args):
     if gather is not None and hasattr(gather, "check"):
         gather.check()          # a gather that gave up its bounded wait would have timed garbage
 
-    # ---- every GEMV launch on its own: L2 flushed (a 256 MB write) before each launch, events around the launch
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    # ---- every GEMV launch on its own (IsolatedTimer: L2 flushed before each launch)
+    timer = IsolatedTimer(dev)
     per_case = {}
-    s_ = torch.cuda.current_stream().cuda_stream
     for (b, t, k, n) in order:
-        best = float("inf")
-        for _ in range(5):
-            flush.fill_(1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+        def one(b=b, t=t, k=k, n=n):
             L.cq_mmvq(int(GgmlDType[t]), capi.ACT_Q8_1, capi.F32, mats[(t, k, n)].qtensor.device_ptr(), q8[(k, b)].data_ptr(),
-                      outs[(n, b)].data_ptr(), k, n // world, kp[k] // 32, n // world, b, s_)
-            e1.record()
-            torch.cuda.synchronize()
-            best = min(best, e0.elapsed_time(e1))
-        per_case.setdefault(t, {}).setdefault(f"{k}x{n}", {})[str(b)] = round(gemv_bytes(t, k, n // world, b) / best / 1e6, 1)
-    del flush
+                      outs[(n, b)].data_ptr(), k, n // world, kp[k] // 32, n // world, b, torch.cuda.current_stream().cuda_stream)
+        per_case.setdefault(t, {}).setdefault(f"{k}x{n}", {})[str(b)] = round(gemv_bytes(t, k, n // world, b) / timer.ms(one) / 1e6, 1)
+    del timer
     capi.check("per-case sweep")
 
     # ---- e2e: host activations -> device, QMatMul.forward, result -> host, all inside the timed region
@@ -541,7 +571,7 @@ def run_gpu(args):
         "gpu_launches": 2 * len(order) * args.steps,
         "sustained": {"value": total_bytes / ms_sustained / 1e6, "unit": UNIT, "steps": sus_steps, "ms_per_step": ms_sustained,
                       "gemv_only_GBps": total_bytes / ms_gemv_sustained / 1e6},
-        "gemv_cases": {"unit": "GB/s per launch (algorithmic bytes, this rank's shard), L2 flushed before each launch, best of 5",
+        "gemv_cases": {"unit": "GB/s per launch (algorithmic bytes, this rank's shard): graph of 5 {256 MB L2 flush, launch} pairs minus the flushes",
                        "by_type_shape_batch": per_case},
         "int8_peak": int8_peak,
         "prefill": prefill,
@@ -592,6 +622,8 @@ def run_case(args):
     L = capi.lib()
     if args.mma_min_batch is not None:
         L.cq_set_mma_min_batch(args.mma_min_batch)
+    if args.mma_kernel is not None:
+        L.cq_set_mma_kernel(args.mma_kernel)
     if args.no_pdl:
         L.cq_set_pdl(0)
     ncopies = max(2, min(16, int(300e6 // (n * k * BYTES_PER_ELEM[t])) + 1))     # rotate through > L2 of weights
@@ -614,7 +646,13 @@ def run_case(args):
     capi.check("case")
     nbytes = gemv_bytes(t, k, n, b)
     best = min(times[1:]) if len(times) > 1 else times[0]
-    print(json.dumps({"case": args.case, "us": times, "algorithmic_bytes": nbytes, "best_GBps": nbytes / best / 1e3}))
+    iso_us = IsolatedTimer(dev).ms(lambda: L.cq_mmvq(int(GgmlDType[t]), capi.ACT_Q8_1, capi.F32, ws[0].data_ptr(), y.data_ptr(), out.data_ptr(),
+                                                      k, n, kp // 32, n, b, torch.cuda.current_stream().cuda_stream)) * 1e3
+    plan = (__import__("ctypes").c_int * 4)()
+    L.cq_mmvq_plan(int(GgmlDType[t]), capi.ACT_Q8_1, k, n, b, plan)
+    print(json.dumps({"case": args.case, "plan_kernel_rows_grid_threads": list(plan), "us": [round(v, 1) for v in times],
+                      "algorithmic_bytes": nbytes, "best_GBps": round(nbytes / best / 1e3, 1),
+                      "isolated_us": round(iso_us, 2), "isolated_GBps": round(nbytes / iso_us / 1e3, 1)}))
 
 
 def run_prefill_case(args):
@@ -756,6 +794,7 @@ def main():
     ap.add_argument("--decode-case", default=None, help="profile helper: BATCH:PROMPT:STEPS, runs only the decoder measurement")
     ap.add_argument("--no-graph", action="store_true", help="with --decode-case: launch decode steps eagerly")
     ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
+    ap.add_argument("--mma-kernel", type=int, default=None, help="with --case: 1 only the CTA-shared tensor-core GEMV, 2 the warp-private one")
     ap.add_argument("--no-pdl", action="store_true", help="with --case: plain launches instead of programmatic dependent launches")
     ap.add_argument("--tune", default=None, help="with --decode-case: RB:CTAS_PER_SM forced for every GEMV (experiment hook)")
     ap.add_argument("--moe-decode-case", default=None, help="BATCH:PROMPT:STEPS, runs the mixture-of-experts decoder measurement "

@@ -92,6 +92,7 @@ def lib() -> C.CDLL:
         L.cq_attention_split_scratch_floats.restype = C.c_size_t
         L.cq_attention_split.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]
         L.cq_set_mma_min_batch.argtypes = [i32]
+        L.cq_set_mma_kernel.argtypes = [i32]
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]

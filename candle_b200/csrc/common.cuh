@@ -206,13 +206,19 @@ template <int NW> __device__ __forceinline__ void cq_lds_words(const uint8_t *p,
 __device__ __forceinline__ uint32_t cq_lds_u16(const uint8_t *p) { return *(const uint16_t *)p; }
 
 // Sum NV per-lane values over the 32 lanes of a warp.  Every value is reduced with the same
-// xor butterfly (16, 8, 4, 2, 1), so the result for one value does not depend on NV.
-// NV must be a power of two <= 32.  On return lane l holds the total of value  l / (32 / NV)  in v[0].
+// xor butterfly (1, 2, 4, 8, 16) - the balanced binary tree over the lanes in natural order: (l0 + l1) + (l2 + l3) ... -
+// so the result for one value does not depend on NV, and a kernel that meets the 32 addends one after the other (the
+// tensor-core GEMV) can rebuild the same tree with a five-deep stack.
+// NV must be a power of two <= 32.  On return the lanes l < NV hold the total of value cq_reduce_slot<NV>(l) in v[0].
+template <int NV> __device__ __forceinline__ int cq_reduce_slot(int lane) {
+    constexpr int LG = NV <= 1 ? 0 : NV <= 2 ? 1 : NV <= 4 ? 2 : NV <= 8 ? 3 : NV <= 16 ? 4 : 5;
+    return LG == 0 ? 0 : (int)(__brev((unsigned)lane) >> (32 - LG));
+}
 template <int NV> __device__ __forceinline__ float cq_warp_reduce_many(float (&v)[NV]) {
     const int lane = threadIdx.x & 31;
     int n = NV;
 #pragma unroll
-    for (int s = 16; s >= 1; s >>= 1) {
+    for (int s = 1; s <= 16; s <<= 1) {
         if (n > 1) {
             const int half = n >> 1;
             const bool up = lane & s;

@@ -15,9 +15,14 @@
 //     lane (about one shuffle per value), warps are then added in index order through shared memory.
 //     The order of additions for one output does not depend on RB, on the grid or on N, so a row gives the
 //     same bits whether the matrix is whole or sharded by rows across GPUs, and whatever the batch size.
+#include <cuda.h>
+
+#include <unordered_map>
+
 #include "../../include/candle_q_b200.h"
 #include "gemv_body.cuh"
 #include "gemv_mma.cuh"
+#include "gemv_mma2.cuh"
 #include "gemv_plan.cuh"
 
 namespace {
@@ -59,7 +64,7 @@ constexpr int g_force_ctas_per_sm = 0;
 
 // Read-only plan query (cq_mmvq_plan): when set, the launch helpers below record what they would launch and return.
 thread_local int *g_plan_out = nullptr;
-enum { kPlanStaged = 0, kPlanMma = 1 };
+enum { kPlanStaged = 0, kPlanMma = 1, kPlanMma2 = 2, kPlanMma2Split = 3 };
 inline bool record_plan(int kind, int rows_per_batch, int grid, int threads) {
     if (!g_plan_out) return false;
     g_plan_out[0] = kind; g_plan_out[1] = rows_per_batch; g_plan_out[2] = grid; g_plan_out[3] = threads;
@@ -108,6 +113,9 @@ int g_mma_min_batch = 0;        // rows from which the tensor-core kernel is use
 // tensor-core 2250 at any row count; Q6_K dp4a 3267 at 4 rows, 1820 at 8, tensor-core 2130; Q8_0 dp4a 4140 at 8 rows,
 // tensor-core 2750.
 constexpr int mma_default_min_batch(int wtype) { return wtype == CQ_Q8_0 ? 9 : 5; }
+// Rows from which the warp-private tensor-core kernel is used where its shape rules hold.  Measured on B200 (4096 ->
+// 128256, GB/s of weights, any row count): Q4_K 3450, Q6_K 2720, Q8_0 4700 - against the dp4a figures above.
+constexpr int mma2_default_min_batch(int wtype) { return wtype == CQ_Q8_0 ? 6 : 5; }
 
 template <int TYPE>
 __global__ void __launch_bounds__(cq_mma::kThreads, 2)
@@ -133,6 +141,128 @@ bool launch_mma(const void *w, const void *y, void *dst, int out_kind, int K, in
     cq_launch_k(gemv_mma_kernel<TYPE>, dim3(grid), dim3(cq_mma::kThreads), (size_t)smem, st, (const uint8_t *)w, (const uint8_t *)y, dst,
                 out_kind, K / cq_mma::Fmt<TYPE>::CHUNK, N, sy, sd, B, row_bytes, tpc);
     return cq_check_launch("gemv (tensor core)");
+}
+
+// ---- tensor-core variant with warp-private tiles (gemv_mma2.cuh); same bits again ----
+int g_mma_kernel = 0;           // 0: automatic, 1: only the CTA-shared kernel above, 2: the warp-private kernel wherever its shape rules allow
+
+template <int TYPE, bool SPLIT>
+__global__ void __launch_bounds__(cq_mma2::kMaxThreads, 2)
+gemv_mma2_kernel(const __grid_constant__ CUtensorMap tmap, const uint8_t *__restrict__ y, void *__restrict__ dst, int out_kind, int nunits,
+                 int nrows, int stride_col_y, int stride_col_dst, int b, int spw) {
+    cq_mma2::gemv_mma2_body<TYPE, SPLIT>(&tmap, y, dst, out_kind, nunits, nrows, stride_col_y, stride_col_dst, b, spw, &g_gemv_timeout_flag);
+}
+
+// Tensor map of the weight matrix as bytes [nrows, row_bytes], box 16 rows x `box_w` bytes, no swizzle, zero fill outside.
+// The driver's encoder is reached through the runtime (no link against libcuda); maps are cached per (pointer, shape).
+struct TmapKey {
+    const void *p; int row_bytes, nrows, box_w;
+    bool operator==(const TmapKey &o) const { return p == o.p && row_bytes == o.row_bytes && nrows == o.nrows && box_w == o.box_w; }
+};
+struct TmapHash {
+    size_t operator()(const TmapKey &k) const {
+        return std::hash<const void *>()(k.p) ^ ((size_t)k.row_bytes * 1000003u) ^ ((size_t)k.nrows * 7919u) ^ (size_t)k.box_w;
+    }
+};
+bool weight_tensor_map(const void *w, int row_bytes, int nrows, int box_w, CUtensorMap &out) {
+    using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static std::mutex mu;
+    static Encode encode = nullptr;
+    static bool looked_up = false;
+    static std::unordered_map<TmapKey, CUtensorMap, TmapHash> cache;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!looked_up) {
+        looked_up = true;
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            encode = (Encode)fn;
+        else
+            (void)cudaGetLastError();
+    }
+    if (!encode) return false;
+    const TmapKey key{w, row_bytes, nrows, box_w};
+    auto it = cache.find(key);
+    if (it != cache.end()) { out = it->second; return true; }
+    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)nrows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)box_w, (cuuint32_t)cq_mma2::kTileRows};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() >= 8192) cache.clear();
+    cache.emplace(key, out);
+    return true;
+}
+
+// Shape rules: K a whole number of 32-chunk groups (so the tree needs no padding; row sizes are then multiples of 16
+// bytes, as the tensor map wants), a 16-byte aligned matrix, the activation tables of K fit in shared memory beside the
+// rings, and - unless forced - at least two (tile, warp) work items per SM.  A matrix with many tiles (the vocabulary head) gives
+// every warp whole tiles; otherwise the groups of a tile are spread over `spw` warps of a CTA.
+template <int TYPE>
+bool launch_mma2(const void *w, const void *y, void *dst, int out_kind, int K, int N, int sy, int sd, int B, cudaStream_t st, bool forced) {
+    static KernelEntry ke_whole{(const void *)gemv_mma2_kernel<TYPE, false>}, ke_split{(const void *)gemv_mma2_kernel<TYPE, true>};
+    using F = cq_mma2::Fmt<TYPE>;
+    const int unit_elems = F::UNIT_BLOCKS * 32;
+    const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
+    if (K % (8 * unit_elems) != 0 || (uintptr_t)w % 16 != 0 || row_bytes % 16 != 0) return false;
+    const DevInfo di = dev_info();
+    const int nunits = K / unit_elems, nblk = nunits * F::UNIT_BLOCKS, ngroups = nunits / 8;
+    const int ntiles = (N + cq_mma2::kTileRows - 1) / cq_mma2::kTileRows;
+    int warps = 0, grid = 0, smem = 0, spw = 1;
+    const bool split = ngroups >= 2 && ntiles < 16 * di.sms;
+    if (split)      // warps per tile: the largest divisor of the group count that a CTA of 8 warps holds
+        for (int dv = cq_mma2::kMaxWarps; dv >= 1; --dv)
+            if (ngroups % dv == 0) { spw = dv; break; }
+    // Too little parallel work, or a shape where the other kernels were measured faster (B200, 8 rows, one launch after an
+    // L2 flush, us: 14336 -> 4096 Q4_K 25.8 against 37.4, Q6_K 37.1 / 39.0, Q8_0 32.9 / 37.1; 4096 -> 14336 Q4_K 18.1 / 25.7,
+    // Q6_K 28.3 / 35.6, but Q8_0 23.7 / 20.1 (dp4a); 4096 -> 4096 Q4_K 16.7 / 12.9): leave those to them.
+    if (!forced && (ntiles * spw < 8 * di.sms || (split && TYPE == CQ_Q8_0 && K < 8192))) return false;
+    if (split) {
+        int slots = cq_mma2::kMaxWarps / spw;
+        // keep at least about one CTA per SM: fewer tile slots per CTA when the tiles are few
+        while (slots > 1 && (ntiles + slots - 1) / slots < di.sms) --slots;
+        warps = slots * spw;
+        smem = cq_mma2::smem_bytes<TYPE>(nblk, warps, cq_mma2::red_floats(slots, ngroups));
+        if (smem > di.smem_optin) return false;
+        const int cps = 2 * (smem + 1024) <= 228 * 1024 ? 2 : 1;
+        grid = (ntiles + slots - 1) / slots;
+        if (grid > di.sms * cps) grid = di.sms * cps;
+    } else {
+        // Warps per CTA (5..8) and grid: the pair that leaves the fewest idle warp-rounds (a warp runs whole tiles, so the
+        // kernel lasts as long as the warp with the most tiles); more warps win ties.
+        double best_eff = -1.0;
+        for (int wv = cq_mma2::kMaxWarps; wv >= 5; --wv) {
+            const int smem_w = cq_mma2::smem_bytes<TYPE>(nblk, wv);
+            if (smem_w > di.smem_optin) continue;
+            const int cps = 2 * (smem_w + 1024) <= 228 * 1024 ? 2 : 1;
+            int grid_w = (ntiles + wv - 1) / wv;
+            if (grid_w > di.sms * cps) grid_w = di.sms * cps;
+            const long long slots = (long long)grid_w * wv;
+            const long long rounds = (ntiles + slots - 1) / slots;
+            // idle warp-rounds count, and so do warp slots of the machine that the grid leaves empty
+            const double eff = (double)ntiles / (double)(rounds * (long long)di.sms * cps * wv);
+            if (eff > best_eff + 1e-9) { best_eff = eff; warps = wv; grid = grid_w; smem = smem_w; }
+        }
+        if (warps == 0) return false;
+    }
+    if (record_plan(split ? kPlanMma2Split : kPlanMma2, cq_mma2::kTileRows, grid, warps * 32)) return true;
+    CUtensorMap tmap;
+    if (!weight_tensor_map(w, row_bytes, N, F::RS, tmap)) return false;
+    if (split) {
+        ensure_smem_attr(&ke_split);
+        cq_launch_k(gemv_mma2_kernel<TYPE, true>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,
+                    nunits, N, sy, sd, B, spw);
+    } else {
+        ensure_smem_attr(&ke_whole);
+        cq_launch_k(gemv_mma2_kernel<TYPE, false>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,
+                    nunits, N, sy, sd, B, 1);
+    }
+    return cq_check_launch("gemv (tensor core, warp tiles)");
 }
 
 // ---- two matrices that read the same single activation row, one launch (decode: [wq|wk] in Q4_K and wv in Q6_K) ----
@@ -225,7 +355,15 @@ extern "C" void cq_mmvq(int wtype, int act, int out_kind, const void *vx, const 
     auto run = [&](int j0, int bb) -> bool {
         const uint8_t *yy = (const uint8_t *)vy + (size_t)j0 * stride_col_y * CQ_Q8_BYTES;
         uint8_t *dd = (uint8_t *)dst + (size_t)j0 * stride_col_dst * elem_bytes(out_kind);
-        if (!cpu_act && bb >= (g_mma_min_batch > 0 ? g_mma_min_batch : mma_default_min_batch(wtype))) {
+        if (!cpu_act && g_mma_kernel != 1 && bb >= (g_mma_min_batch > 0 ? g_mma_min_batch : mma2_default_min_batch(wtype))) {
+            const bool forced = g_mma_kernel == 2;
+            switch (wtype) {
+            case CQ_Q8_0: if (launch_mma2<CQ_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st, forced)) return true; break;
+            case CQ_Q4_K: if (launch_mma2<CQ_Q4_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st, forced)) return true; break;
+            case CQ_Q6_K: if (launch_mma2<CQ_Q6_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st, forced)) return true; break;
+            }
+        }
+        if (!cpu_act && g_mma_kernel != 2 && bb >= (g_mma_min_batch > 0 ? g_mma_min_batch : mma_default_min_batch(wtype))) {
             switch (wtype) {
             case CQ_Q8_0: if (launch_mma<CQ_Q8_0>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)) return true; break;
             case CQ_Q4_K: if (launch_mma<CQ_Q4_K>(vx, yy, dd, out_kind, ncols_x, nrows_x, stride_col_y, stride_col_dst, bb, st)) return true; break;
@@ -320,6 +458,9 @@ extern "C" int cq_mmvq_plan(int wtype, int act, int ncols_x, int nrows_x, int b_
 
 // Rows from which the tensor-core GEMV replaces the dp4a one (0: per-format default; 9 or more: never).  Same bits either way.
 extern "C" void cq_set_mma_min_batch(int rows) { g_mma_min_batch = rows < 0 ? 0 : rows; }
+// Which tensor-core GEMV may run: 0 automatic, 1 only the CTA-shared kernel, 2 the warp-private kernel wherever K is a
+// whole number of 2048-element groups (1024 for Q8_0) and its activation tables fit in shared memory.  Same bits either way.
+extern "C" void cq_set_mma_kernel(int which) { g_mma_kernel = which < 0 || which > 2 ? 0 : which; }
 
 // 1 if any GEMV launch on the current device gave up waiting for a staged copy (synchronises the device).
 extern "C" int cq_device_timeout_flag(void) {

@@ -93,7 +93,7 @@ __device__ __forceinline__ void gemv_body(const uint8_t *__restrict__ w, const M
         }
         const float tot = cq_warp_reduce_many<NV>(v);
         float *rbuf = red + (it & 1) * nwarps * NV;
-        if ((lane & (32 / NV - 1)) == 0) rbuf[warp * NV + lane / (32 / NV)] = tot;
+        if (lane < NV) rbuf[warp * NV + cq_reduce_slot<NV>(lane)] = tot;
         const int failed = __syncthreads_or(!ok);
         if (failed) {       // uniform across the CTA: record, drain, leave
             if (tid == 0) {

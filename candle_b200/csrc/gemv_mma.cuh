@@ -8,7 +8,7 @@
 // Results are bit-identical to the dp4a GEMV: the f32 value of every (row, column, chunk) is computed with the same
 // operations as ChunkW<TYPE>::dot (integer parts are exact either way; int -> float conversions are exact in both), and
 // the chunk values of one output are added in the same tree: within a group of 32 chunks - the chunks one warp of the
-// dp4a kernel owns - the xor butterfly (l, l^16), (l, l^8), ... and then the groups in index order.  So a row gives the
+// dp4a kernel owns - the xor butterfly (l, l^1), (l, l^2), ... and then the groups in index order.  So a row gives the
 // same bits for any batch size, which candle's own `qmm_batch` test asks of batches 2, 4 and 6
 // (candle-core/tests/quantized_tests.rs:224-259), and for any sharding of the rows.
 //
@@ -325,17 +325,18 @@ __device__ __forceinline__ void gemv_mma_body(const uint8_t *__restrict__ wgt, c
             return;
         }
         if (w == 0 && item + S < nitems) issue(item + S);
-        // tree over the 32 chunk values of each of the 128 outputs: two threads per output (even / odd leaves)
+        // tree over the 32 chunk values of each of the 128 outputs (balanced, natural order: the dp4a kernel's butterfly
+        // 1, 2, 4, 8, 16): two threads per output, one per half of the leaves
         {
             const int o = tid >> 1, e = tid & 1;
             float x[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) x[i] = vbuf[(2 * i + e) * kValStride + o];
+            for (int i = 0; i < 16; ++i) x[i] = vbuf[(16 * e + i) * kValStride + o];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = x[i] + x[i + 8];
+            for (int i = 0; i < 8; ++i) x[i] = x[2 * i] + x[2 * i + 1];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) x[i] = x[i] + x[i + 4];
-            x[0] = x[0] + x[2]; x[1] = x[1] + x[3];
+            for (int i = 0; i < 4; ++i) x[i] = x[2 * i] + x[2 * i + 1];
+            x[0] = x[0] + x[1]; x[1] = x[2] + x[3];
             float tot = x[0] + x[1];
             tot = tot + __shfl_xor_sync(0xffffffffu, tot, 1);
             if (e == 0) {

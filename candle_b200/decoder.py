@@ -117,10 +117,16 @@ class LlamaShapedDecoder:
         self._graph = None
         self.fuse_quantize = True       # decode steps: producers store Q8_1 containers directly
         self._att_scratch = None        # split-context attention: partial results and arrival counters
+        self.tap = None                 # tests set a dict here: forward() then records copies of its intermediate tensors
         if world > 1:       # ranks build their shards at different speeds: line up before the first gather, whose polls are bounded
             import torch.distributed as dist
             torch.cuda.synchronize(self.device)
             dist.barrier(group=group)
+
+    def _rec(self, key: str, t: torch.Tensor) -> None:
+        """Record a copy of an intermediate tensor when a test has set `self.tap` to a dict (no-op otherwise)."""
+        if self.tap is not None:
+            self.tap[key] = t.detach().clone()
 
     # ---- glue -------------------------------------------------------------------------------------------------
     def _norm(self, x: torch.Tensor, delta, w: torch.Tensor) -> torch.Tensor:
@@ -186,17 +192,22 @@ class LlamaShapedDecoder:
         with torch.cuda.device(self.device):
             x = self.tok_embd.index_select(0, tokens.reshape(-1))                       # [R, d], private to this call
             delta = None                                                                # residual not yet added to x
-            for L in self.layers:
+            for li, L in enumerate(self.layers):
+                self._rec(f"{li}.x_in", x)
+                if delta is not None:
+                    self._rec(f"{li}.delta_in", delta)
                 if fused:
                     h = self._norm_q8(x, delta, L.attn_norm)
                     qk, v = L.wqk.forward_q8_1_pair(L.wv, h)
                 else:
                     h = self._norm(x, delta, L.attn_norm)
                     qk, v = L.wqk.forward(h), L.wv.forward(h)                           # [R, q_cols + kv_cols], [R, kv_cols]
+                self._rec(f"{li}.h_attn", h), self._rec(f"{li}.qk", qk), self._rec(f"{li}.v", v)
                 lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), self.cos.data_ptr(),
                                          self.sin.data_ptr(), self.pos.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
                                          B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, q_cols + kv_cols, q_cols + kv_cols,
                                          kv_cols, st)
+                self._rec(f"{li}.q_rot", qk)
                 if fused:
                     att = torch.empty((R, q_cols // 32 * 36), **u8)
                     self._attention(qk, L, B, T, att, True)
@@ -209,14 +220,20 @@ class LlamaShapedDecoder:
                 else:
                     att = torch.empty((R, q_cols), **f32)
                     self._attention(qk, L, B, T, att, False)
+                    self._rec(f"{li}.att", att)
                     delta = L.wo.forward(self.gather(att))
+                    self._rec(f"{li}.x_mid", x), self._rec(f"{li}.wo", delta)
                     h = self._norm(x, delta, L.ffn_norm)
                     gu = L.gate_up.forward(h)
                     a = torch.empty((R, f_l), **f32)
                     lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R, f_l, st)
+                    self._rec(f"{li}.h_ffn", h), self._rec(f"{li}.gu", gu), self._rec(f"{li}.act", a)
                     delta = self.gather(L.down.forward(self.gather(a)))
+                    self._rec(f"{li}.down", delta)
+            self._rec("final.x_in", x), self._rec("final.delta_in", delta)
             h = (self._norm_q8 if fused else self._norm)(x, delta, self.out_norm)
             capi.check("decoder glue")
+            self._rec("final.h", h)
             last = h.view(B, T, -1)[:, -1, :].contiguous()
             logits = self.output.forward_q8_1(last) if fused else self.output.forward(last)     # [B, vocab / world]
             self.last_logits = logits       # this rank's vocabulary slice, last position (read by tests)

@@ -110,10 +110,12 @@ class MoeShapedDecoder:
         self._pos_host = 0      # host copy of pos: positions are checked against max_pos before anything is launched
         self._graph = None
         self._att_scratch = None
+        self.tap = None                 # tests set a dict here: forward() then records copies of its intermediate tensors
         self.hq_l, self.hkv_l = cfg.n_heads, cfg.n_kv_heads      # attention is replicated: every rank owns all heads
 
     # the norm and attention helpers are those of the dense harness
     _norm = LlamaShapedDecoder._norm
+    _rec = LlamaShapedDecoder._rec
     reset = LlamaShapedDecoder.reset
     check = LlamaShapedDecoder.check
     _claim_positions = LlamaShapedDecoder._claim_positions
@@ -139,8 +141,8 @@ class MoeShapedDecoder:
             lib.cq_attention_f32(qkv.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
                                  B, T, cfg.n_heads, cfg.n_kv_heads, hd, cfg.max_pos, scale, stride, st)
 
-    def _moe(self, h: torch.Tensor, L) -> torch.Tensor:
-        """fused_moe.rs:222-301 for rows h [R, d] -> [R, d]."""
+    def _moe(self, h: torch.Tensor, L, key: str = "") -> torch.Tensor:
+        """fused_moe.rs:222-301 for rows h [R, d] -> [R, d].  `key`: prefix of the recorded intermediates (tests)."""
         cfg, lib = self.cfg, capi.lib()
         R, k, f = h.shape[0], cfg.experts_per_tok, cfg.expert_ffn
         st = torch.cuda.current_stream(self.device).cuda_stream
@@ -148,6 +150,7 @@ class MoeShapedDecoder:
         ids = torch.empty((R, k), dtype=torch.int32, device=self.device)
         w = torch.empty((R, k), dtype=torch.float32, device=self.device)
         lib.cq_moe_route_f32(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), R, cfg.experts, k, 1 if cfg.norm_topk_prob else 0, st)
+        self._rec(key + "router_logits", logits), self._rec(key + "ids", ids), self._rec(key + "route_w", w)
         local = ids - self.e0 if self.world > 1 else ids           # other ranks' experts fall outside [0, e_local): skipped
         zero = self.world > 1
         a = torch.empty((R, k, f), dtype=torch.float32, device=self.device)
@@ -161,6 +164,7 @@ class MoeShapedDecoder:
             gu = L.gate_up.indexed_moe_forward(h.view(R, 1, -1), local, zero_init=zero)           # [R, k, 2f]
             lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
             y = L.down.indexed_moe_forward(a, local, zero_init=zero)                              # [R, k, d]
+        self._rec(key + "gu", gu.view(R, k, 2 * f)), self._rec(key + "act", a), self._rec(key + "down", y)
         if self.world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)                            # one value plus zeros: exact
         return (y * w.unsqueeze(-1)).sum(dim=1)
@@ -176,21 +180,31 @@ class MoeShapedDecoder:
         with torch.cuda.device(self.device):
             x = self.tok_embd.index_select(0, tokens.reshape(-1))
             delta = None
-            for L in self.layers:
+            for li, L in enumerate(self.layers):
+                self._rec(f"{li}.x_in", x)
+                if delta is not None:
+                    self._rec(f"{li}.delta_in", delta)
                 h = self._norm(x, delta, L.attn_norm)
                 qkv = L.wqkv.forward(h)                                                           # [R, stride]
+                self._rec(f"{li}.h_attn", h), self._rec(f"{li}.qkv", qkv)
                 base = qkv.data_ptr()
                 lib.cq_qknorm_rope_store_kv_f32(base, base + 4 * q_cols, base + 4 * (q_cols + kv_cols), L.q_norm.data_ptr(),
                                                 L.k_norm.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
                                                 L.k_cache.data_ptr(), L.v_cache.data_ptr(), B, T, cfg.n_heads, cfg.n_kv_heads, hd,
                                                 cfg.max_pos, stride, stride, stride, cfg.rms_eps, 1, st)
+                self._rec(f"{li}.q_rot", qkv)
                 att = torch.empty((R, q_cols), dtype=torch.float32, device=self.device)
                 self._attention(qkv, L, B, T, att)
+                self._rec(f"{li}.att", att)
                 delta = L.wo.forward(att)
+                self._rec(f"{li}.x_mid", x), self._rec(f"{li}.wo", delta)
                 h = self._norm(x, delta, L.ffn_norm)
-                delta = self._moe(h, L)
+                delta = self._moe(h, L, f"{li}.")
+                self._rec(f"{li}.h_ffn", h), self._rec(f"{li}.moe", delta)
+            self._rec("final.x_in", x), self._rec("final.delta_in", delta)
             h = self._norm(x, delta, self.out_norm)
             capi.check("moe decoder glue")
+            self._rec("final.h", h)
             last = h.view(B, T, cfg.d_model)[:, -1, :].contiguous()
             logits = self.output.forward(last)
             self.last_logits = logits       # last position (read by tests)

@@ -305,6 +305,10 @@ int cq_mmvq_pair_q4k_q6k(const void *wa, int nrows_a, float *dst_a, const void *
  * Q8_1 activations (0: per-format default, which is 5 for Q4_K / Q6_K and never for Q8_0; 9: never).  Both kernels
  * produce the same bits, so the choice only affects speed. */
 void cq_set_mma_min_batch(int rows);
+/* Which tensor-core GEMV may run for those rows: 0 (default) automatic - the warp-private kernel (gemv_mma2.cuh) for
+ * matrices with enough 16-row tiles, the CTA-shared one (gemv_mma.cuh) otherwise; 1: only the CTA-shared kernel; 2: the
+ * warp-private kernel whenever its shape rules hold.  All GEMV kernels produce the same bits. */
+void cq_set_mma_kernel(int which);
 
 /* De-quantize n_rows rows of k elements (replaces candle-kernels/src/quantized.cu:759-1460 `dequantize_block_*`), and
  * the gathered-row form behind QTensor::embedding.  cq_get_rows_bad_id: 1 if an id was out of range since the last query
@@ -318,7 +322,7 @@ int cq_get_rows_bad_id(void);
 void cq_convert_plain(int ggml_dtype, const void *src, void *out, int out_kind, int64_t n, void *stream);
 
 /* Read-only: what cq_mmvq would launch for these arguments, nothing is launched.  out[0] kernel (0 staged dp4a GEMV,
- * 1 tensor-core GEMV), out[1] weight rows per staged batch (rows per CTA for the tensor-core kernel), out[2] grid,
+ * 1 tensor-core GEMV with CTA-shared items, 2 tensor-core GEMV with warp-private tiles, 3 the same with the groups of a tile spread over the warps of a CTA), out[1] weight rows per staged batch (rows per CTA for the tensor-core kernel), out[2] grid,
  * out[3] threads per CTA.  Returns 0, or -1 when cq_mmvq would reject the arguments.  No counterpart in the reference
  * (its launch shape is fixed: one CTA per weight row, candle-kernels/src/mmvq_gguf.cu:915-1008); tests use it to show
  * which kernel instantiations a parity case exercised. */

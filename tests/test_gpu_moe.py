@@ -261,18 +261,21 @@ def test_expert_parallel_tokens_match_single_gpu(tmp_path):
 
 @pytest.mark.parametrize("tname", ["q4_k", "q6_k"])
 @pytest.mark.parametrize("with_weights", [False, True])
-def test_grouped_tensor_core_gemm_matches_cpu_arithmetic(oracle, cuda_dev, tname, with_weights):
+@pytest.mark.parametrize("e,n,k", [(5, 192, 512), (16, 512, 256), (16, 512, 512), (6, 2048, 768)])
+def test_grouped_tensor_core_gemm_matches_cpu_arithmetic(oracle, cuda_dev, tname, with_weights, e, n, k):
     """cq_moe_prefill_gemm: pairs sorted by expert, experts with more than one tile, with an empty expert, and with ids of
     another rank's experts (skipped).  Oracle: the reference CPU matmul (Q8_K activations) of each pair's expert."""
     from candle_b200.moe import moe_prefill_gemm
     wt = TYPES[tname]
-    e, n, k, topk = 5, 192, 512, 2
+    topk = 2       # (16, 512, 256): one super-block per row, many experts with few pairs each - the tiny decoder's shape
     wq = _experts(oracle, wt, e, n, k, seed=11)
     rng = np.random.default_rng(12)
     tokens = 170
     # expert 0 gets 300 pairs (three tiles), expert 2 none, the others a few; two pairs belong to "another rank" (-1, 7)
     flat = np.concatenate([np.zeros(300, np.int32), np.full(17, 1, np.int32), np.full(20, 3, np.int32), np.full(1, 4, np.int32),
-                           np.array([-1, 7], np.int32)])
+                           np.array([-1, e + 2], np.int32)])
+    if e > 5:       # spread a part of expert 0's pairs over the further experts (expert 2 stays empty)
+        flat[200:300] = rng.integers(5, e, size=100).astype(np.int32)
     assert flat.size == tokens * topk
     rng.shuffle(flat)
     order = np.argsort(flat, kind="stable").astype(np.int32)        # sorted_token_ids
