@@ -11,8 +11,9 @@ Q8_0} x batch {1, 2, 4, 8}: 60 activation-quantize + GEMV pairs.  Weights are se
 Metric: achieved HBM bandwidth in GB/s = algorithmic bytes of the step (weights once + f32 activations in +
 f32 outputs, per GEMV) / device time of the step.
   value     : inputs resident in HBM, the step replayed as one CUDA graph, CUDA-event timed.
-  e2e       : the same step through the public API (QMatMul.forward) with activations starting in pinned host
-              memory and results copied back to pinned host memory inside the timed region.
+  e2e       : the same step through the host-buffer entry point (QMatMul.forward_host = cqh_qmatmul_forward_host):
+              activations start in pinned host memory and results end in pinned host memory; upload, quantize, GEMV and
+              copy-back are inside the timed region (with several GPUs: copy, QMatMul.forward, gather, copy).
   roofline  : the GEMV kernels alone (no quantize launches), CUDA-event timed in this run.
   cpu_baseline : the reference's CPU algorithm (oracle port, AVX2, host threads = physical cores) on the same sweep.
 Further objects of the same JSON line (reported beside the headline, not part of `value`):
@@ -57,7 +58,50 @@ def gemv_bytes(tname: str, k: int, n: int, b: int) -> float:
     return n * k * BYTES_PER_ELEM[tname] + b * k * 4 + b * n * 4
 
 
-DRAM_TRAFFIC_RATIO = 1.014      # measured: (295.52 + 4.57) MB of DRAM traffic for 296.03 MB algorithmic
+# dram__bytes_read + dram__bytes_write over algorithmic bytes, one ncu-captured launch per (format, K, N, rows)
+# (profiles/gemv_sweep_dram_traffic.md).  Batches 2 and 4 take the figure of batch 1 (same kernel family).
+DRAM_TRAFFIC_RATIO = {
+    ("Q4K", 4096, 4096, 1): 0.998,
+    ("Q4K", 4096, 4096, 8): 0.979,
+    ("Q4K", 4096, 1024, 1): 0.998,
+    ("Q4K", 4096, 1024, 8): 0.958,
+    ("Q4K", 4096, 14336, 1): 0.998,
+    ("Q4K", 4096, 14336, 8): 0.984,
+    ("Q4K", 14336, 4096, 1): 0.999,
+    ("Q4K", 14336, 4096, 8): 0.987,
+    ("Q4K", 4096, 128256, 1): 1.0,
+    ("Q4K", 4096, 128256, 8): 0.994,
+    ("Q6K", 4096, 4096, 1): 0.999,
+    ("Q6K", 4096, 4096, 8): 0.986,
+    ("Q6K", 4096, 1024, 1): 0.999,
+    ("Q6K", 4096, 1024, 8): 0.973,
+    ("Q6K", 4096, 14336, 1): 0.999,
+    ("Q6K", 4096, 14336, 8): 0.989,
+    ("Q6K", 14336, 4096, 1): 0.999,
+    ("Q6K", 14336, 4096, 8): 0.991,
+    ("Q6K", 4096, 128256, 1): 1.001,
+    ("Q6K", 4096, 128256, 8): 1.024,
+    ("Q8_0", 4096, 4096, 1): 0.999,
+    ("Q8_0", 4096, 4096, 8): 0.988,
+    ("Q8_0", 4096, 1024, 1): 0.999,
+    ("Q8_0", 4096, 1024, 8): 0.975,
+    ("Q8_0", 4096, 14336, 1): 0.999,
+    ("Q8_0", 4096, 14336, 8): 0.992,
+    ("Q8_0", 14336, 4096, 1): 0.999,
+    ("Q8_0", 14336, 4096, 8): 0.993,
+    ("Q8_0", 4096, 128256, 1): 1.0,
+    ("Q8_0", 4096, 128256, 8): 0.998,
+}
+
+
+def step_traffic_bytes(world: int = 1) -> float:
+    """DRAM bytes of one step and GPU from the measured per-launch ratios."""
+    tot = 0.0
+    for b in BATCHES:
+        for t in TYPE_NAMES:
+            for (k, n) in SHAPES:
+                tot += gemv_bytes(t, k, n // world, b) * DRAM_TRAFFIC_RATIO[(t, k, n, 8 if b == 8 else 1)]
+    return tot
 
 
 def step_bytes(batches=BATCHES) -> float:
@@ -519,13 +563,17 @@ def run_gpu(args):
     d2h = sum(b * n * 4 for (b, _, _, n) in order)
 
     def step_e2e():
+        if world == 1:      # host buffers in, host buffers out: one library call per matmul, copy-backs overlap the next call
+            last = None
+            for (b, t, k, n) in order:
+                last = mats[(t, k, n)]
+                last.forward_host(h_x[(k, b)], h_y[(n, b)])
+            last.host_flush()
+            return
         for (b, t, k, n) in order:
             d_x[(k, b)].copy_(h_x[(k, b)], non_blocking=True)
             y = mats[(t, k, n)].forward(d_x[(k, b)], out=outs[(n, b)])
-            if world > 1:
-                h_y[(n, b)].copy_(gather(y), non_blocking=True)
-            else:
-                h_y[(n, b)].copy_(y, non_blocking=True)
+            h_y[(n, b)].copy_(gather(y), non_blocking=True)
 
     ms_e2e = timed(step_e2e, args.steps, args.warmup, False)
     if gather is not None and hasattr(gather, "check"):
@@ -579,12 +627,12 @@ def run_gpu(args):
         "e2e": {"value": total_bytes / ms_e2e / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
         "roofline": {"bound": "hbm", "achieved": gemv_gbs / world, "peak": peak, "unit": "GB/s",
-                     "frac": gemv_gbs / world / peak, "traffic": DRAM_TRAFFIC_RATIO * total_bytes / world,
-                     "traffic_source": "bytes per step and GPU: algorithmic bytes x 1.014, the ratio of dram__bytes_read+write to "
-                                       "algorithmic bytes in the ncu capture of the Q4_K 4096->128256 launch "
-                                       "(profiles/gemv_staged_q4k_4096x128256_b1.md); the 60 launches of a step are too many to capture",
+                     "frac": gemv_gbs / world / peak, "traffic": step_traffic_bytes(world),
+                     "traffic_source": "bytes per step and GPU: every launch's algorithmic bytes x the dram__bytes_read+write / "
+                                       "algorithmic ratio of that (format, shape) in a one-launch ncu capture at 1 and 8 rows "
+                                       "(profiles/gemv_sweep_dram_traffic.md: 0.96 - 1.02; rows 2 and 4 take the 1-row ratio)",
                      "peak_source": peak_src,
-                     "kernel": "gemv_staged_kernel / gemv_mma_kernel (all 60 GEMV launches of the step, quantize launches excluded)",
+                     "kernel": "gemv_staged_kernel / gemv_mma_kernel / gemv_mma2_kernel (all 60 GEMV launches of the step, quantize launches excluded)",
                      "ms_per_step": ms_gemv, "per_gpu": True},
         "clocks": clocks,
         "decode": {"model": "Llama-3-8B-shaped, Q4_K_M mix, random weights", "prompt": 512, "steps": 256,
@@ -653,6 +701,38 @@ def run_case(args):
     print(json.dumps({"case": args.case, "plan_kernel_rows_grid_threads": list(plan), "us": [round(v, 1) for v in times],
                       "algorithmic_bytes": nbytes, "best_GBps": round(nbytes / best / 1e3, 1),
                       "isolated_us": round(iso_us, 2), "isolated_GBps": round(nbytes / iso_us / 1e3, 1)}))
+
+
+def run_traffic_sweep(args):
+    """Profiling helper: every (format, shape) GEMV of the sweep once at batch 1 and once at batch 8, in a fixed order that
+    is printed as JSON - the launch list an `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum,gpu__time_duration.sum
+    -k regex:gemv_` capture of this command maps onto, one captured launch per printed case (--traffic-types limits the
+    formats so that a capture stays small)."""
+    import torch
+    from candle_b200 import capi
+    from candle_b200.quantized import GgmlDType
+    from candle_b200.synth import random_blocks
+    dev = torch.device("cuda:0")
+    L = capi.lib()
+    s = torch.cuda.current_stream().cuda_stream
+    cases = []
+    for t in args.traffic_types.split(","):
+        for (k, n) in SHAPES:
+            w = random_blocks(GgmlDType[t], n, k, seed=1, device=dev)
+            kp = capi.pad(k, 512)
+            for b in (1, 8):
+                x = torch.randn((b, k), device=dev)
+                y = torch.empty((b, kp // 32 * 36), dtype=torch.uint8, device=dev)
+                out = torch.empty((b, n), device=dev)
+                L.cq_quantize_act(x.data_ptr(), capi.F32, y.data_ptr(), k, kp, b, capi.ACT_Q8_1, s)
+                L.cq_mmvq(int(GgmlDType[t]), capi.ACT_Q8_1, capi.F32, w.data_ptr(), y.data_ptr(), out.data_ptr(), k, n, kp // 32, n, b, s)
+                torch.cuda.synchronize()
+                plan = (__import__("ctypes").c_int * 4)()
+                L.cq_mmvq_plan(int(GgmlDType[t]), capi.ACT_Q8_1, k, n, b, plan)
+                cases.append({"type": t, "k": k, "n": n, "b": b, "algorithmic_bytes": gemv_bytes(t, k, n, b), "plan": list(plan)})
+            del w
+    capi.check("traffic sweep")
+    print(json.dumps({"traffic_sweep": cases}))
 
 
 def run_prefill_case(args):
@@ -806,6 +886,8 @@ def main():
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
     ap.add_argument("--prefill-type", default="Q4K", choices=["Q4K", "Q6K"], help="weight format of --prefill-case")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
+    ap.add_argument("--traffic-sweep", action="store_true", help="profile helper: each (format, shape) GEMV once at batch 1 and 8")
+    ap.add_argument("--traffic-types", default="Q4K,Q6K,Q8_0", help="with --traffic-sweep: comma-separated formats")
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -825,6 +907,8 @@ def main():
             fn(ctypes.c_int(rb_), ctypes.c_int(cps_))
         torch.cuda.set_device(0)
         print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
+    elif args.traffic_sweep:
+        run_traffic_sweep(args)
     elif args.prefill_case:
         run_prefill_case(args)
     elif args.moe_decode_case:

@@ -42,8 +42,8 @@ def _headers_mtime() -> float:
     return max(os.path.getmtime(h) for h in hs) if hs else 0.0
 
 
-def _compile(src: str, verbose: bool, extra: list[str]) -> str:
-    obj = os.path.join(OBJ, os.path.basename(src) + ".o")
+def _compile(src: str, verbose: bool, extra: list[str], obj_dir: str = OBJ) -> str:
+    obj = os.path.join(obj_dir, os.path.basename(src) + ".o")
     newest = max(os.path.getmtime(src), _headers_mtime())
     if os.path.exists(obj) and os.path.getmtime(obj) >= newest and not extra:
         return obj
@@ -56,13 +56,16 @@ def _compile(src: str, verbose: bool, extra: list[str]) -> str:
     return obj
 
 
-def build(verbose: bool = False, ptxas_info: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
-    os.makedirs(LIBDIR, exist_ok=True)
-    extra = ["-Xptxas", "-v"] if ptxas_info else []
+def build(verbose: bool = False, ptxas_info: bool = False, defines: tuple = (), obj_dir: str = OBJ, lib_path: str = LIB) -> str:
+    """`defines`: extra -D macros, e.g. ("CQ_EXPERIMENT",) for a profiling build with the tuning hooks compiled in; give
+    such a build its own `obj_dir` and `lib_path` so that it never replaces the default library."""
+    os.makedirs(obj_dir, exist_ok=True)
+    os.makedirs(os.path.dirname(lib_path), exist_ok=True)
+    extra = (["-Xptxas", "-v"] if ptxas_info else []) + [f"-D{d}" for d in defines]
     srcs = _sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile(s, verbose or ptxas_info, extra), srcs))
+        objs = list(ex.map(lambda s: _compile(s, verbose or ptxas_info, extra, obj_dir), srcs))
+    LIB = lib_path
     if not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         cmd = [nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -8,7 +8,7 @@
 // warps: no CTA barrier, no shared-memory reduction.  Per warp a ring of shared-memory stages holds one "unit" of the 16
 // rows each (a 256-element super-block; four 32-element blocks for Q8_0).  A stage is filled by ONE tiled TMA copy
 // (cp.async.bulk.tensor.2d over a byte view [rows, row_bytes] of the weight matrix, box 16 rows x the 16-byte aligned
-// window that covers the unit; this GPU's memory only, no multicast), completion counted on the stage's mbarrier with
+// window that covers the unit; this GPU's own memory, every copy private to its CTA), completion counted on the stage's mbarrier with
 // bounded waits, a few units ahead of the arithmetic.  (One plain bulk copy per row segment of 144 bytes was measured at
 // 2 TB/s: the copy engine's cost per request, not the bytes, set the pace.)  The Q8_1 activations of all 8 columns (int8
 // values and a table of their scales) sit in shared memory for the whole kernel, read once per CTA.

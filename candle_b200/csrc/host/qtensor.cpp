@@ -320,6 +320,101 @@ extern "C" const void *cqh_qtensor_device_ptr(void *handle) {
     return (*(std::shared_ptr<QTensor> *)handle)->storage().device_ptr();
 }
 
+// ---- QMatMul::forward over HOST buffers ------------------------------------------------------------------------
+// Where candle moves a CPU tensor to the device, multiplies and moves the result back (Tensor::to_device around
+// QMatMul::forward), this entry point does the three steps itself: host activations -> a device staging buffer (on the
+// caller's stream), the ordinary forward, result -> host on a copy stream of the library, so that the copy-back of one
+// call overlaps the next call's upload and arithmetic.  Per device a ring of four staging slots; a slot's buffers are
+// reused only after its copy-back has finished (the caller's stream waits on that event).  cqh_qmatmul_host_flush makes
+// the caller's stream wait for every copy-back still in flight: synchronise that stream afterwards and the host outputs
+// are complete.  Pinned host memory is needed for the copies to be asynchronous.
+namespace {
+constexpr int kHostSlots = 4;
+struct HostSlot {
+    void *x = nullptr, *y = nullptr;
+    size_t cap_x = 0, cap_y = 0;
+    cudaEvent_t gemv_done = nullptr, d2h_done = nullptr;
+    bool pending = false;
+};
+struct HostRing {
+    HostSlot s[kHostSlots];
+    int next = 0;
+    cudaStream_t copy_stream = nullptr;
+};
+std::mutex g_host_mu;
+std::map<int, HostRing> g_host_ring;
+
+void grow(void *&p, size_t &cap, size_t need, cudaStream_t copy_stream) {
+    if (cap >= need) return;
+    if (p) {        // nothing may still read or write the old buffer
+        cuda_check(cudaStreamSynchronize(copy_stream), "forward_host: synchronising the copy stream");
+        cuda_check(cudaDeviceSynchronize(), "forward_host: synchronising before a staging buffer grows");
+        cudaFree(p);
+        p = nullptr;
+    }
+    const size_t c = pad(need + need / 4, 1 << 16);
+    cuda_check(cudaMalloc(&p, c), "forward_host: staging cudaMalloc");
+    cap = c;
+}
+}  // namespace
+
+extern "C" int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_dtype, const int64_t *dims, int ndims,
+                                        void *host_out, void *stream) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        QMatMul mm(t);
+        if (ndims < 2) throw Error("input tensor has only one dimension");
+        if (!host_x || !host_out) throw Error("forward_host: null host pointer");
+        const auto &sh = t->shape();
+        size_t rows = 1;
+        for (int i = 0; i + 1 < ndims; ++i) rows *= (size_t)dims[i];
+        const size_t k = (size_t)dims[ndims - 1], n = (size_t)sh[0], es = dtype_size((DType)x_dtype);
+        if (rows == 0) return;
+        const int dev = t->storage().device();
+        DeviceGuard g(dev);
+        cudaStream_t st = (cudaStream_t)stream;
+        std::lock_guard<std::mutex> lk(g_host_mu);
+        HostRing &ring = g_host_ring[dev];
+        if (!ring.copy_stream) {
+            cuda_check(cudaStreamCreateWithFlags(&ring.copy_stream, cudaStreamNonBlocking), "forward_host: copy stream");
+            for (auto &sl : ring.s) {
+                cuda_check(cudaEventCreateWithFlags(&sl.gemv_done, cudaEventDisableTiming), "forward_host: event");
+                cuda_check(cudaEventCreateWithFlags(&sl.d2h_done, cudaEventDisableTiming), "forward_host: event");
+            }
+        }
+        HostSlot &sl = ring.s[ring.next];
+        ring.next = (ring.next + 1) % kHostSlots;
+        if (sl.pending) {       // the slot's last copy-back must be over before its buffers are written again
+            cuda_check(cudaStreamWaitEvent(st, sl.d2h_done, 0), "forward_host: wait for the slot's copy-back");
+            sl.pending = false;
+        }
+        grow(sl.x, sl.cap_x, rows * k * es, ring.copy_stream);
+        grow(sl.y, sl.cap_y, rows * n * es, ring.copy_stream);
+        cuda_check(cudaMemcpyAsync(sl.x, host_x, rows * k * es, cudaMemcpyHostToDevice, st), "forward_host: upload");
+        mm.forward(sl.x, (DType)x_dtype, dims, ndims, sl.y, st);
+        cuda_check(cudaEventRecord(sl.gemv_done, st), "forward_host: event record");
+        cuda_check(cudaStreamWaitEvent(ring.copy_stream, sl.gemv_done, 0), "forward_host: copy stream wait");
+        cuda_check(cudaMemcpyAsync(host_out, sl.y, rows * n * es, cudaMemcpyDeviceToHost, ring.copy_stream), "forward_host: copy-back");
+        cuda_check(cudaEventRecord(sl.d2h_done, ring.copy_stream), "forward_host: event record");
+        sl.pending = true;
+    });
+}
+
+// Makes `stream` wait for every copy-back of cqh_qmatmul_forward_host still in flight on `device`.
+extern "C" int cqh_qmatmul_host_flush(int device, void *stream) {
+    return guarded([&] {
+        DeviceGuard g(device);
+        std::lock_guard<std::mutex> lk(g_host_mu);
+        auto it = g_host_ring.find(device);
+        if (it == g_host_ring.end()) return;
+        for (auto &sl : it->second.s)
+            if (sl.pending) {
+                cuda_check(cudaStreamWaitEvent((cudaStream_t)stream, sl.d2h_done, 0), "host_flush: wait");
+                sl.pending = false;
+            }
+    });
+}
+
 extern "C" int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
                                    void *stream) {
     return guarded([&] {

@@ -170,7 +170,7 @@ namespace {
 void moe_ffi(const void *in, int in_elem, const void *w, const int32_t *sorted, const int32_t *experts, const float *tw,
              void *out, int num_experts, int topk, int size_m, int size_n, int size_k, int code, cudaStream_t st) {
     const int wtype = wtype_of_moe_code(code);
-    if (wtype < 0) { cq_set_status(CQ_ERR_UNSUPPORTED, "moe_gemm_gguf: this library covers Q8_0, Q4K and Q6K experts"); return; }
+    if (wtype < 0) { cq_set_status(CQ_ERR_UNSUPPORTED, "moe_gemm_gguf: gguf_dtype must be one of the codes 0..5 (Q8_0, Q4K, Q2K, Q3K, Q5K, Q6K)"); return; }
     if (!in || size_m <= 0 || topk <= 0 || size_k <= 0) { cq_set_status(CQ_ERR_BAD_ARG, "moe_gemm_gguf: null input or empty shape"); return; }
     const int k_padded = (size_k + 511) / 512 * 512;
     const int rows_in = tw ? size_m : size_m / topk;

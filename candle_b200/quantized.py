@@ -274,6 +274,32 @@ class QMatMul:
                                                         out.data_ptr(), stream))
         return out
 
+    def forward_host(self, xs: torch.Tensor, out: torch.Tensor, stream: int | None = None) -> torch.Tensor:
+        """x . W^T for activations and results in HOST memory (pinned for asynchronous copies): upload, multiply and
+        copy back in one library call; the copy-back overlaps the next call.  Call `host_flush()` and synchronise the
+        stream before reading `out`."""
+        if self.kind != "QTensor":
+            raise CandleQError("forward_host needs the quantized variant")
+        if xs.is_cuda or out.is_cuda or xs.dtype not in _ELEM or out.dtype != xs.dtype:
+            raise CandleQError("forward_host takes CPU tensors of one f32 / f16 / bf16 type")
+        if not xs.is_contiguous() or not out.is_contiguous():
+            raise CandleQError("input tensor is not contiguous")
+        n = self.qtensor.shape[0]
+        if tuple(out.shape) != (*xs.shape[:-1], n):
+            raise CandleQError(f"forward_host: output shape {tuple(out.shape)} does not match {(*xs.shape[:-1], n)}")
+        dims, nd = _dims(xs.shape)
+        dev = self.qtensor.device
+        st = torch.cuda.current_stream(dev).cuda_stream if stream is None else stream
+        with torch.cuda.device(dev):
+            capi.hcheck(capi.lib().cqh_qmatmul_forward_host(self.qtensor._h, xs.data_ptr(), _ELEM[xs.dtype], dims, nd, out.data_ptr(), st))
+        return out
+
+    def host_flush(self, stream: int | None = None) -> None:
+        """Make the stream wait for every copy-back of `forward_host` still in flight on this tensor's device."""
+        dev = self.qtensor.device
+        st = torch.cuda.current_stream(dev).cuda_stream if stream is None else stream
+        capi.hcheck(capi.lib().cqh_qmatmul_host_flush(dev.index or 0, st))
+
     def forward_q8_1(self, act: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """The GEMV alone: `act` holds Q8_1 containers, uint8 [rows, pad(k, 512) / 32 * 36], made by a fused producer
         (or the stand-alone quantizer).  Returns f32 [rows, n]."""

@@ -2,10 +2,16 @@
  * candle_q_b200.h -- C ABI of libcandle_q_b200: GGUF quantized matmul for NVIDIA B200 (sm_100a).
  *
  * The first group of functions has exactly the names and signatures that candle's Rust host binds in
- * candle-kernels/src/ffi.rs, so this library can stand in for candle's kernel archive for the Q4_0, Q8_0,
- * Q4_K and Q6_K formats.  All pointers are device pointers unless stated otherwise, `stream` is a
+ * candle-kernels/src/ffi.rs, so this library can stand in for candle's kernel archive for all ten block
+ * formats of that file.  All pointers are device pointers unless stated otherwise, `stream` is a
  * cudaStream_t, nothing synchronises, and the caller owns every buffer.  Like the reference launchers they
  * return void; the outcome of a failing call is kept in a side channel (cq_last_status).
+ *
+ * Weight buffers must be readable for 16 bytes either side of the tensor: staged copies round their start
+ * down and their end up to 16 bytes (at most 14 bytes before a 2-byte aligned tensor, 15 past its last row).
+ * Device allocations with candle's tail padding (512 elements, candle-core/src/quantized/cuda.rs:989-1008)
+ * and row shards cut out of a larger allocation satisfy this; a tensor that ends exactly at the end of an
+ * unpadded mapping does not.  Q4_K and Q5_K weights need a 16-byte aligned base, the others a 2-byte one.
  *
  * The second group (prefix cq_) is this library's own surface: the status channel, the generic entry points
  * the compatible symbols forward to, activation encodings that reproduce candle's CPU path bit for bit, and
@@ -71,8 +77,9 @@ CQ_DECL_MMVQ(launch_mmvq_gguf_q6_k_bf16_plain);
 #undef CQ_DECL_MMVQ
 
 /* Expert-indexed GEMV for quantized MoE layers.  Replaces candle-kernels/src/ffi.rs:25-39 (moe_gemm_gguf) and
- * :41-56 (moe_gemm_gguf_prefill) for Q8_0 (code 0), Q4K (1) and Q6K (5) experts; other codes record
- * "unsupported".  weights: [num_experts, size_n, size_k] GGUF blocks; sorted_token_ids / expert_ids: device i32
+ * :41-56 (moe_gemm_gguf_prefill) for all six `gguf_dtype` codes of ffi.rs:36 - Q8_0 (0), Q4K (1), Q2K (2), Q3K (3), Q5K (4),
+ * Q6K (5); any other code records "unsupported".  Both take their activation scratch from cudaMallocAsync on the caller's
+ * stream and free it there, like the reference's entry points; cq_moe_gemv_sorted / cq_moe_prefill_gemm take a caller's.  weights: [num_experts, size_n, size_k] GGUF blocks; sorted_token_ids / expert_ids: device i32
  * [size_m]; topk_weights: device f32 or null; output: f32 [rows, size_n]; `stream` is the cudaStream_t as an integer.
  * Job m: pair = sorted_token_ids[m]; input row = pair (topk_weights given) else pair / topk; output row = pair,
  * scaled by topk_weights[pair] when given; jobs whose expert id is outside [0, num_experts) write nothing. */
@@ -347,6 +354,15 @@ int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int6
 void cqh_qtensor_free(void *handle);
 int cqh_qtensor_data(void *handle, void *host_out, size_t nbytes);
 const void *cqh_qtensor_device_ptr(void *handle);
+/* QMatMul::forward over HOST buffers (where candle's caller does Tensor::to_device, QMatMul::forward, to_device back:
+ * candle-core/src/quantized/mod.rs:1020-1043 around a CPU tensor).  host_x [.., k] -> host_out [.., n], same element
+ * type; the upload and the arithmetic run on `stream`, the copy-back on a copy stream of the library so that it
+ * overlaps the next call; staging buffers are kept per device (ring of four slots, grows-only).  After the last call,
+ * cqh_qmatmul_host_flush(device, stream) makes `stream` wait for every copy-back in flight: synchronise `stream` and the
+ * outputs are complete.  Use pinned host memory (else the copies are synchronous). */
+int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_dtype, const int64_t *dims, int ndims, void *host_out,
+                             void *stream);
+int cqh_qmatmul_host_flush(int device, void *stream);
 /* QMatMul::forward: x [.., k] (device, contiguous, x_dtype = CQ_ELEM_*) -> out [.., n], same element type. */
 int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
                         void *stream);

@@ -304,3 +304,32 @@ def test_qmatmul_forward_api(oracle, cuda_dev):
     xc = np.concatenate([x] * 5)
     yc = mm.forward(torch.from_numpy(xc).to(cuda_dev))
     assert rel_err(yc.cpu().numpy(), oracle.matmul(wt, xc, wq, n)) <= TOL
+
+
+def test_forward_over_host_buffers_matches_device_forward(oracle, cuda_dev):
+    """QMatMul.forward_host: upload, multiply and copy back inside the library, the copy-back on its own stream.  Ten calls in
+    a row (the staging ring has four slots, so slots are reused while earlier copy-backs may still run), different row
+    counts, element types and two matrices; after host_flush + synchronize every output has the bits of the device forward."""
+    k = 2048
+    mats = []
+    for tname, n in (("q4_k", 300), ("q8_0", 130)):
+        _, _, wq = make_case(oracle, TYPES[tname], k, n, 1, seed=n)
+        mats.append(QMatMul.from_qtensor(QTensor.from_data(wq, GgmlDType(TYPES[tname]), (n, k), cuda_dev)))
+    rng = np.random.default_rng(3)
+    calls = []
+    for i in range(10):
+        mm = mats[i % 2]
+        rows = (1, 8, 3, 40, 2)[i % 5]
+        dt = (torch.float32, torch.bfloat16, torch.float16)[i % 3]
+        x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).to(dt).pin_memory()
+        y = torch.full((rows, mm.qtensor.shape[0]), float("nan"), dtype=dt).pin_memory()
+        calls.append((mm, x, y))
+    for mm, x, y in calls:
+        mm.forward_host(x, y)
+    mats[0].host_flush()
+    torch.cuda.synchronize()
+    for mm, x, y in calls:
+        want = mm.forward(x.to(cuda_dev)).cpu()
+        assert torch.equal(y, want)
+    with pytest.raises(capi.CandleQError, match="output shape"):
+        mats[0].forward_host(calls[0][1], torch.empty((2, 2)).pin_memory())
