@@ -23,6 +23,7 @@ Further objects of the same JSON line (reported beside the headline, not part of
   prefill     : prompt-phase GEMM, Q4_K 4096->14336 and 14336->4096, M = 128 .. 8192 tokens, f32 and bf16 inputs: useful
                 TOP/s of the tcgen05 kernel, of the whole forward (quantize + GEMM), and of the reference's own two-call
                 protocol (launch_mmq_quantize_q8_1_DS4 + launch_mmq_gguf_q4_k) served by this library.
+  prefill_block_formats : the Q8_0 / Q4_0 prompt kernel at 2048 tokens on the same shapes, and the two-call protocol beside it.
   moe         : Qwen3-30B-A3B-shaped mixture-of-experts decoder (tokens/s) and the grouped expert GEMM (TOP/s).
   decode      : Llama-3-8B-shaped Q4_K_M decoder, tokens/s at batch 1 and 8.
 
@@ -406,6 +407,46 @@ def measure_prefill(dev, rank, world, peak_tops):
     return out
 
 
+def measure_prefill_block_formats(dev, peak_tops):
+    """The prompt kernel of the 32-element block formats (Q8_0, Q4_0) on the same two shapes at 2048 tokens, f32 inputs:
+    useful TOP/s of QMatMul.forward, and of the reference's two-call protocol (GEMV passes) beside it."""
+    import torch
+    from candle_b200 import capi
+    from candle_b200.quantized import GgmlDType, QMatMul, QTensor
+    from candle_b200.synth import random_blocks
+    L = capi.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    res = []
+    m = 2048
+    for tname, lay in (("Q8_0", "D4"), ("Q4_0", "DS4")):
+        for (k, n) in ((4096, 14336), (14336, 4096)):
+            ws = [random_blocks(GgmlDType[tname], n, k, seed=3 + i, device=dev) for i in range(3)]
+            mms = [QMatMul.from_qtensor(QTensor.from_device_blocks(w, GgmlDType[tname], (n, k))) for w in ws]
+            x = torch.randn((m, k), device=dev)
+            y = torch.empty((m, n), device=dev)
+            t_fwd = _time_launches(lambda i: mms[i % 3].forward(x, out=y), 10)
+            kp = capi.pad(k, 512)
+            mmq_scratch = torch.empty(((kp // 128) * m + 128) * 144, dtype=torch.uint8, device=dev)
+            fixup = torch.empty(4 << 20, dtype=torch.float32, device=dev)
+
+            def dropin(i):
+                getattr(L, f"launch_mmq_quantize_q8_1_{lay}")(x.data_ptr(), None, mmq_scratch.data_ptr(), 0, k, k, 0, 0, kp, m, 1, 1, st)
+                getattr(L, f"launch_mmq_gguf_{tname.lower()}")(fixup.data_ptr(), ws[i % 3].data_ptr(), mmq_scratch.data_ptr(), y.data_ptr(), k, n, m,
+                                                               k // 32, n, 1000, 148, 232448, 32, st)
+            t_drop = _time_launches(dropin, 3)
+            capi.check("block-format prefill bench")
+            ops = 2.0 * m * n * k
+            row = {"type": tname, "k": k, "n": n, "m": m, "forward_ms": t_fwd, "forward_tops": ops / t_fwd / 1e9, "dropin_mmq_ms": t_drop,
+                   "dropin_mmq_tops": ops / t_drop / 1e9}
+            if peak_tops:
+                row["forward_frac_of_int8_peak"] = row["forward_tops"] / peak_tops
+            res.append(row)
+            del ws, mms, x, y, mmq_scratch, fixup
+            torch.cuda.empty_cache()
+    assert L.cq_prefill32_timeout_flag() == 0, "a block-format prefill launch gave up a bounded wait"
+    return res
+
+
 def measure_moe_gemm(dev):
     """The grouped expert GEMM at the Qwen3-30B-A3B shape: 1024 tokens x top-8 = 8192 (token, expert) pairs over 128
     Q4_K experts, gate|up (2048 -> 1536) and down (768 -> 2048); useful TOP/s = 2 * pairs * n * k / t."""
@@ -584,9 +625,10 @@ def run_gpu(args):
     gather = None
     torch.cuda.empty_cache()
     int8_peak = measure_int8_peak(dev) if not args.no_prefill else None
-    prefill = None
+    prefill = prefill_b32 = None
     if not args.no_prefill:
         prefill = measure_prefill(dev, rank, world, int8_peak["burst_tops"] if int8_peak else None)
+        prefill_b32 = measure_prefill_block_formats(dev, int8_peak["burst_tops"] if int8_peak else None) if world == 1 else None
     decode = None
     if not args.no_decode:
         decode = [decode_tok_s(dev, rank, world, b) for b in (1, 8)]
@@ -623,6 +665,7 @@ def run_gpu(args):
                        "by_type_shape_batch": per_case},
         "int8_peak": int8_peak,
         "prefill": prefill,
+        "prefill_block_formats": prefill_b32,
         "moe": moe,
         "e2e": {"value": total_bytes / ms_e2e / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
@@ -746,17 +789,20 @@ def run_prefill_case(args):
     dev = torch.device("cuda:0")
     L = capi.lib()
     wt = GgmlDType[args.prefill_type]
+    block32 = wt in (GgmlDType.Q8_0, GgmlDType.Q4_0)        # the block-format kernel (prefill_b32.cu)
+    scratch_bytes, quantize, gemm = ((L.cq_prefill32_scratch_bytes, L.cq_prefill32_quantize, L.cq_prefill32_gemm) if block32 else
+                                     (L.cq_prefill_scratch_bytes, L.cq_prefill_quantize, L.cq_prefill_gemm))
     w = random_blocks(wt, n, k, seed=1, device=dev)
     x = torch.randn((m, k), device=dev)
-    scratch = torch.empty(L.cq_prefill_scratch_bytes(m, k), dtype=torch.uint8, device=dev)
+    scratch = torch.empty(scratch_bytes(m, k), dtype=torch.uint8, device=dev)
     out = torch.empty((m, n), device=dev)
     s = torch.cuda.current_stream().cuda_stream
-    L.cq_prefill_quantize(x.data_ptr(), capi.F32, scratch.data_ptr(), k, m, s)
+    quantize(x.data_ptr(), capi.F32, scratch.data_ptr(), k, m, s)
     times = []
     for _ in range(args.iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        L.cq_prefill_gemm(int(wt), w.data_ptr(), scratch.data_ptr(), out.data_ptr(), capi.F32, k, n, m, n, s)
+        gemm(int(wt), w.data_ptr(), scratch.data_ptr(), out.data_ptr(), capi.F32, k, n, m, n, s)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
@@ -884,7 +930,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the int8 peak and prompt-phase GEMM measurements")
     ap.add_argument("--no-moe", action="store_true", help="skip the mixture-of-experts measurements")
     ap.add_argument("--prefill-case", default=None, help="profile helper: M:K:N, runs the Q4_K prefill GEMM --iters times")
-    ap.add_argument("--prefill-type", default="Q4K", choices=["Q4K", "Q6K"], help="weight format of --prefill-case")
+    ap.add_argument("--prefill-type", default="Q4K", choices=["Q4K", "Q6K", "Q8_0", "Q4_0"], help="weight format of --prefill-case")
     ap.add_argument("--case", default=None, help="profile helper: TYPE:K:N:B, runs that GEMV --iters times")
     ap.add_argument("--traffic-sweep", action="store_true", help="profile helper: each (format, shape) GEMV once at batch 1 and 8")
     ap.add_argument("--traffic-types", default="Q4K,Q6K,Q8_0", help="with --traffic-sweep: comma-separated formats")

@@ -56,6 +56,11 @@ def lib() -> C.CDLL:
         L.cq_prefill_quantize.argtypes = [vp, i32, vp, i32, i32, vp]
         L.cq_prefill_gemm.argtypes = [i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_prefill_timeout_flag.restype = i32
+        L.cq_prefill32_scratch_bytes.argtypes = [i32, i32]
+        L.cq_prefill32_scratch_bytes.restype = C.c_size_t
+        L.cq_prefill32_quantize.argtypes = [vp, i32, vp, i32, i32, vp]
+        L.cq_prefill32_gemm.argtypes = [i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.cq_prefill32_timeout_flag.restype = i32
         i64 = C.c_int64
         L.moe_gemm_gguf.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64]
         L.moe_gemm_gguf_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64]

@@ -15,15 +15,12 @@
 //     lane (about one shuffle per value), warps are then added in index order through shared memory.
 //     The order of additions for one output does not depend on RB, on the grid or on N, so a row gives the
 //     same bits whether the matrix is whole or sharded by rows across GPUs, and whatever the batch size.
-#include <cuda.h>
-
-#include <unordered_map>
-
 #include "../../include/candle_q_b200.h"
 #include "gemv_body.cuh"
 #include "gemv_mma.cuh"
 #include "gemv_mma2.cuh"
 #include "gemv_plan.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
@@ -153,52 +150,6 @@ gemv_mma2_kernel(const __grid_constant__ CUtensorMap tmap, const uint8_t *__rest
     cq_mma2::gemv_mma2_body<TYPE, SPLIT>(&tmap, y, dst, out_kind, nunits, nrows, stride_col_y, stride_col_dst, b, spw, &g_gemv_timeout_flag);
 }
 
-// Tensor map of the weight matrix as bytes [nrows, row_bytes], box 16 rows x `box_w` bytes, no swizzle, zero fill outside.
-// The driver's encoder is reached through the runtime (no link against libcuda); maps are cached per (pointer, shape).
-struct TmapKey {
-    const void *p; int row_bytes, nrows, box_w;
-    bool operator==(const TmapKey &o) const { return p == o.p && row_bytes == o.row_bytes && nrows == o.nrows && box_w == o.box_w; }
-};
-struct TmapHash {
-    size_t operator()(const TmapKey &k) const {
-        return std::hash<const void *>()(k.p) ^ ((size_t)k.row_bytes * 1000003u) ^ ((size_t)k.nrows * 7919u) ^ (size_t)k.box_w;
-    }
-};
-bool weight_tensor_map(const void *w, int row_bytes, int nrows, int box_w, CUtensorMap &out) {
-    using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static std::mutex mu;
-    static Encode encode = nullptr;
-    static bool looked_up = false;
-    static std::unordered_map<TmapKey, CUtensorMap, TmapHash> cache;
-    std::lock_guard<std::mutex> lk(mu);
-    if (!looked_up) {
-        looked_up = true;
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            encode = (Encode)fn;
-        else
-            (void)cudaGetLastError();
-    }
-    if (!encode) return false;
-    const TmapKey key{w, row_bytes, nrows, box_w};
-    auto it = cache.find(key);
-    if (it != cache.end()) { out = it->second; return true; }
-    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)nrows};
-    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)box_w, (cuuint32_t)cq_mma2::kTileRows};
-    const cuuint32_t estr[2] = {1, 1};
-    if (encode(&out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (cache.size() >= 8192) cache.clear();
-    cache.emplace(key, out);
-    return true;
-}
-
 // Shape rules: K a whole number of 32-chunk groups (so the tree needs no padding; row sizes are then multiples of 16
 // bytes, as the tensor map wants), a 16-byte aligned matrix, the activation tables of K fit in shared memory beside the
 // rings, and - unless forced - at least two (tile, warp) work items per SM.  A matrix with many tiles (the vocabulary head) gives
@@ -252,7 +203,7 @@ bool launch_mma2(const void *w, const void *y, void *dst, int out_kind, int K, i
     }
     if (record_plan(split ? kPlanMma2Split : kPlanMma2, cq_mma2::kTileRows, grid, warps * 32)) return true;
     CUtensorMap tmap;
-    if (!weight_tensor_map(w, row_bytes, N, F::RS, tmap)) return false;
+    if (!cq_tmap::weight_map(w, row_bytes, N, F::RS, cq_mma2::kTileRows, 1, tmap)) return false;
     if (split) {
         ensure_smem_attr(&ke_split);
         cq_launch_k(gemv_mma2_kernel<TYPE, true>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,

@@ -24,6 +24,7 @@
 // and in either kernel, which candle's `qmm_batch` test asks for (candle-core/tests/quantized_tests.rs:224-259).
 #pragma once
 #include "gemv_mma.cuh"
+#include "tensor_map.cuh"
 
 namespace cq_mma2 {
 
@@ -187,14 +188,6 @@ template <> struct Unit<CQ_Q6_K> {
 
 // ---- the kernel body ----
 // nunits: units per weight row (a multiple of 8: groups of 32 chunks are whole).
-// One tiled copy: box (x .. x + RS bytes, rows y .. y + 16) of the byte view described by `tmap` into shared memory.
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                     cq_smem_u32(smem_dst)),
-                 "l"(tmap), "r"(x), "r"(y), "r"(cq_smem_u32(bar))
-                 : "memory");
-}
-
 // nunits: units per weight row (a multiple of 8: groups of 32 chunks are whole).  SPLIT: `spw` warps share a tile, each
 // takes nunits / spw consecutive units (a whole number of groups); else a warp owns whole tiles (spw is ignored).
 template <int TYPE, bool SPLIT>
@@ -234,7 +227,7 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
     auto issue = [&](int stage) {
         if (lane == 0) {
             cq_mbar_expect_tx(&bars[stage], (unsigned)stage_bytes<TYPE>());
-            tma_load_2d(ring + stage * stage_bytes<TYPE>(), tmap, ((u_first + pu) * F::UNIT_BYTES) & ~15, ptile * kTileRows, &bars[stage]);
+            cq_tmap::load_2d(ring + stage * stage_bytes<TYPE>(), tmap, ((u_first + pu) * F::UNIT_BYTES) & ~15, ptile * kTileRows, &bars[stage]);
         }
         ++inflight;
         if (++pu == upw) { pu = 0; ptile += tstride; }

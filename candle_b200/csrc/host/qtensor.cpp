@@ -197,6 +197,16 @@ void QCudaStorage::fwd(size_t n, size_t k, const void *x, DType x_dtype, const i
         lib_check("qmatmul prefill");
         return;
     }
+    // The 32-element block formats Q4_0 / Q8_0 have their own tensor-core prompt kernel (Q8_0 activations, the CPU path's
+    // arithmetic, in every mode); K must be a whole number of 256-element stages.
+    if (rows > kPrefillMinRows && (dtype_ == GgmlDType::Q4_0 || dtype_ == GgmlDType::Q8_0) && k % 256 == 0) {
+        const size_t need = cq_prefill32_scratch_bytes((int)rows, (int)k);
+        uint8_t *scratch = (uint8_t *)workspace_ensure(device_, need);
+        cq_prefill32_quantize(x, (int)x_dtype, scratch, (int)k, (int)rows, stream);
+        cq_prefill32_gemm((int)dtype_, ptr_, scratch, out, (int)x_dtype, (int)k, (int)n, (int)rows, (int)n, stream);
+        lib_check("qmatmul prefill (block formats)");
+        return;
+    }
     // Decode path: up to 8 rows per launch.  Other formats with more rows are walked in slices of 8 rows.
     const size_t chunk = MMVQ_MAX_BATCH;
     uint8_t *scratch = (uint8_t *)workspace_ensure(device_, (rows < chunk ? rows : chunk) * row_q8);

@@ -224,6 +224,15 @@ void cq_prefill_quantize(const void *x, int x_elem, void *scratch, int k, int to
 void cq_prefill_gemm(int wtype, const void *vx, const void *scratch, void *dst, int out_elem, int ncols_x, int nrows_x,
                      int tokens, int stride_dst, void *stream);
 int cq_prefill_timeout_flag(void);
+/* The same for the 32-element block formats Q4_0 (wtype 2) and Q8_0 (8): candle-kernels/src/mmq_gguf/mmq_gguf.cuh:305-364,
+ * 927-1062, 1169-1296 behind ffi.rs:471-630.  Activations are quantized like candle's CPU path (BlockQ8_0, k_quants.rs:
+ * 658-687); every 32-element block is one tcgen05 MMA step into a fresh TMEM accumulator that the epilogue scales by
+ * d_w * d_a (k_quants.rs:294-311, 720-738).  k % 256 == 0.  Scratch: cq_prefill32_scratch_bytes, 16-byte aligned. */
+size_t cq_prefill32_scratch_bytes(int tokens, int k);
+void cq_prefill32_quantize(const void *x, int x_elem, void *scratch, int k, int tokens, void *stream);
+void cq_prefill32_gemm(int wtype, const void *vx, const void *scratch, void *dst, int out_elem, int ncols_x, int nrows_x,
+                       int tokens, int stride_dst, void *stream);
+int cq_prefill32_timeout_flag(void);
 
 /* Glue kernels of the decoder harness (f32, fixed order of additions, one launch each).  They stand where candle's
  * quantized models run chains of tensor ops (candle-transformers/src/models/quantized_llama.rs:56-62, 178-262).

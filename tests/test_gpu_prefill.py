@@ -132,3 +132,96 @@ def test_qmatmul_routes_many_rows_to_prefill(oracle, cuda_dev):
     y = mm.forward(torch.from_numpy(x).to(cuda_dev).view(7, 11, k))
     assert y.shape == (7, 11, n)
     assert rel_err(y.view(tokens, n).cpu().numpy(), oracle.matmul(Q4K, x, wq, n)) <= TOL
+
+
+# ---- the 32-element block formats (Q4_0, Q8_0): every block is its own MMA step, scaled in the epilogue ----
+
+def _prefill32(lib, wtype, w_dev, x_dev, k, n, out_dtype=torch.float32):
+    tokens = x_dev.shape[0]
+    elem = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+    scratch = torch.full((lib.cq_prefill32_scratch_bytes(tokens, k),), 0x5A, dtype=torch.uint8, device=x_dev.device)
+    out = torch.full((tokens * n + 32,), float("nan"), dtype=out_dtype, device=x_dev.device)
+    lib.cq_prefill32_quantize(x_dev.data_ptr(), elem[x_dev.dtype], scratch.data_ptr(), k, tokens, _stream())
+    lib.cq_prefill32_gemm(wtype, w_dev.data_ptr(), scratch.data_ptr(), out.data_ptr(), elem[out_dtype], k, n, tokens, n, _stream())
+    capi.check("prefill32")
+    torch.cuda.synchronize()
+    assert lib.cq_prefill32_timeout_flag() == 0
+    assert bool(torch.isnan(out[tokens * n:].float()).all()), "output written past its end"
+    assert not bool(torch.isnan(out[:tokens * n].float()).any()), "an output element was left unwritten"
+    return scratch, out[:tokens * n].view(tokens, n)
+
+
+def _tiles_to_q8_0(scratch, tokens, k):
+    """Undo the tensor-core tiling: int8 [tokens, k] and the f32 scales [tokens, k/32] (f16 values, widened)."""
+    s = scratch.cpu().numpy()
+    nch = k // 256
+    q = np.zeros((tokens, k), dtype=np.int8)
+    d = np.zeros((tokens, k // 32), dtype=np.float32)
+    for tt in range((tokens + 127) // 128):
+        nt = min(128, tokens - tt * 128)
+        rows = (nt + 7) // 8 * 8
+        for c in range(nch):
+            off = tt * 128 * 288 * nch + c * rows * 288
+            blob = s[off:off + rows * 288]
+            slabs = blob[:rows * 256].reshape(16, rows, 16)
+            q[tt * 128:tt * 128 + nt, c * 256:(c + 1) * 256] = slabs.transpose(1, 0, 2).reshape(rows, 256)[:nt].view(np.int8)
+            d[tt * 128:tt * 128 + nt, c * 8:(c + 1) * 8] = blob[rows * 256:].view(np.float32).reshape(8, rows)[:, :nt].T
+    return q, d
+
+
+@pytest.mark.parametrize("tname", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("tokens,k,n", [(128, 256, 64), (17, 512, 65), (100, 1024, 100), (300, 2048, 200), (129, 768, 33),
+                                        (520, 14336, 70), (1000, 4096, 130), (64, 4096, 256)])
+def test_block_format_prefill_matches_cpu_vec_dot(lib, oracle, cuda_dev, tname, tokens, k, n):
+    """Q4_0 / Q8_0 prompt kernel: BlockQ8_0 activations bit-exact (values and f16 scales), outputs within 1e-3 of the
+    reference's CPU matmul (measured: only the order of f32 additions differs); ragged token and row tiles, 1 to 56 stages."""
+    from helpers import TYPES
+    wt = TYPES[tname]
+    _, x, wq = make_case(oracle, wt, k, n, tokens, seed=tokens + k + n)
+    x[0, :32] = 0.0                     # an all-zero block: d = 0, q = 0
+    w_dev = torch.from_numpy(wq).to(cuda_dev)
+    x_dev = torch.from_numpy(x).to(cuda_dev)
+    scratch, out = _prefill32(lib, wt, w_dev, x_dev, k, n)
+    q, d = _tiles_to_q8_0(scratch, tokens, k)
+    ref_blocks = oracle.quantize(oracle.Q8_0, x).reshape(tokens, k // 32, 34)
+    assert np.array_equal(q.reshape(tokens, k // 32, 32), ref_blocks[:, :, 2:].view(np.int8))
+    assert np.array_equal(d, ref_blocks[:, :, :2].copy().view(np.float16).astype(np.float32).reshape(tokens, k // 32))
+    ref = oracle.matmul(wt, x, wq, n)
+    assert rel_err(out.cpu().numpy(), ref) <= TOL
+    assert rel_err(out.cpu().numpy(), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_block_format_prefill_half_types(lib, oracle, cuda_dev, dtype):
+    from helpers import TYPES
+    tokens, k, n = 200, 1024, 130
+    for tname in ("q8_0", "q4_0"):
+        wt = TYPES[tname]
+        _, x, wq = make_case(oracle, wt, k, n, tokens, seed=6)
+        xt = torch.from_numpy(x).to(cuda_dev).to(dtype)
+        _, out = _prefill32(lib, wt, torch.from_numpy(wq).to(cuda_dev), xt, k, n, out_dtype=dtype)
+        ref = torch.from_numpy(oracle.matmul(wt, xt.float().cpu().numpy(), wq, n)).to(dtype).float().numpy()
+        assert rel_err(out.float().cpu().numpy(), ref) <= (2 ** -8 if dtype == torch.bfloat16 else 2 ** -11) * 1.01
+
+
+def test_qmatmul_routes_block_formats_to_their_prefill_kernel(oracle, cuda_dev):
+    """More than 16 rows of a Q8_0 / Q4_0 matrix take the tensor-core kernel (CPU arithmetic in every mode) when K is a
+    multiple of 256, and the GEMV passes otherwise; duplicated rows give identical outputs; the benchmark's shape class."""
+    from helpers import TYPES
+    for tname, dt in (("q8_0", GgmlDType.Q8_0), ("q4_0", GgmlDType.Q4_0)):
+        wt = TYPES[tname]
+        k, n, tokens = 4096, 520, 300
+        _, x, wq = make_case(oracle, wt, k, n, tokens, seed=9)
+        mm = QMatMul.from_qtensor(QTensor.from_data(wq, dt, (n, k), cuda_dev))
+        xd = torch.from_numpy(x).to(cuda_dev)
+        y = mm.forward(xd)
+        assert rel_err(y.cpu().numpy(), oracle.matmul(wt, x, wq, n)) <= 1e-5
+        y2 = mm.forward(torch.cat([xd[:150], xd[:150]]))
+        assert torch.equal(y2[:150], y2[150:]) and torch.equal(y2[:150], y[:150])
+        # K = 288 is not a whole number of stages: GEMV passes (Q8_1 arithmetic) serve it
+        k2 = 288
+        _, x2, wq2 = make_case(oracle, wt, k2, 40, 20, seed=10)
+        mm2 = QMatMul.from_qtensor(QTensor.from_data(wq2, dt, (40, k2), cuda_dev))
+        y3 = mm2.forward(torch.from_numpy(x2).to(cuda_dev))
+        ref3 = oracle.cuda_mmvq(wt, wq2, oracle.cuda_quantize_q8_1(x2[:8]), k2, 40)
+        assert rel_err(y3[:8].cpu().numpy(), ref3) <= 1e-5
