@@ -921,6 +921,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="with --decode-case: launch decode steps eagerly")
     ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
     ap.add_argument("--mma-kernel", type=int, default=None, help="with --case: 1 only the CTA-shared tensor-core GEMV, 2 the warp-private one")
+    ap.add_argument("--cluster-split", type=int, default=None, help="with --case / --decode-case: 0 never, 1 default rule, 2 always "
+                    "(thread-block clusters for the split form of the warp-private tensor-core GEMV)")
     ap.add_argument("--no-pdl", action="store_true", help="with --case: plain launches instead of programmatic dependent launches")
     ap.add_argument("--tune", default=None, help="with --decode-case: RB:CTAS_PER_SM forced for every GEMV (experiment hook)")
     ap.add_argument("--moe-decode-case", default=None, help="BATCH:PROMPT:STEPS, runs the mixture-of-experts decoder measurement "
@@ -940,6 +942,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
+    if args.cluster_split is not None:
+        from candle_b200 import capi as _capi
+        _capi.lib().cq_set_cluster_split(args.cluster_split)
     if args.decode_case:
         import torch
         b_, p_, s_ = (int(v) for v in args.decode_case.split(":"))

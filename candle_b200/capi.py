@@ -83,6 +83,8 @@ def lib() -> C.CDLL:
         L.cq_peer_gather_words.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         L.cq_peer_gather_stage_bytes.argtypes = [i32, i32, i32]
         L.cq_peer_gather_stage_bytes.restype = C.c_size_t
+        L.cq_peer_exchange_rows.argtypes = [vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, vp]
+        L.cq_peer_exchange_rows.restype = None
         L.cq_peer_gather_set_limit_clocks.argtypes = [C.c_longlong]
         L.cq_peer_gather_timeout_flag.restype = i32
         L.cq_add_rms_norm_q8_1.argtypes = [vp, vp, vp, vp, i32, i32, i32, C.c_float, vp]
@@ -96,8 +98,13 @@ def lib() -> C.CDLL:
         L.cq_attention_split_scratch_floats.argtypes = [i32, i32, i32, i32]
         L.cq_attention_split_scratch_floats.restype = C.c_size_t
         L.cq_attention_split.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, i32, vp]
+        L.cq_rope_attention_split.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float,
+                                              i32, i32, i32, i32, vp]
+        L.cq_rope_attention_split.restype = None
         L.cq_set_mma_min_batch.argtypes = [i32]
         L.cq_set_mma_kernel.argtypes = [i32]
+        L.cq_set_cluster_split.argtypes = [i32]
+        L.cq_set_cluster_split.restype = None
         L.cq_qmatmul_decode_static.argtypes = [i32, vp, vp, i32, vp, i32, i32, i32, vp]
         for el in ELEM_NAME.values():
             getattr(L, f"launch_mmvq_gguf_quantize_q8_1_{el}").argtypes = [vp, vp, i32, i32, i32, vp]

@@ -152,12 +152,37 @@ namespace {
 // depend on which CTA that was.  Nothing waits for anything.
 constexpr int kChunk = 128, kSplitThreads = 256, kSplitWarps = 8, kPartFloats = 132;
 
-template <bool Q8>
-__global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+// ROPE (one query per sequence): the kernel also does the step that otherwise precedes it as a launch of its own - the
+// interleaved rotary embedding of q and of the new key, and the store of the new key / value into the caches.  Every CTA
+// rotates its head's query in registers (never in place: the other CTAs of the head read the same row; the split-0 CTA
+// writes a copy to `q_rot` when one is given); the CTA whose chunk holds the new position takes
+// that key and value from the projection outputs instead of the cache, and the first query head of each KV head stores them.
+// Same operations on the same inputs as rope_store_kernel, so the same bits.
+struct RopeFused {
+    float *q_rot;                // null, or where the rotated queries go (rows of q_stride floats; not q itself)
+    const float *k_new, *v_new;  // projection outputs of the new token, rows of k_stride / v_stride floats
+    const float *cosv, *sinv;    // [tmax, 64]
+    float *kc_w, *vc_w;          // the caches, writable
+    int k_stride, v_stride;
+};
+__device__ int g_attn_pos_overflow = 0;
+
+__device__ __forceinline__ float4 rope_rotate4(const float4 x, const float2 c, const float2 s) {
+    float4 r;
+    r.x = __fmaf_rn(x.x, c.x, -__fmul_rn(x.y, s.x));
+    r.y = __fmaf_rn(x.x, s.x, __fmul_rn(x.y, c.x));
+    r.z = __fmaf_rn(x.z, c.y, -__fmul_rn(x.w, s.y));
+    r.w = __fmaf_rn(x.z, s.y, __fmul_rn(x.w, c.y));
+    return r;
+}
+
+template <bool Q8, bool ROPE>
+__global__ void __launch_bounds__(kSplitThreads, 2) attention_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
                                                                        const float *__restrict__ vc, void *__restrict__ out,
                                                                        const int *__restrict__ pos, float *__restrict__ scratch,
                                                                        int *__restrict__ counters, int tq, int hq, int hkv, int tmax,
-                                                                       float scale, int q_stride, int out_blocks, int eager_keys) {
+                                                                       float scale, int q_stride, int out_blocks, int eager_keys,
+                                                                       const RopeFused rf) {
     __shared__ float scores[kChunk];
     __shared__ float red[kSplitWarps];
     __shared__ float4 part[kSplitWarps][32];
@@ -197,6 +222,55 @@ __global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const fl
         n_ctx = min(pos[0] + t + 1, tmax);
         if (key0 >= n_ctx) return;
     }
+    int jn = -1;        // ROPE: index of the new key inside this chunk, if it lies here
+    if constexpr (ROPE) {
+        const int p = pos[0] + t;
+        if (p < 0 || p >= tmax) {       // past the tables and the cache: skip the row, report
+            if (tid == 0) g_attn_pos_overflow = 1;
+            return;
+        }
+        float2 c2[4], s2[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            c2[i] = *reinterpret_cast<const float2 *>(rf.cosv + (size_t)p * (kD / 2) + 2 * (g + 8 * i));
+            s2[i] = *reinterpret_cast<const float2 *>(rf.sinv + (size_t)p * (kD / 2) + 2 * (g + 8 * i));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = rope_rotate4(qv[i], c2[i], s2[i]);
+        if (rf.q_rot && split == 0 && grp == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<float4 *>(rf.q_rot + (size_t)bt * q_stride + (size_t)h * kD + 4 * (g + 8 * i)) = qv[i];
+        }
+        float4 newk[4];
+        bool mine_k = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) newk[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p >= key0 && p < key0 + kChunk) {
+            jn = p - key0;
+            const bool store = h % (hq / hkv) == 0;
+            const size_t crow = (((size_t)b * hkv + kvh) * (size_t)tmax + p) * kD;
+            if (grp == (jn & 31)) {
+                mine_k = true;
+                const float *kn = rf.k_new + (size_t)bt * rf.k_stride + (size_t)kvh * kD;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 kr = rope_rotate4(*reinterpret_cast<const float4 *>(kn + 4 * (g + 8 * i)), c2[i], s2[i]);
+                    newk[i] = kr;
+                    if (store) *reinterpret_cast<float4 *>(rf.kc_w + crow + 4 * (g + 8 * i)) = kr;
+                }
+            }
+        }
+        const int rn = mine_k ? (jn >> 5) : -1;
+#pragma unroll
+        for (int r = 0; r < kChunk / 32; ++r) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                kv[r][i].x = r == rn ? newk[i].x : kv[r][i].x; kv[r][i].y = r == rn ? newk[i].y : kv[r][i].y;
+                kv[r][i].z = r == rn ? newk[i].z : kv[r][i].z; kv[r][i].w = r == rn ? newk[i].w : kv[r][i].w;
+            }
+        }
+    }
     const int nk = min(kChunk, n_ctx - key0), nact = (n_ctx + kChunk - 1) / kChunk;
     // values: warp w takes keys w, w + 8, ... of the chunk
     float4 vv[kChunk / kSplitWarps];
@@ -204,6 +278,19 @@ __global__ void __launch_bounds__(kSplitThreads) attention_split_kernel(const fl
     for (int i = 0; i < kChunk / kSplitWarps; ++i) {
         const int j = warp + i * kSplitWarps;
         vv[i] = j < nk ? *reinterpret_cast<const float4 *>(vp + (size_t)j * kD + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if constexpr (ROPE) {
+        if (jn >= 0 && warp == (jn & (kSplitWarps - 1))) {
+            const float4 vn = *reinterpret_cast<const float4 *>(rf.v_new + (size_t)bt * rf.v_stride + (size_t)kvh * kD + 4 * lane);
+            const int in = jn / kSplitWarps;
+#pragma unroll
+            for (int i = 0; i < kChunk / kSplitWarps; ++i) {
+                vv[i].x = i == in ? vn.x : vv[i].x; vv[i].y = i == in ? vn.y : vv[i].y;
+                vv[i].z = i == in ? vn.z : vv[i].z; vv[i].w = i == in ? vn.w : vv[i].w;
+            }
+            if (h % (hq / hkv) == 0)
+                *reinterpret_cast<float4 *>(rf.vc_w + (((size_t)b * hkv + kvh) * (size_t)tmax + (key0 + jn)) * kD + 4 * lane) = vn;
+        }
     }
     // scores: one key per group of 8 lanes, 32 keys per pass
 #pragma unroll
@@ -380,11 +467,49 @@ extern "C" void cq_attention_split(const float *q, const float *k_cache, const f
     }
     const dim3 grid(hq, (tmax + kChunk - 1) / kChunk, batch * tq);
     const int eager = batch * tq <= 2 ? 1 : 0;
+    const RopeFused none{};
     if (out_q8)
-        cq_launch_k(attention_split_kernel<true>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos, scratch,
-                    counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks, eager);
+        cq_launch_k(attention_split_kernel<true, false>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos,
+                    scratch, counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks, eager, none);
     else
-        cq_launch_k(attention_split_kernel<false>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos,
-                    scratch, counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks, eager);
+        cq_launch_k(attention_split_kernel<false, false>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q, k_cache, v_cache, out, pos,
+                    scratch, counters, tq, hq, hkv, tmax, scale, q_stride, out_blocks, eager, none);
     cq_check_launch("attention_split");
+}
+
+extern "C" void cq_rope_attention_split(const float *q, const float *k, const float *v, float *q_rot, const float *cosv, const float *sinv,
+                                        float *k_cache, float *v_cache, void *out, int out_q8, const int *pos, float *scratch,
+                                        int *counters, int batch, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride,
+                                        int k_stride, int v_stride, int out_blocks, void *stream) {
+    if (!attention_args_ok(q, k_cache, v_cache, out, pos, batch, 1, hq, hkv, head_dim, tmax)) return;
+    if (!scratch || !counters || !k || !v || !cosv || !sinv || (out_q8 && out_blocks < hq * 4) || batch > 65535 ||
+        (q_stride | k_stride | v_stride) % 4 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)q_rot) & 15) || q_rot == q) {
+        cq_set_status(CQ_ERR_BAD_ARG, "rope_attention_split: null pointer, short container row, or rows not 16-byte aligned");
+        return;
+    }
+    const dim3 grid(hq, (tmax + kChunk - 1) / kChunk, batch);
+    const int eager = batch <= 2 ? 1 : 0;
+    const RopeFused rf{q_rot, k, v, cosv, sinv, k_cache, v_cache, k_stride, v_stride};
+    if (out_q8)
+        cq_launch_k(attention_split_kernel<true, true>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q,
+                    (const float *)k_cache, (const float *)v_cache, out, pos, scratch, counters, 1, hq, hkv, tmax, scale, q_stride,
+                    out_blocks, eager, rf);
+    else
+        cq_launch_k(attention_split_kernel<false, true>, grid, dim3(kSplitThreads), 0, (cudaStream_t)stream, q,
+                    (const float *)k_cache, (const float *)v_cache, out, pos, scratch, counters, 1, hq, hkv, tmax, scale, q_stride,
+                    out_blocks, eager, rf);
+    cq_check_launch("rope_attention_split");
+}
+
+// 1 if a fused rope + attention launch met a position beyond the cache since the last query (read and cleared by
+// cq_glue_position_overflow_flag).
+int cq_attn_position_overflow_take() {
+    int v = 0;
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(&v, g_attn_pos_overflow, sizeof(int)) != cudaSuccess) return 0;
+    if (v) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_attn_pos_overflow, &zero, sizeof(int));
+    }
+    return v;
 }

@@ -100,6 +100,22 @@ static inline cudaError_t cq_launch_k(void (*kernel)(P...), dim3 grid, dim3 bloc
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(a)...);
 }
 
+// The same for a kernel whose CTAs form thread-block clusters of `cluster_x` (gridDim.x a multiple of it).
+template <typename... P, typename... A>
+static inline cudaError_t cq_launch_cluster_k(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_x,
+                                              A... a) {
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attrs[2];
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)cluster_x; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = cq_pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(a)...);
+}
+
 // ---- device helpers ----
 __device__ __forceinline__ int cq_dp4a(int a, int b, int c) { return __dp4a(a, b, c); }
 __device__ __forceinline__ int cq_dp4a_u(unsigned a, int b, int c) {   // unsigned bytes x signed bytes

@@ -21,6 +21,8 @@
 #include "gemv_mma2.cuh"
 #include "gemv_plan.cuh"
 #include "tensor_map.cuh"
+#include <mutex>
+#include <vector>
 
 namespace {
 
@@ -61,7 +63,7 @@ constexpr int g_force_ctas_per_sm = 0;
 
 // Read-only plan query (cq_mmvq_plan): when set, the launch helpers below record what they would launch and return.
 thread_local int *g_plan_out = nullptr;
-enum { kPlanStaged = 0, kPlanMma = 1, kPlanMma2 = 2, kPlanMma2Split = 3 };
+enum { kPlanStaged = 0, kPlanMma = 1, kPlanMma2 = 2, kPlanMma2Split = 3, kPlanMma2Cluster = 4 };
 inline bool record_plan(int kind, int rows_per_batch, int grid, int threads) {
     if (!g_plan_out) return false;
     g_plan_out[0] = kind; g_plan_out[1] = rows_per_batch; g_plan_out[2] = grid; g_plan_out[3] = threads;
@@ -143,11 +145,41 @@ bool launch_mma(const void *w, const void *y, void *dst, int out_kind, int K, in
 // ---- tensor-core variant with warp-private tiles (gemv_mma2.cuh); same bits again ----
 int g_mma_kernel = 0;           // 0: automatic, 1: only the CTA-shared kernel above, 2: the warp-private kernel wherever its shape rules allow
 
-template <int TYPE, bool SPLIT>
+// How many clusters of `cluster` CTAs (threads, dynamic shared memory as given) the device runs at once; cached per key.
+int max_active_clusters(const void *fn, int threads, int smem, int cluster) {
+    struct Key { const void *fn; int threads, smem, cluster, dev, val; };
+    static std::mutex mu;
+    static std::vector<Key> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        for (const Key &k : cache)
+            if (k.fn == fn && k.threads == threads && k.smem == smem && k.cluster == cluster && k.dev == dev) return k.val;
+    }
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr{};
+    cfg.gridDim = dim3((unsigned)cluster);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = (unsigned)cluster; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    std::lock_guard<std::mutex> lk(mu);
+    cache.push_back(Key{fn, threads, smem, cluster, dev, n});
+    return n;
+}
+
+int g_cluster_split = 1;         // 0: a tile's K shares go to warps of one CTA, else (default) to the CTAs of a cluster
+
+template <int TYPE, int MODE>
 __global__ void __launch_bounds__(cq_mma2::kMaxThreads, 2)
 gemv_mma2_kernel(const __grid_constant__ CUtensorMap tmap, const uint8_t *__restrict__ y, void *__restrict__ dst, int out_kind, int nunits,
                  int nrows, int stride_col_y, int stride_col_dst, int b, int spw) {
-    cq_mma2::gemv_mma2_body<TYPE, SPLIT>(&tmap, y, dst, out_kind, nunits, nrows, stride_col_y, stride_col_dst, b, spw, &g_gemv_timeout_flag);
+    cq_mma2::gemv_mma2_body<TYPE, MODE>(&tmap, y, dst, out_kind, nunits, nrows, stride_col_y, stride_col_dst, b, spw, &g_gemv_timeout_flag);
 }
 
 // Shape rules: K a whole number of 32-chunk groups (so the tree needs no padding; row sizes are then multiples of 16
@@ -156,7 +188,8 @@ gemv_mma2_kernel(const __grid_constant__ CUtensorMap tmap, const uint8_t *__rest
 // every warp whole tiles; otherwise the groups of a tile are spread over `spw` warps of a CTA.
 template <int TYPE>
 bool launch_mma2(const void *w, const void *y, void *dst, int out_kind, int K, int N, int sy, int sd, int B, cudaStream_t st, bool forced) {
-    static KernelEntry ke_whole{(const void *)gemv_mma2_kernel<TYPE, false>}, ke_split{(const void *)gemv_mma2_kernel<TYPE, true>};
+    static KernelEntry ke_whole{(const void *)gemv_mma2_kernel<TYPE, cq_mma2::kWhole>}, ke_split{(const void *)gemv_mma2_kernel<TYPE, cq_mma2::kSplit>},
+        ke_cluster{(const void *)gemv_mma2_kernel<TYPE, cq_mma2::kCluster>};
     using F = cq_mma2::Fmt<TYPE>;
     const int unit_elems = F::UNIT_BLOCKS * 32;
     const int row_bytes = K / cq_block_elems(TYPE) * cq_type_size(TYPE);
@@ -173,7 +206,29 @@ bool launch_mma2(const void *w, const void *y, void *dst, int out_kind, int K, i
     // L2 flush, us: 14336 -> 4096 Q4_K 25.8 against 37.4, Q6_K 37.1 / 39.0, Q8_0 32.9 / 37.1; 4096 -> 14336 Q4_K 18.1 / 25.7,
     // Q6_K 28.3 / 35.6, but Q8_0 23.7 / 20.1 (dp4a); 4096 -> 4096 Q4_K 16.7 / 12.9): leave those to them.
     if (!forced && (ntiles * spw < 8 * di.sms || (split && TYPE == CQ_Q8_0 && K < 8192))) return false;
-    if (split) {
+    // The spw shares of a tile in the spw CTAs of a cluster instead of spw warps of one CTA: a CTA then holds 1/spw of the
+    // activation tables and eight tiles at a time, where one CTA with all of a long row's K in shared memory leaves an SM with a
+    // single CTA of spw warps.  B200, 8 rows, isolated launch, us, CTA split / cluster split: 14336 -> 4096 Q4_K 25.7 / 16.4,
+    // Q6_K 36.9 / 26.4, Q8_0 33.3 / 27.4; 4096 -> 14336 Q4_K 18.1 / 16.7, Q6_K 28.2 / 25.9.
+    const bool cluster = split && spw >= 2 && g_cluster_split != 0;
+    if (cluster) {
+        // eight tiles at a time, fewer if that lets two CTAs share an SM (the group sums of Q8_0's short groups take room)
+        for (warps = cq_mma2::kMaxWarps; warps >= 4; --warps) {
+            smem = cq_mma2::smem_bytes<TYPE>(nblk / spw, warps, cq_mma2::red_floats(warps, ngroups) / 2);
+            if (2 * (smem + 1024) <= 228 * 1024) break;
+        }
+        if (warps < 4) {
+            warps = cq_mma2::kMaxWarps;
+            smem = cq_mma2::smem_bytes<TYPE>(nblk / spw, warps, cq_mma2::red_floats(warps, ngroups) / 2);
+        }
+        if (smem > di.smem_optin) return false;
+        ensure_smem_attr(&ke_cluster);
+        int nclusters = (ntiles + warps - 1) / warps;
+        const int fit = max_active_clusters((const void *)gemv_mma2_kernel<TYPE, cq_mma2::kCluster>, warps * 32, smem, spw);
+        if (fit <= 0) return false;
+        if (nclusters > fit) nclusters = fit;
+        grid = nclusters * spw;
+    } else if (split) {
         int slots = cq_mma2::kMaxWarps / spw;
         // keep at least about one CTA per SM: fewer tile slots per CTA when the tiles are few
         while (slots > 1 && (ntiles + slots - 1) / slots < di.sms) --slots;
@@ -201,16 +256,19 @@ bool launch_mma2(const void *w, const void *y, void *dst, int out_kind, int K, i
         }
         if (warps == 0) return false;
     }
-    if (record_plan(split ? kPlanMma2Split : kPlanMma2, cq_mma2::kTileRows, grid, warps * 32)) return true;
+    if (record_plan(cluster ? kPlanMma2Cluster : split ? kPlanMma2Split : kPlanMma2, cq_mma2::kTileRows, grid, warps * 32)) return true;
     CUtensorMap tmap;
     if (!cq_tmap::weight_map(w, row_bytes, N, F::RS, cq_mma2::kTileRows, 1, tmap)) return false;
-    if (split) {
+    if (cluster) {
+        cq_launch_cluster_k(gemv_mma2_kernel<TYPE, cq_mma2::kCluster>, dim3(grid), dim3(warps * 32), (size_t)smem, st, spw, tmap,
+                            (const uint8_t *)y, dst, out_kind, nunits, N, sy, sd, B, spw);
+    } else if (split) {
         ensure_smem_attr(&ke_split);
-        cq_launch_k(gemv_mma2_kernel<TYPE, true>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,
+        cq_launch_k(gemv_mma2_kernel<TYPE, cq_mma2::kSplit>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,
                     nunits, N, sy, sd, B, spw);
     } else {
         ensure_smem_attr(&ke_whole);
-        cq_launch_k(gemv_mma2_kernel<TYPE, false>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,
+        cq_launch_k(gemv_mma2_kernel<TYPE, cq_mma2::kWhole>, dim3(grid), dim3(warps * 32), (size_t)smem, st, tmap, (const uint8_t *)y, dst, out_kind,
                     nunits, N, sy, sd, B, 1);
     }
     return cq_check_launch("gemv (tensor core, warp tiles)");
@@ -411,6 +469,7 @@ extern "C" int cq_mmvq_plan(int wtype, int act, int ncols_x, int nrows_x, int b_
 extern "C" void cq_set_mma_min_batch(int rows) { g_mma_min_batch = rows < 0 ? 0 : rows; }
 // Which tensor-core GEMV may run: 0 automatic, 1 only the CTA-shared kernel, 2 the warp-private kernel wherever K is a
 // whole number of 2048-element groups (1024 for Q8_0) and its activation tables fit in shared memory.  Same bits either way.
+extern "C" void cq_set_cluster_split(int policy) { g_cluster_split = policy < 0 || policy > 2 ? 1 : policy; }
 extern "C" void cq_set_mma_kernel(int which) { g_mma_kernel = which < 0 || which > 2 ? 0 : which; }
 
 // 1 if any GEMV launch on the current device gave up waiting for a staged copy (synchronises the device).

@@ -190,7 +190,29 @@ template <> struct Unit<CQ_Q6_K> {
 // nunits: units per weight row (a multiple of 8: groups of 32 chunks are whole).
 // nunits: units per weight row (a multiple of 8: groups of 32 chunks are whole).  SPLIT: `spw` warps share a tile, each
 // takes nunits / spw consecutive units (a whole number of groups); else a warp owns whole tiles (spw is ignored).
-template <int TYPE, bool SPLIT>
+// MODE: kWhole - a warp owns whole tiles;  kSplit - the spw warps of a tile sit in one CTA;  kCluster - they sit in the spw
+// CTAs of a thread-block cluster, CTA rank r taking share r of K for all of its warps' tiles: a CTA then stages only its own
+// 1/spw of the activations (the whole K of a long row does not fit twice into an SM), the group sums travel to the rank-0
+// CTA through distributed shared memory and the cluster meets at its hardware barrier once per round of tiles.
+constexpr int kWhole = 0, kSplit = 1, kCluster = 2;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_id_x() { uint32_t r; asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_count_x() { uint32_t r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `local` (a shared-memory address of this CTA) in the shared memory of CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store_f4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int TYPE, int MODE>
 __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *__restrict__ y, void *__restrict__ dst,
                                                int out_kind, int nunits, int nrows, int stride_col_y, int stride_col_dst, int b,
                                                int spw, int *timeout_flag) {
@@ -200,7 +222,11 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
     uint8_t *smem = smem_raw + ((128u - (cq_smem_u32(smem_raw) & 127u)) & 127u);     // tiled TMA destinations: 128-byte aligned
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t = lane & 3;
     const int nwarps = blockDim.x >> 5;
-    const int nblk = nunits * UB;
+    if (MODE == kWhole) spw = 1;
+    // blocks of K whose activations this CTA keeps: all of them, or the share of its cluster rank
+    const int gi_cta = MODE == kCluster ? (int)cluster_ctarank() : 0;
+    const int nblk = MODE == kCluster ? nunits * UB / spw : nunits * UB;
+    const int blk0 = gi_cta * nblk;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem) + w * S;               // this warp's stage barriers
     uint8_t *aq = smem + 256;
     float *asc = reinterpret_cast<float *>(aq + nblk * 256);
@@ -209,11 +235,13 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
     float4 *red = reinterpret_cast<float4 *>(ring0 + nwarps * S * stage_bytes<TYPE>());      // [2][tile slot][group][lane]
 
     const int ntiles = (nrows + kTileRows - 1) / kTileRows;
-    if (!SPLIT) spw = 1;
-    const int slots = nwarps / spw;                 // tiles a CTA works on at a time
-    const int ts = w / spw, gi = w - ts * spw;      // this warp's tile slot and its share of the tile's units
+    const int slots = MODE == kCluster ? nwarps : nwarps / spw;        // tiles a CTA (cluster) works on at a time
+    const int ts = MODE == kCluster ? w : w / spw;                     // this warp's tile slot
+    const int gi = MODE == kCluster ? gi_cta : w - ts * spw;           // and its share of the tile's units
     const int upw = nunits / spw, u_first = gi * upw, ngroups = nunits >> 3;
-    const int tile0 = blockIdx.x * slots + ts, tstride = gridDim.x * slots;      // tiles tile0, tile0 + tstride, ...
+    const int team = MODE == kCluster ? (int)cluster_id_x() : (int)blockIdx.x;
+    const int nteams = MODE == kCluster ? (int)cluster_count_x() : (int)gridDim.x;
+    const int tile0 = team * slots + ts, tstride = nteams * slots;      // tiles tile0, tile0 + tstride, ...
 
     if (lane == 0) {
         for (int s = 0; s < S; ++s) cq_mbar_init(&bars[s], 1);
@@ -239,12 +267,14 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
     cq_pdl_wait();
 
     // activations of all 8 columns into shared memory: int8 values [block][column][32] and the scale table
+    // (unrolled: the loads of several containers are in flight together - the loop is a chain of L2 round trips otherwise)
+#pragma unroll 4
     for (int e = tid; e < nblk * 8; e += blockDim.x) {
         const int blk = e >> 3, col = e & 7;
         uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         float d = 0.f, s = 0.f;
         if (col < b) {
-            const uint8_t *p = y + ((int64_t)col * stride_col_y + blk) * CQ_Q8_BYTES;
+            const uint8_t *p = y + ((int64_t)col * stride_col_y + blk0 + blk) * CQ_Q8_BYTES;
             const int ds = cq_ld_global_i32(p);
             d = __low2float(*reinterpret_cast<const __half2 *>(&ds));
             int sq = 0;
@@ -258,19 +288,27 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
         if constexpr (F::ASC == 2) reinterpret_cast<float2 *>(asc)[e] = make_float2(d, s);
         else asc[e] = d;
     }
-    __syncthreads();        // the only CTA-wide barrier: the activation tables are complete
-    if (ts >= slots) return;        // a warp beyond the last whole tile slot (never launched by the host's plan)
+    if constexpr (MODE == kCluster) {
+        cluster_sync_all();     // the tables are complete, and every CTA of the cluster runs (its shared memory may be written)
+    } else {
+        __syncthreads();        // the only CTA-wide barrier: the activation tables are complete
+        if (ts >= slots) return;        // a warp beyond the last whole tile slot (never launched by the host's plan)
+    }
+    const uint32_t red_rank0 = MODE == kCluster ? cluster_map(cq_smem_u32(red), 0) : 0u;
 
     int stage = 0, buf = 0;
     unsigned phase = 0;
     bool dead = false;      // a bounded wait gave up: stop computing, keep meeting the other warps at their barriers
     // Every warp of a tile slot runs the same number of rounds (the slot's warps share `tile`), so the barriers pair up.
-    for (int tile = tile0; tile < ntiles; tile += tstride) {
+    // kCluster: every warp of the cluster runs as many rounds as the first tile slot (the cluster barrier counts them all);
+    // a warp whose own tile lies past the matrix only keeps the appointments.
+    for (int tile = tile0; (MODE == kCluster ? tile - ts : tile) < ntiles; tile += tstride) {
         float tot[4] = {0.f, 0.f, 0.f, 0.f};
         float s3[4], s4[4], s5[4];
-        const uint8_t *aq_u = aq + (size_t)u_first * UB * 256;
-        const float *asc_u = asc + (size_t)u_first * UB * 8 * F::ASC;
-        for (int u = 0; u < upw; ++u, aq_u += UB * 256, asc_u += UB * 8 * F::ASC) {
+        const uint8_t *aq_u = aq + (MODE == kCluster ? (size_t)0 : (size_t)u_first * UB * 256);
+        const float *asc_u = asc + (MODE == kCluster ? (size_t)0 : (size_t)u_first * UB * 8 * F::ASC);
+        const int nu = (MODE == kCluster && tile >= ntiles) ? 0 : upw;
+        for (int u = 0; u < nu; ++u, aq_u += UB * 256, asc_u += UB * 8 * F::ASC) {
             if (!dead && !__all_sync(0xffffffffu, cq_mbar_wait_bounded(&bars[stage], phase))) {
                 dead = true;
                 if (lane == 0) atomicExch(timeout_flag, 1);
@@ -306,7 +344,10 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
                     } else {        // a whole group of 32 chunks: groups are added in index order
 #pragma unroll
                         for (int i = 0; i < 4; ++i) uv[i] = s5[i] + uv[i];
-                        if constexpr (SPLIT) {
+                        if constexpr (MODE == kCluster) {
+                            cluster_store_f4(red_rank0 + (uint32_t)(((ts * ngroups + ((u_first + u) >> 3)) * 32 + lane) * 16),
+                                             uv[0], uv[1], uv[2], uv[3]);
+                        } else if constexpr (MODE == kSplit) {
                             red[((buf * slots + ts) * ngroups + ((u_first + u) >> 3)) * 32 + lane] = make_float4(uv[0], uv[1], uv[2], uv[3]);
                         } else {
 #pragma unroll
@@ -316,7 +357,22 @@ __device__ __forceinline__ void gemv_mma2_body(const void *tmap, const uint8_t *
                 }
             }
         }
-        if constexpr (SPLIT) {
+        if constexpr (MODE == kCluster) {
+            // the cluster meets: every group sum of this round has reached the rank-0 CTA, whose warps add them in order
+            cluster_sync_all();
+            const bool more = tile - ts + tstride < ntiles;
+            if (gi == 0 && tile < ntiles) {
+                const float4 *rp = red + (ts * ngroups) * 32 + lane;
+                float4 a = rp[0];
+                for (int gq = 1; gq < ngroups; ++gq) {
+                    const float4 v = rp[gq * 32];
+                    a.x = a.x + v.x; a.y = a.y + v.y; a.z = a.z + v.z; a.w = a.w + v.w;
+                }
+                tot[0] = a.x; tot[1] = a.y; tot[2] = a.z; tot[3] = a.w;
+            }
+            if (more) cluster_sync_all();       // the sums have been read: the next round may overwrite them
+            if (gi != 0 || tile >= ntiles) continue;
+        } else if constexpr (MODE == kSplit) {
             // the warps of this tile slot meet (named barrier 1 + slot); the slot's first warp adds the groups in order
             asm volatile("bar.sync %0, %1;" ::"r"(1 + ts), "r"(spw * 32) : "memory");
             if (gi != 0) { buf ^= 1; continue; }

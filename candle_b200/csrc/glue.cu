@@ -21,6 +21,9 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, c
                                                         float eps) {
     __shared__ float red[32];
     const int n4 = d >> 2, tid = threadIdx.x;
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+    // the norm weights are not written by any kernel of the stream: fetch this thread's first one before the dependency wait
+    const float4 g_first = tid < n4 ? w4[tid] : make_float4(0.f, 0.f, 0.f, 0.f);
     cq_pdl_launch_dependents();
     cq_pdl_wait();
     float4 *xr = reinterpret_cast<float4 *>(x + (size_t)blockIdx.x * d);
@@ -45,14 +48,13 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, c
 #pragma unroll
     for (int i = 1; i < 32; ++i) s += red[i];
     const float inv = rsqrtf(__fadd_rn(__fdiv_rn(s, (float)d), eps));
-    const float4 *w4 = reinterpret_cast<const float4 *>(w);
     const int n4_out = Q8 ? (k_padded >> 2) : n4;
     for (int i0 = 0; i0 < n4_out; i0 += 1024) {         // whole warps stay together for the block quantizer
         const int i = i0 + tid;
         float r[4] = {0.f, 0.f, 0.f, 0.f};
         if (i < n4) {
             const float4 v = (i == tid) ? first : xr[i];      // later ones were written by this same thread
-            const float4 g = w4[i];
+            const float4 g = (i == tid) ? g_first : w4[i];
             r[0] = __fmul_rn(__fmul_rn(v.x, inv), g.x); r[1] = __fmul_rn(__fmul_rn(v.y, inv), g.y);
             r[2] = __fmul_rn(__fmul_rn(v.z, inv), g.z); r[3] = __fmul_rn(__fmul_rn(v.w, inv), g.w);
         }
@@ -307,12 +309,17 @@ extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const f
 
 // 1 if a rope / KV-store launch on the current device met a position at or beyond tmax since the last query
 // (synchronises the device and clears the flag).
+int cq_attn_position_overflow_take();       // attn.cu: the same check inside the fused rope + attention kernel
 extern "C" int cq_glue_position_overflow_flag(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_glue_pos_overflow, sizeof v) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+    const int va = cq_attn_position_overflow_take();
     if (v) {
         const int z = 0;
         cudaMemcpyToSymbol(g_glue_pos_overflow, &z, sizeof z);
+    }
+    v |= va;
+    if (v) {
         cq_set_status(CQ_ERR_BAD_ARG, "rope: a position reached the end of the KV cache / rotary tables");
     }
     return v;

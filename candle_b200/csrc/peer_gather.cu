@@ -100,7 +100,90 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
     }
 }
 
+// ---- exchange of rows that each belong to ONE rank (expert-parallel mixture-of-experts) ----
+// Every row of src / dst [rows, n] is produced by exactly one rank - the one that holds the row's expert: owner[j] is that
+// expert's index relative to this rank's first expert, so this rank owns row j iff 0 <= owner[j] < n_owned.  A thread stores
+// the words of the rows this rank owns into the staging areas of all other ranks (and into its own result), then polls
+// the slots of the rows it does not own.  One slot per word (a row has a single writer), the same {word, epoch} slots,
+// epoch counter, two areas by parity and bounded polls as the gather above; each row crosses a link once, nothing else does
+// (candle's fused MoE block has no multi-GPU form; an all-reduce of the same buffer would send mostly zeros).
+__global__ void __launch_bounds__(256) peer_exchange_rows_kernel(const uint32_t *__restrict__ src, const int *__restrict__ owner,
+                                                                 int n_owned, PeerPtrs stage, uint32_t *__restrict__ dst,
+                                                                 unsigned *state, int rows, int n, int rank, int world) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    const unsigned epoch = *(volatile unsigned *)state + 1u;
+    void *const *area = stage.p[epoch & 1u];
+    const int64_t total = (int64_t)rows * n;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
+    // pass 1: the rows this rank owns, to everybody
+    for (int64_t i = tid; i < total; i += nthr) {
+        const int j = (int)(i / n);
+        if ((unsigned)owner[j] >= (unsigned)n_owned) continue;
+        const uint32_t v = src[i];
+        dst[i] = v;
+        for (int q = 1; q < world; ++q) st_slot((uint2 *)area[(rank + q) % world] + i, v, epoch);
+    }
+    // pass 2: the rows of the others, as they arrive
+    const uint2 *mine = (const uint2 *)area[rank];
+    bool gave_up = false;
+    const long long limit = g_peer_gather_limit;
+    constexpr int U = 4;
+    for (int64_t i0 = tid; i0 < total && !gave_up; i0 += U * nthr) {
+        uint2 v[U];
+        bool want[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * nthr;
+            want[u] = i < total && (unsigned)owner[(int)(i / n)] >= (unsigned)n_owned;
+            if (want[u]) v[u] = ld_slot(mine + i);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!want[u] || gave_up) continue;
+            const int64_t i = i0 + u * nthr;
+            if (v[u].y != epoch) {
+                const long long t0 = clock64();
+                while ((v[u] = ld_slot(mine + i)).y != epoch) {
+                    if (clock64() - t0 > limit) { gave_up = true; break; }
+                }
+                if (gave_up) continue;
+            }
+            dst[i] = v[u].x;
+        }
+    }
+    if (gave_up) atomicExch(&g_peer_gather_timeout, 1);
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(&state[1], 1u) == gridDim.x - 1) {
+        state[1] = 0u;
+        __threadfence();
+        *(volatile unsigned *)state = epoch;
+    }
+}
+
 }  // namespace
+
+extern "C" void cq_peer_exchange_rows(const void *src, const int *owner, int n_owned, void *const *peer_stage, void *dst, void *state,
+                                      int rows, int n, int rank, int world, void *stream) {
+    if (!src || !owner || !peer_stage || !dst || !state || rows <= 0 || n <= 0 || n_owned < 0 || world < 1 || world > CQ_MAX_PEERS ||
+        rank < 0 || rank >= world) {
+        cq_set_status(CQ_ERR_BAD_ARG, "peer row exchange: null pointer or inconsistent shape");
+        return;
+    }
+    PeerPtrs s{};
+    for (int e = 0; e < 2; ++e)
+        for (int p = 0; p < world; ++p) {
+            void *a = peer_stage[e * CQ_MAX_PEERS + p];
+            if (!a || (uintptr_t)a % 8 != 0) { cq_set_status(CQ_ERR_BAD_ARG, "peer row exchange: missing or misaligned staging pointer"); return; }
+            s.p[e][p] = a;
+        }
+    const int64_t total = (int64_t)rows * n;
+    int grid = (int)((total + 255) / 256);
+    if (grid > 64) grid = 64;
+    cq_launch_k(peer_exchange_rows_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const uint32_t *)src, owner, n_owned, s,
+                (uint32_t *)dst, (unsigned *)state, rows, n, rank, world);
+    cq_check_launch("peer row exchange");
+}
 
 extern "C" size_t cq_peer_gather_stage_bytes(int rows, int n_local, int world) {
     if (rows <= 0 || n_local <= 0 || world < 1) return 0;

@@ -116,6 +116,7 @@ class LlamaShapedDecoder:
         self._pos_host = 0      # host copy of pos: positions are checked against max_pos before anything is launched
         self._graph = None
         self.fuse_quantize = True       # decode steps: producers store Q8_1 containers directly
+        self.fuse_rope = True           # decode steps: rotary embedding + cache update inside the attention launch
         self._att_scratch = None        # split-context attention: partial results and arrival counters
         self.tap = None                 # tests set a dict here: forward() then records copies of its intermediate tensors
         if world > 1:       # ranks build their shards at different speeds: line up before the first gather, whose polls are bounded
@@ -173,6 +174,27 @@ class LlamaShapedDecoder:
             lib.cq_attention_f32(qk.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
                                  B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, scale, q_stride, st)
 
+    def _rope_attention(self, qk: torch.Tensor, v: torch.Tensor, L, B: int, out: torch.Tensor, q8: bool, li: int) -> None:
+        """One query per sequence: rotary embedding of q and the new key, the cache update and the attention as one launch
+        (the bits of `cq_rope_store_kv_f32` followed by `_attention`)."""
+        cfg, lib, hd = self.cfg, capi.lib(), self.cfg.head_dim
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        q_cols, kv_cols = self.hq_l * hd, self.hkv_l * hd
+        stride = q_cols + kv_cols
+        if self._att_scratch is None:
+            n = lib.cq_attention_split_scratch_floats(64, 1, self.hq_l, cfg.max_pos)
+            self._att_scratch = (torch.empty(n, dtype=torch.float32, device=self.device),
+                                 torch.zeros(64 * self.hq_l, dtype=torch.int32, device=self.device))
+        scratch, counters = self._att_scratch
+        q_rot = torch.empty_like(qk) if self.tap is not None else None
+        lib.cq_rope_attention_split(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), None if q_rot is None else q_rot.data_ptr(),
+                                    self.cos.data_ptr(), self.sin.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
+                                    out.data_ptr(), 1 if q8 else 0, self.pos.data_ptr(), scratch.data_ptr(), counters.data_ptr(),
+                                    B, self.hq_l, self.hkv_l, hd, cfg.max_pos, 1.0 / math.sqrt(hd), stride, stride, kv_cols,
+                                    q_cols // 32, st)
+        if q_rot is not None:
+            self._rec(f"{li}.q_rot", q_rot)
+
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens: int64 [B, T] at cache positions pos .. pos+T-1.  Returns the greedy next token [B] and advances pos.
 
@@ -203,14 +225,19 @@ class LlamaShapedDecoder:
                     h = self._norm(x, delta, L.attn_norm)
                     qk, v = L.wqk.forward(h), L.wv.forward(h)                           # [R, q_cols + kv_cols], [R, kv_cols]
                 self._rec(f"{li}.h_attn", h), self._rec(f"{li}.qk", qk), self._rec(f"{li}.v", v)
-                lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), self.cos.data_ptr(),
-                                         self.sin.data_ptr(), self.pos.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
-                                         B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, q_cols + kv_cols, q_cols + kv_cols,
-                                         kv_cols, st)
-                self._rec(f"{li}.q_rot", qk)
+                one_launch = self.fuse_rope and T == 1 and hd == 128     # rope + KV store inside the attention kernel
+                if not one_launch:
+                    lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), self.cos.data_ptr(),
+                                             self.sin.data_ptr(), self.pos.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),
+                                             B, T, self.hq_l, self.hkv_l, hd, cfg.max_pos, q_cols + kv_cols, q_cols + kv_cols,
+                                             kv_cols, st)
+                    self._rec(f"{li}.q_rot", qk)
                 if fused:
                     att = torch.empty((R, q_cols // 32 * 36), **u8)
-                    self._attention(qk, L, B, T, att, True)
+                    if one_launch:
+                        self._rope_attention(qk, v, L, B, att, True, li)
+                    else:
+                        self._attention(qk, L, B, T, att, True)
                     delta = L.wo.forward_q8_1(self.gather(att))
                     h = self._norm_q8(x, delta, L.ffn_norm)
                     gu = L.gate_up.forward_q8_1(h)                                      # [R, 2 * f_l]
@@ -219,7 +246,10 @@ class LlamaShapedDecoder:
                     delta = self.gather(L.down.forward_q8_1(self.gather(a)))
                 else:
                     att = torch.empty((R, q_cols), **f32)
-                    self._attention(qk, L, B, T, att, False)
+                    if one_launch:
+                        self._rope_attention(qk, v, L, B, att, False, li)
+                    else:
+                        self._attention(qk, L, B, T, att, False)
                     self._rec(f"{li}.att", att)
                     delta = L.wo.forward(self.gather(att))
                     self._rec(f"{li}.x_mid", x), self._rec(f"{li}.wo", delta)

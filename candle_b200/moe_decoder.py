@@ -112,6 +112,11 @@ class MoeShapedDecoder:
         self._att_scratch = None
         self.tap = None                 # tests set a dict here: forward() then records copies of its intermediate tensors
         self.hq_l, self.hkv_l = cfg.n_heads, cfg.n_kv_heads      # attention is replicated: every rank owns all heads
+        if world > 1:       # the peer-memory exchange of expert outputs (library collectives when peers cannot be mapped)
+            from .parallel import make_gatherer
+            self.gather = make_gatherer(group, world, self.device)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=group)
 
     # the norm and attention helpers are those of the dense harness
     _norm = LlamaShapedDecoder._norm
@@ -166,7 +171,16 @@ class MoeShapedDecoder:
             y = L.down.indexed_moe_forward(a, local, zero_init=zero)                              # [R, k, d]
         self._rec(key + "gu", gu.view(R, k, 2 * f)), self._rec(key + "act", a), self._rec(key + "down", y)
         if self.world > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)                            # one value plus zeros: exact
+            # every (token, slot) row of y was computed by the rank that holds its expert: all-gather by slot, then the
+            # slot-order sum below.  Few rows: one peer-memory kernel; many: an all-reduce (one value plus zeros: exact).
+            got = None
+            xr = getattr(getattr(self, "gather", None), "exchange_rows", None)
+            if xr is not None:
+                got = xr(y.view(R * k, -1), local.reshape(-1).contiguous(), self.e_local)
+            if got is None:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                y = got.view(R, k, -1)
         return (y * w.unsqueeze(-1)).sum(dim=1)
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:

@@ -89,8 +89,8 @@ class PeerGatherer(Gatherer):
         self._slots: dict = {}
         self._last = None
 
-    def _new_slot(self, rows: int, n_local: int, dtype):
-        nbytes = self._capi.lib().cq_peer_gather_stage_bytes(rows, n_local, self.world)
+    def _new_slot(self, rows: int, n_local: int, dtype, writers: int | None = None):
+        nbytes = self._capi.lib().cq_peer_gather_stage_bytes(rows, n_local, self.world if writers is None else writers)
         stage = self._symm.empty((nbytes,), dtype=torch.uint8, device=self.device)
         hdl = self._symm.rendezvous(stage, group=self._group_name)
         stage.zero_()
@@ -135,6 +135,44 @@ class PeerGatherer(Gatherer):
                                                rows, n_local, self.world * n_local, self.rank, self.world,
                                                torch.cuda.current_stream().cuda_stream)
         return full if full.dtype == dtype else full.view(dtype)
+
+    def exchange_rows(self, local: torch.Tensor, owner: torch.Tensor, n_owned: int):
+        """Rows of `local` [rows, n] (4-byte elements) that each belong to one rank - this rank owns row j iff
+        0 <= owner[j] < n_owned (`owner`: int32 [rows] on the device) - as one kernel over peer memory: every rank ends up
+        with all rows.  Returns None when the buffer is too large for the slot protocol (the caller then uses a library
+        collective); the staging areas of a shape are made on first use, outside CUDA-graph capture."""
+        if self.world == 1:
+            return local
+        if local.dim() != 2 or local.element_size() != 4 or not local.is_contiguous():
+            raise ValueError("peer row exchange takes a contiguous 2-d tensor of 4-byte elements")
+        if owner.dtype != torch.int32 or owner.numel() != local.shape[0] or not owner.is_contiguous():
+            raise ValueError("peer row exchange: owner must be a contiguous int32 tensor with one entry per row")
+        if local.numel() * (self.world - 1) > self.MAX_SENT_WORDS * self.world:
+            self._last = None
+            return None
+        rows, n = local.shape
+        key = (rows, n, local.dtype, "rows")
+        if key not in self._slots:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("a new exchange shape inside CUDA-graph capture: run the step once before capturing")
+            areas = [self._new_slot(rows, n, local.dtype, 1) for _ in range(2)]
+            ptrs = (ctypes.c_void_p * (2 * self._capi.MAX_PEERS))()
+            for e in range(2):
+                for p, a in enumerate(areas[e]):
+                    ptrs[e * self._capi.MAX_PEERS + p] = a
+            outs = [torch.empty((rows, n), dtype=local.dtype, device=self.device) for _ in range(2)]
+            self._slots[key] = [outs, 0, ptrs]
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        entry = self._slots[key]
+        if self._last == key:
+            entry[1] ^= 1
+        self._last = key
+        full, ptrs = entry[0][entry[1]], entry[2]
+        self._capi.lib().cq_peer_exchange_rows(local.data_ptr(), owner.data_ptr(), int(n_owned), ptrs, full.data_ptr(),
+                                                self._state.data_ptr(), rows, n, self.rank, self.world,
+                                                torch.cuda.current_stream().cuda_stream)
+        return full
 
     def check(self) -> None:
         """Raises if any gather so far gave up waiting for another rank (synchronises the device)."""

@@ -266,6 +266,15 @@ size_t cq_attention_split_scratch_floats(int batch, int tq, int hq, int tmax);
 void cq_attention_split(const float *q, const float *k_cache, const float *v_cache, void *out, int out_q8, const int *pos,
                         float *scratch, int *counters, int batch, int tq, int hq, int hkv, int head_dim, int tmax, float scale,
                         int q_stride, int out_blocks, void *stream);
+/* The same with the step before it folded in, for one query per sequence (a decode step): interleaved rotary embedding
+ * of q and of the new key (rows of q / k / v: the projection outputs, k_stride / v_stride floats apart), the new key and
+ * value stored into the caches at position pos[0], then the attention.  q is not changed; q_rot (optional, rows of
+ * q_stride floats, not q itself) receives the rotated queries.  Same bits as cq_rope_store_kv_f32 followed by
+ * cq_attention_split.  A position beyond tmax is skipped and reported through cq_glue_position_overflow_flag. */
+void cq_rope_attention_split(const float *q, const float *k, const float *v, float *q_rot, const float *cosv, const float *sinv,
+                             float *k_cache, float *v_cache, void *out, int out_q8, const int *pos, float *scratch, int *counters,
+                             int batch, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, int k_stride,
+                             int v_stride, int out_blocks, void *stream);
 void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
                           float *k_cache, float *v_cache, int batch, int t, int hq, int hkv, int head_dim, int tmax,
                           int q_stride, int k_stride, int v_stride, void *stream);
@@ -285,6 +294,12 @@ void cq_silu_mul_f32(const float *gate_up, float *out, int rows, int f, void *st
 size_t cq_peer_gather_stage_bytes(int rows, int n_local, int world);
 void cq_peer_gather_words(const void *src, int src_stride, void *const *peer_stage, void *dst, void *state, int rows,
                           int n_local, int n_total, int rank, int world, void *stream);
+/* Rows that each belong to one rank (expert-parallel MoE: the rank holding the row's expert): rank r owns row j iff
+ * 0 <= owner[j] < n_owned (owner: device int32 [rows], the expert index relative to the rank's first expert).  Owned rows
+ * of src [rows, n] (32-bit words) go to every rank's dst [rows, n]; the others are received.  Staging areas: as above, two
+ * per site, rows * n * 8 bytes each (cq_peer_gather_stage_bytes(rows, n, 1)); same epoch state, limits and give-up flag. */
+void cq_peer_exchange_rows(const void *src, const int *owner, int n_owned, void *const *peer_stage, void *dst, void *state,
+                           int rows, int n, int rank, int world, void *stream);
 int cq_peer_gather_timeout_flag(void);
 void cq_peer_gather_clear_timeout(void);                /* after a reported give-up */
 void cq_peer_gather_set_limit_clocks(long long clocks); /* how long a poll may last (default 2e9 SM clocks) */
@@ -325,6 +340,11 @@ void cq_set_mma_min_batch(int rows);
  * matrices with enough 16-row tiles, the CTA-shared one (gemv_mma.cuh) otherwise; 1: only the CTA-shared kernel; 2: the
  * warp-private kernel whenever its shape rules hold.  All GEMV kernels produce the same bits. */
 void cq_set_mma_kernel(int which);
+/* Where the warp-private tensor-core GEMV spreads the K range of a 16-row tile over several workers (matrices with few
+ * rows), those workers are warps of one CTA or the CTAs of a thread-block cluster (each CTA then keeps only its share of the
+ * activations; sums through distributed shared memory; same bits).  0: warps of one CTA, anything else (default): a
+ * cluster.  cq_mmvq_plan reports kind 4 for the cluster form. */
+void cq_set_cluster_split(int policy);
 
 /* De-quantize n_rows rows of k elements (replaces candle-kernels/src/quantized.cu:759-1460 `dequantize_block_*`), and
  * the gathered-row form behind QTensor::embedding.  cq_get_rows_bad_id: 1 if an id was out of range since the last query
@@ -338,7 +358,8 @@ int cq_get_rows_bad_id(void);
 void cq_convert_plain(int ggml_dtype, const void *src, void *out, int out_kind, int64_t n, void *stream);
 
 /* Read-only: what cq_mmvq would launch for these arguments, nothing is launched.  out[0] kernel (0 staged dp4a GEMV,
- * 1 tensor-core GEMV with CTA-shared items, 2 tensor-core GEMV with warp-private tiles, 3 the same with the groups of a tile spread over the warps of a CTA), out[1] weight rows per staged batch (rows per CTA for the tensor-core kernel), out[2] grid,
+ * 1 tensor-core GEMV with CTA-shared items, 2 tensor-core GEMV with warp-private tiles, 3 the same with the groups of a tile spread over the warps of a CTA, 4 over the CTAs of a
+ * thread-block cluster), out[1] weight rows per staged batch (rows per CTA for the tensor-core kernel), out[2] grid,
  * out[3] threads per CTA.  Returns 0, or -1 when cq_mmvq would reject the arguments.  No counterpart in the reference
  * (its launch shape is fixed: one CTA per weight row, candle-kernels/src/mmvq_gguf.cu:915-1008); tests use it to show
  * which kernel instantiations a parity case exercised. */

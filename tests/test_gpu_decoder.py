@@ -89,6 +89,80 @@ def test_split_attention_matches_dense_reference(lib, cuda_dev, pos0):
     assert torch.equal(o8, _quantize_rows(lib, out))
 
 
+@pytest.mark.parametrize("pos0", [0, 5, 127, 128, 300, 699])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_rope_attention_in_one_launch_gives_the_bits_of_the_two_launches(lib, cuda_dev, pos0, batch):
+    """cq_rope_attention_split against cq_rope_store_kv_f32 + cq_attention_split on the same inputs: attention output
+    (f32 and Q8_1), both caches and the rotated queries bit for bit; the inputs themselves stay untouched."""
+    torch.manual_seed(100 + pos0)
+    st = torch.cuda.current_stream().cuda_stream
+    B, Hq, Hkv, D, Tmax = batch, 8, 2, 128, 700
+    q_cols, kv_cols = Hq * D, Hkv * D
+    qk = torch.randn(B, q_cols + kv_cols, device=cuda_dev)
+    v = torch.randn(B, kv_cols, device=cuda_dev)
+    kc0, vc0 = torch.randn(B, Hkv, Tmax, D, device=cuda_dev), torch.randn(B, Hkv, Tmax, D, device=cuda_dev)
+    ang = torch.rand(Tmax, D // 2, device=cuda_dev) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([pos0], dtype=torch.int32, device=cuda_dev)
+    scratch = torch.full((lib.cq_attention_split_scratch_floats(B, 1, Hq, Tmax),), float("nan"), device=cuda_dev)
+    counters = torch.zeros(B * Hq, dtype=torch.int32, device=cuda_dev)
+    tail = (pos.data_ptr(), scratch.data_ptr(), counters.data_ptr())
+    scale, stride = 1.0 / math.sqrt(D), q_cols + kv_cols
+    for q8 in (0, 1):
+        shape, dt = ((B, q_cols // 32 * 36), torch.uint8) if q8 else ((B, q_cols), torch.float32)
+        # two launches (rotate in place, store, attend)
+        qk_a, kc_a, vc_a = qk.clone(), kc0.clone(), vc0.clone()
+        out_a = torch.zeros(shape, dtype=dt, device=cuda_dev)
+        lib.cq_rope_store_kv_f32(qk_a.data_ptr(), qk_a.data_ptr() + 4 * q_cols, v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                 pos.data_ptr(), kc_a.data_ptr(), vc_a.data_ptr(), B, 1, Hq, Hkv, D, Tmax, stride, stride, kv_cols, st)
+        lib.cq_attention_split(qk_a.data_ptr(), kc_a.data_ptr(), vc_a.data_ptr(), out_a.data_ptr(), q8, *tail, B, 1, Hq, Hkv, D, Tmax,
+                               scale, stride, q_cols // 32, st)
+        # one launch
+        qk_b, kc_b, vc_b = qk.clone(), kc0.clone(), vc0.clone()
+        out_b = torch.zeros(shape, dtype=dt, device=cuda_dev)
+        q_rot = torch.zeros_like(qk)
+        lib.cq_rope_attention_split(qk_b.data_ptr(), qk_b.data_ptr() + 4 * q_cols, v.data_ptr(), q_rot.data_ptr(), cos.data_ptr(),
+                                    sin.data_ptr(), kc_b.data_ptr(), vc_b.data_ptr(), out_b.data_ptr(), q8, *tail, B, Hq, Hkv, D, Tmax,
+                                    scale, stride, stride, kv_cols, q_cols // 32, st)
+        capi.check("rope + attention")
+        assert torch.equal(out_a, out_b)
+        assert torch.equal(kc_a, kc_b) and torch.equal(vc_a, vc_b)
+        assert torch.equal(q_rot[:, :q_cols], qk_a[:, :q_cols]) and torch.equal(qk_b, qk)
+        assert int(counters.abs().sum()) == 0
+        # without the optional copy of the rotated queries
+        out_c = torch.zeros(shape, dtype=dt, device=cuda_dev)
+        kc_c, vc_c = kc0.clone(), vc0.clone()
+        lib.cq_rope_attention_split(qk_b.data_ptr(), qk_b.data_ptr() + 4 * q_cols, v.data_ptr(), None, cos.data_ptr(),
+                                    sin.data_ptr(), kc_c.data_ptr(), vc_c.data_ptr(), out_c.data_ptr(), q8, *tail, B, Hq, Hkv, D, Tmax,
+                                    scale, stride, stride, kv_cols, q_cols // 32, st)
+        capi.check("rope + attention")
+        assert torch.equal(out_c, out_a) and torch.equal(kc_c, kc_a)
+    assert lib.cq_glue_position_overflow_flag() == 0
+
+
+def test_rope_attention_reports_a_position_past_the_cache(lib, cuda_dev):
+    st = torch.cuda.current_stream().cuda_stream
+    B, Hq, Hkv, D, Tmax = 1, 4, 1, 128, 256
+    qk = torch.randn(B, (Hq + Hkv) * D, device=cuda_dev)
+    v = torch.randn(B, Hkv * D, device=cuda_dev)
+    kc, vc = torch.zeros(B, Hkv, Tmax, D, device=cuda_dev), torch.zeros(B, Hkv, Tmax, D, device=cuda_dev)
+    cos = torch.ones(Tmax, D // 2, device=cuda_dev)
+    sin = torch.zeros(Tmax, D // 2, device=cuda_dev)
+    pos = torch.tensor([Tmax], dtype=torch.int32, device=cuda_dev)
+    scratch = torch.zeros(lib.cq_attention_split_scratch_floats(B, 1, Hq, Tmax), device=cuda_dev)
+    counters = torch.zeros(B * Hq, dtype=torch.int32, device=cuda_dev)
+    out = torch.zeros(B, Hq * D, device=cuda_dev)
+    lib.cq_rope_attention_split(qk.data_ptr(), qk.data_ptr() + 4 * Hq * D, v.data_ptr(), None, cos.data_ptr(), sin.data_ptr(),
+                                kc.data_ptr(), vc.data_ptr(), out.data_ptr(), 0, pos.data_ptr(), scratch.data_ptr(),
+                                counters.data_ptr(), B, Hq, Hkv, D, Tmax, 0.088, (Hq + Hkv) * D, (Hq + Hkv) * D, Hkv * D,
+                                Hq * D // 32, st)
+    torch.cuda.synchronize()
+    assert lib.cq_glue_position_overflow_flag() == 1
+    lib.cq_clear_status()
+    assert lib.cq_glue_position_overflow_flag() == 0
+    assert float(kc.abs().sum()) == 0.0 and float(out.abs().sum()) == 0.0 and int(counters.abs().sum()) == 0
+
+
 def test_glue_kernels_match_torch(lib, cuda_dev):
     """rms_norm (with and without the pending residual), interleaved RoPE + KV store, SwiGLU - against the tensor
     formulas of candle-transformers/src/models/quantized_llama.rs:56-62 and 178-262."""
@@ -206,6 +280,11 @@ def test_decode_tokens_do_not_depend_on_fusion_or_dependent_launch(lib, cuda_dev
     m.fuse_quantize = False
     assert torch.equal(m.generate(prompt, 10), base)
     m.fuse_quantize = True
+    m.fuse_rope = False
+    assert torch.equal(m.generate(prompt, 10), base)
+    m.fuse_quantize = False
+    assert torch.equal(m.generate(prompt, 10), base)
+    m.fuse_quantize = m.fuse_rope = True
     lib.cq_set_pdl(0)
     try:
         assert torch.equal(m.generate(prompt, 10), base)

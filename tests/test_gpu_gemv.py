@@ -211,17 +211,24 @@ def test_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle, cuda_dev,
 @pytest.mark.parametrize("tname", ["q4_k", "q6_k", "q8_0"])
 @pytest.mark.parametrize("k,n", [(2048, 5), (2048, 16), (4096, 257), (14336, 48), (6144, 1000), (4096, 4800), (1024, 40), (4096, 40000),
                                  (14336, 4096), (8192, 700)])
-def test_warp_tile_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle, cuda_dev, tname, k, n):
+@pytest.mark.parametrize("cluster", [0, 2])
+def test_warp_tile_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle, cuda_dev, tname, k, n, cluster):
     """The warp-private tensor-core kernel, forced for every batch size 1..8, against the dp4a kernel: equal bits and the
     oracle's bar; single and ragged last tiles, more tiles than warps of one CTA (4800 rows: 300 tiles over many CTAs),
     one to seven groups of 32 chunks; both forms of the kernel - a warp owning whole tiles (40000 rows) and the groups of a
-    tile spread over the warps of a CTA with the ordered sum through shared memory (all others with two or more groups).  Shapes whose K is not a whole number of groups fall back (plan query says so)."""
+    tile spread over the warps of a CTA with the ordered sum through shared memory (all others with two or more groups) or,
+    with `cluster` = 2, over the CTAs of a thread-block cluster with the sums sent through distributed shared memory (plan
+    kind 4; clusters of 2 to 7 CTAs, one and several rounds of tiles, ragged last round).  Shapes whose K is not a whole
+    number of groups fall back (plan query says so)."""
     import ctypes
     wt = TYPES[tname]
     whole_groups = k % (1024 if tname == "q8_0" else 2048) == 0
     _, x, wq = make_case(oracle, wt, k, n, 8, seed=k + n)
     w_dev = torch.from_numpy(wq).to(cuda_dev)
+    groups = k // (1024 if tname == "q8_0" else 2048)
+    kinds = set()
     try:
+        lib.cq_set_cluster_split(cluster)
         for b in range(1, 9):
             xb = torch.from_numpy(x[:b]).to(cuda_dev)
             lib.cq_set_mma_min_batch(9)
@@ -230,7 +237,8 @@ def test_warp_tile_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle,
             lib.cq_set_mma_kernel(2)
             plan = (ctypes.c_int * 4)()
             assert lib.cq_mmvq_plan(wt, capi.ACT_Q8_1, k, n, b, plan) == 0
-            assert (plan[0] in (2, 3)) == whole_groups
+            assert (plan[0] in (2, 3, 4)) == whole_groups
+            kinds.add(plan[0])
             got = ref_call_sequence(lib, tname, "f32", w_dev, xb, k, n)[1]
             assert torch.equal(got, ref), f"batch {b}"
             lib.cq_set_mma_kernel(0)
@@ -240,6 +248,9 @@ def test_warp_tile_tensor_core_gemv_gives_the_bits_of_the_dp4a_gemv(lib, oracle,
     finally:
         lib.cq_set_mma_min_batch(0)
         lib.cq_set_mma_kernel(0)
+        lib.cq_set_cluster_split(1)
+    if whole_groups and groups >= 2 and n < 16 * 148 * 16:
+        assert kinds == ({4} if cluster == 2 else {3})
     assert lib.cq_device_timeout_flag() == 0
 
 

@@ -74,6 +74,39 @@ def check_gather(dev, rank, world) -> str:
         if not torch.equal(o1, ref(x1)):
             bad.append(("one-gather graph", rep))
     peer.check()
+    # rows with one owner each (expert-parallel outputs): every rank must end up with each row as its owner holds it
+    e_local = 5
+    gen_all = torch.Generator(device=dev).manual_seed(77)       # the same on all ranks
+    xrows = [(8, 2048), (8, 2048), (64, 96), (1, 3), (16, 2048)]
+    for it, (rows, n) in enumerate(xrows * 3):
+        experts = torch.randint(0, e_local * world, (rows,), device=dev, dtype=torch.int32, generator=gen_all)
+        truth = torch.randn((rows, n), device=dev, generator=gen_all)
+        owner = (experts - rank * e_local).contiguous()
+        mine = (owner >= 0) & (owner < e_local)
+        local = torch.where(mine[:, None], truth, torch.full_like(truth, float("nan")))     # the other rows hold nothing useful
+        got = peer.exchange_rows(local, owner, e_local)
+        if got is None or not torch.equal(got, truth):
+            bad.append(("rows", it, rows, n))
+    ex = torch.zeros((8, 2048), device=dev)
+    ow = torch.zeros(8, dtype=torch.int32, device=dev)
+    peer.exchange_rows(ex, ow, e_local)
+    with torch.cuda.stream(side):
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=side):
+            o2 = peer.exchange_rows(ex, ow, e_local)
+    for rep in range(20):
+        experts = torch.randint(0, e_local * world, (8,), device=dev, dtype=torch.int32, generator=gen_all)
+        truth = torch.randn((8, 2048), device=dev, generator=gen_all)
+        ow.copy_(experts - rank * e_local)
+        ex.copy_(torch.where(((ow >= 0) & (ow < e_local))[:, None], truth, torch.zeros_like(truth)))
+        torch.cuda.synchronize()
+        if rep % 2 == rank % 2:
+            torch.cuda._sleep(2_000_000)
+        g2.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(o2, truth):
+            bad.append(("rows graph", rep))
+    peer.check()
     # cost of one gather: 100 alternating gathers of a decode-sized and a head-sized slice, replayed from a graph
     for name, g_ in (("peer", peer), ("nccl", ref)):
         a, b = torch.randn((1, 4096 // world), device=dev), torch.randn((1, 128256 // world), device=dev)
