@@ -875,7 +875,7 @@ def run_dequant_case(args):
     print(json.dumps({"dequant_case": args.dequant_case, "us": times, "bytes": nbytes, "best_GBps": nbytes / best / 1e3}))
 
 
-def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=True):
+def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=True, fuse_rope=None):
     """Llama-3-8B-shaped Q4_K_M decoder, random prompt of `prompt_len` ids (seed 2), `steps` greedy
     tokens.  Returns (decode tokens/s over all sequences, prompt tokens/s, token checksum)."""
     import torch
@@ -883,6 +883,8 @@ def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=T
     from candle_b200.decoder import DecoderConfig, LlamaShapedDecoder
     cfg = DecoderConfig.llama3_8b()
     m = LlamaShapedDecoder(cfg, dev, rank=rank, world=world, batch=batch, seed=1)
+    if fuse_rope is not None:
+        m.fuse_rope = fuse_rope
     prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), device=dev, generator=torch.Generator(device=dev).manual_seed(2))
     m.forward(prompt)          # grows the activation workspace to its final size before anything is recorded
     graphed = m.capture_decode_step() if use_graph else False
@@ -918,6 +920,7 @@ def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=T
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--decode-case", default=None, help="profile helper: BATCH:PROMPT:STEPS, runs only the decoder measurement")
+    ap.add_argument("--no-fuse-rope", action="store_true", help="with --decode-case: rope + KV store as a launch of its own")
     ap.add_argument("--no-graph", action="store_true", help="with --decode-case: launch decode steps eagerly")
     ap.add_argument("--mma-min-batch", type=int, default=None, help="with --case: rows from which the tensor-core GEMV is used (9: never)")
     ap.add_argument("--mma-kernel", type=int, default=None, help="with --case: 1 only the CTA-shared tensor-core GEMV, 2 the warp-private one")
@@ -957,7 +960,8 @@ def main():
                 raise SystemExit("--tune needs an experiment build of the library (nvcc -DCQ_EXPERIMENT)")
             fn(ctypes.c_int(rb_), ctypes.c_int(cps_))
         torch.cuda.set_device(0)
-        print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph)))
+        print(json.dumps(decode_tok_s(torch.device("cuda:0"), 0, 1, b_, p_, s_, use_graph=not args.no_graph,
+                                      fuse_rope=False if args.no_fuse_rope else None)))
     elif args.traffic_sweep:
         run_traffic_sweep(args)
     elif args.prefill_case:

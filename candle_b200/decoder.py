@@ -225,7 +225,9 @@ class LlamaShapedDecoder:
                     h = self._norm(x, delta, L.attn_norm)
                     qk, v = L.wqk.forward(h), L.wv.forward(h)                           # [R, q_cols + kv_cols], [R, kv_cols]
                 self._rec(f"{li}.h_attn", h), self._rec(f"{li}.qk", qk), self._rec(f"{li}.v", v)
-                one_launch = self.fuse_rope and T == 1 and hd == 128     # rope + KV store inside the attention kernel
+                # rope + KV store inside the attention kernel: one sequence only - with more, the fused kernel's registers
+                # cost more than the launch saves (B200, 512-token context: 533 / 530 tok/s at b=1, 1812 / 1903 at b=8)
+                one_launch = self.fuse_rope and T == 1 and B == 1 and hd == 128
                 if not one_launch:
                     lib.cq_rope_store_kv_f32(qk.data_ptr(), qk.data_ptr() + 4 * q_cols, v.data_ptr(), self.cos.data_ptr(),
                                              self.sin.data_ptr(), self.pos.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(),

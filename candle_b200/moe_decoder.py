@@ -110,6 +110,7 @@ class MoeShapedDecoder:
         self._pos_host = 0      # host copy of pos: positions are checked against max_pos before anything is launched
         self._graph = None
         self._att_scratch = None
+        self.fuse_quantize = True       # decode steps: norm and attention store Q8_1 containers directly
         self.tap = None                 # tests set a dict here: forward() then records copies of its intermediate tensors
         self.hq_l, self.hkv_l = cfg.n_heads, cfg.n_kv_heads      # attention is replicated: every rank owns all heads
         if world > 1:       # the peer-memory exchange of expert outputs (library collectives when peers cannot be mapped)
@@ -128,7 +129,10 @@ class MoeShapedDecoder:
     decode_step = LlamaShapedDecoder.decode_step
     generate = LlamaShapedDecoder.generate
 
-    def _attention(self, qkv, L, B, T, out):
+    _norm_q8 = LlamaShapedDecoder._norm_q8
+
+    def _attention(self, qkv, L, B, T, out, q8: bool = False):
+        """`q8` (at most 64 queries): the result goes out as the Q8_1 containers the next matmul reads."""
         cfg, lib, hd = self.cfg, capi.lib(), self.cfg.head_dim
         st = torch.cuda.current_stream(self.device).cuda_stream
         stride = (cfg.n_heads + 2 * cfg.n_kv_heads) * hd
@@ -139,9 +143,11 @@ class MoeShapedDecoder:
                 self._att_scratch = (torch.empty(n, dtype=torch.float32, device=self.device),
                                      torch.zeros(64 * cfg.n_heads, dtype=torch.int32, device=self.device))
             scratch, counters = self._att_scratch
-            lib.cq_attention_split(qkv.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), 0, self.pos.data_ptr(),
-                                   scratch.data_ptr(), counters.data_ptr(), B, T, cfg.n_heads, cfg.n_kv_heads, hd, cfg.max_pos, scale,
-                                   stride, 0, st)
+            lib.cq_attention_split(qkv.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), 1 if q8 else 0,
+                                   self.pos.data_ptr(), scratch.data_ptr(), counters.data_ptr(), B, T, cfg.n_heads, cfg.n_kv_heads, hd,
+                                   cfg.max_pos, scale, stride, cfg.n_heads * hd // 32, st)
+        elif q8:
+            raise ValueError("Q8_1 attention output is for at most 64 queries")
         else:
             lib.cq_attention_f32(qkv.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
                                  B, T, cfg.n_heads, cfg.n_kv_heads, hd, cfg.max_pos, scale, stride, st)
@@ -191,6 +197,7 @@ class MoeShapedDecoder:
         st = torch.cuda.current_stream(self.device).cuda_stream
         q_cols, kv_cols = cfg.n_heads * hd, cfg.n_kv_heads * hd
         stride = q_cols + 2 * kv_cols
+        fused = self.fuse_quantize and R <= 8 and lib.cqh_get_act_mode() == 0 and cfg.d_model % 512 == 0 and q_cols % 512 == 0
         with torch.cuda.device(self.device):
             x = self.tok_embd.index_select(0, tokens.reshape(-1))
             delta = None
@@ -198,8 +205,12 @@ class MoeShapedDecoder:
                 self._rec(f"{li}.x_in", x)
                 if delta is not None:
                     self._rec(f"{li}.delta_in", delta)
-                h = self._norm(x, delta, L.attn_norm)
-                qkv = L.wqkv.forward(h)                                                           # [R, stride]
+                if fused:       # decode steps: the producers store Q8_1 containers, the matmuls skip their quantize launch
+                    h = self._norm_q8(x, delta, L.attn_norm)
+                    qkv = L.wqkv.forward_q8_1(h)
+                else:
+                    h = self._norm(x, delta, L.attn_norm)
+                    qkv = L.wqkv.forward(h)                                                       # [R, stride]
                 self._rec(f"{li}.h_attn", h), self._rec(f"{li}.qkv", qkv)
                 base = qkv.data_ptr()
                 lib.cq_qknorm_rope_store_kv_f32(base, base + 4 * q_cols, base + 4 * (q_cols + kv_cols), L.q_norm.data_ptr(),
@@ -207,10 +218,15 @@ class MoeShapedDecoder:
                                                 L.k_cache.data_ptr(), L.v_cache.data_ptr(), B, T, cfg.n_heads, cfg.n_kv_heads, hd,
                                                 cfg.max_pos, stride, stride, stride, cfg.rms_eps, 1, st)
                 self._rec(f"{li}.q_rot", qkv)
-                att = torch.empty((R, q_cols), dtype=torch.float32, device=self.device)
-                self._attention(qkv, L, B, T, att)
+                if fused:
+                    att = torch.empty((R, q_cols // 32 * 36), dtype=torch.uint8, device=self.device)
+                    self._attention(qkv, L, B, T, att, q8=True)
+                    delta = L.wo.forward_q8_1(att)
+                else:
+                    att = torch.empty((R, q_cols), dtype=torch.float32, device=self.device)
+                    self._attention(qkv, L, B, T, att)
+                    delta = L.wo.forward(att)
                 self._rec(f"{li}.att", att)
-                delta = L.wo.forward(att)
                 self._rec(f"{li}.x_mid", x), self._rec(f"{li}.wo", delta)
                 h = self._norm(x, delta, L.ffn_norm)
                 delta = self._moe(h, L, f"{li}.")

@@ -272,10 +272,11 @@ def test_fused_producers_store_the_quantizers_bytes(lib, cuda_dev):
     assert torch.equal(o8, _quantize_rows(lib, o))
 
 
-def test_decode_tokens_do_not_depend_on_fusion_or_dependent_launch(lib, cuda_dev):
+@pytest.mark.parametrize("batch", [1, 2])       # one sequence: rope + KV store run inside the attention launch
+def test_decode_tokens_do_not_depend_on_fusion_or_dependent_launch(lib, cuda_dev, batch):
     cfg = DecoderConfig.tiny()
-    prompt = torch.randint(0, cfg.vocab, (2, 20), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(7))
-    m = LlamaShapedDecoder(cfg, cuda_dev, batch=2, seed=3)
+    prompt = torch.randint(0, cfg.vocab, (batch, 20), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(7))
+    m = LlamaShapedDecoder(cfg, cuda_dev, batch=batch, seed=3)
     base = m.generate(prompt, 10)
     m.fuse_quantize = False
     assert torch.equal(m.generate(prompt, 10), base)

@@ -245,6 +245,18 @@ def test_moe_decoder_graph_equals_eager(cuda_dev):
     assert not torch.equal(m.generate((prompt + 1) % cfg.vocab, 10), eager)
 
 
+def test_moe_decode_tokens_do_not_depend_on_fused_quantization(cuda_dev):
+    """Decode steps with the norm and the attention storing Q8_1 containers directly (no quantize launch before wqkv and
+    wo) against the same steps with f32 results and stand-alone quantization."""
+    from candle_b200.moe_decoder import MoeDecoderConfig, MoeShapedDecoder
+    cfg = MoeDecoderConfig.tiny()
+    prompt = torch.randint(0, cfg.vocab, (2, 20), device=cuda_dev, generator=torch.Generator(device=cuda_dev).manual_seed(5))
+    m = MoeShapedDecoder(cfg, cuda_dev, batch=2, seed=2)
+    base = m.generate(prompt, 10)
+    m.fuse_quantize = False
+    assert torch.equal(m.generate(prompt, 10), base)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_expert_parallel_tokens_match_single_gpu(tmp_path):
     import os
