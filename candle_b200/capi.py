@@ -93,6 +93,10 @@ def lib() -> C.CDLL:
         L.cq_set_pdl.argtypes = [i32]
         L.cq_glue_position_overflow_flag.restype = i32
         L.cq_moe_route_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        L.cq_moe_router_f32.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        L.cq_moe_router_f32.restype = None
+        L.cq_moe_weighted_sum_f32.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+        L.cq_moe_weighted_sum_f32.restype = None
         L.cq_qknorm_rope_store_kv_f32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32,
                                                   C.c_float, i32, vp]
         L.cq_attention_split_scratch_floats.argtypes = [i32, i32, i32, i32]
@@ -134,6 +138,9 @@ def lib() -> C.CDLL:
         L.cq_mmvq_pair_q4k_q6k.argtypes = [vp, i32, vp, vp, i32, vp, vp, i32, i32, vp]
         L.cq_mmvq_pair_q4k_q6k.restype = i32
         L.cqh_indexed_moe_forward.argtypes = [vp, vp, i32, vp, i32, i32, vp, vp]
+        L.cqh_indexed_moe_forward_q8_1.argtypes = [vp, vp, i32, vp, i32, i32, vp, vp]
+        L.cq_add_rms_norm_f32_q8_1.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, C.c_float, vp]
+        L.cq_add_rms_norm_f32_q8_1.restype = None
         L.cqh_get_act_mode.restype = i32
         L.cqh_workspace_reserve.argtypes = [i32, sz]
         u64 = C.c_uint64

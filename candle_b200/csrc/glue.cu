@@ -15,10 +15,12 @@ namespace {
 // ...: the first of them stays in registers, so that a row of up to 4096 floats is read once.  Squares are added
 // element by element per thread, then by an xor butterfly, then over the 32 warps in index order.
 // Q8: the result goes out as Q8_1 containers of a row of k_padded values (zero blocks past d; d a multiple of 32).
-template <bool Q8>
+// MODE 0: f32 result in `out`;  1: Q8_1 containers in `out`;  2: both - Q8_1 in `out`, f32 in `out_f32` (a consumer of each).
+template <int MODE>
 __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, const float *__restrict__ residual,
                                                         const float *__restrict__ w, void *__restrict__ out, int d, int k_padded,
-                                                        float eps) {
+                                                        float eps, float *__restrict__ out_f32) {
+    constexpr bool Q8 = MODE != 0;
     __shared__ float red[32];
     const int n4 = d >> 2, tid = threadIdx.x;
     const float4 *w4 = reinterpret_cast<const float4 *>(w);
@@ -61,6 +63,8 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(float *__restrict__ x, c
         if constexpr (Q8) {
             uint8_t *row = reinterpret_cast<uint8_t *>(out) + (size_t)blockIdx.x * (k_padded / 32) * CQ_Q8_BYTES;
             cq_q8_1_store_block(r, row + (size_t)(i >> 3) * CQ_Q8_BYTES, i < n4_out);
+            if constexpr (MODE == 2)
+                if (i < n4) reinterpret_cast<float4 *>(out_f32 + (size_t)blockIdx.x * d)[i] = make_float4(r[0], r[1], r[2], r[3]);
         } else if (i < n4) {
             reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)blockIdx.x * d)[i] = make_float4(r[0], r[1], r[2], r[3]);
         }
@@ -139,20 +143,17 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float *__restrict__
 // Router of a mixture-of-experts block (candle-transformers/src/fused_moe.rs:233-247): softmax over the experts, the k
 // largest probabilities in descending order (lowest index first among equals), optionally divided by their sum.
 // One warp per token; experts <= 1024.  The softmax sum is added lane-strided, then by an xor butterfly.
-__global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int32_t *__restrict__ ids,
-                                                        float *__restrict__ weights, int tokens, int experts, int k, int norm) {
-    cq_pdl_launch_dependents();
-    cq_pdl_wait();
-    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (tok >= tokens) return;
+// One warp routes one token.  VOLATILE: the logits were written by other CTAs of the running kernel (read around L1).
+template <bool VOLATILE>
+__device__ __forceinline__ void moe_route_row(const float *row, int32_t *__restrict__ ids, float *__restrict__ weights, int tok,
+                                              int experts, int k, int norm, int lane) {
     constexpr int PER = 32;                    // experts per lane at most (1024 / 32)
     float p[PER];
-    const float *row = logits + (size_t)tok * experts;
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const int e = lane + 32 * i;
-        p[i] = e < experts ? row[e] : -INFINITY;
+        p[i] = e < experts ? (VOLATILE ? __ldcg(row + e) : row[e]) : -INFINITY;
         mx = fmaxf(mx, p[i]);
     }
 #pragma unroll
@@ -193,6 +194,79 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
         ids[(size_t)tok * k + lane] = chosen_id;
         weights[(size_t)tok * k + lane] = norm ? __fdiv_rn(chosen, total) : chosen;
     }
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int32_t *__restrict__ ids,
+                                                        float *__restrict__ weights, int tokens, int experts, int k, int norm) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= tokens) return;
+    moe_route_row<false>(logits + (size_t)tok * experts, ids, weights, tok, experts, k, norm, lane);
+}
+
+// Router logits and routing in one launch, for the few rows of a decode step: logits[t, e] = h[t, :] . router[e, :] (f32;
+// one warp per (token, expert): a lane adds its float4 strides in order with FMAs, then an xor butterfly), and the CTA that
+// finishes a token's row last (an arrival counter per token, reset by that CTA) routes it with the warp function above.
+// grid (ceil(experts / 8), tokens) x 256 threads; d a multiple of 4.
+__global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict__ h, const float *__restrict__ router,
+                                                         float *__restrict__ logits, int32_t *__restrict__ ids,
+                                                         float *__restrict__ weights, int *__restrict__ counters, int experts, int d,
+                                                         int k, int norm) {
+    __shared__ int is_last;
+    const int tok = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    float4 wv[4];
+    const float4 *wr = reinterpret_cast<const float4 *>(router + (size_t)(e < experts ? e : 0) * d);
+    const int n4 = d >> 2;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wv[i] = lane + 32 * i < n4 ? wr[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);   // weights: before the wait
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    if (e < experts) {
+        const float4 *hr = reinterpret_cast<const float4 *>(h + (size_t)tok * d);
+        float acc = 0.0f;
+        for (int i0 = 0; i0 < n4; i0 += 128) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = i0 + lane + 32 * i;
+                if (j < n4) {
+                    const float4 a = hr[j], b = i0 == 0 ? wv[i] : wr[j];
+                    acc = __fmaf_rn(a.x, b.x, acc); acc = __fmaf_rn(a.y, b.y, acc);
+                    acc = __fmaf_rn(a.z, b.z, acc); acc = __fmaf_rn(a.w, b.w, acc);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        if (lane == 0) logits[(size_t)tok * experts + e] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(&counters[tok], 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    moe_route_row<true>(logits + (size_t)tok * experts, ids, weights, tok, experts, k, norm, lane);
+    if (lane == 0) counters[tok] = 0;       // ready for the next launch
+}
+
+// out[t, :] = sum over the slots s, in slot order, of y[t, s, :] * w[t, s]  (product rounded, then added: the tensor formula
+// (y * w.unsqueeze(-1)).sum(1) of candle-transformers/src/fused_moe.rs:296-301).  One thread per four outputs.
+__global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const float *__restrict__ y, const float *__restrict__ w,
+                                                               float *__restrict__ out, int k, int d) {
+    cq_pdl_launch_dependents();
+    cq_pdl_wait();
+    const int t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= (d >> 2)) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < k; ++s) {
+        const float ws = w[(size_t)t * k + s];
+        const float4 v = reinterpret_cast<const float4 *>(y + ((size_t)t * k + s) * d)[i];
+        acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, ws)); acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, ws));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, ws)); acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, ws));
+    }
+    reinterpret_cast<float4 *>(out + (size_t)t * d)[i] = acc;
 }
 
 // Per-head RMSNorm of q and k (weights qw / kw of head_dim values, either may be null), rotary embedding in the
@@ -271,7 +345,7 @@ bool norm_args_ok(const void *x, const void *w, const void *out, int rows, int d
 
 extern "C" void cq_rms_norm_f32(const float *x, const float *w, float *out, int rows, int d, float eps, void *stream) {
     if (!norm_args_ok(x, w, out, rows, d, "rms_norm: bad arguments (d must be a multiple of 4)")) return;
-    cq_launch_k(rms_norm_kernel<false>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, const_cast<float *>(x), nullptr, w, out, d, d, eps);
+    cq_launch_k(rms_norm_kernel<0>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, const_cast<float *>(x), nullptr, w, out, d, d, eps, nullptr);
     cq_check_launch("rms_norm");
 }
 
@@ -279,7 +353,7 @@ extern "C" void cq_add_rms_norm_f32(float *x, const float *residual, const float
                                     void *stream) {
     if (!residual) { cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm: null residual"); return; }
     if (!norm_args_ok(x, w, out, rows, d, "add_rms_norm: bad arguments (d must be a multiple of 4)")) return;
-    cq_launch_k(rms_norm_kernel<false>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out, d, d, eps);
+    cq_launch_k(rms_norm_kernel<0>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out, d, d, eps, nullptr);
     cq_check_launch("add_rms_norm");
 }
 
@@ -290,8 +364,19 @@ extern "C" void cq_add_rms_norm_q8_1(float *x, const float *residual, const floa
         cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm_q8_1: d and k_padded must be multiples of 32, k_padded >= d");
         return;
     }
-    cq_launch_k(rms_norm_kernel<true>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out_q8, d, k_padded, eps);
+    cq_launch_k(rms_norm_kernel<1>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out_q8, d, k_padded, eps, nullptr);
     cq_check_launch("add_rms_norm_q8_1");
+}
+
+extern "C" void cq_add_rms_norm_f32_q8_1(float *x, const float *residual, const float *w, float *out_f32, void *out_q8, int rows,
+                                         int d, int k_padded, float eps, void *stream) {
+    if (!out_f32 || !norm_args_ok(x, w, out_q8, rows, d, "add_rms_norm_f32_q8_1: bad arguments")) return;
+    if (d % 32 || k_padded < d || k_padded % 32) {
+        cq_set_status(CQ_ERR_BAD_ARG, "add_rms_norm_f32_q8_1: d and k_padded must be multiples of 32, k_padded >= d");
+        return;
+    }
+    cq_launch_k(rms_norm_kernel<2>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, x, residual, w, out_q8, d, k_padded, eps, out_f32);
+    cq_check_launch("add_rms_norm_f32_q8_1");
 }
 
 extern "C" void cq_rope_store_kv_f32(float *q, float *k, const float *v, const float *cosv, const float *sinv, const int *pos,
@@ -354,6 +439,27 @@ extern "C" void cq_moe_route_f32(const float *logits, int32_t *ids, float *weigh
     cq_launch_k(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, ids, weights, tokens, experts, k,
                 norm_topk_prob);
     cq_check_launch("moe_route");
+}
+
+extern "C" void cq_moe_router_f32(const float *h, const float *router, float *logits, int32_t *ids, float *weights, int *counters,
+                                  int tokens, int experts, int d, int k, int norm_topk_prob, void *stream) {
+    if (!h || !router || !logits || !ids || !weights || !counters || tokens <= 0 || tokens > 65535 || experts <= 0 || experts > 1024 ||
+        k <= 0 || k > 32 || k > experts || d <= 0 || d % 4 || (((uintptr_t)h | (uintptr_t)router) & 15)) {
+        cq_set_status(CQ_ERR_BAD_ARG, "moe_router: bad arguments (experts <= 1024, k <= 32, d a multiple of 4, 16-byte aligned rows)");
+        return;
+    }
+    cq_launch_k(moe_router_kernel, dim3((experts + 7) / 8, tokens), dim3(256), 0, (cudaStream_t)stream, h, router, logits, ids, weights,
+                counters, experts, d, k, norm_topk_prob);
+    cq_check_launch("moe_router");
+}
+
+extern "C" void cq_moe_weighted_sum_f32(const float *y, const float *w, float *out, int tokens, int k, int d, void *stream) {
+    if (!y || !w || !out || tokens <= 0 || tokens > 65535 || k <= 0 || d <= 0 || d % 4 || (((uintptr_t)y | (uintptr_t)out) & 15)) {
+        cq_set_status(CQ_ERR_BAD_ARG, "moe_weighted_sum: bad arguments (d a multiple of 4, 16-byte aligned rows)");
+        return;
+    }
+    cq_launch_k(moe_weighted_sum_kernel, dim3((d / 4 + 255) / 256, tokens), dim3(256), 0, (cudaStream_t)stream, y, w, out, k, d);
+    cq_check_launch("moe_weighted_sum");
 }
 
 extern "C" void cq_qknorm_rope_store_kv_f32(float *q, float *k, const float *v, const float *q_norm_w, const float *k_norm_w,

@@ -257,6 +257,21 @@ void QCudaStorage::indexed_moe_forward(size_t experts, size_t n, size_t k, const
     lib_check("indexed_moe_forward");
 }
 
+void QCudaStorage::indexed_moe_forward_q8_1(size_t experts, size_t n, size_t k, const void *act_q8_1, int x_dim1, const uint32_t *ids,
+                                            int batch, int topk, float *out, cudaStream_t stream) const {
+    if (!kernels_support(dtype_)) throw Error(std::string("no B200 kernel for quantized dtype ") + dtype_name(dtype_));
+    if (k % block_size(dtype_) != 0 || experts * n * (k / block_size(dtype_)) * type_size(dtype_) != len_)
+        throw Error("indexed_moe_forward: storage size does not match [experts, n, k]");
+    if (x_dim1 != 1 && x_dim1 != topk) throw Error("indexed_moe_forward: input dim 1 must be 1 or topk");
+    if (act_mode() == ActMode::CpuExact) throw Error("indexed_moe_forward_q8_1: the CPU-exact mode quantizes inside the call");
+    if (batch <= 0 || topk <= 0) return;
+    if (!act_q8_1 || !ids || !out) throw Error("indexed_moe_forward: null pointer");
+    DeviceGuard g(device_);
+    cq_indexed_moe_forward((int)dtype_, CQ_ACT_Q8_1_ENC, ptr_, act_q8_1, ids, out, (int)n, (int)k, batch, topk,
+                           (int)pad(k, MATRIX_ROW_PADDING), x_dim1, (int)experts, stream);
+    lib_check("indexed_moe_forward");
+}
+
 // ---- QTensor / QMatMul -----------------------------------------------------------------------
 QTensor::QTensor(std::unique_ptr<QCudaStorage> storage, std::vector<int64_t> dims)
     : storage_(std::move(storage)), shape_(std::move(dims)) {
@@ -332,24 +347,26 @@ extern "C" const void *cqh_qtensor_device_ptr(void *handle) {
 
 // ---- QMatMul::forward over HOST buffers ------------------------------------------------------------------------
 // Where candle moves a CPU tensor to the device, multiplies and moves the result back (Tensor::to_device around
-// QMatMul::forward), this entry point does the three steps itself: host activations -> a device staging buffer (on the
-// caller's stream), the ordinary forward, result -> host on a copy stream of the library, so that the copy-back of one
-// call overlaps the next call's upload and arithmetic.  Per device a ring of four staging slots; a slot's buffers are
-// reused only after its copy-back has finished (the caller's stream waits on that event).  cqh_qmatmul_host_flush makes
-// the caller's stream wait for every copy-back still in flight: synchronise that stream afterwards and the host outputs
-// are complete.  Pinned host memory is needed for the copies to be asynchronous.
+// QMatMul::forward), this entry point does the three steps itself: host activations -> a device staging buffer on an
+// upload stream of the library, the ordinary forward on the caller's stream (which waits for the upload), result -> host
+// on a copy stream of the library, so that the upload of one call and the copy-back of the previous one overlap the
+// arithmetic in between.  Per device a ring of four staging slots; a slot's buffers are reused only after its copy-back
+// has finished (the upload stream waits on that event).  The host activations must be complete when the call is made (they
+// are read by the upload stream, which does not wait for earlier work of the caller's stream).  cqh_qmatmul_host_flush
+// makes the caller's stream wait for every copy-back still in flight: synchronise that stream afterwards and the host
+// outputs are complete.  Pinned host memory is needed for the copies to be asynchronous.
 namespace {
 constexpr int kHostSlots = 4;
 struct HostSlot {
     void *x = nullptr, *y = nullptr;
     size_t cap_x = 0, cap_y = 0;
-    cudaEvent_t gemv_done = nullptr, d2h_done = nullptr;
+    cudaEvent_t up_done = nullptr, gemv_done = nullptr, d2h_done = nullptr;
     bool pending = false;
 };
 struct HostRing {
     HostSlot s[kHostSlots];
     int next = 0;
-    cudaStream_t copy_stream = nullptr;
+    cudaStream_t copy_stream = nullptr, up_stream = nullptr;
 };
 std::mutex g_host_mu;
 std::map<int, HostRing> g_host_ring;
@@ -387,20 +404,24 @@ extern "C" int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_
         HostRing &ring = g_host_ring[dev];
         if (!ring.copy_stream) {
             cuda_check(cudaStreamCreateWithFlags(&ring.copy_stream, cudaStreamNonBlocking), "forward_host: copy stream");
+            cuda_check(cudaStreamCreateWithFlags(&ring.up_stream, cudaStreamNonBlocking), "forward_host: upload stream");
             for (auto &sl : ring.s) {
+                cuda_check(cudaEventCreateWithFlags(&sl.up_done, cudaEventDisableTiming), "forward_host: event");
                 cuda_check(cudaEventCreateWithFlags(&sl.gemv_done, cudaEventDisableTiming), "forward_host: event");
                 cuda_check(cudaEventCreateWithFlags(&sl.d2h_done, cudaEventDisableTiming), "forward_host: event");
             }
         }
         HostSlot &sl = ring.s[ring.next];
         ring.next = (ring.next + 1) % kHostSlots;
-        if (sl.pending) {       // the slot's last copy-back must be over before its buffers are written again
-            cuda_check(cudaStreamWaitEvent(st, sl.d2h_done, 0), "forward_host: wait for the slot's copy-back");
+        if (sl.pending) {       // the slot's last copy-back (hence its last product) must be over before its buffers are written again
+            cuda_check(cudaStreamWaitEvent(ring.up_stream, sl.d2h_done, 0), "forward_host: wait for the slot's copy-back");
             sl.pending = false;
         }
         grow(sl.x, sl.cap_x, rows * k * es, ring.copy_stream);
         grow(sl.y, sl.cap_y, rows * n * es, ring.copy_stream);
-        cuda_check(cudaMemcpyAsync(sl.x, host_x, rows * k * es, cudaMemcpyHostToDevice, st), "forward_host: upload");
+        cuda_check(cudaMemcpyAsync(sl.x, host_x, rows * k * es, cudaMemcpyHostToDevice, ring.up_stream), "forward_host: upload");
+        cuda_check(cudaEventRecord(sl.up_done, ring.up_stream), "forward_host: event record");
+        cuda_check(cudaStreamWaitEvent(st, sl.up_done, 0), "forward_host: wait for the upload");
         mm.forward(sl.x, (DType)x_dtype, dims, ndims, sl.y, st);
         cuda_check(cudaEventRecord(sl.gemv_done, st), "forward_host: event record");
         cuda_check(cudaStreamWaitEvent(ring.copy_stream, sl.gemv_done, 0), "forward_host: copy stream wait");
@@ -473,6 +494,17 @@ extern "C" int cqh_indexed_moe_forward(void *handle, const float *x, int x_dim1,
         const auto &sh = t->shape();
         t->storage().indexed_moe_forward((size_t)sh[0], (size_t)sh[1], (size_t)sh[2], x, x_dim1, ids, batch, topk, out,
                                          (cudaStream_t)stream);
+    });
+}
+
+extern "C" int cqh_indexed_moe_forward_q8_1(void *handle, const void *act_q8_1, int x_dim1, const uint32_t *ids, int batch, int topk,
+                                            float *out, void *stream) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        if (t->rank() != 3) throw Error("indexed_moe_forward expects a rank-3 [experts, n, k] tensor");
+        const auto &sh = t->shape();
+        t->storage().indexed_moe_forward_q8_1((size_t)sh[0], (size_t)sh[1], (size_t)sh[2], act_q8_1, x_dim1, ids, batch, topk, out,
+                                              (cudaStream_t)stream);
     });
 }
 

@@ -82,6 +82,8 @@ class QCudaStorage {
     // x: f32 [batch, x_dim1, k] with x_dim1 == topk or 1; ids: u32 [batch, topk]; out: f32 [batch, topk, n].
     void indexed_moe_forward(size_t experts, size_t n, size_t k, const float *x, int x_dim1, const uint32_t *ids, int batch,
                              int topk, float *out, cudaStream_t stream) const;
+    void indexed_moe_forward_q8_1(size_t experts, size_t n, size_t k, const void *act_q8_1, int x_dim1, const uint32_t *ids, int batch,
+                             int topk, float *out, cudaStream_t stream) const;
 
   private:
     QCudaStorage() = default;

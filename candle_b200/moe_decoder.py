@@ -110,6 +110,7 @@ class MoeShapedDecoder:
         self._pos_host = 0      # host copy of pos: positions are checked against max_pos before anything is launched
         self._graph = None
         self._att_scratch = None
+        self._router_counters = None    # arrival counters of the one-launch router
         self.fuse_quantize = True       # decode steps: norm and attention store Q8_1 containers directly
         self.tap = None                 # tests set a dict here: forward() then records copies of its intermediate tensors
         self.hq_l, self.hkv_l = cfg.n_heads, cfg.n_kv_heads      # attention is replicated: every rank owns all heads
@@ -152,15 +153,24 @@ class MoeShapedDecoder:
             lib.cq_attention_f32(qkv.data_ptr(), L.k_cache.data_ptr(), L.v_cache.data_ptr(), out.data_ptr(), self.pos.data_ptr(),
                                  B, T, cfg.n_heads, cfg.n_kv_heads, hd, cfg.max_pos, scale, stride, st)
 
-    def _moe(self, h: torch.Tensor, L, key: str = "") -> torch.Tensor:
-        """fused_moe.rs:222-301 for rows h [R, d] -> [R, d].  `key`: prefix of the recorded intermediates (tests)."""
+    def _moe(self, h: torch.Tensor, L, key: str = "", h8: torch.Tensor | None = None) -> torch.Tensor:
+        """fused_moe.rs:222-301 for rows h [R, d] -> [R, d].  `key`: prefix of the recorded intermediates (tests).
+        `h8` (decode steps): the same rows as Q8_1 containers - the expert matmuls then run without quantize launches."""
         cfg, lib = self.cfg, capi.lib()
         R, k, f = h.shape[0], cfg.experts_per_tok, cfg.expert_ffn
         st = torch.cuda.current_stream(self.device).cuda_stream
-        logits = torch.nn.functional.linear(h, L.router)
         ids = torch.empty((R, k), dtype=torch.int32, device=self.device)
         w = torch.empty((R, k), dtype=torch.float32, device=self.device)
-        lib.cq_moe_route_f32(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), R, cfg.experts, k, 1 if cfg.norm_topk_prob else 0, st)
+        small = R <= 64 and cfg.d_model % 4 == 0       # a decode step: logits + routing, and the slot sum, as one launch each
+        if small:
+            if self._router_counters is None:
+                self._router_counters = torch.zeros(64, dtype=torch.int32, device=self.device)
+            logits = torch.empty((R, cfg.experts), dtype=torch.float32, device=self.device)
+            lib.cq_moe_router_f32(h.data_ptr(), L.router.data_ptr(), logits.data_ptr(), ids.data_ptr(), w.data_ptr(),
+                                  self._router_counters.data_ptr(), R, cfg.experts, cfg.d_model, k, 1 if cfg.norm_topk_prob else 0, st)
+        else:
+            logits = torch.nn.functional.linear(h, L.router)
+            lib.cq_moe_route_f32(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), R, cfg.experts, k, 1 if cfg.norm_topk_prob else 0, st)
         self._rec(key + "router_logits", logits), self._rec(key + "ids", ids), self._rec(key + "route_w", w)
         local = ids - self.e0 if self.world > 1 else ids           # other ranks' experts fall outside [0, e_local): skipped
         zero = self.world > 1
@@ -171,6 +181,13 @@ class MoeShapedDecoder:
             lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
             y = moe_prefill_gemm(a.view(R * k, f), L.down, torch.ones(R * k, device=self.device), pairs, experts, k,
                                  zero_init=zero).view(R, k, -1)
+        elif h8 is not None and f % 32 == 0:
+            gu = L.gate_up.indexed_moe_forward_q8_1(h8, 1, local, zero_init=zero)                 # [R, k, 2f]
+            fp = capi.pad(f, 512)
+            a8 = torch.empty((R * k, fp // 32 * 36), dtype=torch.uint8, device=self.device)
+            lib.cq_silu_mul_q8_1(gu.data_ptr(), a8.data_ptr(), R * k, f, fp, st)
+            y = L.down.indexed_moe_forward_q8_1(a8, k, local, zero_init=zero)                     # [R, k, d]
+            a = a8
         else:
             gu = L.gate_up.indexed_moe_forward(h.view(R, 1, -1), local, zero_init=zero)           # [R, k, 2f]
             lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
@@ -187,6 +204,11 @@ class MoeShapedDecoder:
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
             else:
                 y = got.view(R, k, -1)
+        if small:
+            y = y.contiguous()
+            out = torch.empty((R, y.shape[-1]), dtype=torch.float32, device=self.device)
+            lib.cq_moe_weighted_sum_f32(y.data_ptr(), w.data_ptr(), out.data_ptr(), R, k, y.shape[-1], st)
+            return out
         return (y * w.unsqueeze(-1)).sum(dim=1)
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -228,8 +250,15 @@ class MoeShapedDecoder:
                     delta = L.wo.forward(att)
                 self._rec(f"{li}.att", att)
                 self._rec(f"{li}.x_mid", x), self._rec(f"{li}.wo", delta)
-                h = self._norm(x, delta, L.ffn_norm)
-                delta = self._moe(h, L, f"{li}.")
+                if fused and R * cfg.experts_per_tok < max(64, 4 * self.e_local):     # f32 rows for the router, Q8_1 for the experts
+                    h = torch.empty_like(x)
+                    h8 = torch.empty((R, cfg.d_model // 32 * 36), dtype=torch.uint8, device=self.device)
+                    lib.cq_add_rms_norm_f32_q8_1(x.data_ptr(), delta.data_ptr(), L.ffn_norm.data_ptr(), h.data_ptr(), h8.data_ptr(),
+                                                 R, cfg.d_model, cfg.d_model, cfg.rms_eps, st)
+                    delta = self._moe(h, L, f"{li}.", h8)
+                else:
+                    h = self._norm(x, delta, L.ffn_norm)
+                    delta = self._moe(h, L, f"{li}.")
                 self._rec(f"{li}.h_ffn", h), self._rec(f"{li}.moe", delta)
             self._rec("final.x_in", x), self._rec("final.delta_in", delta)
             h = self._norm(x, delta, self.out_norm)

@@ -172,6 +172,24 @@ class QTensor:
                                                             out.data_ptr(), stream))
         return out
 
+    def indexed_moe_forward_q8_1(self, act: torch.Tensor, x_dim1: int, ids: torch.Tensor, zero_init: bool = False) -> torch.Tensor:
+        """`indexed_moe_forward` from activations a fused producer already stored as Q8_1 containers: `act` uint8
+        [batch * x_dim1, pad(k, 512) / 32 * 36].  No quantize launch; f32 [batch, topk, n]."""
+        if self.rank() != 3:
+            raise CandleQError("indexed_moe_forward expects a rank-3 [experts, n, k] tensor")
+        k = self._shape[2]
+        row_bytes = capi.pad(k, 512) // 32 * 36
+        ids32 = ids.to(torch.int32).contiguous()
+        batch, topk = ids32.shape
+        if not act.is_cuda or act.dtype != torch.uint8 or not act.is_contiguous() or tuple(act.shape) != (batch * x_dim1, row_bytes):
+            raise CandleQError(f"indexed_moe_forward_q8_1 expects a contiguous uint8 CUDA tensor [{batch * x_dim1}, {row_bytes}]")
+        out = (torch.zeros if zero_init else torch.empty)((batch, topk, self._shape[1]), dtype=torch.float32, device=act.device)
+        stream = torch.cuda.current_stream(act.device).cuda_stream
+        with torch.cuda.device(act.device):
+            capi.hcheck(capi.lib().cqh_indexed_moe_forward_q8_1(self._h, act.data_ptr(), x_dim1, ids32.data_ptr(), batch, topk,
+                                                                 out.data_ptr(), stream))
+        return out
+
     def dequantize(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """``QTensor::dequantize`` / ``dequantize_f16`` (mod.rs:689-710): the tensor as f32 (f16, bf16) on its device."""
         if dtype not in _ELEM:

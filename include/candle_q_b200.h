@@ -255,6 +255,10 @@ void cq_add_rms_norm_f32(float *x, const float *residual, const float *w, float 
                          void *stream);
 void cq_add_rms_norm_q8_1(float *x, const float *residual, const float *w, void *out_q8, int rows, int d, int k_padded,
                           float eps, void *stream);
+/* The same norm with both results: f32 rows in out_f32 (for a consumer that needs them, e.g. an MoE router) and the Q8_1
+ * containers in out_q8 (for the quantized matmul). */
+void cq_add_rms_norm_f32_q8_1(float *x, const float *residual, const float *w, float *out_f32, void *out_q8, int rows, int d,
+                              int k_padded, float eps, void *stream);
 void cq_silu_mul_q8_1(const float *gate_up, void *out_q8, int rows, int f, int k_padded, void *stream);
 void cq_attention_q8_1(const float *q, const float *k_cache, const float *v_cache, void *out_q8, const int *pos, int batch,
                        int tq, int hq, int hkv, int head_dim, int tmax, float scale, int q_stride, int out_blocks,
@@ -313,6 +317,13 @@ void cq_peer_gather_set_limit_clocks(long long clocks); /* how long a poll may l
  *                                caches - candle-transformers/src/models/quantized_qwen3.rs:136-183.  head_dim 128. */
 void cq_moe_route_f32(const float *logits, int32_t *ids, float *weights, int tokens, int experts, int k, int norm_topk_prob,
                       void *stream);
+/* Decode-sized variants (no counterpart in the reference, which runs these steps as tensor ops):
+ *   cq_moe_router_f32      : the router's logits = h [tokens, d] . router[experts, d]^T (f32, written to `logits`) and the routing
+ *                            above in one launch; counters: `tokens` ints, zero before the first call and after every call.
+ *   cq_moe_weighted_sum_f32: out[t, :] = sum over slots s, in slot order, of y[t, s, :] * w[t, s] (fused_moe.rs:296-301). */
+void cq_moe_router_f32(const float *h, const float *router, float *logits, int32_t *ids, float *weights, int *counters, int tokens,
+                       int experts, int d, int k, int norm_topk_prob, void *stream);
+void cq_moe_weighted_sum_f32(const float *y, const float *w, float *out, int tokens, int k, int d, void *stream);
 void cq_qknorm_rope_store_kv_f32(float *q, float *k, const float *v, const float *q_norm_w, const float *k_norm_w, const float *cosv,
                                  const float *sinv, const int *pos, float *k_cache, float *v_cache, int batch, int t, int hq, int hkv,
                                  int head_dim, int tmax, int q_stride, int k_stride, int v_stride, float eps, int neox, void *stream);
@@ -386,10 +397,15 @@ int cqh_qtensor_data(void *handle, void *host_out, size_t nbytes);
 const void *cqh_qtensor_device_ptr(void *handle);
 /* QMatMul::forward over HOST buffers (where candle's caller does Tensor::to_device, QMatMul::forward, to_device back:
  * candle-core/src/quantized/mod.rs:1020-1043 around a CPU tensor).  host_x [.., k] -> host_out [.., n], same element
- * type; the upload and the arithmetic run on `stream`, the copy-back on a copy stream of the library so that it
- * overlaps the next call; staging buffers are kept per device (ring of four slots, grows-only).  After the last call,
+ * type; the arithmetic runs on `stream`, the upload and the copy-back on two streams of the library so that both overlap
+ * the neighbouring calls' arithmetic (host_x must be complete when the call is made: the upload does not wait for earlier
+ * work of `stream`); staging buffers are kept per device (ring of four slots, grows-only).  After the last call,
  * cqh_qmatmul_host_flush(device, stream) makes `stream` wait for every copy-back in flight: synchronise `stream` and the
  * outputs are complete.  Use pinned host memory (else the copies are synchronous). */
+/* QTensor::indexed_moe_forward from activations already stored as Q8_1 containers (batch * x_dim1 rows of
+ * pad(k, 512) / 32 containers, as cq_add_rms_norm_f32_q8_1 / cq_silu_mul_q8_1 make them): no quantize launch. */
+int cqh_indexed_moe_forward_q8_1(void *handle, const void *act_q8_1, int x_dim1, const uint32_t *ids, int batch, int topk,
+                                 float *out, void *stream);
 int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_dtype, const int64_t *dims, int ndims, void *host_out,
                              void *stream);
 int cqh_qmatmul_host_flush(int device, void *stream);

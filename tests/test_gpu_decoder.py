@@ -224,6 +224,24 @@ def _quantize_rows(lib, x):
     return out
 
 
+def test_norm_with_both_outputs(lib, cuda_dev):
+    """cq_add_rms_norm_f32_q8_1 == cq_add_rms_norm_f32 for the f32 rows and == cq_add_rms_norm_q8_1 for the containers."""
+    torch.manual_seed(9)
+    st = torch.cuda.current_stream().cuda_stream
+    for rows, d in ((1, 2048), (8, 4096), (3, 512)):
+        x0, res = torch.randn(rows, d, device=cuda_dev), torch.randn(rows, d, device=cuda_dev)
+        w = 1.0 + 0.1 * torch.randn(d, device=cuda_dev)
+        xa, xb, xc = x0.clone(), x0.clone(), x0.clone()
+        f_ref, f_got = torch.empty(rows, d, device=cuda_dev), torch.empty(rows, d, device=cuda_dev)
+        q_ref = torch.zeros((rows, d // 32 * 36), dtype=torch.uint8, device=cuda_dev)
+        q_got = torch.zeros_like(q_ref)
+        lib.cq_add_rms_norm_f32(xa.data_ptr(), res.data_ptr(), w.data_ptr(), f_ref.data_ptr(), rows, d, 1e-5, st)
+        lib.cq_add_rms_norm_q8_1(xb.data_ptr(), res.data_ptr(), w.data_ptr(), q_ref.data_ptr(), rows, d, d, 1e-5, st)
+        lib.cq_add_rms_norm_f32_q8_1(xc.data_ptr(), res.data_ptr(), w.data_ptr(), f_got.data_ptr(), q_got.data_ptr(), rows, d, d, 1e-5, st)
+        capi.check("norm with both outputs")
+        assert torch.equal(f_got, f_ref) and torch.equal(q_got, q_ref) and torch.equal(xc, xa) and torch.equal(xb, xa)
+
+
 def test_fused_producers_store_the_quantizers_bytes(lib, cuda_dev):
     """Norm, SwiGLU and attention with Q8_1 output == their f32 result passed through the stand-alone quantizer."""
     torch.manual_seed(4)

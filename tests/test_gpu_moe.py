@@ -88,6 +88,14 @@ def test_indexed_moe_forward(oracle, cuda_dev, tname, x_dim1_is_one):
             xin = x[b, 0 if x_dim1_is_one else s][None]
             r = oracle.cuda_mmvq(wt, wq[ids[b, s]], oracle.cuda_quantize_q8_1(xin, pad(k, 512)), k, n)[0]
             assert rel_err(out[b, s], r) <= TOL
+    # from Q8_1 containers made beforehand (what a fused producer hands over): the same bits, no quantize launch
+    xd = torch.from_numpy(x).to(cuda_dev)
+    rows_in = xd.shape[0] * xd.shape[1]
+    q8 = torch.zeros((rows_in, pad(k, 512) // 32 * 36), dtype=torch.uint8, device=cuda_dev)
+    capi.lib().launch_mmvq_gguf_quantize_q8_1_f32(xd.data_ptr(), q8.data_ptr(), k, pad(k, 512), rows_in,
+                                                  torch.cuda.current_stream().cuda_stream)
+    out_q = qt.indexed_moe_forward_q8_1(q8, xd.shape[1], torch.from_numpy(ids).to(cuda_dev))
+    assert np.array_equal(out_q.cpu().numpy(), out)
     # CPU-exact activations: matches the CPU vec_dot per expert
     set_activation_mode(True)
     try:
@@ -194,6 +202,43 @@ def test_route_kernel_matches_the_tensor_formula(cuda_dev):
         ref_w, ref_ids = route(logits, k, norm)
         assert torch.equal(ids.long(), ref_ids)
         assert torch.allclose(w, ref_w, rtol=1e-5, atol=1e-7)
+
+
+def test_one_launch_router_and_slot_sum(cuda_dev):
+    """cq_moe_router_f32: its logits against the f32 matrix product (summation order differs), its ids and weights bit for
+    bit against cq_moe_route_f32 run on those logits, the arrival counters back at zero, twice in a row.
+    cq_moe_weighted_sum_f32: the slot-order sum, bit for bit against the same operations written with tensor ops."""
+    L = capi.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(11)
+    counters = torch.zeros(64, dtype=torch.int32, device=cuda_dev)
+    for tokens, experts, d, k, norm in ((1, 128, 2048, 8, True), (8, 128, 2048, 8, True), (5, 60, 516, 6, False), (64, 16, 512, 4, True),
+                                        (3, 1024, 64, 32, True)):
+        h = torch.randn(tokens, d, device=cuda_dev)
+        router = torch.randn(experts, d, device=cuda_dev) * 0.05
+        for _ in range(2):
+            logits = torch.full((tokens, experts), float("nan"), device=cuda_dev)
+            ids = torch.full((tokens, k), -1, dtype=torch.int32, device=cuda_dev)
+            w = torch.full((tokens, k), float("nan"), device=cuda_dev)
+            L.cq_moe_router_f32(h.data_ptr(), router.data_ptr(), logits.data_ptr(), ids.data_ptr(), w.data_ptr(), counters.data_ptr(),
+                                tokens, experts, d, k, 1 if norm else 0, st)
+            capi.check("router")
+            want = (h.double() @ router.double().t()).float()
+            assert torch.allclose(logits, want, rtol=1e-4, atol=1e-5)
+            ids2 = torch.empty_like(ids)
+            w2 = torch.empty_like(w)
+            L.cq_moe_route_f32(logits.data_ptr(), ids2.data_ptr(), w2.data_ptr(), tokens, experts, k, 1 if norm else 0, st)
+            capi.check("route")
+            assert torch.equal(ids, ids2) and torch.equal(w, w2)
+            assert int(counters.abs().sum()) == 0
+        y = torch.randn(tokens, k, d, device=cuda_dev)
+        out = torch.empty(tokens, d, device=cuda_dev)
+        L.cq_moe_weighted_sum_f32(y.data_ptr(), w.data_ptr(), out.data_ptr(), tokens, k, d, st)
+        capi.check("weighted sum")
+        acc = torch.zeros(tokens, d, device=cuda_dev)
+        for s_ in range(k):
+            acc = acc + y[:, s_] * w[:, s_:s_ + 1]
+        assert torch.equal(out, acc)
 
 
 def test_qknorm_neox_rope_kernel(cuda_dev):
