@@ -134,6 +134,23 @@ __device__ __forceinline__ void cq_store_out(void *dst, int kind, int64_t i, flo
     else ((__nv_bfloat16 *)dst)[i] = __float2bfloat16(v);
 }
 
+// Eight consecutive outputs of a 16-bit kind (CQ_F16 / CQ_BF16) as one 16-byte store; `dst16` 16-byte aligned.  The same
+// conversions as cq_store_out.
+__device__ __forceinline__ void cq_store_out8_16bit(void *dst16, int kind, const float *v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (kind == CQ_F16) {
+            const __half2 h = __halves2half2(__float2half(v[2 * i]), __float2half(v[2 * i + 1]));
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        } else {
+            const __nv_bfloat162 h = __halves2bfloat162(__float2bfloat16(v[2 * i]), __float2bfloat16(v[2 * i + 1]));
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+    }
+    *reinterpret_cast<uint4 *>(dst16) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Q8_1 quantization of one 32-value block held by 8 consecutive lanes, 4 consecutive values each (value index
 // 4 * (lane & 7) + c).  Same arithmetic as the stand-alone quantizer (quantize_act.cu) and so as the reference
 // (candle-kernels/src/mmvq_gguf.cu:811-911): amax / 127, round(x / d), and the sum added in the order of a 32-lane

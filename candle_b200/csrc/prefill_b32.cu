@@ -367,9 +367,15 @@ prefill32_kernel(const __grid_constant__ CUtensorMap wmap, const uint8_t *__rest
             if (tok < tokens) {
                 const int c0 = row0 + rh * kMyRows;
                 if (out_kind != CQ_F32) {
+                    uint8_t *o16 = (uint8_t *)out_v + 2 * ((size_t)tok * stride_out + c0);
+                    if (c0 + kMyRows <= nrows && (((uintptr_t)o16) & 15) == 0) {
 #pragma unroll
-                    for (int i = 0; i < kMyRows; ++i)
-                        if (c0 + i < nrows) cq_store_out(out_v, out_kind, (int64_t)tok * stride_out + c0 + i, acc[i]);
+                        for (int i = 0; i < kMyRows; i += 8) cq_store_out8_16bit(o16 + 2 * i, out_kind, acc + i);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kMyRows; ++i)
+                            if (c0 + i < nrows) cq_store_out(out_v, out_kind, (int64_t)tok * stride_out + c0 + i, acc[i]);
+                    }
                 } else {
                     float *o = (float *)out_v + (size_t)tok * stride_out + c0;
                     if (c0 + kMyRows <= nrows && (((uintptr_t)o) & 15) == 0) {

@@ -600,9 +600,15 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
             }
             const int c0 = cx.row0 + rh * kMyRows;
             if (store && out_kind != CQ_F32) {
+                uint8_t *o16 = (uint8_t *)out_v + 2 * ((size_t)orow * stride_out + c0);
+                if (c0 + kMyRows <= nrows && (((uintptr_t)o16) & 15) == 0) {       // 32 values = four 16-byte stores
 #pragma unroll
-                for (int i = 0; i < kMyRows; ++i)
-                    if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
+                    for (int i = 0; i < kMyRows; i += 8) cq_store_out8_16bit(o16 + 2 * i, out_kind, acc + i);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kMyRows; ++i)
+                        if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
+                }
             } else if (store) {
                 float *o = (float *)out_v + (size_t)orow * stride_out + c0;
                 if (c0 + kMyRows <= nrows && (((uintptr_t)o) & 15) == 0) {
