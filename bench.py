@@ -397,8 +397,12 @@ def measure_prefill(dev, rank, world, peak_tops):
                 if "dropin_mmq_ms" in row:
                     row["dropin_mmq_ms"] = float(t[2])
                     row["dropin_mmq_tops"] = ops / row["dropin_mmq_ms"] / 1e9
+                # what the tensor pipe executes: per 256-element super-block nine K = 32 steps of N = 128 (two operand planes
+                # of 64 weight rows, plus the block-sums step) where four steps of one plane would be the useful product
+                row["gemm_issued_tops"] = row["gemm_tops"] * 2.25
                 if peak_tops:
                     row["gemm_frac_of_int8_peak"] = row["gemm_tops"] / (peak_tops * world)
+                    row["gemm_issued_frac_of_int8_peak"] = row["gemm_issued_tops"] / (peak_tops * world)
                 out.append(row)
                 del x, y, scratch
         del ws, mms

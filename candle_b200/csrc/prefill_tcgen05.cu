@@ -609,6 +609,42 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
                     for (int i = 0; i < kMyRows; ++i)
                         if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
                 }
+            } else if (!gi.tiles && c0 + kMyRows <= nrows && (stride_out & 3) == 0 && (c0 & 3) == 0 && (((uintptr_t)out_v) & 15) == 0) {
+                // f32, whole 32-row slice (warp-uniform test): three exchange steps turn "a lane holds 32 rows of its token" into
+                // "a lane holds 4 rows of 8 tokens", so that eight lanes write one token's 128 contiguous bytes per store
+                // instruction (four full lines per instruction instead of 32 quarter lines).
+                float cur[kMyRows];
+#pragma unroll
+                for (int i = 0; i < kMyRows; ++i) cur[i] = acc[i];
+#pragma unroll
+                for (int sstep = 0; sstep < 3; ++sstep) {
+                    const int T = 1 << sstep, R = kMyRows >> sstep, H = R >> 1;     // slots held, rows per slot, half
+                    const bool up = (lane >> sstep) & 1;                              // this lane keeps the upper halves
+                    float nxt[kMyRows];
+#pragma unroll
+                    for (int u = 0; u < T; ++u) {
+#pragma unroll
+                        for (int i = 0; i < H; ++i) {
+                            const float lo = cur[u * R + i], hi = cur[u * R + H + i];
+                            const float got = __shfl_xor_sync(0xffffffffu, up ? lo : hi, T);
+                            const float kept = up ? hi : lo;
+                            // slot of the lower-numbered lane first
+                            nxt[(2 * u) * H + i] = up ? got : kept;
+                            nxt[(2 * u + 1) * H + i] = up ? kept : got;
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < kMyRows; ++i) cur[i] = nxt[i];
+                }
+                const int rsub = 16 * (lane & 1) + 8 * ((lane >> 1) & 1) + 4 * ((lane >> 2) & 1);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const int src_lane = (lane & 24) | ((v & 1) << 2) | (v & 2) | ((v >> 2) & 1);     // slot v came from this lane
+                    const int tk = cx.tt * kTokTile + quad * 32 + src_lane;
+                    if (tk < tokens)
+                        *reinterpret_cast<float4 *>((float *)out_v + (size_t)tk * stride_out + c0 + rsub) =
+                            make_float4(cur[4 * v], cur[4 * v + 1], cur[4 * v + 2], cur[4 * v + 3]);
+                }
             } else if (store) {
                 float *o = (float *)out_v + (size_t)orow * stride_out + c0;
                 if (c0 + kMyRows <= nrows && (((uintptr_t)o) & 15) == 0) {
