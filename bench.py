@@ -607,6 +607,11 @@ def run_gpu(args):
     h2d = sum(b * k * 4 for (b, _, k, _) in order)
     d2h = sum(b * n * 4 for (b, _, _, n) in order)
 
+    host_fwd = None
+    if world > 1:
+        from candle_b200.parallel import ShardedHostForward
+        host_fwd = ShardedHostForward(gather, dev)
+
     def step_e2e():
         if world == 1:      # host buffers in, host buffers out: one library call per matmul, copy-backs overlap the next call
             last = None
@@ -615,10 +620,9 @@ def run_gpu(args):
                 last.forward_host(h_x[(k, b)], h_y[(n, b)])
             last.host_flush()
             return
-        for (b, t, k, n) in order:
-            d_x[(k, b)].copy_(h_x[(k, b)], non_blocking=True)
-            y = mats[(t, k, n)].forward(d_x[(k, b)], out=outs[(n, b)])
-            h_y[(n, b)].copy_(gather(y), non_blocking=True)
+        for (b, t, k, n) in order:      # several GPUs: the same overlap around the shard's product and the all-gather
+            host_fwd(mats[(t, k, n)], h_x[(k, b)], h_y[(n, b)])
+        host_fwd.flush()
 
     ms_e2e = timed(step_e2e, args.steps, args.warmup, False)
     if gather is not None and hasattr(gather, "check"):
@@ -628,21 +632,41 @@ def run_gpu(args):
     del mats, xs, outs, q8, h_x, h_y, d_x
     gather = None
     torch.cuda.empty_cache()
-    int8_peak = measure_int8_peak(dev) if not args.no_prefill else None
+    def extra(fn):
+        """One of the additional measurements: a failure in it (a bounded wait that gave up, out of memory) is reported in
+        its place instead of taking the headline down.  Its checks come after its last collective, so the ranks stay in
+        step; they agree on the outcome before going on."""
+        err, out = None, None
+        try:
+            out = fn()
+        except Exception as e:      # noqa: BLE001 - reported in the JSON line
+            err = f"{type(e).__name__}: {e}"
+            L.cq_peer_gather_clear_timeout()
+            L.cq_clear_status()
+            torch.cuda.empty_cache()
+        if world > 1:
+            bad = torch.tensor([1 if err else 0], device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if int(bad.item()) and err is None:
+                err = "failed on another rank"
+        return {"error": err} if err else out
+
+    int8_peak = extra(lambda: measure_int8_peak(dev)) if not args.no_prefill else None
     prefill = prefill_b32 = None
     if not args.no_prefill:
-        prefill = measure_prefill(dev, rank, world, int8_peak["burst_tops"] if int8_peak else None)
-        prefill_b32 = measure_prefill_block_formats(dev, int8_peak["burst_tops"] if int8_peak else None) if world == 1 else None
+        peak_i8 = int8_peak.get("burst_tops") if isinstance(int8_peak, dict) else None
+        prefill = extra(lambda: measure_prefill(dev, rank, world, peak_i8))
+        prefill_b32 = extra(lambda: measure_prefill_block_formats(dev, peak_i8)) if world == 1 else None
     decode = None
     if not args.no_decode:
-        decode = [decode_tok_s(dev, rank, world, b) for b in (1, 8)]
+        decode = [extra(lambda b=b: decode_tok_s(dev, rank, world, b)) for b in (1, 8)]
     moe = None
     if not args.no_moe:
         moe = {"model": "Qwen3-30B-A3B-shaped, experts Q4_K, attention and head Q6_K, random weights", "prompt": 1024, "steps": 128,
                "parallelism": f"expert parallel x{world}" if world > 1 else "single GPU",
-               "runs": [moe_decode_tok_s(dev, rank, world, b, 1024, 128) for b in (1, 8)]}
+               "runs": [extra(lambda b=b: moe_decode_tok_s(dev, rank, world, b, 1024, 128)) for b in (1, 8)]}
         if world == 1:
-            moe["grouped_gemm"] = measure_moe_gemm(dev)
+            moe["grouped_gemm"] = extra(lambda: measure_moe_gemm(dev))
 
     if rank != 0:
         if world > 1:

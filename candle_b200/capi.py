@@ -85,6 +85,8 @@ def lib() -> C.CDLL:
         L.cq_peer_gather_stage_bytes.restype = C.c_size_t
         L.cq_peer_exchange_rows.argtypes = [vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, vp]
         L.cq_peer_exchange_rows.restype = None
+        L.cq_peer_exchange_stage_bytes.argtypes = [i32, i32]
+        L.cq_peer_exchange_stage_bytes.restype = C.c_size_t
         L.cq_peer_gather_set_limit_clocks.argtypes = [C.c_longlong]
         L.cq_peer_gather_timeout_flag.restype = i32
         L.cq_add_rms_norm_q8_1.argtypes = [vp, vp, vp, vp, i32, i32, i32, C.c_float, vp]

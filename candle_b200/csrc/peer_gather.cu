@@ -105,8 +105,13 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint32_t *__rest
 // expert's index relative to this rank's first expert, so this rank owns row j iff 0 <= owner[j] < n_owned.  A thread stores
 // the words of the rows this rank owns into the staging areas of all other ranks (and into its own result), then polls
 // the slots of the rows it does not own.  One slot per word (a row has a single writer), the same {word, epoch} slots,
-// epoch counter, two areas by parity and bounded polls as the gather above; each row crosses a link once, nothing else does
+// epoch counter, two areas by parity and bounded polls as the gather above; each row crosses a link once
 // (candle's fused MoE block has no multi-GPU form; an all-reduce of the same buffer would send mostly zeros).
+// A rank may own no row at all in an exchange, and then nobody would wait for it: two exchanges later a fast rank could
+// overwrite slots that this rank still polls.  So every rank also stores an arrival slot (after the word slots: one per
+// rank) into every other rank's area when it starts, and polls the arrival slots of all ranks before it finishes: no rank
+// completes exchange i + 1 before every rank has begun it, i.e. has finished reading exchange i - the order the gather gets
+// for free because there every rank sends data to everybody.
 __global__ void __launch_bounds__(256) peer_exchange_rows_kernel(const uint32_t *__restrict__ src, const int *__restrict__ owner,
                                                                  int n_owned, PeerPtrs stage, uint32_t *__restrict__ dst,
                                                                  unsigned *state, int rows, int n, int rank, int world) {
@@ -116,7 +121,8 @@ __global__ void __launch_bounds__(256) peer_exchange_rows_kernel(const uint32_t 
     void *const *area = stage.p[epoch & 1u];
     const int64_t total = (int64_t)rows * n;
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
-    // pass 1: the rows this rank owns, to everybody
+    // arrival slots first, then pass 1: the rows this rank owns, to everybody
+    if (tid >= 1 && tid < world) st_slot((uint2 *)area[(rank + (int)tid) % world] + total + rank, 0u, epoch);
     for (int64_t i = tid; i < total; i += nthr) {
         const int j = (int)(i / n);
         if ((unsigned)owner[j] >= (unsigned)n_owned) continue;
@@ -152,6 +158,13 @@ __global__ void __launch_bounds__(256) peer_exchange_rows_kernel(const uint32_t 
             dst[i] = v[u].x;
         }
     }
+    if (tid < world && (int)tid != rank && !gave_up) {       // every other rank has begun this exchange
+        const uint2 *flag = mine + total + tid;
+        const long long t0 = clock64();
+        while (ld_slot(flag).y != epoch) {
+            if (clock64() - t0 > limit) { gave_up = true; break; }
+        }
+    }
     if (gave_up) atomicExch(&g_peer_gather_timeout, 1);
     __syncthreads();
     if (threadIdx.x == 0 && atomicAdd(&state[1], 1u) == gridDim.x - 1) {
@@ -162,6 +175,11 @@ __global__ void __launch_bounds__(256) peer_exchange_rows_kernel(const uint32_t 
 }
 
 }  // namespace
+
+extern "C" size_t cq_peer_exchange_stage_bytes(int rows, int n) {
+    if (rows <= 0 || n <= 0) return 0;
+    return ((size_t)rows * n + CQ_MAX_PEERS) * 8;
+}
 
 extern "C" void cq_peer_exchange_rows(const void *src, const int *owner, int n_owned, void *const *peer_stage, void *dst, void *state,
                                       int rows, int n, int rank, int world, void *stream) {

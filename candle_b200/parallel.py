@@ -89,8 +89,9 @@ class PeerGatherer(Gatherer):
         self._slots: dict = {}
         self._last = None
 
-    def _new_slot(self, rows: int, n_local: int, dtype, writers: int | None = None):
-        nbytes = self._capi.lib().cq_peer_gather_stage_bytes(rows, n_local, self.world if writers is None else writers)
+    def _new_slot(self, rows: int, n_local: int, dtype, row_exchange: bool = False):
+        lib = self._capi.lib()
+        nbytes = lib.cq_peer_exchange_stage_bytes(rows, n_local) if row_exchange else lib.cq_peer_gather_stage_bytes(rows, n_local, self.world)
         stage = self._symm.empty((nbytes,), dtype=torch.uint8, device=self.device)
         hdl = self._symm.rendezvous(stage, group=self._group_name)
         stage.zero_()
@@ -155,7 +156,7 @@ class PeerGatherer(Gatherer):
         if key not in self._slots:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("a new exchange shape inside CUDA-graph capture: run the step once before capturing")
-            areas = [self._new_slot(rows, n, local.dtype, 1) for _ in range(2)]
+            areas = [self._new_slot(rows, n, local.dtype, True) for _ in range(2)]
             ptrs = (ctypes.c_void_p * (2 * self._capi.MAX_PEERS))()
             for e in range(2):
                 for p, a in enumerate(areas[e]):
@@ -178,6 +179,59 @@ class PeerGatherer(Gatherer):
         """Raises if any gather so far gave up waiting for another rank (synchronises the device)."""
         if self._capi.lib().cq_peer_gather_timeout_flag() != 0:
             raise RuntimeError("peer gather: a bounded wait for another rank gave up")
+
+
+class ShardedHostForward:
+    """`QMatMul.forward` of a row shard for callers whose activations and results live in pinned HOST memory, one process
+    per GPU: upload on an upload stream, the shard's product and the all-gather on the caller's stream, the copy-back of the
+    gathered rows on a copy stream - so that the copies of one call overlap the arithmetic of its neighbours, as
+    `QMatMul.forward_host` does on a single GPU.  A ring of four staging slots; `flush()` joins the copy stream.
+    The host activations must be complete when the call is made."""
+
+    SLOTS = 4
+
+    def __init__(self, gather: Gatherer, device):
+        self.gather, self.device = gather, torch.device(device)
+        self.up, self.down = torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device)
+        self._slots = [{"x": None, "free": None} for _ in range(self.SLOTS)]
+        self._next = 0
+        self._result_events: dict = {}      # gathered-result shape -> copy-back events of its last two uses
+
+    def __call__(self, mm, h_x: torch.Tensor, h_y: torch.Tensor) -> None:
+        sl = self._slots[self._next]
+        self._next = (self._next + 1) % self.SLOTS
+        main = torch.cuda.current_stream(self.device)
+        if sl["free"] is not None:      # the product that read this slot's activations is over
+            self.up.wait_event(sl["free"])
+        need = h_x.numel() * h_x.element_size()
+        if sl["x"] is None or sl["x"].numel() < need:
+            torch.cuda.synchronize(self.device)
+            sl["x"] = torch.empty(max(need, 1 << 16), dtype=torch.uint8, device=self.device)
+        d_x = sl["x"][:need].view(h_x.dtype).view(h_x.shape)
+        with torch.cuda.stream(self.up):
+            d_x.copy_(h_x, non_blocking=True)
+            ev_up = torch.cuda.Event()
+            ev_up.record(self.up)
+        main.wait_event(ev_up)
+        y = mm.forward(d_x)
+        # the gatherer alternates two result buffers per shape: their last copy-backs must be over before one is rewritten
+        key = (tuple(y.shape), y.dtype)
+        for ev in self._result_events.get(key, ()):
+            main.wait_event(ev)
+        full = self.gather(y)
+        done = torch.cuda.Event()
+        done.record(main)
+        self.down.wait_event(done)
+        with torch.cuda.stream(self.down):
+            h_y.copy_(full, non_blocking=True)
+            ev_dn = torch.cuda.Event()
+            ev_dn.record(self.down)
+        sl["free"] = done
+        self._result_events[key] = (self._result_events.get(key, ()) + (ev_dn,))[-2:]
+
+    def flush(self) -> None:
+        """The caller's stream waits for every copy-back in flight: synchronise it and the host results are complete."""
+        torch.cuda.current_stream(self.device).wait_stream(self.down)
 
 
 def make_gatherer(group=None, world: int | None = None, device=None) -> Gatherer:

@@ -301,7 +301,10 @@ void cq_peer_gather_words(const void *src, int src_stride, void *const *peer_sta
 /* Rows that each belong to one rank (expert-parallel MoE: the rank holding the row's expert): rank r owns row j iff
  * 0 <= owner[j] < n_owned (owner: device int32 [rows], the expert index relative to the rank's first expert).  Owned rows
  * of src [rows, n] (32-bit words) go to every rank's dst [rows, n]; the others are received.  Staging areas: as above, two
- * per site, rows * n * 8 bytes each (cq_peer_gather_stage_bytes(rows, n, 1)); same epoch state, limits and give-up flag. */
+ * per site, cq_peer_exchange_stage_bytes(rows, n) zeroed bytes each (the word slots, then one arrival slot per rank: every
+ * rank announces itself to all others in every exchange, also when it owns no row); same epoch state, limits and give-up
+ * flag. */
+size_t cq_peer_exchange_stage_bytes(int rows, int n);
 void cq_peer_exchange_rows(const void *src, const int *owner, int n_owned, void *const *peer_stage, void *dst, void *state,
                            int rows, int n, int rank, int world, void *stream);
 int cq_peer_gather_timeout_flag(void);

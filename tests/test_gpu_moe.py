@@ -108,6 +108,33 @@ def test_indexed_moe_forward(oracle, cuda_dev, tname, x_dim1_is_one):
             assert rel_err(out2[b, s], oracle.matmul(wt, xin, wq[ids[b, s]], n)[0]) <= TOL
 
 
+def test_q8_0_experts_use_the_true_expert_stride(oracle, cuda_dev):
+    """A stated deviation from the reference.  Its indexed kernel computes the byte distance between experts as
+    n * k / 256 * sizeof(block) for every format (candle-kernels/src/quantized.cu:4703), which for Q8_0 - 34-byte blocks
+    of 32 values - is an eighth of the true distance, so every expert but the first reads the wrong rows.  This library
+    strides by n * row_bytes: expert e's output is the product with expert e's own weights, and it is NOT what the
+    reference's address arithmetic would have produced."""
+    wt = TYPES["q8_0"]
+    e, n, k, batch, topk = 6, 64, 512, 2, 2
+    wq = _experts(oracle, wt, e, n, k, seed=9)                                      # [e, n, row_bytes]
+    ids = np.array([[1, 4], [5, 2]], dtype=np.int32)
+    x = np.random.default_rng(4).standard_normal((batch, 1, k)).astype(np.float32)
+    qt = QTensor.from_data(wq.reshape(-1), GgmlDType(wt), (e, n, k), cuda_dev)
+    out = qt.indexed_moe_forward(torch.from_numpy(x).to(cuda_dev), torch.from_numpy(ids).to(cuda_dev)).cpu().numpy()
+    flat = wq.reshape(-1)
+    row_bytes = k // 32 * 34
+    for b in range(batch):
+        for s_ in range(topk):
+            ex = int(ids[b, s_])
+            q8 = oracle.cuda_quantize_q8_1(x[b], pad(k, 512))
+            right = oracle.cuda_mmvq(wt, wq[ex], q8, k, n)[0]
+            assert rel_err(out[b, s_], right) <= TOL
+            wrong_start = ex * (n * k // 256 * 34)                                  # the reference's stride
+            wrong_w = flat[wrong_start:wrong_start + n * row_bytes].reshape(n, row_bytes)
+            wrong = oracle.cuda_mmvq(wt, wrong_w, q8, k, n)[0]
+            assert rel_err(out[b, s_], wrong) > 0.1
+
+
 def test_moe_prefill_entry_point_small_and_large(oracle, cuda_dev):
     """moe_gemm_gguf_prefill: under 64 pairs it is the decode entry point on the up-cast values (same bits); from 64 pairs on
     the grouped tensor-core kernel, whose arithmetic is the CPU path's (Q8_K activations)."""

@@ -94,8 +94,10 @@ def check_gather(dev, rank, world) -> str:
         g2 = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g2, stream=side):
             o2 = peer.exchange_rows(ex, ow, e_local)
-    for rep in range(20):
+    for rep in range(30):
         experts = torch.randint(0, e_local * world, (8,), device=dev, dtype=torch.int32, generator=gen_all)
+        if rep % 3 != 2:        # all rows on one rank, several exchanges in a row: the others own nothing and must still be waited for
+            experts = torch.full_like(experts, ((rep // 3) % world) * e_local + 1)
         truth = torch.randn((8, 2048), device=dev, generator=gen_all)
         ow.copy_(experts - rank * e_local)
         ex.copy_(torch.where(((ow >= 0) & (ow < e_local))[:, None], truth, torch.zeros_like(truth)))
@@ -106,6 +108,27 @@ def check_gather(dev, rank, world) -> str:
         torch.cuda.synchronize()
         if not torch.equal(o2, truth):
             bad.append(("rows graph", rep))
+    peer.check()
+    # host buffers in, gathered host buffers out, with the copies on their own streams
+    from candle_b200.parallel import ShardedHostForward
+    from candle_b200.quantized import GgmlDType, QMatMul, QTensor
+    from candle_b200.synth import random_blocks
+    n_all, kk = 1024, 4096
+    mm = QMatMul.from_qtensor(QTensor.from_device_blocks(random_blocks(GgmlDType.Q4K, n_all // world, kk, 5 + rank, dev), GgmlDType.Q4K,
+                                                         (n_all // world, kk)))
+    hf = ShardedHostForward(peer, dev)
+    cpu_gen = torch.Generator().manual_seed(31)         # the same activations on every rank
+    cases = []
+    for b in (1, 8, 3, 1, 1, 8, 8, 2, 5, 1):
+        hx = torch.randn((b, kk), generator=cpu_gen).pin_memory()
+        hy = torch.full((b, n_all), float("nan")).pin_memory()
+        hf(mm, hx, hy)
+        cases.append((hx, hy))
+    hf.flush()
+    torch.cuda.synchronize()
+    for i, (hx, hy) in enumerate(cases):
+        if not torch.equal(hy, ref(mm.forward(hx.to(dev))).cpu()):
+            bad.append(("host forward", i))
     peer.check()
     # cost of one gather: 100 alternating gathers of a decode-sized and a head-sized slice, replayed from a graph
     for name, g_ in (("peer", peer), ("nccl", ref)):
