@@ -173,3 +173,54 @@ def test_reads_a_file_written_by_the_gguf_package(lib, tmp_path):
     assert np.array_equal(c.tensor_bytes("blk.0.attn_norm.weight").view(np.float32), norm)
     info = c.tensor_infos["blk.0.ffn_down.weight"]
     assert info.ggml_dtype == GgmlDType.Q8_0 and info.shape == (4, 64) and c.tensor_bytes("blk.0.ffn_down.weight").tobytes() == q8.tobytes()
+
+
+def test_write_round_trips_through_the_reader_and_the_gguf_package(lib, tmp_path):
+    """`gguf_file.write` (the reference's `gguf_file::write`): every value type, nested and empty arrays, tensors of
+    several block formats with 32-byte padding between them; read back by this library's reader and, when installed, by
+    the independent `gguf` package."""
+    from candle_b200.gguf_file import HostTensor, Value, write
+    rng = np.random.default_rng(11)
+    w1, w2 = _blocks(rng, GgmlDType.Q4K, 8, 512), _blocks(rng, GgmlDType.Q8_0, 5, 96)       # 5 * 3 * 34 = 510 bytes: padded to 512
+    norm = np.arange(7, dtype=np.float32).tobytes()
+    meta = [("general.architecture", Value("string", "llama")), ("llama.block_count", Value("u32", 32)), ("a.u8", Value("u8", 200)),
+            ("a.i8", Value("i8", -5)), ("a.u16", Value("u16", 65000)), ("a.i16", Value("i16", -300)), ("a.i32", Value("i32", -70000)),
+            ("a.f32", Value("f32", 0.5)), ("a.bool", Value("bool", True)), ("a.u64", Value("u64", 2 ** 60 + 1)),
+            ("a.i64", Value("i64", -2 ** 40)), ("a.f64", Value("f64", 0.1)),
+            ("tokens", Value("array", [Value("string", s) for s in ("<s>", "a\"b", "tab\t")])),
+            ("nested", Value("array", [Value("array", [Value("i32", 1), Value("i32", -2)]), Value("array", [])])),
+            ("empty", Value("array", []))]
+    tensors = [("blk.0.attn_q.weight", HostTensor(GgmlDType.Q4K, (8, 512), w1)), ("blk.0.ffn_down.weight", HostTensor(GgmlDType.Q8_0, (5, 96), w2)),
+               ("norm.weight", HostTensor(GgmlDType.F32, (7,), norm))]
+    path = tmp_path / "written.gguf"
+    with open(path, "wb") as f:
+        write(f, meta, tensors)
+    raw = path.read_bytes()
+    assert raw[:8] == struct.pack("<II", 0x46554747, 2) and len(raw) % 32 == 0
+    c = Content.read(path)
+    assert c.magic == 2 and c.tensor_data_offset % 32 == 0
+    md = c.metadata
+    assert md["general.architecture"] == "llama" and md["llama.block_count"] == 32 and md["a.bool"] is True
+    assert (md["a.u8"], md["a.i8"], md["a.u16"], md["a.i16"], md["a.i32"], md["a.f32"]) == (200, -5, 65000, -300, -70000, 0.5)
+    assert md["a.u64"] == 2 ** 60 + 1 and md["a.i64"] == -2 ** 40 and md["a.f64"] == 0.1
+    assert md["tokens"] == ["<s>", "a\"b", "tab\t"] and md["nested"] == [[1, -2], []] and md["empty"] == []
+    q, d, nw = c.tensor_infos["blk.0.attn_q.weight"], c.tensor_infos["blk.0.ffn_down.weight"], c.tensor_infos["norm.weight"]
+    assert (q.ggml_dtype, q.shape, q.offset) == (GgmlDType.Q4K, (8, 512), 0)
+    assert (d.ggml_dtype, d.shape, d.offset) == (GgmlDType.Q8_0, (5, 96), len(w1))
+    assert (nw.ggml_dtype, nw.shape, nw.offset) == (GgmlDType.F32, (7,), len(w1) + 512)
+    assert c.tensor_bytes("blk.0.attn_q.weight").tobytes() == w1 and c.tensor_bytes("blk.0.ffn_down.weight").tobytes() == w2
+    assert c.tensor_bytes("norm.weight").tobytes() == norm
+    c.close()
+    with pytest.raises(CandleQError, match="multiple value-types"):
+        with open(tmp_path / "bad.gguf", "wb") as f:
+            write(f, [("x", Value("array", [Value("u8", 1), Value("i8", 1)]))], [])
+    with pytest.raises(CandleQError, match="do not match shape"):
+        with open(tmp_path / "bad.gguf", "wb") as f:
+            write(f, [], [("w", HostTensor(GgmlDType.Q4K, (2, 256), b"\0" * 100))])
+    gguf = pytest.importorskip("gguf")
+    r = gguf.GGUFReader(str(path))
+    assert int(r.fields["llama.block_count"].parts[-1][0]) == 32
+    by_name = {t.name: t for t in r.tensors}
+    assert bytes(by_name["blk.0.ffn_down.weight"].data.tobytes()) == w2
+    assert bytes(by_name["blk.0.attn_q.weight"].data.tobytes()) == w1
+    assert by_name["norm.weight"].data.tobytes() == norm
