@@ -127,6 +127,7 @@ def lib() -> C.CDLL:
         L.cqh_qtensor_device_ptr.restype = vp
         L.cqh_qmatmul_forward.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
         L.cqh_qmatmul_forward_host.argtypes = [vp, vp, i32, i64p, i32, vp, vp]
+        L.cqh_qmatmul_forward_host_sharded.argtypes = [vp, vp, i32, i64p, i32, vp, vp, vp, i32, i32, vp]
         L.cqh_qmatmul_host_flush.argtypes = [i32, vp]
         L.cqh_set_act_mode.argtypes = [i32]
         L.cqh_qtensor_dequantize.argtypes = [vp, vp, i32, vp]

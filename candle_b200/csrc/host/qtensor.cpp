@@ -358,8 +358,8 @@ extern "C" const void *cqh_qtensor_device_ptr(void *handle) {
 namespace {
 constexpr int kHostSlots = 4;
 struct HostSlot {
-    void *x = nullptr, *y = nullptr;
-    size_t cap_x = 0, cap_y = 0;
+    void *x = nullptr, *y = nullptr, *z = nullptr;      // activations, result, (sharded form) this rank's slice
+    size_t cap_x = 0, cap_y = 0, cap_z = 0;
     cudaEvent_t up_done = nullptr, gemv_done = nullptr, d2h_done = nullptr;
     bool pending = false;
 };
@@ -370,6 +370,17 @@ struct HostRing {
 };
 std::mutex g_host_mu;
 std::map<int, HostRing> g_host_ring;
+
+void ring_init(HostRing &ring) {       // streams and events of a device's ring, on first use
+    if (ring.copy_stream) return;
+    cuda_check(cudaStreamCreateWithFlags(&ring.copy_stream, cudaStreamNonBlocking), "forward_host: copy stream");
+    cuda_check(cudaStreamCreateWithFlags(&ring.up_stream, cudaStreamNonBlocking), "forward_host: upload stream");
+    for (auto &sl : ring.s) {
+        cuda_check(cudaEventCreateWithFlags(&sl.up_done, cudaEventDisableTiming), "forward_host: event");
+        cuda_check(cudaEventCreateWithFlags(&sl.gemv_done, cudaEventDisableTiming), "forward_host: event");
+        cuda_check(cudaEventCreateWithFlags(&sl.d2h_done, cudaEventDisableTiming), "forward_host: event");
+    }
+}
 
 void grow(void *&p, size_t &cap, size_t need, cudaStream_t copy_stream) {
     if (cap >= need) return;
@@ -402,15 +413,7 @@ extern "C" int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_
         cudaStream_t st = (cudaStream_t)stream;
         std::lock_guard<std::mutex> lk(g_host_mu);
         HostRing &ring = g_host_ring[dev];
-        if (!ring.copy_stream) {
-            cuda_check(cudaStreamCreateWithFlags(&ring.copy_stream, cudaStreamNonBlocking), "forward_host: copy stream");
-            cuda_check(cudaStreamCreateWithFlags(&ring.up_stream, cudaStreamNonBlocking), "forward_host: upload stream");
-            for (auto &sl : ring.s) {
-                cuda_check(cudaEventCreateWithFlags(&sl.up_done, cudaEventDisableTiming), "forward_host: event");
-                cuda_check(cudaEventCreateWithFlags(&sl.gemv_done, cudaEventDisableTiming), "forward_host: event");
-                cuda_check(cudaEventCreateWithFlags(&sl.d2h_done, cudaEventDisableTiming), "forward_host: event");
-            }
-        }
+        ring_init(ring);
         HostSlot &sl = ring.s[ring.next];
         ring.next = (ring.next + 1) % kHostSlots;
         if (sl.pending) {       // the slot's last copy-back (hence its last product) must be over before its buffers are written again
@@ -426,6 +429,54 @@ extern "C" int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_
         cuda_check(cudaEventRecord(sl.gemv_done, st), "forward_host: event record");
         cuda_check(cudaStreamWaitEvent(ring.copy_stream, sl.gemv_done, 0), "forward_host: copy stream wait");
         cuda_check(cudaMemcpyAsync(host_out, sl.y, rows * n * es, cudaMemcpyDeviceToHost, ring.copy_stream), "forward_host: copy-back");
+        cuda_check(cudaEventRecord(sl.d2h_done, ring.copy_stream), "forward_host: event record");
+        sl.pending = true;
+    });
+}
+
+// The same for one process per GPU with W sharded by rows: this rank's slice of the product is computed, the slices are
+// exchanged by the peer-memory gather (cq_peer_gather_words; `peer_stage` and `gather_state` as that function takes them, for
+// the shape [rows, n_local]) and the gathered rows [rows, n_local * world] go back to the host.  f32 only (the gather
+// moves 32-bit words).
+extern "C" int cqh_qmatmul_forward_host_sharded(void *handle, const void *host_x, int x_dtype, const int64_t *dims, int ndims,
+                                                void *host_out, void *const *peer_stage, void *gather_state, int rank, int world,
+                                                void *stream) {
+    return guarded([&] {
+        auto &t = *(std::shared_ptr<QTensor> *)handle;
+        QMatMul mm(t);
+        if (ndims < 2) throw Error("input tensor has only one dimension");
+        if (!host_x || !host_out || !peer_stage || !gather_state) throw Error("forward_host_sharded: null pointer");
+        if ((DType)x_dtype != DType::F32) throw Error("forward_host_sharded: f32 activations only");
+        if (world < 1 || rank < 0 || rank >= world) throw Error("forward_host_sharded: bad rank / world");
+        const auto &sh = t->shape();
+        size_t rows = 1;
+        for (int i = 0; i + 1 < ndims; ++i) rows *= (size_t)dims[i];
+        const size_t k = (size_t)dims[ndims - 1], n_local = (size_t)sh[0], n = n_local * (size_t)world;
+        if (rows == 0) return;
+        const int dev = t->storage().device();
+        DeviceGuard g(dev);
+        cudaStream_t st = (cudaStream_t)stream;
+        std::lock_guard<std::mutex> lk(g_host_mu);
+        HostRing &ring = g_host_ring[dev];
+        ring_init(ring);
+        HostSlot &sl = ring.s[ring.next];
+        ring.next = (ring.next + 1) % kHostSlots;
+        if (sl.pending) {
+            cuda_check(cudaStreamWaitEvent(ring.up_stream, sl.d2h_done, 0), "forward_host: wait for the slot's copy-back");
+            sl.pending = false;
+        }
+        grow(sl.x, sl.cap_x, rows * k * 4, ring.copy_stream);
+        grow(sl.z, sl.cap_z, rows * n_local * 4, ring.copy_stream);
+        grow(sl.y, sl.cap_y, rows * n * 4, ring.copy_stream);
+        cuda_check(cudaMemcpyAsync(sl.x, host_x, rows * k * 4, cudaMemcpyHostToDevice, ring.up_stream), "forward_host: upload");
+        cuda_check(cudaEventRecord(sl.up_done, ring.up_stream), "forward_host: event record");
+        cuda_check(cudaStreamWaitEvent(st, sl.up_done, 0), "forward_host: wait for the upload");
+        mm.forward(sl.x, DType::F32, dims, ndims, sl.z, st);
+        cq_peer_gather_words(sl.z, (int)n_local, peer_stage, sl.y, gather_state, (int)rows, (int)n_local, (int)n, rank, world, st);
+        lib_check("forward_host_sharded: gather");
+        cuda_check(cudaEventRecord(sl.gemv_done, st), "forward_host: event record");
+        cuda_check(cudaStreamWaitEvent(ring.copy_stream, sl.gemv_done, 0), "forward_host: copy stream wait");
+        cuda_check(cudaMemcpyAsync(host_out, sl.y, rows * n * 4, cudaMemcpyDeviceToHost, ring.copy_stream), "forward_host: copy-back");
         cuda_check(cudaEventRecord(sl.d2h_done, ring.copy_stream), "forward_host: event record");
         sl.pending = true;
     });

@@ -175,7 +175,9 @@ class MoeShapedDecoder:
         local = ids - self.e0 if self.world > 1 else ids           # other ranks' experts fall outside [0, e_local): skipped
         zero = self.world > 1
         a = torch.empty((R, k, f), dtype=torch.float32, device=self.device)
-        if R * k >= max(64, 4 * self.e_local):     # prompt: pairs sorted by expert, grouped GEMM on the tensor cores
+        # The switch between the two arithmetics (Q8_1 GEMV below it, Q8_K tensor-core GEMM above) depends on the MODEL's expert
+        # count, not on how many experts this rank holds: the same step must take the same path at every world size.
+        if R * k >= max(64, 4 * cfg.experts):     # prompt: pairs sorted by expert, grouped GEMM on the tensor cores
             experts, pairs = torch.sort(local.reshape(-1), stable=True)
             gu = moe_prefill_gemm(h, L.gate_up, None, pairs, experts, k, zero_init=zero)          # [R * k, 2f]
             lib.cq_silu_mul_f32(gu.data_ptr(), a.data_ptr(), R * k, f, st)
@@ -250,7 +252,7 @@ class MoeShapedDecoder:
                     delta = L.wo.forward(att)
                 self._rec(f"{li}.att", att)
                 self._rec(f"{li}.x_mid", x), self._rec(f"{li}.wo", delta)
-                if fused and R * cfg.experts_per_tok < max(64, 4 * self.e_local):     # f32 rows for the router, Q8_1 for the experts
+                if fused and R * cfg.experts_per_tok < max(64, 4 * cfg.experts):     # f32 rows for the router, Q8_1 for the experts
                     h = torch.empty_like(x)
                     h8 = torch.empty((R, cfg.d_model // 32 * 36), dtype=torch.uint8, device=self.device)
                     lib.cq_add_rms_norm_f32_q8_1(x.data_ptr(), delta.data_ptr(), L.ffn_norm.data_ptr(), h.data_ptr(), h8.data_ptr(),

@@ -115,19 +115,7 @@ class PeerGatherer(Gatherer):
             local = local.contiguous()
         rows, n_local = local.shape
         key = (rows, n_local, local.dtype)
-        if key not in self._slots:
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError("a new gather shape inside CUDA-graph capture: run the step once before capturing")
-            areas = [self._new_slot(rows, n_local, local.dtype) for _ in range(2)]      # even / odd epochs
-            ptrs = (ctypes.c_void_p * (2 * self._capi.MAX_PEERS))()
-            for e in range(2):
-                for p, a in enumerate(areas[e]):
-                    ptrs[e * self._capi.MAX_PEERS + p] = a
-            outs = [torch.empty((rows, self.world * n_local), dtype=local.dtype, device=self.device) for _ in range(2)]
-            self._slots[key] = [outs, 0, ptrs]
-            torch.cuda.synchronize()
-            dist.barrier(group=self.group)      # nobody stores into a staging area before its owner has zeroed it
-        entry = self._slots[key]
+        entry = self._ensure(key)
         if self._last == key:
             entry[1] ^= 1       # back-to-back gathers of one shape return different result tensors
         self._last = key
@@ -136,6 +124,41 @@ class PeerGatherer(Gatherer):
                                                rows, n_local, self.world * n_local, self.rank, self.world,
                                                torch.cuda.current_stream().cuda_stream)
         return full if full.dtype == dtype else full.view(dtype)
+
+    def _ensure(self, key):
+        """The staging areas and result buffers of a gather shape (rows, n_local, dtype), made on first use - a collective
+        step, outside CUDA-graph capture."""
+        if key not in self._slots:
+            rows, n_local, dtype = key
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("a new gather shape inside CUDA-graph capture: run the step once before capturing")
+            areas = [self._new_slot(rows, n_local, dtype) for _ in range(2)]      # even / odd epochs
+            ptrs = (ctypes.c_void_p * (2 * self._capi.MAX_PEERS))()
+            for e in range(2):
+                for p, a in enumerate(areas[e]):
+                    ptrs[e * self._capi.MAX_PEERS + p] = a
+            outs = [torch.empty((rows, self.world * n_local), dtype=dtype, device=self.device) for _ in range(2)]
+            self._slots[key] = [outs, 0, ptrs]
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)      # nobody stores into a staging area before its owner has zeroed it
+        return self._slots[key]
+
+    def forward_host(self, mm, h_x: torch.Tensor, h_y: torch.Tensor) -> bool:
+        """`mm.forward` of this rank's row shard on f32 activations in pinned host memory, the gather of the slices and the
+        copy-back of the gathered rows into `h_y`, as ONE library call (uploads and copy-backs on the library's own
+        streams, see `QMatMul.forward_host`; join with `mm.host_flush()`).  False when the slice is too large for the
+        slot protocol: the caller then uses `ShardedHostForward`."""
+        rows = h_x.numel() // h_x.shape[-1]
+        n_local = mm.qtensor.shape[0]
+        if h_x.dtype != torch.float32 or h_y.dtype != torch.float32 or rows * n_local * 4 * (self.world - 1) > 4 * self.MAX_SENT_WORDS:
+            return False
+        entry = self._ensure((rows, n_local, torch.float32))
+        self._last = None
+        dims = (ctypes.c_int64 * h_x.dim())(*[int(d) for d in h_x.shape])
+        self._capi.hcheck(self._capi.lib().cqh_qmatmul_forward_host_sharded(
+            mm.qtensor._h, h_x.data_ptr(), 0, dims, h_x.dim(), h_y.data_ptr(), entry[2], self._state.data_ptr(), self.rank, self.world,
+            torch.cuda.current_stream().cuda_stream), "forward_host_sharded")
+        return True
 
     def exchange_rows(self, local: torch.Tensor, owner: torch.Tensor, n_owned: int):
         """Rows of `local` [rows, n] (4-byte elements) that each belong to one rank - this rank owns row j iff
@@ -198,6 +221,10 @@ class ShardedHostForward:
         self._result_events: dict = {}      # gathered-result shape -> copy-back events of its last two uses
 
     def __call__(self, mm, h_x: torch.Tensor, h_y: torch.Tensor) -> None:
+        one_call = getattr(self.gather, "forward_host", None)
+        if one_call is not None and one_call(mm, h_x, h_y):
+            self._flush_mm = mm
+            return
         sl = self._slots[self._next]
         self._next = (self._next + 1) % self.SLOTS
         main = torch.cuda.current_stream(self.device)
@@ -232,6 +259,9 @@ class ShardedHostForward:
     def flush(self) -> None:
         """The caller's stream waits for every copy-back in flight: synchronise it and the host results are complete."""
         torch.cuda.current_stream(self.device).wait_stream(self.down)
+        mm = getattr(self, "_flush_mm", None)
+        if mm is not None:
+            mm.host_flush()
 
 
 def make_gatherer(group=None, world: int | None = None, device=None) -> Gatherer:

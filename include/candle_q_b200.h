@@ -412,6 +412,11 @@ int cqh_indexed_moe_forward_q8_1(void *handle, const void *act_q8_1, int x_dim1,
 int cqh_qmatmul_forward_host(void *handle, const void *host_x, int x_dtype, const int64_t *dims, int ndims, void *host_out,
                              void *stream);
 int cqh_qmatmul_host_flush(int device, void *stream);
+/* The same for one process per GPU and a matrix sharded by rows: this rank's slice of the product, the peer-memory gather of
+ * the slices (peer_stage / gather_state: what cq_peer_gather_words takes for the shape [rows, n_local]) and the copy-back of
+ * the gathered rows [.., n_local * world] in one call, with the same overlap.  f32 only. */
+int cqh_qmatmul_forward_host_sharded(void *handle, const void *host_x, int x_dtype, const int64_t *dims, int ndims, void *host_out,
+                                     void *const *peer_stage, void *gather_state, int rank, int world, void *stream);
 /* QMatMul::forward: x [.., k] (device, contiguous, x_dtype = CQ_ELEM_*) -> out [.., n], same element type. */
 int cqh_qmatmul_forward(void *handle, const void *x, int x_dtype, const int64_t *dims, int ndims, void *out,
                         void *stream);
