@@ -358,6 +358,7 @@ def measure_prefill(dev, rank, world, peak_tops):
     from candle_b200.synth import random_blocks
     L = capi.lib()
     st = torch.cuda.current_stream().cuda_stream
+    ref_mmq = _load_reference_mmq()
     out = []
     for (k, n) in ((4096, 14336), (14336, 4096)):
         n_l = n // world
@@ -386,6 +387,13 @@ def measure_prefill(dev, rank, world, peak_tops):
                         L.launch_mmq_gguf_q4_k(fixup.data_ptr(), ws[i % 4].data_ptr(), mmq_scratch.data_ptr(), y32.data_ptr(), k, n_l, m,
                                                k // 256, n_l, 1000, 148, 232448, 32, st)
                     row["dropin_mmq_ms"] = _time_launches(dropin, 3 if m >= 2048 else 6)
+                    if ref_mmq is not None and world == 1:      # the reference's tiled int8 mma.sync GEMM itself, same two calls
+                        def reference_pair(i):
+                            ref_mmq.launch_mmq_quantize_q8_1_DS4(x.data_ptr(), None, mmq_scratch.data_ptr(), 0, k, k, 0, 0, kp, m, 1, 1, st)
+                            ref_mmq.launch_mmq_gguf_q4_k(fixup.data_ptr(), ws[i % 4].data_ptr(), mmq_scratch.data_ptr(), y32.data_ptr(), k, n_l, m,
+                                                         k // 256, n_l, 1000, 148, 232448, 32, st)
+                        row["reference_cuda_mmq_ms"] = _time_launches(reference_pair, 6)
+                        row["reference_cuda_mmq_tops"] = ops / row["reference_cuda_mmq_ms"] / 1e9
                     del mmq_scratch, fixup, y32
                 capi.check("prefill bench")
                 t = torch.tensor([row["gemm_ms"], row["forward_ms"], row.get("dropin_mmq_ms", 0.0)], device=dev)
@@ -628,6 +636,24 @@ def run_gpu(args):
     if gather is not None and hasattr(gather, "check"):
         gather.check()
 
+    # ---- the reference's own CUDA kernels on this GPU (oracle/build_ref.py), the same step: quantize + `_plain` GEMV
+    reference_cuda = None
+    ref_lib = _load_reference_mmvq() if world == 1 else None
+    if ref_lib is not None:
+        tags = {"Q4K": "q4_k", "Q6K": "q6_k", "Q8_0": "q8_0"}
+        ref_q8 = {key: torch.empty_like(v) for key, v in q8.items()}
+
+        def step_reference():
+            s_ = torch.cuda.current_stream().cuda_stream
+            for (b, t, k, n) in order:
+                ref_lib.launch_mmvq_gguf_quantize_q8_1_f32(xs[(k, b)].data_ptr(), ref_q8[(k, b)].data_ptr(), k, kp[k], b, s_)
+                getattr(ref_lib, f"launch_mmvq_gguf_{tags[t]}_f32_plain")(mats[(t, k, n)].qtensor.device_ptr(), ref_q8[(k, b)].data_ptr(),
+                                                                          outs[(n, b)].data_ptr(), k, n, kp[k] // 32, n, b, s_)
+        ms_ref = timed(step_reference, max(3, args.steps // 4), 3, True)
+        reference_cuda = {"what": "candle-kernels/src/mmvq_gguf.cu compiled unmodified for sm_100a, the same 60 quantize + GEMV pairs, "
+                                  "CUDA graph replay", "value": total_bytes / ms_ref / 1e6, "unit": UNIT, "ms_per_step": ms_ref}
+        del ref_q8
+
     # free the sweep's buffers before the other measurements
     del mats, xs, outs, q8, h_x, h_y, d_x
     gather = None
@@ -691,6 +717,7 @@ def run_gpu(args):
                       "gemv_only_GBps": total_bytes / ms_gemv_sustained / 1e6},
         "gemv_cases": {"unit": "GB/s per launch (algorithmic bytes, this rank's shard): graph of 5 {256 MB L2 flush, launch} pairs minus the flushes",
                        "by_type_shape_batch": per_case},
+        "reference_cuda": reference_cuda,
         "int8_peak": int8_peak,
         "prefill": prefill,
         "prefill_block_formats": prefill_b32,
@@ -901,6 +928,43 @@ def run_dequant_case(args):
     nbytes = blocks.numel() + 4.0 * n * k
     best = min(times[1:]) if len(times) > 1 else times[0]
     print(json.dumps({"dequant_case": args.dequant_case, "us": times, "bytes": nbytes, "best_GBps": nbytes / best / 1e3}))
+
+
+def _load_reference_mmvq():
+    """The reference's MMVQ kernels built by oracle/build_ref.py, or None (a baseline timed beside, never the product path)."""
+    import ctypes as C
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libcandle_ref_mmvq.so")
+    if not os.path.isfile(path):
+        return None
+    try:
+        lib = C.CDLL(path)
+    except OSError:
+        return None
+    vp, i32 = C.c_void_p, C.c_int
+    lib.launch_mmvq_gguf_quantize_q8_1_f32.argtypes, lib.launch_mmvq_gguf_quantize_q8_1_f32.restype = [vp, vp, i32, i32, i32, vp], None
+    for tag in ("q4_k", "q6_k", "q8_0", "q4_0"):
+        f = getattr(lib, f"launch_mmvq_gguf_{tag}_f32_plain")
+        f.argtypes, f.restype = [vp, vp, vp, i32, i32, i32, i32, i32, vp], None
+    return lib
+
+
+def _load_reference_mmq():
+    import ctypes as C
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libcandle_ref_mmq.so")
+    if not os.path.isfile(path):
+        return None
+    try:
+        lib = C.CDLL(path)
+    except OSError:
+        return None
+    vp, i32, i64 = C.c_void_p, C.c_int, C.c_int64
+    for layout in ("D4", "DS4"):
+        f = getattr(lib, f"launch_mmq_quantize_q8_1_{layout}")
+        f.argtypes, f.restype = [vp, vp, vp, i32, i64, i64, i64, i64, i64, i64, i64, i64, vp], None
+    for tag in ("q4_k", "q6_k", "q8_0", "q4_0"):
+        f = getattr(lib, f"launch_mmq_gguf_{tag}")
+        f.argtypes, f.restype = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i64, i32, vp], None
+    return lib
 
 
 def decode_tok_s(dev, rank, world, batch, prompt_len=512, steps=256, use_graph=True, fuse_rope=None):

@@ -145,10 +145,26 @@ template <> struct ChunkW<CQ_Q4_0> {
     }
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_0> &a) const {
         const int s = idot(a);
-        if constexpr (cq_act_q8_1_like(ACT)) return __fmul_rn(d, __fmaf_rn(cq_small_int_to_float(s), a.d[0], __fmul_rn(-8.0f, a.s[0])));
+        // the reference's tiled kernel keeps signed codes q - 8 in its tensor-core tiles and ignores the stored sum
+        // (candle-kernels/src/mmq_gguf/mmq_gguf.cuh:3278-3283, vec_dot_q8_0_q8_1_mma with the DS4 layout)
+        if constexpr (ACT == CQ_ACT_MMQ_DS4) return __fmul_rn(__fmul_rn(d, a.d[0]), (float)(s - 8 * a.sq[0]));
+        else if constexpr (cq_act_q8_1_like(ACT)) return __fmul_rn(d, __fmaf_rn(cq_small_int_to_float(s), a.d[0], __fmul_rn(-8.0f, a.s[0])));
         else return __fmul_rn(__fmul_rn((float)(s - 8 * a.sq[0]), d), a.d[0]);
     }
 };
+
+// Q4_K / Q5_K over the MMQ scratch: the reference's tile loader stores d * sc and -dmin * m as f16 products
+// (candle-kernels/src/mmq_gguf/mmq_gguf.cuh:2096-2108) and vec_dot_q8_1_q8_1_mma adds, per 32-block,
+// f16(d sc) * d8 * dot  and  f16(-dmin m) * s8  with the stored f16 sum s8.  d * sc is exact in f32, so one rounding to f16.
+__device__ __forceinline__ float cq_mmq_k_pair(float d, float dmin, const int (&sc)[2], const int (&mn)[2], int dot0, int dot1,
+                                               float d8_0, float d8_1, float s8_0, float s8_1) {
+    const float w0 = __half2float(__float2half_rn(__fmul_rn(d, (float)sc[0]))), w1 = __half2float(__float2half_rn(__fmul_rn(d, (float)sc[1])));
+    const float m0 = __half2float(__float2half_rn(__fmul_rn(dmin, (float)mn[0]))), m1 = __half2float(__float2half_rn(__fmul_rn(dmin, (float)mn[1])));
+    float v = __fmul_rn(__fmul_rn(w0, d8_0), (float)dot0);
+    v = __fmaf_rn(-m0, s8_0, v);
+    v = __fmaf_rn(__fmul_rn(w1, d8_1), (float)dot1, v);
+    return __fmaf_rn(-m1, s8_1, v);
+}
 
 // Q4_1, Q5_0, Q5_1: one 32-element block per chunk.  Elements 0..15 are the low nibbles, 16..31 the high nibbles; the
 // 5-bit formats add bit e of the little-endian word qh to element e (candle-core/src/quantized/k_quants.rs:323-351,
@@ -306,7 +322,9 @@ template <> struct ChunkW<CQ_Q4_K_WIDE> {
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q4_K_WIDE> &a) const {
         int d0, d1x16;
         idots(a, d0, d1x16);
-        if constexpr (cq_act_q8_1_like(ACT)) {
+        if constexpr (ACT == CQ_ACT_MMQ_DS4) {
+            return cq_mmq_k_pair(d, dmin, sc, mn, d0, d1x16 >> 4, a.d[0], a.d[1], a.s[0], a.s[1]);
+        } else if constexpr (cq_act_q8_1_like(ACT)) {
             // d1x16 is 16 x an integer, so the shift is exact; both products stay below 2^24 and convert exactly
             const float sd = __fmaf_rn(a.d[1], cq_small_int_to_float((d1x16 >> 4) * sc[1]), __fmul_rn(a.d[0], cq_small_int_to_float(d0 * sc[0])));
             const float sm = __fmaf_rn(a.s[1], cq_small_int_to_float(mn[1]), __fmul_rn(a.s[0], cq_small_int_to_float(mn[0])));
@@ -353,7 +371,9 @@ template <> struct ChunkW<CQ_Q5_K> {
     template <int ACT> __device__ __forceinline__ float dot(const ChunkAct<CQ_Q5_K> &a) const {
         int d0, d1;
         idots(a, d0, d1);
-        if constexpr (cq_act_q8_1_like(ACT)) {      // products below 32 * 31 * 127 * 63 = 7.9e6 < 2^24: the conversion is exact
+        if constexpr (ACT == CQ_ACT_MMQ_DS4) {
+            return cq_mmq_k_pair(d, dmin, sc, mn, d0, d1, a.d[0], a.d[1], a.s[0], a.s[1]);
+        } else if constexpr (cq_act_q8_1_like(ACT)) {      // products below 32 * 31 * 127 * 63 = 7.9e6 < 2^24: the conversion is exact
             const float sd = __fmaf_rn(a.d[1], (float)(d1 * sc[1]), __fmul_rn(a.d[0], (float)(d0 * sc[0])));
             const float sm = __fmaf_rn(a.s[1], cq_small_int_to_float(mn[1]), __fmul_rn(a.s[0], cq_small_int_to_float(mn[0])));
             return __fmaf_rn(d, sd, -__fmul_rn(dmin, sm));

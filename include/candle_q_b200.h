@@ -100,7 +100,10 @@ void moe_gemm_gguf_prefill(const void *input, const uint8_t *weights, const int3
  * of 128), ne1 tokens.  The bytes are those of the reference kernel.  DS4 serves Q4_0 / Q4_K, D4 serves Q8_0 / Q6_K.
  * Matmul: x = weights [nrows_x, ncols_x] (stride_row_x blocks per row), y = that scratch for ncols_y tokens,
  * dst f32 [ncols_y, stride_col_dst].  tmp_fixup, cc, nsm, smpbo, warp_size are accepted for signature compatibility
- * and not used.  These entries run GEMV passes of eight tokens; the tensor-core prompt path is cq_prefill_gemm. */
+ * and not used.  These entries run GEMV passes of eight tokens; the tensor-core prompt path is cq_prefill_gemm.  Their
+ * arithmetic is that of the reference's tensor-core variants (vec_dot_*_mma, what it runs from Turing on): Q4_0 on signed
+ * codes q - 8 without the stored activation sum, Q4_K / Q5_K with d * sc and dmin * m rounded to f16, Q2_K likewise; checked
+ * against the reference kernels compiled for sm_100a (tests/test_gpu_reference_kernels.py). */
 #define CQ_DECL_MMQ_QUANT(name)                                                                                       \
     void name(const void *x, const int32_t *ids, void *vy, int type_x, int64_t ne00, int64_t s01, int64_t s02,        \
               int64_t s03, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3, void *stream)

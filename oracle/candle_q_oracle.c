@@ -1727,8 +1727,10 @@ void cqo_cuda_quantize_mmq_q8_1(int layout, const float *x, void *vy, int64_t k,
 }
 
 /* Matmul over the MMQ scratch: dst[t * n + r] = sum over 32-blocks of the reference's per-block terms,
- * candle-kernels/src/mmq_gguf/mmq_vecdotq.cuh:112-131 (Q4_0: d4 * (sumi * d8 - 8 * s8)), :240-253 (Q8_0: d8_0 * d8_1 *
- * sumi), :527-551 (Q4_K: dm.x * sum d8 * sc * sumi - dm.y * sum s8 * m), :644-674 (Q6_K: d6 * sum d8 * (sc * sumi)).
+ * as the TENSOR-CORE variants of the reference's tiled kernel compute them - the ones it runs on any GPU from Turing on
+ * (mmq_gguf.cuh:3275-3377 picks vec_dot_*_mma): Q4_0 d4 * d8 * sum (q - 8) q8 on signed tiles; Q8_0 d8_0 * d8_1 * sumi; Q4_K /
+ * Q5_K f16(d * sc) * d8 * sumi - f16(dmin * m) * s8 with the stored f16 sum s8; Q6_K d6 * d8 * sum sc * dot.  Checked
+ * against the reference kernels themselves, compiled for sm_100a (tests/test_gpu_reference_kernels.py).
  * The reference adds the per-block f32 terms in the order of its tile loops (or inside mma accumulators), which no
  * caller can rely on; the integer parts are exact and the block terms are summed in double here. */
 void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k, int64_t n, int64_t tokens) {
@@ -1746,8 +1748,12 @@ void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k
                     const blk_q4_0 *b = (const blk_q4_0 *)row + b32;
                     int sumi = 0;
                     for (int i = 0; i < 16; ++i) sumi += (b->qs[i] & 0xF) * q8[i] + (b->qs[i] >> 4) * q8[i + 16];
-                    const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
-                    acc += (double)f16_to_f32(b->d) * ((double)sumi * d8 - 8.0 * s8);
+                    /* tensor-core tiles hold the signed codes q - 8 (load_tiles_q4_0 under TURING_MMA_AVAILABLE) and
+                     * vec_dot_q8_0_q8_1_mma<DS4> reads only the scale half of ds4: d4 * d8 * sum (q - 8) q8 */
+                    int sumq = 0;
+                    for (int i = 0; i < 32; ++i) sumq += q8[i];
+                    const float d8 = f16_to_f32(g->ds4[2 * j]);
+                    acc += (double)f16_to_f32(b->d) * (double)d8 * (double)(sumi - 8 * sumq);
                 } else if (type == CQO_Q4_1 || type == CQO_Q5_1) {
                     /* DS4, tiles of unsigned codes with (d, m): d * d8 * sumi + m * s8 per 32-block
                      * (mmq_gguf.cuh vec_dot_q8_1_q8_1_mma, f32 products) */
@@ -1783,7 +1789,10 @@ void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k
                     int sumi = 0;
                     for (int i = 0; i < 32; ++i) sumi += ((sub & 1) ? (q4[i] >> 4) : (q4[i] & 0xF)) * q8[i];
                     const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
-                    acc += (double)f16_to_f32(b->d) * d8 * (double)(sc * sumi) - (double)f16_to_f32(b->dmin) * s8 * m;
+                    /* the tile loader keeps d * sc and -dmin * m as f16 products (load_tiles_q4_K, mmq_gguf.cuh:2096-2108) */
+                    const float dsc = f16_to_f32(f32_to_f16(f16_to_f32(b->d) * (float)sc));
+                    const float dmm = f16_to_f32(f32_to_f16(f16_to_f32(b->dmin) * (float)m));
+                    acc += (double)dsc * d8 * (double)sumi - (double)dmm * s8;
                 } else if (type == CQO_Q2K) {
                     /* D2S6, mmq_gguf.cuh:1518-1575 + mmq_vecdotq.cuh:388-437: per 16-run the f16 products
                      * d * (sc & 15) and dmin * (sc >> 4); the first six runs of a 128-group subtract the stored f16 sum
@@ -1816,7 +1825,9 @@ void cqo_cuda_mmq(int type, const void *w, const void *vy, float *dst, int64_t k
                     int sumi = 0;
                     for (int i = 0; i < 32; ++i) sumi += q5k_value(b, 32 * sub + i) * q8[i];
                     const float d8 = f16_to_f32(g->ds4[2 * j]), s8 = f16_to_f32(g->ds4[2 * j + 1]);
-                    acc += (double)f16_to_f32(b->d) * d8 * (double)(sc * sumi) - (double)f16_to_f32(b->dmin) * s8 * m;
+                    const float dsc = f16_to_f32(f32_to_f16(f16_to_f32(b->d) * (float)sc));       /* f16 products, as for Q4_K */
+                    const float dmm = f16_to_f32(f32_to_f16(f16_to_f32(b->dmin) * (float)m));
+                    acc += (double)dsc * d8 * (double)sumi - (double)dmm * s8;
                 } else if (type == CQO_Q6K) {
                     const blk_q6k *b = (const blk_q6k *)row + b32 / 8;
                     const int sub = (int)(b32 % 8), half = sub / 4, pos = sub % 4;     /* 128-half, 32-apart position */
