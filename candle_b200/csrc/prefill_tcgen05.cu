@@ -599,7 +599,10 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
                 }
             }
             const int c0 = cx.row0 + rh * kMyRows;
-            if (store && out_kind != CQ_F32) {
+            // The branches below are chosen by warp-uniform values only (`store` differs between the lanes of a ragged token
+            // tile and must not decide whether a lane reaches the shuffles of the f32 branch).
+            if (out_kind != CQ_F32) {
+              if (store) {
                 uint8_t *o16 = (uint8_t *)out_v + 2 * ((size_t)orow * stride_out + c0);
                 if (c0 + kMyRows <= nrows && (((uintptr_t)o16) & 15) == 0) {       // 32 values = four 16-byte stores
 #pragma unroll
@@ -609,6 +612,7 @@ prefill_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ act, v
                     for (int i = 0; i < kMyRows; ++i)
                         if (c0 + i < nrows) cq_store_out(out_v, out_kind, orow * stride_out + c0 + i, acc[i]);
                 }
+              }
             } else if (!gi.tiles && c0 + kMyRows <= nrows && (stride_out & 3) == 0 && (c0 & 3) == 0 && (((uintptr_t)out_v) & 15) == 0) {
                 // f32, whole 32-row slice (warp-uniform test): three exchange steps turn "a lane holds 32 rows of its token" into
                 // "a lane holds 4 rows of 8 tokens", so that eight lanes write one token's 128 contiguous bytes per store
