@@ -346,7 +346,7 @@ def _time_launches(fn, iters):
 
 
 def measure_prefill(dev, rank, world, peak_tops):
-    """BASELINE config 3: Q4_K 4096->14336 and 14336->4096, M = 128, 512, 2048, 8192 tokens, f32 and bf16 activations;
+    """Benchmark configuration 3 (prompt GEMM): Q4_K 4096->14336 and 14336->4096, M = 128, 512, 2048, 8192 tokens, f32 and bf16 activations;
     the output dimension is sharded over `world` ranks.  Per case the useful rate 2*M*N*K / t of (a) the tcgen05 GEMM
     alone, (b) QMatMul.forward (activation tiles + GEMM), (c) for f32: the reference's two-call protocol served by this
     library (launch_mmq_quantize_q8_1_DS4 + launch_mmq_gguf_q4_k).  Weights rotate through four copies so that

@@ -28,7 +28,7 @@ def rel_err(a, ref):
     return float(np.abs(a - ref).max() / max(np.abs(ref).max(), 1e-30))
 
 
-# ---- the benchmark's own inputs (BASELINE configs), regenerated from seeds ------------------------------------------------
+# ---- the benchmark's own inputs (its stated configurations), regenerated from seeds ------------------------------------------------
 # Weights: f32 N(0, 0.02) from seed 0, quantized by the reference's quantizer (restated in the oracle); activations: f32
 # N(0, 1) from seed 1.  numpy's PCG64 + ziggurat float32 stream; rows are drawn in order, so generating in row chunks
 # gives the same values as one call.  tests/golden/baseline_sha256.json pins the resulting bytes.

@@ -62,7 +62,7 @@ def _sample_rows(n, rows_per_batch, grid):
 
 
 def test_config1_q4_0_single_matmul(lib, oracle, cuda_dev):
-    """BASELINE config 1 exactly: Q4_0 weight 4096 x 4096 (seed 0), activation [1, 4096] (seed 1), f32 output [1, 4096]
+    """Benchmark configuration 1 exactly: Q4_0 weight 4096 x 4096 (seed 0), activation [1, 4096] (seed 1), f32 output [1, 4096]
     against the reference's CPU vec_dot; plus the CUDA path's Q8_1 gate on the same inputs."""
     k = n = 4096
     wq = baseline_weights(oracle, oracle.Q4_0, k, n)
@@ -96,7 +96,7 @@ def test_config1_q4_0_single_matmul(lib, oracle, cuda_dev):
 @pytest.mark.parametrize("k,n", SHAPES)
 @pytest.mark.parametrize("tname", SWEEP_TYPES)
 def test_config2_gemv_sweep_full_size(lib, oracle, cuda_dev, tname, k, n):
-    """BASELINE config 2: every (format, shape) of the sweep at its full N, batches 1, 2, 4 and 8; all rows compared."""
+    """Benchmark configuration 2: every (format, shape) of the sweep at its full N, batches 1, 2, 4 and 8; all rows compared."""
     wt = TYPES[tname]
     wq = baseline_weights(oracle, wt, k, n)
     assert sha256_hex(wq) == SHA["weights"][f"{tname}:{k}:{n}"]
@@ -173,7 +173,7 @@ def test_timed_plans_are_the_checked_plans(lib, cuda_dev):
 
 @pytest.mark.parametrize("k,n", [(4096, 14336), (14336, 4096)])
 def test_config3_prefill_full_size(lib, oracle, cuda_dev, k, n):
-    """BASELINE config 3: Q4_K weights of 4096 -> 14336 and 14336 -> 4096 (seed 0), activations [M, K] (seed 1) for
+    """Benchmark configuration 3: Q4_K weights of 4096 -> 14336 and 14336 -> 4096 (seed 0), activations [M, K] (seed 1) for
     M = 128, 512, 2048 and 8192 in f32 and bf16, through QMatMul.forward.  The GPU computes the whole output; the oracle
     (reference CPU matmul: the prompt kernel uses its Q8_K arithmetic) checks every weight row for sampled tokens:
     first / last token of several 128-token tiles, the last token, and seeded random ones."""
