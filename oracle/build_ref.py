@@ -28,11 +28,27 @@ MOE = os.path.join(OUT, "libcandle_ref_moe.so")
 MMQ_FORMATS = ("q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k")
 
 
+_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-Xcompiler", "-fPIC"]
+
+
 def _nvcc(out: str, sources: list[str], verbose: bool) -> None:
-    cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-o", out] + sources
-    if verbose:
-        print(" ".join(cmd), flush=True)
-    subprocess.run(cmd, check=True)
+    """One shared library from `sources`; several sources are compiled side by side (the per-format MMQ instances take
+    most of a minute each), then linked."""
+    def run(cmd):
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+
+    if len(sources) == 1:
+        run(["nvcc"] + _FLAGS + ["-shared", "-o", out] + sources)
+        return
+    import concurrent.futures
+    import tempfile
+    with tempfile.TemporaryDirectory(dir=OUT) as tmp:
+        objs = [os.path.join(tmp, os.path.splitext(os.path.basename(s))[0] + ".o") for s in sources]
+        with concurrent.futures.ThreadPoolExecutor(max_workers=min(len(sources), os.cpu_count() or 1)) as pool:
+            list(pool.map(lambda so: run(["nvcc"] + _FLAGS + ["-c", "-o", so[1], so[0]]), zip(sources, objs)))
+        run(["nvcc"] + _FLAGS + ["-shared", "-o", out] + objs)
 
 
 def build(reference_root: str, verbose: bool = False, force: bool = False) -> list[str]:
