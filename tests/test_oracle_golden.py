@@ -204,3 +204,27 @@ def test_degenerate_blocks_do_not_trap(oracle):
     for dt in (oracle.Q4_0, oracle.Q4_1, oracle.Q5_0, oracle.Q5_1, oracle.Q8_0, oracle.Q2K, oracle.Q3K, oracle.Q4K, oracle.Q5K, oracle.Q6K, oracle.Q8K):
         d = oracle.dequantize(dt, oracle.quantize(dt, z), 512)[0]
         assert np.all(d == 0)
+
+
+def test_prompt_pair_arithmetic_follows_the_tensor_core_variants(oracle):
+    """What running the reference's own tiled kernel on a B200 showed (tests/test_gpu_reference_kernels.py): from Turing on
+    it computes Q4_0 on signed codes q - 8 and ignores the stored activation sum - so over the DS4 scratch it agrees with
+    the CPU `vec_dot` on Q8_0 blocks to rounding, and NOT with the GEMV formula d4 * (sumi * d8 - 8 * s8), which carries the
+    quantization error of the activation sum (~1e-2).  Q4_K / Q5_K round d * sc and dmin * m to f16: within 2e-3 of the
+    unrounded GEMV arithmetic, not equal to it."""
+    rng = np.random.default_rng(21)
+    k, n, m = 2048, 48, 6
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    rel = lambda a, b: float(np.abs(a - b).max() / np.abs(b).max())
+    wq = oracle.quantize(oracle.Q4_0, w)
+    pair = oracle.cuda_mmq(oracle.Q4_0, wq, oracle.cuda_quantize_mmq_q8_1(x, "DS4"), k, n)
+    assert rel(pair, oracle.matmul(oracle.Q4_0, x, wq, n)) <= 1e-5
+    gemv = oracle.cuda_mmvq(oracle.Q4_0, wq, oracle.cuda_quantize_q8_1(x, 2048), k, n)
+    assert 1e-3 < rel(pair, gemv) < 5e-2
+    for dt in (oracle.Q4K, oracle.Q5K):
+        wq = oracle.quantize(dt, w)
+        pair = oracle.cuda_mmq(dt, wq, oracle.cuda_quantize_mmq_q8_1(x, "DS4"), k, n)
+        gemv = oracle.cuda_mmvq(dt, wq, oracle.cuda_quantize_q8_1(x, 2048), k, n)
+        # the f16 products AND the different sum term (stored f16 sum of the floats here, d8 * sum(q8) in the GEMV) separate them
+        assert 1e-5 < rel(pair, gemv) < 2e-2
