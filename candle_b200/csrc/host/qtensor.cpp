@@ -322,6 +322,45 @@ extern "C" int cqh_qtensor_load(int ggml_dtype, const void *host_bytes, size_t n
     });
 }
 
+// Weight-side quantization on the host (QTensor::quantize / quantize_onto, mod.rs:543-562, 645-671; the CUDA storage
+// quantizes on the CPU and uploads, cuda.rs:704-725).  cqh_quantize_f32 touches no device.
+static size_t quantized_bytes(GgmlDType dt, const int64_t *dims, int ndims, int64_t *elems_out) {
+    if (ndims < 1) throw Error("quantize: a tensor of rank 0 has no last dimension");
+    const size_t bs = block_size(dt);
+    int64_t elems = 1;
+    for (int i = 0; i < ndims; ++i) elems *= dims[i];
+    if (dims[ndims - 1] % (int64_t)bs != 0) {
+        std::string shape = "[";
+        for (int i = 0; i < ndims; ++i) shape += (i ? ", " : "") + std::to_string(dims[i]);
+        throw Error("tensor size (" + shape + "]) is not divisible by block size " + std::to_string(bs));
+    }
+    *elems_out = elems;
+    return (size_t)elems / bs * type_size(dt);
+}
+
+extern "C" int cqh_quantize_f32(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, void *host_out,
+                                size_t out_bytes) {
+    return guarded([&] {
+        const GgmlDType dt = ggml_dtype_from_u32((uint32_t)ggml_dtype);
+        int64_t elems = 0;
+        const size_t need = quantized_bytes(dt, dims, ndims, &elems);
+        if (need != out_bytes) throw Error("quantize: the output holds " + std::to_string(out_bytes) + " bytes, the blocks take " + std::to_string(need));
+        quantize_weights(dt, host_x, elems, (uint8_t *)host_out);
+    });
+}
+
+extern "C" int cqh_qtensor_quantize_onto(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, int device,
+                                         void **out_handle) {
+    return guarded([&] {
+        const GgmlDType dt = ggml_dtype_from_u32((uint32_t)ggml_dtype);
+        int64_t elems = 0;
+        std::vector<uint8_t> blocks(quantized_bytes(dt, dims, ndims, &elems));
+        quantize_weights(dt, host_x, elems, blocks.data());
+        auto st = QCudaStorage::load_quantized(device, dt, blocks.data(), blocks.size());
+        *out_handle = new std::shared_ptr<QTensor>(new QTensor(std::move(st), std::vector<int64_t>(dims, dims + ndims)));
+    });
+}
+
 extern "C" int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int64_t *dims, int ndims,
                                 int device, void **out_handle) {
     return guarded([&] {

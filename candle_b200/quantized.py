@@ -71,6 +71,19 @@ def set_activation_mode(cpu_exact: bool) -> None:
     capi.lib().cqh_set_act_mode(1 if cpu_exact else 0)
 
 
+def quantize_blocks(src, dtype: GgmlDType) -> bytes:
+    """f32 values -> GGUF blocks in host memory, with the reference's CPU ``from_float`` arithmetic (k_quants.rs); Q4_0,
+    Q8_0, Q4K, Q6K.  Uses no device.  ``src``: a numpy array or CPU tensor whose last dimension is a multiple of the block
+    size."""
+    dtype = GgmlDType(dtype)
+    x = np.ascontiguousarray(src.detach().cpu().numpy() if isinstance(src, torch.Tensor) else src, dtype=np.float32)
+    dims, nd = _dims(x.shape)
+    out = np.empty(x.size // dtype.block_size() * dtype.type_size() if x.ndim and x.shape[-1] % dtype.block_size() == 0 else 0,
+                   dtype=np.uint8)
+    capi.hcheck(capi.lib().cqh_quantize_f32(int(dtype), x.ctypes.data, dims, nd, out.ctypes.data, out.size), "quantize_blocks")
+    return out.tobytes()
+
+
 def _dims(shape: Sequence[int]):
     arr = (C.c_int64 * len(shape))(*[int(d) for d in shape])
     return arr, len(shape)
@@ -109,6 +122,31 @@ class QTensor:
         capi.hcheck(capi.lib().cqh_qtensor_load(int(dtype), buf.ctypes.data, buf.size, dims, nd,
                                                  device.index or 0, C.byref(h)), "QTensor.from_data")
         return cls(h.value, dtype, tuple(shape), device)
+
+    @classmethod
+    def quantize_onto(cls, src: torch.Tensor, dtype: GgmlDType, device="cuda:0") -> "QTensor":
+        """``QTensor::quantize_onto`` (mod.rs:645-671): quantizes a tensor held on the CPU with the reference's CPU
+        ``from_float`` arithmetic and puts the blocks on ``device``.  Built for Q4_0, Q8_0, Q4K and Q6K."""
+        dtype = GgmlDType(dtype)
+        if src.device.type != "cpu":
+            raise CandleQError("`quantize_onto` expects a `src` to be on the cpu, got cuda.")
+        device = torch.device(device)
+        x = src.detach().to(torch.float32).contiguous()
+        dims, nd = _dims(tuple(x.shape))
+        h = C.c_void_p()
+        capi.hcheck(capi.lib().cqh_qtensor_quantize_onto(int(dtype), x.data_ptr(), dims, nd, device.index or 0, C.byref(h)),
+                    "QTensor.quantize_onto")
+        return cls(h.value, dtype, tuple(x.shape), device)
+
+    @classmethod
+    def quantize(cls, src: torch.Tensor, dtype: GgmlDType) -> "QTensor":
+        """``QTensor::quantize`` (mod.rs:543-562): the quantized tensor lives on ``src``'s device, which must be a CUDA
+        device here.  As in the reference's CUDA storage (cuda.rs:704-725) the values are brought to the host, quantized
+        there and the blocks uploaded; this is a load-time step."""
+        if not src.is_cuda:
+            raise CandleQError("QTensor.quantize: this library holds quantized tensors on CUDA devices only; "
+                               "use quantize_onto(src, dtype, device) for a tensor on the cpu")
+        return cls.quantize_onto(src.detach().to("cpu", torch.float32), dtype, src.device)
 
     @classmethod
     def from_device_blocks(cls, blocks: torch.Tensor, dtype: GgmlDType, shape: Sequence[int]) -> "QTensor":

@@ -1,0 +1,119 @@
+"""Weight-side quantization (`QTensor::quantize` / `quantize_onto`, candle-core/src/quantized/mod.rs:543-562, 645-671).
+
+The library's host quantizer (Q4_0, Q8_0, Q4K, Q6K) must write the bytes candle's CPU `from_float` writes: it is compared
+with the oracle's restatement of those routines byte for byte, and with the known answers of candle's own tests.
+"""
+import numpy as np
+import pytest
+import torch
+
+from candle_b200 import capi
+from candle_b200.quantized import GgmlDType, QTensor, quantize_blocks
+
+FORMATS = ["Q4_0", "Q8_0", "Q4K", "Q6K"]
+
+
+def _inputs(k):
+    rng = np.random.default_rng(20240611)
+    n = 6 * k
+    ramp = np.arange(n, dtype=np.float32)
+    spikes = rng.standard_normal(n).astype(np.float32)
+    spikes[::37] *= 50.0
+    yield "normal", rng.standard_normal(n).astype(np.float32)
+    yield "ramp", ramp
+    yield "centred ramp", ((ramp - np.float32(n) / 2) * np.float32(0.5) / (np.float32(n) / 2)).astype(np.float32)
+    yield "cosine", (np.float32(0.1) + np.float32(2.0) * np.cos(ramp)).astype(np.float32)
+    yield "zeros", np.zeros(n, dtype=np.float32)
+    yield "constant", np.full(n, 0.75, dtype=np.float32)
+    yield "negative constant", np.full(n, -3.0, dtype=np.float32)
+    yield "one value per block", np.where(np.arange(n) % 32 == 5, np.float32(-1.25), np.float32(0)).astype(np.float32)
+    yield "outliers", spikes
+    yield "tiny", (rng.standard_normal(n) * 1e-30).astype(np.float32)
+    yield "large", (rng.standard_normal(n) * 1e4).astype(np.float32)
+    yield "uniform positive", rng.random(n, dtype=np.float32)
+    yield "signed zeros", np.where(np.arange(n) % 2 == 0, np.float32(0.0), np.float32(-0.0)).astype(np.float32)
+
+
+@pytest.mark.parametrize("name", FORMATS)
+def test_blocks_equal_the_reference_cpu_quantizer(lib, oracle, name):
+    dt, odt = GgmlDType[name], getattr(oracle, name)
+    for label, x in _inputs(dt.block_size()):
+        mine = np.frombuffer(quantize_blocks(x, dt), dtype=np.uint8)
+        ref = oracle.quantize(odt, x).reshape(-1)
+        assert mine.size == ref.size == x.size // dt.block_size() * dt.type_size()
+        assert np.array_equal(mine, ref), (name, label, int(np.flatnonzero(mine != ref)[0]))
+
+
+@pytest.mark.parametrize("name", FORMATS)
+def test_rows_are_quantized_independently(lib, oracle, name):
+    """A [rows, k] tensor gives the rows' blocks one after another (mod.rs:543-562 quantizes the flattened storage)."""
+    dt = GgmlDType[name]
+    k = 2 * dt.block_size()
+    x = np.random.default_rng(7).standard_normal((5, 3, k)).astype(np.float32)
+    whole = quantize_blocks(x, dt)
+    rows = b"".join(quantize_blocks(r, dt) for r in x.reshape(-1, k))
+    assert whole == rows
+    assert whole == quantize_blocks(torch.from_numpy(x), dt)
+
+
+def test_q4_0_known_answer(lib, oracle):
+    """candle-core/tests/quantized_tests.rs:345-377: 0..127 through Q4_0 and back (first and last block of the vector)."""
+    src = np.arange(128, dtype=np.float32)
+    blocks = np.frombuffer(quantize_blocks(src, GgmlDType.Q4_0), dtype=np.uint8)
+    d = oracle.dequantize(oracle.Q4_0, blocks.reshape(1, -1), 128)[0]
+    assert d[:10].tolist() == [-0.0, -0.0, 3.875, 3.875, 3.875, 3.875, 7.75, 7.75, 7.75, 7.75]
+    assert d[30:36].tolist() == [31.0, 31.0, 31.5, 31.5, 31.5, 31.5]
+    assert d[-8:].tolist() == [127.0] * 8
+
+
+@pytest.mark.parametrize("name,probe,tol", [("Q4K", [-0.5, -0.373, -0.25, 0.0, 0.288, 0.498], 0.017),      # quantized_tests.rs:846-891
+                                            ("Q6K", [-0.497, -0.372, -0.25, -0.0, 0.284, 0.5], 0.008)])    # quantized_tests.rs:940-985
+def test_k_quant_known_answers(lib, oracle, name, probe, tol):
+    v = np.arange(1024, dtype=np.float32)
+    src = ((v - np.float32(512.0)) * np.float32(0.5) / np.float32(512.0)).astype(np.float32)
+    blocks = np.frombuffer(quantize_blocks(src, GgmlDType[name]), dtype=np.uint8)
+    d = oracle.dequantize(getattr(oracle, name), blocks.reshape(1, -1), 1024)[0]
+    assert np.abs(d - src).max() < tol
+    r = np.round(np.float32(1000.0) * d) / np.float32(1000.0)
+    assert [float(r[i]) for i in (0, 128, 256, 512, 800, 1023)] == [float(np.float32(p)) for p in probe]
+
+
+@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q8_0", 0.002), ("Q4K", 0.002), ("Q6K", 0.002)])
+def test_quantization_rmse(lib, oracle, name, limit):
+    """ggml_quantization_error_test, candle-core/tests/quantized_tests.rs:531-552 (limits :14-17)."""
+    src = (np.float32(0.1) + np.float32(2.0) * np.cos(np.arange(4096, dtype=np.float32))).astype(np.float32)
+    blocks = np.frombuffer(quantize_blocks(src, GgmlDType[name]), dtype=np.uint8)
+    d = oracle.dequantize(getattr(oracle, name), blocks.reshape(1, -1), 4096)[0]
+    assert float(np.sqrt(((src - d) ** 2).sum()) / 4096) <= limit
+
+
+def test_errors(lib):
+    with pytest.raises(capi.CandleQError, match=r"tensor size \(\[4, 100\]\) is not divisible by block size 32"):
+        quantize_blocks(np.zeros((4, 100), dtype=np.float32), GgmlDType.Q8_0)
+    with pytest.raises(capi.CandleQError, match=r"tensor size \(\[2, 128\]\) is not divisible by block size 256"):
+        quantize_blocks(np.zeros((2, 128), dtype=np.float32), GgmlDType.Q4K)
+    with pytest.raises(capi.CandleQError, match="weight-side quantization to Q5K is not built"):
+        quantize_blocks(np.zeros((2, 256), dtype=np.float32), GgmlDType.Q5K)
+    with pytest.raises(capi.CandleQError, match="expects a `src` to be on the cpu"):
+        QTensor.quantize_onto(torch.zeros(2, 256, device="meta"), GgmlDType.Q4K)
+    with pytest.raises(capi.CandleQError, match="CUDA devices only"):
+        QTensor.quantize(torch.zeros(2, 256), GgmlDType.Q4K)
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_quantize_onto_fails_loudly_without_a_gpu(lib):
+    """The blocks are made on the host, but the tensor lives on a CUDA device: without one the call is an error."""
+    with pytest.raises(capi.CandleQError):
+        QTensor.quantize_onto(torch.zeros(2, 256), GgmlDType.Q4K)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", FORMATS)
+def test_quantize_onto_uploads_the_blocks(lib, name):
+    dt = GgmlDType[name]
+    x = torch.from_numpy(np.random.default_rng(11).standard_normal((24, 512)).astype(np.float32))
+    host = quantize_blocks(x, dt)
+    t = QTensor.quantize_onto(x, dt, "cuda:0")
+    assert t.shape == (24, 512) and t.dtype is dt and t.data() == host
+    t2 = QTensor.quantize(x.to("cuda:0"), dt)
+    assert t2.device.type == "cuda" and t2.data() == host
