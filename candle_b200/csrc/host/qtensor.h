@@ -30,7 +30,7 @@ size_t block_size(GgmlDType t);                 // mod.rs:409-421
 const char *dtype_name(GgmlDType t);
 bool kernels_support(GgmlDType t);              // the four formats this library has kernels for
 // f32 values (a whole number of blocks) -> GGUF blocks on the host, with candle's CPU `from_float` arithmetic
-// (k_quants.rs); Q4_0, Q8_0, Q4K, Q6K.  Throws Error for another format.
+// (k_quants.rs); the ten GGUF block formats Q4_0 ... Q6K.  Throws Error for another format.
 void quantize_weights(GgmlDType dtype, const float *x, int64_t elems, uint8_t *out);
 
 enum class DType : int { F32 = 0, F16 = 1, BF16 = 2 };

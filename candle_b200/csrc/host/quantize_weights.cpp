@@ -2,10 +2,10 @@
 //
 // candle quantizes weights on the CPU whatever the device (QCudaStorage::quantize copies the tensor to the host, runs the
 // CPU `from_float` and uploads the blocks: candle-core/src/quantized/cuda.rs:704-725; QTensor::quantize / quantize_onto,
-// candle-core/src/quantized/mod.rs:543-562, 645-671).  This file is that host routine for the four formats of the hot
-// path - Q4_0 (k_quants.rs:241-277), Q8_0 (:658-687), Q4_K (:1542-1600 with make_qkx1_quants, utils.rs:227-284) and Q6_K
-// (:2094-2164 with make_qx_quants, utils.rs:62-224) - with the same f32 operations in the same order, so the bytes are
-// the reference's.  It is not on the matmul path; nothing here runs per token.
+// candle-core/src/quantized/mod.rs:543-562, 645-671).  This file is that host routine for the ten GGUF block formats -
+// first the four of the hot path: Q4_0 (k_quants.rs:241-277), Q8_0 (:658-687), Q4_K (:1542-1600 with make_qkx1_quants,
+// utils.rs:227-284) and Q6_K (:2094-2164 with make_qx_quants, utils.rs:62-224), then Q4_1, Q5_0, Q5_1, Q2K, Q3K, Q5K -
+// with the same f32 operations in the same order, so the bytes are the reference's.  It is not on the matmul path; nothing here runs per token.
 #include <cuda_fp16.h>
 
 #include <cmath>
@@ -267,6 +267,230 @@ void quantize_q6_k(const float *x, uint8_t *out, int64_t elems) {
     }
 }
 
+inline uint8_t to_u8(float v) { return (uint8_t)clamp(to_i32(v), 0, 255); }       // Rust `as u8`
+inline int8_t to_i8(float v) { return (int8_t)clamp(to_i32(v), -128, 127); }      // Rust `as i8`
+inline void put32(uint8_t *p, uint32_t v) { std::memcpy(p, &v, 4); }
+
+// ---- Q4_1 (k_quants.rs:353-389) and Q5_1 (:562-601): f16 d, f16 min, [4 bytes of fifth bits], 16 bytes of nibbles ----
+template <int BITS> void quantize_q_1(const float *x, uint8_t *out, int64_t elems) {
+    constexpr int kLevels = (1 << BITS) - 1, kBytes = BITS == 4 ? 20 : 24;
+    for (int64_t i = 0; i < elems / 32; ++i) {
+        const float *xs = x + i * 32;
+        uint8_t *b = out + i * kBytes, *qs = b + kBytes - 16;
+        float mn = INFINITY, mx = -INFINITY;
+        for (int j = 0; j < 32; ++j) {         // f32::min / max: a NaN is passed over; of two zeros the first seen stays
+            if (xs[j] < mn) mn = xs[j];
+            if (xs[j] > mx) mx = xs[j];
+        }
+        const float d = (mx - mn) / (float)kLevels;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        put16(b, f16_bits(d));
+        put16(b + 2, f16_bits(mn));
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            uint8_t a = to_u8((xs[j] - mn) * id + 0.5f), c = to_u8((xs[16 + j] - mn) * id + 0.5f);
+            if (BITS == 4) { a = a > 15 ? 15 : a; c = c > 15 ? 15 : c; }
+            qs[j] = (uint8_t)((a & 0x0F) | ((c & 0x0F) << 4));
+            qh |= (uint32_t)((a & 0x10) >> 4) << j;
+            qh |= (uint32_t)((c & 0x10) >> 4) << (j + 16);
+        }
+        if (BITS == 5) put32(b + 4, qh);
+    }
+}
+
+// ---- Q5_0 (k_quants.rs:457-493): f16 d, 4 bytes of fifth bits, 16 bytes of nibbles ----
+void quantize_q5_0(const float *x, uint8_t *out, int64_t elems) {
+    for (int64_t i = 0; i < elems / 32; ++i) {
+        const float *xs = x + i * 32;
+        uint8_t *b = out + i * 22;
+        float amax = 0.f, max = 0.f;
+        for (int j = 0; j < 32; ++j)
+            if (amax < std::fabs(xs[j])) { amax = std::fabs(xs[j]); max = xs[j]; }
+        const float d = max / -16.0f;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        put16(b, f16_bits(d));
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            int8_t a = to_i8(xs[j] * id + 16.5f), c = to_i8(xs[j + 16] * id + 16.5f);
+            a = a > 31 ? 31 : a;
+            c = c > 31 ? 31 : c;
+            const uint8_t u0 = (uint8_t)a, u1 = (uint8_t)c;
+            b[6 + j] = (uint8_t)((u0 & 0x0F) | ((u1 & 0x0F) << 4));
+            qh |= (uint32_t)((u0 & 0x10) >> 4) << j;
+            qh |= (uint32_t)((u1 & 0x10) >> 4) << (j + 16);
+        }
+        put32(b + 2, qh);
+    }
+}
+
+// ---- Q2K (k_quants.rs:891-953): 16 bytes of 4-bit scale | min, 64 bytes of 2-bit codes, f16 d, f16 dmin ----
+void quantize_q2_k(const float *x, uint8_t *out, int64_t elems) {
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256;
+        uint8_t *b = out + ib * 84, *sc = b, *qs = b + 16;
+        float mins[16], scales[16];
+        for (int j = 0; j < 16; ++j) make_qkx1(3, 5, xb + 16 * j, 16, scales[j], mins[j]);
+        float max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 16; ++j) { max_scale = std::fmax(scales[j], max_scale); max_min = std::fmax(mins[j], max_min); }
+        uint16_t d16 = f16_bits(0.f), m16 = f16_bits(0.f);
+        std::memset(sc, 0, 16);
+        if (max_scale > 0.f) {
+            const float iscale = 15.0f / max_scale;
+            for (int j = 0; j < 16; ++j) sc[j] = (uint8_t)clamp(nearest_int(iscale * scales[j]), 0, 255);
+            d16 = f16_bits(max_scale / 15.0f);
+        }
+        if (max_min > 0.f) {
+            const float iscale = 15.0f / max_min;
+            for (int j = 0; j < 16; ++j) sc[j] |= (uint8_t)((uint8_t)clamp(nearest_int(iscale * mins[j]), 0, 255) << 4);
+            m16 = f16_bits(max_min / 15.0f);
+        }
+        put16(b + 80, d16);
+        put16(b + 82, m16);
+        uint8_t L[256] = {};
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_value(d16) * (float)(sc[j] & 0xF);
+            if (d == 0.f) continue;
+            const float dm = f16_value(m16) * (float)(sc[j] >> 4);
+            for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (uint8_t)clamp(nearest_int((xb[16 * j + ii] + dm) / d), 0, 3);
+        }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; ++l)
+                qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+// make_q3_quants(x, nmax, do_rmse = true) -> scale, utils.rs:287-352
+float make_q3(const float *x, int n, int nmax) {
+    int8_t l[32];
+    float max = 0.f, amax = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const float ax = std::fabs(x[i]);
+        if (ax > amax) { amax = ax; max = x[i]; }
+    }
+    if (amax == 0.f) return 0.f;
+    const float iscale = -(float)nmax / max;
+    float sumlx = 0.f, suml2 = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const int32_t li = clamp(nearest_int(iscale * x[i]), -nmax, nmax - 1);
+        l[i] = (int8_t)li;
+        const float w = x[i] * x[i];
+        sumlx += w * x[i] * (float)li;
+        suml2 += w * (float)(li * li);
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int n_changed = 0;
+        for (int i = 0; i < n; ++i) {
+            const float w = x[i] * x[i];
+            float slx = sumlx - w * x[i] * (float)l[i];
+            if (slx > 0.f) {
+                float sl2 = suml2 - w * (float)((int32_t)l[i] * (int32_t)l[i]);
+                const int32_t new_l = clamp(nearest_int(x[i] * sl2 / slx), -nmax, nmax - 1);
+                if (new_l != (int32_t)l[i]) {
+                    slx += w * x[i] * (float)new_l;
+                    sl2 += w * (float)(new_l * new_l);
+                    if (sl2 > 0.f && slx * slx * suml2 > sumlx * sumlx * sl2) {
+                        l[i] = (int8_t)new_l;
+                        sumlx = slx; suml2 = sl2;
+                        ++n_changed;
+                    }
+                }
+            }
+        }
+        if (!n_changed) break;
+    }
+    return sumlx / suml2;
+}
+
+// 6-bit scale j of a Q3K block minus 32 (k_quants.rs:1227-1233)
+inline int q3k_scale(const uint8_t *sc12, int j) {
+    const int lo = j < 8 ? (sc12[j] & 0xF) : (sc12[j - 8] >> 4);
+    return (lo | (((sc12[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32;
+}
+
+// ---- Q3K (k_quants.rs:1190-1268): 32 bytes of third bits, 64 bytes of 2-bit codes, 12 bytes of 6-bit scales, f16 d ----
+void quantize_q3_k(const float *x, uint8_t *out, int64_t elems) {
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256;
+        uint8_t *b = out + ib * 110, *hmask = b, *qs = b + 32, *sc12 = b + 96;
+        float scales[16];
+        for (int j = 0; j < 16; ++j) scales[j] = make_q3(xb + 16 * j, 16, 4);
+        float max_scale = 0.f;
+        for (int j = 0; j < 16; ++j)
+            if (std::fabs(scales[j]) > std::fabs(max_scale)) max_scale = scales[j];
+        std::memset(sc12, 0, 12);
+        uint16_t d16 = f16_bits(0.f);
+        if (max_scale != 0.f) {
+            const float iscale = -32.0f / max_scale;
+            for (int j = 0; j < 16; ++j) {
+                int32_t lv = clamp(nearest_int(iscale * scales[j]), -32, 31) + 32;
+                if (j < 8) sc12[j] = (uint8_t)(lv & 0xF);
+                else sc12[j - 8] |= (uint8_t)((lv & 0xF) << 4);
+                lv >>= 4;
+                sc12[j % 4 + 8] |= (uint8_t)(lv << (2 * (j / 4)));
+            }
+            d16 = f16_bits(1.0f / iscale);
+        }
+        put16(b + 108, d16);
+        int8_t L[256] = {};
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_value(d16) * (float)q3k_scale(sc12, j);
+            if (d != 0.f)
+                for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (int8_t)(clamp(nearest_int(xb[16 * j + ii] / d), -4, 3) + 4);
+        }
+        std::memset(hmask, 0, 32);
+        for (int e = 0; e < 256; ++e)          // element e: bit e / 32 of byte e % 32
+            if (L[e] > 3) { hmask[e % 32] |= (uint8_t)(1u << (e / 32)); L[e] -= 4; }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; ++l)
+                qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+// ---- Q5K (k_quants.rs:1804-1877): as Q4K with 31 levels; 32 bytes of fifth bits between the scales and the nibbles ----
+void quantize_q5_k(const float *x, uint8_t *out, int64_t elems) {
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256;
+        uint8_t *b = out + ib * 176, *sc12 = b + 4, *qh = b + 16, *qs = b + 48;
+        float mins[8], scales[8];
+        for (int j = 0; j < 8; ++j) make_qkx1(31, 5, xb + 32 * j, 32, scales[j], mins[j]);
+        float max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 8; ++j) { max_scale = std::fmax(scales[j], max_scale); max_min = std::fmax(mins[j], max_min); }
+        const float inv_scale = max_scale > 0.f ? 63.0f / max_scale : 0.f;
+        const float inv_min = max_min > 0.f ? 63.0f / max_min : 0.f;
+        std::memset(sc12, 0, 12);
+        for (int j = 0; j < 8; ++j) {
+            const uint8_t ls = (uint8_t)clamp(std::min(nearest_int(inv_scale * scales[j]), 63), 0, 255);
+            const uint8_t lm = (uint8_t)clamp(std::min(nearest_int(inv_min * mins[j]), 63), 0, 255);
+            if (j < 4) { sc12[j] = ls; sc12[j + 4] = lm; }
+            else {
+                sc12[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                sc12[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                sc12[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        const uint16_t d16 = f16_bits(max_scale / 63.0f), m16 = f16_bits(max_min / 63.0f);
+        put16(b, d16);
+        put16(b + 2, m16);
+        uint8_t l[256] = {};
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, m;
+            scale_min_k4(j, sc12, sc, m);
+            const float d = f16_value(d16) * (float)sc;
+            if (d == 0.f) continue;
+            const float dm = f16_value(m16) * (float)m;
+            for (int ii = 0; ii < 32; ++ii) l[32 * j + ii] = (uint8_t)clamp(nearest_int((xb[32 * j + ii] + dm) / d), 0, 31);
+        }
+        std::memset(qh, 0, 32);
+        for (int g = 0; g < 4; ++g)            // 64 elements: sub-block 2g in the low nibbles (fifth bit 2g), 2g + 1 in the high
+            for (int j = 0; j < 32; ++j) {
+                const uint8_t l1 = l[64 * g + j], l2 = l[64 * g + j + 32];
+                if (l1 > 15) qh[j] |= (uint8_t)(1u << (2 * g));
+                if (l2 > 15) qh[j] |= (uint8_t)(2u << (2 * g));
+                qs[32 * g + j] = (uint8_t)((l1 & 15) | ((l2 & 15) << 4));
+            }
+    }
+}
+
 }  // namespace
 
 // `elems` f32 values (a whole number of blocks) -> GGUF blocks.  Throws for a format without a host quantizer here.
@@ -276,7 +500,13 @@ void quantize_weights(GgmlDType dtype, const float *x, int64_t elems, uint8_t *o
     case GgmlDType::Q8_0: quantize_q8_0(x, out, elems); break;
     case GgmlDType::Q4K: quantize_q4_k(x, out, elems); break;
     case GgmlDType::Q6K: quantize_q6_k(x, out, elems); break;
-    default: throw Error(std::string("weight-side quantization to ") + dtype_name(dtype) + " is not built (Q4_0, Q8_0, Q4K, Q6K are)");
+    case GgmlDType::Q4_1: quantize_q_1<4>(x, out, elems); break;
+    case GgmlDType::Q5_0: quantize_q5_0(x, out, elems); break;
+    case GgmlDType::Q5_1: quantize_q_1<5>(x, out, elems); break;
+    case GgmlDType::Q2K: quantize_q2_k(x, out, elems); break;
+    case GgmlDType::Q3K: quantize_q3_k(x, out, elems); break;
+    case GgmlDType::Q5K: quantize_q5_k(x, out, elems); break;
+    default: throw Error(std::string("weight-side quantization to ") + dtype_name(dtype) + " is not built (the ten GGUF block formats from Q4_0 to Q6K are)");
     }
 }
 

@@ -72,8 +72,8 @@ def set_activation_mode(cpu_exact: bool) -> None:
 
 
 def quantize_blocks(src, dtype: GgmlDType) -> bytes:
-    """f32 values -> GGUF blocks in host memory, with the reference's CPU ``from_float`` arithmetic (k_quants.rs); Q4_0,
-    Q8_0, Q4K, Q6K.  Uses no device.  ``src``: a numpy array or CPU tensor whose last dimension is a multiple of the block
+    """f32 values -> GGUF blocks in host memory, with the reference's CPU ``from_float`` arithmetic (k_quants.rs); the ten
+    GGUF block formats.  Uses no device.  ``src``: a numpy array or CPU tensor whose last dimension is a multiple of the block
     size."""
     dtype = GgmlDType(dtype)
     x = np.ascontiguousarray(src.detach().cpu().numpy() if isinstance(src, torch.Tensor) else src, dtype=np.float32)
@@ -126,7 +126,7 @@ class QTensor:
     @classmethod
     def quantize_onto(cls, src: torch.Tensor, dtype: GgmlDType, device="cuda:0") -> "QTensor":
         """``QTensor::quantize_onto`` (mod.rs:645-671): quantizes a tensor held on the CPU with the reference's CPU
-        ``from_float`` arithmetic and puts the blocks on ``device``.  Built for Q4_0, Q8_0, Q4K and Q6K."""
+        ``from_float`` arithmetic and puts the blocks on ``device``.  Built for the ten GGUF block formats (Q4_0 ... Q6K)."""
         dtype = GgmlDType(dtype)
         if src.device.type != "cpu":
             raise CandleQError("`quantize_onto` expects a `src` to be on the cpu, got cuda.")

@@ -400,7 +400,7 @@ int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int6
                      void **out_handle);
 /* Weight-side quantization: f32 values in HOST memory -> GGUF blocks with candle's CPU `from_float` arithmetic
  * (QTensor::quantize / quantize_onto, candle-core/src/quantized/mod.rs:543-562, 645-671; candle's CUDA storage also
- * quantizes on the CPU and uploads, cuda.rs:704-725).  Formats: Q4_0, Q8_0, Q4K, Q6K.  The last dimension must be a
+ * quantizes on the CPU and uploads, cuda.rs:704-725).  Formats: the ten GGUF block formats, Q4_0 to Q6K.  The last dimension must be a
  * multiple of the block size ("tensor size ([..]) is not divisible by block size N").  cqh_quantize_f32 writes the blocks
  * to host memory and uses no device; cqh_qtensor_quantize_onto uploads them and returns a QTensor handle. */
 int cqh_quantize_f32(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, void *host_out, size_t out_bytes);

@@ -1,6 +1,6 @@
 """Weight-side quantization (`QTensor::quantize` / `quantize_onto`, candle-core/src/quantized/mod.rs:543-562, 645-671).
 
-The library's host quantizer (Q4_0, Q8_0, Q4K, Q6K) must write the bytes candle's CPU `from_float` writes: it is compared
+The library's host quantizer (the ten GGUF block formats) must write the bytes candle's CPU `from_float` writes: it is compared
 with the oracle's restatement of those routines byte for byte, and with the known answers of candle's own tests.
 """
 import numpy as np
@@ -10,7 +10,7 @@ import torch
 from candle_b200 import capi
 from candle_b200.quantized import GgmlDType, QTensor, quantize_blocks
 
-FORMATS = ["Q4_0", "Q8_0", "Q4K", "Q6K"]
+FORMATS = ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2K", "Q3K", "Q4K", "Q5K", "Q6K"]
 
 
 def _inputs(k):
@@ -66,8 +66,11 @@ def test_q4_0_known_answer(lib, oracle):
     assert d[-8:].tolist() == [127.0] * 8
 
 
-@pytest.mark.parametrize("name,probe,tol", [("Q4K", [-0.5, -0.373, -0.25, 0.0, 0.288, 0.498], 0.017),      # quantized_tests.rs:846-891
-                                            ("Q6K", [-0.497, -0.372, -0.25, -0.0, 0.284, 0.5], 0.008)])    # quantized_tests.rs:940-985
+@pytest.mark.parametrize("name,probe,tol", [("Q2K", [-0.499, -0.366, -0.249, 0.0, 0.295, 0.492], 0.1),      # quantized_tests.rs:752-797
+                                            ("Q3K", [-0.493, -0.37, -0.243, -0.0, 0.292, 0.492], 0.03),     # quantized_tests.rs:799-844
+                                            ("Q4K", [-0.5, -0.373, -0.25, 0.0, 0.288, 0.498], 0.017),       # quantized_tests.rs:846-891
+                                            ("Q5K", [-0.5, -0.373, -0.25, 0.0, 0.279, 0.499], 0.009),       # quantized_tests.rs:893-938
+                                            ("Q6K", [-0.497, -0.372, -0.25, -0.0, 0.284, 0.5], 0.008)])     # quantized_tests.rs:940-985
 def test_k_quant_known_answers(lib, oracle, name, probe, tol):
     v = np.arange(1024, dtype=np.float32)
     src = ((v - np.float32(512.0)) * np.float32(0.5) / np.float32(512.0)).astype(np.float32)
@@ -78,7 +81,8 @@ def test_k_quant_known_answers(lib, oracle, name, probe, tol):
     assert [float(r[i]) for i in (0, 128, 256, 512, 800, 1023)] == [float(np.float32(p)) for p in probe]
 
 
-@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q8_0", 0.002), ("Q4K", 0.002), ("Q6K", 0.002)])
+@pytest.mark.parametrize("name,limit", [("Q4_0", 0.002), ("Q4_1", 0.002), ("Q5_0", 0.002), ("Q5_1", 0.002), ("Q8_0", 0.002),
+                                        ("Q2K", 0.0075), ("Q3K", 0.0040), ("Q4K", 0.002), ("Q5K", 0.002), ("Q6K", 0.002)])
 def test_quantization_rmse(lib, oracle, name, limit):
     """ggml_quantization_error_test, candle-core/tests/quantized_tests.rs:531-552 (limits :14-17)."""
     src = (np.float32(0.1) + np.float32(2.0) * np.cos(np.arange(4096, dtype=np.float32))).astype(np.float32)
@@ -92,8 +96,8 @@ def test_errors(lib):
         quantize_blocks(np.zeros((4, 100), dtype=np.float32), GgmlDType.Q8_0)
     with pytest.raises(capi.CandleQError, match=r"tensor size \(\[2, 128\]\) is not divisible by block size 256"):
         quantize_blocks(np.zeros((2, 128), dtype=np.float32), GgmlDType.Q4K)
-    with pytest.raises(capi.CandleQError, match="weight-side quantization to Q5K is not built"):
-        quantize_blocks(np.zeros((2, 256), dtype=np.float32), GgmlDType.Q5K)
+    with pytest.raises(capi.CandleQError, match="weight-side quantization to Q8K is not built"):
+        quantize_blocks(np.zeros((2, 256), dtype=np.float32), GgmlDType.Q8K)
     with pytest.raises(capi.CandleQError, match="expects a `src` to be on the cpu"):
         QTensor.quantize_onto(torch.zeros(2, 256, device="meta"), GgmlDType.Q4K)
     with pytest.raises(capi.CandleQError, match="CUDA devices only"):
