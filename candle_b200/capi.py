@@ -122,6 +122,8 @@ def lib() -> C.CDLL:
         L.cqh_qtensor_wrap.argtypes = [i32, vp, sz, i64p, i32, i32, C.POINTER(vp)]
         L.cqh_quantize_f32.argtypes = [i32, vp, i64p, i32, vp, sz]
         L.cqh_qtensor_quantize_onto.argtypes = [i32, vp, i64p, i32, i32, C.POINTER(vp)]
+        L.cqh_quantize_imatrix_f32.argtypes = [i32, vp, i64p, i32, vp, C.c_int64, vp, sz]
+        L.cqh_qtensor_quantize_imatrix_onto.argtypes = [i32, vp, i64p, i32, vp, C.c_int64, i32, C.POINTER(vp)]
         L.cqh_qtensor_free.argtypes = [vp]
         L.cqh_qtensor_free.restype = None
         L.cqh_qtensor_data.argtypes = [vp, vp, sz]

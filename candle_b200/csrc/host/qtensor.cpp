@@ -361,6 +361,38 @@ extern "C" int cqh_qtensor_quantize_onto(int ggml_dtype, const float *host_x, co
     });
 }
 
+// The importance-weighted variants (QTensor::quantize_imatrix / quantize_imatrix_onto, mod.rs:564-642).
+static void check_imatrix(const int64_t *dims, int ndims, int64_t imatrix_len) {
+    if (ndims >= 1 && imatrix_len != dims[ndims - 1])
+        throw Error("imatrix weights must have the same length " + std::to_string(imatrix_len) + " as the last dim of src " +
+                    std::to_string(dims[ndims - 1]));
+}
+
+extern "C" int cqh_quantize_imatrix_f32(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, const float *imatrix,
+                                        int64_t imatrix_len, void *host_out, size_t out_bytes) {
+    return guarded([&] {
+        const GgmlDType dt = ggml_dtype_from_u32((uint32_t)ggml_dtype);
+        check_imatrix(dims, ndims, imatrix_len);
+        int64_t elems = 0;
+        const size_t need = quantized_bytes(dt, dims, ndims, &elems);
+        if (need != out_bytes) throw Error("quantize: the output holds " + std::to_string(out_bytes) + " bytes, the blocks take " + std::to_string(need));
+        quantize_weights_imatrix(dt, host_x, elems, imatrix, imatrix_len, (uint8_t *)host_out);
+    });
+}
+
+extern "C" int cqh_qtensor_quantize_imatrix_onto(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims,
+                                                 const float *imatrix, int64_t imatrix_len, int device, void **out_handle) {
+    return guarded([&] {
+        const GgmlDType dt = ggml_dtype_from_u32((uint32_t)ggml_dtype);
+        check_imatrix(dims, ndims, imatrix_len);
+        int64_t elems = 0;
+        std::vector<uint8_t> blocks(quantized_bytes(dt, dims, ndims, &elems));
+        quantize_weights_imatrix(dt, host_x, elems, imatrix, imatrix_len, blocks.data());
+        auto st = QCudaStorage::load_quantized(device, dt, blocks.data(), blocks.size());
+        *out_handle = new std::shared_ptr<QTensor>(new QTensor(std::move(st), std::vector<int64_t>(dims, dims + ndims)));
+    });
+}
+
 extern "C" int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int64_t *dims, int ndims,
                                 int device, void **out_handle) {
     return guarded([&] {

@@ -32,6 +32,9 @@ bool kernels_support(GgmlDType t);              // the four formats this library
 // f32 values (a whole number of blocks) -> GGUF blocks on the host, with candle's CPU `from_float` arithmetic
 // (k_quants.rs); the ten GGUF block formats Q4_0 ... Q6K.  Throws Error for another format.
 void quantize_weights(GgmlDType dtype, const float *x, int64_t elems, uint8_t *out);
+// The importance-weighted variant (`from_float_imatrix`, k_quants.rs): one importance value per column of a matrix row of
+// `n_per_row` elements; Q2K, Q3K, Q4K, Q5K, Q6K.
+void quantize_weights_imatrix(GgmlDType dtype, const float *x, int64_t elems, const float *imatrix, int64_t n_per_row, uint8_t *out);
 
 enum class DType : int { F32 = 0, F16 = 1, BF16 = 2 };
 inline size_t dtype_size(DType d) { return d == DType::F32 ? 4 : 2; }

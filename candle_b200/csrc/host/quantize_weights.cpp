@@ -30,6 +30,11 @@ inline int32_t to_i32(float v) {
 inline int32_t nearest_int(float v) { return to_i32(std::round(v)); }        // utils.rs:1-3 (round half away from zero)
 inline int32_t clamp(int32_t v, int32_t lo, int32_t hi) { return v < lo ? lo : (v > hi ? hi : v); }
 inline uint16_t f16_bits(float f) {
+    if (f != f) {       // half::f16::from_f32 keeps a NaN's sign and top payload bits and sets the quiet bit
+        uint32_t u;
+        std::memcpy(&u, &f, 4);
+        return (uint16_t)(((u >> 16) & 0x8000u) | 0x7E00u | ((u & 0x007FFFFFu) >> 13));
+    }
     const __half h = __float2half_rn(f);
     uint16_t b;
     std::memcpy(&b, &h, 2);
@@ -491,6 +496,355 @@ void quantize_q5_k(const float *x, uint8_t *out, int64_t elems) {
     }
 }
 
+// ===== importance-weighted quantization (`from_float_imatrix`) for the five K formats =====================================
+// Per 256-block the reference builds element weights from the importance row (the block's position inside its matrix row)
+// and searches scales that minimise the WEIGHTED error; codes are then placed exactly as in the plain quantizers.
+
+inline float sum_of_squares(const float *x, int n) {
+    float s = -0.0f;                        // Rust's f32 iterator sum starts from -0.0
+    for (int i = 0; i < n; ++i) s += x[i] * x[i];
+    return s;
+}
+
+// make_qkx3_quants(nmax, x[n], Some(weights), rmin, rdelta, nstep, use_mad = false) -> (scale, -min), utils.rs:356-466:
+// a grid of candidate scales; for each the least-squares (scale, min) of the resulting codes, keeping the smallest weighted error.
+void make_qkx3(int nmax, const float *x, const float *w, int n, float rmin, float rdelta, int nstep, float &out_scale,
+               float &out_min) {
+    uint8_t aux[32];
+    float lo = x[0], hi = x[0];
+    float sum_w = w[0], sum_x = sum_w * x[0];
+    for (int i = 1; i < n; ++i) {
+        if (x[i] < lo) lo = x[i];
+        if (x[i] > hi) hi = x[i];
+        sum_w += w[i];
+        sum_x += w[i] * x[i];
+    }
+    if (lo > 0.f) lo = 0.f;
+    if (hi <= lo) { out_scale = 0.f; out_min = -lo; return; }
+    float iscale = (float)nmax / (hi - lo);
+    float scale = 1.0f / iscale;
+    float best = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const int32_t l = clamp(nearest_int(iscale * (x[i] - lo)), 0, nmax);
+        const float diff = scale * (float)l + lo - x[i];
+        best += w[i] * (diff * diff);
+    }
+    for (int is = 0; is <= nstep && nstep >= 1; ++is) {
+        iscale = (rmin + rdelta * (float)is + (float)nmax) / (hi - lo);
+        float sum_l = 0.f, sum_l2 = 0.f, sum_xl = 0.f;
+        for (int i = 0; i < n; ++i) {
+            const int32_t l = clamp(nearest_int(iscale * (x[i] - lo)), 0, nmax);
+            aux[i] = (uint8_t)l;
+            const float lf = (float)l;
+            sum_l += w[i] * lf;
+            sum_l2 += w[i] * (lf * lf);
+            sum_xl += w[i] * lf * x[i];
+        }
+        const float det = sum_w * sum_l2 - sum_l * sum_l;
+        if (!(det > 0.f)) continue;
+        float this_scale = (sum_w * sum_xl - sum_x * sum_l) / det;
+        float this_min = (sum_l2 * sum_x - sum_l * sum_xl) / det;
+        if (this_min > 0.f) { this_min = 0.f; this_scale = sum_xl / sum_l2; }
+        float err = 0.f;
+        for (int i = 0; i < n; ++i) {
+            const float diff = this_scale * (float)aux[i] + this_min - x[i];
+            err += w[i] * (diff * diff);
+        }
+        if (err < best) { best = err; scale = this_scale; lo = this_min; }       // later candidates start from the new minimum
+    }
+    out_scale = scale;
+    out_min = -lo;
+}
+
+// make_qp_quants(n, nmax, x[n] >= 0, codes, weights) -> scale, utils.rs:470-562: the per-block super scale of the sub-block
+// scales (or mins), codes 0..nmax.
+float make_qp(int n, int nmax, const float *x, uint8_t *l, const float *w) {
+    float max = 0.f;
+    for (int i = 0; i < n; ++i) max = x[i] > max ? x[i] : max;      // fold(0.0, f32::max)
+    if (max == 0.f) {
+        for (int i = 0; i < n; ++i) l[i] = 0;
+        return 0.f;
+    }
+    float iscale = (float)nmax / max;
+    for (int i = 0; i < n; ++i) l[i] = (uint8_t)nearest_int(iscale * x[i]);      // i32 -> u8 keeps the low byte
+    const float scale = 1.0f / iscale;
+    float best = -0.0f;
+    for (int i = 0; i < n; ++i) {
+        const float diff = x[i] - scale * (float)l[i];
+        best += w[i] * diff * diff;
+    }
+    for (int is = -4; is <= 4; ++is) {
+        if (is == 0) continue;
+        const float iscale_is = (0.1f * (float)is + (float)nmax) / max;
+        const float scale_is = 1.0f / iscale_is;
+        float mse = -0.0f;
+        for (int i = 0; i < n; ++i) {
+            uint8_t li = (uint8_t)nearest_int(iscale_is * x[i]);
+            li = li < nmax ? li : (uint8_t)nmax;
+            const float diff = x[i] - scale_is * (float)li;
+            mse += w[i] * diff * diff;
+        }
+        if (mse < best) { best = mse; iscale = iscale_is; }
+    }
+    float sumlx = 0.f, suml2 = 0.f;
+    for (int i = 0; i < n; ++i) {
+        uint8_t li = to_u8(std::round(iscale * x[i]));                            // f32 -> u8 saturates
+        li = li < nmax ? li : (uint8_t)nmax;
+        l[i] = li;
+        sumlx += w[i] * x[i] * (float)li;
+        suml2 += w[i] * ((float)li * (float)li);
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int n_changed = 0;
+        for (int i = 0; i < n; ++i) {
+            float slx = sumlx - w[i] * x[i] * (float)l[i];
+            float sl2 = suml2 - w[i] * ((float)l[i] * (float)l[i]);
+            if (slx > 0.f && sl2 > 0.f) {
+                uint8_t nl = (uint8_t)nearest_int(x[i] * sl2 / slx);
+                nl = nl < nmax ? nl : (uint8_t)nmax;
+                if (nl != l[i]) {
+                    slx += w[i] * x[i] * (float)nl;
+                    sl2 += w[i] * ((float)nl * (float)nl);
+                    if (slx * slx * suml2 > sumlx * sumlx * sl2) {
+                        l[i] = nl;
+                        sumlx = slx; suml2 = sl2;
+                        ++n_changed;
+                    }
+                }
+            }
+        }
+        if (!n_changed) break;
+    }
+    return sumlx / suml2;
+}
+
+// make_qx_quants(n, nmax, x, codes, rmse_type = 1, weights), utils.rs:62-185 with a weight per element
+float make_qx_weighted(int n, int nmax, const float *x, int8_t *ls, const float *qw) {
+    float max = 0.f, amax = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const float ax = std::fabs(x[i]);
+        if (ax > amax) { amax = ax; max = x[i]; }
+    }
+    if (amax == 0.f) {
+        for (int i = 0; i < n; ++i) ls[i] = 0;
+        return 0.f;
+    }
+    const float iscale = -(float)nmax / max;
+    float sumlx = 0.f, suml2 = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const int32_t l = clamp(nearest_int(iscale * x[i]), -nmax, nmax - 1);
+        ls[i] = (int8_t)(l + nmax);
+        const float lf = (float)l;
+        sumlx += qw[i] * x[i] * lf;
+        suml2 += qw[i] * lf * lf;
+    }
+    float scale = sumlx / suml2;
+    float best = scale * sumlx;
+    for (int itry = 0; itry < 3; ++itry) {
+        const float is = 1.0f / scale;
+        float slx = 0.f, sl2 = 0.f;
+        bool changed = false;
+        for (int i = 0; i < n; ++i) {
+            const int32_t l = clamp(nearest_int(is * x[i]), -nmax, nmax - 1);
+            if (l + nmax != (int32_t)ls[i]) changed = true;
+            const float lf = (float)l;
+            slx += qw[i] * x[i] * lf;
+            sl2 += qw[i] * lf * lf;
+        }
+        if (!changed || sl2 == 0.f || slx * slx <= best * sl2) break;
+        for (int i = 0; i < n; ++i) ls[i] = (int8_t)(nmax + clamp(nearest_int(is * x[i]), -nmax, nmax - 1));
+        sumlx = slx; suml2 = sl2;
+        scale = sumlx / suml2;
+        best = scale * sumlx;
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int n_changed = 0;
+        for (int i = 0; i < n; ++i) {
+            const int32_t l = (int32_t)ls[i] - nmax;
+            float slx = sumlx - qw[i] * x[i] * (float)l;
+            if (slx > 0.f) {
+                float sl2 = suml2 - qw[i] * (float)l * (float)l;
+                const int32_t new_l = clamp(nearest_int(x[i] * sl2 / slx), -nmax, nmax - 1);
+                if (new_l != l) {
+                    slx += qw[i] * x[i] * (float)new_l;
+                    sl2 += qw[i] * (float)new_l * (float)new_l;
+                    if (sl2 > 0.f && slx * slx * suml2 > sumlx * sumlx * sl2) {
+                        ls[i] = (int8_t)(nmax + new_l);
+                        sumlx = slx; suml2 = sl2;
+                        scale = sumlx / suml2;
+                        best = scale * sumlx;
+                        ++n_changed;
+                    }
+                }
+            }
+        }
+        if (!n_changed) break;
+    }
+    return scale;
+}
+
+// Element weights of one sub-block: importance * sqrt(sigma2 + x^2); returns their sum.
+inline float element_weights(const float *x, const float *imp, int n, float sigma2, float *w) {
+    for (int l = 0; l < n; ++l) w[l] = imp[l] * std::sqrt(sigma2 + x[l] * x[l]);
+    float s = -0.0f;
+    for (int l = 0; l < n; ++l) s += w[l];
+    return s;
+}
+
+// Q4K (k_quants.rs:1602-1664) and Q5K (:1879-1957) with importance weights; BITS = 4 or 5.
+template <int BITS> void quantize_q45_k_imatrix(const float *x, uint8_t *out, int64_t elems, const float *imatrix, int64_t n_per_row) {
+    constexpr int kLevels = (1 << BITS) - 1, kBytes = BITS == 4 ? 144 : 176;
+    const int64_t blocks_per_row = n_per_row / 256;
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256, *imp = imatrix + (ib % blocks_per_row) * 256;
+        uint8_t *b = out + ib * kBytes, *sc12 = b + 4, *qh = b + 16, *qs = b + kBytes - 128;
+        float mins[8], scales[8], sw[8], w[32];
+        uint8_t ls[8] = {}, lm[8] = {};
+        const float sigma2 = 2.0f * sum_of_squares(xb, 256) / 256.0f;
+        for (int j = 0; j < 8; ++j) {
+            sw[j] = element_weights(xb + 32 * j, imp + 32 * j, 32, sigma2, w);
+            make_qkx3(kLevels, xb + 32 * j, w, 32, -0.9f, 0.05f, 36, scales[j], mins[j]);
+        }
+        const float d_block = make_qp(8, 63, scales, ls, sw);
+        const float m_block = make_qp(8, 63, mins, lm, sw);
+        std::memset(sc12, 0, 12);
+        for (int j = 0; j < 8; ++j) {
+            const uint8_t a = ls[j] < 63 ? ls[j] : 63, c = lm[j] < 63 ? lm[j] : 63;
+            if (j < 4) { sc12[j] = a; sc12[j + 4] = c; }
+            else {
+                sc12[j + 4] = (uint8_t)((a & 0xF) | ((c & 0xF) << 4));
+                sc12[j - 4] |= (uint8_t)((a >> 4) << 6);
+                sc12[j] |= (uint8_t)((c >> 4) << 6);
+            }
+        }
+        const uint16_t d16 = f16_bits(d_block), m16 = f16_bits(m_block);
+        put16(b, d16);
+        put16(b + 2, m16);
+        uint8_t l[256] = {};
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, m;
+            scale_min_k4(j, sc12, sc, m);
+            const float d = f16_value(d16) * (float)sc;
+            if (d == 0.f) continue;
+            const float dm = f16_value(m16) * (float)m;
+            for (int ii = 0; ii < 32; ++ii) l[32 * j + ii] = (uint8_t)clamp(nearest_int((xb[32 * j + ii] + dm) / d), 0, kLevels);
+        }
+        if (BITS == 5) std::memset(qh, 0, 32);
+        for (int g = 0; g < 4; ++g)
+            for (int j = 0; j < 32; ++j) {
+                const uint8_t l1 = l[64 * g + j], l2 = l[64 * g + j + 32];
+                if (BITS == 5) {
+                    if (l1 > 15) qh[j] |= (uint8_t)(1u << (2 * g));
+                    if (l2 > 15) qh[j] |= (uint8_t)(2u << (2 * g));
+                }
+                qs[32 * g + j] = (uint8_t)((l1 & 15) | ((l2 & 15) << 4));
+            }
+    }
+}
+
+// Q2K with importance weights (k_quants.rs:955-1011)
+void quantize_q2_k_imatrix(const float *x, uint8_t *out, int64_t elems, const float *imatrix, int64_t n_per_row) {
+    const int64_t blocks_per_row = n_per_row / 256;
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256, *imp = imatrix + (ib % blocks_per_row) * 256;
+        uint8_t *b = out + ib * 84, *sc = b, *qs = b + 16;
+        float mins[16], scales[16], sw[16], w[16];
+        uint8_t ls[16] = {}, lm[16] = {};
+        const float sigma2 = sum_of_squares(xb, 256) / 256.0f;
+        for (int j = 0; j < 16; ++j) {
+            sw[j] = element_weights(xb + 16 * j, imp + 16 * j, 16, sigma2, w);
+            make_qkx3(3, xb + 16 * j, w, 16, -0.9f, 0.05f, 36, scales[j], mins[j]);
+        }
+        const uint16_t d16 = f16_bits(make_qp(16, 15, scales, ls, sw));
+        const uint16_t m16 = f16_bits(make_qp(16, 15, mins, lm, sw));
+        put16(b + 80, d16);
+        put16(b + 82, m16);
+        for (int j = 0; j < 16; ++j) sc[j] = (uint8_t)(ls[j] | (lm[j] << 4));
+        uint8_t L[256] = {};
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_value(d16) * (float)(sc[j] & 0xF);
+            if (d == 0.f) continue;
+            const float dm = f16_value(m16) * (float)(sc[j] >> 4);
+            for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (uint8_t)clamp(nearest_int((xb[16 * j + ii] + dm) / d), 0, 3);
+        }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; ++l)
+                qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+// Q3K with importance weights (k_quants.rs:1271-1366)
+void quantize_q3_k_imatrix(const float *x, uint8_t *out, int64_t elems, const float *imatrix, int64_t n_per_row) {
+    const int64_t blocks_per_row = n_per_row / 256;
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256, *imp = imatrix + (ib % blocks_per_row) * 256;
+        uint8_t *b = out + ib * 110, *hmask = b, *qs = b + 32, *sc12 = b + 96;
+        float scales[16], sw[16], w[16];
+        int8_t ls[16] = {}, L[256] = {};
+        const float sigma2 = 2.0f * sum_of_squares(xb, 256) / 256.0f;
+        for (int j = 0; j < 16; ++j) {
+            sw[j] = element_weights(xb + 16 * j, imp + 16 * j, 16, sigma2, w);
+            scales[j] = make_qx_weighted(16, 4, xb + 16 * j, L + 16 * j, w);
+        }
+        std::memset(sc12, 0, 12);
+        const uint16_t d16 = f16_bits(make_qx_weighted(16, 32, scales, ls, sw));
+        put16(b + 108, d16);
+        for (int j = 0; j < 16; ++j) {
+            const int8_t lv = ls[j];
+            if (j < 8) sc12[j] = (uint8_t)(lv & 0xF);
+            else sc12[j - 8] |= (uint8_t)((lv & 0xF) << 4);
+            sc12[j % 4 + 8] |= (uint8_t)((int8_t)(lv >> 4) << (2 * (j / 4)));
+        }
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_value(d16) * (float)q3k_scale(sc12, j);
+            if (d != 0.f)
+                for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (int8_t)(clamp(nearest_int(xb[16 * j + ii] / d), -4, 3) + 4);
+        }
+        std::memset(hmask, 0, 32);
+        for (int e = 0; e < 256; ++e)
+            if (L[e] > 3) { hmask[e % 32] |= (uint8_t)(1u << (e / 32)); L[e] -= 4; }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; ++l)
+                qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+// Q6K with importance weights (k_quants.rs:2166-2243): the importance values themselves weigh the elements
+void quantize_q6_k_imatrix(const float *x, uint8_t *out, int64_t elems, const float *imatrix, int64_t n_per_row) {
+    const int64_t blocks_per_row = n_per_row / 256;
+    int8_t L[256] = {};
+    float scales[16];
+    for (int64_t ib = 0; ib < elems / 256; ++ib) {
+        const float *xb = x + ib * 256, *imp = imatrix + (ib % blocks_per_row) * 256;
+        uint8_t *b = out + ib * 210;
+        int8_t *sc = reinterpret_cast<int8_t *>(b + 192);
+        float max_scale = 0.f, max_abs = 0.f;
+        for (int j = 0; j < 16; ++j) {
+            const float s = make_qx_weighted(16, 32, xb + 16 * j, L + 16 * j, imp + 16 * j);
+            scales[j] = s;
+            if (std::fabs(s) > max_abs) { max_abs = std::fabs(s); max_scale = s; }
+        }
+        const float iscale = -128.0f / max_scale;
+        const uint16_t d16 = f16_bits(1.0f / iscale);
+        put16(b + 208, d16);
+        for (int j = 0; j < 16; ++j) sc[j] = (int8_t)std::min(nearest_int(iscale * scales[j]), 127);     // i32 -> i8 keeps the low byte
+        for (int j = 0; j < 16; ++j) {
+            const float d = f16_value(d16) * (float)sc[j];
+            if (d == 0.f) continue;
+            for (int ii = 0; ii < 16; ++ii) L[16 * j + ii] = (int8_t)(clamp(nearest_int(xb[16 * j + ii] / d), -32, 31) + 32);
+        }
+        for (int j = 0; j < 256; j += 128) {
+            uint8_t *ql = b + j / 2, *qh = b + 128 + j / 4;
+            for (int t = 0; t < 32; ++t) {
+                const int8_t a0 = L[j + t], a1 = L[j + t + 32], a2 = L[j + t + 64], a3 = L[j + t + 96];
+                ql[t] = (uint8_t)((a0 & 0xF) | ((a2 & 0xF) << 4));
+                ql[t + 32] = (uint8_t)((a1 & 0xF) | ((a3 & 0xF) << 4));
+                qh[t] = (uint8_t)((a0 >> 4) | ((a1 >> 4) << 2) | ((a2 >> 4) << 4) | ((a3 >> 4) << 6));
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // `elems` f32 values (a whole number of blocks) -> GGUF blocks.  Throws for a format without a host quantizer here.
@@ -507,6 +861,20 @@ void quantize_weights(GgmlDType dtype, const float *x, int64_t elems, uint8_t *o
     case GgmlDType::Q3K: quantize_q3_k(x, out, elems); break;
     case GgmlDType::Q5K: quantize_q5_k(x, out, elems); break;
     default: throw Error(std::string("weight-side quantization to ") + dtype_name(dtype) + " is not built (the ten GGUF block formats from Q4_0 to Q6K are)");
+    }
+}
+
+// As quantize_weights, with one importance value per column of the matrix row (`from_float_imatrix`); `n_per_row` = the
+// last dimension = the number of importance values.  The five K formats; the reference panics for the others
+// (k_quants.rs:34-43).
+void quantize_weights_imatrix(GgmlDType dtype, const float *x, int64_t elems, const float *imatrix, int64_t n_per_row, uint8_t *out) {
+    switch (dtype) {
+    case GgmlDType::Q2K: quantize_q2_k_imatrix(x, out, elems, imatrix, n_per_row); break;
+    case GgmlDType::Q3K: quantize_q3_k_imatrix(x, out, elems, imatrix, n_per_row); break;
+    case GgmlDType::Q4K: quantize_q45_k_imatrix<4>(x, out, elems, imatrix, n_per_row); break;
+    case GgmlDType::Q5K: quantize_q45_k_imatrix<5>(x, out, elems, imatrix, n_per_row); break;
+    case GgmlDType::Q6K: quantize_q6_k_imatrix(x, out, elems, imatrix, n_per_row); break;
+    default: throw Error(std::string("`from_float_imatrix` is unimplemented for ") + dtype_name(dtype));
     }
 }
 

@@ -71,16 +71,22 @@ def set_activation_mode(cpu_exact: bool) -> None:
     capi.lib().cqh_set_act_mode(1 if cpu_exact else 0)
 
 
-def quantize_blocks(src, dtype: GgmlDType) -> bytes:
+def quantize_blocks(src, dtype: GgmlDType, imatrix=None) -> bytes:
     """f32 values -> GGUF blocks in host memory, with the reference's CPU ``from_float`` arithmetic (k_quants.rs); the ten
     GGUF block formats.  Uses no device.  ``src``: a numpy array or CPU tensor whose last dimension is a multiple of the block
-    size."""
+    size.  With ``imatrix`` (one importance value per element of the last dimension) the importance-weighted
+    ``from_float_imatrix`` runs instead (Q2K, Q3K, Q4K, Q5K, Q6K)."""
     dtype = GgmlDType(dtype)
     x = np.ascontiguousarray(src.detach().cpu().numpy() if isinstance(src, torch.Tensor) else src, dtype=np.float32)
     dims, nd = _dims(x.shape)
     out = np.empty(x.size // dtype.block_size() * dtype.type_size() if x.ndim and x.shape[-1] % dtype.block_size() == 0 else 0,
                    dtype=np.uint8)
-    capi.hcheck(capi.lib().cqh_quantize_f32(int(dtype), x.ctypes.data, dims, nd, out.ctypes.data, out.size), "quantize_blocks")
+    if imatrix is None:
+        capi.hcheck(capi.lib().cqh_quantize_f32(int(dtype), x.ctypes.data, dims, nd, out.ctypes.data, out.size), "quantize_blocks")
+    else:
+        im = np.ascontiguousarray(imatrix, dtype=np.float32).reshape(-1)
+        capi.hcheck(capi.lib().cqh_quantize_imatrix_f32(int(dtype), x.ctypes.data, dims, nd, im.ctypes.data, im.size,
+                                                         out.ctypes.data, out.size), "quantize_blocks")
     return out.tobytes()
 
 
@@ -137,6 +143,30 @@ class QTensor:
         capi.hcheck(capi.lib().cqh_qtensor_quantize_onto(int(dtype), x.data_ptr(), dims, nd, device.index or 0, C.byref(h)),
                     "QTensor.quantize_onto")
         return cls(h.value, dtype, tuple(x.shape), device)
+
+    @classmethod
+    def quantize_imatrix_onto(cls, src: torch.Tensor, imatrix_weights, dtype: GgmlDType, device="cuda:0") -> "QTensor":
+        """``QTensor::quantize_imatrix_onto`` (mod.rs:601-642): as ``quantize_onto`` with one importance value per element of
+        the last dimension (``from_float_imatrix``; Q2K, Q3K, Q4K, Q5K, Q6K)."""
+        dtype = GgmlDType(dtype)
+        if src.device.type != "cpu":
+            raise CandleQError("`quantize_onto` expects a `src` to be on the cpu, got cuda.")
+        device = torch.device(device)
+        x = src.detach().to(torch.float32).contiguous()
+        im = np.ascontiguousarray(imatrix_weights, dtype=np.float32).reshape(-1)
+        dims, nd = _dims(tuple(x.shape))
+        h = C.c_void_p()
+        capi.hcheck(capi.lib().cqh_qtensor_quantize_imatrix_onto(int(dtype), x.data_ptr(), dims, nd, im.ctypes.data, im.size,
+                                                                  device.index or 0, C.byref(h)), "QTensor.quantize_imatrix_onto")
+        return cls(h.value, dtype, tuple(x.shape), device)
+
+    @classmethod
+    def quantize_imatrix(cls, src: torch.Tensor, imatrix_weights, dtype: GgmlDType) -> "QTensor":
+        """``QTensor::quantize_imatrix`` (mod.rs:564-598); the result lives on ``src``'s CUDA device."""
+        if not src.is_cuda:
+            raise CandleQError("QTensor.quantize_imatrix: this library holds quantized tensors on CUDA devices only; "
+                               "use quantize_imatrix_onto(src, imatrix, dtype, device) for a tensor on the cpu")
+        return cls.quantize_imatrix_onto(src.detach().to("cpu", torch.float32), imatrix_weights, dtype, src.device)
 
     @classmethod
     def quantize(cls, src: torch.Tensor, dtype: GgmlDType) -> "QTensor":

@@ -406,6 +406,13 @@ int cqh_qtensor_wrap(int ggml_dtype, void *device_ptr, size_t nbytes, const int6
 int cqh_quantize_f32(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, void *host_out, size_t out_bytes);
 int cqh_qtensor_quantize_onto(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, int device,
                               void **out_handle);
+/* The importance-weighted variants (QTensor::quantize_imatrix / quantize_imatrix_onto, mod.rs:564-642; `from_float_imatrix`
+ * of Q2K, Q3K, Q4K, Q5K, Q6K in k_quants.rs): `imatrix` holds one importance value per element of the last dimension
+ * ("imatrix weights must have the same length L as the last dim of src N" otherwise). */
+int cqh_quantize_imatrix_f32(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, const float *imatrix,
+                             int64_t imatrix_len, void *host_out, size_t out_bytes);
+int cqh_qtensor_quantize_imatrix_onto(int ggml_dtype, const float *host_x, const int64_t *dims, int ndims, const float *imatrix,
+                                      int64_t imatrix_len, int device, void **out_handle);
 void cqh_qtensor_free(void *handle);
 int cqh_qtensor_data(void *handle, void *host_out, size_t nbytes);
 const void *cqh_qtensor_device_ptr(void *handle);
